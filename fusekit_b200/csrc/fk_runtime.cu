@@ -1,0 +1,570 @@
+// libfusekit_cuda.so -- host runtime behind include/fusekit_cuda.h: handle table, device memory,
+// weight objects, eager launches, CUDA-graph capture/replay of the per-token task list, decode
+// chunk loops and the NCCL hook for tensor parallelism.  No PyTorch, no CPU fallback.
+#include "../../include/fusekit_cuda.h"
+#include "fk_common.cuh"
+#include "fk_kernels.cuh"
+#include "fk_synth.cuh"
+
+#include <dlfcn.h>
+#include <math.h>
+#include <mutex>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+#include <string>
+#include <vector>
+
+// ------------------------------------------------------------------ errors
+static thread_local char g_err[512] = "";
+static fk_status fail(fk_status code, const char *fmt, ...) {
+    va_list ap; va_start(ap, fmt); vsnprintf(g_err, sizeof g_err, fmt, ap); va_end(ap);
+    return code;
+}
+#define CU(call)                                                                                   \
+    do {                                                                                           \
+        cudaError_t e_ = (call);                                                                   \
+        if (e_ != cudaSuccess) return fail(FK_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+
+// ------------------------------------------------------------------ NCCL (loaded on demand)
+typedef struct ncclComm *ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+struct Nccl {
+    void *dl = nullptr;
+    int (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    int (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*CommDestroy)(ncclComm_t) = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+};
+static Nccl g_nccl;
+static fk_status nccl_load() {
+    if (g_nccl.dl) return FK_OK;
+    const char *names[] = {getenv("FK_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) { if (n && (g_nccl.dl = dlopen(n, RTLD_NOW | RTLD_GLOBAL))) break; }
+    if (!g_nccl.dl) return fail(FK_ERR_NCCL, "cannot load libnccl.so.2 (set FK_NCCL_LIB): %s", dlerror());
+    g_nccl.GetUniqueId = (int (*)(ncclUniqueId *))dlsym(g_nccl.dl, "ncclGetUniqueId");
+    g_nccl.CommInitRank = (int (*)(ncclComm_t *, int, ncclUniqueId, int))dlsym(g_nccl.dl, "ncclCommInitRank");
+    g_nccl.AllReduce = (int (*)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t))dlsym(g_nccl.dl, "ncclAllReduce");
+    g_nccl.CommDestroy = (int (*)(ncclComm_t))dlsym(g_nccl.dl, "ncclCommDestroy");
+    g_nccl.GetErrorString = (const char *(*)(int))dlsym(g_nccl.dl, "ncclGetErrorString");
+    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce) return fail(FK_ERR_NCCL, "libnccl lacks required symbols");
+    return FK_OK;
+}
+
+// ------------------------------------------------------------------ objects
+struct Weight {
+    long long n = 0, k = 0; int bits = 0; bool finalized = false;
+    uint32_t *w = nullptr; uint16_t *s = nullptr, *b = nullptr;
+    size_t w_bytes = 0, sb_bytes = 0;
+    WView view() const { WView v; v.w = w; v.s = s; v.b = b; v.n = n; v.k = k; v.bits = bits; return v; }
+};
+struct Graph {
+    std::vector<fk_task> tasks;
+    cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
+};
+struct Ctx {
+    int device = 0; bool open = false;
+    cudaStream_t stream = nullptr; cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    FkState *state = nullptr; uint32_t *history = nullptr; uint32_t hist_cap = 0;
+    uint32_t *pinned = nullptr;                 // host staging for state / history
+    std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
+    bool pending = false; bool pdl = true; int sm_count = 148;
+    ncclComm_t comm = nullptr; int rank = 0, world = 1;
+    long long launches = 0;
+};
+static std::mutex g_mu;
+static std::vector<Ctx *> g_ctx;
+#define FK_HIST_CAP 8192
+
+static Ctx *get(fk_handle h) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (h == 0 || h > g_ctx.size() || !g_ctx[h - 1]->open) return nullptr;
+    return g_ctx[h - 1];
+}
+#define CTX(h)                                                          \
+    Ctx *c = get(h);                                                    \
+    if (!c) return fail(FK_ERR_VALUE, "invalid handle %llu", (unsigned long long)(h)); \
+    CU(cudaSetDevice(c->device))
+
+template <typename K> static cudaError_t big_smem(K kern) {
+    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+}
+
+extern "C" const char *fk_last_error(void) { return g_err; }
+extern "C" const char *fk_version(void) { return "fusekit-b200 0.1 (sm_100a)"; }
+
+extern "C" fk_status fk_open(int device, fk_handle *out) {
+    if (!out) return fail(FK_ERR_VALUE, "out is null");
+    int ndev = 0; CU(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev) return fail(FK_ERR_VALUE, "device %d out of range (%d visible)", device, ndev);
+    CU(cudaSetDevice(device));
+    cudaDeviceProp prop; CU(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return fail(FK_ERR_STATE, "device %d is sm_%d%d; this library carries sm_100a code only", device, prop.major, prop.minor);
+    Ctx *c = new Ctx(); c->device = device; c->sm_count = prop.multiProcessorCount;
+    CU(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    CU(cudaEventCreate(&c->ev0)); CU(cudaEventCreate(&c->ev1));
+    CU(cudaMalloc(&c->state, sizeof(FkState))); CU(cudaMemset(c->state, 0, sizeof(FkState)));
+    c->hist_cap = FK_HIST_CAP;
+    CU(cudaMalloc(&c->history, sizeof(uint32_t) * c->hist_cap)); CU(cudaMemset(c->history, 0, sizeof(uint32_t) * c->hist_cap));
+    CU(cudaMallocHost(&c->pinned, sizeof(uint32_t) * (c->hist_cap + 64)));
+    const char *e = getenv("FK_PDL"); if (e && e[0] == '0') c->pdl = false;
+    CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
+    CU(big_smem(k_linear_residual<4>)); CU(big_smem(k_linear_residual<8>)); CU(big_smem(k_linear_residual<16>));
+    CU(big_smem(k_rmsnorm_gateup_act<4>)); CU(big_smem(k_rmsnorm_gateup_act<8>)); CU(big_smem(k_rmsnorm_gateup_act<16>));
+    CU(big_smem(k_final_head<4>)); CU(big_smem(k_final_head<8>)); CU(big_smem(k_final_head<16>));
+    c->open = true;
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_ctx.push_back(c); *out = g_ctx.size();
+    return FK_OK;
+}
+
+extern "C" fk_status fk_close(fk_handle h) {
+    CTX(h);
+    cudaStreamSynchronize(c->stream);
+    for (auto &g : c->graphs) { if (g.exec) cudaGraphExecDestroy(g.exec); if (g.graph) cudaGraphDestroy(g.graph); }
+    for (auto &w : c->weights) { cudaFree(w.w); cudaFree(w.s); cudaFree(w.b); }
+    for (void *p : c->allocs) cudaFree(p);
+    if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
+    cudaFree(c->state); cudaFree(c->history); cudaFreeHost(c->pinned);
+    cudaEventDestroy(c->ev0); cudaEventDestroy(c->ev1); cudaStreamDestroy(c->stream);
+    c->graphs.clear(); c->weights.clear(); c->allocs.clear(); c->open = false;
+    return FK_OK;
+}
+
+extern "C" fk_status fk_info(fk_handle h, char *buf, size_t cap) {
+    CTX(h);
+    if (!buf || cap == 0) return fail(FK_ERR_VALUE, "buf is null");
+    cudaDeviceProp prop; CU(cudaGetDeviceProperties(&prop, c->device));
+    size_t fr = 0, tot = 0; CU(cudaMemGetInfo(&fr, &tot));
+    snprintf(buf, cap, "{\"device\": %d, \"name\": \"%s\", \"sm\": %d, \"cc\": \"%d.%d\", \"mem_total\": %zu, \"mem_free\": %zu, "
+             "\"weights\": %zu, \"graphs\": %zu, \"pdl\": %s, \"rank\": %d, \"world\": %d, \"kernel_launches\": %lld}",
+             c->device, prop.name, prop.multiProcessorCount, prop.major, prop.minor, tot, fr, c->weights.size(), c->graphs.size(),
+             c->pdl ? "true" : "false", c->rank, c->world, c->launches);
+    return FK_OK;
+}
+static const char *kKernelNames[FK_TASK_KIND_COUNT] = {
+    "fusekit_step_init", "fusekit_embed_lookup_decode", "fusekit_rmsnorm_qkv", "fusekit_qk_norm_rope_store",
+    "fusekit_sdpa_decode", "fusekit_linear_residual", "fusekit_rmsnorm_gateup_act", "fusekit_final_rmsnorm_lm_head",
+    "fusekit_argmax_finalize", "fusekit_allreduce", "fusekit_residual_add"};
+extern "C" fk_status fk_kernel_names(char *buf, size_t cap) {
+    if (!buf || cap == 0) return fail(FK_ERR_VALUE, "buf is null");
+    std::string s;
+    for (int i = 0; i < FK_TASK_KIND_COUNT; ++i) { if (i) s += ","; s += kKernelNames[i]; }
+    snprintf(buf, cap, "%s", s.c_str());
+    return FK_OK;
+}
+
+// ------------------------------------------------------------------ memory
+extern "C" fk_status fk_alloc(fk_handle h, size_t nbytes, fk_dptr *out) {
+    CTX(h);
+    if (!out || nbytes == 0) return fail(FK_ERR_VALUE, "fk_alloc: bad arguments");
+    void *p = nullptr; CU(cudaMalloc(&p, (nbytes + 255) & ~(size_t)255));
+    CU(cudaMemsetAsync(p, 0, nbytes, c->stream));
+    c->allocs.push_back(p); *out = (fk_dptr)p;
+    return FK_OK;
+}
+extern "C" fk_status fk_free(fk_handle h, fk_dptr p) {
+    CTX(h);
+    for (size_t i = 0; i < c->allocs.size(); ++i)
+        if (c->allocs[i] == (void *)p) { CU(cudaStreamSynchronize(c->stream)); CU(cudaFree((void *)p)); c->allocs.erase(c->allocs.begin() + i); return FK_OK; }
+    return fail(FK_ERR_VALUE, "fk_free: address not owned by this handle");
+}
+extern "C" fk_status fk_upload(fk_handle h, fk_dptr dst, const void *src, size_t n) {
+    CTX(h);
+    if (!dst || !src) return fail(FK_ERR_VALUE, "fk_upload: null pointer");
+    CU(cudaMemcpyAsync((void *)dst, src, n, cudaMemcpyHostToDevice, c->stream)); CU(cudaStreamSynchronize(c->stream));
+    return FK_OK;
+}
+extern "C" fk_status fk_download(fk_handle h, void *dst, fk_dptr src, size_t n) {
+    CTX(h);
+    if (!dst || !src) return fail(FK_ERR_VALUE, "fk_download: null pointer");
+    CU(cudaMemcpyAsync(dst, (const void *)src, n, cudaMemcpyDeviceToHost, c->stream)); CU(cudaStreamSynchronize(c->stream));
+    return FK_OK;
+}
+extern "C" fk_status fk_memset(fk_handle h, fk_dptr dst, int byte, size_t n) {
+    CTX(h); CU(cudaMemsetAsync((void *)dst, byte, n, c->stream)); return FK_OK;
+}
+extern "C" fk_status fk_sync(fk_handle h) { CTX(h); CU(cudaStreamSynchronize(c->stream)); return FK_OK; }
+extern "C" fk_status fk_kv_cache_alloc(fk_handle h, int n_kv, int capacity, int head_dim, fk_dptr *k_out, fk_dptr *v_out) {
+    if (n_kv <= 0 || capacity <= 0 || head_dim <= 0 || (head_dim & 7)) return fail(FK_ERR_VALUE, "fk_kv_cache_alloc: bad shape");
+    const size_t bytes = (size_t)n_kv * capacity * head_dim * 2;
+    fk_status s = fk_alloc(h, bytes, k_out); if (s) return s;
+    return fk_alloc(h, bytes, v_out);
+}
+
+// ------------------------------------------------------------------ weights
+static Weight *get_w(Ctx *c, fk_weight w) { return (w == 0 || w > c->weights.size()) ? nullptr : &c->weights[w - 1]; }
+
+extern "C" fk_status fk_weight_alloc(fk_handle h, int64_t n, int64_t k, int bits, fk_weight *out) {
+    CTX(h);
+    if (!out || n <= 0 || k <= 0 || (k % 64) || (bits != 4 && bits != 8 && bits != 16)) return fail(FK_ERR_VALUE, "fk_weight_alloc: need n>0, k%%64==0, bits in {4,8,16}");
+    Weight w; w.n = n; w.k = k; w.bits = bits;
+    w.w_bytes = (size_t)n * k * bits / 8; w.sb_bytes = bits == 16 ? 0 : (size_t)n * (k / 64) * 2;
+    CU(cudaMalloc(&w.w, w.w_bytes));
+    if (w.sb_bytes) { CU(cudaMalloc(&w.s, w.sb_bytes)); CU(cudaMalloc(&w.b, w.sb_bytes)); }
+    c->weights.push_back(w); *out = c->weights.size();
+    return FK_OK;
+}
+extern "C" fk_status fk_weight_upload_rows(fk_handle h, fk_weight wid, int64_t r0, int64_t nr, const void *packed, const void *scales, const void *biases) {
+    CTX(h); Weight *w = get_w(c, wid);
+    if (!w) return fail(FK_ERR_VALUE, "bad weight id");
+    if (w->finalized) return fail(FK_ERR_STATE, "weight already finalized");
+    if (r0 < 0 || nr <= 0 || r0 + nr > w->n || !packed) return fail(FK_ERR_VALUE, "row range out of bounds");
+    const size_t rb = (size_t)w->k * w->bits / 8, gb = (size_t)(w->k / 64) * 2;
+    CU(cudaMemcpyAsync((char *)w->w + r0 * rb, packed, nr * rb, cudaMemcpyHostToDevice, c->stream));
+    if (w->bits != 16) {
+        if (!scales || !biases) return fail(FK_ERR_VALUE, "scales/biases required");
+        CU(cudaMemcpyAsync((char *)w->s + r0 * gb, scales, nr * gb, cudaMemcpyHostToDevice, c->stream));
+        CU(cudaMemcpyAsync((char *)w->b + r0 * gb, biases, nr * gb, cudaMemcpyHostToDevice, c->stream));
+    }
+    CU(cudaStreamSynchronize(c->stream));
+    return FK_OK;
+}
+extern "C" fk_status fk_weight_synth_rows(fk_handle h, fk_weight wid, int64_t r0, int64_t nr, uint64_t stream, float std, int64_t k_global, int64_t src_row0, int64_t k0) {
+    CTX(h); Weight *w = get_w(c, wid);
+    if (!w) return fail(FK_ERR_VALUE, "bad weight id");
+    if (w->finalized) return fail(FK_ERR_STATE, "weight already finalized");
+    if (r0 < 0 || nr <= 0 || r0 + nr > w->n) return fail(FK_ERR_VALUE, "row range out of bounds");
+    if (w->bits == 16) {
+        const long long tot = nr * w->k;
+        k_synth_dense<<<(unsigned)((tot + 255) / 256), 256, 0, c->stream>>>((uint16_t *)w->w, w->k, r0, nr, stream, std, k_global, src_row0, k0);
+    } else {
+        const long long tot = nr * (w->k / 64);
+        k_synth_qweight<<<(unsigned)((tot + 127) / 128), 128, 0, c->stream>>>(w->w, w->s, w->b, w->k, w->bits, r0, nr, stream, std, k_global, src_row0, k0);
+    }
+    CU(cudaGetLastError());
+    return FK_OK;
+}
+extern "C" fk_status fk_weight_finalize(fk_handle h, fk_weight wid) {
+    CTX(h); Weight *w = get_w(c, wid);
+    if (!w) return fail(FK_ERR_VALUE, "bad weight id");
+    w->finalized = true;
+    return FK_OK;
+}
+extern "C" fk_status fk_weight_dequant(fk_handle h, fk_weight wid, int64_t row0, int64_t nrows, float *host_out) {
+    CTX(h); Weight *w = get_w(c, wid);
+    if (!w || !host_out || row0 < 0 || nrows <= 0 || row0 + nrows > w->n) return fail(FK_ERR_VALUE, "fk_weight_dequant: bad arguments");
+    float *d = nullptr; const long long tot = nrows * w->k;
+    CU(cudaMalloc(&d, tot * 4));
+    k_dequant<<<(unsigned)((tot + 255) / 256), 256, 0, c->stream>>>(w->w, w->s, w->b, w->k, w->bits, row0, nrows, d);
+    cudaError_t e = cudaMemcpyAsync(host_out, d, tot * 4, cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    cudaFree(d);
+    CU(e);
+    return FK_OK;
+}
+extern "C" fk_status fk_weight_nbytes(fk_handle h, fk_weight wid, uint64_t *out) {
+    CTX(h); Weight *w = get_w(c, wid);
+    if (!w || !out) return fail(FK_ERR_VALUE, "bad weight id");
+    *out = w->w_bytes + 2 * w->sb_bytes;
+    return FK_OK;
+}
+extern "C" fk_status fk_synth_normal_bf16(fk_handle h, fk_dptr dst, uint64_t stream, uint64_t idx0, uint64_t n, float mean, float std) {
+    CTX(h);
+    if (!dst || n == 0) return fail(FK_ERR_VALUE, "fk_synth_normal_bf16: bad arguments");
+    k_synth_normal_bf16<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>((uint16_t *)dst, stream, idx0, n, mean, std);
+    CU(cudaGetLastError());
+    return FK_OK;
+}
+
+// ------------------------------------------------------------------ launches
+template <typename... KA, typename... A>
+static cudaError_t launch(Ctx *c, void (*kern)(KA...), dim3 grid, dim3 block, size_t smem, A... args) {
+    cudaLaunchConfig_t cfg; memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = c->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = c->pdl ? 1 : 0;
+    c->launches++;
+    return cudaLaunchKernelEx(&cfg, kern, KA(args)...);
+}
+#define BITS_SWITCH(bits, CALL)                  \
+    switch (bits) {                              \
+        case 4: { constexpr int B = 4; CALL; break; }   \
+        case 8: { constexpr int B = 8; CALL; break; }   \
+        default: { constexpr int B = 16; CALL; break; } \
+    }
+
+static int grid_for(Ctx *c, long long units, int warps_per_block) {
+    long long blocks = (units + warps_per_block - 1) / warps_per_block;
+    const long long cap = (long long)c->sm_count * 4;
+    if (blocks > cap) blocks = cap;
+    return (int)(blocks < 1 ? 1 : blocks);
+}
+
+static fk_status run_task(Ctx *c, const fk_task &t) {
+    const uint64_t *b = t.buf; const int32_t *i = t.iarg; const float *f = t.farg;
+    cudaError_t e = cudaSuccess;
+    switch (t.kind) {
+    case FK_TASK_STEP_INIT: return FK_OK;     // offset/token advance is fused into the argmax finalisation
+    case FK_TASK_EMBED_LOOKUP_DECODE: {
+        if (!b[0] || !b[1] || i[0] <= 0 || i[1] <= 0 || i[1] > FK_MAX_ROWS) return fail(FK_ERR_VALUE, "embed: bad arguments");
+        EmbedArgs a{(const uint16_t *)b[0], (uint16_t *)b[1], i[0], i[1], f[0]};
+        e = launch(c, k_embed_lookup, dim3((i[0] * i[1] + 255) / 256), dim3(256), 0, (const FkState *)c->state, a);
+        break;
+    }
+    case FK_TASK_RMSNORM_QKV: {
+        Weight *w = get_w(c, b[2]);
+        if (!w || !w->finalized) return fail(FK_ERR_VALUE, "rmsnorm_qkv: weight missing or not finalized");
+        const int H = i[0], nq = i[1], nkv = i[2], hd = i[3], cap = i[4], sinks = i[5];
+        if (w->k != H || w->n != (long long)(nq + 2 * nkv) * hd || (hd & 1) || cap <= 0) return fail(FK_ERR_VALUE, "rmsnorm_qkv: shape mismatch");
+        if (sinks ? (!b[5] || !b[6]) : (!b[7] || !b[8])) return fail(FK_ERR_VALUE, "rmsnorm_qkv: output buffers missing");
+        QkvArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], w->view(), (const uint16_t *)b[3], (uint16_t *)b[4], (uint16_t *)b[5],
+                  (uint16_t *)b[6], (uint16_t *)b[7], (uint16_t *)b[8], (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11],
+                  H, nq, nkv, hd, cap, sinks, f[0], (float)log2((double)f[1])};
+        const int grid = grid_for(c, w->n / 2, 8);
+        BITS_SWITCH(w->bits, e = launch(c, k_rmsnorm_qkv<B>, dim3(grid), dim3(256), smem_bytes_for(H), (const FkState *)c->state, a));
+        break;
+    }
+    case FK_TASK_QK_NORM_ROPE_STORE: {
+        const int nq = i[0], nkv = i[1], hd = i[2], cap = i[3];
+        if (hd > 512 || (hd & 1) || !b[0] || !b[1] || !b[2] || !b[5] || !b[6]) return fail(FK_ERR_VALUE, "qk_norm_rope_store: bad arguments");
+        QkNormArgs a{(uint16_t *)b[0], (const uint16_t *)b[1], (const uint16_t *)b[2], (const uint16_t *)b[3], (const uint16_t *)b[4],
+                     (uint16_t *)b[5], (uint16_t *)b[6], nq, nkv, hd, cap, f[0], (float)log2((double)f[1])};
+        e = launch(c, k_qk_norm_rope_store, dim3(nq + nkv), dim3((hd + 31) / 32 * 32), 0, (const FkState *)c->state, a);
+        break;
+    }
+    case FK_TASK_SDPA_DECODE: {
+        const int nq = i[0], nkv = i[1], hd = i[2], cap = i[3];
+        if (nkv <= 0 || nq % nkv || nq / nkv > FK_SDPA_MAXG || hd > 256 || (hd & 7) || !b[4] || !b[5]) return fail(FK_ERR_VALUE, "sdpa: unsupported shape (group <= 8, head_dim <= 256)");
+        const int chunks = (cap + FK_SDPA_KEYS - 1) / FK_SDPA_KEYS, G = nq / nkv;
+        SdpaArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], (uint32_t *)b[5],
+                   nq, nkv, hd, cap, chunks, f[0]};
+        const size_t smem = sizeof(float) * (size_t)(G * hd + G * FK_SDPA_KEYS + 2 * G + 8);
+        e = launch(c, k_sdpa_decode, dim3(chunks, nkv), dim3(hd <= 128 ? 128 : 256), smem, (const FkState *)c->state, a);
+        break;
+    }
+    case FK_TASK_LINEAR_RESIDUAL: {
+        Weight *w = get_w(c, b[1]);
+        if (!w || !w->finalized) return fail(FK_ERR_VALUE, "linear_residual: weight missing or not finalized");
+        if (w->k != i[0] || w->n != i[1] || !b[0] || (!b[3] && !b[4])) return fail(FK_ERR_VALUE, "linear_residual: shape mismatch");
+        LinArgs a{(const uint16_t *)b[0], w->view(), (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], i[0], i[1]};
+        const int grid = grid_for(c, w->n, 8);
+        BITS_SWITCH(w->bits, e = launch(c, k_linear_residual<B>, dim3(grid), dim3(256), smem_bytes_for(i[0]), (const FkState *)c->state, a));
+        break;
+    }
+    case FK_TASK_RMSNORM_GATEUP_ACT: {
+        Weight *wg = get_w(c, b[2]), *wu = get_w(c, b[3]);
+        if (!wg || !wu || !wg->finalized || !wu->finalized) return fail(FK_ERR_VALUE, "gateup: weights missing or not finalized");
+        if (wg->k != i[0] || wu->k != i[0] || wg->n != i[1] || wu->n != i[1] || wg->bits != wu->bits) return fail(FK_ERR_VALUE, "gateup: shape mismatch");
+        GateUpArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], wg->view(), wu->view(), (uint16_t *)b[4],
+                     (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0]};
+        const int grid = grid_for(c, wg->n, 8);
+        BITS_SWITCH(wg->bits, e = launch(c, k_rmsnorm_gateup_act<B>, dim3(grid), dim3(256), smem_bytes_for(i[0]), (const FkState *)c->state, a));
+        break;
+    }
+    case FK_TASK_FINAL_RMSNORM_LM_HEAD: {
+        Weight *w = get_w(c, b[2]);
+        if (!w || !w->finalized) return fail(FK_ERR_VALUE, "lm_head: weight missing or not finalized");
+        if (w->k != i[0] || w->n != i[1] || !b[4] || !b[5]) return fail(FK_ERR_VALUE, "lm_head: shape mismatch");
+        HeadArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], w->view(), (uint16_t *)b[3], (unsigned long long *)b[4], (uint32_t *)b[5],
+                   (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], c->history, i[0], i[1], i[2], i[3], f[0]};
+        const int grid = grid_for(c, w->n, 8);
+        BITS_SWITCH(w->bits, e = launch(c, k_final_head<B>, dim3(grid), dim3(256), smem_bytes_for(i[0]), c->state, a));
+        break;
+    }
+    case FK_TASK_ARGMAX_FINALIZE: {
+        if (!b[4] || i[0] <= 0) return fail(FK_ERR_VALUE, "argmax_finalize: bad arguments");
+        e = launch(c, k_argmax_finalize, dim3(1), dim3(32), 0, c->state, (const unsigned long long *)b[4], i[0], c->history);
+        break;
+    }
+    case FK_TASK_ALLREDUCE: {
+        if (!c->comm) return fail(FK_ERR_STATE, "allreduce task without fk_comm_init");
+        const int dtype = i[1] == 1 ? 5 /* ncclUint64 */ : 7 /* ncclFloat32 */, op = i[1] == 1 ? 2 /* ncclMax */ : 0 /* ncclSum */;
+        int r = g_nccl.AllReduce((const void *)b[0], (void *)b[0], (size_t)i[0], dtype, op, c->comm, c->stream);
+        if (r != 0) return fail(FK_ERR_NCCL, "ncclAllReduce: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "error");
+        break;
+    }
+    case FK_TASK_RESIDUAL_ADD: {
+        if (!b[0] || !b[2] || i[0] <= 0) return fail(FK_ERR_VALUE, "residual_add: bad arguments");
+        e = launch(c, k_residual_add, dim3((i[0] + 255) / 256), dim3(256), 0, (const float *)b[0], (const uint16_t *)b[1], (uint16_t *)b[2], i[0]);
+        break;
+    }
+    default: return fail(FK_ERR_VALUE, "unknown task kind %d", t.kind);
+    }
+    if (e != cudaSuccess) return fail(FK_ERR_CUDA, "launch of %s failed: %s", kKernelNames[t.kind], cudaGetErrorString(e));
+    return FK_OK;
+}
+
+extern "C" fk_status fk_launch(fk_handle h, const fk_task *task) {
+    CTX(h);
+    if (!task) return fail(FK_ERR_VALUE, "task is null");
+    fk_status s = run_task(c, *task); if (s) return s;
+    CU(cudaStreamSynchronize(c->stream));
+    return FK_OK;
+}
+extern "C" fk_status fk_launch_batch(fk_handle h, const fk_task *tasks, int n) {
+    CTX(h);
+    if (!tasks || n <= 0) return fail(FK_ERR_VALUE, "empty task list");
+    for (int j = 0; j < n; ++j) { fk_status s = run_task(c, tasks[j]); if (s) return s; }
+    CU(cudaStreamSynchronize(c->stream));
+    return FK_OK;
+}
+extern "C" fk_status fk_smoke(fk_handle h, const uint16_t *a, const uint16_t *b, uint16_t *out, int n) {
+    CTX(h);
+    if (!a || !b || !out || n <= 0) return fail(FK_ERR_VALUE, "fk_smoke: bad arguments");
+    uint16_t *d = nullptr; CU(cudaMalloc(&d, (size_t)n * 6));
+    cudaError_t e = cudaMemcpyAsync(d, a, (size_t)n * 2, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d + n, b, (size_t)n * 2, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) { k_add_bf16<<<(n + 255) / 256, 256, 0, c->stream>>>(d, d + n, d + 2 * n, n); e = cudaGetLastError(); c->launches++; }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(out, d + 2 * n, (size_t)n * 2, cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    cudaFree(d);
+    CU(e);
+    return FK_OK;
+}
+
+// ------------------------------------------------------------------ state
+static fk_status set_state(Ctx *c, uint32_t token, uint32_t offset) {
+    FkState *s = (FkState *)c->pinned; memset(s, 0, sizeof(FkState));
+    s->token[0] = token; s->offset = offset; s->hist_counter = 0; s->error = 0; s->hist_cap = c->hist_cap;
+    CU(cudaMemcpyAsync(c->state, s, sizeof(FkState), cudaMemcpyHostToDevice, c->stream));
+    return FK_OK;
+}
+extern "C" fk_status fk_state_set(fk_handle h, uint32_t token, uint32_t offset) {
+    CTX(h); fk_status s = set_state(c, token, offset); if (s) return s;
+    CU(cudaStreamSynchronize(c->stream)); return FK_OK;
+}
+extern "C" fk_status fk_state_get(fk_handle h, uint32_t *token, uint32_t *offset, uint32_t *err) {
+    CTX(h);
+    CU(cudaMemcpyAsync(c->pinned, c->state, sizeof(FkState), cudaMemcpyDeviceToHost, c->stream)); CU(cudaStreamSynchronize(c->stream));
+    const FkState *s = (const FkState *)c->pinned;
+    if (token) *token = s->token[0]; if (offset) *offset = s->offset; if (err) *err = s->error;
+    return FK_OK;
+}
+
+// ------------------------------------------------------------------ graph
+static Graph *get_g(Ctx *c, fk_graph g) { return (g == 0 || g > c->graphs.size()) ? nullptr : &c->graphs[g - 1]; }
+
+extern "C" fk_status fk_graph_capture(fk_handle h, const fk_task *tasks, int n, fk_graph *out) {
+    CTX(h);
+    if (!tasks || n <= 0 || !out) return fail(FK_ERR_VALUE, "empty task list");
+    Graph g; g.tasks.assign(tasks, tasks + n);
+    CU(cudaStreamSynchronize(c->stream));
+    CU(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    fk_status s = FK_OK;
+    for (int j = 0; j < n && s == FK_OK; ++j) s = run_task(c, tasks[j]);
+    cudaError_t e = cudaStreamEndCapture(c->stream, &g.graph);
+    if (s) { if (g.graph) cudaGraphDestroy(g.graph); return s; }
+    CU(e);
+    CU(cudaGraphInstantiate(&g.exec, g.graph, 0));
+    CU(cudaGraphUpload(g.exec, c->stream));
+    c->graphs.push_back(g); *out = c->graphs.size();
+    return FK_OK;
+}
+extern "C" fk_status fk_graph_node_count(fk_handle h, fk_graph gid, int *n_out) {
+    CTX(h); Graph *g = get_g(c, gid);
+    if (!g || !n_out) return fail(FK_ERR_VALUE, "bad graph id");
+    size_t n = 0; CU(cudaGraphGetNodes(g->graph, nullptr, &n)); *n_out = (int)n;
+    return FK_OK;
+}
+extern "C" fk_status fk_graph_launch_async(fk_handle h, fk_graph gid) {
+    CTX(h); Graph *g = get_g(c, gid);
+    if (!g) return fail(FK_ERR_VALUE, "bad graph id");
+    if (c->pending) return fail(FK_ERR_STATE, "a launch is already pending; call fk_wait");
+    CU(cudaEventRecord(c->ev0, c->stream));
+    CU(cudaGraphLaunch(g->exec, c->stream));
+    CU(cudaEventRecord(c->ev1, c->stream));
+    c->pending = true;
+    return FK_OK;
+}
+extern "C" fk_status fk_wait(fk_handle h, double *gpu_seconds) {
+    CTX(h);
+    if (!c->pending) return fail(FK_ERR_STATE, "nothing pending");
+    c->pending = false;
+    CU(cudaEventSynchronize(c->ev1));
+    float ms = 0.0f; CU(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+    if (gpu_seconds) *gpu_seconds = ms * 1e-3;
+    return FK_OK;
+}
+extern "C" fk_status fk_graph_launch(fk_handle h, fk_graph gid, double *gpu_seconds) {
+    fk_status s = fk_graph_launch_async(h, gid); if (s) return s;
+    return fk_wait(h, gpu_seconds);
+}
+extern "C" fk_status fk_graph_profile_nodes(fk_handle h, fk_graph gid, int repeats, double *seconds_out, int cap, int *n_out) {
+    CTX(h); Graph *g = get_g(c, gid);
+    if (!g || !seconds_out || repeats <= 0) return fail(FK_ERR_VALUE, "bad arguments");
+    const int n = (int)g->tasks.size();
+    if (n_out) *n_out = n;
+    if (cap < n) return fail(FK_ERR_VALUE, "seconds_out holds %d entries, %d needed", cap, n);
+    // each task alone between two events, state restored afterwards (profile_icb_commands, lib.rs:821-869)
+    CU(cudaMemcpyAsync(c->pinned + 32, c->state, sizeof(FkState), cudaMemcpyDeviceToHost, c->stream));
+    CU(cudaStreamSynchronize(c->stream));
+    for (int j = 0; j < n; ++j) {
+        double best = 1e30;
+        for (int r = 0; r < repeats; ++r) {
+            CU(cudaMemcpyAsync(c->state, c->pinned + 32, sizeof(FkState), cudaMemcpyHostToDevice, c->stream));
+            CU(cudaEventRecord(c->ev0, c->stream));
+            fk_status s = run_task(c, g->tasks[j]); if (s) return s;
+            CU(cudaEventRecord(c->ev1, c->stream));
+            CU(cudaEventSynchronize(c->ev1));
+            float ms = 0.0f; CU(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+            if (ms * 1e-3 < best) best = ms * 1e-3;
+        }
+        seconds_out[j] = best;
+    }
+    CU(cudaMemcpyAsync(c->state, c->pinned + 32, sizeof(FkState), cudaMemcpyHostToDevice, c->stream));
+    CU(cudaStreamSynchronize(c->stream));
+    return FK_OK;
+}
+
+extern "C" fk_status fk_step(fk_handle h, fk_graph gid, uint32_t token, uint32_t offset, uint32_t *next_token, double *gpu_seconds) {
+    return fk_decode_chunk(h, gid, offset, token, 1, next_token, gpu_seconds);
+}
+extern "C" fk_status fk_decode_chunk(fk_handle h, fk_graph gid, uint32_t base_offset, uint32_t seed_token, int count,
+                                     uint32_t *out_history, double *gpu_seconds) {
+    CTX(h); Graph *g = get_g(c, gid);
+    if (!g) return fail(FK_ERR_VALUE, "bad graph id");
+    if (count <= 0 || (uint32_t)count > c->hist_cap) return fail(FK_ERR_VALUE, "count must be in 1..%u", c->hist_cap);
+    if (c->pending) return fail(FK_ERR_STATE, "a launch is pending; call fk_wait");
+    fk_status s = set_state(c, seed_token, base_offset); if (s) return s;
+    CU(cudaEventRecord(c->ev0, c->stream));
+    for (int j = 0; j < count; ++j) CU(cudaGraphLaunch(g->exec, c->stream));
+    CU(cudaEventRecord(c->ev1, c->stream));
+    uint32_t *hist = c->pinned + 64;
+    CU(cudaMemcpyAsync(hist, c->history, sizeof(uint32_t) * count, cudaMemcpyDeviceToHost, c->stream));
+    CU(cudaMemcpyAsync(c->pinned + 32, c->state, sizeof(FkState), cudaMemcpyDeviceToHost, c->stream));
+    CU(cudaStreamSynchronize(c->stream));
+    float ms = 0.0f; CU(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+    if (gpu_seconds) *gpu_seconds = ms * 1e-3;
+    if (out_history) memcpy(out_history, hist, sizeof(uint32_t) * count);
+    const FkState *st = (const FkState *)(c->pinned + 32);
+    if (st->error) return fail(FK_ERR_DEVICE, "device error word 0x%x", st->error);
+    return FK_OK;
+}
+extern "C" fk_status fk_decode_chunk_host(fk_handle h, fk_graph gid, uint32_t base_offset, uint32_t seed_token, int count,
+                                          uint32_t *out_history, double *gpu_seconds) {
+    CTX(h); Graph *g = get_g(c, gid);
+    if (!g || count <= 0 || !out_history) return fail(FK_ERR_VALUE, "bad arguments");
+    uint32_t tok = seed_token; double tot = 0.0;
+    for (int j = 0; j < count; ++j) {
+        double t = 0.0;
+        fk_status s = fk_decode_chunk(h, gid, base_offset + j, tok, 1, &tok, &t); if (s) return s;
+        out_history[j] = tok; tot += t;
+    }
+    if (gpu_seconds) *gpu_seconds = tot;
+    return FK_OK;
+}
+
+// ------------------------------------------------------------------ tensor parallel
+extern "C" fk_status fk_comm_unique_id(void *id128, size_t cap) {
+    if (!id128 || cap < sizeof(ncclUniqueId)) return fail(FK_ERR_VALUE, "id buffer must hold 128 bytes");
+    fk_status s = nccl_load(); if (s) return s;
+    ncclUniqueId id; int r = g_nccl.GetUniqueId(&id);
+    if (r != 0) return fail(FK_ERR_NCCL, "ncclGetUniqueId failed (%d)", r);
+    memcpy(id128, &id, sizeof id);
+    return FK_OK;
+}
+extern "C" fk_status fk_comm_init(fk_handle h, const void *id128, int rank, int world) {
+    CTX(h);
+    if (!id128 || world < 1 || rank < 0 || rank >= world) return fail(FK_ERR_VALUE, "fk_comm_init: bad arguments");
+    fk_status s = nccl_load(); if (s) return s;
+    ncclUniqueId id; memcpy(&id, id128, sizeof id);
+    int r = g_nccl.CommInitRank(&c->comm, world, id, rank);
+    if (r != 0) return fail(FK_ERR_NCCL, "ncclCommInitRank: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "error");
+    c->rank = rank; c->world = world;
+    return FK_OK;
+}

@@ -1,0 +1,429 @@
+"""Host side of the decode path: binds model tensors to device buffers, builds the
+per-token dispatch list, captures it once as a CUDA graph and replays it per token.
+
+It mirrors the reference's ``Dispatcher`` (python/fusekit_runtime/dispatch.py:
+``_build_dispatches`` :3163-3611, ``_ensure_icb`` :3864-4024, ``_try_run_single``
+:4380-4548) and the greedy chunk loop of ``_fast_generate_step``
+(python/fusekit_runtime/__init__.py:4782-5139), with the Metal indirect command buffer
+replaced by a graph that the native library owns.  Everything numeric happens in
+``libfusekit_cuda.so``; this module only does bookkeeping.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import math
+
+import numpy as np
+
+from . import _native as N
+from .model_spec import ModelSpec, stream_id, tensor_name
+
+FK_CHUNK = 64          # tokens pre-submitted per chunk (reference FK_CHUNK, dispatch.py:1103)
+
+
+def _bf16_round(v: float) -> float:
+    u = int(np.array([v], np.float32).view(np.uint32)[0])
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return float(np.array([u], np.uint32).view(np.float32)[0])
+
+
+class Runtime:
+    """Thin owner of one ``fk_handle`` (reference: ``load_dispatcher`` handle, lib.rs:115)."""
+
+    def __init__(self, device: int = 0):
+        self.L = N.lib()
+        h = C.c_uint64()
+        N.check(self.L.fk_open(device, C.byref(h)), "fk_open")
+        self.h = h.value
+        self.device = device
+
+    def close(self):
+        if self.h:
+            self.L.fk_close(self.h)
+            self.h = 0
+
+    def info(self) -> dict:
+        buf = C.create_string_buffer(1024)
+        N.check(self.L.fk_info(self.h, buf, len(buf)), "fk_info")
+        return json.loads(buf.value.decode())
+
+    def alloc(self, nbytes: int) -> int:
+        p = C.c_uint64()
+        N.check(self.L.fk_alloc(self.h, nbytes, C.byref(p)), "fk_alloc")
+        return p.value
+
+    def upload(self, dptr: int, arr: np.ndarray):
+        arr = np.ascontiguousarray(arr)
+        N.check(self.L.fk_upload(self.h, dptr, arr.ctypes.data, arr.nbytes), "fk_upload")
+
+    def to_device(self, arr: np.ndarray) -> int:
+        p = self.alloc(arr.nbytes)
+        self.upload(p, arr)
+        return p
+
+    def download(self, dptr: int, shape, dtype) -> np.ndarray:
+        out = np.empty(shape, dtype)
+        N.check(self.L.fk_download(self.h, out.ctypes.data, dptr, out.nbytes), "fk_download")
+        return out
+
+    def sync(self):
+        N.check(self.L.fk_sync(self.h), "fk_sync")
+
+    def smoke(self, a: np.ndarray, b: np.ndarray) -> np.ndarray:
+        out = np.empty_like(a)
+        N.check(self.L.fk_smoke(self.h, a.ctypes.data, b.ctypes.data, out.ctypes.data, a.size), "fk_smoke")
+        return out
+
+    # ---- weights
+    def weight_alloc(self, n: int, k: int, bits: int) -> int:
+        w = C.c_uint64()
+        N.check(self.L.fk_weight_alloc(self.h, n, k, bits, C.byref(w)), "fk_weight_alloc")
+        return w.value
+
+    def weight_upload_rows(self, wid: int, row0: int, packed, scales=None, biases=None):
+        packed = np.ascontiguousarray(packed)
+        sp = np.ascontiguousarray(scales).ctypes.data if scales is not None else None
+        bp = np.ascontiguousarray(biases).ctypes.data if biases is not None else None
+        N.check(self.L.fk_weight_upload_rows(self.h, wid, row0, packed.shape[0], packed.ctypes.data, sp, bp), "fk_weight_upload_rows")
+
+    def weight_synth_rows(self, wid, dst_row0, nrows, stream, std, k_global, src_row0, k0):
+        N.check(self.L.fk_weight_synth_rows(self.h, wid, dst_row0, nrows, stream, std, k_global, src_row0, k0), "fk_weight_synth_rows")
+
+    def weight_finalize(self, wid):
+        N.check(self.L.fk_weight_finalize(self.h, wid), "fk_weight_finalize")
+
+    def weight_dequant(self, wid, row0, nrows, k) -> np.ndarray:
+        out = np.empty((nrows, k), np.float32)
+        N.check(self.L.fk_weight_dequant(self.h, wid, row0, nrows, out.ctypes.data), "fk_weight_dequant")
+        return out
+
+    def synth_normal(self, dptr, stream, idx0, n, mean, std):
+        N.check(self.L.fk_synth_normal_bf16(self.h, dptr, stream, idx0, n, mean, std), "fk_synth_normal_bf16")
+
+    # ---- launches
+    def launch(self, task: N.Task):
+        N.check(self.L.fk_launch(self.h, C.byref(task)), "fk_launch")
+
+    def launch_batch(self, tasks):
+        arr = (N.Task * len(tasks))(*tasks)
+        N.check(self.L.fk_launch_batch(self.h, arr, len(tasks)), "fk_launch_batch")
+
+    def state_set(self, token: int, offset: int):
+        N.check(self.L.fk_state_set(self.h, token, offset), "fk_state_set")
+
+    def state_get(self):
+        t, o, e = C.c_uint32(), C.c_uint32(), C.c_uint32()
+        N.check(self.L.fk_state_get(self.h, C.byref(t), C.byref(o), C.byref(e)), "fk_state_get")
+        return t.value, o.value, e.value
+
+
+class DecodeEngine:
+    """One model instance (or one tensor-parallel slice of it) resident on a GPU."""
+
+    def __init__(self, spec: ModelSpec, capacity: int, device: int = 0, tp_rank: int = 0, tp_size: int = 1,
+                 want_logits: bool = False, runtime: Runtime | None = None):
+        if spec.n_kv % tp_size or spec.n_q % tp_size or spec.inter % tp_size or spec.vocab % tp_size:
+            raise ValueError("tensor-parallel degree must divide heads, intermediate size and vocabulary")
+        if (spec.inter // tp_size) % 64 or (spec.n_q // tp_size * spec.head_dim) % 64:
+            raise ValueError("row-split shards must keep whole quantisation groups of 64")
+        if tp_size > 1 and spec.arch != "qwen2":
+            raise ValueError("tensor parallelism is wired for the Qwen-shaped layer only")
+        self.spec, self.capacity, self.rank, self.world = spec, capacity, tp_rank, tp_size
+        self.rt = runtime or Runtime(device)
+        self.want_logits = want_logits
+        s = spec
+        self.nq, self.nkv, self.inter, self.vocab = s.n_q // tp_size, s.n_kv // tp_size, s.inter // tp_size, s.vocab // tp_size
+        self.W: dict[str, int] = {}      # name -> fk_weight id
+        self.V: dict[str, int] = {}      # name -> device address of a bf16 vector
+        self.cache: list[tuple[int, int, int]] = []     # (k, v, capacity) per layer
+        self.graph = 0
+        self._alloc_buffers()
+
+    # ------------------------------------------------------------------ buffers
+    def _alloc_buffers(self):
+        s, rt, H = self.spec, self.rt, self.spec.hidden
+        L = s.n_layers
+        self.X = rt.alloc((L + 1) * H * 2)            # residual stream at each layer input (+ final)
+        self.HB = rt.alloc(L * H * 2)                 # residual stream after attention
+        self.q_buf = rt.alloc(self.nq * s.head_dim * 2)
+        self.k_buf = rt.alloc(self.nkv * s.head_dim * 2)
+        self.v_buf = rt.alloc(self.nkv * s.head_dim * 2)
+        self.sdpa_buf = rt.alloc(self.nq * s.head_dim * 2)
+        self.act_buf = rt.alloc(self.inter * 2)
+        self.o_buf = rt.alloc(H * 2)                  # Gemma: o_proj output before its post-norm
+        self.d_buf = rt.alloc(L * H * 2)              # Gemma: down_proj output before its post-norm
+        self.part_f32 = rt.alloc(H * 4)               # tensor-parallel partial sums
+        max_cap = max(s.layer_capacity(l, self.capacity) for l in range(L))
+        chunks = (max_cap + 63) // 64
+        self.sdpa_part = rt.alloc(self.nq * chunks * (s.head_dim + 2) * 4)
+        self.sdpa_counter = rt.alloc(max(self.nkv, 1) * 4)
+        self.argmax_scratch = rt.alloc(8 * 1024)
+        self.head_counter = rt.alloc(4)
+        self.logits = rt.alloc(self.vocab * 2) if self.want_logits else 0
+        for l in range(L):
+            cap = s.layer_capacity(l, self.capacity)
+            k, v = C.c_uint64(), C.c_uint64()
+            N.check(rt.L.fk_kv_cache_alloc(rt.h, self.nkv, cap, s.head_dim, C.byref(k), C.byref(v)), "fk_kv_cache_alloc")
+            self.cache.append((k.value, v.value, cap))
+
+    def x_ptr(self, l: int) -> int:
+        return self.X + l * self.spec.hidden * 2
+
+    def hb_ptr(self, l: int) -> int:
+        return self.HB + l * self.spec.hidden * 2
+
+    def d_ptr(self, l: int) -> int:
+        return self.d_buf + l * self.spec.hidden * 2
+
+    # ------------------------------------------------------------------ tensors
+    def _linear_plan(self):
+        """(name, [(leaf, src_row0, nrows)], k_global, k0, k) for every weight object of this rank."""
+        s, r, hd = self.spec, self.rank, self.spec.head_dim
+        H, nq, nkv, I = s.hidden, self.nq, self.nkv, self.inter
+        plan = []
+        for l in range(s.n_layers):
+            plan.append((f"layers.{l}.qkv", [("q_proj", r * nq * hd, nq * hd), ("k_proj", r * nkv * hd, nkv * hd),
+                                             ("v_proj", r * nkv * hd, nkv * hd)], H, 0, H, l))
+            plan.append((f"layers.{l}.o", [("o_proj", 0, H)], s.n_q * hd, r * nq * hd, nq * hd, l))
+            plan.append((f"layers.{l}.gate", [("gate_proj", r * I, I)], H, 0, H, l))
+            plan.append((f"layers.{l}.up", [("up_proj", r * I, I)], H, 0, H, l))
+            plan.append((f"layers.{l}.down", [("down_proj", 0, H)], s.inter, r * I, I, l))
+        plan.append(("lm_head", [("lm_head", r * self.vocab, self.vocab)], H, 0, H, -1))
+        return plan
+
+    def _vector_plan(self):
+        """(name, leaf, layer, idx0, n, mean, std) for every bf16 vector/table of this rank."""
+        s, r, hd, H = self.spec, self.rank, self.spec.head_dim, self.spec.hidden
+        out = [("embed_tokens", "embed_tokens", -1, 0, s.vocab * H, 0.0, 0.02), ("final_norm", "final_norm", -1, 0, H, 1.0, 0.02)]
+        for l in range(s.n_layers):
+            out.append((f"layers.{l}.input_norm", "input_norm", l, 0, H, 1.0, 0.02))
+            out.append((f"layers.{l}.post_attention_norm", "post_attention_norm", l, 0, H, 1.0, 0.02))
+            if s.arch == "qwen2":
+                out.append((f"layers.{l}.q_bias", "q_bias", l, r * self.nq * hd, self.nq * hd, 0.0, 0.02))
+                out.append((f"layers.{l}.k_bias", "k_bias", l, r * self.nkv * hd, self.nkv * hd, 0.0, 0.02))
+                out.append((f"layers.{l}.v_bias", "v_bias", l, r * self.nkv * hd, self.nkv * hd, 0.0, 0.02))
+            else:
+                for leaf, n in (("pre_feedforward_norm", H), ("post_feedforward_norm", H), ("q_norm", hd), ("k_norm", hd)):
+                    out.append((f"layers.{l}.{leaf}", leaf, l, 0, n, 1.0, 0.02))
+        return out
+
+    def load_synthetic(self):
+        """Generate every tensor on the device from its named stream (seeded, bit-identical to the
+        documented CPU generator)."""
+        s, rt = self.spec, self.rt
+        for name, segs, k_global, k0, k, layer in self._linear_plan():
+            wid = rt.weight_alloc(sum(n for _, _, n in segs), k, s.bits)
+            row = 0
+            for leaf, src_row0, n in segs:
+                rt.weight_synth_rows(wid, row, n, stream_id(s.seed, tensor_name(layer, leaf)), 0.02, k_global, src_row0, k0)
+                row += n
+            rt.weight_finalize(wid)
+            self.W[name] = wid
+        self._load_vectors(lambda leaf, layer, idx0, n, mean, std, dst: rt.synth_normal(
+            dst, stream_id(s.seed, tensor_name(layer, leaf)), idx0, n, mean, std))
+        rt.sync()
+
+    def load_from(self, weight_provider, vector_provider):
+        """Upload host tensors in MLX-affine layout.  ``weight_provider(leaf, layer, src_row0, nrows,
+        k_global, k0, k, bits) -> (packed_or_dense, scales, biases)``; ``vector_provider(leaf, layer,
+        idx0, n, mean, std) -> uint16 array``."""
+        s, rt = self.spec, self.rt
+        for name, segs, k_global, k0, k, layer in self._linear_plan():
+            wid = rt.weight_alloc(sum(n for _, _, n in segs), k, s.bits)
+            row = 0
+            for leaf, src_row0, n in segs:
+                p, sc, bi = weight_provider(leaf, layer, src_row0, n, k_global, k0, k, s.bits)
+                rt.weight_upload_rows(wid, row, p, sc, bi)
+                row += n
+            rt.weight_finalize(wid)
+            self.W[name] = wid
+        self._load_vectors(lambda leaf, layer, idx0, n, mean, std, dst: rt.upload(dst, vector_provider(leaf, layer, idx0, n, mean, std)))
+        rt.sync()
+
+    def _load_vectors(self, fill):
+        s, rt = self.spec, self.rt
+        for name, leaf, layer, idx0, n, mean, std in self._vector_plan():
+            if leaf in ("q_bias", "k_bias", "v_bias"):
+                continue
+            self.V[name] = rt.alloc(n * 2)
+            fill(leaf, layer, idx0, n, mean, std, self.V[name])
+        if s.arch == "qwen2":          # q|k|v biases concatenated like the fused weight rows
+            hd = s.head_dim
+            for l in range(s.n_layers):
+                nq, nkv = self.nq * hd, self.nkv * hd
+                p = rt.alloc((nq + 2 * nkv) * 2)
+                fill("q_bias", l, self.rank * nq, nq, 0.0, 0.02, p)
+                fill("k_bias", l, self.rank * nkv, nkv, 0.0, 0.02, p + nq * 2)
+                fill("v_bias", l, self.rank * nkv, nkv, 0.0, 0.02, p + (nq + nkv) * 2)
+                self.V[f"layers.{l}.qkv_bias"] = p
+
+    def prefill_kv_synthetic(self, ctx: int):
+        """Fill positions [0, ctx) of every cache with N(0,1) values keyed by (layer, global kv head,
+        position); ring caches keep the last `window` positions at row p % window."""
+        s, rt, hd = self.spec, self.rt, self.spec.head_dim
+        for l, (ck, cv, cap) in enumerate(self.cache):
+            sk, sv = stream_id(s.seed, f"layers.{l}.cache_k"), stream_id(s.seed, f"layers.{l}.cache_v")
+            for hh in range(self.nkv):
+                gh = self.rank * self.nkv + hh
+                p0 = max(0, ctx - cap) if s.is_sliding(l) else 0
+                segs = []
+                p = p0
+                while p < ctx:                     # contiguous runs of rows inside the ring
+                    row = p % cap if s.is_sliding(l) else p
+                    run = min(ctx - p, cap - row)
+                    segs.append((p, row, run)); p += run
+                for p, row, run in segs:
+                    idx0 = (gh * 1048576 + p) * hd
+                    off = (hh * cap + row) * hd * 2
+                    rt.synth_normal(ck + off, sk, idx0, run * hd, 0.0, 1.0)
+                    rt.synth_normal(cv + off, sv, idx0, run * hd, 0.0, 1.0)
+        rt.sync()
+
+    def upload_kv(self, layer: int, k: np.ndarray, v: np.ndarray):
+        ck, cv, _ = self.cache[layer]
+        self.rt.upload(ck, k); self.rt.upload(cv, v)
+
+    # ------------------------------------------------------------------ dispatch list
+    def build_dispatches(self) -> list:
+        """The per-token kernel list in replay order (reference order: embed -> per layer RmsNormQkv,
+        SDPA, LinearResidual, gate/up chain, LinearResidual -> final head -> argmax;
+        src/codegen/task_graph_json.rs:1619-1664, dispatch.py:3163-3611)."""
+        s, T, hd, H = self.spec, N.Task.make, self.spec.head_dim, self.spec.hidden
+        scale = 1.0 / math.sqrt(hd)
+        # Gemma-family embedding scale sqrt(H), held in bf16 (embed_lookup_decode.rs OUTPUT_SCALE)
+        emb_scale = _bf16_round(math.sqrt(H)) if s.arch == "gemma3" else 1.0
+        tasks = [T(N.TASK_EMBED_LOOKUP_DECODE, -1, {0: self.V["embed_tokens"], 1: self.x_ptr(0)}, [H, 1], [emb_scale])]
+        tp = self.world > 1
+        for l in range(s.n_layers):
+            ck, cv, cap = self.cache[l]
+            theta = s.layer_theta(l)
+            pend = {}
+            if s.arch == "gemma3" and l > 0:
+                pend = {9: self.d_ptr(l - 1), 10: self.V[f"layers.{l-1}.post_feedforward_norm"], 11: self.x_ptr(l)}
+            x_in = self.hb_ptr(l - 1) if (s.arch == "gemma3" and l > 0) else self.x_ptr(l)
+            if s.arch == "qwen2":
+                tasks.append(T(N.TASK_RMSNORM_QKV, l, {0: x_in, 1: self.V[f"layers.{l}.input_norm"], 2: self.W[f"layers.{l}.qkv"],
+                                                       3: self.V[f"layers.{l}.qkv_bias"], 4: self.q_buf, 5: ck, 6: cv},
+                               [H, self.nq, self.nkv, hd, cap, 1], [s.eps, theta]))
+            else:
+                tasks.append(T(N.TASK_RMSNORM_QKV, l, {0: x_in, 1: self.V[f"layers.{l}.input_norm"], 2: self.W[f"layers.{l}.qkv"],
+                                                       4: self.q_buf, 7: self.k_buf, 8: self.v_buf, **pend},
+                               [H, self.nq, self.nkv, hd, cap, 0], [s.eps, theta]))
+                tasks.append(T(N.TASK_QK_NORM_ROPE_STORE, l, {0: self.q_buf, 1: self.k_buf, 2: self.v_buf, 3: self.V[f"layers.{l}.q_norm"],
+                                                              4: self.V[f"layers.{l}.k_norm"], 5: ck, 6: cv},
+                               [self.nq, self.nkv, hd, cap], [s.eps, theta]))
+            tasks.append(T(N.TASK_SDPA_DECODE, l, {0: self.q_buf, 1: ck, 2: cv, 3: self.sdpa_buf, 4: self.sdpa_part, 5: self.sdpa_counter},
+                           [self.nq, self.nkv, hd, cap], [scale]))
+            ko = self.nq * hd
+            if s.arch == "qwen2" and not tp:
+                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa_buf, 1: self.W[f"layers.{l}.o"], 2: self.x_ptr(l), 3: self.hb_ptr(l)}, [ko, H]))
+                tasks.append(T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: self.hb_ptr(l), 1: self.V[f"layers.{l}.post_attention_norm"],
+                                                              2: self.W[f"layers.{l}.gate"], 3: self.W[f"layers.{l}.up"], 4: self.act_buf},
+                               [H, self.inter, s.act], [s.eps]))
+                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 2: self.hb_ptr(l), 3: self.x_ptr(l + 1)}, [self.inter, H]))
+            elif s.arch == "qwen2":
+                # row-split o/down: fp32 partial -> all-reduce over ranks -> residual add
+                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa_buf, 1: self.W[f"layers.{l}.o"], 4: self.part_f32}, [ko, H]))
+                tasks.append(T(N.TASK_ALLREDUCE, l, {0: self.part_f32}, [H, 0]))
+                tasks.append(T(N.TASK_RESIDUAL_ADD, l, {0: self.part_f32, 1: self.x_ptr(l), 2: self.hb_ptr(l)}, [H]))
+                tasks.append(T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: self.hb_ptr(l), 1: self.V[f"layers.{l}.post_attention_norm"],
+                                                              2: self.W[f"layers.{l}.gate"], 3: self.W[f"layers.{l}.up"], 4: self.act_buf},
+                               [H, self.inter, s.act], [s.eps]))
+                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 4: self.part_f32}, [self.inter, H]))
+                tasks.append(T(N.TASK_ALLREDUCE, l, {0: self.part_f32}, [H, 0]))
+                tasks.append(T(N.TASK_RESIDUAL_ADD, l, {0: self.part_f32, 1: self.hb_ptr(l), 2: self.x_ptr(l + 1)}, [H]))
+            else:
+                # Gemma-shaped: o_proj plain; post-attention norm + residual + pre-ffn norm fused into the gate/up prologue
+                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa_buf, 1: self.W[f"layers.{l}.o"], 3: self.o_buf}, [ko, H]))
+                x_res = self.x_ptr(l)
+                tasks.append(T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: x_res, 1: self.V[f"layers.{l}.pre_feedforward_norm"],
+                                                              2: self.W[f"layers.{l}.gate"], 3: self.W[f"layers.{l}.up"], 4: self.act_buf,
+                                                              9: self.o_buf, 10: self.V[f"layers.{l}.post_attention_norm"], 11: self.hb_ptr(l)},
+                               [H, self.inter, s.act], [s.eps]))
+                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 3: self.d_ptr(l)}, [self.inter, H]))
+        Lr = s.n_layers
+        pend = {}
+        x_fin = self.x_ptr(Lr)
+        if s.arch == "gemma3":
+            pend = {9: self.d_ptr(Lr - 1), 10: self.V[f"layers.{Lr-1}.post_feedforward_norm"], 11: self.x_ptr(Lr)}
+            x_fin = self.hb_ptr(Lr - 1)
+        tasks.append(T(N.TASK_FINAL_RMSNORM_LM_HEAD, -1, {0: x_fin, 1: self.V["final_norm"], 2: self.W["lm_head"], 3: self.logits,
+                                                          4: self.argmax_scratch, 5: self.head_counter, **pend},
+                       [H, self.vocab, self.rank * self.vocab, 0 if tp else 1], [s.eps]))
+        if tp:
+            tasks.append(T(N.TASK_ALLREDUCE, -1, {0: self.argmax_scratch}, [1, 1]))
+            tasks.append(T(N.TASK_ARGMAX_FINALIZE, -1, {4: self.argmax_scratch}, [1]))
+        return tasks
+
+    # ------------------------------------------------------------------ replay
+    def capture(self) -> int:
+        tasks = self.build_dispatches()
+        self.tasks = tasks
+        arr = (N.Task * len(tasks))(*tasks)
+        g = C.c_uint64()
+        N.check(self.rt.L.fk_graph_capture(self.rt.h, arr, len(tasks), C.byref(g)), "fk_graph_capture")
+        self.graph = g.value
+        return self.graph
+
+    def run_eager(self, token: int, offset: int):
+        """One token through the task list without a graph (verification path)."""
+        self.rt.state_set(token, offset)
+        self.rt.launch_batch(self.build_dispatches())
+        return self.rt.state_get()[0]
+
+    def decode_chunk(self, base_offset: int, seed_token: int, count: int):
+        """`count` greedy tokens with on-device token feedback; returns (tokens, gpu_seconds)."""
+        if not self.graph:
+            self.capture()
+        out = np.empty(count, np.uint32)
+        secs = C.c_double()
+        N.check(self.rt.L.fk_decode_chunk(self.rt.h, self.graph, base_offset, seed_token, count, out.ctypes.data, C.byref(secs)), "fk_decode_chunk")
+        return out, secs.value
+
+    def generate(self, seed_token: int, base_offset: int, max_tokens: int, chunk: int = FK_CHUNK):
+        """Greedy loop in chunks of `chunk` tokens (reference: _fast_generate_step)."""
+        toks, secs, tok, off = [], 0.0, seed_token, base_offset
+        while len(toks) < max_tokens:
+            n = min(chunk, max_tokens - len(toks))
+            out, t = self.decode_chunk(off, tok, n)
+            toks.extend(int(v) for v in out); secs += t; tok = int(out[-1]); off += n
+        return np.array(toks, np.uint32), secs
+
+    def profile_nodes(self, repeats: int = 3):
+        if not self.graph:
+            self.capture()
+        n = len(self.tasks)
+        out = (C.c_double * n)()
+        cnt = C.c_int()
+        N.check(self.rt.L.fk_graph_profile_nodes(self.rt.h, self.graph, repeats, out, n, C.byref(cnt)), "fk_graph_profile_nodes")
+        return [(self.tasks[i].kind, self.tasks[i].layer, out[i]) for i in range(n)]
+
+    def hidden_states(self) -> np.ndarray:
+        """Residual stream after every layer of the last decoded token, [n_layers, H] bf16 bits."""
+        s = self.spec
+        return self.rt.download(self.x_ptr(1), (s.n_layers, s.hidden), np.uint16)
+
+    def last_logits(self) -> np.ndarray:
+        if not self.logits:
+            raise N.FusekitError("engine was created without want_logits")
+        return self.rt.download(self.logits, (self.vocab,), np.uint16)
+
+    def comm_init(self, unique_id: bytes):
+        buf = C.create_string_buffer(unique_id, 128)
+        N.check(self.rt.L.fk_comm_init(self.rt.h, buf, self.rank, self.world), "fk_comm_init")
+
+    def close(self):
+        self.rt.close()
+
+
+def comm_unique_id() -> bytes:
+    buf = C.create_string_buffer(128)
+    N.check(N.lib().fk_comm_unique_id(buf, 128), "fk_comm_unique_id")
+    return buf.raw
+
+
+def attach(spec: ModelSpec, capacity: int, device: int = 0, **kw) -> DecodeEngine:
+    """Counterpart of ``fusekit_runtime.attach`` (python/fusekit_runtime/__init__.py:3101-3156):
+    returns an engine whose decode calls run on the CUDA runtime."""
+    return DecodeEngine(spec, capacity, device, **kw)

@@ -1,0 +1,167 @@
+/*
+ * fusekit_cuda.h -- C ABI of the B200 decode runtime (libfusekit_cuda.so).
+ *
+ * This is the boundary a FuseKit host binds in place of its Metal dispatcher
+ * module `_fusekit_runtime_native` (python_runtime/src/lib.rs:1939-1971 in the
+ * FuseKit tree).  Every entry point names the reference function it replaces.
+ * The library owns device memory, the bf16 KV cache, the per-token kernel list
+ * and its CUDA-graph replay; there is no CPU fallback and no PyTorch type in
+ * any signature.  All calls return 0 on success or a negative fk_status; the
+ * text of the last failure on the calling thread is in fk_last_error().
+ * A handle is used from one host thread at a time (the reference serialises
+ * every call behind one mutex, lib.rs:112).
+ */
+#ifndef FUSEKIT_CUDA_H
+#define FUSEKIT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t fk_status;
+enum {
+    FK_OK = 0,
+    FK_ERR_VALUE = -1,    /* bad handle / argument / range (reference: PyValueError, lib.rs:1977-1985) */
+    FK_ERR_CUDA = -2,     /* a CUDA runtime call failed */
+    FK_ERR_STATE = -3,    /* call made in the wrong order */
+    FK_ERR_NCCL = -4,     /* collective backend failure */
+    FK_ERR_DEVICE = -5    /* a kernel reported an error status word */
+};
+
+typedef uint64_t fk_handle;   /* index into a process-global table that only grows (lib.rs:112, 152-168) */
+typedef uint64_t fk_graph;    /* captured per-token kernel list (reference: ICB id, lib.rs:559-569) */
+typedef uint64_t fk_weight;   /* a linear layer's weights in the library's HBM layout */
+typedef uint64_t fk_dptr;     /* raw device address returned by fk_alloc */
+
+/* ---- task kinds: one per fused decode task of the reference task graph --- */
+enum {
+    FK_TASK_STEP_INIT = 0,             /* fusekit_step_init, src/codegen/kernels/mod.rs:542-579 */
+    FK_TASK_EMBED_LOOKUP_DECODE = 1,   /* kernels/embed_lookup_decode.rs:17-104 */
+    FK_TASK_RMSNORM_QKV = 2,           /* kernels/rmsnorm_qkv.rs:53-736 (with QkvDecodeSinks: RoPE + KV store) */
+    FK_TASK_QK_NORM_ROPE_STORE = 3,    /* single.rs:4222-4311 + 4335-4485 + kv_cache_store_decode.rs (Gemma-shaped) */
+    FK_TASK_SDPA_DECODE = 4,           /* kernels/sdpa_decode.rs:697-715, 992-1046 (partial + combine) */
+    FK_TASK_LINEAR_RESIDUAL = 5,       /* kernels/linear_residual.rs:17-388; residual optional (QmvFanout single target) */
+    FK_TASK_RMSNORM_GATEUP_ACT = 6,    /* fused_chain.rs:2902-3552 / qmv_swiglu.rs (SwiGLU or GeGLU-tanh tail) */
+    FK_TASK_FINAL_RMSNORM_LM_HEAD = 7, /* final_rmsnorm_lm_head.rs:144-360 + direct argmax msl.rs:1674-1890 */
+    FK_TASK_ARGMAX_FINALIZE = 8,       /* argmax_logits_finalize.rs:16-115 (+ history capture) */
+    FK_TASK_ALLREDUCE = 9,             /* no reference counterpart: tensor-parallel sum over ranks */
+    FK_TASK_RESIDUAL_ADD = 10,         /* no reference counterpart: y = T(sum + residual) after FK_TASK_ALLREDUCE */
+    FK_TASK_KIND_COUNT = 11
+};
+
+/* activation selector for FK_TASK_RMSNORM_GATEUP_ACT */
+enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
+
+/*
+ * One entry of the per-token dispatch list (reference: the (kernel, buffers,
+ * grid, threadgroup) tuples that dispatch.py:3163-3611 builds and build_icb
+ * encodes).  `buf` holds device addresses from fk_alloc / fk_kv_cache_alloc or
+ * fk_weight ids; unused slots are 0.  Slot meaning per kind:
+ *
+ * EMBED_LOOKUP_DECODE  buf0 table T[V,H]  buf1 x_out T[rows,H]            i0 H  i1 rows         f0 scale
+ * RMSNORM_QKV          buf0 x T[H]  buf1 norm_w  buf2 weight(qkv rows: q|k|v)  buf3 lin_bias|0
+ *                      buf4 q_out  buf5 cache_k  buf6 cache_v  buf7 k_out|0  buf8 v_out|0
+ *                      buf9 pending_y|0  buf10 pending_norm_w  buf11 h_out   (Gemma: x <- T(x + rmsnorm(pending_y)))
+ *                      i0 H  i1 n_q  i2 n_kv  i3 head_dim  i4 capacity  i5 sinks(1 = RoPE + cache store)
+ *                      f0 eps  f1 rope_theta
+ * QK_NORM_ROPE_STORE   buf0 q(in/out)  buf1 k_in  buf2 v_in  buf3 q_norm_w  buf4 k_norm_w  buf5 cache_k  buf6 cache_v
+ *                      i0 n_q  i1 n_kv  i2 head_dim  i3 capacity   f0 eps  f1 rope_theta
+ * SDPA_DECODE          buf0 q  buf1 cache_k  buf2 cache_v  buf3 out  buf4 partials(f32)  buf5 counter(u32)
+ *                      i0 n_q  i1 n_kv  i2 head_dim  i3 capacity   f0 scale
+ * LINEAR_RESIDUAL      buf0 x T[K]  buf1 weight  buf2 residual|0  buf3 y_out T[N]  buf4 y_f32_out|0   i0 K  i1 N
+ * RMSNORM_GATEUP_ACT   buf0 x  buf1 norm_w  buf2 weight(gate)  buf3 weight(up)  buf4 act_out T[I]
+ *                      buf9..11 pending (as RMSNORM_QKV)     i0 H  i1 I  i2 act   f0 eps
+ * FINAL_RMSNORM_LM_HEAD buf0 x  buf1 norm_w  buf2 weight(head)  buf3 logits_out|0  buf4 argmax scratch(u64)
+ *                      buf5 counter(u32)  buf9..11 pending     i0 H  i1 V(local)  i2 vocab_offset  i3 finalize(1/0)   f0 eps
+ * ARGMAX_FINALIZE      buf4 argmax scratch  i0 entries
+ * ALLREDUCE            buf0 f32 buffer   i0 count
+ * RESIDUAL_ADD         buf0 sum f32[N]  buf1 residual T[N]  buf2 y_out T[N]   i0 N
+ */
+typedef struct fk_task {
+    int32_t  kind;
+    int32_t  layer;
+    uint64_t buf[12];
+    int32_t  iarg[8];
+    float    farg[4];
+} fk_task;
+
+/* ---- lifetime and introspection ------------------------------------------ */
+/* replaces load_dispatcher (lib.rs:115-169): binds a device, creates the stream and decode state */
+fk_status fk_open(int device, fk_handle *out);
+fk_status fk_close(fk_handle h);
+/* replaces version / dispatcher_info / kernel_names (lib.rs:1879, 193, 222); JSON text into `buf` */
+const char *fk_version(void);
+fk_status fk_info(fk_handle h, char *buf, size_t cap);
+fk_status fk_kernel_names(char *buf, size_t cap);
+const char *fk_last_error(void);
+
+/* ---- device memory (reference: alloc_uniform lib.rs:1657, register_host_buffer lib.rs:1681; the
+ *      reference wraps unified host memory zero-copy, a discrete GPU needs explicit copies) ------ */
+fk_status fk_alloc(fk_handle h, size_t nbytes, fk_dptr *out);
+fk_status fk_free(fk_handle h, fk_dptr p);
+fk_status fk_upload(fk_handle h, fk_dptr dst, const void *src, size_t nbytes);
+fk_status fk_download(fk_handle h, void *dst, fk_dptr src, size_t nbytes);
+fk_status fk_memset(fk_handle h, fk_dptr dst, int byte, size_t nbytes);
+fk_status fk_sync(fk_handle h);
+/* bf16 KV cache of one layer, layout [n_kv, capacity, head_dim] (sdpa_decode.rs:300-304), zero-filled */
+fk_status fk_kv_cache_alloc(fk_handle h, int n_kv, int capacity, int head_dim, fk_dptr *k_out, fk_dptr *v_out);
+
+/* ---- weights --------------------------------------------------------------
+ * MLX-affine layout at the boundary (src/fusion/ir.rs:236-247): packed u32 [N, K*bits/32] LSB-first,
+ * scales/biases bf16 [N, K/64]; bits 16 = dense bf16 [N,K].  Rows may be filled from several host
+ * tensors (q|k|v concatenation).  fk_weight_finalize freezes the object before first use. */
+fk_status fk_weight_alloc(fk_handle h, int64_t n, int64_t k, int bits, fk_weight *out);
+fk_status fk_weight_upload_rows(fk_handle h, fk_weight w, int64_t dst_row0, int64_t nrows,
+                                const void *packed_or_dense, const void *scales, const void *biases);
+/* synthetic rows generated on the device, bit-identical to the documented counter-based generator:
+ * value(row, col) = std * z(stream, (src_row0 + r) * k_global + k0 + c), quantised per group of 64 */
+fk_status fk_weight_synth_rows(fk_handle h, fk_weight w, int64_t dst_row0, int64_t nrows, uint64_t stream,
+                               float std, int64_t k_global, int64_t src_row0, int64_t k0);
+fk_status fk_weight_finalize(fk_handle h, fk_weight w);
+/* dequantised fp32 [nrows, K] of rows [row0, row0+nrows) -- the bit-exactness probe */
+fk_status fk_weight_dequant(fk_handle h, fk_weight w, int64_t row0, int64_t nrows, float *host_out);
+fk_status fk_weight_nbytes(fk_handle h, fk_weight w, uint64_t *out);
+/* out[i] = bf16(mean + std * z(stream, idx0 + i)) written at a device address */
+fk_status fk_synth_normal_bf16(fk_handle h, fk_dptr dst, uint64_t stream, uint64_t idx0, uint64_t n, float mean, float std);
+
+/* ---- eager launches (reference: dispatch_kernel lib.rs:397, dispatch_batch lib.rs:1722,
+ *      smoke_dispatch lib.rs:238 = elementwise_add_bf16 over n values) ------------------------- */
+fk_status fk_launch(fk_handle h, const fk_task *task);
+fk_status fk_launch_batch(fk_handle h, const fk_task *tasks, int n);
+fk_status fk_smoke(fk_handle h, const uint16_t *a, const uint16_t *b, uint16_t *out, int n);
+
+/* ---- decode state (reference: the token/offset/kv_len uniforms that step_decode pokes,
+ *      lib.rs:884-1012, and the device-side counters of fusekit_step_init) -------------------- */
+fk_status fk_state_set(fk_handle h, uint32_t token, uint32_t offset);
+fk_status fk_state_get(fk_handle h, uint32_t *token, uint32_t *offset, uint32_t *error_word);
+
+/* ---- per-token graph (reference: build_icb lib.rs:459-570, execute_icb lib.rs:718-760,
+ *      submit_icb_async / wait_pending_icb lib.rs:659-715, profile_icb_commands lib.rs:821-869) - */
+fk_status fk_graph_capture(fk_handle h, const fk_task *tasks, int n, fk_graph *out);
+fk_status fk_graph_launch(fk_handle h, fk_graph g, double *gpu_seconds);
+fk_status fk_graph_launch_async(fk_handle h, fk_graph g);
+fk_status fk_wait(fk_handle h, double *gpu_seconds);
+fk_status fk_graph_profile_nodes(fk_handle h, fk_graph g, int repeats, double *seconds_out, int cap, int *n_out);
+fk_status fk_graph_node_count(fk_handle h, fk_graph g, int *n_out);
+
+/* one token: write token/offset, replay, read the argmax back (step_decode, lib.rs:884-1012) */
+fk_status fk_step(fk_handle h, fk_graph g, uint32_t token, uint32_t offset, uint32_t *next_token, double *gpu_seconds);
+/* `count` tokens pre-submitted, token feedback on the device, one wait; out_history[count] on the host
+ * (decode_chunk_gpu_chain, lib.rs:1275-1420) */
+fk_status fk_decode_chunk(fk_handle h, fk_graph g, uint32_t base_offset, uint32_t seed_token, int count,
+                          uint32_t *out_history, double *gpu_seconds);
+/* same result with a host round trip per token (decode_chunk_host_loop, lib.rs:1129-1257) */
+fk_status fk_decode_chunk_host(fk_handle h, fk_graph g, uint32_t base_offset, uint32_t seed_token, int count,
+                               uint32_t *out_history, double *gpu_seconds);
+
+/* ---- tensor parallelism (no reference counterpart; NCCL over NVLink) ------ */
+fk_status fk_comm_unique_id(void *id128, size_t cap);          /* rank 0 makes the 128-byte id */
+fk_status fk_comm_init(fk_handle h, const void *id128, int rank, int world);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUSEKIT_CUDA_H */

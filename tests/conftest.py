@@ -1,0 +1,21 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def runtime():
+    """One CUDA runtime handle shared by the GPU tests; fails loudly without the built library."""
+    from fusekit_b200.runtime import Runtime
+    rt = Runtime(0)
+    yield rt
+    rt.close()

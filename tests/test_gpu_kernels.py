@@ -1,0 +1,238 @@
+"""GPU parity of each decode kernel against the CPU oracle, called through the C ABI."""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+
+from fusekit_b200 import _native as N
+from fusekit_b200.model_spec import stream_id
+from oracle import oracle as O
+from tests.helpers import assert_close_bf16, bf
+
+pytestmark = pytest.mark.gpu
+T = N.Task.make
+
+
+def dev_weight(rt, w: O.QWeight) -> int:
+    wid = rt.weight_alloc(w.n, w.k, w.bits)
+    if w.bits == 16:
+        rt.weight_upload_rows(wid, 0, w.dense)
+    else:
+        rt.weight_upload_rows(wid, 0, w.packed, w.scales, w.biases)
+    rt.weight_finalize(wid)
+    return wid
+
+
+def normal(name, n, std=1.0, mean=0.0, seed=99):
+    return O.fill_normal_bf16(stream_id(seed, name), 0, n, mean, std)
+
+
+def test_smoke_add_is_exact(runtime):
+    a, b = normal("sa", 1024), normal("sb", 1024)
+    got = runtime.smoke(a, b)
+    assert np.array_equal(got, O.f32_to_bf16(bf(a) + bf(b)))      # max abs err 0.0, as the reference's smoke reports
+
+
+@pytest.mark.parametrize("bits", [4, 8, 16])
+def test_device_generator_and_dequant_are_bit_exact(runtime, bits):
+    n, k, kg, row0, k0 = 40, 320, 640, 17, 192
+    s = stream_id(4, f"gen{bits}")
+    ref = O.gen_weight(s, n, k, bits, k_global=kg, row0=row0, k0=k0)
+    wid = runtime.weight_alloc(n + 8, k, bits)
+    runtime.weight_synth_rows(wid, 8, n, s, 0.02, kg, row0, k0)      # rows land at dst row 8
+    runtime.weight_synth_rows(wid, 0, 8, s, 0.02, kg, 0, k0)
+    runtime.weight_finalize(wid)
+    got = runtime.weight_dequant(wid, 8, n, k)
+    want = bf(ref.dense) if bits == 16 else O.dequant(ref)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    up = dev_weight(runtime, ref)                                    # uploaded MLX-layout tensors dequantise identically
+    assert np.array_equal(runtime.weight_dequant(up, 0, n, k).view(np.uint32), want.view(np.uint32))
+
+
+def test_device_normal_fill_matches_oracle(runtime):
+    s = stream_id(4, "vec")
+    p = runtime.alloc(5000 * 2)
+    runtime.synth_normal(p, s, 123, 5000, 1.0, 0.02)
+    assert np.array_equal(runtime.download(p, (5000,), np.uint16), O.fill_normal_bf16(s, 123, 5000, 1.0, 0.02))
+
+
+SHAPES = [(896, 1152), (896, 100), (4864, 896), (3584, 512), (18944, 96), (2560, 64), (64, 8), (5120, 72)]
+
+
+@pytest.mark.parametrize("bits", [4, 8, 16])
+@pytest.mark.parametrize("k,n", SHAPES)
+@pytest.mark.parametrize("residual", [False, True])
+def test_linear_residual(runtime, bits, k, n, residual):
+    w = O.gen_weight(stream_id(1, f"lin{bits}.{k}.{n}"), n, k, bits)
+    x, res = normal(f"x{k}", k), normal(f"r{n}", n)
+    want = O.qmatvec(w, x, res if residual else None)
+    xd, yd = runtime.to_device(x), runtime.alloc(n * 2)
+    rd = runtime.to_device(res) if residual else 0
+    runtime.launch(T(N.TASK_LINEAR_RESIDUAL, 0, {0: xd, 1: dev_weight(runtime, w), 2: rd, 3: yd}, [k, n]))
+    assert_close_bf16(runtime.download(yd, (n,), np.uint16), want, f"linear q{bits} {k}->{n}")
+
+
+@pytest.mark.parametrize("bits", [4, 8, 16])
+@pytest.mark.parametrize("h,nq,nkv,hd,pos,cap", [(896, 14, 2, 64, 37, 64), (512, 4, 2, 128, 700, 512), (256, 2, 1, 256, 5, 16)])
+def test_rmsnorm_qkv_rope_store(runtime, bits, h, nq, nkv, hd, pos, cap):
+    n = (nq + 2 * nkv) * hd
+    w = O.gen_weight(stream_id(2, f"qkv{bits}.{h}"), n, h, bits)
+    x, nw, lb = normal("qx", h, 1.3), normal("qnw", h, 0.02, 1.0), normal("qb", n, 0.02)
+    theta, eps = 1e6, 1e-6
+    w.lin_bias = lb
+    nf = O.rmsnorm(x, nw, eps)
+    acc = O.linear_acc(w, nf)
+    y = O.f32_to_bf16(acc)
+    q = O.rope(y[:nq * hd], nq, hd, pos, theta)
+    kk = O.rope(y[nq * hd:(nq + nkv) * hd], nkv, hd, pos, theta)
+    v = y[(nq + nkv) * hd:]
+    rt = runtime
+    ck, cv, qd = rt.alloc(nkv * cap * hd * 2), rt.alloc(nkv * cap * hd * 2), rt.alloc(nq * hd * 2)
+    rt.state_set(0, pos)
+    rt.launch(T(N.TASK_RMSNORM_QKV, 0, {0: rt.to_device(x), 1: rt.to_device(nw), 2: dev_weight(rt, w), 3: rt.to_device(lb),
+                                        4: qd, 5: ck, 6: cv}, [h, nq, nkv, hd, cap, 1], [eps, theta]))
+    row = pos % cap
+    assert_close_bf16(rt.download(qd, (nq * hd,), np.uint16), q, "q")
+    gk = rt.download(ck, (nkv, cap, hd), np.uint16)
+    gv = rt.download(cv, (nkv, cap, hd), np.uint16)
+    assert_close_bf16(gk[:, row].reshape(-1), kk, "k row")
+    assert_close_bf16(gv[:, row].reshape(-1), v, "v row")
+    mask = np.ones(cap, bool); mask[row] = False
+    assert not gk[:, mask].any() and not gv[:, mask].any()           # only the write row is touched
+    # without sinks the raw projections come back
+    ko, vo = rt.alloc(nkv * hd * 2), rt.alloc(nkv * hd * 2)
+    rt.launch(T(N.TASK_RMSNORM_QKV, 0, {0: rt.to_device(x), 1: rt.to_device(nw), 2: dev_weight(rt, w), 3: rt.to_device(lb),
+                                        4: qd, 7: ko, 8: vo}, [h, nq, nkv, hd, cap, 0], [eps, theta]))
+    assert_close_bf16(rt.download(qd, (nq * hd,), np.uint16), y[:nq * hd], "raw q")
+    assert_close_bf16(rt.download(ko, (nkv * hd,), np.uint16), y[nq * hd:(nq + nkv) * hd], "raw k")
+
+
+@pytest.mark.parametrize("nq,nkv,hd", [(14, 2, 64), (28, 4, 128), (8, 4, 256), (5, 1, 128), (1, 1, 64)])
+@pytest.mark.parametrize("pos,cap", [(0, 64), (62, 64), (63, 64), (64, 200), (136, 200), (199, 200), (1000, 96)])
+def test_sdpa_decode(runtime, nq, nkv, hd, pos, cap):
+    rt = runtime
+    q = normal(f"sq{nq}", nq * hd)
+    ck, cv = normal(f"sk{hd}", nkv * cap * hd), normal(f"sv{hd}", nkv * cap * hd)
+    kv_len = min(pos + 1, cap)
+    scale = 1.0 / math.sqrt(hd)
+    want = O.sdpa_decode(q, ck, cv, nq, nkv, hd, cap, kv_len, scale)
+    chunks = (cap + 63) // 64
+    out, part, cnt = rt.alloc(nq * hd * 2), rt.alloc(nq * chunks * (hd + 2) * 4), rt.alloc(nkv * 4)
+    task = T(N.TASK_SDPA_DECODE, 0, {0: rt.to_device(q), 1: rt.to_device(ck), 2: rt.to_device(cv), 3: out, 4: part, 5: cnt},
+             [nq, nkv, hd, cap], [scale])
+    rt.state_set(0, pos)
+    rt.launch(task)
+    got = rt.download(out, (nq * hd,), np.uint16)
+    assert_close_bf16(got, want, f"sdpa kv_len {kv_len}")
+    rt.launch(task)                                                   # the ticket counters reset themselves
+    assert np.array_equal(rt.download(out, (nq * hd,), np.uint16), got)
+    assert not rt.download(cnt, (nkv,), np.uint32).any()
+
+
+@pytest.mark.parametrize("bits", [4, 8, 16])
+@pytest.mark.parametrize("act", [0, 1])
+@pytest.mark.parametrize("h,inter", [(896, 4864), (256, 100)])
+def test_rmsnorm_gateup_act(runtime, bits, act, h, inter):
+    rt = runtime
+    wg = O.gen_weight(stream_id(3, f"g{bits}.{h}"), inter, h, bits)
+    wu = O.gen_weight(stream_id(3, f"u{bits}.{h}"), inter, h, bits)
+    x, nw = normal("gx", h, 40.0), normal("gnw", h, 0.02, 1.0)       # large activations exercise the tails
+    nf = O.rmsnorm(x, nw, 1e-6)
+    want = O.act(O.linear_acc(wg, nf), O.linear_acc(wu, nf), act)
+    out = rt.alloc(inter * 2)
+    rt.launch(T(N.TASK_RMSNORM_GATEUP_ACT, 0, {0: rt.to_device(x), 1: rt.to_device(nw), 2: dev_weight(rt, wg), 3: dev_weight(rt, wu), 4: out},
+                [h, inter, act], [1e-6]))
+    assert_close_bf16(rt.download(out, (inter,), np.uint16), want, f"gateup act{act}")
+
+
+def test_pending_norm_prologue(runtime):
+    """Gemma-shaped residual advance fused into the next kernel's prologue: x' = T(x + rmsnorm(y, w_post))."""
+    rt, h, inter = runtime, 320, 128
+    wg, wu = O.gen_weight(stream_id(3, "pg"), inter, h, 4), O.gen_weight(stream_id(3, "pu"), inter, h, 4)
+    x, y, wp, nw = normal("px", h), normal("py", h, 3.0), normal("pw", h, 0.02, 1.0), normal("pn", h, 0.02, 1.0)
+    hnew = O.f32_to_bf16(bf(x) + O.rmsnorm(y, wp, 1e-6))
+    nf = O.rmsnorm(hnew, nw, 1e-6)
+    want = O.act(O.linear_acc(wg, nf), O.linear_acc(wu, nf), 1)
+    out, hout = rt.alloc(inter * 2), rt.alloc(h * 2)
+    rt.launch(T(N.TASK_RMSNORM_GATEUP_ACT, 0, {0: rt.to_device(x), 1: rt.to_device(nw), 2: dev_weight(rt, wg), 3: dev_weight(rt, wu), 4: out,
+                                               9: rt.to_device(y), 10: rt.to_device(wp), 11: hout}, [h, inter, 1], [1e-6]))
+    got_h = rt.download(hout, (h,), np.uint16)
+    assert np.mean(got_h != hnew) < 0.02
+    assert_close_bf16(got_h, hnew, "advanced residual")
+    assert_close_bf16(rt.download(out, (inter,), np.uint16), want, "gateup after pending norm")
+
+
+@pytest.mark.parametrize("bits", [4, 8, 16])
+def test_final_head_argmax(runtime, bits):
+    rt, h, v = runtime, 896, 5000
+    w = O.gen_weight(stream_id(5, f"head{bits}"), v, h, bits)
+    x, nw = normal("hx", h, 2.0), normal("hnw", h, 0.02, 1.0)
+    nf = O.rmsnorm(x, nw, 1e-6)
+    want_logits = O.f32_to_bf16(O.linear_acc(w, nf))
+    lg, scr, cnt = rt.alloc(v * 2), rt.alloc(8192), rt.alloc(4)
+    rt.state_set(7, 11)
+    rt.launch(T(N.TASK_FINAL_RMSNORM_LM_HEAD, -1, {0: rt.to_device(x), 1: rt.to_device(nw), 2: dev_weight(rt, w), 3: lg, 4: scr, 5: cnt},
+                [h, v, 0, 1], [1e-6]))
+    got = rt.download(lg, (v,), np.uint16)
+    assert_close_bf16(got, want_logits, "logits")
+    tok, off, err = rt.state_get()
+    assert err == 0 and off == 12                                     # the state advanced on the device
+    assert tok == O.argmax_bf16(got)                                  # argmax of the T-rounded logits, lowest index on ties
+    top = np.sort(bf(want_logits))[-2:]
+    if top[1] - top[0] > 0.02:
+        assert tok == O.argmax_bf16(want_logits)
+
+
+def test_argmax_tie_breaks_to_lowest_index(runtime):
+    rt, h, v = runtime, 64, 300
+    # identical rows -> identical logits everywhere: the winner must be index 0 (+ vocab offset)
+    row = O.gen_weight(stream_id(6, "tie"), 1, h, 16)
+    w = O.QWeight(v, h, 16, None, None, None, dense=np.repeat(row.dense, v, axis=0))
+    x, nw = normal("tx", h), normal("tnw", h, 0.02, 1.0)
+    scr, cnt = rt.alloc(8192), rt.alloc(4)
+    rt.state_set(0, 0)
+    rt.launch(T(N.TASK_FINAL_RMSNORM_LM_HEAD, -1, {0: rt.to_device(x), 1: rt.to_device(nw), 2: dev_weight(rt, w), 4: scr, 5: cnt},
+                [h, v, 1000, 1], [1e-6]))
+    assert rt.state_get()[0] == 1000
+
+
+def test_qk_norm_rope_store(runtime):
+    rt, nq, nkv, hd, cap, pos = runtime, 4, 2, 256, 16, 37
+    q, k, v = normal("nq", nq * hd, 2.0), normal("nk", nkv * hd, 2.0), normal("nv", nkv * hd)
+    wq, wk = normal("wq", hd, 0.02, 1.0), normal("wk", hd, 0.02, 1.0)
+    def hn(vec, heads, w):
+        return np.concatenate([O.f32_to_bf16(O.rmsnorm(vec[i * hd:(i + 1) * hd], w, 1e-6)) for i in range(heads)])
+    want_q = O.rope(hn(q, nq, wq), nq, hd, pos, 1e4)
+    want_k = O.rope(hn(k, nkv, wk), nkv, hd, pos, 1e4)
+    qd, ck, cv = rt.to_device(q), rt.alloc(nkv * cap * hd * 2), rt.alloc(nkv * cap * hd * 2)
+    rt.state_set(0, pos)
+    rt.launch(T(N.TASK_QK_NORM_ROPE_STORE, 0, {0: qd, 1: rt.to_device(k), 2: rt.to_device(v), 3: rt.to_device(wq), 4: rt.to_device(wk), 5: ck, 6: cv},
+                [nq, nkv, hd, cap], [1e-6, 1e4]))
+    assert_close_bf16(rt.download(qd, (nq * hd,), np.uint16), want_q, "q")
+    row = pos % cap
+    assert_close_bf16(rt.download(ck, (nkv, cap, hd), np.uint16)[:, row].reshape(-1), want_k, "k")
+    assert np.array_equal(rt.download(cv, (nkv, cap, hd), np.uint16)[:, row].reshape(-1), v)
+
+
+def test_embed_lookup(runtime):
+    rt, vocab, h = runtime, 50, 96
+    table = normal("emb", vocab * h, 0.02)
+    out = rt.alloc(h * 2)
+    rt.state_set(31, 0)
+    rt.launch(T(N.TASK_EMBED_LOOKUP_DECODE, -1, {0: rt.to_device(table), 1: out}, [h, 1], [50.5]))
+    want = O.f32_to_bf16(bf(table.reshape(vocab, h)[31]) * np.float32(50.5))
+    assert np.array_equal(rt.download(out, (h,), np.uint16), want)
+
+
+def test_bad_arguments_are_refused(runtime):
+    rt = runtime
+    with pytest.raises(N.FusekitError, match="weight missing"):
+        rt.launch(T(N.TASK_LINEAR_RESIDUAL, 0, {0: rt.alloc(64), 1: 9999, 3: rt.alloc(64)}, [64, 8]))
+    w = O.gen_weight(stream_id(1, "bad"), 8, 64, 4)
+    with pytest.raises(N.FusekitError, match="shape mismatch"):
+        rt.launch(T(N.TASK_LINEAR_RESIDUAL, 0, {0: rt.alloc(64), 1: dev_weight(rt, w), 3: rt.alloc(64)}, [128, 8]))
+    with pytest.raises(N.FusekitError, match="unknown task kind"):
+        rt.launch(T(77))
+    wid = C.c_uint64()
+    assert rt.L.fk_weight_alloc(rt.h, 8, 100, 4, C.byref(wid)) == -1     # k must be a multiple of the group size

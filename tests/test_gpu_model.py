@@ -1,0 +1,132 @@
+"""GPU parity of whole decode steps: per-layer hidden states, greedy tokens, graph replay."""
+import os
+
+import numpy as np
+import pytest
+
+from fusekit_b200.model_spec import CONFIGS
+from fusekit_b200.runtime import DecodeEngine
+from oracle import oracle as O
+from tests.helpers import MAX_ABS_TOL, REL_RMS_TOL, max_abs, oracle_config, rel_rms, vector_provider, weight_provider
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def check_hidden(got, want, what):
+    """north-star bar: <= 1e-2 max-abs and <= 1e-3 relative RMS per layer, in bf16"""
+    for l in range(want.shape[0]):
+        ma, rr = max_abs(got[l], want[l]), rel_rms(got[l], want[l])
+        assert ma <= MAX_ABS_TOL and rr <= REL_RMS_TOL, f"{what} layer {l}: max-abs {ma:.4g}, rel-rms {rr:.4g}"
+
+
+@pytest.mark.parametrize("name", ["tiny-qwen", "tiny-gemma"])
+@pytest.mark.parametrize("bits", [4, 8, 16])
+def test_tiny_models_match_oracle(name, bits):
+    spec = CONFIGS[name].with_bits(bits)
+    ctx, steps = (20, 24) if name == "tiny-qwen" else (37, 24)
+    cap = ctx + steps + 8
+    m = O.Model(oracle_config(spec, cap)); m.prefill_kv(ctx)
+    eng = DecodeEngine(spec, cap)
+    try:
+        eng.load_synthetic(); eng.prefill_kv_synthetic(ctx)
+        # the device-generated cache equals the oracle's
+        for l, (ck, cv, c) in enumerate(eng.cache):
+            n = spec.n_kv * c * spec.head_dim
+            assert np.array_equal(eng.rt.download(ck, (n,), np.uint16), m.vec(l, 7, n)), f"cache_k layer {l}"
+        tok = 3
+        want_tok, want_hid, _ = m.step(tok, ctx, want_hidden=True)
+        got_tok = eng.run_eager(tok, ctx)
+        check_hidden(eng.hidden_states(), want_hid[:spec.n_layers], f"{name} q{bits}")
+        assert got_tok == want_tok
+        # restart both sides and compare the greedy stream (graph replay, on-device token feedback)
+        m2 = O.Model(oracle_config(spec, cap)); m2.prefill_kv(ctx)
+        want, _ = m2.greedy(3, ctx, steps)
+        eng.prefill_kv_synthetic(ctx)
+        got, secs = eng.decode_chunk(ctx, 3, steps)
+        assert list(got) == list(want) and secs > 0
+        if bits == 4:
+            g = np.load(os.path.join(GOLD, f"model_{name}.npz"))
+            assert list(got) == list(g["tokens"])
+        # host-loop variant gives the same tokens
+        eng.prefill_kv_synthetic(ctx)
+        import ctypes as C
+        from fusekit_b200 import _native as N
+        out = np.empty(steps, np.uint32)
+        N.check(eng.rt.L.fk_decode_chunk_host(eng.rt.h, eng.graph, ctx, 3, steps, out.ctypes.data, None), "host loop")
+        assert list(out) == list(want)
+    finally:
+        eng.close()
+
+
+def test_uploaded_weights_equal_device_generated_weights():
+    spec = CONFIGS["tiny-qwen"]
+    a, b = DecodeEngine(spec, 64), DecodeEngine(spec, 64)
+    try:
+        a.load_synthetic()
+        b.load_from(weight_provider(spec), vector_provider(spec))
+        for name in a.W:
+            n, k = (spec.hidden, spec.inter) if name.endswith("down") else (8, spec.hidden)
+            wa = a.rt.weight_dequant(a.W[name], 0, 8, k if not name.endswith(".o") else spec.n_q * spec.head_dim)
+            wb = b.rt.weight_dequant(b.W[name], 0, 8, k if not name.endswith(".o") else spec.n_q * spec.head_dim)
+            assert np.array_equal(wa.view(np.uint32), wb.view(np.uint32)), name
+        for name in a.V:
+            n = 64
+            assert np.array_equal(a.rt.download(a.V[name], (n,), np.uint16), b.rt.download(b.V[name], (n,), np.uint16)), name
+        ta, _ = a.decode_chunk(0, 5, 8)
+        tb, _ = b.decode_chunk(0, 5, 8)
+        assert list(ta) == list(tb)
+    finally:
+        a.close(); b.close()
+
+
+def test_config1_qwen05b_prompt_then_64_greedy_steps():
+    """Benchmark config 1: Qwen2.5-0.5B-shaped q4, a 32-token uniform-random prompt then greedy decode.
+    Greedy tokens must be identical for the first 64 decode steps; hidden states within tolerance."""
+    spec = CONFIGS["qwen2.5-0.5b"]
+    from fusekit_b200.model_spec import stream_id
+    prompt = [O.uniform_u32(stream_id(spec.seed, "prompt"), i, spec.vocab) for i in range(32)]
+    cap = 32 + 64 + 8
+    m = O.Model(oracle_config(spec, cap))
+    eng = DecodeEngine(spec, cap)
+    try:
+        eng.load_synthetic(); eng.capture()
+        for i, t in enumerate(prompt[:-1]):            # prompt tokens one position at a time
+            m.step(t, i)
+        for i, t in enumerate(prompt[:-1]):
+            eng.decode_chunk(i, t, 1)
+        want_tok, want_hid, _ = m.step(prompt[-1], 31, want_hidden=True)
+        got, _ = eng.decode_chunk(31, prompt[-1], 1)
+        check_hidden(eng.hidden_states(), want_hid[:spec.n_layers], "0.5B")
+        assert int(got[0]) == want_tok
+        want, _ = m.greedy(want_tok, 32, 63)
+        got, secs = eng.decode_chunk(32, want_tok, 63)
+        assert list(got) == list(want), f"first mismatch at step {int(np.argmax(got != want))}"
+    finally:
+        eng.close()
+
+
+@pytest.mark.parametrize("name,bits", [("qwen2.5-7b", 4), ("qwen2.5-7b", 8), ("gemma3-4b", 4), ("qwen2.5-32b", 4)])
+def test_full_size_projections_on_sampled_rows(runtime, name, bits):
+    """At benchmark sizes the oracle checks sampled output rows of every projection shape: the device
+    generates the full tensor, the CPU regenerates 48 rows of it and recomputes their outputs."""
+    from fusekit_b200 import _native as N
+    from fusekit_b200.model_spec import stream_id
+    spec = CONFIGS[name].with_bits(bits)
+    hd, H, I = spec.head_dim, spec.hidden, spec.inter
+    rt = runtime
+    for leaf, k, n in (("q_proj", H, spec.n_q * hd), ("o_proj", spec.n_q * hd, H), ("down_proj", I, H), ("up_proj", H, I)):
+        s = stream_id(spec.seed, f"layers.0.{leaf}")
+        wid = rt.weight_alloc(n, k, bits)
+        rt.weight_synth_rows(wid, 0, n, s, 0.02, k, 0, 0)
+        rt.weight_finalize(wid)
+        x = O.fill_normal_bf16(stream_id(1, f"x.{leaf}"), 0, k, 0.0, 1.0)
+        yd = rt.alloc(n * 2)
+        rt.launch(N.Task.make(N.TASK_LINEAR_RESIDUAL, 0, {0: rt.to_device(x), 1: wid, 3: yd}, [k, n]))
+        got = rt.download(yd, (n,), np.uint16)
+        for r0 in (0, (n // 2) // 16 * 16, n - 16):
+            ref = O.gen_weight(s, 16, k, bits, k_global=k, row0=r0)
+            assert np.array_equal(rt.weight_dequant(wid, r0, 16, k).view(np.uint32), O.dequant(ref).view(np.uint32))
+            want = O.qmatvec(ref, x)
+            ma, rr = max_abs(got[r0:r0 + 16], want), rel_rms(got[r0:r0 + 16], want)
+            assert ma <= MAX_ABS_TOL * max(1.0, float(np.abs(O.bf16_to_f32(want)).max())) and rr <= 4 * REL_RMS_TOL, (leaf, r0, ma, rr)
