@@ -404,6 +404,11 @@ class DecodeEngine:
         s = self.spec
         return self.rt.download(self.x_ptr(1), (s.n_layers, s.hidden), np.uint16)
 
+    def residual_stream(self) -> np.ndarray:
+        """Embedding output followed by the residual stream after every layer, [n_layers + 1, H]."""
+        s = self.spec
+        return self.rt.download(self.x_ptr(0), (s.n_layers + 1, s.hidden), np.uint16)
+
     def last_logits(self) -> np.ndarray:
         if not self.logits:
             raise N.FusekitError("engine was created without want_logits")

@@ -480,61 +480,69 @@ static void head_norm(bf16_t *v, int n_heads, int hd, const bf16_t *w, float eps
     }
 }
 
-/* One decode step for token `tok` at position `pos` (single rank: tp_size 1,
- * or one rank's slice when partial_* reduction is done by the caller -- only
- * tp_size 1 is supported by this whole-model step).
- * hidden_out (optional): [n_layers+1, H] T -- the residual stream after each
- * layer, then the final-normed vector.  logits_out (optional): [vocab] T.
- * Order of ops: scripts/debug_qwen2_layer0_forced.py:70-103 (Qwen2 shape),
- * scripts/debug_gemma4_layer0.py:126-157 minus v_norm/per-layer inputs (Gemma shape). */
-uint32_t fko_decode_step(fko_model *M, uint32_t tok, uint32_t pos, bf16_t *hidden_out, bf16_t *logits_out) {
+/* One layer applied in place to the residual stream x (T[H]) of the token at `pos`; writes the
+ * layer's K/V row into its cache.  Order of ops: scripts/debug_qwen2_layer0_forced.py:70-103
+ * (Qwen2 shape), scripts/debug_gemma4_layer0.py:126-157 minus v_norm/per-layer inputs (Gemma shape).
+ * Single rank only (tp_size 1). */
+void fko_layer_step(fko_model *M, int l, bf16_t *x, uint32_t pos) {
     const fko_config *c = &M->c; const int H = c->hidden, hd = c->head_dim, nq = c->n_q, nkv = c->n_kv, I = c->inter;
-    bf16_t *x = (bf16_t *)malloc((size_t)H * 2), *h = (bf16_t *)malloc((size_t)H * 2), *tmp = (bf16_t *)malloc((size_t)H * 2);
+    bf16_t *h = (bf16_t *)malloc((size_t)H * 2), *tmp = (bf16_t *)malloc((size_t)H * 2);
     float *nf = (float *)malloc(sizeof(float) * (size_t)(H > I ? H : I));
     bf16_t *q = (bf16_t *)malloc((size_t)nq * hd * 2), *k = (bf16_t *)malloc((size_t)nkv * hd * 2), *v = (bf16_t *)malloc((size_t)nkv * hd * 2);
     bf16_t *a = (bf16_t *)malloc((size_t)nq * hd * 2), *s = (bf16_t *)malloc((size_t)I * 2);
     float *ga = (float *)malloc(sizeof(float) * (size_t)I), *ua = (float *)malloc(sizeof(float) * (size_t)I);
     float *af = (float *)malloc(sizeof(float) * (size_t)(nq * hd > I ? nq * hd : I));
+    const float scale = 1.0f / sqrtf((float)hd);          /* sdpa_decode.rs:248-252 */
+    fko_layer *Y = &M->L[l];
+    fko_rmsnorm(x, Y->w_in, H, c->eps, nf);
+    fko_linear_apply(&Y->q, nf, NULL, q, NULL);
+    fko_linear_apply(&Y->k, nf, NULL, k, NULL);
+    fko_linear_apply(&Y->v, nf, NULL, v, NULL);
+    if (c->arch == 1) { head_norm(q, nq, hd, Y->w_qn, c->eps); head_norm(k, nkv, hd, Y->w_kn, c->eps); }
+    fko_rope(q, nq, hd, pos, Y->theta); fko_rope(k, nkv, hd, pos, Y->theta);
+    /* cache row = pos % capacity; kv_len = min(pos+1, capacity)
+     * (rope_kv_cache_store_decode.rs:95; python/fusekit_runtime/dispatch.py:2324-2354) */
+    int64_t row = (int64_t)pos % Y->cap, kv_len = (int64_t)pos + 1 < Y->cap ? (int64_t)pos + 1 : Y->cap;
+    for (int hh = 0; hh < nkv; ++hh) {
+        memcpy(Y->ck + ((int64_t)hh * Y->cap + row) * hd, k + hh * hd, (size_t)hd * 2);
+        memcpy(Y->cv + ((int64_t)hh * Y->cap + row) * hd, v + hh * hd, (size_t)hd * 2);
+    }
+    fko_sdpa_decode(q, Y->ck, Y->cv, nq, nkv, hd, Y->cap, kv_len, scale, a);
+    for (int i = 0; i < nq * hd; ++i) af[i] = bf2f(a[i]);
+    if (c->arch == 0) {
+        fko_linear_apply(&Y->o, af, x, h, NULL);                    /* h = T(Wo a + x) */
+        fko_rmsnorm(h, Y->w_post, H, c->eps, nf);
+    } else {
+        fko_linear_apply(&Y->o, af, NULL, tmp, NULL);               /* o = T(Wo a) */
+        fko_rmsnorm(tmp, Y->w_postattn, H, c->eps, nf);
+        for (int i = 0; i < H; ++i) h[i] = f2bf(bf2f(x[i]) + nf[i]); /* h = T(x + norm(o)) */
+        fko_rmsnorm(h, Y->w_preffn, H, c->eps, nf);
+    }
+    fko_linear_apply(&Y->gate, nf, NULL, NULL, ga);
+    fko_linear_apply(&Y->up, nf, NULL, NULL, ua);
+    fko_act(ga, ua, I, c->arch == 1, s);
+    for (int i = 0; i < I; ++i) af[i] = bf2f(s[i]);
+    if (c->arch == 0) {
+        fko_linear_apply(&Y->down, af, h, x, NULL);                 /* x = T(Wd s + h) */
+    } else {
+        fko_linear_apply(&Y->down, af, NULL, tmp, NULL);
+        fko_rmsnorm(tmp, Y->w_postffn, H, c->eps, nf);
+        for (int i = 0; i < H; ++i) x[i] = f2bf(bf2f(h[i]) + nf[i]);
+    }
+    free(h); free(tmp); free(nf); free(q); free(k); free(v); free(a); free(s); free(ga); free(ua); free(af);
+}
+
+/* One decode step for token `tok` at position `pos`.
+ * hidden_out (optional): [n_layers+1, H] T -- the residual stream after each layer, then the
+ * final-normed vector.  logits_out (optional): [vocab] T. */
+uint32_t fko_decode_step(fko_model *M, uint32_t tok, uint32_t pos, bf16_t *hidden_out, bf16_t *logits_out) {
+    const fko_config *c = &M->c; const int H = c->hidden;
+    bf16_t *x = (bf16_t *)malloc((size_t)H * 2);
+    float *nf = (float *)malloc(sizeof(float) * (size_t)H);
     /* embed: x = T(embed[tok] * scale) (embed_lookup_decode.rs:95-98) */
     for (int i = 0; i < H; ++i) x[i] = f2bf(bf2f(M->embed[(int64_t)tok * H + i]) * M->embed_scale);
-    const float scale = 1.0f / sqrtf((float)hd);          /* sdpa_decode.rs:248-252 */
     for (int l = 0; l < c->n_layers; ++l) {
-        fko_layer *Y = &M->L[l];
-        fko_rmsnorm(x, Y->w_in, H, c->eps, nf);
-        fko_linear_apply(&Y->q, nf, NULL, q, NULL);
-        fko_linear_apply(&Y->k, nf, NULL, k, NULL);
-        fko_linear_apply(&Y->v, nf, NULL, v, NULL);
-        if (c->arch == 1) { head_norm(q, nq, hd, Y->w_qn, c->eps); head_norm(k, nkv, hd, Y->w_kn, c->eps); }
-        fko_rope(q, nq, hd, pos, Y->theta); fko_rope(k, nkv, hd, pos, Y->theta);
-        /* cache row = pos % capacity; kv_len = min(pos+1, capacity)
-         * (rope_kv_cache_store_decode.rs:95; python/fusekit_runtime/dispatch.py:2324-2354) */
-        int64_t row = (int64_t)pos % Y->cap, kv_len = (int64_t)pos + 1 < Y->cap ? (int64_t)pos + 1 : Y->cap;
-        for (int hh = 0; hh < nkv; ++hh) {
-            memcpy(Y->ck + ((int64_t)hh * Y->cap + row) * hd, k + hh * hd, (size_t)hd * 2);
-            memcpy(Y->cv + ((int64_t)hh * Y->cap + row) * hd, v + hh * hd, (size_t)hd * 2);
-        }
-        fko_sdpa_decode(q, Y->ck, Y->cv, nq, nkv, hd, Y->cap, kv_len, scale, a);
-        for (int i = 0; i < nq * hd; ++i) af[i] = bf2f(a[i]);
-        if (c->arch == 0) {
-            fko_linear_apply(&Y->o, af, x, h, NULL);                    /* h = T(Wo a + x) */
-            fko_rmsnorm(h, Y->w_post, H, c->eps, nf);
-        } else {
-            fko_linear_apply(&Y->o, af, NULL, tmp, NULL);               /* o = T(Wo a) */
-            fko_rmsnorm(tmp, Y->w_postattn, H, c->eps, nf);
-            for (int i = 0; i < H; ++i) h[i] = f2bf(bf2f(x[i]) + nf[i]); /* h = T(x + norm(o)) */
-            fko_rmsnorm(h, Y->w_preffn, H, c->eps, nf);
-        }
-        fko_linear_apply(&Y->gate, nf, NULL, NULL, ga);
-        fko_linear_apply(&Y->up, nf, NULL, NULL, ua);
-        fko_act(ga, ua, I, c->arch == 1, s);
-        for (int i = 0; i < I; ++i) af[i] = bf2f(s[i]);
-        if (c->arch == 0) {
-            fko_linear_apply(&Y->down, af, h, x, NULL);                 /* x = T(Wd s + h) */
-        } else {
-            fko_linear_apply(&Y->down, af, NULL, tmp, NULL);
-            fko_rmsnorm(tmp, Y->w_postffn, H, c->eps, nf);
-            for (int i = 0; i < H; ++i) x[i] = f2bf(bf2f(h[i]) + nf[i]);
-        }
+        fko_layer_step(M, l, x, pos);
         if (hidden_out) memcpy(hidden_out + (int64_t)l * H, x, (size_t)H * 2);
     }
     fko_rmsnorm(x, M->w_final, H, c->eps, nf);
@@ -543,8 +551,17 @@ uint32_t fko_decode_step(fko_model *M, uint32_t tok, uint32_t pos, bf16_t *hidde
     fko_linear_apply(&M->head, nf, NULL, logits, NULL);
     uint32_t next = fko_argmax_bf16(logits, c->vocab);
     if (!logits_out) free(logits);
-    free(x); free(h); free(tmp); free(nf); free(q); free(k); free(v); free(a); free(s); free(ga); free(ua); free(af);
+    free(x); free(nf);
     return next;
+}
+/* logits of the head for a given residual stream (final norm + lm_head) */
+uint32_t fko_head_step(fko_model *M, const bf16_t *x, bf16_t *logits_out) {
+    const fko_config *c = &M->c; const int H = c->hidden;
+    float *nf = (float *)malloc(sizeof(float) * (size_t)H);
+    fko_rmsnorm(x, M->w_final, H, c->eps, nf);
+    fko_linear_apply(&M->head, nf, NULL, logits_out, NULL);
+    free(nf);
+    return fko_argmax_bf16(logits_out, c->vocab);
 }
 
 /* greedy loop: tokens[i+1] = step(tokens[i], pos0+i); returns seconds spent */

@@ -82,6 +82,8 @@ def lib():
     L.fko_model_layer_theta.restype = f32; L.fko_model_layer_theta.argtypes = [vp, i32]
     L.fko_model_embed_scale.restype = f32; L.fko_model_embed_scale.argtypes = [vp]
     L.fko_decode_step.restype = u32; L.fko_decode_step.argtypes = [vp, u32, u32, vp, vp]
+    L.fko_layer_step.restype = None; L.fko_layer_step.argtypes = [vp, i32, vp, u32]
+    L.fko_head_step.restype = u32; L.fko_head_step.argtypes = [vp, vp, vp]
     L.fko_decode_greedy.restype = C.c_double; L.fko_decode_greedy.argtypes = [vp, u32, u32, i32, vp]
     L.fko_num_threads.restype = i32
     L.fko_f32_to_bf16.restype = C.c_uint16; L.fko_f32_to_bf16.argtypes = [f32]
@@ -267,6 +269,17 @@ class Model:
         lg = np.empty(c.vocab, np.uint16) if want_logits else None
         nxt = lib().fko_decode_step(self._h, tok, pos, _p(hid), _p(lg))
         return int(nxt), hid, lg
+
+    def layer_step(self, layer: int, x_bf16: np.ndarray, pos: int) -> np.ndarray:
+        """Layer `layer` applied to a given residual stream (teacher-forced per-layer check)."""
+        x = np.ascontiguousarray(x_bf16, np.uint16).copy()
+        lib().fko_layer_step(self._h, layer, _p(x), pos)
+        return x
+
+    def head_step(self, x_bf16: np.ndarray):
+        lg = np.empty(self.cfg.vocab, np.uint16)
+        tok = lib().fko_head_step(self._h, _p(np.ascontiguousarray(x_bf16, np.uint16)), _p(lg))
+        return int(tok), lg
 
     def greedy(self, first_tok: int, pos0: int, steps: int):
         out = np.empty(steps, np.uint32)
