@@ -256,7 +256,13 @@ class Model:
         if not ptr:
             return None
         buf = (C.c_byte * (n * 2)).from_address(ptr)
-        return np.frombuffer(buf, dtype=np.uint16)
+        return np.frombuffer(buf, dtype=np.uint16)       # a writable view of the oracle's own memory
+
+    def set_cache(self, layer: int, k_bits: np.ndarray, v_bits: np.ndarray):
+        """Overwrite a layer's K/V cache (bf16 bits, [n_kv, capacity, head_dim])."""
+        n = k_bits.size
+        self.vec(layer, 7, n)[:] = np.asarray(k_bits, np.uint16).reshape(-1)
+        self.vec(layer, 8, n)[:] = np.asarray(v_bits, np.uint16).reshape(-1)
 
     def layer_cap(self, l): return int(lib().fko_model_layer_cap(self._h, l))
     def layer_sliding(self, l): return bool(lib().fko_model_layer_sliding(self._h, l))

@@ -53,3 +53,20 @@ def assert_close_bf16(got_bits, want_bits, what="", max_abs_tol=MAX_ABS_TOL, rel
     ref = max(1.0, float(np.max(np.abs(bf(want_bits))))) if scale_abs else 1.0
     assert ma <= max_abs_tol * ref, f"{what}: max-abs {ma:.4g} > {max_abs_tol * ref:.4g}"
     assert rr <= rel_rms_tol, f"{what}: relative RMS {rr:.4g} > {rel_rms_tol}"
+
+
+def compare_greedy(got_tokens, oracle_model, first_tok: int, pos0: int, tie_ulps: float = 2.0):
+    """Walk the oracle along the GPU's token stream.  Returns (mismatches, ties): a mismatch where the
+    oracle's own margin between its winner and the GPU's token is at most `tie_ulps` bf16 ulps of the logit
+    is a near-tie (random-init logits are almost flat; the reference itself documents token flips
+    from reordered fp32 sums); anything larger is a real mismatch."""
+    tok, mism, ties = first_tok, [], []
+    for i, g in enumerate(int(t) for t in got_tokens):
+        want, _, lg = oracle_model.step(tok, pos0 + i, want_logits=True)
+        if want != g:
+            l = bf(lg)
+            margin = float(l[want] - l[g])
+            ulp = 2.0 ** (np.floor(np.log2(max(abs(float(l[want])), 1e-30))) - 7)
+            (ties if margin <= tie_ulps * ulp else mism).append((i, want, g, margin, ulp))
+        tok = g
+    return mism, ties
