@@ -59,6 +59,7 @@ def lib():
         "fk_memset": [u64, u64, i32, sz], "fk_sync": [u64], "fk_kv_cache_alloc": [u64, i32, i32, i32, P(u64), P(u64)],
         "fk_weight_alloc": [u64, i64, i64, i32, P(u64)], "fk_weight_upload_rows": [u64, u64, i64, i64, vp, vp, vp],
         "fk_weight_synth_rows": [u64, u64, i64, i64, u64, f32, i64, i64, i64], "fk_weight_finalize": [u64, u64],
+        "fk_weight_set_rows": [u64, u64, i32, i32, i32], "fk_weight_pair": [u64, u64, u64, P(u64)],
         "fk_weight_dequant": [u64, u64, i64, i64, vp], "fk_weight_nbytes": [u64, u64, P(u64)],
         "fk_synth_normal_bf16": [u64, u64, u64, u64, u64, f32, f32],
         "fk_launch": [u64, P(Task)], "fk_launch_batch": [u64, P(Task), i32], "fk_smoke": [u64, vp, vp, vp, i32],
@@ -69,7 +70,7 @@ def lib():
         "fk_step": [u64, u64, u32, u32, P(u32), P(C.c_double)],
         "fk_decode_chunk": [u64, u64, u32, u32, i32, vp, P(C.c_double)],
         "fk_decode_chunk_host": [u64, u64, u32, u32, i32, vp, P(C.c_double)],
-        "fk_comm_unique_id": [vp, sz], "fk_comm_init": [u64, vp, i32, i32],
+        "fk_debug_timeline": [u64, u64], "fk_comm_unique_id": [vp, sz], "fk_comm_init": [u64, vp, i32, i32],
     }
     for name, args in sig.items():
         fn = getattr(L, name)

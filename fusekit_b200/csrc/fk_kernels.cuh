@@ -4,6 +4,8 @@
 // shapes the streamed kernels (fk_stream.cuh) do not take.
 #pragma once
 #include "fk_common.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
 
 // ---------------------------------------------------------------- activations in shared memory
 // x is staged per block as fp32 in a swizzled order so that a lane reading the 32 (or 16, 8)
@@ -257,100 +259,327 @@ __global__ void k_qk_norm_rope_store(const FkState *st, QkNormArgs a) {
 
 struct SdpaArgs {
     const uint16_t *q, *ck, *cv; uint16_t *out; float *part; uint32_t *counter;
-    int n_q, n_kv, hd, capacity, chunk; float scale;
+    int n_q, n_kv, hd, capacity, chunk; float scale; unsigned long long *tl;
 };
-#define FK_SDPA_KEYS 64        // keys per block (the reference's BLOCK, sdpa_decode.rs:35-55)
+__device__ __forceinline__ void sd_stamp(unsigned long long *tl, int slot) {
+    if (tl && threadIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tl[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = t; }
+}
+#define FK_SDPA_KEYS 32        // keys per block
 #define FK_SDPA_MAXG 8         // q heads sharing one kv head
-// Split-K GQA decode attention.  Block (chunk, kv head) scores 64 keys against every q head of the
-// group, so K/V are read once per group: s = dot(q,k)*scale, partial (m, l, o[hd]) in fp32
-// (sdpa_decode.rs:697-715).  The last block of a kv head to finish merges the chunks and writes
-// T(o * (1/l)) (sdpa_decode.rs:992-1046) -- a ticket counter, no waiting.  kv_len = min(pos+1, capacity).
-__global__ void k_sdpa_decode(const FkState *st, SdpaArgs a) {
+#define FK_SDPA_THREADS 256
+__host__ __device__ inline size_t sdpa_smem_bytes(int G, int hd, int chunks) {
+    return sizeof(float) * (size_t)(G * hd + G * FK_SDPA_KEYS + 2 * G + (FK_SDPA_THREADS / hd) * G * hd + G * chunks + 16);
+}
+// Split-K GQA decode attention.  Block (chunk, kv head) scores 32 keys against every q head of the group, so
+// K/V are read once per group: s = dot(q,k)*scale, partial (m, l, o[hd]) in fp32 (sdpa_decode.rs:697-715).
+// The last block of a kv head to finish merges the chunks and writes T(o * (1/l)) (sdpa_decode.rs:992-1046)
+// -- a ticket counter, no waiting.  kv_len = min(pos+1, capacity).  head_dim in {64, 128, 256}.
+__global__ void __launch_bounds__(FK_SDPA_THREADS) k_sdpa_decode(const FkState *st, SdpaArgs a) {
     extern __shared__ float sm[];
     const int G = a.n_q / a.n_kv, hd = a.hd, kvh = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x;
-    float *qs = sm;                        // [G][hd]
-    float *sc = qs + G * hd;               // [G][64]
-    float *ml = sc + G * FK_SDPA_KEYS;     // [G][2]
+    const int nparts = FK_SDPA_THREADS / hd;               // key slices of the PV phase
+    float *qs = sm;                                        // [G][hd]
+    float *sc = qs + G * hd;                               // [G][KEYS]
+    float *ml = sc + G * FK_SDPA_KEYS;                     // [G][2]
+    float *op = ml + 2 * G;                                // [nparts][G][hd]
+    float *wc = op + nparts * G * hd;                      // [G][chunks] merge weights
     __shared__ int is_last;
+    sd_stamp(a.tl, 0);
     pdl_launch_dependents(); pdl_wait();
     const uint32_t pos = st->offset;
     const int kv_len = (int)min(pos + 1u, (uint32_t)a.capacity);
     const int n_active = (kv_len + FK_SDPA_KEYS - 1) / FK_SDPA_KEYS;
     if (chunk >= n_active) return;
     const int k0 = chunk * FK_SDPA_KEYS, bs = min(FK_SDPA_KEYS, kv_len - k0);
-    for (int i = tid; i < G * hd; i += blockDim.x) qs[i] = bf2f(a.q[kvh * G * hd + i]);
-    __syncthreads();
     const uint16_t *K = a.ck + ((size_t)kvh * a.capacity + k0) * hd, *V = a.cv + ((size_t)kvh * a.capacity + k0) * hd;
-    if (tid < bs) {
+    // V values of this thread's (dim, key slice), fetched before the score phase so the latency overlaps it
+    const int vd = tid % hd, vpart = tid / hd, kpp = FK_SDPA_KEYS / nparts;
+    uint16_t vreg[FK_SDPA_KEYS];
+#pragma unroll
+    for (int i = 0; i < FK_SDPA_KEYS; ++i) vreg[i] = 0;
+    if (hd == 128) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { const int key = vpart * 16 + i; if (key < bs) vreg[i] = __ldg(V + (size_t)key * hd + vd); }
+    } else if (hd == 64) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const int key = vpart * 8 + i; if (key < bs) vreg[i] = __ldg(V + (size_t)key * hd + vd); }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { if (i < bs) vreg[i] = __ldg(V + (size_t)i * hd + vd); }
+    }
+    for (int i = tid; i < G * hd; i += FK_SDPA_THREADS) qs[i] = bf2f(a.q[kvh * G * hd + i]);
+    __syncthreads();
+    sd_stamp(a.tl, 1);
+    {   // scores: 8 threads per key, each over head_dim/8 dims
+        const int key = tid >> 3, part = tid & 7, dpp = hd >> 3;
         float dot[FK_SDPA_MAXG];
 #pragma unroll
         for (int g = 0; g < FK_SDPA_MAXG; ++g) dot[g] = 0.0f;
-        const uint4 *kr = reinterpret_cast<const uint4 *>(K + (size_t)tid * hd);
-        for (int c = 0; c < (hd >> 3); ++c) {
-            const uint4 v = __ldg(kr + c);
-            const float kf[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
+        if (key < bs) {
+            const uint4 *kr = reinterpret_cast<const uint4 *>(K + (size_t)key * hd + part * dpp);
+            for (int c = 0; c < (dpp >> 3); ++c) {
+                const uint4 v = __ldg(kr + c);
+                const float kf[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
+                const float *qp = qs + part * dpp + c * 8;
 #pragma unroll
-            for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) {
+                for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) dot[g] = fmaf(qs[g * hd + c * 8 + j], kf[j], dot[g]);
+                    for (int j = 0; j < 8; ++j) dot[g] = fmaf(qp[g * hd + j], kf[j], dot[g]);
+                }
             }
         }
 #pragma unroll
-        for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) sc[g * FK_SDPA_KEYS + tid] = dot[g] * a.scale;
+        for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) {
+            float d = dot[g];
+            d += __shfl_xor_sync(0xffffffffu, d, 1); d += __shfl_xor_sync(0xffffffffu, d, 2); d += __shfl_xor_sync(0xffffffffu, d, 4);
+            if (part == 0) sc[g * FK_SDPA_KEYS + key] = key < bs ? d * a.scale : -INFINITY;
+        }
     }
     __syncthreads();
-    const int lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
-    for (int g = wid; g < G; g += nw) {
-        const float s0 = lane < bs ? sc[g * FK_SDPA_KEYS + lane] : -INFINITY;
-        const float s1 = lane + 32 < bs ? sc[g * FK_SDPA_KEYS + lane + 32] : -INFINITY;
-        const float m = warp_max(fmaxf(s0, s1));
-        const float p0 = lane < bs ? expf(s0 - m) : 0.0f, p1 = lane + 32 < bs ? expf(s1 - m) : 0.0f;
-        sc[g * FK_SDPA_KEYS + lane] = p0; sc[g * FK_SDPA_KEYS + lane + 32] = p1;
-        const float l = warp_sum(p0 + p1);
-        if (lane == 0) { ml[2 * g] = m; ml[2 * g + 1] = l; }
+    sd_stamp(a.tl, 2);
+    const int lane = tid & 31, wid = tid >> 5;
+    if (wid < G) {      // softmax pieces of head `wid` over the 32 keys
+        const float s0 = sc[wid * FK_SDPA_KEYS + lane];
+        const float m = warp_max(s0);
+        const float p0 = lane < bs ? expf(s0 - m) : 0.0f;
+        sc[wid * FK_SDPA_KEYS + lane] = p0;
+        const float l = warp_sum(p0);
+        if (lane == 0) { ml[2 * wid] = m; ml[2 * wid + 1] = l; }
     }
     __syncthreads();
-    const int stride = hd + 2;
-    if (tid < hd) {
+    {   // o[g][d] over this thread's key slice
         float o[FK_SDPA_MAXG];
 #pragma unroll
         for (int g = 0; g < FK_SDPA_MAXG; ++g) o[g] = 0.0f;
-        for (int i = 0; i < bs; ++i) {
-            const float v = bf2f(__ldg(V + (size_t)i * hd + tid));
 #pragma unroll
-            for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) o[g] = fmaf(sc[g * FK_SDPA_KEYS + i], v, o[g]);
+        for (int i = 0; i < FK_SDPA_KEYS; ++i) {
+            if (i < kpp) {
+                const float v = bf2f(vreg[i]); const int key = vpart * kpp + i;
+#pragma unroll
+                for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) o[g] = fmaf(sc[g * FK_SDPA_KEYS + key], v, o[g]);
+            }
         }
 #pragma unroll
-        for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) {
-            float *p = a.part + ((size_t)(kvh * G + g) * a.chunk + chunk) * stride;
-            p[2 + tid] = o[g];
-            if (tid == 0) { p[0] = ml[2 * g]; p[1] = ml[2 * g + 1]; }
-        }
+        for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) op[(vpart * G + g) * hd + vd] = o[g];
     }
+    __syncthreads();
+    const int stride = hd + 2;
+    for (int i = tid; i < G * hd; i += FK_SDPA_THREADS) {
+        float o = 0.0f;
+        for (int q = 0; q < nparts; ++q) o += op[q * G * hd + i];
+        const int g = i / hd, d = i - g * hd;
+        float *p = a.part + ((size_t)(kvh * G + g) * a.chunk + chunk) * stride;
+        if (n_active == 1) a.out[(kvh * G + g) * hd + d] = f2bf(o * __fdiv_rn(1.0f, ml[2 * g + 1]));
+        else { p[2 + d] = o; if (d == 0) { p[0] = ml[2 * g]; p[1] = ml[2 * g + 1]; } }
+    }
+    if (n_active == 1) return;
+    sd_stamp(a.tl, 3);
     __threadfence();
     __syncthreads();
+    sd_stamp(a.tl, 4);
     if (tid == 0) {
         const uint32_t t = atomicAdd(a.counter + kvh, 1u);
         is_last = (t == (uint32_t)(n_active - 1));
         if (is_last) a.counter[kvh] = 0u;
     }
     __syncthreads();
+    sd_stamp(a.tl, 5);
     if (!is_last) return;
     __threadfence();
-    if (tid < hd) {
-        for (int g = 0; g < G; ++g) {
-            const float *p = a.part + (size_t)(kvh * G + g) * a.chunk * stride;
-            float M = -INFINITY;
-            for (int c = 0; c < n_active; ++c) M = fmaxf(M, __ldcg(p + (size_t)c * stride));
-            float L = 0.0f, O = 0.0f;
-            for (int c = 0; c < n_active; ++c) {
-                const float w = expf(__ldcg(p + (size_t)c * stride) - M);
-                L = fmaf(__ldcg(p + (size_t)c * stride + 1), w, L);
-                O = fmaf(__ldcg(p + (size_t)c * stride + 2 + tid), w, O);
+    if (wid < G) {      // merge weights w_c = exp(m_c - M) and the normaliser, one warp per head
+        const float *p = a.part + (size_t)(kvh * G + wid) * a.chunk * stride;
+        float M = -INFINITY;
+        for (int c = lane; c < n_active; c += 32) M = fmaxf(M, __ldcg(p + (size_t)c * stride));
+        M = warp_max(M);
+        float L = 0.0f;
+        for (int c = lane; c < n_active; c += 32) {
+            const float w = expf(__ldcg(p + (size_t)c * stride) - M);
+            wc[wid * a.chunk + c] = w;
+            L = fmaf(__ldcg(p + (size_t)c * stride + 1), w, L);
+        }
+        L = warp_sum(L);
+        if (lane == 0) ml[2 * wid + 1] = L;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * hd; i += FK_SDPA_THREADS) {
+        const int g = i / hd, d = i - g * hd;
+        const float *p = a.part + (size_t)(kvh * G + g) * a.chunk * stride + 2 + d;
+        float O = 0.0f;
+        for (int c = 0; c < n_active; ++c) O = fmaf(__ldcg(p + (size_t)c * stride), wc[g * a.chunk + c], O);
+        a.out[(kvh * G + g) * hd + d] = f2bf(O * __fdiv_rn(1.0f, ml[2 * g + 1]));
+    }
+    __syncthreads();
+    sd_stamp(a.tl, 6);
+}
+
+// ---------------------------------------------------------------- cluster SDPA
+#define FK_SDPA_CL 8            // CTAs per kv head (portable cluster size); they split the keys
+#define FK_SDPA_CW 16           // warps per CTA
+#define FK_SDPA_KPW 8           // keys per warp iteration (4 lanes per key)
+__host__ __device__ inline size_t sdpa_cl_smem_bytes(int G, int hd) {
+    return sizeof(float) * (size_t)(G * hd + FK_SDPA_CW * G * (hd + 2) + G * (hd + 2) + 16);
+}
+// Split-K GQA decode attention on a thread-block cluster: the CTAs of a cluster share one kv head and take
+// contiguous key ranges; inside a CTA every warp runs an online softmax over 8-key blocks, four lanes per key for
+// the scores (s = dot(q,k)*scale in fp32) and head_dim/32 output dims per lane for p*V, with running (m, l, o)
+// (sdpa_decode.rs:1064-1211).  K and V rows of a block are requested together, and the first block before the
+// dependency wait: every cache row but the newest was written by earlier tokens.  Warp partials merge through
+// shared memory, CTA partials through distributed shared memory (sdpa_decode.rs:992-1046 combine),
+// out = T(o * (1/l)).  No global scratch, no spinning.
+template <int HD, int MAXG>
+__global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_cluster(const FkState *st, SdpaArgs a) {
+    extern __shared__ float sm[];
+    cg::cluster_group cluster = cg::this_cluster();
+    constexpr int DPL = HD / 32;                 // output dims per lane
+    constexpr int KV4 = HD / 32;                 // uint4 per quarter row (HD/4 dims * 2 B / 16)
+    constexpr int NT = FK_SDPA_CW * 32;
+    const int G = a.n_q / a.n_kv, kvh = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int rank = (int)cluster.block_rank(), CL = (int)cluster.num_blocks();
+    const int stride = HD + 2;
+    float *qs = sm;                              // [G][HD]
+    float *wpart = qs + G * HD;                  // [CW][G][HD+2]
+    float *cpart = wpart + FK_SDPA_CW * G * stride;   // [G][HD+2]   read by the other CTAs of the cluster
+    sd_stamp(a.tl, 0);
+    pdl_launch_dependents();
+    const uint32_t pos = st->offset;             // advanced by the previous token's head kernel, not by the QKV kernel in flight
+    const int kv_len = (int)min(pos + 1u, (uint32_t)a.capacity);
+    const int newest = (int)(pos % (uint32_t)a.capacity);
+    const int kpc = ((kv_len + CL * FK_SDPA_KPW - 1) / (CL * FK_SDPA_KPW)) * FK_SDPA_KPW;
+    const int k_begin = rank * kpc, k_end = min(kv_len, k_begin + kpc);
+    const uint16_t *K = a.ck + (size_t)kvh * a.capacity * HD, *V = a.cv + (size_t)kvh * a.capacity * HD;
+    const int part = lane & 3, kl = lane >> 2;
+    uint4 kreg[KV4]; uint4 vraw[FK_SDPA_KPW];    // V rows: DPL bf16 per lane, in the low words of vraw
+    auto load_k = [&](int kb, int skip) {
+        const int key = kb + kl;
+        const uint4 *kr = reinterpret_cast<const uint4 *>(K + (size_t)key * HD + part * (HD / 4));
+#pragma unroll
+        for (int c = 0; c < KV4; ++c) kreg[c] = (key < k_end && key != skip) ? __ldg(kr + c) : make_uint4(0, 0, 0, 0);
+    };
+    auto load_v_row = [&](int row) -> uint4 {
+        uint4 r = make_uint4(0, 0, 0, 0);
+        if (DPL == 4) { const uint2 v = *(reinterpret_cast<const uint2 *>(V + (size_t)row * HD) + lane); r.x = v.x; r.y = v.y; }
+        else if (DPL == 2) r.x = *(reinterpret_cast<const uint32_t *>(V + (size_t)row * HD) + lane);
+        else r = *(reinterpret_cast<const uint4 *>(V + (size_t)row * HD) + lane);
+        return r;
+    };
+    auto load_v = [&](int kb, int skip) {
+#pragma unroll
+        for (int kk = 0; kk < FK_SDPA_KPW; ++kk) vraw[kk] = (kb + kk < k_end && kb + kk != skip) ? load_v_row(kb + kk) : make_uint4(0, 0, 0, 0);
+    };
+    int kb = k_begin + wid * FK_SDPA_KPW;
+    if (kb < k_end) { load_k(kb, newest); load_v(kb, newest); }
+    pdl_wait();
+    for (int i = tid; i < G * HD; i += NT) qs[i] = bf2f(a.q[kvh * G * HD + i]);
+    float m[MAXG], l[MAXG], o[MAXG][DPL];
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) { m[g] = -INFINITY; l[g] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) o[g][j] = 0.0f; }
+    if (kb < k_end && newest >= kb && newest < kb + FK_SDPA_KPW && newest < k_end) {       // the row the QKV kernel just wrote
+        if (kb + kl == newest) load_k(kb, -1);
+#pragma unroll
+        for (int kk = 0; kk < FK_SDPA_KPW; ++kk) if (kb + kk == newest) vraw[kk] = load_v_row(newest);
+    }
+    __syncthreads();
+    sd_stamp(a.tl, 1);
+    for (bool first = true; kb < k_end; kb += FK_SDPA_CW * FK_SDPA_KPW, first = false) {
+        const bool valid = kb + kl < k_end;
+        if (!first) { load_k(kb, -1); load_v(kb, -1); }
+        float dot[MAXG];
+#pragma unroll
+        for (int g = 0; g < MAXG; ++g) dot[g] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < KV4; ++c) {
+            const uint4 v = kreg[c];
+            const float kf[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
+            const float *qp = qs + part * (HD / 4) + c * 8;
+#pragma unroll
+            for (int g = 0; g < MAXG; ++g) if (g < G) {
+                const float4 q0 = *reinterpret_cast<const float4 *>(qp + g * HD), q1 = *reinterpret_cast<const float4 *>(qp + g * HD + 4);
+                dot[g] = fmaf(q0.x, kf[0], dot[g]); dot[g] = fmaf(q0.y, kf[1], dot[g]); dot[g] = fmaf(q0.z, kf[2], dot[g]); dot[g] = fmaf(q0.w, kf[3], dot[g]);
+                dot[g] = fmaf(q1.x, kf[4], dot[g]); dot[g] = fmaf(q1.y, kf[5], dot[g]); dot[g] = fmaf(q1.z, kf[6], dot[g]); dot[g] = fmaf(q1.w, kf[7], dot[g]);
             }
-            a.out[(kvh * G + g) * hd + tid] = f2bf(O * __fdiv_rn(1.0f, L));
+        }
+        float p[MAXG];
+        if (first) sd_stamp(a.tl, 5);
+#pragma unroll
+        for (int g = 0; g < MAXG; ++g) if (g < G) {
+            float d = dot[g];
+            d += __shfl_xor_sync(0xffffffffu, d, 1); d += __shfl_xor_sync(0xffffffffu, d, 2);
+            const float s = valid ? d * a.scale : -INFINITY;
+            float mb = s;
+            mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 4)); mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 8));
+            mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
+            const float mn = fmaxf(m[g], mb);                 // finite: the block holds at least one valid key
+            const float alpha = expf(m[g] - mn);
+            p[g] = valid ? expf(s - mn) : 0.0f;
+            float ls = p[g];
+            ls += __shfl_xor_sync(0xffffffffu, ls, 4); ls += __shfl_xor_sync(0xffffffffu, ls, 8); ls += __shfl_xor_sync(0xffffffffu, ls, 16);
+            l[g] = fmaf(l[g], alpha, ls); m[g] = mn;
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) o[g][j] *= alpha;
+        }
+        if (first) sd_stamp(a.tl, 7);
+#pragma unroll
+        for (int kk = 0; kk < FK_SDPA_KPW; ++kk) {
+#pragma unroll
+            for (int g = 0; g < MAXG; ++g) if (g < G) {
+                const float pk = __shfl_sync(0xffffffffu, p[g], kk * 4);
+#pragma unroll
+                for (int j = 0; j < DPL; ++j) {
+                    const uint32_t wv = j < 2 ? vraw[kk].x : j < 4 ? vraw[kk].y : j < 6 ? vraw[kk].z : vraw[kk].w;
+                    o[g][j] = fmaf(pk, (j & 1) ? bf_hi(wv) : bf_lo(wv), o[g][j]);
+                }
+            }
         }
     }
+    sd_stamp(a.tl, 2);
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) if (g < G) {
+        float *w = wpart + (wid * G + g) * stride;
+        if (lane == 0) { w[0] = m[g]; w[1] = l[g]; }
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) w[2 + lane * DPL + j] = o[g][j];
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += NT) {             // fold the warps of this CTA
+        const int g = i / HD, d = i - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < FK_SDPA_CW; ++w) M = fmaxf(M, wpart[(w * G + g) * stride]);
+        float L = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int w = 0; w < FK_SDPA_CW; ++w) {
+            const float *pw = wpart + (w * G + g) * stride;
+            const float e = pw[0] == -INFINITY ? 0.0f : expf(pw[0] - M);
+            L = fmaf(pw[1], e, L); O = fmaf(pw[2 + d], e, O);
+        }
+        float *cp = cpart + g * stride;
+        cp[2 + d] = O;
+        if (d == 0) { cp[0] = M; cp[1] = L; }
+    }
+    sd_stamp(a.tl, 3);
+    cluster.sync();
+    sd_stamp(a.tl, 4);
+    const int total = G * HD, per = (total + CL - 1) / CL;
+    for (int i = rank * per + tid; i < min(total, (rank + 1) * per); i += NT) {      // fold the CTAs: this CTA's slice of outputs
+        const int g = i / HD, d = i - g * HD;
+        float mm[FK_SDPA_CL], ll[FK_SDPA_CL], oo[FK_SDPA_CL];
+#pragma unroll
+        for (int r = 0; r < FK_SDPA_CL; ++r) {
+            if (r < CL) { const float *rp = cluster.map_shared_rank(cpart, r) + g * stride; mm[r] = rp[0]; ll[r] = rp[1]; oo[r] = rp[2 + d]; }
+            else { mm[r] = -INFINITY; ll[r] = 0.0f; oo[r] = 0.0f; }
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < FK_SDPA_CL; ++r) M = fmaxf(M, mm[r]);
+        float L = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int r = 0; r < FK_SDPA_CL; ++r) { const float e = mm[r] == -INFINITY ? 0.0f : expf(mm[r] - M); L = fmaf(ll[r], e, L); O = fmaf(oo[r], e, O); }
+        a.out[(kvh * G + g) * HD + d] = f2bf(O * __fdiv_rn(1.0f, L));
+    }
+    cluster.sync();                                      // peers may still be reading this CTA's partial
+    sd_stamp(a.tl, 6);
 }
 
 struct LinArgs { const uint16_t *x; WView W; const uint16_t *residual; uint16_t *y; float *y_f32; int k, n; };

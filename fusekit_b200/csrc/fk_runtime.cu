@@ -5,6 +5,7 @@
 #include "fk_common.cuh"
 #include "fk_kernels.cuh"
 #include "fk_synth.cuh"
+#include "fk_stream.cuh"
 
 #include <dlfcn.h>
 #include <math.h>
@@ -56,9 +57,14 @@ static fk_status nccl_load() {
 // ------------------------------------------------------------------ objects
 struct Weight {
     long long n = 0, k = 0; int bits = 0; bool finalized = false;
-    uint32_t *w = nullptr; uint16_t *s = nullptr, *b = nullptr;
+    uint32_t *w = nullptr; uint16_t *s = nullptr, *b = nullptr;       // MLX-affine rows (until repacked)
     size_t w_bytes = 0, sb_bytes = 0;
+    // tiled layout (fk_stream.cuh): set by fk_weight_finalize / fk_weight_pair for 4- and 8-bit weights
+    bool tiled = false; uint4 *units = nullptr; int ntiles = 0, nsb = 0; size_t unit_bytes = 0;
+    int rows_kind = FK_ROWS_PLAIN, hd = 0, n_rot = 0;
     WView view() const { WView v; v.w = w; v.s = s; v.b = b; v.n = n; v.k = k; v.bits = bits; return v; }
+    TiledW tview() const { TiledW t; t.units = units; t.ntiles = ntiles; t.nsb = nsb; t.n = (int)n; t.k = (int)k; t.bits = bits;
+                           t.rows_kind = rows_kind; t.hd = hd; t.n_rot = n_rot; return t; }
 };
 struct Graph {
     std::vector<fk_task> tasks;
@@ -71,7 +77,9 @@ struct Ctx {
     uint32_t *pinned = nullptr;                 // host staging for state / history
     std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
     bool pending = false; bool pdl = true; int sm_count = 148;
+    bool use_tiled = true; int stages = 2; int prefetch = 1; int force_warps = 0; bool sdpa_cluster = true;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
+    unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
 };
 static std::mutex g_mu;
@@ -88,8 +96,11 @@ static Ctx *get(fk_handle h) {
     if (!c) return fail(FK_ERR_VALUE, "invalid handle %llu", (unsigned long long)(h)); \
     CU(cudaSetDevice(c->device))
 
+// opt in to the full 227 KB of shared memory per block (minus the kernel's static part)
 template <typename K> static cudaError_t big_smem(K kern) {
-    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncAttributes fa; cudaError_t e = cudaFuncGetAttributes(&fa, kern);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - (int)fa.sharedSizeBytes);
 }
 
 extern "C" const char *fk_last_error(void) { return g_err; }
@@ -110,6 +121,14 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     CU(cudaMalloc(&c->history, sizeof(uint32_t) * c->hist_cap)); CU(cudaMemset(c->history, 0, sizeof(uint32_t) * c->hist_cap));
     CU(cudaMallocHost(&c->pinned, sizeof(uint32_t) * (c->hist_cap + 64)));
     const char *e = getenv("FK_PDL"); if (e && e[0] == '0') c->pdl = false;
+    e = getenv("FK_LAYOUT"); if (e && !strcmp(e, "mlx")) c->use_tiled = false;
+    e = getenv("FK_STAGES"); if (e && atoi(e) >= 1 && atoi(e) <= 4) c->stages = atoi(e);
+    e = getenv("FK_SDPA"); if (e && !strcmp(e, "ticket")) c->sdpa_cluster = false;
+    e = getenv("FK_WARPS"); if (e) c->force_warps = atoi(e);
+    e = getenv("FK_PREFETCH"); if (e && atoi(e) >= 0 && atoi(e) <= 64) c->prefetch = atoi(e);
+#define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>))
+    BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head);
+    CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
     CU(big_smem(k_linear_residual<4>)); CU(big_smem(k_linear_residual<8>)); CU(big_smem(k_linear_residual<16>));
     CU(big_smem(k_rmsnorm_gateup_act<4>)); CU(big_smem(k_rmsnorm_gateup_act<8>)); CU(big_smem(k_rmsnorm_gateup_act<16>));
@@ -124,7 +143,7 @@ extern "C" fk_status fk_close(fk_handle h) {
     CTX(h);
     cudaStreamSynchronize(c->stream);
     for (auto &g : c->graphs) { if (g.exec) cudaGraphExecDestroy(g.exec); if (g.graph) cudaGraphDestroy(g.graph); }
-    for (auto &w : c->weights) { cudaFree(w.w); cudaFree(w.s); cudaFree(w.b); }
+    for (auto &w : c->weights) { cudaFree(w.w); cudaFree(w.s); cudaFree(w.b); cudaFree(w.units); }
     for (void *p : c->allocs) cudaFree(p);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     cudaFree(c->state); cudaFree(c->history); cudaFreeHost(c->pinned);
@@ -237,18 +256,72 @@ extern "C" fk_status fk_weight_synth_rows(fk_handle h, fk_weight wid, int64_t r0
     CU(cudaGetLastError());
     return FK_OK;
 }
+static fk_status repack(Ctx *c, Weight *dstw, const Weight *a, const Weight *b2) {
+    const int kpu = a->bits == 4 ? 512 : 256;                    // activations per unit
+    dstw->ntiles = (int)((dstw->n + 15) / 16); dstw->nsb = (int)((a->k + kpu - 1) / kpu);
+    dstw->unit_bytes = (size_t)dstw->ntiles * dstw->nsb * FK_UNIT_BYTES;
+    CU(cudaMalloc(&dstw->units, dstw->unit_bytes));
+    SrcW sa{a->w, a->s, a->b}, sb{b2 ? b2->w : a->w, b2 ? b2->s : a->s, b2 ? b2->b : a->b};
+    const long long tot = (long long)dstw->ntiles * dstw->nsb * FK_UNIT_VEC;
+    k_repack_tiled<<<(unsigned)((tot + 255) / 256), 256, 0, c->stream>>>(sa, sb, dstw->units, a->n, (int)a->k, a->bits, dstw->ntiles, dstw->nsb,
+                                                                        dstw->rows_kind, dstw->hd, dstw->n_rot);
+    CU(cudaGetLastError());
+    CU(cudaStreamSynchronize(c->stream));
+    dstw->tiled = true;
+    return FK_OK;
+}
+static void drop_rows(Weight *w) { cudaFree(w->w); cudaFree(w->s); cudaFree(w->b); w->w = nullptr; w->s = w->b = nullptr; }
+
+extern "C" fk_status fk_weight_set_rows(fk_handle h, fk_weight wid, int kind, int head_dim, int n_rot_rows) {
+    CTX(h); Weight *w = get_w(c, wid);
+    if (!w) return fail(FK_ERR_VALUE, "bad weight id");
+    if (w->finalized) return fail(FK_ERR_STATE, "weight already finalized");
+    if (kind != FK_ROWS_PLAIN && kind != FK_ROWS_ROPE_PAIRS) return fail(FK_ERR_VALUE, "row order must be plain (0) or rope pairs (1)");
+    if (kind == FK_ROWS_ROPE_PAIRS && (head_dim <= 0 || head_dim % 16 || n_rot_rows % head_dim || n_rot_rows > w->n)) return fail(FK_ERR_VALUE, "rope pairs need head_dim % 16 == 0 and whole heads");
+    w->rows_kind = kind; w->hd = head_dim; w->n_rot = n_rot_rows;
+    return FK_OK;
+}
 extern "C" fk_status fk_weight_finalize(fk_handle h, fk_weight wid) {
     CTX(h); Weight *w = get_w(c, wid);
     if (!w) return fail(FK_ERR_VALUE, "bad weight id");
+    if (w->finalized) return FK_OK;
+    if (c->use_tiled && w->bits != 16) {
+        fk_status s = repack(c, w, w, nullptr); if (s) return s;
+        drop_rows(w);
+    } else { w->rows_kind = FK_ROWS_PLAIN; }
     w->finalized = true;
+    return FK_OK;
+}
+extern "C" fk_status fk_weight_pair(fk_handle h, fk_weight gate, fk_weight up, fk_weight *out) {
+    CTX(h); Weight *g = get_w(c, gate), *u = get_w(c, up);
+    if (!g || !u || !out || gate == up) return fail(FK_ERR_VALUE, "bad weight ids");
+    if (g->finalized || u->finalized) return fail(FK_ERR_STATE, "pair the weights before finalizing them");
+    if (g->n != u->n || g->k != u->k || g->bits != u->bits) return fail(FK_ERR_VALUE, "gate and up must have one shape");
+    if (!c->use_tiled || g->bits == 16) return fail(FK_ERR_STATE, "pairing needs the tiled layout (4- or 8-bit weights)");
+    Weight p; p.n = 2 * g->n; p.k = g->k; p.bits = g->bits; p.rows_kind = FK_ROWS_GATE_UP;
+    fk_status s = repack(c, &p, g, u); if (s) return s;
+    p.finalized = true; p.w_bytes = g->w_bytes + u->w_bytes; p.sb_bytes = g->sb_bytes + u->sb_bytes;
+    drop_rows(g); drop_rows(u); g->finalized = u->finalized = true; g->n = u->n = 0;      // consumed
+    g = u = nullptr;
+    c->weights.push_back(p); *out = c->weights.size();
     return FK_OK;
 }
 extern "C" fk_status fk_weight_dequant(fk_handle h, fk_weight wid, int64_t row0, int64_t nrows, float *host_out) {
     CTX(h); Weight *w = get_w(c, wid);
-    if (!w || !host_out || row0 < 0 || nrows <= 0 || row0 + nrows > w->n) return fail(FK_ERR_VALUE, "fk_weight_dequant: bad arguments");
+    if (!w || !host_out || row0 < 0 || nrows <= 0) return fail(FK_ERR_VALUE, "fk_weight_dequant: bad arguments");
+    // a gate/up pair is addressed as rows [0, n/2) = gate, [n/2, n) = up
+    const long long half = w->rows_kind == FK_ROWS_GATE_UP ? w->n / 2 : w->n;
+    const int which = (w->rows_kind == FK_ROWS_GATE_UP && row0 >= half) ? 1 : 0;
+    const long long r0 = which ? row0 - half : row0;
+    if (r0 + nrows > half) return fail(FK_ERR_VALUE, "fk_weight_dequant: row range out of bounds");
     float *d = nullptr; const long long tot = nrows * w->k;
     CU(cudaMalloc(&d, tot * 4));
-    k_dequant<<<(unsigned)((tot + 255) / 256), 256, 0, c->stream>>>(w->w, w->s, w->b, w->k, w->bits, row0, nrows, d);
+    if (w->tiled) {
+        const long long th = (long long)w->ntiles * w->nsb * 256;
+        k_dequant_tiled<<<(unsigned)((th + 255) / 256), 256, 0, c->stream>>>(w->tview(), which, r0, nrows, d);
+    } else {
+        k_dequant<<<(unsigned)((tot + 255) / 256), 256, 0, c->stream>>>(w->w, w->s, w->b, w->k, w->bits, row0, nrows, d);
+    }
     cudaError_t e = cudaMemcpyAsync(host_out, d, tot * 4, cudaMemcpyDeviceToHost, c->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
     cudaFree(d);
@@ -258,7 +331,7 @@ extern "C" fk_status fk_weight_dequant(fk_handle h, fk_weight wid, int64_t row0,
 extern "C" fk_status fk_weight_nbytes(fk_handle h, fk_weight wid, uint64_t *out) {
     CTX(h); Weight *w = get_w(c, wid);
     if (!w || !out) return fail(FK_ERR_VALUE, "bad weight id");
-    *out = w->w_bytes + 2 * w->sb_bytes;
+    *out = w->tiled ? w->unit_bytes : w->w_bytes + 2 * w->sb_bytes;
     return FK_OK;
 }
 extern "C" fk_status fk_synth_normal_bf16(fk_handle h, fk_dptr dst, uint64_t stream, uint64_t idx0, uint64_t n, float mean, float std) {
@@ -281,6 +354,19 @@ static cudaError_t launch(Ctx *c, void (*kern)(KA...), dim3 grid, dim3 block, si
     c->launches++;
     return cudaLaunchKernelEx(&cfg, kern, KA(args)...);
 }
+template <typename... KA, typename... A>
+static cudaError_t launch_cluster(Ctx *c, void (*kern)(KA...), dim3 grid, dim3 block, size_t smem, int cluster_x, A... args) {
+    cudaLaunchConfig_t cfg; memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = c->stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = cluster_x; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = c->pdl ? 2 : 1;
+    c->launches++;
+    return cudaLaunchKernelEx(&cfg, kern, KA(args)...);
+}
 #define BITS_SWITCH(bits, CALL)                  \
     switch (bits) {                              \
         case 4: { constexpr int B = 4; CALL; break; }   \
@@ -295,7 +381,62 @@ static int grid_for(Ctx *c, long long units, int warps_per_block) {
     return (int)(blocks < 1 ? 1 : blocks);
 }
 
-static fk_status run_task(Ctx *c, const fk_task &t) {
+// Work split of a streamed kernel.  Blocks have 8 warps and sit two to an SM when their shared memory (ring +
+// staged activations) allows, else 16 warps and one per SM.  A warp owns whole row tiles when the grid has at least
+// one tile per warp; otherwise a block takes one tile at a time and its warps split K.
+struct Shape { int splits, grid, warps; size_t smem; };
+static Shape plan_shape(Ctx *c, const Weight *w) {
+    Shape s;
+    s.warps = 8;
+    s.smem = stream_smem_bytes(w->nsb, c->stages, 8);
+    if (s.smem > 113 * 1024 || c->force_warps == 16) { s.warps = 16; s.smem = stream_smem_bytes(w->nsb, c->stages, 16); }
+    const int slots = c->sm_count * (16 / s.warps), gw = slots * s.warps;
+    long long blocks;
+    s.splits = 1;
+    if (w->ntiles >= gw) blocks = slots;
+    else {
+        s.splits = w->nsb < s.warps ? w->nsb : s.warps;
+        if (s.splits == 1) blocks = (w->ntiles + s.warps - 1) / s.warps;          // a single super-block: warp per tile
+        else blocks = w->ntiles < slots ? w->ntiles : slots;
+    }
+    s.grid = (int)(blocks < 1 ? 1 : blocks);
+    return s;
+}
+static Weight *get_w(Ctx *c, fk_weight w);
+// the tiled weight a task streams, if any
+static Weight *task_stream_weight(Ctx *c, const fk_task *t) {
+    if (!t) return nullptr;
+    Weight *w = nullptr;
+    switch (t->kind) {
+    case FK_TASK_RMSNORM_QKV: case FK_TASK_RMSNORM_GATEUP_ACT: case FK_TASK_FINAL_RMSNORM_LM_HEAD: w = get_w(c, t->buf[2]); break;
+    case FK_TASK_LINEAR_RESIDUAL: w = get_w(c, t->buf[1]); break;
+    default: break;
+    }
+    return (w && w->tiled) ? w : nullptr;
+}
+static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *next) {
+    const Shape sh = plan_shape(c, w);
+    p->W = w->tview(); p->splits = sh.splits; p->stages = c->stages;
+    p->timeline = c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr;
+    p->next_units = nullptr; p->next_ntiles = p->next_nsb = p->next_splits = p->next_grid = p->next_warps = p->next_prefetch = 0;
+    if (next && c->prefetch > 0) {
+        const Shape ns = plan_shape(c, next);
+        p->next_units = next->units; p->next_ntiles = next->ntiles; p->next_nsb = next->nsb; p->next_splits = ns.splits;
+        p->next_grid = ns.grid; p->next_warps = ns.warps; p->next_prefetch = c->prefetch;
+    }
+    return sh;
+}
+// launch a streamed kernel template instance for (bits, warps)
+#define STREAM_LAUNCH(KERN, w, sh, ...)                                                                                  \
+    do {                                                                                                                 \
+        if ((w)->bits == 4 && (sh).warps == 8) e = launch(c, KERN<4, 8>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);        \
+        else if ((w)->bits == 4) e = launch(c, KERN<4, 16>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                     \
+        else if ((sh).warps == 8) e = launch(c, KERN<8, 8>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);                     \
+        else e = launch(c, KERN<8, 16>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                                         \
+    } while (0)
+#define BITS48(bits, CALL) do { if ((bits) == 4) { constexpr int B = 4; CALL; } else { constexpr int B = 8; CALL; } } while (0)
+
+static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullptr) {
     const uint64_t *b = t.buf; const int32_t *i = t.iarg; const float *f = t.farg;
     cudaError_t e = cudaSuccess;
     switch (t.kind) {
@@ -315,6 +456,16 @@ static fk_status run_task(Ctx *c, const fk_task &t) {
         QkvArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], w->view(), (const uint16_t *)b[3], (uint16_t *)b[4], (uint16_t *)b[5],
                   (uint16_t *)b[6], (uint16_t *)b[7], (uint16_t *)b[8], (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11],
                   H, nq, nkv, hd, cap, sinks, f[0], (float)log2((double)f[1])};
+        if (w->tiled) {
+            if (sinks && (w->rows_kind != FK_ROWS_ROPE_PAIRS || w->hd != hd || w->n_rot != (nq + nkv) * hd)) return fail(FK_ERR_VALUE, "rmsnorm_qkv: weight rows must be laid out as RoPE pairs (fk_weight_set_rows)");
+            if (!sinks && w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "rmsnorm_qkv without sinks takes plain row order");
+            SQkvArgs sa{a.x, a.norm_w, StreamPlan(), a.lin_bias, a.q_out, a.cache_k, a.cache_v, a.k_out, a.v_out, a.pending, a.pending_w, a.h_out,
+                        H, nq, nkv, hd, cap, sinks, a.eps, a.log2theta};
+            if (H > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "rmsnorm_qkv: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
+            const Shape sh = make_plan(c, w, &sa.P, nextw);
+            STREAM_LAUNCH(k_s_rmsnorm_qkv, w, sh, c->state, sa);
+            break;
+        }
         const int grid = grid_for(c, w->n / 2, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_rmsnorm_qkv<B>, dim3(grid), dim3(256), smem_bytes_for(H), (const FkState *)c->state, a));
         break;
@@ -329,12 +480,21 @@ static fk_status run_task(Ctx *c, const fk_task &t) {
     }
     case FK_TASK_SDPA_DECODE: {
         const int nq = i[0], nkv = i[1], hd = i[2], cap = i[3];
-        if (nkv <= 0 || nq % nkv || nq / nkv > FK_SDPA_MAXG || hd > 256 || (hd & 7) || !b[4] || !b[5]) return fail(FK_ERR_VALUE, "sdpa: unsupported shape (group <= 8, head_dim <= 256)");
+        if (nkv <= 0 || nq % nkv || nq / nkv > FK_SDPA_MAXG || (hd != 64 && hd != 128 && hd != 256) || !b[4] || !b[5]) return fail(FK_ERR_VALUE, "sdpa: unsupported shape (group <= 8, head_dim in {64,128,256})");
         const int chunks = (cap + FK_SDPA_KEYS - 1) / FK_SDPA_KEYS, G = nq / nkv;
         SdpaArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], (uint32_t *)b[5],
-                   nq, nkv, hd, cap, chunks, f[0]};
-        const size_t smem = sizeof(float) * (size_t)(G * hd + G * FK_SDPA_KEYS + 2 * G + 8);
-        e = launch(c, k_sdpa_decode, dim3(chunks, nkv), dim3(hd <= 128 ? 128 : 256), smem, (const FkState *)c->state, a);
+                   nq, nkv, hd, cap, chunks, f[0], c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr};
+        if (c->sdpa_cluster && (hd != 256 || G <= 2)) {
+            const size_t smem = sdpa_cl_smem_bytes(G, hd);
+            const dim3 cgrid(FK_SDPA_CL, nkv), cblock(FK_SDPA_CW * 32);
+            if (hd == 64) e = launch_cluster(c, k_sdpa_cluster<64, 8>, cgrid, cblock, smem, FK_SDPA_CL, (const FkState *)c->state, a);
+            else if (hd == 128) e = launch_cluster(c, k_sdpa_cluster<128, 8>, cgrid, cblock, smem, FK_SDPA_CL, (const FkState *)c->state, a);
+            else e = launch_cluster(c, k_sdpa_cluster<256, 2>, cgrid, cblock, smem, FK_SDPA_CL, (const FkState *)c->state, a);
+            break;
+        }
+        const size_t smem = sdpa_smem_bytes(G, hd, chunks);
+        if (smem > 200 * 1024) return fail(FK_ERR_VALUE, "sdpa: capacity too large for the merge table");
+        e = launch(c, k_sdpa_decode, dim3(chunks, nkv), dim3(FK_SDPA_THREADS), smem, (const FkState *)c->state, a);
         break;
     }
     case FK_TASK_LINEAR_RESIDUAL: {
@@ -342,13 +502,30 @@ static fk_status run_task(Ctx *c, const fk_task &t) {
         if (!w || !w->finalized) return fail(FK_ERR_VALUE, "linear_residual: weight missing or not finalized");
         if (w->k != i[0] || w->n != i[1] || !b[0] || (!b[3] && !b[4])) return fail(FK_ERR_VALUE, "linear_residual: shape mismatch");
         LinArgs a{(const uint16_t *)b[0], w->view(), (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], i[0], i[1]};
+        if (w->tiled) {
+            if (w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "linear_residual takes plain row order");
+            SLinArgs sa{a.x, StreamPlan(), a.residual, a.y, a.y_f32, i[0], i[1]};
+            const Shape sh = make_plan(c, w, &sa.P, nextw);
+            STREAM_LAUNCH(k_s_linear, w, sh, c->state, sa);
+            break;
+        }
         const int grid = grid_for(c, w->n, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_linear_residual<B>, dim3(grid), dim3(256), smem_bytes_for(i[0]), (const FkState *)c->state, a));
         break;
     }
     case FK_TASK_RMSNORM_GATEUP_ACT: {
         Weight *wg = get_w(c, b[2]), *wu = get_w(c, b[3]);
+        if (wg && wg->tiled && wg->rows_kind == FK_ROWS_GATE_UP) {       // paired gate/up weight (fk_weight_pair)
+            if (wg->k != i[0] || wg->n != 2LL * i[1] || !b[4]) return fail(FK_ERR_VALUE, "gateup: shape mismatch");
+            SGateUpArgs sa{(const uint16_t *)b[0], (const uint16_t *)b[1], StreamPlan(), (uint16_t *)b[4],
+                           (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0]};
+            if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "gateup: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
+            const Shape sh = make_plan(c, wg, &sa.P, nextw);
+            STREAM_LAUNCH(k_s_gateup, wg, sh, c->state, sa);
+            break;
+        }
         if (!wg || !wu || !wg->finalized || !wu->finalized) return fail(FK_ERR_VALUE, "gateup: weights missing or not finalized");
+        if (wg->tiled || wu->tiled) return fail(FK_ERR_VALUE, "gateup: pair the gate and up weights with fk_weight_pair");
         if (wg->k != i[0] || wu->k != i[0] || wg->n != i[1] || wu->n != i[1] || wg->bits != wu->bits) return fail(FK_ERR_VALUE, "gateup: shape mismatch");
         GateUpArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], wg->view(), wu->view(), (uint16_t *)b[4],
                      (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0]};
@@ -362,6 +539,15 @@ static fk_status run_task(Ctx *c, const fk_task &t) {
         if (w->k != i[0] || w->n != i[1] || !b[4] || !b[5]) return fail(FK_ERR_VALUE, "lm_head: shape mismatch");
         HeadArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], w->view(), (uint16_t *)b[3], (unsigned long long *)b[4], (uint32_t *)b[5],
                    (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], c->history, i[0], i[1], i[2], i[3], f[0]};
+        if (w->tiled) {
+            if (w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "lm_head takes plain row order");
+            SHeadArgs sa{a.x, a.norm_w, StreamPlan(), a.logits, a.scratch, a.counter, a.pending, a.pending_w, a.h_out, a.history,
+                         a.h, a.v, a.vocab_offset, a.finalize, a.eps};
+            if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "lm_head: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
+            const Shape sh = make_plan(c, w, &sa.P, nextw);
+            STREAM_LAUNCH(k_s_head, w, sh, c->state, sa);
+            break;
+        }
         const int grid = grid_for(c, w->n, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_final_head<B>, dim3(grid), dim3(256), smem_bytes_for(i[0]), c->state, a));
         break;
@@ -389,6 +575,18 @@ static fk_status run_task(Ctx *c, const fk_task &t) {
     return FK_OK;
 }
 
+// the next streamed weight after task j (looking a few tasks ahead; wrapping to the start of the list when the
+// list is replayed token after token)
+static const Weight *next_stream_weight(Ctx *c, const fk_task *tasks, int n, int j, bool wrap) {
+    for (int d = 1; d <= 4; ++d) {
+        int q = j + d;
+        if (q >= n) { if (!wrap) return nullptr; q -= n; if (q >= n) return nullptr; }
+        Weight *w = task_stream_weight(c, &tasks[q]);
+        if (w) return w;
+    }
+    return nullptr;
+}
+
 extern "C" fk_status fk_launch(fk_handle h, const fk_task *task) {
     CTX(h);
     if (!task) return fail(FK_ERR_VALUE, "task is null");
@@ -399,7 +597,7 @@ extern "C" fk_status fk_launch(fk_handle h, const fk_task *task) {
 extern "C" fk_status fk_launch_batch(fk_handle h, const fk_task *tasks, int n) {
     CTX(h);
     if (!tasks || n <= 0) return fail(FK_ERR_VALUE, "empty task list");
-    for (int j = 0; j < n; ++j) { fk_status s = run_task(c, tasks[j]); if (s) return s; }
+    for (int j = 0; j < n; ++j) { fk_status s = run_task(c, tasks[j], next_stream_weight(c, tasks, n, j, false)); if (s) return s; }
     CU(cudaStreamSynchronize(c->stream));
     return FK_OK;
 }
@@ -446,7 +644,8 @@ extern "C" fk_status fk_graph_capture(fk_handle h, const fk_task *tasks, int n, 
     CU(cudaStreamSynchronize(c->stream));
     CU(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     fk_status s = FK_OK;
-    for (int j = 0; j < n && s == FK_OK; ++j) s = run_task(c, tasks[j]);
+    for (int j = 0; j < n && s == FK_OK; ++j) { c->timeline_task = j; s = run_task(c, tasks[j], next_stream_weight(c, tasks, n, j, true)); }
+    c->timeline_task = 0;
     cudaError_t e = cudaStreamEndCapture(c->stream, &g.graph);
     if (s) { if (g.graph) cudaGraphDestroy(g.graph); return s; }
     CU(e);
@@ -498,7 +697,7 @@ extern "C" fk_status fk_graph_profile_nodes(fk_handle h, fk_graph gid, int repea
         for (int r = 0; r < repeats; ++r) {
             CU(cudaMemcpyAsync(c->state, c->pinned + 32, sizeof(FkState), cudaMemcpyHostToDevice, c->stream));
             CU(cudaEventRecord(c->ev0, c->stream));
-            fk_status s = run_task(c, g->tasks[j]); if (s) return s;
+            fk_status s = run_task(c, g->tasks[j], next_stream_weight(c, g->tasks.data(), n, j, true)); if (s) return s;
             CU(cudaEventRecord(c->ev1, c->stream));
             CU(cudaEventSynchronize(c->ev1));
             float ms = 0.0f; CU(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
@@ -548,6 +747,9 @@ extern "C" fk_status fk_decode_chunk_host(fk_handle h, fk_graph gid, uint32_t ba
     if (gpu_seconds) *gpu_seconds = tot;
     return FK_OK;
 }
+
+// tuning aid: per-block phase timestamps of the next streamed launches land in `dptr` ([grid][8] u64), 0 = off
+extern "C" fk_status fk_debug_timeline(fk_handle h, fk_dptr dptr) { CTX(h); c->timeline = (unsigned long long *)dptr; return FK_OK; }
 
 // ------------------------------------------------------------------ tensor parallel
 extern "C" fk_status fk_comm_unique_id(void *id128, size_t cap) {

@@ -1,0 +1,666 @@
+// Streamed batch-1 quantized matvec engine for sm_100a.
+//
+// HBM layout ("tiled"): a linear layer is cut into units of 16 output rows x 8 quantisation groups
+// (512 weights per row at 4 bit, 256 at 8 bit).  A unit is 4608 contiguous bytes already in the order
+// the consuming warp reads them: for each group j, one 16-byte vector per lane holding two packed words
+// of tile row g and two of row g+8 (g = lane/4), then one 16-byte vector per lane with the four scales
+// and four biases that lane applies.  One cp.async.bulk (TMA, 1-D) moves a unit into a per-warp ring in
+// shared memory; a warp then needs one conflict-free LDS.128 per group.
+//
+// Arithmetic: packed weights become fp16 integers with one LOP3 per pair (0x6400 | q reads as 1024+q, and a
+// nibble left in bits 4-7 reads as 1024+16q) and one HFMA2 per pair that removes the offset exactly -- the
+// logic ops run on the ALU pipe, the fix-up on the FMA pipe.  Activations (bf16, 8 significant bits) are
+// staged as fp16 scaled per quantisation group by a power of two, so the conversion is exact, and
+// mma.sync.m16n8k16 accumulates x*q in fp32 -- the tensor pipe is the dot-product unit because unpack +
+// convert + FMA on the CUDA cores costs >2 issue slots per weight, more than the SM has at HBM speed.
+// The eight groups of a unit go to the eight accumulator columns (the activations of group j sit in B
+// column j, zeros elsewhere), so after a unit every lane owns four (row, group) sums and applies
+// s * c / scale_g + b * sum(x_g) to them.  8-bit weights use the same path with whole bytes (0x6400 | byte).
+//
+// Scheduling: blocks of 8 warps, two per SM, each warp with its own ring and mbarriers.  With at least one
+// row tile per warp in the grid a warp owns whole tiles (all of K); otherwise the warps of a block split K
+// of the block's tile and fold their sums through shared memory in warp order (deterministic, no global
+// round trip).  Rings are filled before griddepcontrol.wait: weights do not depend on the previous kernel,
+// so under programmatic dependent launch a block of the next kernel that lands on an SM slot freed by this
+// one streams its weights while this kernel finishes; each warp also pulls the first units its slot will
+// need in the next kernel into L2 once its own loads are all in flight.
+#pragma once
+#include "fk_common.cuh"
+
+#define FK_UNIT_VEC 288                 // uint4 per unit: 8 groups x 32 lanes + 32 scale/bias vectors
+#define FK_UNIT_BYTES (FK_UNIT_VEC * 16)
+#define FK_STREAM_MAXWARPS 16         // blocks run 8 warps (two blocks per SM) or 16 (one per SM, large activations)
+#define FK_WAIT_LIMIT (1u << 24)        // bounded mbarrier wait; on expiry the kernel flags an error and leaves
+
+enum { FK_ROWS_PLAIN = 0, FK_ROWS_ROPE_PAIRS = 1, FK_ROWS_GATE_UP = 2 };
+
+struct TiledW {
+    const uint4 *units;     // [ntiles][nsb][FK_UNIT_VEC]
+    int ntiles, nsb;        // row tiles of 16, super-blocks of 8 groups
+    int n, k, bits;         // logical shape (rows after pairing/interleave)
+    int rows_kind, hd, n_rot;   // row order inside tiles (see tile_row)
+};
+
+// source row of tile row r (0..15): plain order; RoPE pairs (rows 0-7 = dims d..d+7 of a head, rows 8-15 =
+// the same dims + head_dim/2) for the first n_rot rows; gate/up interleave (rows 0-7 gate, 8-15 up).
+__host__ __device__ inline long long tile_row(int kind, int hd, int n_rot, int tile, int r) {
+    if (kind == FK_ROWS_ROPE_PAIRS && tile < n_rot / 16) {
+        const int tph = hd / 16, head = tile / tph, c = tile - head * tph;
+        return (long long)head * hd + c * 8 + (r & 7) + (r >= 8 ? hd / 2 : 0);
+    }
+    if (kind == FK_ROWS_GATE_UP) return (long long)tile * 8 + (r & 7);     // which matrix: r >= 8 -> up
+    return (long long)tile * 16 + r;
+}
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: returns false if the barrier never completed
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    for (uint32_t i = 0; i < FK_WAIT_LIMIT; ++i) if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// (w & mask) | 0x64006400 -> fp16x2 (1024 + field) for the fields selected by mask
+template <uint32_t MASK> __device__ __forceinline__ uint32_t magic(uint32_t w) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, 0x64006400, 0xEA;" : "=r"(r) : "r"(w), "n"(MASK));
+    return r;
+}
+__device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+#define H2_ONE 0x3C003C00u          // (1, 1)
+#define H2_M1024 0xE400E400u        // (-1024, -1024)
+#define H2_SIXTEENTH 0x2C002C00u    // (1/16, 1/16)
+#define H2_M64 0xD400D400u          // (-64, -64)
+__device__ __forceinline__ uint32_t q_lo(uint32_t w) { return hfma2(magic<0x000F000Fu>(w), H2_ONE, H2_M1024); }        // nibbles at bits 0-3
+__device__ __forceinline__ uint32_t q_hi(uint32_t w) { return hfma2(magic<0x00F000F0u>(w), H2_SIXTEENTH, H2_M64); }    // nibbles at bits 4-7
+__device__ __forceinline__ uint32_t q_byte(uint32_t w) { return hfma2(magic<0x00FF00FFu>(w), H2_ONE, H2_M1024); }      // bytes at bits 0-7
+
+// ------------------------------------------------------------------ shared-memory plan of a streamed kernel
+struct StreamSmem {
+    uint64_t *bars;     // [warps * stages]
+    uint4 *zero;        // 8 zero vectors
+    float *xsum;        // [groups] sum of the activations of a group
+    float *xinv;        // [groups] 1 / (power-of-two scale applied to the group's fp16 activations)
+    float *red;         // [48]
+    float *fold;        // [2][warps][16] per-warp row sums of a k-split tile
+    uint4 *xs;          // [groups * 8] permuted, group-scaled fp16 activations
+    uint4 *ring;        // [warps * stages * FK_UNIT_VEC]
+};
+__host__ __device__ inline int stream_groups(int nsb) { return nsb * 8; }
+__host__ __device__ inline size_t stream_smem_bytes(int nsb, int stages, int warps) {
+    size_t b = 512 /*bars*/ + 128 /*zero*/ + (size_t)stream_groups(nsb) * 8 + 192 /*red*/ + 2 * FK_STREAM_MAXWARPS * 16 * 4 /*fold*/;
+    b = (b + 15) & ~(size_t)15;
+    b += (size_t)stream_groups(nsb) * 8 * 16;                  // xs
+    b = (b + 127) & ~(size_t)127;
+    b += (size_t)warps * stages * FK_UNIT_BYTES;
+    return b + 128;
+}
+__device__ __forceinline__ StreamSmem stream_carve(unsigned char *base, int nsb, int stages) {
+    StreamSmem s;
+    base = (unsigned char *)(((uintptr_t)base + 127) & ~(uintptr_t)127);
+    s.bars = (uint64_t *)base; base += 512;
+    s.zero = (uint4 *)base; base += 128;
+    s.xsum = (float *)base; base += (size_t)stream_groups(nsb) * 4;
+    s.xinv = (float *)base; base += (size_t)stream_groups(nsb) * 4;
+    s.red = (float *)base; base += 192;
+    s.fold = (float *)base; base += 2 * FK_STREAM_MAXWARPS * 16 * 4;
+    base = (unsigned char *)(((uintptr_t)base + 15) & ~(uintptr_t)15);
+    s.xs = (uint4 *)base; base += (size_t)stream_groups(nsb) * 8 * 16;
+    base = (unsigned char *)(((uintptr_t)base + 127) & ~(uintptr_t)127);
+    s.ring = (uint4 *)base;
+    return s;
+}
+
+// Activation staging.  A thread owns blocks of 8 consecutive activations (one 16-byte load), keeps them in
+// registers, and writes them as fp16, scaled by the group's power of two and permuted for the MMA B operand:
+//   4-bit: slots [x0,x4,x1,x5,x2,x6,x3,x7] so the pair registers line up with the (n_j, n_j+4) nibble pairs of a
+//          packed word; a group is 64 activations = 8 vectors (8 threads).
+//   8-bit: a packed word holds 4 activations; lane t of a 32-activation group owns one vector
+//          [x0,x2,x1,x3 of word A | x0,x2,x1,x3 of word B], word B being 16 activations further on (4 threads).
+// Group maximum (for the scale) and group sum are reduced with shuffles across the threads of a group.
+__device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
+    f[0] = bf_lo(v.x); f[1] = bf_hi(v.x); f[2] = bf_lo(v.y); f[3] = bf_hi(v.y);
+    f[4] = bf_lo(v.z); f[5] = bf_hi(v.z); f[6] = bf_lo(v.w); f[7] = bf_hi(v.w);
+}
+__device__ __forceinline__ uint32_t h2pack(float a, float b) {
+    return (uint32_t)__half_as_ushort(__float2half_rn(a)) | ((uint32_t)__half_as_ushort(__float2half_rn(b)) << 16);
+}
+template <int BITS>
+__device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const float (&f)[8], bool valid) {
+    float s8 = 0.0f, m8 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { s8 += f[i]; m8 = fmaxf(m8, fabsf(f[i])); }
+    if (!valid) { s8 = 0.0f; m8 = 0.0f; }
+    constexpr int TPG = BITS == 4 ? 8 : 4;          // threads per group
+#pragma unroll
+    for (int o = 1; o < TPG; o <<= 1) { s8 += __shfl_xor_sync(0xffffffffu, s8, o); m8 = fmaxf(m8, __shfl_xor_sync(0xffffffffu, m8, o)); }
+    // scale = 2^(12 - exponent(max)): the largest activation lands in [2^12, 2^13); bf16 -> fp16 is then exact
+    // for everything within 2^-26 of the maximum
+    int e = m8 > 0.0f ? (int)((__float_as_uint(m8) >> 23) & 0xffu) - 127 : 12;
+    e = e < -100 ? -100 : (e > 100 ? 100 : e);
+    const float scale = __uint_as_float((uint32_t)(127 + 12 - e) << 23), inv = __uint_as_float((uint32_t)(127 - 12 + e) << 23);
+    if (!valid) return;
+    if (BITS == 4) {
+        sm.xs[blk] = make_uint4(h2pack(f[0] * scale, f[4] * scale), h2pack(f[1] * scale, f[5] * scale),
+                                h2pack(f[2] * scale, f[6] * scale), h2pack(f[3] * scale, f[7] * scale));
+        if ((blk & 7) == 0) { sm.xsum[blk >> 3] = s8; sm.xinv[blk >> 3] = inv; }
+    } else {
+        const int k0 = blk * 8, grp = k0 >> 5, o = k0 & 31, half = o >> 4, t = (o >> 2) & 3;
+        uint2 *dst = reinterpret_cast<uint2 *>(sm.xs) + ((grp * 64 + t * 8 + half * 4) >> 2);
+        dst[0] = make_uint2(h2pack(f[0] * scale, f[2] * scale), h2pack(f[1] * scale, f[3] * scale));        // lane t
+        dst[2] = make_uint2(h2pack(f[4] * scale, f[6] * scale), h2pack(f[5] * scale, f[7] * scale));        // lane t+1
+        if ((blk & 3) == 0) { sm.xsum[blk >> 2] = s8; sm.xinv[blk >> 2] = inv; }
+    }
+}
+// zero vectors, padded tail of xs / xsum (k rounded up to whole units)
+template <int BITS>
+__device__ __forceinline__ void stage_pad(const StreamSmem &sm, int k, int nsb) {
+    const int per_group = BITS == 4 ? 64 : 32, groups = stream_groups(nsb), g0 = k / per_group;
+    if (threadIdx.x < 8) sm.zero[threadIdx.x] = make_uint4(0, 0, 0, 0);
+    for (int i = g0 * 8 + threadIdx.x; i < groups * 8; i += blockDim.x) sm.xs[i] = make_uint4(0, 0, 0, 0);
+    for (int i = g0 + threadIdx.x; i < groups; i += blockDim.x) { sm.xsum[i] = 0.0f; sm.xinv[i] = 0.0f; }
+}
+__device__ __forceinline__ void stamp_raw(unsigned long long *tl, int slot) {
+    if (tl && threadIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tl[blockIdx.x * 8 + slot] = t; }
+}
+#define FK_STAGE_MAXB 4          // 8-blocks per thread held in registers during staging (h <= 8 * 256 * 4)
+template <int BITS>
+__device__ __forceinline__ void stage_plain(const StreamSmem &sm, const uint16_t *x, int k, int nsb) {
+    stage_pad<BITS>(sm, k, nsb);
+    const int nblk = k >> 3;
+    for (int b0 = 0; b0 < nblk; b0 += FK_STAGE_MAXB * blockDim.x) {
+        uint4 v[FK_STAGE_MAXB];
+#pragma unroll
+        for (int i = 0; i < FK_STAGE_MAXB; ++i) {          // all loads in flight before the first use
+            const int blk = b0 + i * blockDim.x + threadIdx.x;
+            v[i] = blk < nblk ? *reinterpret_cast<const uint4 *>(x + (size_t)blk * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < FK_STAGE_MAXB; ++i) {
+            const int blk = b0 + i * blockDim.x + threadIdx.x;
+            if (b0 + i * (int)blockDim.x >= nblk) break;   // uniform across the block
+            float f[8]; unpack8(v[i], f);
+            store_block<BITS>(sm, blk, f, blk < nblk);
+        }
+    }
+    __syncthreads();
+}
+// RMSNorm (two roundings to T, src/codegen/kernels/mod.rs:4464-4472; rmsnorm_qkv.rs:325), optionally after advancing the
+// residual stream with a pending post-norm, x' = T(x + rmsnorm(pending) * w_p) (Gemma-shaped layers); block 0
+// publishes x' to h_out.  One round of global loads: x, w (and the pending pair) stay in registers.
+template <int BITS>
+__device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16_t *x, const uint16_t *w, int h, int nsb, float eps,
+                                              const uint16_t *pending, const uint16_t *pending_w, uint16_t *h_out,
+                                              unsigned long long *tl = nullptr) {
+    stage_pad<BITS>(sm, h, nsb);
+    const int nblk = h >> 3;
+    uint4 xv[FK_STAGE_MAXB], wv[FK_STAGE_MAXB];
+#pragma unroll
+    for (int i = 0; i < FK_STAGE_MAXB; ++i) {
+        const int blk = i * blockDim.x + threadIdx.x;
+        xv[i] = wv[i] = make_uint4(0, 0, 0, 0);
+        if (blk < nblk) { xv[i] = *reinterpret_cast<const uint4 *>(x + (size_t)blk * 8); wv[i] = *reinterpret_cast<const uint4 *>(w + (size_t)blk * 8); }
+    }
+    if (pending) {
+        uint4 pv[FK_STAGE_MAXB], pw[FK_STAGE_MAXB];
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < FK_STAGE_MAXB; ++i) {
+            const int blk = i * blockDim.x + threadIdx.x;
+            pv[i] = pw[i] = make_uint4(0, 0, 0, 0);
+            if (blk < nblk) { pv[i] = *reinterpret_cast<const uint4 *>(pending + (size_t)blk * 8); pw[i] = *reinterpret_cast<const uint4 *>(pending_w + (size_t)blk * 8); }
+            float f[8]; unpack8(pv[i], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+        }
+        ss = block_sum(ss, sm.red);
+        const float rp = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)h), eps)));
+#pragma unroll
+        for (int i = 0; i < FK_STAGE_MAXB; ++i) {
+            const int blk = i * blockDim.x + threadIdx.x;
+            float f[8], pf[8], wf[8]; unpack8(xv[i], f); unpack8(pv[i], pf); unpack8(pw[i], wf);
+            uint16_t o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = f2bf(f[j] + rT(wf[j] * rT(pf[j] * rp)));
+            xv[i] = make_uint4(o[0] | ((uint32_t)o[1] << 16), o[2] | ((uint32_t)o[3] << 16), o[4] | ((uint32_t)o[5] << 16), o[6] | ((uint32_t)o[7] << 16));
+            if (blk < nblk && blockIdx.x == 0 && h_out) *reinterpret_cast<uint4 *>(h_out + (size_t)blk * 8) = xv[i];
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < FK_STAGE_MAXB; ++i) {
+        float f[8]; unpack8(xv[i], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+    }
+    stamp_raw(tl, 4);
+    ss = block_sum(ss, sm.red);
+    stamp_raw(tl, 5);
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)h), eps)));
+#pragma unroll
+    for (int i = 0; i < FK_STAGE_MAXB; ++i) {
+        const int blk = i * blockDim.x + threadIdx.x;
+        if (i * (int)blockDim.x >= nblk) break;            // uniform across the block
+        float f[8], wf[8]; unpack8(xv[i], f); unpack8(wv[i], wf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = rT(wf[j] * rT(f[j] * r));
+        store_block<BITS>(sm, blk, f, blk < nblk);
+    }
+    __syncthreads();
+}
+
+// ------------------------------------------------------------------ one unit: 16 rows x 8 groups
+template <int BITS>
+__device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
+    const int g = lane >> 2, t = lane & 3;
+    float cc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { cc[i][0] = cc[i][1] = cc[i][2] = cc[i][3] = 0.f; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint4 w = u[j * 32 + lane];
+        const uint4 *xp = (g == j) ? sm.xs + (size_t)(sb * 8 + j) * 8 : sm.zero;
+        float (&c)[4] = cc[j & 3];
+        if (BITS == 4) {
+            const uint4 xa = xp[t], xb = xp[4 + t];
+            const uint32_t ax = w.x >> 8, az = w.z >> 8, ay = w.y >> 8, aw = w.w >> 8;
+            // word A: rows g (w.x) and g+8 (w.z); word B: rows g (w.y) and g+8 (w.w)
+            mma_f16(c, q_lo(w.x), q_lo(w.z), q_hi(w.x), q_hi(w.z), xa.x, xa.y);
+            mma_f16(c, q_lo(ax), q_lo(az), q_hi(ax), q_hi(az), xa.z, xa.w);
+            mma_f16(c, q_lo(w.y), q_lo(w.w), q_hi(w.y), q_hi(w.w), xb.x, xb.y);
+            mma_f16(c, q_lo(ay), q_lo(aw), q_hi(ay), q_hi(aw), xb.z, xb.w);
+        } else {
+            const uint4 xv = xp[t];                       // (x0,x2),(x1,x3) of word A, then of word B
+            mma_f16(c, q_byte(w.x), q_byte(w.z), q_byte(w.x >> 8), q_byte(w.z >> 8), xv.x, xv.y);
+            mma_f16(c, q_byte(w.y), q_byte(w.w), q_byte(w.y >> 8), q_byte(w.w >> 8), xv.z, xv.w);
+        }
+    }
+    const uint4 sb4 = u[256 + lane];
+    const float X0 = sm.xsum[sb * 8 + 2 * t], X1 = sm.xsum[sb * 8 + 2 * t + 1];
+    const float i0 = sm.xinv[sb * 8 + 2 * t], i1 = sm.xinv[sb * 8 + 2 * t + 1];
+    const float s00 = bf_lo(sb4.x), s01 = bf_hi(sb4.x), s10 = bf_lo(sb4.y), s11 = bf_hi(sb4.y);
+    const float b00 = bf_lo(sb4.z), b01 = bf_hi(sb4.z), b10 = bf_lo(sb4.w), b11 = bf_hi(sb4.w);
+    const float c0 = ((cc[0][0] + cc[1][0]) + (cc[2][0] + cc[3][0])) * i0, c1 = ((cc[0][1] + cc[1][1]) + (cc[2][1] + cc[3][1])) * i1;
+    const float c2 = ((cc[0][2] + cc[1][2]) + (cc[2][2] + cc[3][2])) * i0, c3 = ((cc[0][3] + cc[1][3]) + (cc[2][3] + cc[3][3])) * i1;
+    acc_lo = fmaf(s00, c0, acc_lo); acc_lo = fmaf(b00, X0, acc_lo);
+    acc_lo = fmaf(s01, c1, acc_lo); acc_lo = fmaf(b01, X1, acc_lo);
+    acc_hi = fmaf(s10, c2, acc_hi); acc_hi = fmaf(b10, X0, acc_hi);
+    acc_hi = fmaf(s11, c3, acc_hi); acc_hi = fmaf(b11, X1, acc_hi);
+}
+
+// ------------------------------------------------------------------ per-warp unit stream
+struct StreamPlan {
+    TiledW W;
+    int splits;             // 1: a warp owns whole tiles; >1: the first `splits` warps of a block split K of the block's tile
+    int stages;             // ring depth per warp
+    // the streamed kernel that runs next: its first units are pulled into L2 while this kernel drains
+    const uint4 *next_units; int next_ntiles, next_nsb, next_splits, next_grid, next_warps, next_prefetch;
+    unsigned long long *timeline;   // optional [grid][8] phase timestamps (ns) for tuning; null in normal use
+};
+__device__ __forceinline__ void stamp(const StreamPlan &p, int slot) {
+    if (p.timeline && threadIdx.x == 0) {
+        unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.timeline[blockIdx.x * 8 + slot] = t;
+    }
+}
+// position of a warp in its sequence of units: tiles tile0, tile0+stride, ... and super-blocks [sb0, sb1) of each
+struct Cursor {
+    int tile, sb, sb0, sb1, stride, ntiles;
+    __device__ __forceinline__ void init(int ntiles_, int nsb, int splits, int block, int nblocks, int wid, int nwarps) {
+        ntiles = ntiles_;
+        if (splits == 1) { tile = block * nwarps + wid; stride = nblocks * nwarps; sb0 = 0; sb1 = nsb; }
+        else {
+            tile = block; stride = nblocks;
+            if (wid < splits) { sb0 = wid * nsb / splits; sb1 = (wid + 1) * nsb / splits; } else { sb0 = sb1 = 0; tile = ntiles_; }
+        }
+        sb = sb0;
+        if (sb0 >= sb1) tile = ntiles_;
+    }
+    __device__ __forceinline__ bool valid() const { return tile < ntiles; }
+    __device__ __forceinline__ size_t unit_index(int nsb) const { return (size_t)tile * nsb + sb; }
+    __device__ __forceinline__ void advance() { if (++sb >= sb1) { sb = sb0; tile += stride; } }
+};
+__device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+// L2 prefetch of the units this (block, warp) slot will consume first in the next streamed kernel
+__device__ __forceinline__ void prefetch_next(const StreamPlan &p) {
+    if (!p.next_units || (threadIdx.x & 31) != 0 || (int)blockIdx.x >= p.next_grid || (int)(threadIdx.x >> 5) >= p.next_warps) return;
+    Cursor c; c.init(p.next_ntiles, p.next_nsb, p.next_splits, blockIdx.x, p.next_grid, threadIdx.x >> 5, p.next_warps);
+    for (int i = 0; i < p.next_prefetch && c.valid(); ++i) { l2_prefetch(p.next_units + c.unit_index(p.next_nsb) * FK_UNIT_VEC, FK_UNIT_BYTES); c.advance(); }
+}
+
+struct WarpStream { uint64_t *bars; uint4 *ring; Cursor prod; int stages; };
+__device__ __forceinline__ void stream_issue(WarpStream &ws, const StreamPlan &p, int stage) {
+    if ((threadIdx.x & 31) == 0) {
+        mbar_expect_tx(ws.bars + stage, FK_UNIT_BYTES);
+        bulk_g2s(ws.ring + (size_t)stage * FK_UNIT_VEC, p.W.units + ws.prod.unit_index(p.W.nsb) * FK_UNIT_VEC, FK_UNIT_BYTES, ws.bars + stage);
+    }
+    ws.prod.advance();
+}
+// before griddepcontrol.wait: barriers up, ring filled with the warp's first units
+__device__ __forceinline__ void stream_begin(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    ws.stages = p.stages; ws.bars = sm.bars + wid * p.stages; ws.ring = sm.ring + (size_t)wid * p.stages * FK_UNIT_VEC;
+    ws.prod.init(p.W.ntiles, p.W.nsb, p.splits, blockIdx.x, gridDim.x, wid, blockDim.x >> 5);
+    if (lane == 0) { for (int s = 0; s < p.stages; ++s) mbar_init(ws.bars + s, 1); mbar_fence_init(); }
+    __syncwarp();
+    for (int s = 0; s < p.stages && ws.prod.valid(); ++s) stream_issue(ws, p, s);
+}
+
+// Walk the warp's units; `epi(tile, g, v_lo, v_hi)` receives the finished sums of tile rows g and g+8 on lanes with
+// (lane & 3) == 0 (of the owning warp, or of warp 0 when K is split across the block).  Returns false if a barrier
+// wait expired.  With splits > 1 every warp of the block must call this (it synchronises the block per tile).
+template <int BITS, class Epi>
+__device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm, Epi &epi) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    Cursor cons; cons.init(p.W.ntiles, p.W.nsb, p.splits, blockIdx.x, gridDim.x, wid, blockDim.x >> 5);
+    int consumed = 0;
+    bool prefetched = false, ok = true;
+    if (!ws.prod.valid()) { prefetch_next(p); prefetched = true; }       // everything this warp needs is already in flight
+    const int rounds = p.splits == 1 ? 0 : (p.W.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    for (int round = 0; p.splits == 1 ? cons.valid() : round < rounds; ++round) {
+        const int tile = p.splits == 1 ? cons.tile : (int)blockIdx.x + round * (int)gridDim.x;
+        float acc_lo = 0.0f, acc_hi = 0.0f;
+        while (ok && cons.valid() && cons.tile == tile) {
+            const int s = consumed % ws.stages;
+            if (!mbar_wait(ws.bars + s, (uint32_t)(consumed / ws.stages) & 1u)) { ok = false; break; }
+            unit_compute<BITS>(ws.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb, lane, acc_lo, acc_hi);
+            __syncwarp();
+            if (ws.prod.valid()) stream_issue(ws, p, s);                  // refill the stage just drained
+            else if (!prefetched) { prefetch_next(p); prefetched = true; }
+            ++consumed;
+            cons.advance();
+        }
+        acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 1); acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 2);
+        acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 1); acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 2);
+        if (p.splits == 1) {
+            if (t == 0) epi(tile, g, acc_lo, acc_hi);
+        } else {
+            float *fold = sm.fold + (round & 1) * FK_STREAM_MAXWARPS * 16;
+            if (t == 0 && wid < p.splits) { fold[wid * 16 + g] = acc_lo; fold[wid * 16 + 8 + g] = acc_hi; }
+            __syncthreads();
+            if (wid == 0 && t == 0) {
+                float lo = 0.0f, hi = 0.0f;
+                for (int q = 0; q < p.splits; ++q) { lo += fold[q * 16 + g]; hi += fold[q * 16 + 8 + g]; }
+                epi(tile, g, lo, hi);
+            }
+        }
+    }
+    return ok;
+}
+
+// ------------------------------------------------------------------ repack / probe kernels
+struct SrcW { const uint32_t *w; const uint16_t *s, *b; };
+// one thread per destination vector; sources are MLX-affine rows (src/fusion/ir.rs:236-247)
+__global__ void k_repack_tiled(SrcW a, SrcW bsrc, uint4 *dst, long long n_src, int k, int bits, int ntiles, int nsb,
+                               int rows_kind, int hd, int n_rot) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)ntiles * nsb * FK_UNIT_VEC) return;
+    const int e = (int)(idx % FK_UNIT_VEC); const long long unit = idx / FK_UNIT_VEC;
+    const int tile = (int)(unit / nsb), sb = (int)(unit % nsb);
+    const int per_word = 32 / bits, kpg = bits == 4 ? 64 : 32;       // activations per nibble group
+    const int words_per_row = k / per_word, groups_per_row = k / 64;
+    const int lane = e & 31, g = lane >> 2, t = lane & 3;
+    const long long r0 = tile_row(rows_kind, hd, n_rot, tile, g), r1 = tile_row(rows_kind, hd, n_rot, tile, g + 8);
+    const SrcW &s0 = a, &s1 = (rows_kind == FK_ROWS_GATE_UP) ? bsrc : a;
+    uint4 out = make_uint4(0, 0, 0, 0);
+    if (e < 256) {
+        const int j = e >> 5;
+        const int kA = sb * 8 * kpg + j * kpg + per_word * t, kB = kA + kpg / 2;
+        if (r0 < n_src) { if (kA < k) out.x = s0.w[r0 * words_per_row + kA / per_word]; if (kB < k) out.y = s0.w[r0 * words_per_row + kB / per_word]; }
+        if (r1 < n_src) { if (kA < k) out.z = s1.w[r1 * words_per_row + kA / per_word]; if (kB < k) out.w = s1.w[r1 * words_per_row + kB / per_word]; }
+    } else {
+        uint32_t sv[4] = {0, 0, 0, 0}, bv[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int kk = (sb * 8 + 2 * t + q) * kpg;            // first activation of nibble group 2t+q
+            if (kk < k) {
+                const int gi = kk / 64;
+                if (r0 < n_src) { sv[q] = s0.s[r0 * groups_per_row + gi]; bv[q] = s0.b[r0 * groups_per_row + gi]; }
+                if (r1 < n_src) { sv[2 + q] = s1.s[r1 * groups_per_row + gi]; bv[2 + q] = s1.b[r1 * groups_per_row + gi]; }
+            }
+        }
+        out.x = sv[0] | (sv[1] << 16); out.y = sv[2] | (sv[3] << 16); out.z = bv[0] | (bv[1] << 16); out.w = bv[2] | (bv[3] << 16);
+    }
+    dst[idx] = out;
+}
+
+// fp32 dequantised values scattered back to source order: out[(row - row0) * k + col] for rows of matrix `which`
+// (0 = first / only source, 1 = the up matrix of a gate/up pair)
+__global__ void k_dequant_tiled(TiledW W, int which, long long row0, long long nrows, float *out) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)W.ntiles * W.nsb * 256) return;
+    const int e = (int)(idx & 255); const long long unit = idx >> 8;
+    const int tile = (int)(unit / W.nsb), sb = (int)(unit % W.nsb);
+    const int j = e >> 5, lane = e & 31, g = lane >> 2, t = lane & 3;
+    const int per_word = 32 / W.bits, kpg = W.bits == 4 ? 64 : 32;
+    const uint4 *u = W.units + (size_t)unit * FK_UNIT_VEC;
+    const uint4 w = u[j * 32 + lane];
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+    const int jl = j >> 1;                                   // the lane (t = j/2) holding this group's scale pair
+    const uint4 sb4 = u[256 + (g << 2) + jl];
+    const uint32_t mask = (1u << W.bits) - 1u;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int r = g + (q >= 2 ? 8 : 0);
+        if (W.rows_kind == FK_ROWS_GATE_UP && ((r >= 8) != (which == 1))) continue;
+        const long long src = tile_row(W.rows_kind, W.hd, W.n_rot, tile, r);
+        if (src < row0 || src >= row0 + nrows) continue;
+        const uint32_t sp = (q >= 2) ? sb4.y : sb4.x, bp = (q >= 2) ? sb4.w : sb4.z;
+        const float s = (j & 1) ? bf_hi(sp) : bf_lo(sp), b = (j & 1) ? bf_hi(bp) : bf_lo(bp);
+        const int kbase = sb * 8 * kpg + j * kpg + per_word * t + ((q & 1) ? kpg / 2 : 0);
+        for (int i = 0; i < per_word; ++i) {
+            const int kk = kbase + i;
+            if (kk < W.k) out[(src - row0) * W.k + kk] = __fadd_rn(__fmul_rn((float)((words[q] >> (i * W.bits)) & mask), s), b);
+        }
+    }
+}
+
+// ================================================================ streamed kernels
+
+struct SLinArgs { const uint16_t *x; StreamPlan P; const uint16_t *residual; uint16_t *y; float *y_f32; int k, n; };
+// y = T(acc + float(residual)) (src/codegen/msl.rs:2759-2775); residual optional; optional fp32 copy of acc
+template <int BITS, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st, SLinArgs a) {
+    extern __shared__ unsigned char smem_stream[];
+    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages);
+    stamp(a.P, 0);
+    WarpStream ws; stream_begin(ws, a.P, sm);
+    pdl_launch_dependents(); pdl_wait();
+    stamp(a.P, 1);
+    stage_plain<BITS>(sm, a.x, a.k, a.P.W.nsb);
+    stamp(a.P, 2);
+    auto epi = [&](int tile, int g, float lo, float hi) {
+        const float v[2] = {lo, hi};
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int r = tile * 16 + g + 8 * q;
+            if (r >= a.n) continue;
+            float acc = v[q];
+            if (a.y_f32) a.y_f32[r] = acc;
+            if (a.residual) acc += bf2f(a.residual[r]);
+            if (a.y) a.y[r] = f2bf(acc);
+        }
+    };
+    if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x100u);
+    __syncthreads(); stamp(a.P, 3);
+}
+
+struct SQkvArgs {
+    const uint16_t *x, *norm_w; StreamPlan P; const uint16_t *lin_bias;
+    uint16_t *q_out, *cache_k, *cache_v, *k_out, *v_out;
+    const uint16_t *pending, *pending_w; uint16_t *h_out;
+    int h, n_q, n_kv, hd, capacity, sinks; float eps, log2theta;
+};
+__device__ __forceinline__ void rope_rotate(float lo, float hi, int d, int half, uint32_t pos, float log2theta, uint16_t *o_lo, uint16_t *o_hi) {
+    const float e = __fmul_rn(-__fdiv_rn((float)d, (float)half), log2theta);
+    const float ang = __fmul_rn((float)pos, exp2f(e));
+    float s, c; sincosf(ang, &s, &c);
+    *o_lo = f2bf(__fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, s)));
+    *o_hi = f2bf(__fadd_rn(__fmul_rn(hi, c), __fmul_rn(lo, s)));
+}
+// RMSNorm -> QKV (+bias) -> RoPE -> K/V into the live cache (src/codegen/kernels/rmsnorm_qkv.rs:616-726).  With sinks the
+// weight rows are tiled as RoPE pairs, so a lane owns dims d and d + head_dim/2 of one head.
+template <int BITS, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkState *st, SQkvArgs a) {
+    extern __shared__ unsigned char smem_stream[];
+    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages);
+    stamp(a.P, 0);
+    WarpStream ws; stream_begin(ws, a.P, sm);
+    pdl_launch_dependents(); pdl_wait();
+    stamp(a.P, 1);
+    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline);
+    stamp(a.P, 2);
+    const uint32_t pos = st->offset;
+    const int wrow = (int)(pos % (uint32_t)a.capacity), half = a.hd >> 1;
+    const int nq_rows = a.n_q * a.hd, nqk = (a.n_q + a.n_kv) * a.hd, n = nqk + a.n_kv * a.hd;
+    auto store = [&](int r, uint16_t v) {
+        if (r < nq_rows) a.q_out[r] = v;
+        else if (r < nqk) {
+            const int kr = r - nq_rows, kh = kr / a.hd, d = kr - kh * a.hd;
+            if (a.sinks) a.cache_k[((size_t)kh * a.capacity + wrow) * a.hd + d] = v; else a.k_out[kr] = v;
+        } else if (r < n) {
+            const int vr = r - nqk, kh = vr / a.hd, d = vr - kh * a.hd;
+            if (a.sinks) a.cache_v[((size_t)kh * a.capacity + wrow) * a.hd + d] = v; else a.v_out[vr] = v;
+        }
+    };
+    auto epi = [&](int tile, int g, float lo, float hi) {
+        const int r0 = (int)tile_row(a.P.W.rows_kind, a.hd, a.P.W.n_rot, tile, g), r1 = (int)tile_row(a.P.W.rows_kind, a.hd, a.P.W.n_rot, tile, g + 8);
+        if (a.lin_bias) { if (r0 < n) lo += bf2f(a.lin_bias[r0]); if (r1 < n) hi += bf2f(a.lin_bias[r1]); }
+        if (a.sinks && tile < a.P.W.n_rot / 16) {
+            uint16_t o0, o1; rope_rotate(rT(lo), rT(hi), r0 % a.hd, half, pos, a.log2theta, &o0, &o1);
+            store(r0, o0); store(r1, o1);
+        } else { store(r0, f2bf(lo)); store(r1, f2bf(hi)); }
+    };
+    if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x200u);
+    __syncthreads(); stamp(a.P, 3);
+}
+
+struct SGateUpArgs {
+    const uint16_t *x, *norm_w; StreamPlan P; uint16_t *act_out;
+    const uint16_t *pending, *pending_w; uint16_t *h_out;
+    int h, inter, act; float eps;
+};
+__device__ __forceinline__ uint16_t s_act_swiglu(float ga, float ua) {
+    const float g = rT(ga), u = rT(ua);
+    return f2bf((__fdiv_rn(1.0f, 1.0f + expf(-g)) * g) * u);
+}
+__device__ __forceinline__ uint16_t s_act_geglu(float ga, float ua) {
+    const float g = rT(ga), u = rT(ua);
+    const float g3 = rT(rT(g * g) * g);
+    const float t2 = rT(g + rT(0.044715f * g3));
+    const float t3 = rT(0.7978845608028654f * t2);
+    const float t4 = rT(tanhf(fminf(fmaxf(t3, -20.0f), 20.0f)));
+    return f2bf(rT(rT(0.5f * g) * rT(1.0f + t4)) * u);
+}
+// RMSNorm -> gate & up -> activation tail in registers (src/codegen/kernels/fused_chain.rs:2902-3552; msl.rs:1286-1294).
+// The paired weight interleaves 8 gate rows with the 8 matching up rows per tile, so a lane holds both.
+template <int BITS, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st, SGateUpArgs a) {
+    extern __shared__ unsigned char smem_stream[];
+    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages);
+    stamp(a.P, 0);
+    WarpStream ws; stream_begin(ws, a.P, sm);
+    pdl_launch_dependents(); pdl_wait();
+    stamp(a.P, 1);
+    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline);
+    stamp(a.P, 2);
+    auto epi = [&](int tile, int g, float gate, float up) {
+        const int r = tile * 8 + g;
+        if (r < a.inter) a.act_out[r] = a.act == 1 ? s_act_geglu(gate, up) : s_act_swiglu(gate, up);
+    };
+    if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x400u);
+    __syncthreads(); stamp(a.P, 3);
+}
+
+struct SHeadArgs {
+    const uint16_t *x, *norm_w; StreamPlan P; uint16_t *logits; unsigned long long *scratch; uint32_t *counter;
+    const uint16_t *pending, *pending_w; uint16_t *h_out; uint32_t *history;
+    int h, v, vocab_offset, finalize; float eps;
+};
+__device__ __forceinline__ void s_finalize_token(FkState *st, uint32_t *history, unsigned long long best) {
+    const uint32_t next = 0xffffffffu - (uint32_t)(best & 0xffffffffull);
+    st->token[0] = next;
+    if (history && st->hist_counter < st->hist_cap) history[st->hist_counter] = next;
+    st->hist_counter += 1;
+    st->offset += 1;
+}
+// final RMSNorm -> lm_head -> argmax on T-rounded logits, ties to the lowest index, no logits round trip
+// (final_rmsnorm_lm_head.rs:250-326; msl.rs:1805-1838); the last block folds the per-block keys and advances the state
+template <int BITS, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, SHeadArgs a) {
+    extern __shared__ unsigned char smem_stream[];
+    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages);
+    __shared__ unsigned long long wbest[WARPS]; __shared__ int is_last;
+    stamp(a.P, 0);
+    WarpStream ws; stream_begin(ws, a.P, sm);
+    pdl_launch_dependents(); pdl_wait();
+    stamp(a.P, 1);
+    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline);
+    stamp(a.P, 2);
+    unsigned long long best = 0ull;
+    auto epi = [&](int tile, int g, float lo, float hi) {
+        const float v[2] = {lo, hi};
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int r = tile * 16 + g + 8 * q;
+            if (r >= a.v) continue;
+            const uint16_t tb = f2bf(v[q]);
+            if (a.logits) a.logits[r] = tb;
+            const unsigned long long key = argmax_key(tb, (uint32_t)(r + a.vocab_offset));
+            best = key > best ? key : best;
+        }
+    };
+    const bool ok = stream_run<BITS>(ws, a.P, sm, epi);
+    if (!ok) atomicOr(&st->error, 0x800u);
+    stamp(a.P, 3);
+    best = warp_max_u64(best);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) wbest[wid] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < WARPS; ++i) best = wbest[i] > best ? wbest[i] : best;
+        a.scratch[blockIdx.x] = best;
+        __threadfence();
+        const uint32_t tk = atomicAdd(a.counter, 1u);
+        is_last = (tk == gridDim.x - 1);
+        if (is_last) *a.counter = 0u;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (wid == 0) {
+        unsigned long long b = 0ull;
+        for (int i = lane; i < (int)gridDim.x; i += 32) { const unsigned long long v = __ldcg(a.scratch + i); b = v > b ? v : b; }
+        b = warp_max_u64(b);
+        if (lane == 0) { if (a.finalize) s_finalize_token(st, a.history, b); else a.scratch[0] = b; }
+    }
+}

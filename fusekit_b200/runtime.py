@@ -93,6 +93,20 @@ class Runtime:
     def weight_finalize(self, wid):
         N.check(self.L.fk_weight_finalize(self.h, wid), "fk_weight_finalize")
 
+    def weight_set_rows(self, wid, kind: int, head_dim: int, n_rot_rows: int):
+        N.check(self.L.fk_weight_set_rows(self.h, wid, kind, head_dim, n_rot_rows), "fk_weight_set_rows")
+
+    def weight_pair(self, gate: int, up: int) -> int:
+        out = C.c_uint64()
+        N.check(self.L.fk_weight_pair(self.h, gate, up, C.byref(out)), "fk_weight_pair")
+        return out.value
+
+    @property
+    def tiled(self) -> bool:
+        """True when 4/8-bit weights are repacked into the streaming layout (default)."""
+        import os
+        return os.environ.get("FK_LAYOUT", "") != "mlx"
+
     def weight_dequant(self, wid, row0, nrows, k) -> np.ndarray:
         out = np.empty((nrows, k), np.float32)
         N.check(self.L.fk_weight_dequant(self.h, wid, row0, nrows, out.ctypes.data), "fk_weight_dequant")
@@ -155,7 +169,7 @@ class DecodeEngine:
         self.d_buf = rt.alloc(L * H * 2)              # Gemma: down_proj output before its post-norm
         self.part_f32 = rt.alloc(H * 4)               # tensor-parallel partial sums
         max_cap = max(s.layer_capacity(l, self.capacity) for l in range(L))
-        chunks = (max_cap + 63) // 64
+        chunks = (max_cap + 31) // 32
         self.sdpa_part = rt.alloc(self.nq * chunks * (s.head_dim + 2) * 4)
         self.sdpa_counter = rt.alloc(max(self.nkv, 1) * 4)
         self.argmax_scratch = rt.alloc(8 * 1024)
@@ -218,8 +232,7 @@ class DecodeEngine:
             for leaf, src_row0, n in segs:
                 rt.weight_synth_rows(wid, row, n, stream_id(s.seed, tensor_name(layer, leaf)), 0.02, k_global, src_row0, k0)
                 row += n
-            rt.weight_finalize(wid)
-            self.W[name] = wid
+            self._finish_weight(name, wid)
         self._load_vectors(lambda leaf, layer, idx0, n, mean, std, dst: rt.synth_normal(
             dst, stream_id(s.seed, tensor_name(layer, leaf)), idx0, n, mean, std))
         rt.sync()
@@ -236,10 +249,30 @@ class DecodeEngine:
                 p, sc, bi = weight_provider(leaf, layer, src_row0, n, k_global, k0, k, s.bits)
                 rt.weight_upload_rows(wid, row, p, sc, bi)
                 row += n
-            rt.weight_finalize(wid)
-            self.W[name] = wid
+            self._finish_weight(name, wid)
         self._load_vectors(lambda leaf, layer, idx0, n, mean, std, dst: rt.upload(dst, vector_provider(leaf, layer, idx0, n, mean, std)))
         rt.sync()
+
+    def _finish_weight(self, name: str, wid: int):
+        """Choose the tile row order the consuming kernel wants, then freeze the weight."""
+        s, rt = self.spec, self.rt
+        paired = rt.tiled and s.bits != 16
+        if name.endswith(".qkv") and s.arch == "qwen2" and paired:
+            rt.weight_set_rows(wid, 1, s.head_dim, (self.nq + self.nkv) * s.head_dim)
+        if paired and (name.endswith(".gate") or name.endswith(".up")):
+            self.W[name] = wid                       # frozen together once both halves exist
+            g, u = name.rsplit(".", 1)[0] + ".gate", name.rsplit(".", 1)[0] + ".up"
+            if g in self.W and u in self.W:
+                self.W[name.rsplit(".", 1)[0] + ".gateup"] = rt.weight_pair(self.W.pop(g), self.W.pop(u))
+            return
+        rt.weight_finalize(wid)
+        self.W[name] = wid
+
+    def _gateup_bufs(self, l: int) -> dict:
+        key = f"layers.{l}.gateup"
+        if key in self.W:
+            return {2: self.W[key], 3: 0}
+        return {2: self.W[f"layers.{l}.gate"], 3: self.W[f"layers.{l}.up"]}
 
     def _load_vectors(self, fill):
         s, rt = self.spec, self.rt
@@ -319,7 +352,7 @@ class DecodeEngine:
             if s.arch == "qwen2" and not tp:
                 tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa_buf, 1: self.W[f"layers.{l}.o"], 2: self.x_ptr(l), 3: self.hb_ptr(l)}, [ko, H]))
                 tasks.append(T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: self.hb_ptr(l), 1: self.V[f"layers.{l}.post_attention_norm"],
-                                                              2: self.W[f"layers.{l}.gate"], 3: self.W[f"layers.{l}.up"], 4: self.act_buf},
+                                                              **self._gateup_bufs(l), 4: self.act_buf},
                                [H, self.inter, s.act], [s.eps]))
                 tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 2: self.hb_ptr(l), 3: self.x_ptr(l + 1)}, [self.inter, H]))
             elif s.arch == "qwen2":
@@ -328,7 +361,7 @@ class DecodeEngine:
                 tasks.append(T(N.TASK_ALLREDUCE, l, {0: self.part_f32}, [H, 0]))
                 tasks.append(T(N.TASK_RESIDUAL_ADD, l, {0: self.part_f32, 1: self.x_ptr(l), 2: self.hb_ptr(l)}, [H]))
                 tasks.append(T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: self.hb_ptr(l), 1: self.V[f"layers.{l}.post_attention_norm"],
-                                                              2: self.W[f"layers.{l}.gate"], 3: self.W[f"layers.{l}.up"], 4: self.act_buf},
+                                                              **self._gateup_bufs(l), 4: self.act_buf},
                                [H, self.inter, s.act], [s.eps]))
                 tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 4: self.part_f32}, [self.inter, H]))
                 tasks.append(T(N.TASK_ALLREDUCE, l, {0: self.part_f32}, [H, 0]))
@@ -338,7 +371,7 @@ class DecodeEngine:
                 tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa_buf, 1: self.W[f"layers.{l}.o"], 3: self.o_buf}, [ko, H]))
                 x_res = self.x_ptr(l)
                 tasks.append(T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: x_res, 1: self.V[f"layers.{l}.pre_feedforward_norm"],
-                                                              2: self.W[f"layers.{l}.gate"], 3: self.W[f"layers.{l}.up"], 4: self.act_buf,
+                                                              **self._gateup_bufs(l), 4: self.act_buf,
                                                               9: self.o_buf, 10: self.V[f"layers.{l}.post_attention_norm"], 11: self.hb_ptr(l)},
                                [H, self.inter, s.act], [s.eps]))
                 tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 3: self.d_ptr(l)}, [self.inter, H]))

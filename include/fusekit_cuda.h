@@ -120,7 +120,16 @@ fk_status fk_weight_upload_rows(fk_handle h, fk_weight w, int64_t dst_row0, int6
  * value(row, col) = std * z(stream, (src_row0 + r) * k_global + k0 + c), quantised per group of 64 */
 fk_status fk_weight_synth_rows(fk_handle h, fk_weight w, int64_t dst_row0, int64_t nrows, uint64_t stream,
                                float std, int64_t k_global, int64_t src_row0, int64_t k0);
+/* Row order inside the library's 16-row tiles, chosen before fk_weight_finalize: 0 = plain, 1 = RoPE pairs
+ * (the first n_rot_rows rows are heads of head_dim; dims d and d + head_dim/2 of a head share a lane so the
+ * fused QKV kernel rotates them in registers -- required for RMSNORM_QKV with sinks). */
+fk_status fk_weight_set_rows(fk_handle h, fk_weight w, int kind, int head_dim, int n_rot_rows);
+/* Freezes the object; 4- and 8-bit rows are repacked into the streaming layout (16 rows x 8 groups per
+ * 4608-byte unit, lane-ordered) and the MLX-layout copy is released. */
 fk_status fk_weight_finalize(fk_handle h, fk_weight w);
+/* Interleaves a gate and an up projection (same shape, not yet finalized) into one weight whose tiles hold
+ * 8 gate rows and the 8 matching up rows; consumes both inputs.  RMSNORM_GATEUP_ACT takes it in buf2 (buf3 0). */
+fk_status fk_weight_pair(fk_handle h, fk_weight gate, fk_weight up, fk_weight *out);
 /* dequantised fp32 [nrows, K] of rows [row0, row0+nrows) -- the bit-exactness probe */
 fk_status fk_weight_dequant(fk_handle h, fk_weight w, int64_t row0, int64_t nrows, float *host_out);
 fk_status fk_weight_nbytes(fk_handle h, fk_weight w, uint64_t *out);
@@ -156,6 +165,11 @@ fk_status fk_decode_chunk(fk_handle h, fk_graph g, uint32_t base_offset, uint32_
 /* same result with a host round trip per token (decode_chunk_host_loop, lib.rs:1129-1257) */
 fk_status fk_decode_chunk_host(fk_handle h, fk_graph g, uint32_t base_offset, uint32_t seed_token, int count,
                                uint32_t *out_history, double *gpu_seconds);
+
+/* tuning aid (no reference counterpart): while `buf` is non-zero the streamed kernels write per-block phase
+ * timestamps ([grid][8] u64 nanoseconds: start, dependency met, activations staged, rows done) into it; a graph
+ * captured while it is set gives task j the slice starting at entry j * 4096 */
+fk_status fk_debug_timeline(fk_handle h, fk_dptr buf);
 
 /* ---- tensor parallelism (no reference counterpart; NCCL over NVLink) ------ */
 fk_status fk_comm_unique_id(void *id128, size_t cap);          /* rank 0 makes the 128-byte id */

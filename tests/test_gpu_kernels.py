@@ -14,14 +14,24 @@ pytestmark = pytest.mark.gpu
 T = N.Task.make
 
 
-def dev_weight(rt, w: O.QWeight) -> int:
+def dev_weight(rt, w: O.QWeight, rope_rows=None, finalize=True) -> int:
+    """Upload MLX-layout tensors; `rope_rows=(head_dim, n_rot_rows)` asks for the RoPE-pair tile order."""
     wid = rt.weight_alloc(w.n, w.k, w.bits)
     if w.bits == 16:
         rt.weight_upload_rows(wid, 0, w.dense)
     else:
         rt.weight_upload_rows(wid, 0, w.packed, w.scales, w.biases)
-    rt.weight_finalize(wid)
+    if rope_rows and w.bits != 16 and rt.tiled:
+        rt.weight_set_rows(wid, 1, *rope_rows)
+    if finalize:
+        rt.weight_finalize(wid)
     return wid
+
+
+def gateup_bufs(rt, wg: O.QWeight, wu: O.QWeight) -> dict:
+    if wg.bits != 16 and rt.tiled:
+        return {2: rt.weight_pair(dev_weight(rt, wg, finalize=False), dev_weight(rt, wu, finalize=False)), 3: 0}
+    return {2: dev_weight(rt, wg), 3: dev_weight(rt, wu)}
 
 
 def normal(name, n, std=1.0, mean=0.0, seed=99):
@@ -48,6 +58,22 @@ def test_device_generator_and_dequant_are_bit_exact(runtime, bits):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     up = dev_weight(runtime, ref)                                    # uploaded MLX-layout tensors dequantise identically
     assert np.array_equal(runtime.weight_dequant(up, 0, n, k).view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_repacked_layouts_dequantise_bit_exactly(runtime, bits):
+    """Bit-exact dequantised weights out of the streaming layout: plain rows with ragged N and K, RoPE-pair
+    row order, and the gate/up interleave."""
+    rt = runtime
+    for n, k, rope in ((100, 896, None), (48, 4864, None), ((4 + 2 * 2) * 64, 320, (64, (4 + 2) * 64))):
+        w = O.gen_weight(stream_id(8, f"rp{bits}.{n}.{k}"), n, k, bits)
+        wid = dev_weight(rt, w, rope_rows=rope)
+        assert np.array_equal(rt.weight_dequant(wid, 0, n, k).view(np.uint32), O.dequant(w).view(np.uint32)), (n, k, rope)
+        assert np.array_equal(rt.weight_dequant(wid, n - 7, 7, k).view(np.uint32), O.dequant(w)[n - 7:].view(np.uint32))
+    wg, wu = O.gen_weight(stream_id(8, f"pg{bits}"), 40, 576, bits), O.gen_weight(stream_id(8, f"pu{bits}"), 40, 576, bits)
+    pid = gateup_bufs(rt, wg, wu)[2]
+    assert np.array_equal(rt.weight_dequant(pid, 0, 40, 576).view(np.uint32), O.dequant(wg).view(np.uint32))
+    assert np.array_equal(rt.weight_dequant(pid, 40, 40, 576).view(np.uint32), O.dequant(wu).view(np.uint32))
 
 
 def test_device_normal_fill_matches_oracle(runtime):
@@ -90,8 +116,8 @@ def test_rmsnorm_qkv_rope_store(runtime, bits, h, nq, nkv, hd, pos, cap):
     rt = runtime
     ck, cv, qd = rt.alloc(nkv * cap * hd * 2), rt.alloc(nkv * cap * hd * 2), rt.alloc(nq * hd * 2)
     rt.state_set(0, pos)
-    rt.launch(T(N.TASK_RMSNORM_QKV, 0, {0: rt.to_device(x), 1: rt.to_device(nw), 2: dev_weight(rt, w), 3: rt.to_device(lb),
-                                        4: qd, 5: ck, 6: cv}, [h, nq, nkv, hd, cap, 1], [eps, theta]))
+    rt.launch(T(N.TASK_RMSNORM_QKV, 0, {0: rt.to_device(x), 1: rt.to_device(nw), 2: dev_weight(rt, w, rope_rows=(hd, (nq + nkv) * hd)),
+                                        3: rt.to_device(lb), 4: qd, 5: ck, 6: cv}, [h, nq, nkv, hd, cap, 1], [eps, theta]))
     row = pos % cap
     assert_close_bf16(rt.download(qd, (nq * hd,), np.uint16), q, "q")
     gk = rt.download(ck, (nkv, cap, hd), np.uint16)
@@ -117,7 +143,7 @@ def test_sdpa_decode(runtime, nq, nkv, hd, pos, cap):
     kv_len = min(pos + 1, cap)
     scale = 1.0 / math.sqrt(hd)
     want = O.sdpa_decode(q, ck, cv, nq, nkv, hd, cap, kv_len, scale)
-    chunks = (cap + 63) // 64
+    chunks = (cap + 31) // 32
     out, part, cnt = rt.alloc(nq * hd * 2), rt.alloc(nq * chunks * (hd + 2) * 4), rt.alloc(nkv * 4)
     task = T(N.TASK_SDPA_DECODE, 0, {0: rt.to_device(q), 1: rt.to_device(ck), 2: rt.to_device(cv), 3: out, 4: part, 5: cnt},
              [nq, nkv, hd, cap], [scale])
@@ -141,7 +167,7 @@ def test_rmsnorm_gateup_act(runtime, bits, act, h, inter):
     nf = O.rmsnorm(x, nw, 1e-6)
     want = O.act(O.linear_acc(wg, nf), O.linear_acc(wu, nf), act)
     out = rt.alloc(inter * 2)
-    rt.launch(T(N.TASK_RMSNORM_GATEUP_ACT, 0, {0: rt.to_device(x), 1: rt.to_device(nw), 2: dev_weight(rt, wg), 3: dev_weight(rt, wu), 4: out},
+    rt.launch(T(N.TASK_RMSNORM_GATEUP_ACT, 0, {0: rt.to_device(x), 1: rt.to_device(nw), **gateup_bufs(rt, wg, wu), 4: out},
                 [h, inter, act], [1e-6]))
     assert_close_bf16(rt.download(out, (inter,), np.uint16), want, f"gateup act{act}")
 
@@ -155,7 +181,7 @@ def test_pending_norm_prologue(runtime):
     nf = O.rmsnorm(hnew, nw, 1e-6)
     want = O.act(O.linear_acc(wg, nf), O.linear_acc(wu, nf), 1)
     out, hout = rt.alloc(inter * 2), rt.alloc(h * 2)
-    rt.launch(T(N.TASK_RMSNORM_GATEUP_ACT, 0, {0: rt.to_device(x), 1: rt.to_device(nw), 2: dev_weight(rt, wg), 3: dev_weight(rt, wu), 4: out,
+    rt.launch(T(N.TASK_RMSNORM_GATEUP_ACT, 0, {0: rt.to_device(x), 1: rt.to_device(nw), **gateup_bufs(rt, wg, wu), 4: out,
                                                9: rt.to_device(y), 10: rt.to_device(wp), 11: hout}, [h, inter, 1], [1e-6]))
     got_h = rt.download(hout, (h,), np.uint16)
     assert np.mean(got_h != hnew) < 0.02
