@@ -389,8 +389,13 @@ static Shape plan_shape(Ctx *c, const Weight *w) {
     Shape s;
     s.warps = 8;
     s.smem = stream_smem_bytes(w->nsb, c->stages, 8);
-    if (s.smem > 113 * 1024 || c->force_warps == 16) { s.warps = 16; s.smem = stream_smem_bytes(w->nsb, c->stages, 16); }
-    const int slots = c->sm_count * (16 / s.warps), gw = slots * s.warps;
+    int per_sm = 2;
+    if (s.smem > 113 * 1024 || c->force_warps == 16) {
+        per_sm = 1;
+        const size_t wide = stream_smem_bytes(w->nsb, c->stages, 16);
+        if (wide <= 226 * 1024) { s.warps = 16; s.smem = wide; }          // else: 8 warps, one block per SM (very long K)
+    }
+    const int slots = c->sm_count * per_sm, gw = slots * s.warps;
     long long blocks;
     s.splits = 1;
     if (w->ntiles >= gw) blocks = slots;
