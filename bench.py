@@ -39,6 +39,8 @@ WORKLOADS = {
     "qwen0.5b-q4-ctx32": ("qwen2.5-0.5b", 4, 32),
 }
 METRIC = "batch-1 decode tok/s, 7B-shaped int4 ctx512"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
+NCU_TRAFFIC = {"fusekit_rmsnorm_gateup_act": 81.9e6 + 1.2e6, "fusekit_final_rmsnorm_lm_head": 315.9e6 + 0.4e6}
 KIND_NAMES = ["step_init", "embed_lookup_decode", "rmsnorm_qkv", "qk_norm_rope_store", "sdpa_decode", "linear_residual",
               "rmsnorm_gateup_act", "final_rmsnorm_lm_head", "argmax_finalize", "allreduce", "residual_add"]
 
@@ -154,9 +156,10 @@ def main():
     ap.add_argument("--impl", default="fusekit", choices=["fusekit", "reference"])
     ap.add_argument("--workload", default="qwen7b-q4-ctx512", choices=sorted(WORKLOADS))
     ap.add_argument("--chunk", type=int, default=CHUNK, help="tokens per step (64 = the reference's FK_CHUNK); smaller for profiler captures")
+    ap.add_argument("--tp", action="store_true", help="N ranks form one tensor-parallel group (one stream) instead of N replicas")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
-    ap.add_argument("--profile-nodes", type=int, default=3, help="repeats of the per-kernel timing pass (0 = skip)")
+    ap.add_argument("--profile-nodes", type=int, default=5, help="repeats of the per-kernel timing pass (0 = skip)")
     args = ap.parse_args()
     CHUNK = args.chunk
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -177,7 +180,15 @@ def main():
     config, bits, ctx = WORKLOADS[args.workload]
     spec = CONFIGS[config].with_bits(bits)
     cap = ctx + CHUNK * max(args.steps, args.warmup) + 8
-    eng = DecodeEngine(spec, cap, device=local)          # N > 1: N independent replicas, one per GPU
+    if args.tp and world > 1:
+        from fusekit_b200.runtime import comm_unique_id
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        uid = [comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        eng = DecodeEngine(spec, cap, device=local, tp_rank=rank, tp_size=world)
+        eng.comm_init(uid[0])
+    else:
+        eng = DecodeEngine(spec, cap, device=local)      # N > 1: N independent replicas, one per GPU
     eng.load_synthetic()
     eng.prefill_kv_synthetic(ctx)
     eng.capture()
@@ -207,31 +218,46 @@ def main():
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dev_s, wall_s = float(times[0]), float(times[1])
-    tokens = args.steps * CHUNK * world
+    streams = 1 if args.tp else world
+    tokens = args.steps * CHUNK * streams
     peak, peak_kind = measured_peak()
 
-    # per-kernel timing pass: every task of the token alone between two CUDA events on the library's
-    # stream (weights of 28 distinct layers are touched in turn, so each launch reads cold data)
+    # per-kernel timing: all launches of one kernel kind (one per layer, each touching its own layer's weights, so
+    # every launch reads cold data) back to back between two CUDA events on the library's stream
     roofline = None
     shares = {}
     if args.profile_nodes > 0 and rank == 0:
         eng.rt.state_set(tok, ctx + CHUNK)
-        prof = eng.profile_nodes(args.profile_nodes)
         by_kind = {}
-        for kind, layer, secs in prof:
-            by_kind.setdefault(kind, []).append(secs)
-        tot = sum(sum(v) for v in by_kind.values())
-        shares = {KIND_NAMES[k]: {"launches": len(v), "avg_us": 1e6 * sum(v) / len(v), "share": sum(v) / tot} for k, v in by_kind.items()}
-        dom = max(by_kind, key=lambda k: sum(by_kind[k]))
+        for t in eng.tasks:
+            by_kind.setdefault(t.kind, []).append(t)
+        per_kind = {k: eng.time_tasks(v, args.profile_nodes) / len(v) for k, v in by_kind.items()}
+        # a kernel kind may cover shapes of different size (o_proj and down_proj): time them apart
+        lin = by_kind.get(5, [])
+        subs = {}
+        for t in lin:
+            subs.setdefault((t.iarg[0], t.iarg[1]), []).append(t)
+        lin_times = {shape: eng.time_tasks(v, args.profile_nodes) / len(v) for shape, v in subs.items()}
+        tot = sum(per_kind[k] * len(v) for k, v in by_kind.items())
+        shares = {KIND_NAMES[k]: {"launches": len(v), "avg_us": 1e6 * per_kind[k], "share": per_kind[k] * len(v) / tot} for k, v in by_kind.items()}
+        for (kk, nn), tsec in lin_times.items():
+            shares[f"linear_residual[{kk}->{nn}]"] = {"launches": len(subs[(kk, nn)]), "avg_us": 1e6 * tsec}
         H, I = spec.hidden, spec.inter
-        algo = {6: 2 * spec.linear_bytes(H, I) - 2 * H - 2 * I,            # gate+up weights, x once, one T[I] out
-                5: None, 7: spec.linear_bytes(H, spec.vocab) - 2 * spec.vocab, 2: spec.linear_bytes(H, (spec.n_q + 2 * spec.n_kv) * spec.head_dim)}.get(dom)
-        if algo is None:
-            algo = spec.linear_bytes(I, H, True)
-        avg = sum(by_kind[dom]) / len(by_kind[dom])
+        algo_by_kind = {6: 2 * spec.linear_bytes(H, I) - 2 * H - 2 * I,            # gate+up weights, x once, one T[I] out
+                        7: spec.linear_bytes(H, spec.vocab) - 2 * spec.vocab,      # no logits are written
+                        2: spec.linear_bytes(H, (spec.n_q + 2 * spec.n_kv) * spec.head_dim)}
+        cands = {k: per_kind[k] * len(by_kind[k]) for k in algo_by_kind if k in per_kind}
+        for (kk, nn), tsec in lin_times.items():
+            cands[("lin", kk, nn)] = tsec * len(subs[(kk, nn)])
+        dom = max(cands, key=cands.get)
+        if isinstance(dom, tuple):
+            algo, avg, name = spec.linear_bytes(dom[1], dom[2], True), lin_times[(dom[1], dom[2])], f"fusekit_linear_residual[{dom[1]}->{dom[2]}]"
+        else:
+            algo, avg, name = algo_by_kind[dom], per_kind[dom], "fusekit_" + KIND_NAMES[dom]
         ach = algo / avg / 1e9
-        roofline = {"bound": "hbm", "kernel": "fusekit_" + KIND_NAMES[dom], "achieved": ach, "peak": peak, "peak_kind": peak_kind,
-                    "unit": "GB/s", "frac": ach / peak, "bytes_per_launch": algo, "avg_launch_us": avg * 1e6, "traffic": None}
+        roofline = {"bound": "hbm", "kernel": name, "achieved": ach, "peak": peak, "peak_kind": peak_kind,
+                    "unit": "GB/s", "frac": ach / peak, "bytes_per_launch": algo, "avg_launch_us": avg * 1e6,
+                    "traffic": NCU_TRAFFIC.get(name)}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -244,15 +270,15 @@ def main():
         bpt = spec.bytes_per_token(ctx + CHUNK * args.steps // 2)
         line = {
             "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "strong" if args.tp else "weak", "vs_baseline": None,
             "dtype": f"int{bits}" if bits != 16 else "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "tokens_per_step": CHUNK, "batch": 1, "ctx_start": ctx, "graph_nodes_per_token": nodes,
-                       "l2": "inputs (weights) larger than L2", "replicas": world, "pdl": eng.rt.info().get("pdl")},
+                       "l2": "inputs (weights) larger than L2", "replicas": streams, "tensor_parallel": world if args.tp else 1, "pdl": eng.rt.info().get("pdl")},
             "e2e": {"value": tokens / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 80, "d2h_bytes_per_step": CHUNK * 4 + 80},
             "gpu_launches": nodes * CHUNK * args.steps,
             "clocks": clocks,
-            "token_roofline": {"bytes_per_token": bpt, "achieved_gbs": bpt * (tps / world) / 1e9, "peak": peak, "peak_kind": peak_kind,
-                               "frac": bpt * (tps / world) / 1e9 / peak, "frac_of_8tbs": bpt * (tps / world) / 8e12},
+            "token_roofline": {"bytes_per_token": bpt, "achieved_gbs": bpt * (tps / streams) / 1e9, "peak": peak, "peak_kind": peak_kind,
+                               "frac": bpt * (tps / streams) / 1e9 / peak / (world if args.tp else 1), "frac_of_8tbs": bpt * (tps / streams) / 8e12 / (world if args.tp else 1)},
             "roofline": roofline, "kernel_shares": shares, "cpu_baseline": cpu_baseline,
         }
         print(json.dumps(line), flush=True)

@@ -67,6 +67,7 @@ def lib():
         "fk_graph_capture": [u64, P(Task), i32, P(u64)], "fk_graph_launch": [u64, u64, P(C.c_double)],
         "fk_graph_launch_async": [u64, u64], "fk_wait": [u64, P(C.c_double)],
         "fk_graph_profile_nodes": [u64, u64, i32, P(C.c_double), i32, P(i32)], "fk_graph_node_count": [u64, u64, P(i32)],
+        "fk_time_tasks": [u64, P(Task), i32, i32, P(C.c_double)],
         "fk_step": [u64, u64, u32, u32, P(u32), P(C.c_double)],
         "fk_decode_chunk": [u64, u64, u32, u32, i32, vp, P(C.c_double)],
         "fk_decode_chunk_host": [u64, u64, u32, u32, i32, vp, P(C.c_double)],

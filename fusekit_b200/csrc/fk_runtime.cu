@@ -715,6 +715,26 @@ extern "C" fk_status fk_graph_profile_nodes(fk_handle h, fk_graph gid, int repea
     return FK_OK;
 }
 
+// CUDA-event time of a list of tasks launched back to back on the library's stream, averaged over `repeats` passes
+// (reference: execute_icb_range returns GPU seconds for a command range, lib.rs:769); the decode state is restored.
+extern "C" fk_status fk_time_tasks(fk_handle h, const fk_task *tasks, int n, int repeats, double *seconds_per_pass) {
+    CTX(h);
+    if (!tasks || n <= 0 || repeats <= 0 || !seconds_per_pass) return fail(FK_ERR_VALUE, "bad arguments");
+    CU(cudaMemcpyAsync(c->pinned + 32, c->state, sizeof(FkState), cudaMemcpyDeviceToHost, c->stream));
+    CU(cudaStreamSynchronize(c->stream));
+    for (int j = 0; j < n; ++j) { fk_status s = run_task(c, tasks[j], next_stream_weight(c, tasks, n, j, true)); if (s) return s; }   // warm-up pass
+    CU(cudaEventRecord(c->ev0, c->stream));
+    for (int r = 0; r < repeats; ++r)
+        for (int j = 0; j < n; ++j) { fk_status s = run_task(c, tasks[j], next_stream_weight(c, tasks, n, j, true)); if (s) return s; }
+    CU(cudaEventRecord(c->ev1, c->stream));
+    CU(cudaEventSynchronize(c->ev1));
+    float ms = 0.0f; CU(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+    *seconds_per_pass = ms * 1e-3 / repeats;
+    CU(cudaMemcpyAsync(c->state, c->pinned + 32, sizeof(FkState), cudaMemcpyHostToDevice, c->stream));
+    CU(cudaStreamSynchronize(c->stream));
+    return FK_OK;
+}
+
 extern "C" fk_status fk_step(fk_handle h, fk_graph gid, uint32_t token, uint32_t offset, uint32_t *next_token, double *gpu_seconds) {
     return fk_decode_chunk(h, gid, offset, token, 1, next_token, gpu_seconds);
 }

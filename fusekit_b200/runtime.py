@@ -132,17 +132,60 @@ class Runtime:
         return t.value, o.value, e.value
 
 
+def linear_plan(spec: ModelSpec, rank: int = 0, world: int = 1):
+    """(name, [(leaf, src_row0, nrows)], k_global, k0, k, layer) for every weight object of tensor-parallel rank
+    `rank`: q/k/v, gate/up and the lm_head are split by output rows (whole heads), o/down by input columns
+    (whole quantisation groups), so a rank's tensors are exact slices of the full model's."""
+    hd, H = spec.head_dim, spec.hidden
+    nq, nkv, I, V = spec.n_q // world, spec.n_kv // world, spec.inter // world, spec.vocab // world
+    r = rank
+    plan = []
+    for l in range(spec.n_layers):
+        plan.append((f"layers.{l}.qkv", [("q_proj", r * nq * hd, nq * hd), ("k_proj", r * nkv * hd, nkv * hd),
+                                         ("v_proj", r * nkv * hd, nkv * hd)], H, 0, H, l))
+        plan.append((f"layers.{l}.o", [("o_proj", 0, H)], spec.n_q * hd, r * nq * hd, nq * hd, l))
+        plan.append((f"layers.{l}.gate", [("gate_proj", r * I, I)], H, 0, H, l))
+        plan.append((f"layers.{l}.up", [("up_proj", r * I, I)], H, 0, H, l))
+        plan.append((f"layers.{l}.down", [("down_proj", 0, H)], spec.inter, r * I, I, l))
+    plan.append(("lm_head", [("lm_head", r * V, V)], H, 0, H, -1))
+    return plan
+
+
+def vector_plan(spec: ModelSpec, rank: int = 0, world: int = 1):
+    """(name, leaf, layer, idx0, n, mean, std) for every bf16 vector/table of rank `rank` (norms and the embedding
+    are replicated, the q/k/v biases follow their heads)."""
+    hd, H = spec.head_dim, spec.hidden
+    nq, nkv = spec.n_q // world, spec.n_kv // world
+    r = rank
+    out = [("embed_tokens", "embed_tokens", -1, 0, spec.vocab * H, 0.0, 0.02), ("final_norm", "final_norm", -1, 0, H, 1.0, 0.02)]
+    for l in range(spec.n_layers):
+        out.append((f"layers.{l}.input_norm", "input_norm", l, 0, H, 1.0, 0.02))
+        out.append((f"layers.{l}.post_attention_norm", "post_attention_norm", l, 0, H, 1.0, 0.02))
+        if spec.arch == "qwen2":
+            out.append((f"layers.{l}.q_bias", "q_bias", l, r * nq * hd, nq * hd, 0.0, 0.02))
+            out.append((f"layers.{l}.k_bias", "k_bias", l, r * nkv * hd, nkv * hd, 0.0, 0.02))
+            out.append((f"layers.{l}.v_bias", "v_bias", l, r * nkv * hd, nkv * hd, 0.0, 0.02))
+        else:
+            for leaf, n in (("pre_feedforward_norm", H), ("post_feedforward_norm", H), ("q_norm", hd), ("k_norm", hd)):
+                out.append((f"layers.{l}.{leaf}", leaf, l, 0, n, 1.0, 0.02))
+    return out
+
+
+def check_tp(spec: ModelSpec, world: int):
+    if spec.n_kv % world or spec.n_q % world or spec.inter % world or spec.vocab % world:
+        raise ValueError("tensor-parallel degree must divide heads, intermediate size and vocabulary")
+    if (spec.inter // world) % 64 or (spec.n_q // world * spec.head_dim) % 64:
+        raise ValueError("row-split shards must keep whole quantisation groups of 64")
+    if world > 1 and spec.arch != "qwen2":
+        raise ValueError("tensor parallelism is wired for the Qwen-shaped layer only")
+
+
 class DecodeEngine:
     """One model instance (or one tensor-parallel slice of it) resident on a GPU."""
 
     def __init__(self, spec: ModelSpec, capacity: int, device: int = 0, tp_rank: int = 0, tp_size: int = 1,
                  want_logits: bool = False, runtime: Runtime | None = None):
-        if spec.n_kv % tp_size or spec.n_q % tp_size or spec.inter % tp_size or spec.vocab % tp_size:
-            raise ValueError("tensor-parallel degree must divide heads, intermediate size and vocabulary")
-        if (spec.inter // tp_size) % 64 or (spec.n_q // tp_size * spec.head_dim) % 64:
-            raise ValueError("row-split shards must keep whole quantisation groups of 64")
-        if tp_size > 1 and spec.arch != "qwen2":
-            raise ValueError("tensor parallelism is wired for the Qwen-shaped layer only")
+        check_tp(spec, tp_size)
         self.spec, self.capacity, self.rank, self.world = spec, capacity, tp_rank, tp_size
         self.rt = runtime or Runtime(device)
         self.want_logits = want_logits
@@ -192,35 +235,10 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ tensors
     def _linear_plan(self):
-        """(name, [(leaf, src_row0, nrows)], k_global, k0, k) for every weight object of this rank."""
-        s, r, hd = self.spec, self.rank, self.spec.head_dim
-        H, nq, nkv, I = s.hidden, self.nq, self.nkv, self.inter
-        plan = []
-        for l in range(s.n_layers):
-            plan.append((f"layers.{l}.qkv", [("q_proj", r * nq * hd, nq * hd), ("k_proj", r * nkv * hd, nkv * hd),
-                                             ("v_proj", r * nkv * hd, nkv * hd)], H, 0, H, l))
-            plan.append((f"layers.{l}.o", [("o_proj", 0, H)], s.n_q * hd, r * nq * hd, nq * hd, l))
-            plan.append((f"layers.{l}.gate", [("gate_proj", r * I, I)], H, 0, H, l))
-            plan.append((f"layers.{l}.up", [("up_proj", r * I, I)], H, 0, H, l))
-            plan.append((f"layers.{l}.down", [("down_proj", 0, H)], s.inter, r * I, I, l))
-        plan.append(("lm_head", [("lm_head", r * self.vocab, self.vocab)], H, 0, H, -1))
-        return plan
+        return linear_plan(self.spec, self.rank, self.world)
 
     def _vector_plan(self):
-        """(name, leaf, layer, idx0, n, mean, std) for every bf16 vector/table of this rank."""
-        s, r, hd, H = self.spec, self.rank, self.spec.head_dim, self.spec.hidden
-        out = [("embed_tokens", "embed_tokens", -1, 0, s.vocab * H, 0.0, 0.02), ("final_norm", "final_norm", -1, 0, H, 1.0, 0.02)]
-        for l in range(s.n_layers):
-            out.append((f"layers.{l}.input_norm", "input_norm", l, 0, H, 1.0, 0.02))
-            out.append((f"layers.{l}.post_attention_norm", "post_attention_norm", l, 0, H, 1.0, 0.02))
-            if s.arch == "qwen2":
-                out.append((f"layers.{l}.q_bias", "q_bias", l, r * self.nq * hd, self.nq * hd, 0.0, 0.02))
-                out.append((f"layers.{l}.k_bias", "k_bias", l, r * self.nkv * hd, self.nkv * hd, 0.0, 0.02))
-                out.append((f"layers.{l}.v_bias", "v_bias", l, r * self.nkv * hd, self.nkv * hd, 0.0, 0.02))
-            else:
-                for leaf, n in (("pre_feedforward_norm", H), ("post_feedforward_norm", H), ("q_norm", hd), ("k_norm", hd)):
-                    out.append((f"layers.{l}.{leaf}", leaf, l, 0, n, 1.0, 0.02))
-        return out
+        return vector_plan(self.spec, self.rank, self.world)
 
     def load_synthetic(self):
         """Generate every tensor on the device from its named stream (seeded, bit-identical to the
@@ -432,6 +450,13 @@ class DecodeEngine:
         N.check(self.rt.L.fk_graph_profile_nodes(self.rt.h, self.graph, repeats, out, n, C.byref(cnt)), "fk_graph_profile_nodes")
         return [(self.tasks[i].kind, self.tasks[i].layer, out[i]) for i in range(n)]
 
+    def time_tasks(self, tasks, repeats: int = 5) -> float:
+        """Seconds per pass of `tasks` launched back to back (CUDA events on the library's stream)."""
+        arr = (N.Task * len(tasks))(*tasks)
+        secs = C.c_double()
+        N.check(self.rt.L.fk_time_tasks(self.rt.h, arr, len(tasks), repeats, C.byref(secs)), "fk_time_tasks")
+        return secs.value
+
     def hidden_states(self) -> np.ndarray:
         """Residual stream after every layer of the last decoded token, [n_layers, H] bf16 bits."""
         s = self.spec
@@ -448,6 +473,7 @@ class DecodeEngine:
         return self.rt.download(self.logits, (self.vocab,), np.uint16)
 
     def comm_init(self, unique_id: bytes):
+        _ensure_nccl_path()
         buf = C.create_string_buffer(unique_id, 128)
         N.check(self.rt.L.fk_comm_init(self.rt.h, buf, self.rank, self.world), "fk_comm_init")
 
@@ -455,7 +481,22 @@ class DecodeEngine:
         self.rt.close()
 
 
+def _ensure_nccl_path():
+    """Point the library at the NCCL shipped in the Python environment unless FK_NCCL_LIB is already set."""
+    import importlib.util
+    import os
+    if os.environ.get("FK_NCCL_LIB"):
+        return
+    spec = importlib.util.find_spec("nvidia")
+    for base in (list(spec.submodule_search_locations) if spec and spec.submodule_search_locations else []):
+        cand = os.path.join(base, "nccl", "lib", "libnccl.so.2")
+        if os.path.exists(cand):
+            os.environ["FK_NCCL_LIB"] = cand
+            return
+
+
 def comm_unique_id() -> bytes:
+    _ensure_nccl_path()
     buf = C.create_string_buffer(128)
     N.check(N.lib().fk_comm_unique_id(buf, 128), "fk_comm_unique_id")
     return buf.raw

@@ -155,6 +155,9 @@ fk_status fk_graph_launch_async(fk_handle h, fk_graph g);
 fk_status fk_wait(fk_handle h, double *gpu_seconds);
 fk_status fk_graph_profile_nodes(fk_handle h, fk_graph g, int repeats, double *seconds_out, int cap, int *n_out);
 fk_status fk_graph_node_count(fk_handle h, fk_graph g, int *n_out);
+/* CUDA-event time of `n` tasks launched back to back, averaged over `repeats` passes after one warm-up pass
+ * (reference: execute_icb_range returns the GPU seconds of a command range, lib.rs:769) */
+fk_status fk_time_tasks(fk_handle h, const fk_task *tasks, int n, int repeats, double *seconds_per_pass);
 
 /* one token: write token/offset, replay, read the argmax back (step_decode, lib.rs:884-1012) */
 fk_status fk_step(fk_handle h, fk_graph g, uint32_t token, uint32_t offset, uint32_t *next_token, double *gpu_seconds);
