@@ -71,7 +71,8 @@ def lib():
         "fk_step": [u64, u64, u32, u32, P(u32), P(C.c_double)],
         "fk_decode_chunk": [u64, u64, u32, u32, i32, vp, P(C.c_double)],
         "fk_decode_chunk_host": [u64, u64, u32, u32, i32, vp, P(C.c_double)],
-        "fk_debug_timeline": [u64, u64], "fk_comm_unique_id": [vp, sz], "fk_comm_init": [u64, vp, i32, i32],
+        "fk_debug_timeline": [u64, u64],
+        "fk_sdpa_decode_noalloc": [vp, vp, vp, vp, i32, i32, i32, i32, u32, f32, vp], "fk_comm_unique_id": [vp, sz], "fk_comm_init": [u64, vp, i32, i32],
     }
     for name, args in sig.items():
         fn = getattr(L, name)

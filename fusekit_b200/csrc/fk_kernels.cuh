@@ -260,6 +260,7 @@ __global__ void k_qk_norm_rope_store(const FkState *st, QkNormArgs a) {
 struct SdpaArgs {
     const uint16_t *q, *ck, *cv; uint16_t *out; float *part; uint32_t *counter;
     int n_q, n_kv, hd, capacity, chunk; float scale; unsigned long long *tl;
+    int pos_override;       // >= 0: decode position given by the caller instead of the device-resident state
 };
 __device__ __forceinline__ void sd_stamp(unsigned long long *tl, int slot) {
     if (tl && threadIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tl[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = t; }
@@ -286,7 +287,7 @@ __global__ void __launch_bounds__(FK_SDPA_THREADS) k_sdpa_decode(const FkState *
     __shared__ int is_last;
     sd_stamp(a.tl, 0);
     pdl_launch_dependents(); pdl_wait();
-    const uint32_t pos = st->offset;
+    const uint32_t pos = a.pos_override >= 0 ? (uint32_t)a.pos_override : st->offset;
     const int kv_len = (int)min(pos + 1u, (uint32_t)a.capacity);
     const int n_active = (kv_len + FK_SDPA_KEYS - 1) / FK_SDPA_KEYS;
     if (chunk >= n_active) return;

@@ -488,7 +488,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (nkv <= 0 || nq % nkv || nq / nkv > FK_SDPA_MAXG || (hd != 64 && hd != 128 && hd != 256) || !b[4] || !b[5]) return fail(FK_ERR_VALUE, "sdpa: unsupported shape (group <= 8, head_dim in {64,128,256})");
         const int chunks = (cap + FK_SDPA_KEYS - 1) / FK_SDPA_KEYS, G = nq / nkv;
         SdpaArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], (uint32_t *)b[5],
-                   nq, nkv, hd, cap, chunks, f[0], c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr};
+                   nq, nkv, hd, cap, chunks, f[0], c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr, -1};
         if (c->sdpa_cluster && (hd != 256 || G <= 2)) {
             const size_t smem = sdpa_cl_smem_bytes(G, hd);
             const dim3 cgrid(FK_SDPA_CL, nkv), cblock(FK_SDPA_CW * 32);
@@ -770,6 +770,54 @@ extern "C" fk_status fk_decode_chunk_host(fk_handle h, fk_graph gid, uint32_t ba
         out_history[j] = tok; tot += t;
     }
     if (gpu_seconds) *gpu_seconds = tot;
+    return FK_OK;
+}
+
+// ------------------------------------------------------------------ allocation-free attention entry point
+// Scratch of fk_sdpa_decode_noalloc: split-K partials (m, l, o[head_dim] per q head and 32-key chunk) followed by one
+// arrival counter per kv head.  It lives in the library image, so every GPU that loads the library carries these
+// 4 MiB + 256 B until the process exits, and every call on a device shares them.
+#define FK_NOALLOC_PART_FLOATS (1u << 20)
+#define FK_NOALLOC_MAX_KV 64
+static __device__ __align__(256) unsigned char g_noalloc_scratch[FK_NOALLOC_PART_FLOATS * 4 + FK_NOALLOC_MAX_KV * 4];
+static void *g_noalloc_ptr[64];             // device address of the scratch, per device ordinal (host-side cache)
+static std::mutex g_noalloc_mu;
+
+extern "C" fk_status fk_sdpa_decode_noalloc(const void *q, const void *cache_k, const void *cache_v, void *out,
+                                            int n_q, int n_kv, int head_dim, int capacity, uint32_t pos, float scale, void *stream) {
+    if (!q || !cache_k || !cache_v || !out) return fail(FK_ERR_VALUE, "fk_sdpa_decode_noalloc: null pointer");
+    if (n_kv <= 0 || n_q <= 0 || n_q % n_kv || n_q / n_kv > FK_SDPA_MAXG || (head_dim != 64 && head_dim != 128 && head_dim != 256) || capacity <= 0)
+        return fail(FK_ERR_VALUE, "fk_sdpa_decode_noalloc: unsupported shape (group <= 8, head_dim in {64,128,256})");
+    const int chunks = (capacity + FK_SDPA_KEYS - 1) / FK_SDPA_KEYS, G = n_q / n_kv;
+    const size_t need = (size_t)n_q * chunks * (head_dim + 2);
+    if (need > FK_NOALLOC_PART_FLOATS || n_kv > FK_NOALLOC_MAX_KV)
+        return fail(FK_ERR_VALUE, "fk_sdpa_decode_noalloc: n_q * ceil(capacity/32) * (head_dim+2) = %zu floats exceeds the built-in scratch of %u floats (or more than %d kv heads)",
+                    need, FK_NOALLOC_PART_FLOATS, FK_NOALLOC_MAX_KV);
+    const size_t smem = sdpa_smem_bytes(G, head_dim, chunks);
+    if (smem > 200 * 1024) return fail(FK_ERR_VALUE, "fk_sdpa_decode_noalloc: capacity too large for the merge table");
+    int dev = 0; CU(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(FK_ERR_VALUE, "device ordinal %d out of range", dev);
+    void *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        if (!g_noalloc_ptr[dev]) {
+            // first call on this device: resolve the device address of the array (its name is only a host-side handle)
+            // and raise the kernel's shared-memory limit; neither allocates
+            void *p = nullptr;
+            CU(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+            CU(big_smem(k_sdpa_decode));
+            g_noalloc_ptr[dev] = p;
+        }
+        scratch = g_noalloc_ptr[dev];
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    float *part = (float *)scratch;
+    uint32_t *counters = (uint32_t *)((unsigned char *)scratch + (size_t)FK_NOALLOC_PART_FLOATS * 4);
+    CU(cudaMemsetAsync(counters, 0, FK_NOALLOC_MAX_KV * 4, st));       // the arrival counters must start at zero
+    SdpaArgs a{(const uint16_t *)q, (const uint16_t *)cache_k, (const uint16_t *)cache_v, (uint16_t *)out, part, counters,
+               n_q, n_kv, head_dim, capacity, chunks, scale, nullptr, (int)pos};
+    k_sdpa_decode<<<dim3(chunks, n_kv), dim3(FK_SDPA_THREADS), smem, st>>>((const FkState *)nullptr, a);
+    CU(cudaGetLastError());
     return FK_OK;
 }
 

@@ -169,6 +169,22 @@ fk_status fk_decode_chunk(fk_handle h, fk_graph g, uint32_t base_offset, uint32_
 fk_status fk_decode_chunk_host(fk_handle h, fk_graph g, uint32_t base_offset, uint32_t seed_token, int count,
                                uint32_t *out_history, double *gpu_seconds);
 
+/*
+ * Split-K GQA decode attention that allocates nothing.  It has no counterpart in the reference: it exists for
+ * hosts that must not touch the device allocator on their decode path -- a runtime that pre-sizes all device
+ * memory at start-up and forbids later cudaMalloc calls (they synchronise the device and can fail under memory
+ * pressure), or a host that only holds buffers handed to it by another framework.  q [n_q*head_dim], cache_k /
+ * cache_v [n_kv, capacity, head_dim] and out [n_q*head_dim] are bf16 device buffers of the caller; `pos` is the
+ * position being decoded (keys 0..min(pos+1, capacity)-1 are attended); `stream` is a cudaStream_t (0 = default)
+ * and the call returns once the work is queued.  The split-K partial sums live in a fixed 4 MiB array inside the
+ * library image, so the shape is limited to  n_q * ceil(capacity/32) * (head_dim+2) <= 1048576 floats  and at most
+ * 64 kv heads; larger shapes are refused with FK_ERR_VALUE.  The first call on a device looks up the array's device
+ * address (cudaGetSymbolAddress); make that call before any stream capture.  All calls on a device share the array:
+ * two calls whose kernels overlap on the GPU (different streams) race; calls queued on one stream are safe.
+ */
+fk_status fk_sdpa_decode_noalloc(const void *q, const void *cache_k, const void *cache_v, void *out,
+                                 int n_q, int n_kv, int head_dim, int capacity, uint32_t pos, float scale, void *stream);
+
 /* tuning aid (no reference counterpart): while `buf` is non-zero the streamed kernels write per-block phase
  * timestamps ([grid][8] u64 nanoseconds: start, dependency met, activations staged, rows done) into it; a graph
  * captured while it is set gives task j the slice starting at entry j * 4096 */
