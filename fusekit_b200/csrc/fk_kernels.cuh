@@ -418,7 +418,7 @@ __global__ void __launch_bounds__(FK_SDPA_THREADS) k_sdpa_decode(const FkState *
 #define FK_SDPA_CW 16           // warps per CTA
 #define FK_SDPA_KPW 8           // keys per warp iteration (4 lanes per key)
 __host__ __device__ inline size_t sdpa_cl_smem_bytes(int G, int hd) {
-    return sizeof(float) * (size_t)(G * hd + FK_SDPA_CW * G * (hd + 2) + G * (hd + 2) + 16);
+    return sizeof(float) * (size_t)(G * (hd + 16) + FK_SDPA_CW * G * (hd + 2) + G * (hd + 2) + FK_SDPA_CW * G + G + 16);
 }
 // Split-K GQA decode attention on a thread-block cluster: the CTAs of a cluster share one kv head and take
 // contiguous key ranges; inside a CTA every warp runs an online softmax over 8-key blocks, four lanes per key for
@@ -437,9 +437,11 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_cluster(const FkState 
     const int G = a.n_q / a.n_kv, kvh = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int rank = (int)cluster.block_rank(), CL = (int)cluster.num_blocks();
     const int stride = HD + 2;
-    float *qs = sm;                              // [G][HD]
-    float *wpart = qs + G * HD;                  // [CW][G][HD+2]
+    constexpr int QS = HD + 16, QP = HD / 4 + 4; // q rows padded per quarter so the four lanes of a key hit distinct banks
+    float *qs = sm;                              // [G][4][HD/4 + 4]
+    float *wpart = qs + G * QS;                  // [CW][G][HD+2]
     float *cpart = wpart + FK_SDPA_CW * G * stride;   // [G][HD+2]   read by the other CTAs of the cluster
+    float *wexp = cpart + G * stride;            // [CW][G] merge weights of the warp partials
     sd_stamp(a.tl, 0);
     pdl_launch_dependents();
     const uint32_t pos = st->offset;             // advanced by the previous token's head kernel, not by the QKV kernel in flight
@@ -470,7 +472,7 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_cluster(const FkState 
     int kb = k_begin + wid * FK_SDPA_KPW;
     if (kb < k_end) { load_k(kb, newest); load_v(kb, newest); }
     pdl_wait();
-    for (int i = tid; i < G * HD; i += NT) qs[i] = bf2f(a.q[kvh * G * HD + i]);
+    for (int i = tid; i < G * HD; i += NT) { const int g = i / HD, d = i - g * HD; qs[g * QS + (d / (HD / 4)) * QP + d % (HD / 4)] = bf2f(a.q[kvh * G * HD + i]); }
     float m[MAXG], l[MAXG], o[MAXG][DPL];
 #pragma unroll
     for (int g = 0; g < MAXG; ++g) { m[g] = -INFINITY; l[g] = 0.0f;
@@ -493,10 +495,10 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_cluster(const FkState 
         for (int c = 0; c < KV4; ++c) {
             const uint4 v = kreg[c];
             const float kf[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
-            const float *qp = qs + part * (HD / 4) + c * 8;
+            const float *qp = qs + part * QP + c * 8;
 #pragma unroll
             for (int g = 0; g < MAXG; ++g) if (g < G) {
-                const float4 q0 = *reinterpret_cast<const float4 *>(qp + g * HD), q1 = *reinterpret_cast<const float4 *>(qp + g * HD + 4);
+                const float4 q0 = *reinterpret_cast<const float4 *>(qp + g * QS), q1 = *reinterpret_cast<const float4 *>(qp + g * QS + 4);
                 dot[g] = fmaf(q0.x, kf[0], dot[g]); dot[g] = fmaf(q0.y, kf[1], dot[g]); dot[g] = fmaf(q0.z, kf[2], dot[g]); dot[g] = fmaf(q0.w, kf[3], dot[g]);
                 dot[g] = fmaf(q1.x, kf[4], dot[g]); dot[g] = fmaf(q1.y, kf[5], dot[g]); dot[g] = fmaf(q1.z, kf[6], dot[g]); dot[g] = fmaf(q1.w, kf[7], dot[g]);
             }
@@ -543,21 +545,25 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_cluster(const FkState 
         for (int j = 0; j < DPL; ++j) w[2 + lane * DPL + j] = o[g][j];
     }
     __syncthreads();
-    for (int i = tid; i < G * HD; i += NT) {             // fold the warps of this CTA
-        const int g = i / HD, d = i - g * HD;
+    // fold the warps of this CTA: weights e^(m_w - M) once per (warp, head), then every thread sums its outputs
+    const int nwp = min(FK_SDPA_CW, (k_end - k_begin + FK_SDPA_KPW - 1) / FK_SDPA_KPW);      // warps that saw keys
+    if (tid < G) {
         float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < FK_SDPA_CW; ++w) M = fmaxf(M, wpart[(w * G + g) * stride]);
-        float L = 0.0f, O = 0.0f;
-#pragma unroll
-        for (int w = 0; w < FK_SDPA_CW; ++w) {
-            const float *pw = wpart + (w * G + g) * stride;
+        for (int w = 0; w < nwp; ++w) M = fmaxf(M, wpart[(w * G + tid) * stride]);
+        float L = 0.0f;
+        for (int w = 0; w < nwp; ++w) {
+            const float *pw = wpart + (w * G + tid) * stride;
             const float e = pw[0] == -INFINITY ? 0.0f : expf(pw[0] - M);
-            L = fmaf(pw[1], e, L); O = fmaf(pw[2 + d], e, O);
+            wexp[w * G + tid] = e; L = fmaf(pw[1], e, L);
         }
-        float *cp = cpart + g * stride;
-        cp[2 + d] = O;
-        if (d == 0) { cp[0] = M; cp[1] = L; }
+        cpart[tid * stride] = M; cpart[tid * stride + 1] = L;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += NT) {
+        const int g = i / HD, d = i - g * HD;
+        float O = 0.0f;
+        for (int w = 0; w < nwp; ++w) O = fmaf(wpart[(w * G + g) * stride + 2 + d], wexp[w * G + g], O);
+        cpart[g * stride + 2 + d] = O;
     }
     sd_stamp(a.tl, 3);
     cluster.sync();
