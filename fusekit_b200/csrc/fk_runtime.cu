@@ -465,12 +465,14 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             if (sinks && (w->rows_kind != FK_ROWS_ROPE_PAIRS || w->hd != hd || w->n_rot != (nq + nkv) * hd)) return fail(FK_ERR_VALUE, "rmsnorm_qkv: weight rows must be laid out as RoPE pairs (fk_weight_set_rows)");
             if (!sinks && w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "rmsnorm_qkv without sinks takes plain row order");
             SQkvArgs sa{a.x, a.norm_w, StreamPlan(), a.lin_bias, a.q_out, a.cache_k, a.cache_v, a.k_out, a.v_out, a.pending, a.pending_w, a.h_out,
-                        H, nq, nkv, hd, cap, sinks, a.eps, a.log2theta};
+                        H, nq, nkv, hd, cap, sinks, a.eps, a.log2theta, nullptr};
+            if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }      // fp32 all-reduced projection + residual
             if (H > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "rmsnorm_qkv: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             const Shape sh = make_plan(c, w, &sa.P, nextw);
             STREAM_LAUNCH(k_s_rmsnorm_qkv, w, sh, c->state, sa);
             break;
         }
+        if (b[9] && !b[10]) return fail(FK_ERR_VALUE, "rmsnorm_qkv: the fused all-reduce residual needs 4/8-bit streamed weights");
         const int grid = grid_for(c, w->n / 2, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_rmsnorm_qkv<B>, dim3(grid), dim3(256), smem_bytes_for(H), (const FkState *)c->state, a));
         break;
@@ -523,7 +525,8 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (wg && wg->tiled && wg->rows_kind == FK_ROWS_GATE_UP) {       // paired gate/up weight (fk_weight_pair)
             if (wg->k != i[0] || wg->n != 2LL * i[1] || !b[4]) return fail(FK_ERR_VALUE, "gateup: shape mismatch");
             SGateUpArgs sa{(const uint16_t *)b[0], (const uint16_t *)b[1], StreamPlan(), (uint16_t *)b[4],
-                           (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0]};
+                           (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0], nullptr};
+            if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "gateup: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             const Shape sh = make_plan(c, wg, &sa.P, nextw);
             STREAM_LAUNCH(k_s_gateup, wg, sh, c->state, sa);
@@ -547,7 +550,8 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (w->tiled) {
             if (w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "lm_head takes plain row order");
             SHeadArgs sa{a.x, a.norm_w, StreamPlan(), a.logits, a.scratch, a.counter, a.pending, a.pending_w, a.h_out, a.history,
-                         a.h, a.v, a.vocab_offset, a.finalize, a.eps};
+                         a.h, a.v, a.vocab_offset, a.finalize, a.eps, nullptr};
+            if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "lm_head: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             const Shape sh = make_plan(c, w, &sa.P, nextw);
             STREAM_LAUNCH(k_s_head, w, sh, c->state, sa);

@@ -218,7 +218,7 @@ __device__ __forceinline__ void stage_plain(const StreamSmem &sm, const uint16_t
 template <int BITS>
 __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16_t *x, const uint16_t *w, int h, int nsb, float eps,
                                               const uint16_t *pending, const uint16_t *pending_w, uint16_t *h_out,
-                                              unsigned long long *tl = nullptr) {
+                                              unsigned long long *tl = nullptr, const float *pend_sum = nullptr) {
     stage_pad<BITS>(sm, h, nsb);
     const int nblk = h >> 3;
     uint4 xv[FK_STAGE_MAXB], wv[FK_STAGE_MAXB];
@@ -227,6 +227,20 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
         const int blk = i * blockDim.x + threadIdx.x;
         xv[i] = wv[i] = make_uint4(0, 0, 0, 0);
         if (blk < nblk) { xv[i] = *reinterpret_cast<const uint4 *>(x + (size_t)blk * 8); wv[i] = *reinterpret_cast<const uint4 *>(w + (size_t)blk * 8); }
+    }
+    if (pend_sum) {     // tensor parallel: x' = T(all-reduced projection + residual x); block 0 publishes it
+#pragma unroll
+        for (int i = 0; i < FK_STAGE_MAXB; ++i) {
+            const int blk = i * blockDim.x + threadIdx.x;
+            if (blk < nblk) {
+                const float4 s0 = *reinterpret_cast<const float4 *>(pend_sum + (size_t)blk * 8), s1 = *reinterpret_cast<const float4 *>(pend_sum + (size_t)blk * 8 + 4);
+                float f[8]; unpack8(xv[i], f);
+                const uint16_t o0 = f2bf(s0.x + f[0]), o1 = f2bf(s0.y + f[1]), o2 = f2bf(s0.z + f[2]), o3 = f2bf(s0.w + f[3]);
+                const uint16_t o4 = f2bf(s1.x + f[4]), o5 = f2bf(s1.y + f[5]), o6 = f2bf(s1.z + f[6]), o7 = f2bf(s1.w + f[7]);
+                xv[i] = make_uint4(o0 | ((uint32_t)o1 << 16), o2 | ((uint32_t)o3 << 16), o4 | ((uint32_t)o5 << 16), o6 | ((uint32_t)o7 << 16));
+                if (blockIdx.x == 0 && h_out) *reinterpret_cast<uint4 *>(h_out + (size_t)blk * 8) = xv[i];
+            }
+        }
     }
     if (pending) {
         uint4 pv[FK_STAGE_MAXB], pw[FK_STAGE_MAXB];
@@ -518,7 +532,7 @@ struct SQkvArgs {
     const uint16_t *x, *norm_w; StreamPlan P; const uint16_t *lin_bias;
     uint16_t *q_out, *cache_k, *cache_v, *k_out, *v_out;
     const uint16_t *pending, *pending_w; uint16_t *h_out;
-    int h, n_q, n_kv, hd, capacity, sinks; float eps, log2theta;
+    int h, n_q, n_kv, hd, capacity, sinks; float eps, log2theta; const float *pend_sum;
 };
 __device__ __forceinline__ void rope_rotate(float lo, float hi, int d, int half, uint32_t pos, float log2theta, uint16_t *o_lo, uint16_t *o_hi) {
     const float e = __fmul_rn(-__fdiv_rn((float)d, (float)half), log2theta);
@@ -537,7 +551,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkStat
     WarpStream ws; stream_begin(ws, a.P, sm);
     pdl_launch_dependents(); pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline);
+    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
     const uint32_t pos = st->offset;
     const int wrow = (int)(pos % (uint32_t)a.capacity), half = a.hd >> 1;
@@ -567,7 +581,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkStat
 struct SGateUpArgs {
     const uint16_t *x, *norm_w; StreamPlan P; uint16_t *act_out;
     const uint16_t *pending, *pending_w; uint16_t *h_out;
-    int h, inter, act; float eps;
+    int h, inter, act; float eps; const float *pend_sum;
 };
 __device__ __forceinline__ uint16_t s_act_swiglu(float ga, float ua) {
     const float g = rT(ga), u = rT(ua);
@@ -591,7 +605,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st
     WarpStream ws; stream_begin(ws, a.P, sm);
     pdl_launch_dependents(); pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline);
+    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
     auto epi = [&](int tile, int g, float gate, float up) {
         const int r = tile * 8 + g;
@@ -604,7 +618,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st
 struct SHeadArgs {
     const uint16_t *x, *norm_w; StreamPlan P; uint16_t *logits; unsigned long long *scratch; uint32_t *counter;
     const uint16_t *pending, *pending_w; uint16_t *h_out; uint32_t *history;
-    int h, v, vocab_offset, finalize; float eps;
+    int h, v, vocab_offset, finalize; float eps; const float *pend_sum;
 };
 __device__ __forceinline__ void s_finalize_token(FkState *st, uint32_t *history, unsigned long long best) {
     const uint32_t next = 0xffffffffu - (uint32_t)(best & 0xffffffffull);
@@ -624,7 +638,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, 
     WarpStream ws; stream_begin(ws, a.P, sm);
     pdl_launch_dependents(); pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline);
+    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
     unsigned long long best = 0ull;
     auto epi = [&](int tile, int g, float lo, float hi) {

@@ -210,7 +210,8 @@ class DecodeEngine:
         self.act_buf = rt.alloc(self.inter * 2)
         self.o_buf = rt.alloc(H * 2)                  # Gemma: o_proj output before its post-norm
         self.d_buf = rt.alloc(L * H * 2)              # Gemma: down_proj output before its post-norm
-        self.part_f32 = rt.alloc(H * 4)               # tensor-parallel partial sums
+        self.part_f32 = rt.alloc(H * 4)               # tensor-parallel partial sums (o_proj)
+        self.part_f32_b = rt.alloc(H * 4)             # tensor-parallel partial sums (down_proj)
         max_cap = max(s.layer_capacity(l, self.capacity) for l in range(L))
         chunks = (max_cap + 31) // 32
         self.sdpa_part = rt.alloc(self.nq * chunks * (s.head_dim + 2) * 4)
@@ -354,8 +355,11 @@ class DecodeEngine:
                 pend = {9: self.d_ptr(l - 1), 10: self.V[f"layers.{l-1}.post_feedforward_norm"], 11: self.x_ptr(l)}
             x_in = self.hb_ptr(l - 1) if (s.arch == "gemma3" and l > 0) else self.x_ptr(l)
             if s.arch == "qwen2":
+                tp_pend = {}
+                if tp and l > 0 and s.bits != 16 and self.rt.tiled:      # x[l] = T(all-reduced down_proj + h[l-1])
+                    x_in, tp_pend = self.hb_ptr(l - 1), {9: self.part_f32_b, 11: self.x_ptr(l)}
                 tasks.append(T(N.TASK_RMSNORM_QKV, l, {0: x_in, 1: self.V[f"layers.{l}.input_norm"], 2: self.W[f"layers.{l}.qkv"],
-                                                       3: self.V[f"layers.{l}.qkv_bias"], 4: self.q_buf, 5: ck, 6: cv},
+                                                       3: self.V[f"layers.{l}.qkv_bias"], 4: self.q_buf, 5: ck, 6: cv, **tp_pend},
                                [H, self.nq, self.nkv, hd, cap, 1], [s.eps, theta]))
             else:
                 tasks.append(T(N.TASK_RMSNORM_QKV, l, {0: x_in, 1: self.V[f"layers.{l}.input_norm"], 2: self.W[f"layers.{l}.qkv"],
@@ -374,16 +378,22 @@ class DecodeEngine:
                                [H, self.inter, s.act], [s.eps]))
                 tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 2: self.hb_ptr(l), 3: self.x_ptr(l + 1)}, [self.inter, H]))
             elif s.arch == "qwen2":
-                # row-split o/down: fp32 partial -> all-reduce over ranks -> residual add
-                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa_buf, 1: self.W[f"layers.{l}.o"], 4: self.part_f32}, [ko, H]))
-                tasks.append(T(N.TASK_ALLREDUCE, l, {0: self.part_f32}, [H, 0]))
-                tasks.append(T(N.TASK_RESIDUAL_ADD, l, {0: self.part_f32, 1: self.x_ptr(l), 2: self.hb_ptr(l)}, [H]))
-                tasks.append(T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: self.hb_ptr(l), 1: self.V[f"layers.{l}.post_attention_norm"],
+                # row-split o/down: fp32 partial -> all-reduce over ranks; the residual add is fused into the prologue of
+                # the next norm-first kernel (4/8-bit weights) or done by a small kernel (bf16 weights)
+                fused = s.bits != 16 and self.rt.tiled
+                pa, pb = self.part_f32, self.part_f32_b
+                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa_buf, 1: self.W[f"layers.{l}.o"], 4: pa}, [ko, H]))
+                tasks.append(T(N.TASK_ALLREDUCE, l, {0: pa}, [H, 0]))
+                gu_in = {0: self.x_ptr(l), 9: pa, 11: self.hb_ptr(l)} if fused else {0: self.hb_ptr(l)}
+                if not fused:
+                    tasks.append(T(N.TASK_RESIDUAL_ADD, l, {0: pa, 1: self.x_ptr(l), 2: self.hb_ptr(l)}, [H]))
+                tasks.append(T(N.TASK_RMSNORM_GATEUP_ACT, l, {**gu_in, 1: self.V[f"layers.{l}.post_attention_norm"],
                                                               **self._gateup_bufs(l), 4: self.act_buf},
                                [H, self.inter, s.act], [s.eps]))
-                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 4: self.part_f32}, [self.inter, H]))
-                tasks.append(T(N.TASK_ALLREDUCE, l, {0: self.part_f32}, [H, 0]))
-                tasks.append(T(N.TASK_RESIDUAL_ADD, l, {0: self.part_f32, 1: self.hb_ptr(l), 2: self.x_ptr(l + 1)}, [H]))
+                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 4: pb}, [self.inter, H]))
+                tasks.append(T(N.TASK_ALLREDUCE, l, {0: pb}, [H, 0]))
+                if not fused:
+                    tasks.append(T(N.TASK_RESIDUAL_ADD, l, {0: pb, 1: self.hb_ptr(l), 2: self.x_ptr(l + 1)}, [H]))
             else:
                 # Gemma-shaped: o_proj plain; post-attention norm + residual + pre-ffn norm fused into the gate/up prologue
                 tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa_buf, 1: self.W[f"layers.{l}.o"], 3: self.o_buf}, [ko, H]))
@@ -398,6 +408,9 @@ class DecodeEngine:
         x_fin = self.x_ptr(Lr)
         if s.arch == "gemma3":
             pend = {9: self.d_ptr(Lr - 1), 10: self.V[f"layers.{Lr-1}.post_feedforward_norm"], 11: self.x_ptr(Lr)}
+            x_fin = self.hb_ptr(Lr - 1)
+        elif tp and s.bits != 16 and self.rt.tiled:
+            pend = {9: self.part_f32_b, 11: self.x_ptr(Lr)}
             x_fin = self.hb_ptr(Lr - 1)
         tasks.append(T(N.TASK_FINAL_RMSNORM_LM_HEAD, -1, {0: x_fin, 1: self.V["final_norm"], 2: self.W["lm_head"], 3: self.logits,
                                                           4: self.argmax_scratch, 5: self.head_counter, **pend},

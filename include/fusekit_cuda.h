@@ -64,7 +64,8 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  * EMBED_LOOKUP_DECODE  buf0 table T[V,H]  buf1 x_out T[rows,H]            i0 H  i1 rows         f0 scale
  * RMSNORM_QKV          buf0 x T[H]  buf1 norm_w  buf2 weight(qkv rows: q|k|v)  buf3 lin_bias|0
  *                      buf4 q_out  buf5 cache_k  buf6 cache_v  buf7 k_out|0  buf8 v_out|0
- *                      buf9 pending_y|0  buf10 pending_norm_w  buf11 h_out   (Gemma: x <- T(x + rmsnorm(pending_y)))
+ *                      buf9 pending_y|0  buf10 pending_norm_w  buf11 h_out   (Gemma: x <- T(x + rmsnorm(pending_y)));
+ *                      with buf10 = 0, buf9 is an fp32 all-reduced projection: x <- T(buf9 + x) (tensor parallel)
  *                      i0 H  i1 n_q  i2 n_kv  i3 head_dim  i4 capacity  i5 sinks(1 = RoPE + cache store)
  *                      f0 eps  f1 rope_theta
  * QK_NORM_ROPE_STORE   buf0 q(in/out)  buf1 k_in  buf2 v_in  buf3 q_norm_w  buf4 k_norm_w  buf5 cache_k  buf6 cache_v
