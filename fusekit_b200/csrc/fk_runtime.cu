@@ -382,9 +382,9 @@ static int grid_for(Ctx *c, long long units, int warps_per_block) {
 }
 
 // Work split of a streamed kernel.  Blocks have 8 warps and sit two to an SM when their shared memory (ring +
-// staged activations) allows, else 16 warps and one per SM.  A warp owns whole row tiles when the grid has at least
-// one tile per warp; otherwise a block takes one tile at a time and its warps split K.
-struct Shape { int splits, grid, warps; size_t smem; };
+// staged activations) allows, else 16 warps and one per SM.  A block owns the row tiles block, block+grid, ... and
+// deals their units to its warps in chunks of 8 tiles (fk_stream.cuh).
+struct Shape { int grid, warps; size_t smem; };
 static Shape plan_shape(Ctx *c, const Weight *w) {
     Shape s;
     s.warps = 8;
@@ -395,16 +395,9 @@ static Shape plan_shape(Ctx *c, const Weight *w) {
         const size_t wide = stream_smem_bytes(w->nsb, c->stages, 16);
         if (wide <= 226 * 1024) { s.warps = 16; s.smem = wide; }          // else: 8 warps, one block per SM (very long K)
     }
-    const int slots = c->sm_count * per_sm, gw = slots * s.warps;
-    long long blocks;
-    s.splits = 1;
-    if (w->ntiles >= gw) blocks = slots;
-    else {
-        s.splits = w->nsb < s.warps ? w->nsb : s.warps;
-        if (s.splits == 1) blocks = (w->ntiles + s.warps - 1) / s.warps;          // a single super-block: warp per tile
-        else blocks = w->ntiles < slots ? w->ntiles : slots;
-    }
-    s.grid = (int)(blocks < 1 ? 1 : blocks);
+    const int slots = c->sm_count * per_sm;
+    s.grid = w->ntiles < slots ? w->ntiles : slots;
+    if (s.grid < 1) s.grid = 1;
     return s;
 }
 static Weight *get_w(Ctx *c, fk_weight w);
@@ -421,12 +414,12 @@ static Weight *task_stream_weight(Ctx *c, const fk_task *t) {
 }
 static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *next) {
     const Shape sh = plan_shape(c, w);
-    p->W = w->tview(); p->splits = sh.splits; p->stages = c->stages;
+    p->W = w->tview(); p->stages = c->stages;
     p->timeline = c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr;
-    p->next_units = nullptr; p->next_ntiles = p->next_nsb = p->next_splits = p->next_grid = p->next_warps = p->next_prefetch = 0;
+    p->next_units = nullptr; p->next_ntiles = p->next_nsb = p->next_grid = p->next_warps = p->next_prefetch = 0;
     if (next && c->prefetch > 0) {
         const Shape ns = plan_shape(c, next);
-        p->next_units = next->units; p->next_ntiles = next->ntiles; p->next_nsb = next->nsb; p->next_splits = ns.splits;
+        p->next_units = next->units; p->next_ntiles = next->ntiles; p->next_nsb = next->nsb;
         p->next_grid = ns.grid; p->next_warps = ns.warps; p->next_prefetch = c->prefetch;
     }
     return sh;

@@ -109,13 +109,13 @@ struct StreamSmem {
     float *xsum;        // [groups] sum of the activations of a group
     float *xinv;        // [groups] 1 / (power-of-two scale applied to the group's fp16 activations)
     float *red;         // [48]
-    float *fold;        // [2][warps][16] per-warp row sums of a k-split tile
+    float *fold;        // [2][FK_CHUNK_TILES][16 warps][16] per-warp row sums of the tiles of a chunk
     uint4 *xs;          // [groups * 8] permuted, group-scaled fp16 activations
     uint4 *ring;        // [warps * stages * FK_UNIT_VEC]
 };
 __host__ __device__ inline int stream_groups(int nsb) { return nsb * 8; }
 __host__ __device__ inline size_t stream_smem_bytes(int nsb, int stages, int warps) {
-    size_t b = 512 /*bars*/ + 128 /*zero*/ + (size_t)stream_groups(nsb) * 8 + 192 /*red*/ + 2 * FK_STREAM_MAXWARPS * 16 * 4 /*fold*/;
+    size_t b = 512 /*bars*/ + 128 /*zero*/ + (size_t)stream_groups(nsb) * 8 + 192 /*red*/ + 2 * 8 * FK_STREAM_MAXWARPS * 16 * 4 /*fold: 2 x FK_CHUNK_TILES tiles*/;
     b = (b + 15) & ~(size_t)15;
     b += (size_t)stream_groups(nsb) * 8 * 16;                  // xs
     b = (b + 127) & ~(size_t)127;
@@ -130,7 +130,7 @@ __device__ __forceinline__ StreamSmem stream_carve(unsigned char *base, int nsb,
     s.xsum = (float *)base; base += (size_t)stream_groups(nsb) * 4;
     s.xinv = (float *)base; base += (size_t)stream_groups(nsb) * 4;
     s.red = (float *)base; base += 192;
-    s.fold = (float *)base; base += 2 * FK_STREAM_MAXWARPS * 16 * 4;
+    s.fold = (float *)base; base += 2 * 8 * FK_STREAM_MAXWARPS * 16 * 4;
     base = (unsigned char *)(((uintptr_t)base + 15) & ~(uintptr_t)15);
     s.xs = (uint4 *)base; base += (size_t)stream_groups(nsb) * 8 * 16;
     base = (unsigned char *)(((uintptr_t)base + 127) & ~(uintptr_t)127);
@@ -330,12 +330,12 @@ __device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &s
 }
 
 // ------------------------------------------------------------------ per-warp unit stream
+#define FK_CHUNK_TILES 8            // row tiles a block works on at a time
 struct StreamPlan {
     TiledW W;
-    int splits;             // 1: a warp owns whole tiles; >1: the first `splits` warps of a block split K of the block's tile
     int stages;             // ring depth per warp
     // the streamed kernel that runs next: its first units are pulled into L2 while this kernel drains
-    const uint4 *next_units; int next_ntiles, next_nsb, next_splits, next_grid, next_warps, next_prefetch;
+    const uint4 *next_units; int next_ntiles, next_nsb, next_grid, next_warps, next_prefetch;
     unsigned long long *timeline;   // optional [grid][8] phase timestamps (ns) for tuning; null in normal use
 };
 __device__ __forceinline__ void stamp(const StreamPlan &p, int slot) {
@@ -344,22 +344,34 @@ __device__ __forceinline__ void stamp(const StreamPlan &p, int slot) {
         p.timeline[blockIdx.x * 8 + slot] = t;
     }
 }
-// position of a warp in its sequence of units: tiles tile0, tile0+stride, ... and super-blocks [sb0, sb1) of each
+// Work of a block: its row tiles are block, block+grid, block+2*grid, ... taken in chunks of FK_CHUNK_TILES; the
+// units (tile, super-block) of a chunk are dealt to the warps round-robin, so every warp gets the same number of
+// units (+-1) whatever the tile count, and a tile's K range is shared by the warps of one block only.
 struct Cursor {
-    int tile, sb, sb0, sb1, stride, ntiles;
-    __device__ __forceinline__ void init(int ntiles_, int nsb, int splits, int block, int nblocks, int wid, int nwarps) {
-        ntiles = ntiles_;
-        if (splits == 1) { tile = block * nwarps + wid; stride = nblocks * nwarps; sb0 = 0; sb1 = nsb; }
-        else {
-            tile = block; stride = nblocks;
-            if (wid < splits) { sb0 = wid * nsb / splits; sb1 = (wid + 1) * nsb / splits; } else { sb0 = sb1 = 0; tile = ntiles_; }
-        }
-        sb = sb0;
-        if (sb0 >= sb1) tile = ntiles_;
+    int nsb, ntl, nwarps, wid, block, grid;     // ntl: tiles of this block
+    int chunk, tq, sbv, left;                   // current chunk, tile inside the chunk, super-block, units left in the chunk
+    __device__ __forceinline__ void init(int ntiles, int nsb_, int block_, int grid_, int wid_, int nwarps_) {
+        nsb = nsb_; nwarps = nwarps_; wid = wid_; block = block_; grid = grid_;
+        ntl = block_ < ntiles ? (ntiles - block_ + grid_ - 1) / grid_ : 0;
+        chunk = -1; left = 0;
+        next_chunk();
     }
-    __device__ __forceinline__ bool valid() const { return tile < ntiles; }
-    __device__ __forceinline__ size_t unit_index(int nsb) const { return (size_t)tile * nsb + sb; }
-    __device__ __forceinline__ void advance() { if (++sb >= sb1) { sb = sb0; tile += stride; } }
+    __device__ __forceinline__ int chunk_tiles(int c) const { const int r = ntl - c * FK_CHUNK_TILES; return r < FK_CHUNK_TILES ? r : FK_CHUNK_TILES; }
+    // a warp takes a contiguous run of the chunk's units (tile-major), so it rarely changes tile
+    __device__ __forceinline__ void next_chunk() {
+        while (left == 0 && (++chunk) * FK_CHUNK_TILES < ntl) {
+            const int total = chunk_tiles(chunk) * nsb, u0 = wid * total / nwarps, u1 = (wid + 1) * total / nwarps;
+            left = u1 - u0; tq = u0 / nsb; sbv = u0 - tq * nsb;
+        }
+    }
+    __device__ __forceinline__ bool valid() const { return left > 0; }
+    __device__ __forceinline__ int tile_local() const { return chunk * FK_CHUNK_TILES + tq; }
+    __device__ __forceinline__ int sb() const { return sbv; }
+    __device__ __forceinline__ size_t unit_index() const { return (size_t)(block + tile_local() * grid) * nsb + sbv; }
+    __device__ __forceinline__ void advance() {
+        if (++sbv >= nsb) { sbv = 0; ++tq; }
+        if (--left == 0) next_chunk();
+    }
 };
 __device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
@@ -367,66 +379,76 @@ __device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
 // L2 prefetch of the units this (block, warp) slot will consume first in the next streamed kernel
 __device__ __forceinline__ void prefetch_next(const StreamPlan &p) {
     if (!p.next_units || (threadIdx.x & 31) != 0 || (int)blockIdx.x >= p.next_grid || (int)(threadIdx.x >> 5) >= p.next_warps) return;
-    Cursor c; c.init(p.next_ntiles, p.next_nsb, p.next_splits, blockIdx.x, p.next_grid, threadIdx.x >> 5, p.next_warps);
-    for (int i = 0; i < p.next_prefetch && c.valid(); ++i) { l2_prefetch(p.next_units + c.unit_index(p.next_nsb) * FK_UNIT_VEC, FK_UNIT_BYTES); c.advance(); }
+    Cursor c; c.init(p.next_ntiles, p.next_nsb, blockIdx.x, p.next_grid, threadIdx.x >> 5, p.next_warps);
+    for (int i = 0; i < p.next_prefetch && c.valid(); ++i) { l2_prefetch(p.next_units + c.unit_index() * FK_UNIT_VEC, FK_UNIT_BYTES); c.advance(); }
 }
 
 struct WarpStream { uint64_t *bars; uint4 *ring; Cursor prod; int stages; };
 __device__ __forceinline__ void stream_issue(WarpStream &ws, const StreamPlan &p, int stage) {
     if ((threadIdx.x & 31) == 0) {
         mbar_expect_tx(ws.bars + stage, FK_UNIT_BYTES);
-        bulk_g2s(ws.ring + (size_t)stage * FK_UNIT_VEC, p.W.units + ws.prod.unit_index(p.W.nsb) * FK_UNIT_VEC, FK_UNIT_BYTES, ws.bars + stage);
+        bulk_g2s(ws.ring + (size_t)stage * FK_UNIT_VEC, p.W.units + ws.prod.unit_index() * FK_UNIT_VEC, FK_UNIT_BYTES, ws.bars + stage);
     }
     ws.prod.advance();
 }
-// before griddepcontrol.wait: barriers up, ring filled with the warp's first units
+// before griddepcontrol.wait: barriers up, ring filled with the warp's first units, fold buffer cleared
 __device__ __forceinline__ void stream_begin(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     ws.stages = p.stages; ws.bars = sm.bars + wid * p.stages; ws.ring = sm.ring + (size_t)wid * p.stages * FK_UNIT_VEC;
-    ws.prod.init(p.W.ntiles, p.W.nsb, p.splits, blockIdx.x, gridDim.x, wid, blockDim.x >> 5);
+    ws.prod.init(p.W.ntiles, p.W.nsb, blockIdx.x, gridDim.x, wid, blockDim.x >> 5);
     if (lane == 0) { for (int s = 0; s < p.stages; ++s) mbar_init(ws.bars + s, 1); mbar_fence_init(); }
+    for (int i = threadIdx.x; i < 2 * FK_CHUNK_TILES * FK_STREAM_MAXWARPS * 16; i += blockDim.x) sm.fold[i] = 0.0f;
     __syncwarp();
     for (int s = 0; s < p.stages && ws.prod.valid(); ++s) stream_issue(ws, p, s);
 }
 
-// Walk the warp's units; `epi(tile, g, v_lo, v_hi)` receives the finished sums of tile rows g and g+8 on lanes with
-// (lane & 3) == 0 (of the owning warp, or of warp 0 when K is split across the block).  Returns false if a barrier
-// wait expired.  With splits > 1 every warp of the block must call this (it synchronises the block per tile).
+// Walk the block's chunks; `epi(tile, g, v_lo, v_hi)` receives the finished sums of tile rows g and g+8 on lanes with
+// (lane & 3) == 0 of the warp that folds the tile.  Returns false if a barrier wait expired.  Every warp of the block
+// must call this (it synchronises the block once per chunk).  The staging code must have synchronised the block
+// after stream_begin (it does), so the cleared fold buffer is visible.
 template <int BITS, class Epi>
 __device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm, Epi &epi) {
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    Cursor cons; cons.init(p.W.ntiles, p.W.nsb, p.splits, blockIdx.x, gridDim.x, wid, blockDim.x >> 5);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5, g = lane >> 2, t = lane & 3;
+    Cursor cons; cons.init(p.W.ntiles, p.W.nsb, blockIdx.x, gridDim.x, wid, nw);
     int consumed = 0;
     bool prefetched = false, ok = true;
     if (!ws.prod.valid()) { prefetch_next(p); prefetched = true; }       // everything this warp needs is already in flight
-    const int rounds = p.splits == 1 ? 0 : (p.W.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    for (int round = 0; p.splits == 1 ? cons.valid() : round < rounds; ++round) {
-        const int tile = p.splits == 1 ? cons.tile : (int)blockIdx.x + round * (int)gridDim.x;
-        float acc_lo = 0.0f, acc_hi = 0.0f;
-        while (ok && cons.valid() && cons.tile == tile) {
-            const int s = consumed % ws.stages;
-            if (!mbar_wait(ws.bars + s, (uint32_t)(consumed / ws.stages) & 1u)) { ok = false; break; }
-            unit_compute<BITS>(ws.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb, lane, acc_lo, acc_hi);
-            __syncwarp();
-            if (ws.prod.valid()) stream_issue(ws, p, s);                  // refill the stage just drained
-            else if (!prefetched) { prefetch_next(p); prefetched = true; }
-            ++consumed;
-            cons.advance();
-        }
-        acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 1); acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 2);
-        acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 1); acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 2);
-        if (p.splits == 1) {
-            if (t == 0) epi(tile, g, acc_lo, acc_hi);
-        } else {
-            float *fold = sm.fold + (round & 1) * FK_STREAM_MAXWARPS * 16;
-            if (t == 0 && wid < p.splits) { fold[wid * 16 + g] = acc_lo; fold[wid * 16 + 8 + g] = acc_hi; }
-            __syncthreads();
-            if (wid == 0 && t == 0) {
-                float lo = 0.0f, hi = 0.0f;
-                for (int q = 0; q < p.splits; ++q) { lo += fold[q * 16 + g]; hi += fold[q * 16 + 8 + g]; }
-                epi(tile, g, lo, hi);
+    const int nchunks = (cons.ntl + FK_CHUNK_TILES - 1) / FK_CHUNK_TILES;
+    for (int c = 0; c < nchunks; ++c) {
+        float *fold = sm.fold + (c & 1) * FK_CHUNK_TILES * FK_STREAM_MAXWARPS * 16;
+        const int ct = cons.chunk_tiles(c);
+        const bool whole = (ct % nw) == 0;          // every warp owns whole tiles of this chunk: no fold, no barrier
+        while (ok && cons.valid() && cons.chunk == c) {
+            const int tl = cons.tile_local();
+            float acc_lo = 0.0f, acc_hi = 0.0f;
+            while (ok && cons.valid() && cons.chunk == c && cons.tile_local() == tl) {
+                const int s = consumed % ws.stages;
+                if (!mbar_wait(ws.bars + s, (uint32_t)(consumed / ws.stages) & 1u)) { ok = false; break; }
+                unit_compute<BITS>(ws.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
+                __syncwarp();
+                if (ws.prod.valid()) stream_issue(ws, p, s);              // refill the stage just drained
+                else if (!prefetched) { prefetch_next(p); prefetched = true; }
+                ++consumed;
+                cons.advance();
+            }
+            acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 1); acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 2);
+            acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 1); acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 2);
+            if (t == 0) {
+                if (whole) epi((int)blockIdx.x + tl * (int)gridDim.x, g, acc_lo, acc_hi);
+                else { float *f = fold + ((tl - c * FK_CHUNK_TILES) * FK_STREAM_MAXWARPS + wid) * 16; f[g] = acc_lo; f[8 + g] = acc_hi; }
             }
         }
+        if (whole) continue;
+        __syncthreads();
+        for (int q = wid; q < ct; q += nw) {                  // fold tile q of the chunk in warp order, then its epilogue
+            if (t == 0) {
+                float *f = fold + q * FK_STREAM_MAXWARPS * 16;
+                float lo = 0.0f, hi = 0.0f;
+                for (int w = 0; w < nw; ++w) { lo += f[w * 16 + g]; hi += f[w * 16 + 8 + g]; f[w * 16 + g] = 0.0f; f[w * 16 + 8 + g] = 0.0f; }
+                epi((int)blockIdx.x + (c * FK_CHUNK_TILES + q) * (int)gridDim.x, g, lo, hi);
+            }
+        }
+        // the buffer of chunk c is cleared by its folding warps before chunk c+2 writes it: chunk c+1's barrier orders them
     }
     return ok;
 }
