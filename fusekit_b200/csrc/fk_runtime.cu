@@ -388,11 +388,11 @@ struct Shape { int grid, warps; size_t smem; };
 static Shape plan_shape(Ctx *c, const Weight *w) {
     Shape s;
     s.warps = 8;
-    s.smem = stream_smem_bytes(w->nsb, c->stages, 8);
+    s.smem = stream_smem_bytes(w->nsb, c->stages, 8, w->bits);
     int per_sm = 2;
     if (s.smem > 113 * 1024 || c->force_warps == 16) {
         per_sm = 1;
-        const size_t wide = stream_smem_bytes(w->nsb, c->stages, 16);
+        const size_t wide = stream_smem_bytes(w->nsb, c->stages, 16, w->bits);
         if (wide <= 226 * 1024) { s.warps = 16; s.smem = wide; }          // else: 8 warps, one block per SM (very long K)
     }
     const int slots = c->sm_count * per_sm;

@@ -7,15 +7,16 @@
 // and four biases that lane applies.  One cp.async.bulk (TMA, 1-D) moves a unit into a per-warp ring in
 // shared memory; a warp then needs one conflict-free LDS.128 per group.
 //
-// Arithmetic: packed weights become fp16 integers with one LOP3 per pair (0x6400 | q reads as 1024+q, and a
-// nibble left in bits 4-7 reads as 1024+16q) and one HFMA2 per pair that removes the offset exactly -- the
-// logic ops run on the ALU pipe, the fix-up on the FMA pipe.  Activations (bf16, 8 significant bits) are
-// staged as fp16 scaled per quantisation group by a power of two, so the conversion is exact, and
-// mma.sync.m16n8k16 accumulates x*q in fp32 -- the tensor pipe is the dot-product unit because unpack +
-// convert + FMA on the CUDA cores costs >2 issue slots per weight, more than the SM has at HBM speed.
-// The eight groups of a unit go to the eight accumulator columns (the activations of group j sit in B
-// column j, zeros elsewhere), so after a unit every lane owns four (row, group) sums and applies
-// s * c / scale_g + b * sum(x_g) to them.  8-bit weights use the same path with whole bytes (0x6400 | byte).
+// Arithmetic: integer tensor cores, exact.  The activations of a quantisation group (bf16, 8 significant bits)
+// are scaled by a power of two so the largest lands in [2^20, 2^21), rounded to integers (exact for everything
+// within 2^-13 of the group maximum, +-2^-21 of it below) and split into three 7-bit digits d0, d1 (unsigned) and
+// d2 (signed).  Packed nibbles become bytes four at a time (w & 0x0F0F0F0F and (w >> 4) & 0x0F0F0F0F: three ALU
+// ops per eight weights), 8-bit weights are used as stored, and mma.sync.m16n8k32 (u8 x u8/s8, s32 accumulate)
+// forms sum(q * digit) exactly; the three digit sums are recombined in fp32.  The tensor pipe is the dot-product
+// unit because unpack + convert + FMA on the CUDA cores costs >2 issue slots per weight, more than an SM has at
+// HBM speed.  The eight groups of a unit go to the eight accumulator columns (the activations of group j sit in
+// B column j, zeros elsewhere), so after a unit every lane owns four (row, group) sums and applies
+// s * c / scale_g + b * sum(x_g) to them.
 //
 // Scheduling: blocks of 8 warps, two per SM, each warp with its own ring and mbarriers.  With at least one
 // row tile per warp in the grid a warp owns whole tiles (all of K); otherwise the warps of a block split K
@@ -79,78 +80,68 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     for (uint32_t i = 0; i < FK_WAIT_LIMIT; ++i) if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// D[16x8] += A[16x32] * B[32x8], 8-bit operands, s32 accumulators.  B signed for the top digit only.
+__device__ __forceinline__ void imma_uu(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// (w & mask) | 0x64006400 -> fp16x2 (1024 + field) for the fields selected by mask
-template <uint32_t MASK> __device__ __forceinline__ uint32_t magic(uint32_t w) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, 0x64006400, 0xEA;" : "=r"(r) : "r"(w), "n"(MASK));
-    return r;
+__device__ __forceinline__ void imma_us(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t r;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
-#define H2_ONE 0x3C003C00u          // (1, 1)
-#define H2_M1024 0xE400E400u        // (-1024, -1024)
-#define H2_SIXTEENTH 0x2C002C00u    // (1/16, 1/16)
-#define H2_M64 0xD400D400u          // (-64, -64)
-__device__ __forceinline__ uint32_t q_lo(uint32_t w) { return hfma2(magic<0x000F000Fu>(w), H2_ONE, H2_M1024); }        // nibbles at bits 0-3
-__device__ __forceinline__ uint32_t q_hi(uint32_t w) { return hfma2(magic<0x00F000F0u>(w), H2_SIXTEENTH, H2_M64); }    // nibbles at bits 4-7
-__device__ __forceinline__ uint32_t q_byte(uint32_t w) { return hfma2(magic<0x00FF00FFu>(w), H2_ONE, H2_M1024); }      // bytes at bits 0-7
 
 // ------------------------------------------------------------------ shared-memory plan of a streamed kernel
 struct StreamSmem {
     uint64_t *bars;     // [warps * stages]
-    uint4 *zero;        // 8 zero vectors
+    uint4 *zero;        // 16 zero vectors (what a lane reads for the groups that are not its own)
     float *xsum;        // [groups] sum of the activations of a group
     float *xinv;        // [groups] 1 / (power-of-two scale applied to the group's fp16 activations)
     float *red;         // [48]
     float *fold;        // [2][FK_CHUNK_TILES][16 warps][16] per-warp row sums of the tiles of a chunk
-    uint4 *xs;          // [groups * 8] permuted, group-scaled fp16 activations
+    uint2 *xs;          // [groups][3 digits][4 lanes][1 or 2] activation digits in MMA B-operand order
     uint4 *ring;        // [warps * stages * FK_UNIT_VEC]
 };
 __host__ __device__ inline int stream_groups(int nsb) { return nsb * 8; }
-__host__ __device__ inline size_t stream_smem_bytes(int nsb, int stages, int warps) {
-    size_t b = 512 /*bars*/ + 128 /*zero*/ + (size_t)stream_groups(nsb) * 8 + 192 /*red*/ + 2 * 8 * FK_STREAM_MAXWARPS * 16 * 4 /*fold: 2 x FK_CHUNK_TILES tiles*/;
+// bytes of staged activation digits per group: 4-bit 3 x 4 x 16, 8-bit 3 x 4 x 8
+__host__ __device__ inline int xs_group_bytes(int bits) { return bits == 4 ? 192 : 96; }
+__host__ __device__ inline size_t stream_smem_bytes(int nsb, int stages, int warps, int bits) {
+    size_t b = 512 /*bars*/ + 256 /*zero*/ + (size_t)stream_groups(nsb) * 8 + 192 /*red*/ + 2 * 8 * FK_STREAM_MAXWARPS * 16 * 4 /*fold: 2 x FK_CHUNK_TILES tiles*/;
     b = (b + 15) & ~(size_t)15;
-    b += (size_t)stream_groups(nsb) * 8 * 16;                  // xs
+    b += (size_t)stream_groups(nsb) * xs_group_bytes(bits);    // xs
     b = (b + 127) & ~(size_t)127;
     b += (size_t)warps * stages * FK_UNIT_BYTES;
     return b + 128;
 }
-__device__ __forceinline__ StreamSmem stream_carve(unsigned char *base, int nsb, int stages) {
+__device__ __forceinline__ StreamSmem stream_carve(unsigned char *base, int nsb, int stages, int bits) {
     StreamSmem s;
     base = (unsigned char *)(((uintptr_t)base + 127) & ~(uintptr_t)127);
     s.bars = (uint64_t *)base; base += 512;
-    s.zero = (uint4 *)base; base += 128;
+    s.zero = (uint4 *)base; base += 256;
     s.xsum = (float *)base; base += (size_t)stream_groups(nsb) * 4;
     s.xinv = (float *)base; base += (size_t)stream_groups(nsb) * 4;
     s.red = (float *)base; base += 192;
     s.fold = (float *)base; base += 2 * 8 * FK_STREAM_MAXWARPS * 16 * 4;
     base = (unsigned char *)(((uintptr_t)base + 15) & ~(uintptr_t)15);
-    s.xs = (uint4 *)base; base += (size_t)stream_groups(nsb) * 8 * 16;
+    s.xs = (uint2 *)base; base += (size_t)stream_groups(nsb) * xs_group_bytes(bits);
     base = (unsigned char *)(((uintptr_t)base + 127) & ~(uintptr_t)127);
     s.ring = (uint4 *)base;
     return s;
 }
 
 // Activation staging.  A thread owns blocks of 8 consecutive activations (one 16-byte load), keeps them in
-// registers, and writes them as fp16, scaled by the group's power of two and permuted for the MMA B operand:
-//   4-bit: slots [x0,x4,x1,x5,x2,x6,x3,x7] so the pair registers line up with the (n_j, n_j+4) nibble pairs of a
-//          packed word; a group is 64 activations = 8 vectors (8 threads).
-//   8-bit: a packed word holds 4 activations; lane t of a 32-activation group owns one vector
-//          [x0,x2,x1,x3 of word A | x0,x2,x1,x3 of word B], word B being 16 activations further on (4 threads).
+// registers, and writes their three digits in MMA B-operand order:
+//   4-bit: a packed word covers the block; its even nibbles unpack into one A register and its odd nibbles into the
+//          other, so each digit is stored as bytes (x0,x2,x4,x6 | x1,x3,x5,x7); a group is 64 activations (8 threads);
+//          lane t of the MMA reads {word A pair, word B pair} = 16 bytes per digit, word B being 32 activations on.
+//   8-bit: a packed word covers 4 activations in order; a group (one MMA k-extent) is 32 activations (4 threads);
+//          lane t reads {word A, word B} = 8 bytes per digit, word B being 16 activations on.
 // Group maximum (for the scale) and group sum are reduced with shuffles across the threads of a group.
 __device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
     f[0] = bf_lo(v.x); f[1] = bf_hi(v.x); f[2] = bf_lo(v.y); f[3] = bf_hi(v.y);
     f[4] = bf_lo(v.z); f[5] = bf_hi(v.z); f[6] = bf_lo(v.w); f[7] = bf_hi(v.w);
 }
-__device__ __forceinline__ uint32_t h2pack(float a, float b) {
-    return (uint32_t)__half_as_ushort(__float2half_rn(a)) | ((uint32_t)__half_as_ushort(__float2half_rn(b)) << 16);
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 255) | ((uint32_t)(b & 255) << 8) | ((uint32_t)(c & 255) << 16) | ((uint32_t)(d & 255) << 24);
 }
 template <int BITS>
 __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const float (&f)[8], bool valid) {
@@ -161,21 +152,32 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
     constexpr int TPG = BITS == 4 ? 8 : 4;          // threads per group
 #pragma unroll
     for (int o = 1; o < TPG; o <<= 1) { s8 += __shfl_xor_sync(0xffffffffu, s8, o); m8 = fmaxf(m8, __shfl_xor_sync(0xffffffffu, m8, o)); }
-    // scale = 2^(12 - exponent(max)): the largest activation lands in [2^12, 2^13); bf16 -> fp16 is then exact
-    // for everything within 2^-26 of the maximum
-    int e = m8 > 0.0f ? (int)((__float_as_uint(m8) >> 23) & 0xffu) - 127 : 12;
+    // scale = 2^(20 - exponent(max)): the largest activation becomes an integer in [2^20, 2^21)
+    int e = m8 > 0.0f ? (int)((__float_as_uint(m8) >> 23) & 0xffu) - 127 : 20;
     e = e < -100 ? -100 : (e > 100 ? 100 : e);
-    const float scale = __uint_as_float((uint32_t)(127 + 12 - e) << 23), inv = __uint_as_float((uint32_t)(127 - 12 + e) << 23);
+    const float scale = __uint_as_float((uint32_t)(127 + 20 - e) << 23), inv = __uint_as_float((uint32_t)(127 - 20 + e) << 23);
     if (!valid) return;
+    int xi[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) xi[i] = __float2int_rn(f[i] * scale);
     if (BITS == 4) {
-        sm.xs[blk] = make_uint4(h2pack(f[0] * scale, f[4] * scale), h2pack(f[1] * scale, f[5] * scale),
-                                h2pack(f[2] * scale, f[6] * scale), h2pack(f[3] * scale, f[7] * scale));
-        if ((blk & 7) == 0) { sm.xsum[blk >> 3] = s8; sm.xinv[blk >> 3] = inv; }
+        const int grp = blk >> 3, bb = blk & 7;
+        uint2 *dst = sm.xs + (size_t)grp * 24 + (bb & 3) * 2 + (bb >> 2);        // [digit][lane][A|B], 8 uint2 per digit
+        dst[0] = make_uint2(pack4(xi[0] & 127, xi[2] & 127, xi[4] & 127, xi[6] & 127), pack4(xi[1] & 127, xi[3] & 127, xi[5] & 127, xi[7] & 127));
+        dst[8] = make_uint2(pack4((xi[0] >> 7) & 127, (xi[2] >> 7) & 127, (xi[4] >> 7) & 127, (xi[6] >> 7) & 127),
+                            pack4((xi[1] >> 7) & 127, (xi[3] >> 7) & 127, (xi[5] >> 7) & 127, (xi[7] >> 7) & 127));
+        dst[16] = make_uint2(pack4(xi[0] >> 14, xi[2] >> 14, xi[4] >> 14, xi[6] >> 14), pack4(xi[1] >> 14, xi[3] >> 14, xi[5] >> 14, xi[7] >> 14));
+        if (bb == 0) { sm.xsum[grp] = s8; sm.xinv[grp] = inv; }
     } else {
         const int k0 = blk * 8, grp = k0 >> 5, o = k0 & 31, half = o >> 4, t = (o >> 2) & 3;
-        uint2 *dst = reinterpret_cast<uint2 *>(sm.xs) + ((grp * 64 + t * 8 + half * 4) >> 2);
-        dst[0] = make_uint2(h2pack(f[0] * scale, f[2] * scale), h2pack(f[1] * scale, f[3] * scale));        // lane t
-        dst[2] = make_uint2(h2pack(f[4] * scale, f[6] * scale), h2pack(f[5] * scale, f[7] * scale));        // lane t+1
+        uint32_t *dst = reinterpret_cast<uint32_t *>(sm.xs) + (size_t)grp * 24 + t * 2 + half;   // [digit][lane][A|B] as words
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {                    // the two 4-blocks of this thread: lanes t and t+1
+            const int *x4 = xi + 4 * q;
+            dst[2 * q] = pack4(x4[0] & 127, x4[1] & 127, x4[2] & 127, x4[3] & 127);
+            dst[8 + 2 * q] = pack4((x4[0] >> 7) & 127, (x4[1] >> 7) & 127, (x4[2] >> 7) & 127, (x4[3] >> 7) & 127);
+            dst[16 + 2 * q] = pack4(x4[0] >> 14, x4[1] >> 14, x4[2] >> 14, x4[3] >> 14);
+        }
         if ((blk & 3) == 0) { sm.xsum[blk >> 2] = s8; sm.xinv[blk >> 2] = inv; }
     }
 }
@@ -183,8 +185,9 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
 template <int BITS>
 __device__ __forceinline__ void stage_pad(const StreamSmem &sm, int k, int nsb) {
     const int per_group = BITS == 4 ? 64 : 32, groups = stream_groups(nsb), g0 = k / per_group;
-    if (threadIdx.x < 8) sm.zero[threadIdx.x] = make_uint4(0, 0, 0, 0);
-    for (int i = g0 * 8 + threadIdx.x; i < groups * 8; i += blockDim.x) sm.xs[i] = make_uint4(0, 0, 0, 0);
+    constexpr int V = BITS == 4 ? 24 : 12;          // uint2 per group
+    if (threadIdx.x < 16) sm.zero[threadIdx.x] = make_uint4(0, 0, 0, 0);
+    for (int i = g0 * V + threadIdx.x; i < groups * V; i += blockDim.x) sm.xs[i] = make_uint2(0, 0);
     for (int i = g0 + threadIdx.x; i < groups; i += blockDim.x) { sm.xsum[i] = 0.0f; sm.xinv[i] = 0.0f; }
 }
 __device__ __forceinline__ void stamp_raw(unsigned long long *tl, int slot) {
@@ -294,26 +297,30 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
 template <int BITS>
 __device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     const int g = lane >> 2, t = lane & 3;
-    float cc[4][4];
+    int cc[2][3][4];                                 // [group parity][digit][fragment]: six independent MMA chains
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { cc[i][0] = cc[i][1] = cc[i][2] = cc[i][3] = 0.f; }
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int d = 0; d < 3; ++d) { cc[i][d][0] = cc[i][d][1] = cc[i][d][2] = cc[i][d][3] = 0; }
+    const uint2 *zero2 = reinterpret_cast<const uint2 *>(sm.zero);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const uint4 w = u[j * 32 + lane];
-        const uint4 *xp = (g == j) ? sm.xs + (size_t)(sb * 8 + j) * 8 : sm.zero;
-        float (&c)[4] = cc[j & 3];
         if (BITS == 4) {
-            const uint4 xa = xp[t], xb = xp[4 + t];
-            const uint32_t ax = w.x >> 8, az = w.z >> 8, ay = w.y >> 8, aw = w.w >> 8;
-            // word A: rows g (w.x) and g+8 (w.z); word B: rows g (w.y) and g+8 (w.w)
-            mma_f16(c, q_lo(w.x), q_lo(w.z), q_hi(w.x), q_hi(w.z), xa.x, xa.y);
-            mma_f16(c, q_lo(ax), q_lo(az), q_hi(ax), q_hi(az), xa.z, xa.w);
-            mma_f16(c, q_lo(w.y), q_lo(w.w), q_hi(w.y), q_hi(w.w), xb.x, xb.y);
-            mma_f16(c, q_lo(ay), q_lo(aw), q_hi(ay), q_hi(aw), xb.z, xb.w);
+            const uint4 *xp = (g == j) ? reinterpret_cast<const uint4 *>(sm.xs + (size_t)(sb * 8 + j) * 24) : reinterpret_cast<const uint4 *>(sm.zero);
+            // rows g (w.x word A, w.y word B) and g+8 (w.z, w.w): even nibbles -> k-slots 4t.., odd nibbles -> 4t+16..
+            const uint32_t ea = w.x & 0x0F0F0F0Fu, oa = (w.x >> 4) & 0x0F0F0F0Fu, ea8 = w.z & 0x0F0F0F0Fu, oa8 = (w.z >> 4) & 0x0F0F0F0Fu;
+            const uint32_t eb = w.y & 0x0F0F0F0Fu, ob = (w.y >> 4) & 0x0F0F0F0Fu, eb8 = w.w & 0x0F0F0F0Fu, ob8 = (w.w >> 4) & 0x0F0F0F0Fu;
+            const uint4 x0 = xp[t], x1 = xp[4 + t], x2 = xp[8 + t];     // digits 0..2: {A even, A odd, B even, B odd}
+            imma_uu(cc[j & 1][0], ea, ea8, oa, oa8, x0.x, x0.y); imma_uu(cc[j & 1][0], eb, eb8, ob, ob8, x0.z, x0.w);
+            imma_uu(cc[j & 1][1], ea, ea8, oa, oa8, x1.x, x1.y); imma_uu(cc[j & 1][1], eb, eb8, ob, ob8, x1.z, x1.w);
+            imma_us(cc[j & 1][2], ea, ea8, oa, oa8, x2.x, x2.y); imma_us(cc[j & 1][2], eb, eb8, ob, ob8, x2.z, x2.w);
         } else {
-            const uint4 xv = xp[t];                       // (x0,x2),(x1,x3) of word A, then of word B
-            mma_f16(c, q_byte(w.x), q_byte(w.z), q_byte(w.x >> 8), q_byte(w.z >> 8), xv.x, xv.y);
-            mma_f16(c, q_byte(w.y), q_byte(w.w), q_byte(w.y >> 8), q_byte(w.w >> 8), xv.z, xv.w);
+            const uint2 *xp = (g == j) ? sm.xs + (size_t)(sb * 8 + j) * 12 : zero2;
+            const uint2 x0 = xp[t], x1 = xp[4 + t], x2 = xp[8 + t];     // digits 0..2: {word A, word B}
+            imma_uu(cc[j & 1][0], w.x, w.z, w.y, w.w, x0.x, x0.y);
+            imma_uu(cc[j & 1][1], w.x, w.z, w.y, w.w, x1.x, x1.y);
+            imma_us(cc[j & 1][2], w.x, w.z, w.y, w.w, x2.x, x2.y);
         }
     }
     const uint4 sb4 = u[256 + lane];
@@ -321,12 +328,14 @@ __device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &s
     const float i0 = sm.xinv[sb * 8 + 2 * t], i1 = sm.xinv[sb * 8 + 2 * t + 1];
     const float s00 = bf_lo(sb4.x), s01 = bf_hi(sb4.x), s10 = bf_lo(sb4.y), s11 = bf_hi(sb4.y);
     const float b00 = bf_lo(sb4.z), b01 = bf_hi(sb4.z), b10 = bf_lo(sb4.w), b11 = bf_hi(sb4.w);
-    const float c0 = ((cc[0][0] + cc[1][0]) + (cc[2][0] + cc[3][0])) * i0, c1 = ((cc[0][1] + cc[1][1]) + (cc[2][1] + cc[3][1])) * i1;
-    const float c2 = ((cc[0][2] + cc[1][2]) + (cc[2][2] + cc[3][2])) * i0, c3 = ((cc[0][3] + cc[1][3]) + (cc[2][3] + cc[3][3])) * i1;
-    acc_lo = fmaf(s00, c0, acc_lo); acc_lo = fmaf(b00, X0, acc_lo);
-    acc_lo = fmaf(s01, c1, acc_lo); acc_lo = fmaf(b01, X1, acc_lo);
-    acc_hi = fmaf(s10, c2, acc_hi); acc_hi = fmaf(b10, X0, acc_hi);
-    acc_hi = fmaf(s11, c3, acc_hi); acc_hi = fmaf(b11, X1, acc_hi);
+    float c[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)      // digits recombined: d0 + 128 d1 + 16384 d2 (each partial sum is exact in fp32)
+        c[i] = fmaf(16384.0f, (float)(cc[0][2][i] + cc[1][2][i]), fmaf(128.0f, (float)(cc[0][1][i] + cc[1][1][i]), (float)(cc[0][0][i] + cc[1][0][i])));
+    acc_lo = fmaf(s00, c[0] * i0, acc_lo); acc_lo = fmaf(b00, X0, acc_lo);
+    acc_lo = fmaf(s01, c[1] * i1, acc_lo); acc_lo = fmaf(b01, X1, acc_lo);
+    acc_hi = fmaf(s10, c[2] * i0, acc_hi); acc_hi = fmaf(b10, X0, acc_hi);
+    acc_hi = fmaf(s11, c[3] * i1, acc_hi); acc_hi = fmaf(b11, X1, acc_hi);
 }
 
 // ------------------------------------------------------------------ per-warp unit stream
@@ -527,7 +536,7 @@ struct SLinArgs { const uint16_t *x; StreamPlan P; const uint16_t *residual; uin
 template <int BITS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st, SLinArgs a) {
     extern __shared__ unsigned char smem_stream[];
-    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages);
+    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
     pdl_launch_dependents(); pdl_wait();
@@ -568,7 +577,7 @@ __device__ __forceinline__ void rope_rotate(float lo, float hi, int d, int half,
 template <int BITS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkState *st, SQkvArgs a) {
     extern __shared__ unsigned char smem_stream[];
-    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages);
+    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
     pdl_launch_dependents(); pdl_wait();
@@ -622,7 +631,7 @@ __device__ __forceinline__ uint16_t s_act_geglu(float ga, float ua) {
 template <int BITS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st, SGateUpArgs a) {
     extern __shared__ unsigned char smem_stream[];
-    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages);
+    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
     pdl_launch_dependents(); pdl_wait();
@@ -654,7 +663,7 @@ __device__ __forceinline__ void s_finalize_token(FkState *st, uint32_t *history,
 template <int BITS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, SHeadArgs a) {
     extern __shared__ unsigned char smem_stream[];
-    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages);
+    const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     __shared__ unsigned long long wbest[WARPS]; __shared__ int is_last;
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
