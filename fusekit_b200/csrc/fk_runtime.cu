@@ -77,7 +77,7 @@ struct Ctx {
     uint32_t *pinned = nullptr;                 // host staging for state / history
     std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
     bool pending = false; bool pdl = true; int sm_count = 148;
-    bool use_tiled = true; int stages = 2; int prefetch = 1; int force_warps = 0; bool sdpa_cluster = true;
+    bool use_tiled = true; int stages = FK_STAGES; int prefetch = 1; int force_warps = 0; bool sdpa_cluster = true; int dbg_mode = 0;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
@@ -122,8 +122,8 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     CU(cudaMallocHost(&c->pinned, sizeof(uint32_t) * (c->hist_cap + 64)));
     const char *e = getenv("FK_PDL"); if (e && e[0] == '0') c->pdl = false;
     e = getenv("FK_LAYOUT"); if (e && !strcmp(e, "mlx")) c->use_tiled = false;
-    e = getenv("FK_STAGES"); if (e && atoi(e) >= 1 && atoi(e) <= 4) c->stages = atoi(e);
     e = getenv("FK_SDPA"); if (e && !strcmp(e, "ticket")) c->sdpa_cluster = false;
+    e = getenv("FK_DBG"); if (e) c->dbg_mode = atoi(e);
     e = getenv("FK_WARPS"); if (e) c->force_warps = atoi(e);
     e = getenv("FK_PREFETCH"); if (e && atoi(e) >= 0 && atoi(e) <= 64) c->prefetch = atoi(e);
 #define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>))
@@ -414,7 +414,7 @@ static Weight *task_stream_weight(Ctx *c, const fk_task *t) {
 }
 static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *next) {
     const Shape sh = plan_shape(c, w);
-    p->W = w->tview(); p->stages = c->stages;
+    p->W = w->tview(); p->stages = c->stages; p->dbg_mode = c->dbg_mode;
     p->timeline = c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr;
     p->next_units = nullptr; p->next_ntiles = p->next_nsb = p->next_grid = p->next_warps = p->next_prefetch = 0;
     if (next && c->prefetch > 0) {

@@ -31,6 +31,7 @@
 #define FK_UNIT_VEC 288                 // uint4 per unit: 8 groups x 32 lanes + 32 scale/bias vectors
 #define FK_UNIT_BYTES (FK_UNIT_VEC * 16)
 #define FK_STREAM_MAXWARPS 16         // blocks run 8 warps (two blocks per SM) or 16 (one per SM, large activations)
+#define FK_STAGES 2                     // ring depth per warp
 #define FK_WAIT_LIMIT (1u << 24)        // bounded mbarrier wait; on expiry the kernel flags an error and leaves
 
 enum { FK_ROWS_PLAIN = 0, FK_ROWS_ROPE_PAIRS = 1, FK_ROWS_GATE_UP = 2 };
@@ -94,8 +95,7 @@ __device__ __forceinline__ void imma_us(int (&c)[4], uint32_t a0, uint32_t a1, u
 struct StreamSmem {
     uint64_t *bars;     // [warps * stages]
     uint4 *zero;        // 16 zero vectors (what a lane reads for the groups that are not its own)
-    float *xsum;        // [groups] sum of the activations of a group
-    float *xinv;        // [groups] 1 / (power-of-two scale applied to the group's fp16 activations)
+    float2 *xsi;        // [groups] (sum of the group's activations, 1 / power-of-two scale of its integer digits)
     float *red;         // [48]
     float *fold;        // [2][FK_CHUNK_TILES][16 warps][16] per-warp row sums of the tiles of a chunk
     uint2 *xs;          // [groups][3 digits][4 lanes][1 or 2] activation digits in MMA B-operand order
@@ -117,8 +117,7 @@ __device__ __forceinline__ StreamSmem stream_carve(unsigned char *base, int nsb,
     base = (unsigned char *)(((uintptr_t)base + 127) & ~(uintptr_t)127);
     s.bars = (uint64_t *)base; base += 512;
     s.zero = (uint4 *)base; base += 256;
-    s.xsum = (float *)base; base += (size_t)stream_groups(nsb) * 4;
-    s.xinv = (float *)base; base += (size_t)stream_groups(nsb) * 4;
+    s.xsi = (float2 *)base; base += (size_t)stream_groups(nsb) * 8;
     s.red = (float *)base; base += 192;
     s.fold = (float *)base; base += 2 * 8 * FK_STREAM_MAXWARPS * 16 * 4;
     base = (unsigned char *)(((uintptr_t)base + 15) & ~(uintptr_t)15);
@@ -167,7 +166,7 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
         dst[8] = make_uint2(pack4((xi[0] >> 7) & 127, (xi[2] >> 7) & 127, (xi[4] >> 7) & 127, (xi[6] >> 7) & 127),
                             pack4((xi[1] >> 7) & 127, (xi[3] >> 7) & 127, (xi[5] >> 7) & 127, (xi[7] >> 7) & 127));
         dst[16] = make_uint2(pack4(xi[0] >> 14, xi[2] >> 14, xi[4] >> 14, xi[6] >> 14), pack4(xi[1] >> 14, xi[3] >> 14, xi[5] >> 14, xi[7] >> 14));
-        if (bb == 0) { sm.xsum[grp] = s8; sm.xinv[grp] = inv; }
+        if (bb == 0) sm.xsi[grp] = make_float2(s8, inv);
     } else {
         const int k0 = blk * 8, grp = k0 >> 5, o = k0 & 31, half = o >> 4, t = (o >> 2) & 3;
         uint32_t *dst = reinterpret_cast<uint32_t *>(sm.xs) + (size_t)grp * 24 + t * 2 + half;   // [digit][lane][A|B] as words
@@ -178,7 +177,7 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
             dst[8 + 2 * q] = pack4((x4[0] >> 7) & 127, (x4[1] >> 7) & 127, (x4[2] >> 7) & 127, (x4[3] >> 7) & 127);
             dst[16 + 2 * q] = pack4(x4[0] >> 14, x4[1] >> 14, x4[2] >> 14, x4[3] >> 14);
         }
-        if ((blk & 3) == 0) { sm.xsum[blk >> 2] = s8; sm.xinv[blk >> 2] = inv; }
+        if ((blk & 3) == 0) sm.xsi[blk >> 2] = make_float2(s8, inv);
     }
 }
 // zero vectors, padded tail of xs / xsum (k rounded up to whole units)
@@ -188,7 +187,7 @@ __device__ __forceinline__ void stage_pad(const StreamSmem &sm, int k, int nsb) 
     constexpr int V = BITS == 4 ? 24 : 12;          // uint2 per group
     if (threadIdx.x < 16) sm.zero[threadIdx.x] = make_uint4(0, 0, 0, 0);
     for (int i = g0 * V + threadIdx.x; i < groups * V; i += blockDim.x) sm.xs[i] = make_uint2(0, 0);
-    for (int i = g0 + threadIdx.x; i < groups; i += blockDim.x) { sm.xsum[i] = 0.0f; sm.xinv[i] = 0.0f; }
+    for (int i = g0 + threadIdx.x; i < groups; i += blockDim.x) sm.xsi[i] = make_float2(0.0f, 0.0f);
 }
 __device__ __forceinline__ void stamp_raw(unsigned long long *tl, int slot) {
     if (tl && threadIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tl[blockIdx.x * 8 + slot] = t; }
@@ -297,11 +296,9 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
 template <int BITS>
 __device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     const int g = lane >> 2, t = lane & 3;
-    int cc[2][3][4];                                 // [group parity][digit][fragment]: six independent MMA chains
+    int cc[3][4];                                    // [digit][fragment]: three independent MMA chains
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-        for (int d = 0; d < 3; ++d) { cc[i][d][0] = cc[i][d][1] = cc[i][d][2] = cc[i][d][3] = 0; }
+    for (int d = 0; d < 3; ++d) { cc[d][0] = cc[d][1] = cc[d][2] = cc[d][3] = 0; }
     const uint2 *zero2 = reinterpret_cast<const uint2 *>(sm.zero);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -312,26 +309,25 @@ __device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &s
             const uint32_t ea = w.x & 0x0F0F0F0Fu, oa = (w.x >> 4) & 0x0F0F0F0Fu, ea8 = w.z & 0x0F0F0F0Fu, oa8 = (w.z >> 4) & 0x0F0F0F0Fu;
             const uint32_t eb = w.y & 0x0F0F0F0Fu, ob = (w.y >> 4) & 0x0F0F0F0Fu, eb8 = w.w & 0x0F0F0F0Fu, ob8 = (w.w >> 4) & 0x0F0F0F0Fu;
             const uint4 x0 = xp[t], x1 = xp[4 + t], x2 = xp[8 + t];     // digits 0..2: {A even, A odd, B even, B odd}
-            imma_uu(cc[j & 1][0], ea, ea8, oa, oa8, x0.x, x0.y); imma_uu(cc[j & 1][0], eb, eb8, ob, ob8, x0.z, x0.w);
-            imma_uu(cc[j & 1][1], ea, ea8, oa, oa8, x1.x, x1.y); imma_uu(cc[j & 1][1], eb, eb8, ob, ob8, x1.z, x1.w);
-            imma_us(cc[j & 1][2], ea, ea8, oa, oa8, x2.x, x2.y); imma_us(cc[j & 1][2], eb, eb8, ob, ob8, x2.z, x2.w);
+            imma_uu(cc[0], ea, ea8, oa, oa8, x0.x, x0.y); imma_uu(cc[1], ea, ea8, oa, oa8, x1.x, x1.y); imma_us(cc[2], ea, ea8, oa, oa8, x2.x, x2.y);
+            imma_uu(cc[0], eb, eb8, ob, ob8, x0.z, x0.w); imma_uu(cc[1], eb, eb8, ob, ob8, x1.z, x1.w); imma_us(cc[2], eb, eb8, ob, ob8, x2.z, x2.w);
         } else {
             const uint2 *xp = (g == j) ? sm.xs + (size_t)(sb * 8 + j) * 12 : zero2;
             const uint2 x0 = xp[t], x1 = xp[4 + t], x2 = xp[8 + t];     // digits 0..2: {word A, word B}
-            imma_uu(cc[j & 1][0], w.x, w.z, w.y, w.w, x0.x, x0.y);
-            imma_uu(cc[j & 1][1], w.x, w.z, w.y, w.w, x1.x, x1.y);
-            imma_us(cc[j & 1][2], w.x, w.z, w.y, w.w, x2.x, x2.y);
+            imma_uu(cc[0], w.x, w.z, w.y, w.w, x0.x, x0.y);
+            imma_uu(cc[1], w.x, w.z, w.y, w.w, x1.x, x1.y);
+            imma_us(cc[2], w.x, w.z, w.y, w.w, x2.x, x2.y);
         }
     }
     const uint4 sb4 = u[256 + lane];
-    const float X0 = sm.xsum[sb * 8 + 2 * t], X1 = sm.xsum[sb * 8 + 2 * t + 1];
-    const float i0 = sm.xinv[sb * 8 + 2 * t], i1 = sm.xinv[sb * 8 + 2 * t + 1];
+    const float2 xi0 = sm.xsi[sb * 8 + 2 * t], xi1 = sm.xsi[sb * 8 + 2 * t + 1];      // (group sum, 1/scale)
+    const float X0 = xi0.x, X1 = xi1.x, i0 = xi0.y, i1 = xi1.y;
     const float s00 = bf_lo(sb4.x), s01 = bf_hi(sb4.x), s10 = bf_lo(sb4.y), s11 = bf_hi(sb4.y);
     const float b00 = bf_lo(sb4.z), b01 = bf_hi(sb4.z), b10 = bf_lo(sb4.w), b11 = bf_hi(sb4.w);
     float c[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)      // digits recombined: d0 + 128 d1 + 16384 d2 (each partial sum is exact in fp32)
-        c[i] = fmaf(16384.0f, (float)(cc[0][2][i] + cc[1][2][i]), fmaf(128.0f, (float)(cc[0][1][i] + cc[1][1][i]), (float)(cc[0][0][i] + cc[1][0][i])));
+    for (int i = 0; i < 4; ++i)      // digits recombined: (d0 + 128 d1) in s32, + 16384 d2 in fp32 (each part exact)
+        c[i] = fmaf(16384.0f, (float)cc[2][i], (float)(cc[0][i] + (cc[1][i] << 7)));
     acc_lo = fmaf(s00, c[0] * i0, acc_lo); acc_lo = fmaf(b00, X0, acc_lo);
     acc_lo = fmaf(s01, c[1] * i1, acc_lo); acc_lo = fmaf(b01, X1, acc_lo);
     acc_hi = fmaf(s10, c[2] * i0, acc_hi); acc_hi = fmaf(b10, X0, acc_hi);
@@ -346,6 +342,7 @@ struct StreamPlan {
     // the streamed kernel that runs next: its first units are pulled into L2 while this kernel drains
     const uint4 *next_units; int next_ntiles, next_nsb, next_grid, next_warps, next_prefetch;
     unsigned long long *timeline;   // optional [grid][8] phase timestamps (ns) for tuning; null in normal use
+    int dbg_mode;                   // tuning experiments: 1 = skip the unit arithmetic (memory only), 3 = recompute one resident unit (arithmetic only); results invalid
 };
 __device__ __forceinline__ void stamp(const StreamPlan &p, int slot) {
     if (p.timeline && threadIdx.x == 0) {
@@ -431,9 +428,10 @@ __device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, 
             const int tl = cons.tile_local();
             float acc_lo = 0.0f, acc_hi = 0.0f;
             while (ok && cons.valid() && cons.chunk == c && cons.tile_local() == tl) {
-                const int s = consumed % ws.stages;
-                if (!mbar_wait(ws.bars + s, (uint32_t)(consumed / ws.stages) & 1u)) { ok = false; break; }
-                unit_compute<BITS>(ws.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
+                const int s = consumed & (FK_STAGES - 1);
+                if (p.dbg_mode != 3 && !mbar_wait(ws.bars + s, (uint32_t)(consumed >> 1) & 1u)) { ok = false; break; }
+                if (p.dbg_mode == 0) unit_compute<BITS>(ws.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
+                else if (p.dbg_mode == 3) { if (ws.prod.valid()) ws.prod.advance(); ++consumed; cons.advance(); unit_compute<BITS>(ws.ring + (size_t)s * FK_UNIT_VEC, sm, 0, lane, acc_lo, acc_hi); continue; }
                 __syncwarp();
                 if (ws.prod.valid()) stream_issue(ws, p, s);              // refill the stage just drained
                 else if (!prefetched) { prefetch_next(p); prefetched = true; }
