@@ -418,7 +418,7 @@ __device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, 
     Cursor cons; cons.init(p.W.ntiles, p.W.nsb, blockIdx.x, gridDim.x, wid, nw);
     int consumed = 0;
     bool prefetched = false, ok = true;
-    if (!ws.prod.valid()) { prefetch_next(p); prefetched = true; }       // everything this warp needs is already in flight
+    if (!ws.prod.valid()) { pdl_launch_dependents(); prefetch_next(p); prefetched = true; }      // everything this warp needs is already in flight
     const int nchunks = (cons.ntl + FK_CHUNK_TILES - 1) / FK_CHUNK_TILES;
     for (int c = 0; c < nchunks; ++c) {
         float *fold = sm.fold + (c & 1) * FK_CHUNK_TILES * FK_STREAM_MAXWARPS * 16;
@@ -434,7 +434,7 @@ __device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, 
                 else if (p.dbg_mode == 3) { if (ws.prod.valid()) ws.prod.advance(); ++consumed; cons.advance(); unit_compute<BITS>(ws.ring + (size_t)s * FK_UNIT_VEC, sm, 0, lane, acc_lo, acc_hi); continue; }
                 __syncwarp();
                 if (ws.prod.valid()) stream_issue(ws, p, s);              // refill the stage just drained
-                else if (!prefetched) { prefetch_next(p); prefetched = true; }
+                else if (!prefetched) { pdl_launch_dependents(); prefetch_next(p); prefetched = true; }
                 ++consumed;
                 cons.advance();
             }
@@ -537,7 +537,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
-    pdl_launch_dependents(); pdl_wait();
+    pdl_wait();
     stamp(a.P, 1);
     stage_plain<BITS>(sm, a.x, a.k, a.P.W.nsb);
     stamp(a.P, 2);
@@ -554,6 +554,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st
         }
     };
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x100u);
+    pdl_launch_dependents();
     __syncthreads(); stamp(a.P, 3);
 }
 
@@ -578,7 +579,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkStat
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
-    pdl_launch_dependents(); pdl_wait();
+    pdl_wait();
     stamp(a.P, 1);
     stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
@@ -604,6 +605,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkStat
         } else { store(r0, f2bf(lo)); store(r1, f2bf(hi)); }
     };
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x200u);
+    pdl_launch_dependents();
     __syncthreads(); stamp(a.P, 3);
 }
 
@@ -632,7 +634,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
-    pdl_launch_dependents(); pdl_wait();
+    pdl_wait();
     stamp(a.P, 1);
     stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
@@ -641,6 +643,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st
         if (r < a.inter) a.act_out[r] = a.act == 1 ? s_act_geglu(gate, up) : s_act_swiglu(gate, up);
     };
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x400u);
+    pdl_launch_dependents();
     __syncthreads(); stamp(a.P, 3);
 }
 
@@ -665,7 +668,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, 
     __shared__ unsigned long long wbest[WARPS]; __shared__ int is_last;
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
-    pdl_launch_dependents(); pdl_wait();
+    pdl_wait();
     stamp(a.P, 1);
     stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
@@ -683,6 +686,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, 
         }
     };
     const bool ok = stream_run<BITS>(ws, a.P, sm, epi);
+    pdl_launch_dependents();
     if (!ok) atomicOr(&st->error, 0x800u);
     stamp(a.P, 3);
     best = warp_max_u64(best);
