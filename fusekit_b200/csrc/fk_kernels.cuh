@@ -443,6 +443,7 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_cluster(const FkState 
     float *cpart = wpart + FK_SDPA_CW * G * stride;   // [G][HD+2]   read by the other CTAs of the cluster
     float *wexp = cpart + G * stride;            // [CW][G] merge weights of the warp partials
     sd_stamp(a.tl, 0);
+    pdl_launch_dependents();                     // attention occupies few SMs: the next projection may start prefetching now
     const uint32_t pos = st->offset;             // advanced by the previous token's head kernel, not by the QKV kernel in flight
     const int kv_len = (int)min(pos + 1u, (uint32_t)a.capacity);
     const int newest = (int)(pos % (uint32_t)a.capacity);
@@ -536,7 +537,6 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_cluster(const FkState 
         }
     }
     sd_stamp(a.tl, 2);
-    pdl_launch_dependents();
 #pragma unroll
     for (int g = 0; g < MAXG; ++g) if (g < G) {
         float *w = wpart + (wid * G + g) * stride;

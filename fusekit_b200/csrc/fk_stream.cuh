@@ -193,19 +193,20 @@ __device__ __forceinline__ void stamp_raw(unsigned long long *tl, int slot) {
     if (tl && threadIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tl[blockIdx.x * 8 + slot] = t; }
 }
 #define FK_STAGE_MAXB 4          // 8-blocks per thread held in registers during staging (h <= 8 * 256 * 4)
+#define FK_PLAIN_MAXB 8          // 8-blocks per thread requested together by the plain staging
 template <int BITS>
 __device__ __forceinline__ void stage_plain(const StreamSmem &sm, const uint16_t *x, int k, int nsb) {
     stage_pad<BITS>(sm, k, nsb);
     const int nblk = k >> 3;
-    for (int b0 = 0; b0 < nblk; b0 += FK_STAGE_MAXB * blockDim.x) {
-        uint4 v[FK_STAGE_MAXB];
+    for (int b0 = 0; b0 < nblk; b0 += FK_PLAIN_MAXB * blockDim.x) {
+        uint4 v[FK_PLAIN_MAXB];
 #pragma unroll
-        for (int i = 0; i < FK_STAGE_MAXB; ++i) {          // all loads in flight before the first use
+        for (int i = 0; i < FK_PLAIN_MAXB; ++i) {          // all loads in flight before the first use
             const int blk = b0 + i * blockDim.x + threadIdx.x;
             v[i] = blk < nblk ? *reinterpret_cast<const uint4 *>(x + (size_t)blk * 8) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int i = 0; i < FK_STAGE_MAXB; ++i) {
+        for (int i = 0; i < FK_PLAIN_MAXB; ++i) {
             const int blk = b0 + i * blockDim.x + threadIdx.x;
             if (b0 + i * (int)blockDim.x >= nblk) break;   // uniform across the block
             float f[8]; unpack8(v[i], f);
