@@ -17,6 +17,7 @@ import math
 import numpy as np
 
 from . import _native as N
+from . import task_graph
 from .model_spec import ModelSpec, stream_id, tensor_name
 
 FK_CHUNK = 64          # tokens pre-submitted per chunk (reference FK_CHUNK, dispatch.py:1103)
@@ -287,12 +288,6 @@ class DecodeEngine:
         rt.weight_finalize(wid)
         self.W[name] = wid
 
-    def _gateup_bufs(self, l: int) -> dict:
-        key = f"layers.{l}.gateup"
-        if key in self.W:
-            return {2: self.W[key], 3: 0}
-        return {2: self.W[f"layers.{l}.gate"], 3: self.W[f"layers.{l}.up"]}
-
     def _load_vectors(self, fill):
         s, rt = self.spec, self.rt
         for name, leaf, layer, idx0, n, mean, std in self._vector_plan():
@@ -337,88 +332,62 @@ class DecodeEngine:
         self.rt.upload(ck, k); self.rt.upload(cv, v)
 
     # ------------------------------------------------------------------ dispatch list
+    def task_graph(self) -> dict:
+        """This engine's decode step as a v2 ``task_graph.json`` document (see task_graph.emit)."""
+        return task_graph.emit(self.spec, self.capacity, self.rank, self.world,
+                               fused_weights=self.rt.tiled, want_logits=self.want_logits)
+
+    def _resolve(self, role: str) -> int:
+        """Device address (or fk_weight id) behind one role string of the task graph."""
+        p = role.split(".")
+        if p[0] == "param":
+            return self.W["lm_head"] if p[1] == "lm_head" else self.V[p[1]]
+        if p[0] == "layer_param":
+            l, rel = int(p[1]), ".".join(p[2:])
+            w = {"self_attn.qkv_proj": "qkv", "self_attn.o_proj": "o", "mlp.gate_up_proj": "gateup", "mlp.gate_proj": "gate",
+                 "mlp.up_proj": "up", "mlp.down_proj": "down"}
+            v = {"input_layernorm.weight": "input_norm", "self_attn.qkv_proj.bias": "qkv_bias", "post_attention_layernorm.weight": "post_attention_norm",
+                 "pre_feedforward_layernorm.weight": "pre_feedforward_norm", "post_feedforward_layernorm.weight": "post_feedforward_norm",
+                 "self_attn.q_norm.weight": "q_norm", "self_attn.k_norm.weight": "k_norm"}
+            return self.W[f"layers.{l}.{w[rel]}"] if rel in w else self.V[f"layers.{l}.{v[rel]}"]
+        if p[0] == "layer_cache_k":
+            return self.cache[int(p[1])][0]
+        if p[0] == "layer_cache_v":
+            return self.cache[int(p[1])][1]
+        if p[0] == "global_scratch":
+            if p[1] == "x_in":
+                return self.x_ptr(int(p[2]))
+            return {"sdpa_partials": self.sdpa_part, "sdpa_counter": self.sdpa_counter, "argmax_scratch": self.argmax_scratch,
+                    "head_counter": self.head_counter, "logits": self.logits, "tp_partial_a": self.part_f32, "tp_partial_b": self.part_f32_b}[p[1]]
+        if p[0] == "layer_scratch":
+            if p[1].isdigit():
+                return {"h_attn": self.hb_ptr, "out_buf": self.d_ptr}[p[2]](int(p[1]))
+            return {"q_buf": self.q_buf, "k_buf": self.k_buf, "v_buf": self.v_buf, "sdpa_buf": self.sdpa_buf, "silu_up": self.act_buf,
+                    "o_buf": self.o_buf}[p[1]]
+        raise KeyError(f"unknown task-graph role {role!r}")
+
+    def dispatches_from(self, graph: dict) -> list:
+        """Resolve a task graph document (from task_graph.emit or read back from JSON) to the fk_task list, in
+        decode_pipeline order (the reference's replay order, src/codegen/task_graph_json.rs:1619-1664)."""
+        if graph.get("version") != task_graph.VERSION:
+            raise ValueError(f"task graph version {graph.get('version')} (this runtime reads {task_graph.VERSION})")
+        if graph.get("active_m", 1) != 1:
+            raise ValueError("only batch-1 decode graphs are dispatchable")
+        if not graph["decode_capabilities"]["dispatchable"]:
+            raise ValueError("task graph is not dispatchable: " + "; ".join(graph["decode_capabilities"]["reasons"]))
+        by_id = {t["id"]: t for t in graph["tasks"]}
+        out = []
+        for tid in graph["decode_pipeline"]:
+            t = by_id[tid]
+            bufs = {slot: self._resolve(role) for slot, role in task_graph.task_slots(t).items()}
+            out.append(N.Task.make(t["kind"], t.get("layer_idx", -1), bufs, t["iargs"], t["fargs"]))
+        return out
+
     def build_dispatches(self) -> list:
         """The per-token kernel list in replay order (reference order: embed -> per layer RmsNormQkv,
         SDPA, LinearResidual, gate/up chain, LinearResidual -> final head -> argmax;
         src/codegen/task_graph_json.rs:1619-1664, dispatch.py:3163-3611)."""
-        s, T, hd, H = self.spec, N.Task.make, self.spec.head_dim, self.spec.hidden
-        scale = 1.0 / math.sqrt(hd)
-        # Gemma-family embedding scale sqrt(H), held in bf16 (embed_lookup_decode.rs OUTPUT_SCALE)
-        emb_scale = _bf16_round(math.sqrt(H)) if s.arch == "gemma3" else 1.0
-        tasks = [T(N.TASK_EMBED_LOOKUP_DECODE, -1, {0: self.V["embed_tokens"], 1: self.x_ptr(0)}, [H, 1], [emb_scale])]
-        tp = self.world > 1
-        for l in range(s.n_layers):
-            ck, cv, cap = self.cache[l]
-            theta = s.layer_theta(l)
-            pend = {}
-            if s.arch == "gemma3" and l > 0:
-                pend = {9: self.d_ptr(l - 1), 10: self.V[f"layers.{l-1}.post_feedforward_norm"], 11: self.x_ptr(l)}
-            x_in = self.hb_ptr(l - 1) if (s.arch == "gemma3" and l > 0) else self.x_ptr(l)
-            if s.arch == "qwen2":
-                tp_pend = {}
-                if tp and l > 0 and s.bits != 16 and self.rt.tiled:      # x[l] = T(all-reduced down_proj + h[l-1])
-                    x_in, tp_pend = self.hb_ptr(l - 1), {9: self.part_f32_b, 11: self.x_ptr(l)}
-                tasks.append(T(N.TASK_RMSNORM_QKV, l, {0: x_in, 1: self.V[f"layers.{l}.input_norm"], 2: self.W[f"layers.{l}.qkv"],
-                                                       3: self.V[f"layers.{l}.qkv_bias"], 4: self.q_buf, 5: ck, 6: cv, **tp_pend},
-                               [H, self.nq, self.nkv, hd, cap, 1], [s.eps, theta]))
-            else:
-                tasks.append(T(N.TASK_RMSNORM_QKV, l, {0: x_in, 1: self.V[f"layers.{l}.input_norm"], 2: self.W[f"layers.{l}.qkv"],
-                                                       4: self.q_buf, 7: self.k_buf, 8: self.v_buf, **pend},
-                               [H, self.nq, self.nkv, hd, cap, 0], [s.eps, theta]))
-                tasks.append(T(N.TASK_QK_NORM_ROPE_STORE, l, {0: self.q_buf, 1: self.k_buf, 2: self.v_buf, 3: self.V[f"layers.{l}.q_norm"],
-                                                              4: self.V[f"layers.{l}.k_norm"], 5: ck, 6: cv},
-                               [self.nq, self.nkv, hd, cap], [s.eps, theta]))
-            tasks.append(T(N.TASK_SDPA_DECODE, l, {0: self.q_buf, 1: ck, 2: cv, 3: self.sdpa_buf, 4: self.sdpa_part, 5: self.sdpa_counter},
-                           [self.nq, self.nkv, hd, cap], [scale]))
-            ko = self.nq * hd
-            if s.arch == "qwen2" and not tp:
-                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa_buf, 1: self.W[f"layers.{l}.o"], 2: self.x_ptr(l), 3: self.hb_ptr(l)}, [ko, H]))
-                tasks.append(T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: self.hb_ptr(l), 1: self.V[f"layers.{l}.post_attention_norm"],
-                                                              **self._gateup_bufs(l), 4: self.act_buf},
-                               [H, self.inter, s.act], [s.eps]))
-                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 2: self.hb_ptr(l), 3: self.x_ptr(l + 1)}, [self.inter, H]))
-            elif s.arch == "qwen2":
-                # row-split o/down: fp32 partial -> all-reduce over ranks; the residual add is fused into the prologue of
-                # the next norm-first kernel (4/8-bit weights) or done by a small kernel (bf16 weights)
-                fused = s.bits != 16 and self.rt.tiled
-                pa, pb = self.part_f32, self.part_f32_b
-                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa_buf, 1: self.W[f"layers.{l}.o"], 4: pa}, [ko, H]))
-                tasks.append(T(N.TASK_ALLREDUCE, l, {0: pa}, [H, 0]))
-                gu_in = {0: self.x_ptr(l), 9: pa, 11: self.hb_ptr(l)} if fused else {0: self.hb_ptr(l)}
-                if not fused:
-                    tasks.append(T(N.TASK_RESIDUAL_ADD, l, {0: pa, 1: self.x_ptr(l), 2: self.hb_ptr(l)}, [H]))
-                tasks.append(T(N.TASK_RMSNORM_GATEUP_ACT, l, {**gu_in, 1: self.V[f"layers.{l}.post_attention_norm"],
-                                                              **self._gateup_bufs(l), 4: self.act_buf},
-                               [H, self.inter, s.act], [s.eps]))
-                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 4: pb}, [self.inter, H]))
-                tasks.append(T(N.TASK_ALLREDUCE, l, {0: pb}, [H, 0]))
-                if not fused:
-                    tasks.append(T(N.TASK_RESIDUAL_ADD, l, {0: pb, 1: self.hb_ptr(l), 2: self.x_ptr(l + 1)}, [H]))
-            else:
-                # Gemma-shaped: o_proj plain; post-attention norm + residual + pre-ffn norm fused into the gate/up prologue
-                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa_buf, 1: self.W[f"layers.{l}.o"], 3: self.o_buf}, [ko, H]))
-                x_res = self.x_ptr(l)
-                tasks.append(T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: x_res, 1: self.V[f"layers.{l}.pre_feedforward_norm"],
-                                                              **self._gateup_bufs(l), 4: self.act_buf,
-                                                              9: self.o_buf, 10: self.V[f"layers.{l}.post_attention_norm"], 11: self.hb_ptr(l)},
-                               [H, self.inter, s.act], [s.eps]))
-                tasks.append(T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act_buf, 1: self.W[f"layers.{l}.down"], 3: self.d_ptr(l)}, [self.inter, H]))
-        Lr = s.n_layers
-        pend = {}
-        x_fin = self.x_ptr(Lr)
-        if s.arch == "gemma3":
-            pend = {9: self.d_ptr(Lr - 1), 10: self.V[f"layers.{Lr-1}.post_feedforward_norm"], 11: self.x_ptr(Lr)}
-            x_fin = self.hb_ptr(Lr - 1)
-        elif tp and s.bits != 16 and self.rt.tiled:
-            pend = {9: self.part_f32_b, 11: self.x_ptr(Lr)}
-            x_fin = self.hb_ptr(Lr - 1)
-        tasks.append(T(N.TASK_FINAL_RMSNORM_LM_HEAD, -1, {0: x_fin, 1: self.V["final_norm"], 2: self.W["lm_head"], 3: self.logits,
-                                                          4: self.argmax_scratch, 5: self.head_counter, **pend},
-                       [H, self.vocab, self.rank * self.vocab, 0 if tp else 1], [s.eps]))
-        if tp:
-            tasks.append(T(N.TASK_ALLREDUCE, -1, {0: self.argmax_scratch}, [1, 1]))
-            tasks.append(T(N.TASK_ARGMAX_FINALIZE, -1, {4: self.argmax_scratch}, [1]))
-        return tasks
+        return self.dispatches_from(self.task_graph())
 
     # ------------------------------------------------------------------ replay
     def capture(self) -> int:

@@ -1,0 +1,164 @@
+"""The compiler -> runtime contract of the decode path: a ``task_graph.json`` in the reference's v2 shape.
+
+The reference writes this file from its fused task graph (src/codegen/task_graph_json.rs:33-226) and its runtime
+reads it back (src/runtime/plan.rs:39-164, python/fusekit_runtime/dispatch.py:318-329).  Capture needs MLX, so here
+the graph is produced from the model shape: one task per fused decode kernel, buffers named by the reference's
+role strings (``slot_role_key``, src/codegen/kernels/mod.rs:5531-5576), in replay order (embed -> per layer
+RmsNormQkv, SDPA, LinearResidual, gate/up chain, LinearResidual -> final head; task_graph_json.rs:1619-1664).
+``DecodeEngine.build_dispatches`` resolves exactly this structure to device addresses, so the JSON is the list the
+GPU replays, not a description on the side.
+"""
+from __future__ import annotations
+
+import math
+
+from .model_spec import ModelSpec
+
+VERSION = 2
+KINDS = ["step_init", "embed_lookup_decode", "rmsnorm_qkv", "qk_norm_rope_store", "sdpa_decode", "linear_residual",
+         "rmsnorm_gateup_act", "final_rmsnorm_lm_head", "argmax_finalize", "allreduce", "residual_add"]
+KERNEL = {k: "fusekit_" + k for k in KINDS}
+(K_STEP, K_EMBED, K_QKV, K_QKNORM, K_SDPA, K_LIN, K_GATEUP, K_HEAD, K_ARGMAX, K_ALLREDUCE, K_RESADD) = range(11)
+
+
+def _bf16_round(v: float) -> float:
+    import struct
+    u = struct.unpack("<I", struct.pack("<f", v))[0]
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return struct.unpack("<f", struct.pack("<I", u))[0]
+
+
+def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fused_weights: bool = True,
+         want_logits: bool = False) -> dict:
+    """Build the v2 task graph of one decode step for `spec` (one tensor-parallel rank of it).
+
+    `fused_weights`: 4/8-bit weights in the streaming layout (gate/up paired, residual add after an all-reduce fused
+    into the next norm-first kernel); False describes the generic kernels (bf16 weights)."""
+    s, hd, H = spec, spec.head_dim, spec.hidden
+    nq, nkv, inter, vocab = s.n_q // tp_size, s.n_kv // tp_size, s.inter // tp_size, s.vocab // tp_size
+    tp = tp_size > 1
+    fused = fused_weights and s.bits != 16
+    tasks: list[dict] = []
+
+    def add(kind, layer, bufs, iargs, fargs=()):
+        tasks.append({"kind": kind, "layer": layer, "bufs": {int(k): v for k, v in bufs.items() if v}, "iargs": [int(v) for v in iargs],
+                      "fargs": [float(v) for v in fargs]})
+
+    x = lambda l: f"global_scratch.x_in.{l}"           # residual stream entering layer l (l = n_layers: final)
+    hb = lambda l: f"layer_scratch.{l}.h_attn"
+    lp = lambda l, rel: f"layer_param.{l}.{rel}"
+    gateup = (lambda l: {2: lp(l, "mlp.gate_up_proj")}) if fused else (lambda l: {2: lp(l, "mlp.gate_proj"), 3: lp(l, "mlp.up_proj")})
+    emb_scale = _bf16_round(math.sqrt(H)) if s.arch == "gemma3" else 1.0      # embed_lookup_decode.rs OUTPUT_SCALE
+    add(K_EMBED, -1, {0: "param.embed_tokens", 1: x(0)}, [H, 1], [emb_scale])
+    scale = 1.0 / math.sqrt(hd)
+    for l in range(s.n_layers):
+        cap, theta = s.layer_capacity(l, capacity), s.layer_theta(l)
+        ck, cv = f"layer_cache_k.{l}", f"layer_cache_v.{l}"
+        if s.arch == "qwen2":
+            x_in, pend = x(l), {}
+            if tp and l > 0 and fused:                     # x[l] = T(all-reduced down_proj + h[l-1])
+                x_in, pend = hb(l - 1), {9: "global_scratch.tp_partial_b", 11: x(l)}
+            add(K_QKV, l, {0: x_in, 1: lp(l, "input_layernorm.weight"), 2: lp(l, "self_attn.qkv_proj"), 3: lp(l, "self_attn.qkv_proj.bias"),
+                           4: "layer_scratch.q_buf", 5: ck, 6: cv, **pend}, [H, nq, nkv, hd, cap, 1], [s.eps, theta])
+        else:
+            x_in, pend = x(l), {}
+            if l > 0:                                      # Gemma: x[l] = T(h[l-1] + rmsnorm(down_out[l-1]))
+                x_in, pend = hb(l - 1), {9: f"layer_scratch.{l-1}.out_buf", 10: lp(l - 1, "post_feedforward_layernorm.weight"), 11: x(l)}
+            add(K_QKV, l, {0: x_in, 1: lp(l, "input_layernorm.weight"), 2: lp(l, "self_attn.qkv_proj"), 4: "layer_scratch.q_buf",
+                           7: "layer_scratch.k_buf", 8: "layer_scratch.v_buf", **pend}, [H, nq, nkv, hd, cap, 0], [s.eps, theta])
+            add(K_QKNORM, l, {0: "layer_scratch.q_buf", 1: "layer_scratch.k_buf", 2: "layer_scratch.v_buf", 3: lp(l, "self_attn.q_norm.weight"),
+                              4: lp(l, "self_attn.k_norm.weight"), 5: ck, 6: cv}, [nq, nkv, hd, cap], [s.eps, theta])
+        add(K_SDPA, l, {0: "layer_scratch.q_buf", 1: ck, 2: cv, 3: "layer_scratch.sdpa_buf", 4: "global_scratch.sdpa_partials",
+                        5: "global_scratch.sdpa_counter"}, [nq, nkv, hd, cap], [scale])
+        ko = nq * hd
+        if s.arch == "qwen2" and not tp:
+            add(K_LIN, l, {0: "layer_scratch.sdpa_buf", 1: lp(l, "self_attn.o_proj"), 2: x(l), 3: hb(l)}, [ko, H])
+            add(K_GATEUP, l, {0: hb(l), 1: lp(l, "post_attention_layernorm.weight"), **gateup(l), 4: "layer_scratch.silu_up"}, [H, inter, s.act], [s.eps])
+            add(K_LIN, l, {0: "layer_scratch.silu_up", 1: lp(l, "mlp.down_proj"), 2: hb(l), 3: x(l + 1)}, [inter, H])
+        elif s.arch == "qwen2":
+            # row-split o/down: fp32 partial -> all-reduce over the ranks; the residual add rides in the next norm-first
+            # kernel's prologue (streamed weights) or in a small kernel (generic weights)
+            pa, pb = "global_scratch.tp_partial_a", "global_scratch.tp_partial_b"
+            add(K_LIN, l, {0: "layer_scratch.sdpa_buf", 1: lp(l, "self_attn.o_proj"), 4: pa}, [ko, H])
+            add(K_ALLREDUCE, l, {0: pa}, [H, 0])
+            if not fused:
+                add(K_RESADD, l, {0: pa, 1: x(l), 2: hb(l)}, [H])
+            gin = {0: x(l), 9: pa, 11: hb(l)} if fused else {0: hb(l)}
+            add(K_GATEUP, l, {**gin, 1: lp(l, "post_attention_layernorm.weight"), **gateup(l), 4: "layer_scratch.silu_up"}, [H, inter, s.act], [s.eps])
+            add(K_LIN, l, {0: "layer_scratch.silu_up", 1: lp(l, "mlp.down_proj"), 4: pb}, [inter, H])
+            add(K_ALLREDUCE, l, {0: pb}, [H, 0])
+            if not fused:
+                add(K_RESADD, l, {0: pb, 1: hb(l), 2: x(l + 1)}, [H])
+        else:
+            # Gemma-shaped: o_proj plain; post-attention norm + residual + pre-ffn norm in the gate/up prologue
+            add(K_LIN, l, {0: "layer_scratch.sdpa_buf", 1: lp(l, "self_attn.o_proj"), 3: "layer_scratch.o_buf"}, [ko, H])
+            add(K_GATEUP, l, {0: x(l), 1: lp(l, "pre_feedforward_layernorm.weight"), **gateup(l), 4: "layer_scratch.silu_up",
+                              9: "layer_scratch.o_buf", 10: lp(l, "post_attention_layernorm.weight"), 11: hb(l)}, [H, inter, s.act], [s.eps])
+            add(K_LIN, l, {0: "layer_scratch.silu_up", 1: lp(l, "mlp.down_proj"), 3: f"layer_scratch.{l}.out_buf"}, [inter, H])
+    L = s.n_layers
+    x_fin, pend = x(L), {}
+    if s.arch == "gemma3":
+        x_fin, pend = hb(L - 1), {9: f"layer_scratch.{L-1}.out_buf", 10: lp(L - 1, "post_feedforward_layernorm.weight"), 11: x(L)}
+    elif tp and fused:
+        x_fin, pend = hb(L - 1), {9: "global_scratch.tp_partial_b", 11: x(L)}
+    add(K_HEAD, -1, {0: x_fin, 1: "param.final_norm", 2: "param.lm_head", 3: "global_scratch.logits" if want_logits else None,
+                     4: "global_scratch.argmax_scratch", 5: "global_scratch.head_counter", **pend},
+        [H, vocab, tp_rank * vocab, 0 if tp else 1], [s.eps])
+    if tp:
+        add(K_ALLREDUCE, -1, {0: "global_scratch.argmax_scratch"}, [1, 1])
+        add(K_ARGMAX, -1, {4: "global_scratch.argmax_scratch"}, [1])
+
+    # ---- v2 envelope: tasks with bindings, a linear event chain, layer groups, the decode pipeline
+    out_slots = {K_EMBED: [1], K_QKV: [4, 5, 6, 7, 8, 11], K_QKNORM: [0, 5, 6], K_SDPA: [3, 4, 5], K_LIN: [3, 4], K_GATEUP: [4, 11],
+                 K_HEAD: [3, 4, 5, 11], K_ARGMAX: [], K_ALLREDUCE: [0], K_RESADD: [2]}
+    jtasks, groups = [], {}
+    for i, t in enumerate(tasks):
+        ins, outs, extra = [], [], []
+        for slot, role in sorted(t["bufs"].items()):
+            if role.startswith(("param.", "layer_param.")):
+                ins.append({"role": "external", "tensor_id": len(ins), "source_path": "model." + role.split(".", 1)[1], "role_name": role})
+            elif slot in out_slots[t["kind"]]:
+                outs.append({"role": "scratch", "scratch_id": slot, "role_name": role})
+            else:
+                ins.append({"role": "scratch", "scratch_id": slot, "role_name": role})
+            extra.append({"slot": slot, "role": role})
+        if t["kind"] not in (K_ALLREDUCE, K_RESADD):
+            extra += [{"slot": 100, "role": "token_id_in" if t["kind"] == K_EMBED else "layer_offset"}]
+        if t["kind"] in (K_HEAD, K_ARGMAX):
+            extra += [{"slot": 101, "role": "next_token_out"}]
+        jt = {"id": i, "fusion_id": i, "kernel": KERNEL[KINDS[t["kind"]]], "kind": t["kind"], "grid_threads": [0, 1, 1], "threadgroup": [0, 1, 1],
+              "inputs": ins, "outputs": outs, "extra_bindings": extra, "depends_on": [i - 1] if i else [], "trigger_event": i,
+              "iargs": t["iargs"], "fargs": t["fargs"]}
+        if t["layer"] >= 0:
+            jt["layer_idx"] = t["layer"]
+        jtasks.append(jt)
+        region = "embed" if t["kind"] == K_EMBED else (f"layer.{t['layer']}" if t["layer"] >= 0 else "post")
+        groups.setdefault(region, []).append(i)
+    return {
+        "version": VERSION, "active_m": 1, "tasks": jtasks,
+        "events": [{"id": i, "num_triggers": 1, "fires": [i + 1] if i + 1 < len(jtasks) else []} for i in range(len(jtasks))],
+        "scratch_buffers": [], "initial_tasks": [0], "model_params": [],
+        "layer_groups": [{"region": r, "task_ids": ids} for r, ids in groups.items()],
+        "decode_pipeline": list(range(len(jtasks))),
+        "decode_capabilities": {"dispatchable": True, "reasons": []},
+        "target": {"chip": "b200", "arch": "sm_100a", "tensor_parallel": tp_size, "rank": tp_rank, "bits": s.bits,
+                   "launch": "grid and block sizes are chosen by the runtime from the SM count (plan_shape)"},
+    }
+
+
+def task_slots(jtask: dict) -> dict:
+    """slot -> role of a serialised task (the explicit extra_bindings below slot 100)."""
+    return {b["slot"]: b["role"] for b in jtask["extra_bindings"] if b["slot"] < 100}
+
+
+def write(path, graph: dict):
+    """Serialise like the reference does (pretty-printed JSON, task_graph_json.rs:260-270)."""
+    import json
+    with open(path, "w") as f:
+        json.dump(graph, f, indent=2)
+
+
+def read(path) -> dict:
+    import json
+    with open(path) as f:
+        return json.load(f)

@@ -99,6 +99,93 @@ def check_stages_qwen(eng, m, tok, pos, what):
     return worst
 
 
+def check_stages_gemma(eng, m, tok, pos, what):
+    """Stage-wise bar for the Gemma-shaped layer (sandwich norms, per-head q/k norm, GeGLU, ring caches): each stage
+    is recomputed by the oracle from the GPU's own inputs to it.  Returns the worst relative RMS seen."""
+    import math
+    from fusekit_b200 import _native as N
+    sp, rt = eng.spec, eng.rt
+    H, hd, nq, nkv, I = sp.hidden, sp.head_dim, sp.n_q, sp.n_kv, sp.inter
+    tasks = eng.build_dispatches()
+    rt.state_set(tok, pos)
+    rt.launch_batch([t for t in tasks if t.kind == N.TASK_EMBED_LOOKUP_DECODE])
+    worst = 0.0
+
+    def cmp(name, got, want):
+        nonlocal worst
+        ma, rr = max_abs(got, want), rel_rms(got, want)
+        worst = max(worst, rr)
+        assert ma <= MAX_ABS_TOL * mag(want) and rr <= REL_RMS_TOL, f"{what} {name}: max-abs {ma:.4g}, rel-rms {rr:.4g}"
+
+    def head_norm(v, n, w):
+        return np.concatenate([O.f32_to_bf16(O.rmsnorm(v[h * hd:(h + 1) * hd], w, sp.eps)) for h in range(n)])
+
+    def sandwich(res, y, w):          # T(res + rmsnorm(y, w))
+        return O.f32_to_bf16(O.bf16_to_f32(res) + O.rmsnorm(y, w, sp.eps))
+
+    get = lambda p, n: rt.download(p, (n,), np.uint16)
+    for l in range(sp.n_layers):
+        ck_d, cv_d, cap = eng.cache[l]
+        shape, theta = (nkv, cap, hd), sp.layer_theta(l)
+        ck_before, cv_before = rt.download(ck_d, shape, np.uint16), rt.download(cv_d, shape, np.uint16)
+        mine = [t for t in tasks if t.layer == l]
+        rt.state_set(tok, pos)
+        rt.launch_batch(mine[:1])                           # RmsNormQkv (+ the previous layer's closing sandwich norm)
+        x_in = get(eng.x_ptr(l), H)
+        if l > 0:
+            cmp(f"L{l} x_in", x_in, sandwich(get(eng.hb_ptr(l - 1), H), get(eng.d_ptr(l - 1), H), m.vec(l - 1, 4, H)))
+        lq, lk, lv, lo, lg, lu, ld = [m.linear(l, i) for i in range(7)]
+        nf = O.rmsnorm(x_in, m.vec(l, 0, H), sp.eps)
+        q_raw, k_raw, v_raw = get(eng.q_buf, nq * hd), get(eng.k_buf, nkv * hd), get(eng.v_buf, nkv * hd)
+        cmp(f"L{l} q_raw", q_raw, O.f32_to_bf16(O.linear_acc(lq, nf)))
+        cmp(f"L{l} k_raw", k_raw, O.f32_to_bf16(O.linear_acc(lk, nf)))
+        cmp(f"L{l} v_raw", v_raw, O.f32_to_bf16(O.linear_acc(lv, nf)))
+        rt.launch_batch(mine[1:])
+        row, kv_len = pos % cap, min(pos + 1, cap)
+        gq = get(eng.q_buf, nq * hd)
+        gk, gv = rt.download(ck_d, shape, np.uint16), rt.download(cv_d, shape, np.uint16)
+        cmp(f"L{l} q", gq, O.rope(head_norm(q_raw, nq, m.vec(l, 5, hd)), nq, hd, pos, theta))
+        cmp(f"L{l} k", gk[:, row].reshape(-1), O.rope(head_norm(k_raw, nkv, m.vec(l, 6, hd)), nkv, hd, pos, theta))
+        assert np.array_equal(gv[:, row].reshape(-1), v_raw), f"{what} L{l} v row"
+        keep = np.ones(cap, bool); keep[row] = False
+        assert np.array_equal(gk[:, keep], ck_before[:, keep]) and np.array_equal(gv[:, keep], cv_before[:, keep])
+        ga = get(eng.sdpa_buf, nq * hd)
+        cmp(f"L{l} attn", ga, O.sdpa_decode(gq, gk, gv, nq, nkv, hd, cap, kv_len, 1.0 / math.sqrt(hd)))
+        go = get(eng.o_buf, H)
+        cmp(f"L{l} o", go, O.qmatvec(lo, ga))
+        gh = get(eng.hb_ptr(l), H)
+        cmp(f"L{l} h", gh, sandwich(x_in, go, m.vec(l, 2, H)))
+        nf2 = O.rmsnorm(gh, m.vec(l, 3, H), sp.eps)
+        gs = get(eng.act_buf, I)
+        cmp(f"L{l} act", gs, O.act(O.linear_acc(lg, nf2), O.linear_acc(lu, nf2), 1))
+        cmp(f"L{l} down", get(eng.d_ptr(l), H), O.qmatvec(ld, gs))
+    return worst
+
+
+def test_gemma_4b_shaped_layers_stage_by_stage():
+    """Gemma-3-4B-shaped layers at full width (hidden 2560, head_dim 256, GeGLU 10240, 5 sliding layers with a wrapped
+    1024-row ring cache, then a global layer), cut to 7 layers and a 16k vocabulary so the oracle finishes in seconds."""
+    import dataclasses
+    spec = dataclasses.replace(CONFIGS["gemma3-4b"], name="gemma3-4b-7layers", n_layers=7, vocab=16384)
+    ctx, cap = 1100, 1200
+    assert ctx > spec.window and any(not spec.is_sliding(l) for l in range(spec.n_layers))
+    m = O.Model(oracle_config(spec, cap)); m.prefill_kv(ctx)
+    eng = DecodeEngine(spec, cap)
+    try:
+        eng.load_synthetic(); eng.prefill_kv_synthetic(ctx)
+        for l, (ck, cv, c) in enumerate(eng.cache):
+            n = spec.n_kv * c * spec.head_dim
+            assert np.array_equal(eng.rt.download(ck, (n,), np.uint16), m.vec(l, 7, n)), f"cache_k layer {l}"
+            assert np.array_equal(eng.rt.download(cv, (n,), np.uint16), m.vec(l, 8, n)), f"cache_v layer {l}"
+        print("gemma-4b-shaped stage-wise worst rel-rms:", check_stages_gemma(eng, m, 11, ctx, "gemma-4b-shaped"))
+        eng.prefill_kv_synthetic(ctx)
+        got, _ = eng.decode_chunk(ctx, 11, 16)
+        mism, ties = compare_greedy(got, m, 11, ctx)
+        assert not mism and len(ties) <= 2, f"mismatches {mism}, near-ties {ties}"
+    finally:
+        eng.close()
+
+
 @pytest.mark.parametrize("name", ["tiny-qwen", "tiny-gemma"])
 @pytest.mark.parametrize("bits", [4, 8, 16])
 def test_tiny_models_match_oracle(name, bits):
@@ -226,3 +313,15 @@ def test_full_size_projections_on_sampled_rows(runtime, name, bits):
             want = O.qmatvec(ref, x)
             ma, rr = max_abs(got[r0:r0 + 16], want), rel_rms(got[r0:r0 + 16], want)
             assert ma <= MAX_ABS_TOL * max(1.0, float(np.abs(O.bf16_to_f32(want)).max())) and rr <= 4 * REL_RMS_TOL, (leaf, r0, ma, rr)
+
+
+@pytest.mark.gpu
+def test_task_graph_file_drives_the_same_dispatch_list(runtime, tmp_path):
+    """A task_graph.json written to disk and read back resolves to byte-identical fk_task records."""
+    from fusekit_b200 import task_graph
+    eng = DecodeEngine(CONFIGS["tiny-gemma"], 256, runtime=runtime)
+    eng.load_synthetic()
+    task_graph.write(tmp_path / "task_graph.json", eng.task_graph())
+    a = eng.build_dispatches()
+    b = eng.dispatches_from(task_graph.read(tmp_path / "task_graph.json"))
+    assert len(a) == len(b) and all(bytes(x) == bytes(y) for x, y in zip(a, b))

@@ -1,0 +1,112 @@
+"""Host-side checks of the task_graph.json document (reference schema: src/codegen/task_graph_json.rs:33-226) and
+of its resolution to the fk_task list, without a GPU: a stand-in engine hands out fake addresses."""
+import json
+
+import pytest
+
+from fusekit_b200 import task_graph as TG
+from fusekit_b200.model_spec import CONFIGS
+from fusekit_b200.runtime import DecodeEngine, linear_plan, vector_plan
+
+V2_KEYS = {"version", "active_m", "tasks", "events", "scratch_buffers", "initial_tasks", "model_params", "layer_groups",
+           "decode_pipeline", "decode_capabilities"}
+TASK_KEYS = {"id", "fusion_id", "kernel", "grid_threads", "threadgroup", "inputs", "outputs", "extra_bindings", "depends_on", "trigger_event"}
+
+
+class _Names(dict):
+    """name -> fake address, remembering what was asked for."""
+    def __init__(self, known):
+        super().__init__()
+        self.known, self.asked = set(known), []
+
+    def __missing__(self, k):
+        if k not in self.known:
+            raise KeyError(k)
+        self.asked.append(k)
+        self[k] = 0x1000 + 16 * len(self.asked)
+        return self[k]
+
+
+def _fake_engine(spec, world=1, rank=0, fused=True):
+    e = DecodeEngine.__new__(DecodeEngine)
+    e.spec, e.capacity, e.rank, e.world, e.want_logits = spec, 1024, rank, world, False
+    wn = {p[0] for p in linear_plan(spec, rank, world)}
+    if fused and spec.bits != 16:
+        wn = {n for n in wn if not n.endswith((".gate", ".up"))} | {f"layers.{l}.gateup" for l in range(spec.n_layers)}
+    vn = {p[0] for p in vector_plan(spec, rank, world) if not p[0].endswith(("q_bias", "k_bias", "v_bias"))}
+    if spec.arch == "qwen2":
+        vn |= {f"layers.{l}.qkv_bias" for l in range(spec.n_layers)}
+    e.W, e.V = _Names(wn), _Names(vn)
+    e.cache = [(0x100000 + 2 * l, 0x100001 + 2 * l, spec.layer_capacity(l, 1024)) for l in range(spec.n_layers)]
+    e.X, e.HB, e.d_buf = 0x200000, 0x300000, 0x400000
+    for i, n in enumerate(["q_buf", "k_buf", "v_buf", "sdpa_buf", "act_buf", "o_buf", "part_f32", "part_f32_b", "sdpa_part",
+                           "sdpa_counter", "argmax_scratch", "head_counter"]):
+        setattr(e, n, 0x500000 + 256 * i)
+    e.logits = 0
+
+    class _Rt:
+        tiled = fused
+    e.rt = _Rt()
+    return e
+
+
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_schema_and_json_round_trip(name):
+    spec = CONFIGS[name]
+    g = TG.emit(spec, 1024)
+    assert V2_KEYS <= set(g) and g["version"] == 2 and g["active_m"] == 1
+    assert g["initial_tasks"] == [0] and g["decode_capabilities"] == {"dispatchable": True, "reasons": []}
+    per_layer = 5 if spec.arch == "qwen2" else 6
+    assert len(g["tasks"]) == 2 + per_layer * spec.n_layers == len(g["decode_pipeline"]) == len(g["events"])
+    for i, t in enumerate(g["tasks"]):
+        assert TASK_KEYS <= set(t) and t["id"] == i and t["kernel"].startswith("fusekit_")
+        assert t["depends_on"] == ([i - 1] if i else [])
+        assert ("layer_idx" in t) == (0 < i < len(g["tasks"]) - 1)
+        for b in t["inputs"] + t["outputs"]:
+            assert b["role"] in ("external", "scratch") and b["role_name"]
+    assert [r["region"] for r in g["layer_groups"]] == ["embed"] + [f"layer.{l}" for l in range(spec.n_layers)] + ["post"]
+    assert sorted(i for r in g["layer_groups"] for i in r["task_ids"]) == g["decode_pipeline"]
+    assert json.loads(json.dumps(g)) == g
+    # the reference's replay order inside a layer (task_graph_json.rs:1619-1664)
+    kinds = [t["kernel"][8:] for t in g["tasks"] if t.get("layer_idx") == 0]
+    want = ["rmsnorm_qkv", "sdpa_decode", "linear_residual", "rmsnorm_gateup_act", "linear_residual"]
+    if spec.arch != "qwen2":
+        want.insert(1, "qk_norm_rope_store")
+    assert kinds == want
+
+
+@pytest.mark.parametrize("name,world,fused", [("qwen2.5-7b", 1, True), ("qwen2.5-7b", 2, True), ("qwen2.5-7b", 2, False),
+                                               ("gemma3-4b", 1, True), ("tiny-qwen", 1, False), ("tiny-gemma", 1, True)])
+def test_every_role_resolves_and_every_tensor_is_used(name, world, fused):
+    spec = CONFIGS[name]
+    e = _fake_engine(spec, world, world - 1, fused)
+    g = json.loads(json.dumps(e.task_graph()))
+    tasks = e.dispatches_from(g)
+    assert len(tasks) == len(g["tasks"])
+    assert set(e.W.asked) == e.W.known and set(e.V.asked) == e.V.known
+    # data flow: every buffer a task reads from the residual stream was written by an earlier task
+    written = set()
+    for t in g["tasks"]:
+        outs = {b["role_name"] for b in t["outputs"]}
+        for b in t["inputs"]:
+            if b["role"] == "scratch" and b["role_name"].startswith(("global_scratch.x_in", "layer_scratch")) and b["role_name"] not in outs:
+                assert b["role_name"] in written, (t["id"], t["kernel"], b["role_name"])
+        written |= outs
+    # iargs carry this rank's slice of the shape
+    head = tasks[-1] if world == 1 else tasks[-3]
+    assert head.iarg[1] == spec.vocab // world and head.iarg[2] == (world - 1) * (spec.vocab // world)
+
+
+def test_reader_refuses_what_it_cannot_dispatch():
+    e = _fake_engine(CONFIGS["tiny-qwen"])
+    g = e.task_graph()
+    with pytest.raises(ValueError):
+        e.dispatches_from({**g, "version": 1})
+    with pytest.raises(ValueError):
+        e.dispatches_from({**g, "active_m": 16})
+    with pytest.raises(ValueError):
+        e.dispatches_from({**g, "decode_capabilities": {"dispatchable": False, "reasons": ["unsupported kernel"]}})
+    bad = json.loads(json.dumps(g))
+    bad["tasks"][1]["extra_bindings"][0]["role"] = "layer_scratch.nonesuch"
+    with pytest.raises(KeyError):
+        e.dispatches_from(bad)
