@@ -157,6 +157,7 @@ def main():
     ap.add_argument("--workload", default="qwen7b-q4-ctx512", choices=sorted(WORKLOADS))
     ap.add_argument("--chunk", type=int, default=CHUNK, help="tokens per step (64 = the reference's FK_CHUNK); smaller for profiler captures")
     ap.add_argument("--tp", action="store_true", help="N ranks form one tensor-parallel group (one stream) instead of N replicas")
+    ap.add_argument("--persistent", default="auto", choices=["auto", "on", "off"], help="run a token as one persistent kernel (auto: when the task list allows)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--profile-nodes", type=int, default=5, help="repeats of the per-kernel timing pass (0 = skip)")
@@ -191,8 +192,8 @@ def main():
         eng = DecodeEngine(spec, cap, device=local)      # N > 1: N independent replicas, one per GPU
     eng.load_synthetic()
     eng.prefill_kv_synthetic(ctx)
-    eng.capture()
-    nodes = len(eng.tasks)
+    eng.capture({"auto": None, "on": True, "off": False}[args.persistent])
+    nodes = len(eng.replay)
 
     def barrier():
         if dist is not None:
@@ -258,6 +259,14 @@ def main():
         roofline = {"bound": "hbm", "kernel": name, "achieved": ach, "peak": peak, "peak_kind": peak_kind,
                     "unit": "GB/s", "frac": ach / peak, "bytes_per_launch": algo, "avg_launch_us": avg * 1e6,
                     "traffic": NCU_TRAFFIC.get(name)}
+        if eng.persistent:
+            # the timed region is launches of one kernel, the persistent token kernel: its roofline is the token's.  The
+            # per-task figures above (same tasks, one kernel each) stay in kernel_shares as the breakdown.
+            bpl = spec.bytes_per_token(ctx + CHUNK * args.steps // 2)
+            avg = dev_s / (args.steps * CHUNK)
+            roofline = {"bound": "hbm", "kernel": "fusekit_decode_token", "achieved": bpl / avg / 1e9, "peak": peak, "peak_kind": peak_kind,
+                        "unit": "GB/s", "frac": bpl / avg / 1e9 / peak, "bytes_per_launch": bpl, "avg_launch_us": avg * 1e6,
+                        "traffic": NCU_TRAFFIC.get("fusekit_decode_token"), "per_task_dominant": roofline}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -273,7 +282,7 @@ def main():
             "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "strong" if args.tp else "weak", "vs_baseline": None,
             "dtype": f"int{bits}" if bits != 16 else "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "tokens_per_step": CHUNK, "batch": 1, "ctx_start": ctx, "graph_nodes_per_token": nodes,
-                       "l2": "inputs (weights) larger than L2", "replicas": streams, "tensor_parallel": world if args.tp else 1, "pdl": eng.rt.info().get("pdl")},
+                       "l2": "inputs (weights) larger than L2", "persistent_kernel": eng.persistent, "replicas": streams, "tensor_parallel": world if args.tp else 1, "pdl": eng.rt.info().get("pdl")},
             "e2e": {"value": tokens / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 80, "d2h_bytes_per_step": CHUNK * 4 + 80},
             "gpu_launches": nodes * CHUNK * args.steps,
             "clocks": clocks,

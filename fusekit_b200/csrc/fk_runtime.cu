@@ -6,6 +6,7 @@
 #include "fk_kernels.cuh"
 #include "fk_synth.cuh"
 #include "fk_stream.cuh"
+#include "fk_mega.cuh"
 
 #include <dlfcn.h>
 #include <math.h>
@@ -66,6 +67,17 @@ struct Weight {
     TiledW tview() const { TiledW t; t.units = units; t.ntiles = ntiles; t.nsb = nsb; t.n = (int)n; t.k = (int)k; t.bits = bits;
                            t.rows_kind = rows_kind; t.hd = hd; t.n_rot = n_rot; return t; }
 };
+// a task list compiled for the persistent kernel (fk_mega.cuh)
+struct Program {
+    MegaSlot *ops = nullptr; MegaWeight *wtab = nullptr; MegaSync *sync = nullptr; float *part = nullptr;
+    int nops = 0, nweights = 0, max_nsb = 0, bits = 0, attn_bytes = 0, barriers = 0; size_t smem = 0;
+};
+struct Recorder {               // filled by run_task instead of launching while a program is being built
+    std::vector<MegaSlot> ops; std::vector<MegaWeight> wtab;
+    int bits = 0, max_nsb = 0, attn_bytes = 0, barriers = 0, min_grid = 1;
+    float *part = nullptr; size_t part_floats = 0;
+    bool have_attn = false; MegaAttn attn;
+};
 struct Graph {
     std::vector<fk_task> tasks;
     cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
@@ -81,6 +93,7 @@ struct Ctx {
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
+    std::vector<Program> programs; Recorder *rec = nullptr;
 };
 static std::mutex g_mu;
 static std::vector<Ctx *> g_ctx;
@@ -128,6 +141,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     e = getenv("FK_PREFETCH"); if (e && atoi(e) >= 0 && atoi(e) <= 64) c->prefetch = atoi(e);
 #define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>))
     BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head);
+    CU(big_smem(k_decode_token<4>)); CU(big_smem(k_decode_token<8>));
     CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
     CU(big_smem(k_linear_residual<4>)); CU(big_smem(k_linear_residual<8>)); CU(big_smem(k_linear_residual<16>));
@@ -166,7 +180,7 @@ extern "C" fk_status fk_info(fk_handle h, char *buf, size_t cap) {
 static const char *kKernelNames[FK_TASK_KIND_COUNT] = {
     "fusekit_step_init", "fusekit_embed_lookup_decode", "fusekit_rmsnorm_qkv", "fusekit_qk_norm_rope_store",
     "fusekit_sdpa_decode", "fusekit_linear_residual", "fusekit_rmsnorm_gateup_act", "fusekit_final_rmsnorm_lm_head",
-    "fusekit_argmax_finalize", "fusekit_allreduce", "fusekit_residual_add"};
+    "fusekit_argmax_finalize", "fusekit_allreduce", "fusekit_residual_add", "fusekit_decode_token"};
 extern "C" fk_status fk_kernel_names(char *buf, size_t cap) {
     if (!buf || cap == 0) return fail(FK_ERR_VALUE, "buf is null");
     std::string s;
@@ -434,6 +448,25 @@ static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *nex
     } while (0)
 #define BITS48(bits, CALL) do { if ((bits) == 4) { constexpr int B = 4; CALL; } else { constexpr int B = 8; CALL; } } while (0)
 
+
+// ---- recording a task for the persistent kernel instead of launching it
+static fk_status rec_stream(Ctx *c, MegaOp &op, StreamPlan &P, const Weight *w) {
+    Recorder *r = c->rec;
+    if (r->bits && r->bits != w->bits) return fail(FK_ERR_VALUE, "persistent program: all streamed weights must share one bit width");
+    r->bits = w->bits;
+    P.W = w->tview(); P.stages = FK_STAGES; P.dbg_mode = 0; P.timeline = nullptr; P.next_units = nullptr;
+    P.next_ntiles = P.next_nsb = P.next_grid = P.next_warps = P.next_prefetch = 0;
+    op.widx = (int)r->wtab.size();
+    MegaWeight mw; mw.units = w->units; mw.ntiles = w->ntiles; mw.nsb = w->nsb;
+    r->wtab.push_back(mw);
+    if (w->nsb > r->max_nsb) r->max_nsb = w->nsb;
+    r->barriers++;
+    return FK_OK;
+}
+static void rec_push(Ctx *c, const MegaOp &op) { MegaSlot sl; memset(&sl, 0, sizeof sl); sl.op = op; c->rec->ops.push_back(sl); }
+static MegaOp rec_op(int kind) { MegaOp op; memset(&op, 0, sizeof op); op.kind = kind; op.widx = -1; return op; }
+
+static fk_status launch_program(Ctx *c, uint64_t id);
 static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullptr) {
     const uint64_t *b = t.buf; const int32_t *i = t.iarg; const float *f = t.farg;
     cudaError_t e = cudaSuccess;
@@ -442,6 +475,10 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
     case FK_TASK_EMBED_LOOKUP_DECODE: {
         if (!b[0] || !b[1] || i[0] <= 0 || i[1] <= 0 || i[1] > FK_MAX_ROWS) return fail(FK_ERR_VALUE, "embed: bad arguments");
         EmbedArgs a{(const uint16_t *)b[0], (uint16_t *)b[1], i[0], i[1], f[0]};
+        if (c->rec) {
+            if (i[1] != 1) return fail(FK_ERR_VALUE, "persistent program: one row per step");
+            MegaOp op = rec_op(t.kind); op.u.emb = a; rec_push(c, op); return FK_OK;
+        }
         e = launch(c, k_embed_lookup, dim3((i[0] * i[1] + 255) / 256), dim3(256), 0, (const FkState *)c->state, a);
         break;
     }
@@ -461,10 +498,16 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                         H, nq, nkv, hd, cap, sinks, a.eps, a.log2theta, nullptr};
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }      // fp32 all-reduced projection + residual
             if (H > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "rmsnorm_qkv: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
+            if (c->rec) {
+                if (!sinks || sa.pend_sum) return fail(FK_ERR_VALUE, "persistent program: rmsnorm_qkv needs the fused RoPE + cache store and no all-reduce input");
+                MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, w); if (rs) return rs;
+                op.u.qkv = sa; rec_push(c, op); return FK_OK;
+            }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
             STREAM_LAUNCH(k_s_rmsnorm_qkv, w, sh, c->state, sa);
             break;
         }
+        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs 4/8-bit streamed weights");
         if (b[9] && !b[10]) return fail(FK_ERR_VALUE, "rmsnorm_qkv: the fused all-reduce residual needs 4/8-bit streamed weights");
         const int grid = grid_for(c, w->n / 2, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_rmsnorm_qkv<B>, dim3(grid), dim3(256), smem_bytes_for(H), (const FkState *)c->state, a));
@@ -472,6 +515,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
     }
     case FK_TASK_QK_NORM_ROPE_STORE: {
         const int nq = i[0], nkv = i[1], hd = i[2], cap = i[3];
+        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: qk_norm_rope_store is not expressible yet");
         if (hd > 512 || (hd & 1) || !b[0] || !b[1] || !b[2] || !b[5] || !b[6]) return fail(FK_ERR_VALUE, "qk_norm_rope_store: bad arguments");
         QkNormArgs a{(uint16_t *)b[0], (const uint16_t *)b[1], (const uint16_t *)b[2], (const uint16_t *)b[3], (const uint16_t *)b[4],
                      (uint16_t *)b[5], (uint16_t *)b[6], nq, nkv, hd, cap, f[0], (float)log2((double)f[1])};
@@ -484,6 +528,19 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         const int chunks = (cap + FK_SDPA_KEYS - 1) / FK_SDPA_KEYS, G = nq / nkv;
         SdpaArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], (uint32_t *)b[5],
                    nq, nkv, hd, cap, chunks, f[0], c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr, -1};
+        if (c->rec) {
+            Recorder *r = c->rec;
+            if (hd != 64 && hd != 128) return fail(FK_ERR_VALUE, "persistent program: head_dim must be 64 or 128");
+            if ((size_t)nq * FK_MEGA_PARTS * (hd + 2) > r->part_floats) return fail(FK_ERR_VALUE, "persistent program: attention partial buffer too small");
+            a.part = r->part; a.tl = nullptr;
+            const int ab = (int)mega_attn_scratch_bytes(G, hd);
+            if (ab > r->attn_bytes) r->attn_bytes = ab;
+            if (nkv * FK_MEGA_PARTS > r->min_grid) r->min_grid = nkv * FK_MEGA_PARTS;
+            MegaOp op = rec_op(t.kind); op.u.sdpa = a; rec_push(c, op);
+            r->barriers++;
+            r->have_attn = true; r->attn.part = r->part; r->attn.out = a.out; r->attn.n_q = nq; r->attn.n_kv = nkv; r->attn.hd = hd; r->attn.capacity = cap;
+            return FK_OK;
+        }
         if (c->sdpa_cluster && (hd != 256 || G <= 2)) {
             const size_t smem = sdpa_cl_smem_bytes(G, hd);
             const dim3 cgrid(FK_SDPA_CL, nkv), cblock(FK_SDPA_CW * 32);
@@ -505,10 +562,22 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (w->tiled) {
             if (w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "linear_residual takes plain row order");
             SLinArgs sa{a.x, StreamPlan(), a.residual, a.y, a.y_f32, i[0], i[1]};
+            if (c->rec) {
+                Recorder *r = c->rec;
+                if (sa.y_f32 || !sa.y) return fail(FK_ERR_VALUE, "persistent program: linear_residual writes T outputs only");
+                MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, w); if (rs) return rs;
+                if (r->have_attn && sa.x == r->attn.out) {      // reads the attention output: fold the partials while staging
+                    if (r->attn.n_q * r->attn.hd != i[0]) return fail(FK_ERR_VALUE, "persistent program: o_proj width does not match the attention output");
+                    op.attn_fold = 1; op.attn = r->attn;
+                }
+                r->have_attn = false;
+                op.u.lin = sa; rec_push(c, op); return FK_OK;
+            }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
             STREAM_LAUNCH(k_s_linear, w, sh, c->state, sa);
             break;
         }
+        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs 4/8-bit streamed weights");
         const int grid = grid_for(c, w->n, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_linear_residual<B>, dim3(grid), dim3(256), smem_bytes_for(i[0]), (const FkState *)c->state, a));
         break;
@@ -521,10 +590,16 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                            (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0], nullptr};
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "gateup: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
+            if (c->rec) {
+                if (sa.pend_sum) return fail(FK_ERR_VALUE, "persistent program: no all-reduce inputs");
+                MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, wg); if (rs) return rs;
+                op.u.gu = sa; rec_push(c, op); return FK_OK;
+            }
             const Shape sh = make_plan(c, wg, &sa.P, nextw);
             STREAM_LAUNCH(k_s_gateup, wg, sh, c->state, sa);
             break;
         }
+        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs a paired 4/8-bit gate/up weight");
         if (!wg || !wu || !wg->finalized || !wu->finalized) return fail(FK_ERR_VALUE, "gateup: weights missing or not finalized");
         if (wg->tiled || wu->tiled) return fail(FK_ERR_VALUE, "gateup: pair the gate and up weights with fk_weight_pair");
         if (wg->k != i[0] || wu->k != i[0] || wg->n != i[1] || wu->n != i[1] || wg->bits != wu->bits) return fail(FK_ERR_VALUE, "gateup: shape mismatch");
@@ -546,20 +621,29 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                          a.h, a.v, a.vocab_offset, a.finalize, a.eps, nullptr};
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "lm_head: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
+            if (c->rec) {
+                if (sa.pend_sum || !sa.finalize) return fail(FK_ERR_VALUE, "persistent program: the head must finalise the token itself");
+                MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, w); if (rs) return rs;
+                op.u.head = sa; rec_push(c, op); return FK_OK;
+            }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
             STREAM_LAUNCH(k_s_head, w, sh, c->state, sa);
             break;
         }
+        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs 4/8-bit streamed weights");
         const int grid = grid_for(c, w->n, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_final_head<B>, dim3(grid), dim3(256), smem_bytes_for(i[0]), c->state, a));
         break;
     }
+    case FK_TASK_DECODE_TOKEN: return c->rec ? fail(FK_ERR_VALUE, "persistent program: programs do not nest") : launch_program(c, b[0]);
     case FK_TASK_ARGMAX_FINALIZE: {
+        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: argmax_finalize is not expressible");
         if (!b[4] || i[0] <= 0) return fail(FK_ERR_VALUE, "argmax_finalize: bad arguments");
         e = launch(c, k_argmax_finalize, dim3(1), dim3(32), 0, c->state, (const unsigned long long *)b[4], i[0], c->history);
         break;
     }
     case FK_TASK_ALLREDUCE: {
+        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: collectives are not expressible");
         if (!c->comm) return fail(FK_ERR_STATE, "allreduce task without fk_comm_init");
         const int dtype = i[1] == 1 ? 5 /* ncclUint64 */ : 7 /* ncclFloat32 */, op = i[1] == 1 ? 2 /* ncclMax */ : 0 /* ncclSum */;
         int r = g_nccl.AllReduce((const void *)b[0], (void *)b[0], (size_t)i[0], dtype, op, c->comm, c->stream);
@@ -567,6 +651,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         break;
     }
     case FK_TASK_RESIDUAL_ADD: {
+        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: residual_add is not expressible");
         if (!b[0] || !b[2] || i[0] <= 0) return fail(FK_ERR_VALUE, "residual_add: bad arguments");
         e = launch(c, k_residual_add, dim3((i[0] + 255) / 256), dim3(256), 0, (const float *)b[0], (const uint16_t *)b[1], (uint16_t *)b[2], i[0]);
         break;
@@ -574,6 +659,65 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
     default: return fail(FK_ERR_VALUE, "unknown task kind %d", t.kind);
     }
     if (e != cudaSuccess) return fail(FK_ERR_CUDA, "launch of %s failed: %s", kKernelNames[t.kind], cudaGetErrorString(e));
+    return FK_OK;
+}
+
+
+// ------------------------------------------------------------------ persistent programs
+extern "C" fk_status fk_program_build(fk_handle h, const fk_task *tasks, int n, uint64_t *out) {
+    CTX(h);
+    if (!tasks || n <= 0 || !out) return fail(FK_ERR_VALUE, "empty task list");
+    if (!c->use_tiled) return fail(FK_ERR_VALUE, "persistent program: needs the streamed weight layout");
+    Recorder r;
+    for (int j = 0; j < n; ++j) if (tasks[j].kind == FK_TASK_SDPA_DECODE) {
+        const size_t need = (size_t)tasks[j].iarg[0] * FK_MEGA_PARTS * (tasks[j].iarg[2] + 2);
+        if (need > r.part_floats) r.part_floats = need;
+    }
+    if (r.part_floats) CU(cudaMalloc(&r.part, r.part_floats * sizeof(float)));
+    c->rec = &r;
+    fk_status s = FK_OK;
+    for (int j = 0; j < n && s == FK_OK; ++j) s = run_task(c, tasks[j]);
+    c->rec = nullptr;
+    if (s == FK_OK && (r.ops.empty() || r.wtab.empty() || r.ops.back().op.kind != FK_TASK_FINAL_RMSNORM_LM_HEAD))
+        s = fail(FK_ERR_VALUE, "persistent program: the list must end with the lm_head task");
+    if (s == FK_OK && r.min_grid > c->sm_count) s = fail(FK_ERR_VALUE, "persistent program: %d kv heads x %d key blocks exceed the %d resident blocks", r.min_grid / FK_MEGA_PARTS, FK_MEGA_PARTS, c->sm_count);
+    Program p;
+    if (s == FK_OK) {
+        p.nops = (int)r.ops.size(); p.nweights = (int)r.wtab.size(); p.max_nsb = r.max_nsb; p.bits = r.bits; p.attn_bytes = r.attn_bytes; p.barriers = r.barriers;
+        p.smem = mega_layout(p.nweights, p.max_nsb, p.bits, (size_t)p.attn_bytes).total;
+        if (p.smem > 227 * 1024) s = fail(FK_ERR_VALUE, "persistent program: %zu bytes of shared memory needed, 232448 available", p.smem);
+    }
+    if (s != FK_OK) { cudaFree(r.part); return s; }
+    p.part = r.part;
+    CU(cudaMalloc(&p.ops, r.ops.size() * sizeof(MegaSlot)));
+    CU(cudaMalloc(&p.wtab, r.wtab.size() * sizeof(MegaWeight)));
+    CU(cudaMalloc(&p.sync, sizeof(MegaSync)));
+    CU(cudaMemcpyAsync(p.ops, r.ops.data(), r.ops.size() * sizeof(MegaSlot), cudaMemcpyHostToDevice, c->stream));
+    CU(cudaMemcpyAsync(p.wtab, r.wtab.data(), r.wtab.size() * sizeof(MegaWeight), cudaMemcpyHostToDevice, c->stream));
+    CU(cudaMemsetAsync(p.sync, 0, sizeof(MegaSync), c->stream));
+    CU(cudaStreamSynchronize(c->stream));
+    // the whole grid must be resident at once
+    int per_sm = 0;
+    if (p.bits == 4) CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_token<4>, FK_MEGA_WARPS * 32, p.smem));
+    else CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_token<8>, FK_MEGA_WARPS * 32, p.smem));
+    if (per_sm < 1) { cudaFree(p.ops); cudaFree(p.wtab); cudaFree(p.sync); cudaFree(p.part); return fail(FK_ERR_VALUE, "persistent program: a block does not fit on an SM"); }
+    c->programs.push_back(p); *out = c->programs.size();
+    return FK_OK;
+}
+static fk_status launch_program(Ctx *c, uint64_t id) {
+    if (id == 0 || id > c->programs.size()) return fail(FK_ERR_VALUE, "bad program id");
+    const Program &p = c->programs[id - 1];
+    cudaLaunchConfig_t cfg; memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(c->sm_count); cfg.blockDim = dim3(FK_MEGA_WARPS * 32); cfg.dynamicSmemBytes = p.smem; cfg.stream = c->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeCooperative; at[0].val.cooperative = 1;        // all blocks resident, or the launch fails
+    cfg.attrs = at; cfg.numAttrs = 1;
+    c->launches++;
+    unsigned long long *tl = c->timeline;
+    cudaError_t e;
+    if (p.bits == 4) e = cudaLaunchKernelEx(&cfg, k_decode_token<4>, c->state, (const MegaSlot *)p.ops, p.nops, (const MegaWeight *)p.wtab, p.nweights, p.sync, p.max_nsb, p.attn_bytes, p.barriers, tl, c->dbg_mode);
+    else e = cudaLaunchKernelEx(&cfg, k_decode_token<8>, c->state, (const MegaSlot *)p.ops, p.nops, (const MegaWeight *)p.wtab, p.nweights, p.sync, p.max_nsb, p.attn_bytes, p.barriers, tl, c->dbg_mode);
+    if (e != cudaSuccess) return fail(FK_ERR_CUDA, "launch of fusekit_decode_token failed: %s", cudaGetErrorString(e));
     return FK_OK;
 }
 
@@ -622,6 +766,7 @@ static fk_status set_state(Ctx *c, uint32_t token, uint32_t offset) {
     FkState *s = (FkState *)c->pinned; memset(s, 0, sizeof(FkState));
     s->token[0] = token; s->offset = offset; s->hist_counter = 0; s->error = 0; s->hist_cap = c->hist_cap;
     CU(cudaMemcpyAsync(c->state, s, sizeof(FkState), cudaMemcpyHostToDevice, c->stream));
+    for (Program &p : c->programs) CU(cudaMemsetAsync(p.sync, 0, sizeof(MegaSync), c->stream));     // barrier counters restart with the state
     return FK_OK;
 }
 extern "C" fk_status fk_state_set(fk_handle h, uint32_t token, uint32_t offset) {

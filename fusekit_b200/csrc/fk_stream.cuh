@@ -33,6 +33,11 @@
 #define FK_STREAM_MAXWARPS 16         // blocks run 8 warps (two blocks per SM) or 16 (one per SM, large activations)
 #define FK_STAGES 2                     // ring depth per warp
 #define FK_WAIT_LIMIT (1u << 24)        // bounded mbarrier wait; on expiry the kernel flags an error and leaves
+#ifndef FK_J_UNROLL
+#define FK_J_UNROLL 8                   // unroll factor of the group loop inside a unit (code size against scheduling freedom)
+#endif
+#define FK_STR(x) #x
+#define FK_UNROLL(n) _Pragma(FK_STR(unroll n))
 
 enum { FK_ROWS_PLAIN = 0, FK_ROWS_ROPE_PAIRS = 1, FK_ROWS_GATE_UP = 2 };
 
@@ -203,7 +208,7 @@ __device__ __forceinline__ void stage_plain(const StreamSmem &sm, const uint16_t
 #pragma unroll
         for (int i = 0; i < FK_PLAIN_MAXB; ++i) {          // all loads in flight before the first use
             const int blk = b0 + i * blockDim.x + threadIdx.x;
-            v[i] = blk < nblk ? *reinterpret_cast<const uint4 *>(x + (size_t)blk * 8) : make_uint4(0, 0, 0, 0);
+            v[i] = blk < nblk ? __ldcg(reinterpret_cast<const uint4 *>(x + (size_t)blk * 8)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int i = 0; i < FK_PLAIN_MAXB; ++i) {
@@ -229,14 +234,14 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
     for (int i = 0; i < FK_STAGE_MAXB; ++i) {
         const int blk = i * blockDim.x + threadIdx.x;
         xv[i] = wv[i] = make_uint4(0, 0, 0, 0);
-        if (blk < nblk) { xv[i] = *reinterpret_cast<const uint4 *>(x + (size_t)blk * 8); wv[i] = *reinterpret_cast<const uint4 *>(w + (size_t)blk * 8); }
+        if (blk < nblk) { xv[i] = __ldcg(reinterpret_cast<const uint4 *>(x + (size_t)blk * 8)); wv[i] = *reinterpret_cast<const uint4 *>(w + (size_t)blk * 8); }
     }
     if (pend_sum) {     // tensor parallel: x' = T(all-reduced projection + residual x); block 0 publishes it
 #pragma unroll
         for (int i = 0; i < FK_STAGE_MAXB; ++i) {
             const int blk = i * blockDim.x + threadIdx.x;
             if (blk < nblk) {
-                const float4 s0 = *reinterpret_cast<const float4 *>(pend_sum + (size_t)blk * 8), s1 = *reinterpret_cast<const float4 *>(pend_sum + (size_t)blk * 8 + 4);
+                const float4 s0 = __ldcg(reinterpret_cast<const float4 *>(pend_sum + (size_t)blk * 8)), s1 = __ldcg(reinterpret_cast<const float4 *>(pend_sum + (size_t)blk * 8 + 4));
                 float f[8]; unpack8(xv[i], f);
                 const uint16_t o0 = f2bf(s0.x + f[0]), o1 = f2bf(s0.y + f[1]), o2 = f2bf(s0.z + f[2]), o3 = f2bf(s0.w + f[3]);
                 const uint16_t o4 = f2bf(s1.x + f[4]), o5 = f2bf(s1.y + f[5]), o6 = f2bf(s1.z + f[6]), o7 = f2bf(s1.w + f[7]);
@@ -252,7 +257,7 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
         for (int i = 0; i < FK_STAGE_MAXB; ++i) {
             const int blk = i * blockDim.x + threadIdx.x;
             pv[i] = pw[i] = make_uint4(0, 0, 0, 0);
-            if (blk < nblk) { pv[i] = *reinterpret_cast<const uint4 *>(pending + (size_t)blk * 8); pw[i] = *reinterpret_cast<const uint4 *>(pending_w + (size_t)blk * 8); }
+            if (blk < nblk) { pv[i] = __ldcg(reinterpret_cast<const uint4 *>(pending + (size_t)blk * 8)); pw[i] = *reinterpret_cast<const uint4 *>(pending_w + (size_t)blk * 8); }
             float f[8]; unpack8(pv[i], f);
 #pragma unroll
             for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
@@ -301,7 +306,7 @@ __device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &s
 #pragma unroll
     for (int d = 0; d < 3; ++d) { cc[d][0] = cc[d][1] = cc[d][2] = cc[d][3] = 0; }
     const uint2 *zero2 = reinterpret_cast<const uint2 *>(sm.zero);
-#pragma unroll
+    FK_UNROLL(FK_J_UNROLL)
     for (int j = 0; j < 8; ++j) {
         const uint4 w = u[j * 32 + lane];
         if (BITS == 4) {
@@ -390,37 +395,56 @@ __device__ __forceinline__ void prefetch_next(const StreamPlan &p) {
     for (int i = 0; i < p.next_prefetch && c.valid(); ++i) { l2_prefetch(p.next_units + c.unit_index() * FK_UNIT_VEC, FK_UNIT_BYTES); c.advance(); }
 }
 
-struct WarpStream { uint64_t *bars; uint4 *ring; Cursor prod; int stages; };
-__device__ __forceinline__ void stream_issue(WarpStream &ws, const StreamPlan &p, int stage) {
-    if ((threadIdx.x & 31) == 0) {
-        mbar_expect_tx(ws.bars + stage, FK_UNIT_BYTES);
-        bulk_g2s(ws.ring + (size_t)stage * FK_UNIT_VEC, p.W.units + ws.prod.unit_index() * FK_UNIT_VEC, FK_UNIT_BYTES, ws.bars + stage);
+// Producer side of a warp's ring.  `consumed` counts the units this warp has taken out of the ring since its
+// barriers were initialised: it names the ring slot (consumed % stages) and the barrier phase to wait for.
+struct WarpStream {
+    uint64_t *bars; uint4 *ring; Cursor prod; int stages, consumed; const StreamPlan *plan; bool announced;
+    __device__ __forceinline__ bool valid() const { return prod.valid(); }
+    __device__ __forceinline__ unsigned long long *tl() const { return plan->timeline; }
+    __device__ __forceinline__ void issue(int stage) {
+        if ((threadIdx.x & 31) == 0) {
+            mbar_expect_tx(bars + stage, FK_UNIT_BYTES);
+            bulk_g2s(ring + (size_t)stage * FK_UNIT_VEC, plan->W.units + prod.unit_index() * FK_UNIT_VEC, FK_UNIT_BYTES, bars + stage);
+        }
+        prod.advance();
     }
-    ws.prod.advance();
-}
+    // everything this warp needs is in flight: let the next kernel start and warm L2 with its first units
+    __device__ __forceinline__ void drained() {
+        if (announced) return;
+        announced = true; pdl_launch_dependents(); prefetch_next(*plan);
+    }
+};
 // before griddepcontrol.wait: barriers up, ring filled with the warp's first units, fold buffer cleared
 __device__ __forceinline__ void stream_begin(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     ws.stages = p.stages; ws.bars = sm.bars + wid * p.stages; ws.ring = sm.ring + (size_t)wid * p.stages * FK_UNIT_VEC;
+    ws.consumed = 0; ws.plan = &p; ws.announced = false;
     ws.prod.init(p.W.ntiles, p.W.nsb, blockIdx.x, gridDim.x, wid, blockDim.x >> 5);
     if (lane == 0) { for (int s = 0; s < p.stages; ++s) mbar_init(ws.bars + s, 1); mbar_fence_init(); }
     for (int i = threadIdx.x; i < 2 * FK_CHUNK_TILES * FK_STREAM_MAXWARPS * 16; i += blockDim.x) sm.fold[i] = 0.0f;
     __syncwarp();
-    for (int s = 0; s < p.stages && ws.prod.valid(); ++s) stream_issue(ws, p, s);
+    for (int s = 0; s < p.stages && ws.valid(); ++s) ws.issue(s);
 }
 
-// Walk the block's chunks; `epi(tile, g, v_lo, v_hi)` receives the finished sums of tile rows g and g+8 on lanes with
-// (lane & 3) == 0 of the warp that folds the tile.  Returns false if a barrier wait expired.  Every warp of the block
-// must call this (it synchronises the block once per chunk).  The staging code must have synchronised the block
-// after stream_begin (it does), so the cleared fold buffer is visible.
-template <int BITS, class Epi>
-__device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm, Epi &epi) {
+// Walk the block's chunks of the weight W; `epi(tile, g, v_lo, v_hi)` receives the finished sums of tile rows g and g+8 on
+// lanes with (lane & 3) == 0 of the warp that folds the tile.  `pr` is the warp's producer (valid / issue / drained,
+// bars, ring, consumed): it must hand out W's units in Cursor order, and may run on into whatever is streamed next.
+// Returns false if a barrier wait expired.  Every warp of the block must call this (it synchronises the block once per
+// chunk), after a block-wide synchronisation that follows the clearing of the fold buffer.
+template <int BITS, class Prod, class Epi>
+__device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int dbg_mode, const StreamSmem &sm, Epi &epi) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5, g = lane >> 2, t = lane & 3;
-    Cursor cons; cons.init(p.W.ntiles, p.W.nsb, blockIdx.x, gridDim.x, wid, nw);
-    int consumed = 0;
-    bool prefetched = false, ok = true;
-    if (!ws.prod.valid()) { pdl_launch_dependents(); prefetch_next(p); prefetched = true; }      // everything this warp needs is already in flight
+    Cursor cons; cons.init(W.ntiles, W.nsb, blockIdx.x, gridDim.x, wid, nw);
+    bool ok = true;
+    if (!pr.valid()) pr.drained();
     const int nchunks = (cons.ntl + FK_CHUNK_TILES - 1) / FK_CHUNK_TILES;
+    if (t == 0 && cons.ntl > 0) {
+        // what the epilogue of this lane's first tile needs from global memory (residual, bias) or from slow math (RoPE
+        // angle) is fetched now, under the wait for the first unit, instead of after the last one
+        const int ct0 = cons.chunk_tiles(0);
+        const int first = (ct0 % nw) == 0 ? (cons.valid() ? cons.tile_local() : -1) : (wid < ct0 ? wid : -1);
+        if (first >= 0) epi.prefetch((int)blockIdx.x + first * (int)gridDim.x, g);
+    }
     for (int c = 0; c < nchunks; ++c) {
         float *fold = sm.fold + (c & 1) * FK_CHUNK_TILES * FK_STREAM_MAXWARPS * 16;
         const int ct = cons.chunk_tiles(c);
@@ -429,14 +453,15 @@ __device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, 
             const int tl = cons.tile_local();
             float acc_lo = 0.0f, acc_hi = 0.0f;
             while (ok && cons.valid() && cons.chunk == c && cons.tile_local() == tl) {
-                const int s = consumed & (FK_STAGES - 1);
-                if (p.dbg_mode != 3 && !mbar_wait(ws.bars + s, (uint32_t)(consumed >> 1) & 1u)) { ok = false; break; }
-                if (p.dbg_mode == 0) unit_compute<BITS>(ws.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
-                else if (p.dbg_mode == 3) { if (ws.prod.valid()) ws.prod.advance(); ++consumed; cons.advance(); unit_compute<BITS>(ws.ring + (size_t)s * FK_UNIT_VEC, sm, 0, lane, acc_lo, acc_hi); continue; }
+                const int s = pr.consumed & (FK_STAGES - 1);
+                if (dbg_mode != 3 && !mbar_wait(pr.bars + s, (uint32_t)(pr.consumed >> 1) & 1u)) { ok = false; break; }
+                if (pr.consumed == 0) stamp_raw(pr.tl(), 6);
+                if (dbg_mode == 0) unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
+                else if (dbg_mode == 3) { if (pr.valid()) pr.prod.advance(); ++pr.consumed; cons.advance(); unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, 0, lane, acc_lo, acc_hi); continue; }
                 __syncwarp();
-                if (ws.prod.valid()) stream_issue(ws, p, s);              // refill the stage just drained
-                else if (!prefetched) { pdl_launch_dependents(); prefetch_next(p); prefetched = true; }
-                ++consumed;
+                if (pr.valid()) pr.issue(s);              // refill the stage just drained
+                if (!pr.valid()) pr.drained();
+                ++pr.consumed;
                 cons.advance();
             }
             acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 1); acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 2);
@@ -447,6 +472,7 @@ __device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, 
             }
         }
         if (whole) continue;
+        if (c == 0) stamp_raw(pr.tl(), 7);
         __syncthreads();
         for (int q = wid; q < ct; q += nw) {                  // fold tile q of the chunk in warp order, then its epilogue
             if (t == 0) {
@@ -459,6 +485,10 @@ __device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, 
         // the buffer of chunk c is cleared by its folding warps before chunk c+2 writes it: chunk c+1's barrier orders them
     }
     return ok;
+}
+template <int BITS, class Epi>
+__device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm, Epi &epi) {
+    return stream_consume<BITS>(ws, p.W, p.dbg_mode, sm, epi);
 }
 
 // ------------------------------------------------------------------ repack / probe kernels
@@ -531,7 +561,30 @@ __global__ void k_dequant_tiled(TiledW W, int which, long long row0, long long n
 // ================================================================ streamed kernels
 
 struct SLinArgs { const uint16_t *x; StreamPlan P; const uint16_t *residual; uint16_t *y; float *y_f32; int k, n; };
+// Epilogues are functors: prefetch(tile, g) is called once per lane (lanes with (lane & 3) == 0) for the first tile the
+// lane will finish, before the streaming loop; operator() gets the finished sums of tile rows g and g + 8.
+
 // y = T(acc + float(residual)) (src/codegen/msl.rs:2759-2775); residual optional; optional fp32 copy of acc
+struct EpiLinear {
+    const SLinArgs &a; float res[2]; int ptile;
+    __device__ __forceinline__ EpiLinear(const SLinArgs &a_) : a(a_), ptile(-1) { res[0] = res[1] = 0.0f; }
+    __device__ __forceinline__ void prefetch(int tile, int g) {
+        ptile = tile;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) { const int r = tile * 16 + g + 8 * q; res[q] = (a.residual && r < a.n) ? bf2f(__ldcg(a.residual + r)) : 0.0f; }
+    }
+    __device__ __forceinline__ void operator()(int tile, int g, float lo, float hi) {
+        if (tile != ptile) prefetch(tile, g);
+        const float v[2] = {lo, hi};
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int r = tile * 16 + g + 8 * q;
+            if (r >= a.n) continue;
+            if (a.y_f32) a.y_f32[r] = v[q];
+            if (a.y) a.y[r] = f2bf(v[q] + res[q]);
+        }
+    }
+};
 template <int BITS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st, SLinArgs a) {
     extern __shared__ unsigned char smem_stream[];
@@ -542,18 +595,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st
     stamp(a.P, 1);
     stage_plain<BITS>(sm, a.x, a.k, a.P.W.nsb);
     stamp(a.P, 2);
-    auto epi = [&](int tile, int g, float lo, float hi) {
-        const float v[2] = {lo, hi};
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const int r = tile * 16 + g + 8 * q;
-            if (r >= a.n) continue;
-            float acc = v[q];
-            if (a.y_f32) a.y_f32[r] = acc;
-            if (a.residual) acc += bf2f(a.residual[r]);
-            if (a.y) a.y[r] = f2bf(acc);
-        }
-    };
+    EpiLinear epi(a);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x100u);
     pdl_launch_dependents();
     __syncthreads(); stamp(a.P, 3);
@@ -565,15 +607,54 @@ struct SQkvArgs {
     const uint16_t *pending, *pending_w; uint16_t *h_out;
     int h, n_q, n_kv, hd, capacity, sinks; float eps, log2theta; const float *pend_sum;
 };
-__device__ __forceinline__ void rope_rotate(float lo, float hi, int d, int half, uint32_t pos, float log2theta, uint16_t *o_lo, uint16_t *o_hi) {
+// cos and sin of the RoPE angle of dim d at position pos: inv = exp2(-(d / half) * log2(theta)) (rope_kv_cache_store_decode.rs)
+__device__ __forceinline__ void rope_angle(int d, int half, uint32_t pos, float log2theta, float *c, float *s) {
     const float e = __fmul_rn(-__fdiv_rn((float)d, (float)half), log2theta);
     const float ang = __fmul_rn((float)pos, exp2f(e));
-    float s, c; sincosf(ang, &s, &c);
+    sincosf(ang, s, c);
+}
+__device__ __forceinline__ void rope_apply(float lo, float hi, float c, float s, uint16_t *o_lo, uint16_t *o_hi) {
     *o_lo = f2bf(__fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, s)));
     *o_hi = f2bf(__fadd_rn(__fmul_rn(hi, c), __fmul_rn(lo, s)));
 }
+__device__ __forceinline__ void rope_rotate(float lo, float hi, int d, int half, uint32_t pos, float log2theta, uint16_t *o_lo, uint16_t *o_hi) {
+    float c, s; rope_angle(d, half, pos, log2theta, &c, &s);
+    rope_apply(lo, hi, c, s, o_lo, o_hi);
+}
 // RMSNorm -> QKV (+bias) -> RoPE -> K/V into the live cache (src/codegen/kernels/rmsnorm_qkv.rs:616-726).  With sinks the
 // weight rows are tiled as RoPE pairs, so a lane owns dims d and d + head_dim/2 of one head.
+struct EpiQkv {
+    const SQkvArgs &a; uint32_t pos; int wrow, ptile; float b0, b1, cs, sn;
+    __device__ __forceinline__ EpiQkv(const SQkvArgs &a_, uint32_t pos_) : a(a_), pos(pos_), wrow((int)(pos_ % (uint32_t)a_.capacity)), ptile(-1), b0(0.0f), b1(0.0f), cs(1.0f), sn(0.0f) {}
+    __device__ __forceinline__ int nrows() const { return (a.n_q + 2 * a.n_kv) * a.hd; }
+    __device__ __forceinline__ void store(int r, uint16_t v) const {
+        const int nq_rows = a.n_q * a.hd, nqk = (a.n_q + a.n_kv) * a.hd;
+        if (r < nq_rows) a.q_out[r] = v;
+        else if (r < nqk) {
+            const int kr = r - nq_rows, kh = kr / a.hd, d = kr - kh * a.hd;
+            if (a.sinks) a.cache_k[((size_t)kh * a.capacity + wrow) * a.hd + d] = v; else a.k_out[kr] = v;
+        } else if (r < nrows()) {
+            const int vr = r - nqk, kh = vr / a.hd, d = vr - kh * a.hd;
+            if (a.sinks) a.cache_v[((size_t)kh * a.capacity + wrow) * a.hd + d] = v; else a.v_out[vr] = v;
+        }
+    }
+    __device__ __forceinline__ void prefetch(int tile, int g) {
+        ptile = tile;
+        const int r0 = (int)tile_row(a.P.W.rows_kind, a.hd, a.P.W.n_rot, tile, g), r1 = (int)tile_row(a.P.W.rows_kind, a.hd, a.P.W.n_rot, tile, g + 8);
+        b0 = (a.lin_bias && r0 < nrows()) ? bf2f(a.lin_bias[r0]) : 0.0f;
+        b1 = (a.lin_bias && r1 < nrows()) ? bf2f(a.lin_bias[r1]) : 0.0f;
+        if (a.sinks && tile < a.P.W.n_rot / 16) rope_angle(r0 % a.hd, a.hd >> 1, pos, a.log2theta, &cs, &sn);
+    }
+    __device__ __forceinline__ void operator()(int tile, int g, float lo, float hi) {
+        if (tile != ptile) prefetch(tile, g);
+        const int r0 = (int)tile_row(a.P.W.rows_kind, a.hd, a.P.W.n_rot, tile, g), r1 = (int)tile_row(a.P.W.rows_kind, a.hd, a.P.W.n_rot, tile, g + 8);
+        lo += b0; hi += b1;
+        if (a.sinks && tile < a.P.W.n_rot / 16) {
+            uint16_t o0, o1; rope_apply(rT(lo), rT(hi), cs, sn, &o0, &o1);
+            store(r0, o0); store(r1, o1);
+        } else { store(r0, f2bf(lo)); store(r1, f2bf(hi)); }
+    }
+};
 template <int BITS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkState *st, SQkvArgs a) {
     extern __shared__ unsigned char smem_stream[];
@@ -584,27 +665,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkStat
     stamp(a.P, 1);
     stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
-    const uint32_t pos = st->offset;
-    const int wrow = (int)(pos % (uint32_t)a.capacity), half = a.hd >> 1;
-    const int nq_rows = a.n_q * a.hd, nqk = (a.n_q + a.n_kv) * a.hd, n = nqk + a.n_kv * a.hd;
-    auto store = [&](int r, uint16_t v) {
-        if (r < nq_rows) a.q_out[r] = v;
-        else if (r < nqk) {
-            const int kr = r - nq_rows, kh = kr / a.hd, d = kr - kh * a.hd;
-            if (a.sinks) a.cache_k[((size_t)kh * a.capacity + wrow) * a.hd + d] = v; else a.k_out[kr] = v;
-        } else if (r < n) {
-            const int vr = r - nqk, kh = vr / a.hd, d = vr - kh * a.hd;
-            if (a.sinks) a.cache_v[((size_t)kh * a.capacity + wrow) * a.hd + d] = v; else a.v_out[vr] = v;
-        }
-    };
-    auto epi = [&](int tile, int g, float lo, float hi) {
-        const int r0 = (int)tile_row(a.P.W.rows_kind, a.hd, a.P.W.n_rot, tile, g), r1 = (int)tile_row(a.P.W.rows_kind, a.hd, a.P.W.n_rot, tile, g + 8);
-        if (a.lin_bias) { if (r0 < n) lo += bf2f(a.lin_bias[r0]); if (r1 < n) hi += bf2f(a.lin_bias[r1]); }
-        if (a.sinks && tile < a.P.W.n_rot / 16) {
-            uint16_t o0, o1; rope_rotate(rT(lo), rT(hi), r0 % a.hd, half, pos, a.log2theta, &o0, &o1);
-            store(r0, o0); store(r1, o1);
-        } else { store(r0, f2bf(lo)); store(r1, f2bf(hi)); }
-    };
+    EpiQkv epi(a, st->offset);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x200u);
     pdl_launch_dependents();
     __syncthreads(); stamp(a.P, 3);
@@ -629,6 +690,15 @@ __device__ __forceinline__ uint16_t s_act_geglu(float ga, float ua) {
 }
 // RMSNorm -> gate & up -> activation tail in registers (src/codegen/kernels/fused_chain.rs:2902-3552; msl.rs:1286-1294).
 // The paired weight interleaves 8 gate rows with the 8 matching up rows per tile, so a lane holds both.
+struct EpiGateUp {
+    const SGateUpArgs &a;
+    __device__ __forceinline__ EpiGateUp(const SGateUpArgs &a_) : a(a_) {}
+    __device__ __forceinline__ void prefetch(int, int) {}
+    __device__ __forceinline__ void operator()(int tile, int g, float gate, float up) {
+        const int r = tile * 8 + g;
+        if (r < a.inter) a.act_out[r] = a.act == 1 ? s_act_geglu(gate, up) : s_act_swiglu(gate, up);
+    }
+};
 template <int BITS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st, SGateUpArgs a) {
     extern __shared__ unsigned char smem_stream[];
@@ -639,10 +709,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st
     stamp(a.P, 1);
     stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
-    auto epi = [&](int tile, int g, float gate, float up) {
-        const int r = tile * 8 + g;
-        if (r < a.inter) a.act_out[r] = a.act == 1 ? s_act_geglu(gate, up) : s_act_swiglu(gate, up);
-    };
+    EpiGateUp epi(a);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x400u);
     pdl_launch_dependents();
     __syncthreads(); stamp(a.P, 3);
@@ -660,6 +727,23 @@ __device__ __forceinline__ void s_finalize_token(FkState *st, uint32_t *history,
     st->hist_counter += 1;
     st->offset += 1;
 }
+struct EpiHead {
+    const SHeadArgs &a; unsigned long long best;
+    __device__ __forceinline__ EpiHead(const SHeadArgs &a_) : a(a_), best(0ull) {}
+    __device__ __forceinline__ void prefetch(int, int) {}
+    __device__ __forceinline__ void operator()(int tile, int g, float lo, float hi) {
+        const float v[2] = {lo, hi};
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int r = tile * 16 + g + 8 * q;
+            if (r >= a.v) continue;
+            const uint16_t tb = f2bf(v[q]);
+            if (a.logits) a.logits[r] = tb;
+            const unsigned long long key = argmax_key(tb, (uint32_t)(r + a.vocab_offset));
+            best = key > best ? key : best;
+        }
+    }
+};
 // final RMSNorm -> lm_head -> argmax on T-rounded logits, ties to the lowest index, no logits round trip
 // (final_rmsnorm_lm_head.rs:250-326; msl.rs:1805-1838); the last block folds the per-block keys and advances the state
 template <int BITS, int WARPS>
@@ -673,20 +757,9 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, 
     stamp(a.P, 1);
     stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
-    unsigned long long best = 0ull;
-    auto epi = [&](int tile, int g, float lo, float hi) {
-        const float v[2] = {lo, hi};
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const int r = tile * 16 + g + 8 * q;
-            if (r >= a.v) continue;
-            const uint16_t tb = f2bf(v[q]);
-            if (a.logits) a.logits[r] = tb;
-            const unsigned long long key = argmax_key(tb, (uint32_t)(r + a.vocab_offset));
-            best = key > best ? key : best;
-        }
-    };
+    EpiHead epi(a);
     const bool ok = stream_run<BITS>(ws, a.P, sm, epi);
+    unsigned long long best = epi.best;
     pdl_launch_dependents();
     if (!ok) atomicOr(&st->error, 0x800u);
     stamp(a.P, 3);

@@ -390,12 +390,39 @@ class DecodeEngine:
         return self.dispatches_from(self.task_graph())
 
     # ------------------------------------------------------------------ replay
-    def capture(self) -> int:
-        tasks = self.build_dispatches()
-        self.tasks = tasks
+    def program_build(self, tasks) -> int:
+        """Compile a task list for the persistent kernel; raises FusekitError when the list is not expressible."""
         arr = (N.Task * len(tasks))(*tasks)
+        pid = C.c_uint64()
+        N.check(self.rt.L.fk_program_build(self.rt.h, arr, len(tasks), C.byref(pid)), "fk_program_build")
+        return pid.value
+
+    def replay_list(self, persistent: bool | None = None) -> list:
+        """What a token replays: the task list itself, or -- when it can be compiled for the persistent kernel --
+        the single FK_TASK_DECODE_TOKEN task that runs it.  `persistent`: None = follow FK_PERSISTENT (default 0: one
+        kernel per task, which is the faster path today), True = require the persistent kernel, False = never."""
+        import os
+        tasks = self.build_dispatches()
+        self.tasks, self.persistent = tasks, False
+        if persistent is None and os.environ.get("FK_PERSISTENT", "0") == "0":
+            persistent = False
+        if persistent is False:
+            return tasks
+        try:
+            pid = self.program_build(tasks)
+        except N.FusekitError:
+            if persistent:
+                raise
+            return tasks
+        self.persistent = True
+        return [N.Task.make(N.TASK_DECODE_TOKEN, -1, {0: pid})]
+
+    def capture(self, persistent: bool | None = None) -> int:
+        replay = self.replay_list(persistent)
+        self.replay = replay
+        arr = (N.Task * len(replay))(*replay)
         g = C.c_uint64()
-        N.check(self.rt.L.fk_graph_capture(self.rt.h, arr, len(tasks), C.byref(g)), "fk_graph_capture")
+        N.check(self.rt.L.fk_graph_capture(self.rt.h, arr, len(replay), C.byref(g)), "fk_graph_capture")
         self.graph = g.value
         return self.graph
 
@@ -426,11 +453,11 @@ class DecodeEngine:
     def profile_nodes(self, repeats: int = 3):
         if not self.graph:
             self.capture()
-        n = len(self.tasks)
+        n = len(self.replay)
         out = (C.c_double * n)()
         cnt = C.c_int()
         N.check(self.rt.L.fk_graph_profile_nodes(self.rt.h, self.graph, repeats, out, n, C.byref(cnt)), "fk_graph_profile_nodes")
-        return [(self.tasks[i].kind, self.tasks[i].layer, out[i]) for i in range(n)]
+        return [(self.replay[i].kind, self.replay[i].layer, out[i]) for i in range(n)]
 
     def time_tasks(self, tasks, repeats: int = 5) -> float:
         """Seconds per pass of `tasks` launched back to back (CUDA events on the library's stream)."""

@@ -49,7 +49,10 @@ enum {
     FK_TASK_ARGMAX_FINALIZE = 8,       /* argmax_logits_finalize.rs:16-115 (+ history capture) */
     FK_TASK_ALLREDUCE = 9,             /* no reference counterpart: tensor-parallel sum over ranks */
     FK_TASK_RESIDUAL_ADD = 10,         /* no reference counterpart: y = T(sum + residual) after FK_TASK_ALLREDUCE */
-    FK_TASK_KIND_COUNT = 11
+    FK_TASK_DECODE_TOKEN = 11,         /* a whole token's task list run by one persistent kernel (fk_program_build); the
+                                          reference's counterpart is the replay of its event-ordered task graph,
+                                          src/codegen/task_graph_json.rs:33-226 */
+    FK_TASK_KIND_COUNT = 12
 };
 
 /* activation selector for FK_TASK_RMSNORM_GATEUP_ACT */
@@ -80,6 +83,7 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  * ARGMAX_FINALIZE      buf4 argmax scratch  i0 entries
  * ALLREDUCE            buf0 f32 buffer   i0 count
  * RESIDUAL_ADD         buf0 sum f32[N]  buf1 residual T[N]  buf2 y_out T[N]   i0 N
+ * DECODE_TOKEN         buf0 program id from fk_program_build
  */
 typedef struct fk_task {
     int32_t  kind;
@@ -147,6 +151,14 @@ fk_status fk_smoke(fk_handle h, const uint16_t *a, const uint16_t *b, uint16_t *
  *      lib.rs:884-1012, and the device-side counters of fusekit_step_init) -------------------- */
 fk_status fk_state_set(fk_handle h, uint32_t token, uint32_t offset);
 fk_status fk_state_get(fk_handle h, uint32_t *token, uint32_t *offset, uint32_t *error_word);
+
+/* ---- persistent program: compile a token's task list (embed, rmsnorm_qkv with sinks, sdpa, linear_residual,
+ *      rmsnorm_gateup_act, final_rmsnorm_lm_head; 4/8-bit streamed weights of one width) into records that one
+ *      resident cooperative kernel walks, with grid barriers where the reference's task graph has events
+ *      (src/codegen/task_graph_json.rs:33-226 `events`/`num_triggers`; replay order dispatch.py:3163-3611).
+ *      Launch it as a single FK_TASK_DECODE_TOKEN task, eagerly or captured by fk_graph_capture.  Lists it cannot
+ *      express are refused with FK_ERR_VALUE and the caller keeps the one-kernel-per-task path. ------------------- */
+fk_status fk_program_build(fk_handle h, const fk_task *tasks, int n, uint64_t *program_out);
 
 /* ---- per-token graph (reference: build_icb lib.rs:459-570, execute_icb lib.rs:718-760,
  *      submit_icb_async / wait_pending_icb lib.rs:659-715, profile_icb_commands lib.rs:821-869) - */
