@@ -9,8 +9,10 @@
 //     activation staging of the next task;
 //   * a task boundary is a grid barrier (one atomic arrive per block on a monotone counter + a bounded acquire
 //     spin), the device-side form of the reference's event with `num_triggers` = number of blocks;
-//   * attention splits the keys of a kv head over up to FK_MEGA_PARTS blocks, writes (m, l, o) partials, and the
-//     o_proj staging of every block folds them (sdpa_decode.rs:992-1046) -- no second barrier, no ticket.
+//   * attention splits the keys of a kv head over up to FK_MEGA_PARTS blocks that write (m, l, o) partials; the last
+//     of them to arrive (a ticket, no waiting) folds the partials (sdpa_decode.rs:992-1046);
+//   * a task runs its code once per token and layer, so code size is time: one call site per staging routine, one
+//     instance of the streaming loop with the epilogue chosen inside, rolled loops in attention.
 // Co-residency of the grid is guaranteed by the cooperative launch attribute; every wait is bounded and a block
 // that gives up sets FkState.error, drains its own copies in flight and leaves.
 #pragma once
@@ -18,20 +20,16 @@
 #include "fk_stream.cuh"
 
 #define FK_MEGA_WARPS 16
-#define FK_MEGA_PARTS 8             // blocks that may share one kv head's keys
-#define FK_MEGA_KEYBLOCK 128        // keys per block are a multiple of this (16 warps x 8 keys)
+#define FK_MEGA_PARTS 16            // blocks that may share one kv head's keys
+#define FK_MEGA_KEYBLOCK 64         // keys per block are a multiple of this (one pass of the attention tiles)
 #define FK_MEGA_SPIN_LIMIT (1u << 22)
 
 struct MegaSync { unsigned int count, seq, pad[30]; };
 struct MegaWeight { const uint4 *units; int ntiles, nsb; };     // what a producer needs of a streamed task
 
-struct MegaAttn {               // o_proj input folded from attention partials instead of read from x
-    const float *part; uint16_t *out; int n_q, n_kv, hd, capacity;
-};
 struct alignas(16) MegaOp {
     int kind, widx;             // FK_TASK_* kind; index into the weight table or -1
-    int attn_fold, pad0;
-    MegaAttn attn;
+    int pad0, pad1;
     union { EmbedArgs emb; SQkvArgs qkv; SdpaArgs sdpa; SLinArgs lin; SGateUpArgs gu; SHeadArgs head; } u;
 };
 #define FK_MEGA_OP_BYTES 288
@@ -39,7 +37,6 @@ union alignas(16) MegaSlot { MegaOp op; unsigned char raw[FK_MEGA_OP_BYTES]; }; 
 static_assert(sizeof(MegaSlot) == FK_MEGA_OP_BYTES, "MegaOp grew past its slot");
 
 // shared memory: [op slots 2 x 288][flags 64][bars 512][zero 256][red 192][warp stream state 1024][weight table][xsi][fold][activations | attention scratch][ring]
-__host__ __device__ inline size_t mega_attn_scratch_bytes(int G, int hd) { return sizeof(float) * (size_t)(G * (hd + 16) + (FK_MEGA_WARPS / 2) * G * (hd + 2) + G * (hd + 2) + 64); }
 struct MegaLayout { size_t wtab, xsi, fold, act, ring, total; };
 __host__ __device__ inline MegaLayout mega_layout(int nweights, int max_nsb, int bits, size_t attn_bytes) {
     MegaLayout L;
@@ -88,12 +85,12 @@ struct MegaStream {
     __device__ __forceinline__ unsigned long long *tl() const { return nullptr; }
     // between tasks the state sits in shared memory (one record per warp), so it holds no registers during attention and staging
     __device__ __forceinline__ void save(int *w) const {
-        if ((threadIdx.x & 31) == 0) { w[0] = consumed; w[1] = issued; w[2] = widx; w[3] = prod.chunk; w[4] = prod.tq; w[5] = prod.sbv; w[6] = prod.left; w[7] = prod.ntl; w[8] = prod.nsb; }
+        if ((threadIdx.x & 31) == 0) { w[0] = consumed; w[1] = issued; w[2] = widx; w[3] = prod.chunk; w[4] = prod.tq; w[5] = prod.sbv; w[6] = prod.left; w[7] = prod.ntl; w[8] = prod.nsb; w[9] = prod.nb; }
         __syncwarp();
     }
     __device__ __forceinline__ void load(const int *w, uint64_t *bars_, uint4 *ring_, const MegaWeight *wtab_, int nweights_) {
         bars = bars_; ring = ring_; wtab = wtab_; nweights = nweights_;
-        consumed = w[0]; issued = w[1]; widx = w[2]; prod.chunk = w[3]; prod.tq = w[4]; prod.sbv = w[5]; prod.left = w[6]; prod.ntl = w[7]; prod.nsb = w[8];
+        consumed = w[0]; issued = w[1]; widx = w[2]; prod.chunk = w[3]; prod.tq = w[4]; prod.sbv = w[5]; prod.left = w[6]; prod.ntl = w[7]; prod.nsb = w[8]; prod.nb = w[9];
         prod.nwarps = blockDim.x >> 5; prod.wid = threadIdx.x >> 5; prod.block = blockIdx.x; prod.grid = gridDim.x;
     }
     // bounded wait for the copies still in flight (a block that leaves early must not exit under its own TMA writes)
@@ -111,13 +108,11 @@ __device__ __forceinline__ bool mega_barrier(MegaSync *sync, volatile MegaCtl *c
     if (threadIdx.x == 0) {
         const unsigned int target = ctl->target + gridDim.x;
         ctl->target = target;
-        __threadfence();
-        red_release_add(&sync->count, 1u);
+        red_release_add(&sync->count, 1u);          // release: the block's writes, ordered before this by the block barrier above
         unsigned int it = 0;
         while (ctl->dead == 0 && (int)(ld_acquire_u32(&sync->count) - target) < 0) {
             if (++it > FK_MEGA_SPIN_LIMIT || ((it & 1023u) == 0 && *(volatile uint32_t *)&st->error != 0u)) { ctl->dead = 1; atomicOr(&st->error, 0x1000u); }
         }
-        __threadfence();
     }
     __syncthreads();
     return ctl->dead == 0;
@@ -134,194 +129,188 @@ __device__ __forceinline__ void mega_attn_split(int kv_len, int &kpc, int &n_act
     n_active = (kv_len + kpc - 1) / kpc;
 }
 
-// Attention partials of block (kv head, rank): online softmax per warp over 8-key blocks (four lanes per key for the
-// scores, head_dim/32 output dims per lane for p*V), warps merged pairwise through shared memory, the block's
-// (m, l, o[hd]) per q head written to part[(kvh * PARTS + rank)][g][hd + 2].
-template <int HD, int MAXG>
-__device__ __forceinline__ void mega_sdpa(const FkState *st, const SdpaArgs &a, float *scr, unsigned long long *tl, int opi) {
-    constexpr int DPL = HD / 32, KV4 = HD / 32, KPW = 8, CW = FK_MEGA_WARPS;
-    const int G = a.n_q / a.n_kv, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+// the K and V rows block (kv head, rank) will read in the attention task, pulled into L2 one task early (one thread)
+__device__ __forceinline__ void mega_attn_prefetch(const FkState *st, const SdpaArgs &a) {
     const int kvh = blockIdx.x / FK_MEGA_PARTS, rank = blockIdx.x % FK_MEGA_PARTS;
     if (kvh >= a.n_kv) return;
-    const uint32_t pos = st->offset;
-    const int kv_len = (int)min(pos + 1u, (uint32_t)a.capacity);
+    const int kv_len = (int)min(st->offset + 1u, (uint32_t)a.capacity);
+    int kpc, n_active; mega_attn_split(kv_len, kpc, n_active);
+    if (rank >= n_active) return;
+    const int k_begin = rank * kpc, k_end = min(kv_len, k_begin + kpc);
+    const size_t off = ((size_t)kvh * a.capacity + k_begin) * a.hd;
+    const uint32_t bytes = (uint32_t)(k_end - k_begin) * a.hd * 2;          // rows are multiples of 16 bytes, the caches 256-byte aligned
+    l2_prefetch(a.ck + off, bytes); l2_prefetch(a.cv + off, bytes);
+}
+
+// ---- attention, written for size: a task runs this code once per token and layer, so rolled loops over shared-memory
+// tiles beat unrolled register blocking (the instruction fetch of straight-line code costs more than its execution).
+#define FK_ATT_KEYS 64              // keys per pass (two 32-key groups)
+template <int HD> struct AttLayout {
+    static constexpr int KSTRIDE = HD * 2 + 16;                 // bytes per K row: 16-byte reads of 32 rows hit distinct banks
+    static constexpr int q = 0;                                  // float [G][HD]
+    __host__ __device__ static constexpr int k(int G) { return G * HD * 4; }                    // bf16 [64][HD + 8]
+    __host__ __device__ static constexpr int v(int G) { return k(G) + FK_ATT_KEYS * KSTRIDE; }  // bf16 [64][HD]
+    __host__ __device__ static constexpr int s(int G) { return v(G) + FK_ATT_KEYS * HD * 2; }   // float [G][64] scores, then [G][2] group maxima
+    __host__ __device__ static constexpr int mrg(int G) { return s(G) + G * (FK_ATT_KEYS + 2) * 4; }   // float [G][2][HD + 2] half partials
+    __host__ __device__ static constexpr int bytes(int G) { return mrg(G) + G * 2 * (HD + 2) * 4 + 16; }
+};
+__host__ __device__ inline size_t mega_attn2_bytes(int G, int hd) { return hd == 128 ? AttLayout<128>::bytes(G) : AttLayout<64>::bytes(G); }
+
+// Block (kv head, rank) of the split: partial (m, l, o[HD]) per q head over keys [rank * kpc, ...) in fp32
+// (sdpa_decode.rs:697-715), written to part[(kvh * PARTS + rank)][g][HD + 2]; the last block of a kv head to arrive
+// (ticket) folds the partials into out = T(o / l) (sdpa_decode.rs:992-1046).
+template <int HD>
+__device__ __noinline__ void mega_sdpa2(const FkState *st, const SdpaArgs &a, unsigned char *scr, unsigned long long *tl, int opi) {
+    using L = AttLayout<HD>;
+    constexpr int DPL = HD / 32, CH = HD / 8;                    // output dims per lane; 16-byte chunks per row
+    const int G = a.n_q / a.n_kv, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nthreads = blockDim.x;
+    const int kvh = blockIdx.x / FK_MEGA_PARTS, rank = blockIdx.x % FK_MEGA_PARTS;
+    if (kvh >= a.n_kv) return;
+    const int kv_len = (int)min(st->offset + 1u, (uint32_t)a.capacity);
     int kpc, n_active; mega_attn_split(kv_len, kpc, n_active);
     if (rank >= n_active) return;
     const int stride = HD + 2;
-    constexpr int QS = HD + 16, QP = HD / 4 + 4;
-    float *qs = scr;                              // [G][4][HD/4 + 4]
-    float *wpart = qs + G * QS;                   // [CW/2][G][HD+2]
+    float *qs = reinterpret_cast<float *>(scr + L::q);
+    unsigned char *kt = scr + L::k(G), *vt = scr + L::v(G);
+    float *sc = reinterpret_cast<float *>(scr + L::s(G)), *smax = sc + G * FK_ATT_KEYS;
+    float *mrg = reinterpret_cast<float *>(scr + L::mrg(G));
     const int k_begin = rank * kpc, k_end = min(kv_len, k_begin + kpc);
     const uint16_t *K = a.ck + (size_t)kvh * a.capacity * HD, *V = a.cv + (size_t)kvh * a.capacity * HD;
-    const int part = lane & 3, kl = lane >> 2;
-    uint4 kreg[KV4]; uint4 vraw[KPW];
-    for (int i = tid; i < G * HD; i += CW * 32) { const int g = i / HD, d = i - g * HD; qs[g * QS + (d / (HD / 4)) * QP + d % (HD / 4)] = bf2f(__ldcg(a.q + kvh * G * HD + i)); }
-    float m[MAXG], l[MAXG], o[MAXG][DPL];
+    for (int i = tid; i < G * HD; i += nthreads) qs[i] = bf2f(__ldcg(a.q + kvh * G * HD + i));
+    // this warp's (head, key group) item: scores for 32 keys, then p * V over the same 32 keys
+    const int item_g = wid >> 1, item_kg = wid & 1;
+    const bool has_item = item_g < G;
+    float m_run = -INFINITY, l_run = 0.0f, o[DPL];
 #pragma unroll
-    for (int g = 0; g < MAXG; ++g) { m[g] = -INFINITY; l[g] = 0.0f;
-#pragma unroll
-        for (int j = 0; j < DPL; ++j) o[g][j] = 0.0f; }
-    __syncthreads();
+    for (int j = 0; j < DPL; ++j) o[j] = 0.0f;
     mega_stamp(tl, opi, 4);
-    for (int kb = k_begin + wid * KPW; kb < k_end; kb += CW * KPW) {
-        const int key = kb + kl;
-        const bool valid = key < k_end;
-        {   // rows past the end are clamped to the last valid row (their scores are masked below): no predicated loads,
-            // so all K and V requests of the block are in flight together
-            const int kc = min(key, k_end - 1);
-            const uint4 *kr = reinterpret_cast<const uint4 *>(K + (size_t)kc * HD + part * (HD / 4));
-#pragma unroll
-            for (int c = 0; c < KV4; ++c) kreg[c] = __ldcg(kr + c);
-#pragma unroll
-            for (int kk = 0; kk < KPW; ++kk) {
-                const uint16_t *vr = V + (size_t)min(kb + kk, k_end - 1) * HD;
-                uint4 r = make_uint4(0, 0, 0, 0);
-                if (DPL == 4) { const uint2 v = __ldcg(reinterpret_cast<const uint2 *>(vr) + lane); r.x = v.x; r.y = v.y; }
-                else if (DPL == 2) r.x = __ldcg(reinterpret_cast<const uint32_t *>(vr) + lane);
-                else r = __ldcg(reinterpret_cast<const uint4 *>(vr) + lane);
-                vraw[kk] = r;
+#pragma unroll 1
+    for (int kb = k_begin; kb < k_end; kb += FK_ATT_KEYS) {
+        __syncthreads();                                        // q staged / previous pass done with the tiles
+#pragma unroll 2
+        for (int i = tid; i < FK_ATT_KEYS * CH; i += nthreads) {        // K and V tiles: rows past the end are zero
+            const int row = i / CH, c = i - row * CH;
+            uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
+            if (kb + row < k_end) {
+                kv = __ldcg(reinterpret_cast<const uint4 *>(K + (size_t)(kb + row) * HD) + c);
+                vv = __ldcg(reinterpret_cast<const uint4 *>(V + (size_t)(kb + row) * HD) + c);
             }
+            *reinterpret_cast<uint4 *>(kt + row * L::KSTRIDE + c * 16) = kv;
+            *reinterpret_cast<uint4 *>(vt + row * HD * 2 + c * 16) = vv;
         }
-        float dot[MAXG];
-#pragma unroll
-        for (int g = 0; g < MAXG; ++g) dot[g] = 0.0f;
-#pragma unroll
-        for (int c = 0; c < KV4; ++c) {
-            const uint4 v = kreg[c];
-            const float kf[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
-            const float *qp = qs + part * QP + c * 8;
-#pragma unroll
-            for (int g = 0; g < MAXG; ++g) if (g < G) {
-                const float4 q0 = *reinterpret_cast<const float4 *>(qp + g * QS), q1 = *reinterpret_cast<const float4 *>(qp + g * QS + 4);
-                dot[g] = fmaf(q0.x, kf[0], dot[g]); dot[g] = fmaf(q0.y, kf[1], dot[g]); dot[g] = fmaf(q0.z, kf[2], dot[g]); dot[g] = fmaf(q0.w, kf[3], dot[g]);
-                dot[g] = fmaf(q1.x, kf[4], dot[g]); dot[g] = fmaf(q1.y, kf[5], dot[g]); dot[g] = fmaf(q1.z, kf[6], dot[g]); dot[g] = fmaf(q1.w, kf[7], dot[g]);
+        __syncthreads();
+        if (has_item) {                                         // scores: lane = key
+            const int key = item_kg * 32 + lane;
+            const unsigned char *kr = kt + key * L::KSTRIDE;
+            const float *qg = qs + item_g * HD;
+            float dot = 0.0f;
+#pragma unroll 2
+            for (int c = 0; c < CH; ++c) {
+                const uint4 kv = *reinterpret_cast<const uint4 *>(kr + c * 16);
+                const float4 q0 = *reinterpret_cast<const float4 *>(qg + c * 8), q1 = *reinterpret_cast<const float4 *>(qg + c * 8 + 4);
+                dot = fmaf(q0.x, bf_lo(kv.x), dot); dot = fmaf(q0.y, bf_hi(kv.x), dot); dot = fmaf(q0.z, bf_lo(kv.y), dot); dot = fmaf(q0.w, bf_hi(kv.y), dot);
+                dot = fmaf(q1.x, bf_lo(kv.z), dot); dot = fmaf(q1.y, bf_hi(kv.z), dot); dot = fmaf(q1.z, bf_lo(kv.w), dot); dot = fmaf(q1.w, bf_hi(kv.w), dot);
             }
+            const float sv = (kb + key < k_end) ? dot * a.scale : -INFINITY;
+            sc[item_g * FK_ATT_KEYS + key] = sv;
+            const float mx = warp_max(sv);
+            if (lane == 0) smax[item_g * 2 + item_kg] = mx;
         }
-        float p[MAXG];
+        __syncthreads();
+        if (has_item) {                                         // online softmax step and p * V: lane = output dims
+            const float m_pass = fmaxf(smax[item_g * 2], smax[item_g * 2 + 1]);      // finite: the pass holds a valid key
+            const float m_new = fmaxf(m_run, m_pass);
+            const float alpha = expf(m_run - m_new);            // 0 on the first pass
+            const float sv = sc[item_g * FK_ATT_KEYS + item_kg * 32 + lane];
+            const float pl = sv == -INFINITY ? 0.0f : expf(sv - m_new);
+            l_run = fmaf(l_run, alpha, warp_sum(pl)); m_run = m_new;
 #pragma unroll
-        for (int g = 0; g < MAXG; ++g) if (g < G) {
-            float d = dot[g];
-            d += __shfl_xor_sync(0xffffffffu, d, 1); d += __shfl_xor_sync(0xffffffffu, d, 2);
-            const float s = valid ? d * a.scale : -INFINITY;
-            float mb = s;
-            mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 4)); mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 8));
-            mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
-            const float mn = fmaxf(m[g], mb);                 // finite: the block holds at least one valid key
-            const float alpha = expf(m[g] - mn);
-            p[g] = valid ? expf(s - mn) : 0.0f;
-            float ls = p[g];
-            ls += __shfl_xor_sync(0xffffffffu, ls, 4); ls += __shfl_xor_sync(0xffffffffu, ls, 8); ls += __shfl_xor_sync(0xffffffffu, ls, 16);
-            l[g] = fmaf(l[g], alpha, ls); m[g] = mn;
-#pragma unroll
-            for (int j = 0; j < DPL; ++j) o[g][j] *= alpha;
-        }
-#pragma unroll
-        for (int kk = 0; kk < KPW; ++kk) {
-#pragma unroll
-            for (int g = 0; g < MAXG; ++g) if (g < G) {
-                const float pk = __shfl_sync(0xffffffffu, p[g], kk * 4);
-#pragma unroll
-                for (int j = 0; j < DPL; ++j) {
-                    const uint32_t wv = j < 2 ? vraw[kk].x : j < 4 ? vraw[kk].y : j < 6 ? vraw[kk].z : vraw[kk].w;
-                    o[g][j] = fmaf(pk, (j & 1) ? bf_hi(wv) : bf_lo(wv), o[g][j]);
+            for (int j = 0; j < DPL; ++j) o[j] *= alpha;
+            const unsigned char *vb = vt + (size_t)(item_kg * 32) * HD * 2 + lane * DPL * 2;
+#pragma unroll 4
+            for (int kk = 0; kk < 32; ++kk) {
+                const float pk = __shfl_sync(0xffffffffu, pl, kk);
+                if (DPL == 4) {
+                    const uint2 vv = *reinterpret_cast<const uint2 *>(vb + kk * HD * 2);
+                    o[0] = fmaf(pk, bf_lo(vv.x), o[0]); o[1] = fmaf(pk, bf_hi(vv.x), o[1]); o[2] = fmaf(pk, bf_lo(vv.y), o[2]); o[3] = fmaf(pk, bf_hi(vv.y), o[3]);
+                } else {
+                    const uint32_t vv = *reinterpret_cast<const uint32_t *>(vb + kk * HD * 2);
+                    o[0] = fmaf(pk, bf_lo(vv), o[0]); o[1] = fmaf(pk, bf_hi(vv), o[1]);
                 }
             }
         }
     }
     mega_stamp(tl, opi, 5);
-    // pairwise merge of the warps: the upper half writes, the lower half folds, halving until warp 0 holds the block's sums
-    for (int half = CW / 2; half >= 1; half >>= 1) {
-        if (wid >= half && wid < 2 * half) {
+    // the two key groups of a head merge through shared memory; warp 2g then owns head g's block partial
+    if (has_item) {
+        float *w = mrg + (item_g * 2 + item_kg) * stride;
+        if (lane == 0) { w[0] = m_run; w[1] = l_run; }
 #pragma unroll
-            for (int g = 0; g < MAXG; ++g) if (g < G) {
-                float *w = wpart + ((wid - half) * G + g) * stride;
-                if (lane == 0) { w[0] = m[g]; w[1] = l[g]; }
+        for (int j = 0; j < DPL; ++j) w[2 + lane * DPL + j] = o[j];
+    }
+    __syncthreads();
+    if (has_item && item_kg == 0) {
+        const float *w0 = mrg + (item_g * 2) * stride, *w1 = w0 + stride;
+        const float M = fmaxf(w0[0], w1[0]);
+        const float e0 = w0[0] == -INFINITY ? 0.0f : expf(w0[0] - M), e1 = w1[0] == -INFINITY ? 0.0f : expf(w1[0] - M);
+        float *dst = a.part + ((size_t)(kvh * FK_MEGA_PARTS + rank) * G + item_g) * stride;
+        if (lane == 0) { dst[0] = M; dst[1] = fmaf(w0[1], e0, w1[1] * e1); }
 #pragma unroll
-                for (int j = 0; j < DPL; ++j) w[2 + lane * DPL + j] = o[g][j];
-            }
-        }
-        __syncthreads();
-        if (wid < half) {
-#pragma unroll
-            for (int g = 0; g < MAXG; ++g) if (g < G) {
-                const float *w = wpart + (wid * G + g) * stride;
-                const float m2 = w[0], l2 = w[1];
-                const float mn = fmaxf(m[g], m2);
-                const float e1 = m[g] == -INFINITY ? 0.0f : expf(m[g] - mn), e2 = m2 == -INFINITY ? 0.0f : expf(m2 - mn);
-                l[g] = fmaf(l[g], e1, l2 * e2); m[g] = mn;
-#pragma unroll
-                for (int j = 0; j < DPL; ++j) o[g][j] = fmaf(o[g][j], e1, w[2 + lane * DPL + j] * e2);
-            }
-        }
-        __syncthreads();
+        for (int j = 0; j < DPL; ++j) dst[2 + lane * DPL + j] = fmaf(w0[2 + lane * DPL + j], e0, w1[2 + lane * DPL + j] * e1);
     }
     mega_stamp(tl, opi, 6);
-    if (wid == 0) {
-#pragma unroll
-        for (int g = 0; g < MAXG; ++g) if (g < G) {
-            float *w = a.part + ((size_t)(kvh * FK_MEGA_PARTS + rank) * G + g) * stride;
-            if (lane == 0) { w[0] = m[g]; w[1] = l[g]; }
-#pragma unroll
-            for (int j = 0; j < DPL; ++j) w[2 + lane * DPL + j] = o[g][j];
+    // ticket: the last block of this kv head folds the partials
+    __shared__ int is_last;
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t t;     // release: the block's partial, ordered before this by the block barrier; acquire: the other blocks' partials
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(t) : "l"(a.counter + kvh) : "memory");
+        is_last = (t == (uint32_t)(n_active - 1));
+        if (is_last) a.counter[kvh] = 0u;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    // merge weights e^(m_r - M) / L per (partial, head) into shared memory (the score area is free now), then every
+    // thread sums its outputs over the partials straight from L2, eight loads in flight at a time
+    const float *src = a.part + (size_t)kvh * FK_MEGA_PARTS * G * stride;
+    float *wgt = sc;                                            // [n_active][G], n_active * G <= 16 * 8 <= G * 64 floats
+    if (tid < G) {
+        float M = -INFINITY;
+        for (int r = 0; r < n_active; ++r) M = fmaxf(M, __ldcg(src + (size_t)(r * G + tid) * stride));
+        float Lsum = 0.0f;
+        for (int r = 0; r < n_active; ++r) {
+            const float mr = __ldcg(src + (size_t)(r * G + tid) * stride);
+            const float e = mr == -INFINITY ? 0.0f : expf(mr - M);
+            wgt[r * G + tid] = e; Lsum = fmaf(__ldcg(src + (size_t)(r * G + tid) * stride + 1), e, Lsum);
         }
+        const float inv = __fdiv_rn(1.0f, Lsum);
+        for (int r = 0; r < n_active; ++r) wgt[r * G + tid] *= inv;
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int i = tid; i < G * HD; i += nthreads) {
+        const int g = i / HD, d = i - g * HD;
+        float O = 0.0f;
+#pragma unroll 8
+        for (int r = 0; r < n_active; ++r) O = fmaf(__ldcg(src + (size_t)(r * G + g) * stride + 2 + d), wgt[r * G + g], O);
+        a.out[(kvh * G + g) * HD + d] = f2bf(O);
     }
 }
 
-// o_proj staging: every block folds the attention partials into x = T(o / l) (sdpa_decode.rs:992-1046) and stages its
-// digits; block 0 also publishes x.
-template <int BITS>
-__device__ __forceinline__ void stage_attn(const StreamSmem &sm, const FkState *st, const MegaAttn &A, int nsb) {
-    const int k = A.n_q * A.hd, nblk = k >> 3, G = A.n_q / A.n_kv, stride = A.hd + 2;
-    stage_pad<BITS>(sm, k, nsb);
-    const int kv_len = (int)min(st->offset + 1u, (uint32_t)A.capacity);
-    int kpc, n_active; mega_attn_split(kv_len, kpc, n_active);
-    for (int b0 = 0; b0 < nblk; b0 += blockDim.x) {
-        const int blk = b0 + threadIdx.x;
-        float f[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = 0.0f;
-        if (blk < nblk) {
-            const int head = (blk * 8) / A.hd, d0 = blk * 8 - head * A.hd, kvh = head / G, g = head - kvh * G;
-            const float *p0 = A.part + ((size_t)(kvh * FK_MEGA_PARTS) * G + g) * stride;
-            const size_t rs = (size_t)G * stride;
-            // all (m, l) pairs first, then the outputs four partials at a time: unconditional loads (inactive partials
-            // re-read partial 0 and get weight 0), so each batch is one round trip
-            float2 ml[FK_MEGA_PARTS];
-#pragma unroll
-            for (int r = 0; r < FK_MEGA_PARTS; ++r) ml[r] = __ldcg(reinterpret_cast<const float2 *>(p0 + (r < n_active ? r : 0) * rs));
-            float M = -INFINITY;
-#pragma unroll
-            for (int r = 0; r < FK_MEGA_PARTS; ++r) if (r < n_active) M = fmaxf(M, ml[r].x);
-            float L = 0.0f;
-#pragma unroll
-            for (int h4 = 0; h4 < FK_MEGA_PARTS; h4 += 4) {
-                if (h4 >= n_active) break;
-                float2 o[4][4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float2 *po = reinterpret_cast<const float2 *>(p0 + (h4 + q < n_active ? h4 + q : 0) * rs + 2 + d0);     // 8-byte aligned: stride and d0 are even
-                    o[q][0] = __ldcg(po); o[q][1] = __ldcg(po + 1); o[q][2] = __ldcg(po + 2); o[q][3] = __ldcg(po + 3);
-                }
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float e = (h4 + q < n_active && ml[h4 + q].x != -INFINITY) ? expf(ml[h4 + q].x - M) : 0.0f;
-                    L = fmaf(ml[h4 + q].y, e, L);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) { f[2 * j] = fmaf(o[q][j].x, e, f[2 * j]); f[2 * j + 1] = fmaf(o[q][j].y, e, f[2 * j + 1]); }
-                }
-            }
-            const float inv = __fdiv_rn(1.0f, L);
-            uint16_t ob16[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) { ob16[j] = f2bf(f[j] * inv); f[j] = bf2f(ob16[j]); }
-            if (blockIdx.x == 0 && A.out)
-                *reinterpret_cast<uint4 *>(A.out + (size_t)blk * 8) = make_uint4(ob16[0] | ((uint32_t)ob16[1] << 16), ob16[2] | ((uint32_t)ob16[3] << 16),
-                                                                                 ob16[4] | ((uint32_t)ob16[5] << 16), ob16[6] | ((uint32_t)ob16[7] << 16));
-        }
-        if (b0 < nblk) store_block<BITS>(sm, blk, f, blk < nblk);
+// the epilogue of whichever streamed task is running (one instance of the streaming loop serves them all)
+struct EpiAny {
+    int kind; EpiQkv qkv; EpiLinear lin; EpiGateUp gu; EpiHead head;
+    __device__ __forceinline__ EpiAny(const MegaOp &op, uint32_t pos) : kind(op.kind), qkv(op.u.qkv, pos), lin(op.u.lin), gu(op.u.gu), head(op.u.head) {}
+    __device__ __forceinline__ void prefetch(int tile, int g) {
+        if (kind == FK_TASK_RMSNORM_QKV) qkv.prefetch(tile, g); else if (kind == FK_TASK_LINEAR_RESIDUAL) lin.prefetch(tile, g);
     }
-    __syncthreads();
-}
+    __device__ __forceinline__ void operator()(int tile, int g, float lo, float hi) {
+        if (kind == FK_TASK_RMSNORM_QKV) qkv(tile, g, lo, hi);
+        else if (kind == FK_TASK_LINEAR_RESIDUAL) lin(tile, g, lo, hi);
+        else if (kind == FK_TASK_RMSNORM_GATEUP_ACT) gu(tile, g, lo, hi);
+        else head(tile, g, lo, hi);
+    }
+};
 
 // The persistent kernel.  `ops` is the token's task list, `wtab` the streamed weights in task order.
 template <int BITS>
@@ -359,7 +348,7 @@ k_decode_token(FkState *st, const MegaSlot *ops, int nops, const MegaWeight *wta
     {
         MegaStream ms;
         ms.bars = wbars; ms.ring = wring; ms.consumed = 0; ms.issued = 0; ms.widx = -1; ms.nweights = nweights; ms.wtab = wtab;
-        ms.prod.left = 0; ms.prod.chunk = 0; ms.prod.tq = 0; ms.prod.sbv = 0; ms.prod.ntl = 0; ms.prod.nsb = 1;
+        ms.prod.left = 0; ms.prod.chunk = 0; ms.prod.tq = 0; ms.prod.sbv = 0; ms.prod.ntl = 0; ms.prod.nsb = 1; ms.prod.nb = 0;
         ms.seek();
         for (int s = 0; s < FK_STAGES && ms.valid(); ++s) ms.issue(s);
         ms.save(wstate);
@@ -373,9 +362,12 @@ k_decode_token(FkState *st, const MegaSlot *ops, int nops, const MegaWeight *wta
         if (i + 1 < nops && wid == FK_MEGA_WARPS - 1 && lane < FK_MEGA_OP_BYTES / 16)
             reinterpret_cast<uint4 *>(&opbuf[(i + 1) & 1])[lane] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const unsigned char *>(ops) + (size_t)(i + 1) * FK_MEGA_OP_BYTES) + lane);
         mega_stamp(timeline, i, 0);
+        // One call site per staging routine and one instance of the streaming loop: a task executes its code once, so
+        // the kernel is kept small enough for the instruction cache to hold a layer's worth of it.
+        const int kind = op.kind;
+        const bool streams = op.widx >= 0;
         bool sync_after = true;
-        switch (op.kind) {
-        case FK_TASK_EMBED_LOOKUP_DECODE: {
+        if (kind == FK_TASK_EMBED_LOOKUP_DECODE) {
             // every block writes the same row: a block only ever reads its own copy before the next barrier
             const EmbedArgs &a = op.u.emb;
             const uint32_t tok = st->token[0];
@@ -383,56 +375,50 @@ k_decode_token(FkState *st, const MegaSlot *ops, int nops, const MegaWeight *wta
             __threadfence_block();
             __syncthreads();
             sync_after = false;
-            break;
-        }
-        case FK_TASK_RMSNORM_QKV: {
-            const SQkvArgs &a = op.u.qkv;
-            stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, nullptr, a.pend_sum);
-            mega_stamp(timeline, i, 1);
-            EpiQkv epi(a, st->offset);
-            { MegaStream ms; ms.load(wstate, wbars, wring, wtab, nweights); ok = stream_consume<BITS>(ms, a.P.W, 0, sm, epi); ms.save(wstate); }
-            break;
-        }
-        case FK_TASK_SDPA_DECODE: {
+        } else if (kind == FK_TASK_SDPA_DECODE) {
             const SdpaArgs &a = op.u.sdpa;
             for (int rep = 0; rep <= dbg; ++rep) {       // dbg > 0 (tuning): repeat the task to see it with warm instruction caches
                 if (rep) __syncthreads();
-                if (a.hd == 128) mega_sdpa<128, 8>(st, a, attn_scr, timeline, i); else mega_sdpa<64, 8>(st, a, attn_scr, timeline, i);
+#ifdef FK_MEGA_LEAN
+                mega_sdpa2<128>(st, a, reinterpret_cast<unsigned char *>(attn_scr), timeline, i);
+#else
+                if (a.hd == 128) mega_sdpa2<128>(st, a, reinterpret_cast<unsigned char *>(attn_scr), timeline, i); else mega_sdpa2<64>(st, a, reinterpret_cast<unsigned char *>(attn_scr), timeline, i);
+#endif
             }
-            break;
-        }
-        case FK_TASK_LINEAR_RESIDUAL: {
-            const SLinArgs &a = op.u.lin;
-            if (op.attn_fold) stage_attn<BITS>(sm, st, op.attn, a.P.W.nsb); else stage_plain<BITS>(sm, a.x, a.k, a.P.W.nsb);
-            mega_stamp(timeline, i, 1);
-            EpiLinear epi(a);
-            { MegaStream ms; ms.load(wstate, wbars, wring, wtab, nweights); ok = stream_consume<BITS>(ms, a.P.W, 0, sm, epi); ms.save(wstate); }
-            break;
-        }
-        case FK_TASK_RMSNORM_GATEUP_ACT: {
-            const SGateUpArgs &a = op.u.gu;
-            stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, nullptr, a.pend_sum);
-            mega_stamp(timeline, i, 1);
-            EpiGateUp epi(a);
-            { MegaStream ms; ms.load(wstate, wbars, wring, wtab, nweights); ok = stream_consume<BITS>(ms, a.P.W, 0, sm, epi); ms.save(wstate); }
-            break;
-        }
-        case FK_TASK_FINAL_RMSNORM_LM_HEAD: {
-            const SHeadArgs &a = op.u.head;
-            stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, nullptr, a.pend_sum);
-            mega_stamp(timeline, i, 1);
-            EpiHead epi(a);
-            { MegaStream ms; ms.load(wstate, wbars, wring, wtab, nweights); ok = stream_consume<BITS>(ms, a.P.W, 0, sm, epi); ms.save(wstate); }
-            best = warp_max_u64(epi.best);
-            if (lane == 0) wbest[wid] = best;
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                for (int w = 1; w < FK_MEGA_WARPS; ++w) best = wbest[w] > best ? wbest[w] : best;
-                a.scratch[blockIdx.x] = best;
+        } else if (streams) {
+            const TiledW *W;
+            if (kind == FK_TASK_LINEAR_RESIDUAL) {
+                const SLinArgs &a = op.u.lin;
+                W = &a.P.W;
+                stage_plain<BITS>(sm, a.x, a.k, a.P.W.nsb);
+            } else {
+                // the three norm-first tasks differ only in where their arguments sit
+                const uint16_t *x, *nw, *pending, *pending_w; uint16_t *h_out; const float *pend_sum; int h; float eps;
+                if (kind == FK_TASK_RMSNORM_QKV) { const SQkvArgs &a = op.u.qkv; W = &a.P.W; x = a.x; nw = a.norm_w; pending = a.pending; pending_w = a.pending_w; h_out = a.h_out; pend_sum = a.pend_sum; h = a.h; eps = a.eps; }
+                else if (kind == FK_TASK_RMSNORM_GATEUP_ACT) { const SGateUpArgs &a = op.u.gu; W = &a.P.W; x = a.x; nw = a.norm_w; pending = a.pending; pending_w = a.pending_w; h_out = a.h_out; pend_sum = a.pend_sum; h = a.h; eps = a.eps; }
+                else { const SHeadArgs &a = op.u.head; W = &a.P.W; x = a.x; nw = a.norm_w; pending = a.pending; pending_w = a.pending_w; h_out = a.h_out; pend_sum = a.pend_sum; h = a.h; eps = a.eps; }
+#ifdef FK_MEGA_LEAN
+                stage_rmsnorm<BITS>(sm, x, nw, h, W->nsb, eps, nullptr, nullptr, nullptr, nullptr, nullptr);
+#else
+                stage_rmsnorm<BITS>(sm, x, nw, h, W->nsb, eps, pending, pending_w, h_out, nullptr, pend_sum);
+#endif
             }
-            break;
-        }
-        default: break;
+            mega_stamp(timeline, i, 1);
+            if (kind == FK_TASK_RMSNORM_QKV && threadIdx.x == 0 && i + 1 < nops) {      // the staging above synchronised the block: the next record is in
+                const MegaOp &nx = opbuf[(i + 1) & 1].op;
+                if (nx.kind == FK_TASK_SDPA_DECODE) mega_attn_prefetch(st, nx.u.sdpa);
+            }
+            EpiAny epi(op, st->offset);
+            { MegaStream ms; ms.load(wstate, wbars, wring, wtab, nweights); ok = stream_consume<BITS>(ms, *W, 0, sm, epi); ms.save(wstate); }
+            if (kind == FK_TASK_FINAL_RMSNORM_LM_HEAD) {
+                best = warp_max_u64(epi.head.best);
+                if (lane == 0) wbest[wid] = best;
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    for (int w = 1; w < FK_MEGA_WARPS; ++w) best = wbest[w] > best ? wbest[w] : best;
+                    op.u.head.scratch[blockIdx.x] = best;
+                }
+            }
         }
         if (!ok) { atomicOr(&st->error, 0x2000u); ctl->dead = 1; }      // a ring wait expired in this warp: the block gives up at the boundary
         mega_stamp(timeline, i, 2);

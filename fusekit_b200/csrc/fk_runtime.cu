@@ -71,12 +71,13 @@ struct Weight {
 struct Program {
     MegaSlot *ops = nullptr; MegaWeight *wtab = nullptr; MegaSync *sync = nullptr; float *part = nullptr;
     int nops = 0, nweights = 0, max_nsb = 0, bits = 0, attn_bytes = 0, barriers = 0; size_t smem = 0;
+    std::vector<std::pair<void *, size_t>> zero;
 };
 struct Recorder {               // filled by run_task instead of launching while a program is being built
     std::vector<MegaSlot> ops; std::vector<MegaWeight> wtab;
     int bits = 0, max_nsb = 0, attn_bytes = 0, barriers = 0, min_grid = 1;
     float *part = nullptr; size_t part_floats = 0;
-    bool have_attn = false; MegaAttn attn;
+    std::vector<std::pair<void *, size_t>> zero;      // ticket counters to clear whenever the decode state is reset
 };
 struct Graph {
     std::vector<fk_task> tasks;
@@ -532,13 +533,14 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             Recorder *r = c->rec;
             if (hd != 64 && hd != 128) return fail(FK_ERR_VALUE, "persistent program: head_dim must be 64 or 128");
             if ((size_t)nq * FK_MEGA_PARTS * (hd + 2) > r->part_floats) return fail(FK_ERR_VALUE, "persistent program: attention partial buffer too small");
+            if (G * 2 > FK_MEGA_WARPS) return fail(FK_ERR_VALUE, "persistent program: at most %d q heads per kv head", FK_MEGA_WARPS / 2);
             a.part = r->part; a.tl = nullptr;
-            const int ab = (int)mega_attn_scratch_bytes(G, hd);
+            const int ab = (int)mega_attn2_bytes(G, hd);
             if (ab > r->attn_bytes) r->attn_bytes = ab;
             if (nkv * FK_MEGA_PARTS > r->min_grid) r->min_grid = nkv * FK_MEGA_PARTS;
             MegaOp op = rec_op(t.kind); op.u.sdpa = a; rec_push(c, op);
             r->barriers++;
-            r->have_attn = true; r->attn.part = r->part; r->attn.out = a.out; r->attn.n_q = nq; r->attn.n_kv = nkv; r->attn.hd = hd; r->attn.capacity = cap;
+            r->zero.push_back({(void *)a.counter, sizeof(uint32_t) * (size_t)nkv});
             return FK_OK;
         }
         if (c->sdpa_cluster && (hd != 256 || G <= 2)) {
@@ -563,14 +565,8 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             if (w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "linear_residual takes plain row order");
             SLinArgs sa{a.x, StreamPlan(), a.residual, a.y, a.y_f32, i[0], i[1]};
             if (c->rec) {
-                Recorder *r = c->rec;
                 if (sa.y_f32 || !sa.y) return fail(FK_ERR_VALUE, "persistent program: linear_residual writes T outputs only");
                 MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, w); if (rs) return rs;
-                if (r->have_attn && sa.x == r->attn.out) {      // reads the attention output: fold the partials while staging
-                    if (r->attn.n_q * r->attn.hd != i[0]) return fail(FK_ERR_VALUE, "persistent program: o_proj width does not match the attention output");
-                    op.attn_fold = 1; op.attn = r->attn;
-                }
-                r->have_attn = false;
                 op.u.lin = sa; rec_push(c, op); return FK_OK;
             }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
@@ -688,7 +684,7 @@ extern "C" fk_status fk_program_build(fk_handle h, const fk_task *tasks, int n, 
         if (p.smem > 227 * 1024) s = fail(FK_ERR_VALUE, "persistent program: %zu bytes of shared memory needed, 232448 available", p.smem);
     }
     if (s != FK_OK) { cudaFree(r.part); return s; }
-    p.part = r.part;
+    p.part = r.part; p.zero = r.zero;
     CU(cudaMalloc(&p.ops, r.ops.size() * sizeof(MegaSlot)));
     CU(cudaMalloc(&p.wtab, r.wtab.size() * sizeof(MegaWeight)));
     CU(cudaMalloc(&p.sync, sizeof(MegaSync)));
@@ -766,7 +762,10 @@ static fk_status set_state(Ctx *c, uint32_t token, uint32_t offset) {
     FkState *s = (FkState *)c->pinned; memset(s, 0, sizeof(FkState));
     s->token[0] = token; s->offset = offset; s->hist_counter = 0; s->error = 0; s->hist_cap = c->hist_cap;
     CU(cudaMemcpyAsync(c->state, s, sizeof(FkState), cudaMemcpyHostToDevice, c->stream));
-    for (Program &p : c->programs) CU(cudaMemsetAsync(p.sync, 0, sizeof(MegaSync), c->stream));     // barrier counters restart with the state
+    for (Program &p : c->programs) {        // barrier and ticket counters restart with the state
+        CU(cudaMemsetAsync(p.sync, 0, sizeof(MegaSync), c->stream));
+        for (auto &z : p.zero) CU(cudaMemsetAsync(z.first, 0, z.second, c->stream));
+    }
     return FK_OK;
 }
 extern "C" fk_status fk_state_set(fk_handle h, uint32_t token, uint32_t offset) {

@@ -356,28 +356,38 @@ __device__ __forceinline__ void stamp(const StreamPlan &p, int slot) {
         p.timeline[blockIdx.x * 8 + slot] = t;
     }
 }
-// Work of a block: its row tiles are block, block+grid, block+2*grid, ... taken in chunks of FK_CHUNK_TILES; the
-// units (tile, super-block) of a chunk are dealt to the warps round-robin, so every warp gets the same number of
-// units (+-1) whatever the tile count, and a tile's K range is shared by the warps of one block only.
+// Work of a block: its row tiles are block, block+grid, block+2*grid, ... taken in chunks.  While at least one tile per
+// warp is left a chunk is `nwarps` tiles and every warp owns whole tiles of it (no fold); the remainder goes in chunks
+// of up to FK_CHUNK_TILES tiles whose units (tile, super-block) are dealt to the warps in contiguous runs, so every
+// warp gets the same number of units (+-1) and a tile's K range is shared by the warps of one block only.
 struct Cursor {
-    int nsb, ntl, nwarps, wid, block, grid;     // ntl: tiles of this block
+    int nsb, ntl, nwarps, wid, block, grid, nb; // ntl: tiles of this block; nb: chunks of one tile per warp
     int chunk, tq, sbv, left;                   // current chunk, tile inside the chunk, super-block, units left in the chunk
     __device__ __forceinline__ void init(int ntiles, int nsb_, int block_, int grid_, int wid_, int nwarps_) {
         nsb = nsb_; nwarps = nwarps_; wid = wid_; block = block_; grid = grid_;
         ntl = block_ < ntiles ? (ntiles - block_ + grid_ - 1) / grid_ : 0;
+        nb = ntl / nwarps_;
         chunk = -1; left = 0;
         next_chunk();
     }
-    __device__ __forceinline__ int chunk_tiles(int c) const { const int r = ntl - c * FK_CHUNK_TILES; return r < FK_CHUNK_TILES ? r : FK_CHUNK_TILES; }
+    __device__ __forceinline__ int nbig() const { return nb; }
+    __device__ __forceinline__ int nchunks() const { return nbig() + (ntl - nbig() * nwarps + FK_CHUNK_TILES - 1) / FK_CHUNK_TILES; }
+    __device__ __forceinline__ int chunk_start(int c) const { const int b = nbig(); return c < b ? c * nwarps : b * nwarps + (c - b) * FK_CHUNK_TILES; }
+    __device__ __forceinline__ int chunk_tiles(int c) const {
+        if (c < nbig()) return nwarps;
+        const int r = ntl - chunk_start(c);
+        return r < FK_CHUNK_TILES ? r : FK_CHUNK_TILES;
+    }
     // a warp takes a contiguous run of the chunk's units (tile-major), so it rarely changes tile
     __device__ __forceinline__ void next_chunk() {
-        while (left == 0 && (++chunk) * FK_CHUNK_TILES < ntl) {
+        const int nc = nchunks();
+        while (left == 0 && ++chunk < nc) {
             const int total = chunk_tiles(chunk) * nsb, u0 = wid * total / nwarps, u1 = (wid + 1) * total / nwarps;
             left = u1 - u0; tq = u0 / nsb; sbv = u0 - tq * nsb;
         }
     }
     __device__ __forceinline__ bool valid() const { return left > 0; }
-    __device__ __forceinline__ int tile_local() const { return chunk * FK_CHUNK_TILES + tq; }
+    __device__ __forceinline__ int tile_local() const { return chunk_start(chunk) + tq; }
     __device__ __forceinline__ int sb() const { return sbv; }
     __device__ __forceinline__ size_t unit_index() const { return (size_t)(block + tile_local() * grid) * nsb + sbv; }
     __device__ __forceinline__ void advance() {
@@ -437,18 +447,18 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
     Cursor cons; cons.init(W.ntiles, W.nsb, blockIdx.x, gridDim.x, wid, nw);
     bool ok = true;
     if (!pr.valid()) pr.drained();
-    const int nchunks = (cons.ntl + FK_CHUNK_TILES - 1) / FK_CHUNK_TILES;
+    const int nchunks = cons.nchunks();
     if (t == 0 && cons.ntl > 0) {
         // what the epilogue of this lane's first tile needs from global memory (residual, bias) or from slow math (RoPE
         // angle) is fetched now, under the wait for the first unit, instead of after the last one
         const int ct0 = cons.chunk_tiles(0);
-        const int first = (ct0 % nw) == 0 ? (cons.valid() ? cons.tile_local() : -1) : (wid < ct0 ? wid : -1);
+        const int first = ct0 == nw ? (cons.valid() ? cons.tile_local() : -1) : (wid < ct0 ? wid : -1);
         if (first >= 0) epi.prefetch((int)blockIdx.x + first * (int)gridDim.x, g);
     }
     for (int c = 0; c < nchunks; ++c) {
         float *fold = sm.fold + (c & 1) * FK_CHUNK_TILES * FK_STREAM_MAXWARPS * 16;
-        const int ct = cons.chunk_tiles(c);
-        const bool whole = (ct % nw) == 0;          // every warp owns whole tiles of this chunk: no fold, no barrier
+        const int ct = cons.chunk_tiles(c), cs = cons.chunk_start(c);
+        const bool whole = ct == nw;                // every warp owns one whole tile of this chunk: no fold, no barrier
         while (ok && cons.valid() && cons.chunk == c) {
             const int tl = cons.tile_local();
             float acc_lo = 0.0f, acc_hi = 0.0f;
@@ -468,7 +478,7 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
             acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 1); acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 2);
             if (t == 0) {
                 if (whole) epi((int)blockIdx.x + tl * (int)gridDim.x, g, acc_lo, acc_hi);
-                else { float *f = fold + ((tl - c * FK_CHUNK_TILES) * FK_STREAM_MAXWARPS + wid) * 16; f[g] = acc_lo; f[8 + g] = acc_hi; }
+                else { float *f = fold + ((tl - cs) * FK_STREAM_MAXWARPS + wid) * 16; f[g] = acc_lo; f[8 + g] = acc_hi; }
             }
         }
         if (whole) continue;
@@ -479,7 +489,7 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
                 float *f = fold + q * FK_STREAM_MAXWARPS * 16;
                 float lo = 0.0f, hi = 0.0f;
                 for (int w = 0; w < nw; ++w) { lo += f[w * 16 + g]; hi += f[w * 16 + 8 + g]; f[w * 16 + g] = 0.0f; f[w * 16 + 8 + g] = 0.0f; }
-                epi((int)blockIdx.x + (c * FK_CHUNK_TILES + q) * (int)gridDim.x, g, lo, hi);
+                epi((int)blockIdx.x + (cs + q) * (int)gridDim.x, g, lo, hi);
             }
         }
         // the buffer of chunk c is cleared by its folding warps before chunk c+2 writes it: chunk c+1's barrier orders them
