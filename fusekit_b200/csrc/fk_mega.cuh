@@ -316,7 +316,7 @@ struct EpiAny {
 template <int BITS>
 __global__ void __launch_bounds__(FK_MEGA_WARPS * 32, 1)
 k_decode_token(FkState *st, const MegaSlot *ops, int nops, const MegaWeight *wtab_g, int nweights, MegaSync *sync, int max_nsb,
-               int attn_bytes, int barriers_per_launch, unsigned long long *timeline, int dbg) {
+               int attn_bytes, int barriers_per_launch, unsigned long long *timeline) {
     extern __shared__ unsigned char smem_stream[];
     unsigned char *base = (unsigned char *)(((uintptr_t)smem_stream + 127) & ~(uintptr_t)127);
     const MegaLayout L = mega_layout(nweights, max_nsb, BITS, (size_t)attn_bytes);
@@ -377,14 +377,7 @@ k_decode_token(FkState *st, const MegaSlot *ops, int nops, const MegaWeight *wta
             sync_after = false;
         } else if (kind == FK_TASK_SDPA_DECODE) {
             const SdpaArgs &a = op.u.sdpa;
-            for (int rep = 0; rep <= dbg; ++rep) {       // dbg > 0 (tuning): repeat the task to see it with warm instruction caches
-                if (rep) __syncthreads();
-#ifdef FK_MEGA_LEAN
-                mega_sdpa2<128>(st, a, reinterpret_cast<unsigned char *>(attn_scr), timeline, i);
-#else
-                if (a.hd == 128) mega_sdpa2<128>(st, a, reinterpret_cast<unsigned char *>(attn_scr), timeline, i); else mega_sdpa2<64>(st, a, reinterpret_cast<unsigned char *>(attn_scr), timeline, i);
-#endif
-            }
+            if (a.hd == 128) mega_sdpa2<128>(st, a, reinterpret_cast<unsigned char *>(attn_scr), timeline, i); else mega_sdpa2<64>(st, a, reinterpret_cast<unsigned char *>(attn_scr), timeline, i);
         } else if (streams) {
             const TiledW *W;
             if (kind == FK_TASK_LINEAR_RESIDUAL) {
@@ -393,15 +386,11 @@ k_decode_token(FkState *st, const MegaSlot *ops, int nops, const MegaWeight *wta
                 stage_plain<BITS>(sm, a.x, a.k, a.P.W.nsb);
             } else {
                 // the three norm-first tasks differ only in where their arguments sit
-                const uint16_t *x, *nw, *pending, *pending_w; uint16_t *h_out; const float *pend_sum; int h; float eps;
-                if (kind == FK_TASK_RMSNORM_QKV) { const SQkvArgs &a = op.u.qkv; W = &a.P.W; x = a.x; nw = a.norm_w; pending = a.pending; pending_w = a.pending_w; h_out = a.h_out; pend_sum = a.pend_sum; h = a.h; eps = a.eps; }
-                else if (kind == FK_TASK_RMSNORM_GATEUP_ACT) { const SGateUpArgs &a = op.u.gu; W = &a.P.W; x = a.x; nw = a.norm_w; pending = a.pending; pending_w = a.pending_w; h_out = a.h_out; pend_sum = a.pend_sum; h = a.h; eps = a.eps; }
-                else { const SHeadArgs &a = op.u.head; W = &a.P.W; x = a.x; nw = a.norm_w; pending = a.pending; pending_w = a.pending_w; h_out = a.h_out; pend_sum = a.pend_sum; h = a.h; eps = a.eps; }
-#ifdef FK_MEGA_LEAN
-                stage_rmsnorm<BITS>(sm, x, nw, h, W->nsb, eps, nullptr, nullptr, nullptr, nullptr, nullptr);
-#else
-                stage_rmsnorm<BITS>(sm, x, nw, h, W->nsb, eps, pending, pending_w, h_out, nullptr, pend_sum);
-#endif
+                const uint16_t *x, *nw; int h; float eps;
+                if (kind == FK_TASK_RMSNORM_QKV) { const SQkvArgs &a = op.u.qkv; W = &a.P.W; x = a.x; nw = a.norm_w; h = a.h; eps = a.eps; }
+                else if (kind == FK_TASK_RMSNORM_GATEUP_ACT) { const SGateUpArgs &a = op.u.gu; W = &a.P.W; x = a.x; nw = a.norm_w; h = a.h; eps = a.eps; }
+                else { const SHeadArgs &a = op.u.head; W = &a.P.W; x = a.x; nw = a.norm_w; h = a.h; eps = a.eps; }
+                stage_rmsnorm<BITS>(sm, x, nw, h, W->nsb, eps, nullptr, nullptr, nullptr, nullptr, nullptr);     // lists with pending norms or all-reduce inputs are refused at build time
             }
             mega_stamp(timeline, i, 1);
             if (kind == FK_TASK_RMSNORM_QKV && threadIdx.x == 0 && i + 1 < nops) {      // the staging above synchronised the block: the next record is in

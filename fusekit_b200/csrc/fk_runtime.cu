@@ -500,7 +500,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }      // fp32 all-reduced projection + residual
             if (H > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "rmsnorm_qkv: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             if (c->rec) {
-                if (!sinks || sa.pend_sum) return fail(FK_ERR_VALUE, "persistent program: rmsnorm_qkv needs the fused RoPE + cache store and no all-reduce input");
+                if (!sinks || sa.pend_sum || sa.pending) return fail(FK_ERR_VALUE, "persistent program: rmsnorm_qkv needs the fused RoPE + cache store and no pending norm or all-reduce input");
                 MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, w); if (rs) return rs;
                 op.u.qkv = sa; rec_push(c, op); return FK_OK;
             }
@@ -587,7 +587,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "gateup: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             if (c->rec) {
-                if (sa.pend_sum) return fail(FK_ERR_VALUE, "persistent program: no all-reduce inputs");
+                if (sa.pend_sum || sa.pending) return fail(FK_ERR_VALUE, "persistent program: no pending norm or all-reduce inputs");
                 MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, wg); if (rs) return rs;
                 op.u.gu = sa; rec_push(c, op); return FK_OK;
             }
@@ -618,7 +618,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "lm_head: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             if (c->rec) {
-                if (sa.pend_sum || !sa.finalize) return fail(FK_ERR_VALUE, "persistent program: the head must finalise the token itself");
+                if (sa.pend_sum || sa.pending || !sa.finalize) return fail(FK_ERR_VALUE, "persistent program: the head must finalise the token itself and takes no pending norm");
                 MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, w); if (rs) return rs;
                 op.u.head = sa; rec_push(c, op); return FK_OK;
             }
@@ -711,8 +711,8 @@ static fk_status launch_program(Ctx *c, uint64_t id) {
     c->launches++;
     unsigned long long *tl = c->timeline;
     cudaError_t e;
-    if (p.bits == 4) e = cudaLaunchKernelEx(&cfg, k_decode_token<4>, c->state, (const MegaSlot *)p.ops, p.nops, (const MegaWeight *)p.wtab, p.nweights, p.sync, p.max_nsb, p.attn_bytes, p.barriers, tl, c->dbg_mode);
-    else e = cudaLaunchKernelEx(&cfg, k_decode_token<8>, c->state, (const MegaSlot *)p.ops, p.nops, (const MegaWeight *)p.wtab, p.nweights, p.sync, p.max_nsb, p.attn_bytes, p.barriers, tl, c->dbg_mode);
+    if (p.bits == 4) e = cudaLaunchKernelEx(&cfg, k_decode_token<4>, c->state, (const MegaSlot *)p.ops, p.nops, (const MegaWeight *)p.wtab, p.nweights, p.sync, p.max_nsb, p.attn_bytes, p.barriers, tl);
+    else e = cudaLaunchKernelEx(&cfg, k_decode_token<8>, c->state, (const MegaSlot *)p.ops, p.nops, (const MegaWeight *)p.wtab, p.nweights, p.sync, p.max_nsb, p.attn_bytes, p.barriers, tl);
     if (e != cudaSuccess) return fail(FK_ERR_CUDA, "launch of fusekit_decode_token failed: %s", cudaGetErrorString(e));
     return FK_OK;
 }

@@ -200,7 +200,9 @@ fk_status fk_sdpa_decode_noalloc(const void *q, const void *cache_k, const void 
 
 /* tuning aid (no reference counterpart): while `buf` is non-zero the streamed kernels write per-block phase
  * timestamps ([grid][8] u64 nanoseconds: start, dependency met, activations staged, rows done) into it; a graph
- * captured while it is set gives task j the slice starting at entry j * 4096 */
+ * captured while it is set gives task j the slice starting at entry j * 4096.  A persistent program launched while it
+ * is set writes [task][block][8] instead (task start, activations staged, body done, grid barrier passed).
+ * `python -m fusekit_b200.timeline` prints both forms. */
 fk_status fk_debug_timeline(fk_handle h, fk_dptr buf);
 
 /* ---- tensor parallelism (no reference counterpart; NCCL over NVLink) ------ */
