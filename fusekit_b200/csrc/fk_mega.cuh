@@ -123,8 +123,8 @@ __device__ __forceinline__ void mega_stamp(unsigned long long *tl, int op, int s
 }
 
 // keys per participating block and number of participating blocks of a kv head
-__device__ __forceinline__ void mega_attn_split(int kv_len, int &kpc, int &n_active) {
-    const int per = (kv_len + FK_MEGA_PARTS - 1) / FK_MEGA_PARTS;
+__device__ __forceinline__ void mega_attn_split(int kv_len, int &kpc, int &n_active, int parts = FK_MEGA_PARTS) {
+    const int per = (kv_len + parts - 1) / parts;
     kpc = ((per + FK_MEGA_KEYBLOCK - 1) / FK_MEGA_KEYBLOCK) * FK_MEGA_KEYBLOCK;
     n_active = (kv_len + kpc - 1) / kpc;
 }
@@ -160,14 +160,14 @@ __host__ __device__ inline size_t mega_attn2_bytes(int G, int hd) { return hd ==
 // (sdpa_decode.rs:697-715), written to part[(kvh * PARTS + rank)][g][HD + 2]; the last block of a kv head to arrive
 // (ticket) folds the partials into out = T(o / l) (sdpa_decode.rs:992-1046).
 template <int HD>
-__device__ __noinline__ void mega_sdpa2(const FkState *st, const SdpaArgs &a, unsigned char *scr, unsigned long long *tl, int opi) {
+__device__ __noinline__ void sdpa_tiles_block(const FkState *st, const SdpaArgs &a, unsigned char *scr, int kvh, int rank, int parts,
+                                              unsigned long long *tl, int opi) {
     using L = AttLayout<HD>;
     constexpr int DPL = HD / 32, CH = HD / 8;                    // output dims per lane; 16-byte chunks per row
     const int G = a.n_q / a.n_kv, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nthreads = blockDim.x;
-    const int kvh = blockIdx.x / FK_MEGA_PARTS, rank = blockIdx.x % FK_MEGA_PARTS;
     if (kvh >= a.n_kv) return;
-    const int kv_len = (int)min(st->offset + 1u, (uint32_t)a.capacity);
-    int kpc, n_active; mega_attn_split(kv_len, kpc, n_active);
+    const int kv_len = (int)min((a.pos_override >= 0 ? (uint32_t)a.pos_override : st->offset) + 1u, (uint32_t)a.capacity);
+    int kpc, n_active; mega_attn_split(kv_len, kpc, n_active, parts);
     if (rank >= n_active) return;
     const int stride = HD + 2;
     float *qs = reinterpret_cast<float *>(scr + L::q);
@@ -253,7 +253,7 @@ __device__ __noinline__ void mega_sdpa2(const FkState *st, const SdpaArgs &a, un
         const float *w0 = mrg + (item_g * 2) * stride, *w1 = w0 + stride;
         const float M = fmaxf(w0[0], w1[0]);
         const float e0 = w0[0] == -INFINITY ? 0.0f : expf(w0[0] - M), e1 = w1[0] == -INFINITY ? 0.0f : expf(w1[0] - M);
-        float *dst = a.part + ((size_t)(kvh * FK_MEGA_PARTS + rank) * G + item_g) * stride;
+        float *dst = a.part + ((size_t)(kvh * parts + rank) * G + item_g) * stride;
         if (lane == 0) { dst[0] = M; dst[1] = fmaf(w0[1], e0, w1[1] * e1); }
 #pragma unroll
         for (int j = 0; j < DPL; ++j) dst[2 + lane * DPL + j] = fmaf(w0[2 + lane * DPL + j], e0, w1[2 + lane * DPL + j] * e1);
@@ -272,7 +272,7 @@ __device__ __noinline__ void mega_sdpa2(const FkState *st, const SdpaArgs &a, un
     if (!is_last) return;
     // merge weights e^(m_r - M) / L per (partial, head) into shared memory (the score area is free now), then every
     // thread sums its outputs over the partials straight from L2, eight loads in flight at a time
-    const float *src = a.part + (size_t)kvh * FK_MEGA_PARTS * G * stride;
+    const float *src = a.part + (size_t)kvh * parts * G * stride;
     float *wgt = sc;                                            // [n_active][G], n_active * G <= 16 * 8 <= G * 64 floats
     if (tid < G) {
         float M = -INFINITY;
@@ -295,6 +295,29 @@ __device__ __noinline__ void mega_sdpa2(const FkState *st, const SdpaArgs &a, un
         for (int r = 0; r < n_active; ++r) O = fmaf(__ldcg(src + (size_t)(r * G + g) * stride + 2 + d), wgt[r * G + g], O);
         a.out[(kvh * G + g) * HD + d] = f2bf(O);
     }
+}
+
+// The same attention as a kernel of its own (one kernel per task): grid (parts, kv heads), 16 warps per block.  Chosen
+// for long caches, where many blocks per kv head beat the eight of the cluster kernel.
+#define FK_TILES_WARPS 16
+__host__ __device__ inline int sdpa_tiles_parts(int capacity) { const int p = (capacity + FK_MEGA_KEYBLOCK - 1) / FK_MEGA_KEYBLOCK; return p < FK_MEGA_PARTS ? p : FK_MEGA_PARTS; }
+template <int HD>
+__global__ void __launch_bounds__(FK_TILES_WARPS * 32) k_sdpa_tiles(const FkState *st, SdpaArgs a) {
+    extern __shared__ unsigned char smem_stream[];
+    unsigned char *scr = (unsigned char *)(((uintptr_t)smem_stream + 127) & ~(uintptr_t)127);
+    const int parts = (int)gridDim.x, kvh = blockIdx.y, rank = blockIdx.x;
+    pdl_launch_dependents();                     // attention leaves most SMs idle: the next projection may start prefetching now
+    if (threadIdx.x == 0) {                      // every cache row but the newest was written by earlier tokens: pull this block's rows into L2
+        const int kv_len = (int)min((a.pos_override >= 0 ? (uint32_t)a.pos_override : st->offset) + 1u, (uint32_t)a.capacity);
+        int kpc, n_active; mega_attn_split(kv_len, kpc, n_active, parts);
+        if (rank < n_active) {
+            const int k_begin = rank * kpc, k_end = min(kv_len, k_begin + kpc);
+            const size_t off = ((size_t)kvh * a.capacity + k_begin) * HD;
+            l2_prefetch(a.ck + off, (uint32_t)(k_end - k_begin) * HD * 2); l2_prefetch(a.cv + off, (uint32_t)(k_end - k_begin) * HD * 2);
+        }
+    }
+    pdl_wait();
+    sdpa_tiles_block<HD>(st, a, scr, kvh, rank, parts, a.tl, 0);
 }
 
 // the epilogue of whichever streamed task is running (one instance of the streaming loop serves them all)
@@ -377,7 +400,9 @@ k_decode_token(FkState *st, const MegaSlot *ops, int nops, const MegaWeight *wta
             sync_after = false;
         } else if (kind == FK_TASK_SDPA_DECODE) {
             const SdpaArgs &a = op.u.sdpa;
-            if (a.hd == 128) mega_sdpa2<128>(st, a, reinterpret_cast<unsigned char *>(attn_scr), timeline, i); else mega_sdpa2<64>(st, a, reinterpret_cast<unsigned char *>(attn_scr), timeline, i);
+            const int kvh = blockIdx.x / FK_MEGA_PARTS, rank = blockIdx.x % FK_MEGA_PARTS;
+            if (a.hd == 128) sdpa_tiles_block<128>(st, a, reinterpret_cast<unsigned char *>(attn_scr), kvh, rank, FK_MEGA_PARTS, timeline, i);
+            else sdpa_tiles_block<64>(st, a, reinterpret_cast<unsigned char *>(attn_scr), kvh, rank, FK_MEGA_PARTS, timeline, i);
         } else if (streams) {
             const TiledW *W;
             if (kind == FK_TASK_LINEAR_RESIDUAL) {

@@ -90,7 +90,7 @@ struct Ctx {
     uint32_t *pinned = nullptr;                 // host staging for state / history
     std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
     bool pending = false; bool pdl = true; int sm_count = 148;
-    bool use_tiled = true; int stages = FK_STAGES; int prefetch = 1; int force_warps = 0; bool sdpa_cluster = true; int dbg_mode = 0;
+    bool use_tiled = true; int stages = FK_STAGES; int prefetch = 1; int force_warps = 0; bool sdpa_cluster = true; int sdpa_tiles_from = 0; int dbg_mode = 0;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
@@ -137,12 +137,13 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     const char *e = getenv("FK_PDL"); if (e && e[0] == '0') c->pdl = false;
     e = getenv("FK_LAYOUT"); if (e && !strcmp(e, "mlx")) c->use_tiled = false;
     e = getenv("FK_SDPA"); if (e && !strcmp(e, "ticket")) c->sdpa_cluster = false;
+    e = getenv("FK_SDPA_TILES_FROM"); if (e) c->sdpa_tiles_from = atoi(e);      // capacity from which attention uses the tiled kernel (0 = never)
     e = getenv("FK_DBG"); if (e) c->dbg_mode = atoi(e);
     e = getenv("FK_WARPS"); if (e) c->force_warps = atoi(e);
     e = getenv("FK_PREFETCH"); if (e && atoi(e) >= 0 && atoi(e) <= 64) c->prefetch = atoi(e);
-#define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>))
+#define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>)); CU(big_smem(K<16, 8>)); CU(big_smem(K<16, 16>))
     BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head);
-    CU(big_smem(k_decode_token<4>)); CU(big_smem(k_decode_token<8>));
+    CU(big_smem(k_decode_token<4>)); CU(big_smem(k_decode_token<8>)); CU(big_smem(k_sdpa_tiles<64>)); CU(big_smem(k_sdpa_tiles<128>));
     CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
     CU(big_smem(k_linear_residual<4>)); CU(big_smem(k_linear_residual<8>)); CU(big_smem(k_linear_residual<16>));
@@ -272,10 +273,19 @@ extern "C" fk_status fk_weight_synth_rows(fk_handle h, fk_weight wid, int64_t r0
     return FK_OK;
 }
 static fk_status repack(Ctx *c, Weight *dstw, const Weight *a, const Weight *b2) {
-    const int kpu = a->bits == 4 ? 512 : 256;                    // activations per unit
+    const int kpu = unit_k(a->bits);                             // activations per unit
     dstw->ntiles = (int)((dstw->n + 15) / 16); dstw->nsb = (int)((a->k + kpu - 1) / kpu);
-    dstw->unit_bytes = (size_t)dstw->ntiles * dstw->nsb * FK_UNIT_BYTES;
+    dstw->unit_bytes = (size_t)dstw->ntiles * dstw->nsb * unit_vec(a->bits) * 16;
     CU(cudaMalloc(&dstw->units, dstw->unit_bytes));
+    if (a->bits == 16) {
+        const long long tot16 = (long long)dstw->ntiles * dstw->nsb * 256;
+        k_repack_tiled16<<<(unsigned)((tot16 + 255) / 256), 256, 0, c->stream>>>((const uint16_t *)a->w, (const uint16_t *)(b2 ? b2->w : a->w), dstw->units, a->n,
+                                                                                 (int)a->k, dstw->ntiles, dstw->nsb, dstw->rows_kind, dstw->hd, dstw->n_rot);
+        CU(cudaGetLastError());
+        CU(cudaStreamSynchronize(c->stream));
+        dstw->tiled = true;
+        return FK_OK;
+    }
     SrcW sa{a->w, a->s, a->b}, sb{b2 ? b2->w : a->w, b2 ? b2->s : a->s, b2 ? b2->b : a->b};
     const long long tot = (long long)dstw->ntiles * dstw->nsb * FK_UNIT_VEC;
     k_repack_tiled<<<(unsigned)((tot + 255) / 256), 256, 0, c->stream>>>(sa, sb, dstw->units, a->n, (int)a->k, a->bits, dstw->ntiles, dstw->nsb,
@@ -300,7 +310,7 @@ extern "C" fk_status fk_weight_finalize(fk_handle h, fk_weight wid) {
     CTX(h); Weight *w = get_w(c, wid);
     if (!w) return fail(FK_ERR_VALUE, "bad weight id");
     if (w->finalized) return FK_OK;
-    if (c->use_tiled && w->bits != 16) {
+    if (c->use_tiled) {
         fk_status s = repack(c, w, w, nullptr); if (s) return s;
         drop_rows(w);
     } else { w->rows_kind = FK_ROWS_PLAIN; }
@@ -312,7 +322,7 @@ extern "C" fk_status fk_weight_pair(fk_handle h, fk_weight gate, fk_weight up, f
     if (!g || !u || !out || gate == up) return fail(FK_ERR_VALUE, "bad weight ids");
     if (g->finalized || u->finalized) return fail(FK_ERR_STATE, "pair the weights before finalizing them");
     if (g->n != u->n || g->k != u->k || g->bits != u->bits) return fail(FK_ERR_VALUE, "gate and up must have one shape");
-    if (!c->use_tiled || g->bits == 16) return fail(FK_ERR_STATE, "pairing needs the tiled layout (4- or 8-bit weights)");
+    if (!c->use_tiled) return fail(FK_ERR_STATE, "pairing needs the streaming layout");
     Weight p; p.n = 2 * g->n; p.k = g->k; p.bits = g->bits; p.rows_kind = FK_ROWS_GATE_UP;
     fk_status s = repack(c, &p, g, u); if (s) return s;
     p.finalized = true; p.w_bytes = g->w_bytes + u->w_bytes; p.sb_bytes = g->sb_bytes + u->sb_bytes;
@@ -333,7 +343,8 @@ extern "C" fk_status fk_weight_dequant(fk_handle h, fk_weight wid, int64_t row0,
     CU(cudaMalloc(&d, tot * 4));
     if (w->tiled) {
         const long long th = (long long)w->ntiles * w->nsb * 256;
-        k_dequant_tiled<<<(unsigned)((th + 255) / 256), 256, 0, c->stream>>>(w->tview(), which, r0, nrows, d);
+        if (w->bits == 16) k_dequant_tiled16<<<(unsigned)((th + 255) / 256), 256, 0, c->stream>>>(w->tview(), which, r0, nrows, d);
+        else k_dequant_tiled<<<(unsigned)((th + 255) / 256), 256, 0, c->stream>>>(w->tview(), which, r0, nrows, d);
     } else {
         k_dequant<<<(unsigned)((tot + 255) / 256), 256, 0, c->stream>>>(w->w, w->s, w->b, w->k, w->bits, row0, nrows, d);
     }
@@ -431,11 +442,11 @@ static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *nex
     const Shape sh = plan_shape(c, w);
     p->W = w->tview(); p->stages = c->stages; p->dbg_mode = c->dbg_mode;
     p->timeline = c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr;
-    p->next_units = nullptr; p->next_ntiles = p->next_nsb = p->next_grid = p->next_warps = p->next_prefetch = 0;
+    p->next_units = nullptr; p->next_ntiles = p->next_nsb = p->next_grid = p->next_warps = p->next_prefetch = 0; p->next_uvec = FK_UNIT_VEC;
     if (next && c->prefetch > 0) {
         const Shape ns = plan_shape(c, next);
         p->next_units = next->units; p->next_ntiles = next->ntiles; p->next_nsb = next->nsb;
-        p->next_grid = ns.grid; p->next_warps = ns.warps; p->next_prefetch = c->prefetch;
+        p->next_grid = ns.grid; p->next_warps = ns.warps; p->next_prefetch = c->prefetch; p->next_uvec = unit_vec(next->bits);
     }
     return sh;
 }
@@ -444,8 +455,10 @@ static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *nex
     do {                                                                                                                 \
         if ((w)->bits == 4 && (sh).warps == 8) e = launch(c, KERN<4, 8>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);        \
         else if ((w)->bits == 4) e = launch(c, KERN<4, 16>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                     \
-        else if ((sh).warps == 8) e = launch(c, KERN<8, 8>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);                     \
-        else e = launch(c, KERN<8, 16>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                                         \
+        else if ((w)->bits == 8 && (sh).warps == 8) e = launch(c, KERN<8, 8>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);   \
+        else if ((w)->bits == 8) e = launch(c, KERN<8, 16>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                     \
+        else if ((sh).warps == 8) e = launch(c, KERN<16, 8>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);                    \
+        else e = launch(c, KERN<16, 16>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                                        \
     } while (0)
 #define BITS48(bits, CALL) do { if ((bits) == 4) { constexpr int B = 4; CALL; } else { constexpr int B = 8; CALL; } } while (0)
 
@@ -453,6 +466,7 @@ static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *nex
 // ---- recording a task for the persistent kernel instead of launching it
 static fk_status rec_stream(Ctx *c, MegaOp &op, StreamPlan &P, const Weight *w) {
     Recorder *r = c->rec;
+    if (w->bits == 16) return fail(FK_ERR_VALUE, "persistent program: 4- or 8-bit weights only");
     if (r->bits && r->bits != w->bits) return fail(FK_ERR_VALUE, "persistent program: all streamed weights must share one bit width");
     r->bits = w->bits;
     P.W = w->tview(); P.stages = FK_STAGES; P.dbg_mode = 0; P.timeline = nullptr; P.next_units = nullptr;
@@ -543,7 +557,19 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             r->zero.push_back({(void *)a.counter, sizeof(uint32_t) * (size_t)nkv});
             return FK_OK;
         }
-        if (c->sdpa_cluster && (hd != 256 || G <= 2)) {
+        // shared-memory tiles over up to 16 blocks per kv head with a ticket fold: i4 = 3 asks for it (1 = cluster kernel,
+        // 2 = global-partials kernel, 0 = by shape); measured slower than the cluster kernel at 512 and at 4096 keys, so it
+        // is never chosen by default (FK_SDPA_TILES_FROM=<capacity> enables it from that capacity on)
+        const int variant = i[4];
+        if ((hd == 64 || hd == 128) && G * 2 <= FK_TILES_WARPS && (variant == 3 || (variant == 0 && c->sdpa_tiles_from > 0 && cap >= c->sdpa_tiles_from))) {
+            const int parts = sdpa_tiles_parts(cap);
+            const size_t smem = mega_attn2_bytes(G, hd) + 128;
+            const dim3 tgrid(parts, nkv), tblock(FK_TILES_WARPS * 32);
+            if (hd == 64) e = launch(c, k_sdpa_tiles<64>, tgrid, tblock, smem, (const FkState *)c->state, a);
+            else e = launch(c, k_sdpa_tiles<128>, tgrid, tblock, smem, (const FkState *)c->state, a);
+            break;
+        }
+        if (variant != 2 && c->sdpa_cluster && (hd != 256 || G <= 2)) {
             const size_t smem = sdpa_cl_smem_bytes(G, hd);
             const dim3 cgrid(FK_SDPA_CL, nkv), cblock(FK_SDPA_CW * 32);
             if (hd == 64) e = launch_cluster(c, k_sdpa_cluster<64, 8>, cgrid, cblock, smem, FK_SDPA_CL, (const FkState *)c->state, a);

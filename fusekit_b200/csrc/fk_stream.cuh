@@ -28,8 +28,12 @@
 #pragma once
 #include "fk_common.cuh"
 
-#define FK_UNIT_VEC 288                 // uint4 per unit: 8 groups x 32 lanes + 32 scale/bias vectors
+#define FK_UNIT_VEC 288                 // uint4 per unit: 8 groups x 32 lanes + 32 scale/bias vectors (also the ring slot size)
 #define FK_UNIT_BYTES (FK_UNIT_VEC * 16)
+// bf16 weights use the same machinery with units of 16 rows x 128 activations: 8 mma.m16n8k16 A fragments of 32 lanes
+// x 16 bytes = 256 vectors, no scale/bias tail
+__host__ __device__ inline int unit_vec(int bits) { return bits == 16 ? 256 : FK_UNIT_VEC; }
+__host__ __device__ inline int unit_k(int bits) { return bits == 4 ? 512 : bits == 8 ? 256 : 128; }      // activations covered by a unit
 #define FK_STREAM_MAXWARPS 16         // blocks run 8 warps (two blocks per SM) or 16 (one per SM, large activations)
 #define FK_STAGES 2                     // ring depth per warp
 #define FK_WAIT_LIMIT (1u << 24)        // bounded mbarrier wait; on expiry the kernel flags an error and leaves
@@ -96,6 +100,12 @@ __device__ __forceinline__ void imma_us(int (&c)[4], uint32_t a0, uint32_t a1, u
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// D[16x8] += A[16x16] * B[16x8], bf16 operands, fp32 accumulators
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // ------------------------------------------------------------------ shared-memory plan of a streamed kernel
 struct StreamSmem {
     uint64_t *bars;     // [warps * stages]
@@ -107,8 +117,8 @@ struct StreamSmem {
     uint4 *ring;        // [warps * stages * FK_UNIT_VEC]
 };
 __host__ __device__ inline int stream_groups(int nsb) { return nsb * 8; }
-// bytes of staged activation digits per group: 4-bit 3 x 4 x 16, 8-bit 3 x 4 x 8
-__host__ __device__ inline int xs_group_bytes(int bits) { return bits == 4 ? 192 : 96; }
+// bytes of staged activations per group: 4-bit 3 digits x 4 x 16, 8-bit 3 x 4 x 8, bf16 weights: the bf16 values themselves
+__host__ __device__ inline int xs_group_bytes(int bits) { return bits == 4 ? 192 : bits == 8 ? 96 : 32; }      // bf16: a group is one k16 step, 4 lanes x {b0, b1}
 __host__ __device__ inline size_t stream_smem_bytes(int nsb, int stages, int warps, int bits) {
     size_t b = 512 /*bars*/ + 256 /*zero*/ + (size_t)stream_groups(nsb) * 8 + 192 /*red*/ + 2 * 8 * FK_STREAM_MAXWARPS * 16 * 4 /*fold: 2 x FK_CHUNK_TILES tiles*/;
     b = (b + 15) & ~(size_t)15;
@@ -149,6 +159,13 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 }
 template <int BITS>
 __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const float (&f)[8], bool valid) {
+    if (BITS == 16) {       // bf16 weights: the activations are bf16 already; lane t of k16 step s reads {x[2t], x[2t+1]} and {x[2t+8], x[2t+9]}
+        if (!valid) return;
+        uint32_t *dst = reinterpret_cast<uint32_t *>(sm.xs) + (size_t)(blk >> 1) * 8 + (blk & 1);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) dst[2 * t] = (uint32_t)f2bf(f[2 * t]) | ((uint32_t)f2bf(f[2 * t + 1]) << 16);
+        return;
+    }
     float s8 = 0.0f, m8 = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) { s8 += f[i]; m8 = fmaxf(m8, fabsf(f[i])); }
@@ -188,8 +205,8 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
 // zero vectors, padded tail of xs / xsum (k rounded up to whole units)
 template <int BITS>
 __device__ __forceinline__ void stage_pad(const StreamSmem &sm, int k, int nsb) {
-    const int per_group = BITS == 4 ? 64 : 32, groups = stream_groups(nsb), g0 = k / per_group;
-    constexpr int V = BITS == 4 ? 24 : 12;          // uint2 per group
+    const int per_group = BITS == 4 ? 64 : BITS == 8 ? 32 : 16, groups = stream_groups(nsb), g0 = k / per_group;
+    constexpr int V = BITS == 4 ? 24 : BITS == 8 ? 12 : 4;          // uint2 per group
     if (threadIdx.x < 16) sm.zero[threadIdx.x] = make_uint4(0, 0, 0, 0);
     for (int i = g0 * V + threadIdx.x; i < groups * V; i += blockDim.x) sm.xs[i] = make_uint2(0, 0);
     for (int i = g0 + threadIdx.x; i < groups; i += blockDim.x) sm.xsi[i] = make_float2(0.0f, 0.0f);
@@ -302,6 +319,20 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
 template <int BITS>
 __device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     const int g = lane >> 2, t = lane & 3;
+    if (BITS == 16) {
+        // bf16 weights: eight k16 steps; the activations sit in B column 0 (lanes with g == 0), so D[:, 0] = W x lands in the
+        // lanes with t == 0 and the other lanes add zeros
+        float c[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+        const uint2 *z2 = reinterpret_cast<const uint2 *>(sm.zero);
+#pragma unroll
+        for (int s8 = 0; s8 < 8; ++s8) {
+            const uint4 w = u[s8 * 32 + lane];
+            const uint2 b = (g == 0) ? sm.xs[(size_t)(sb * 8 + s8) * 4 + t] : z2[t];
+            mma_bf16(c[s8 & 1], w.x, w.y, w.z, w.w, b.x, b.y);
+        }
+        acc_lo += c[0][0] + c[1][0]; acc_hi += c[0][2] + c[1][2];
+        return;
+    }
     int cc[3][4];                                    // [digit][fragment]: three independent MMA chains
 #pragma unroll
     for (int d = 0; d < 3; ++d) { cc[d][0] = cc[d][1] = cc[d][2] = cc[d][3] = 0; }
@@ -346,7 +377,7 @@ struct StreamPlan {
     TiledW W;
     int stages;             // ring depth per warp
     // the streamed kernel that runs next: its first units are pulled into L2 while this kernel drains
-    const uint4 *next_units; int next_ntiles, next_nsb, next_grid, next_warps, next_prefetch;
+    const uint4 *next_units; int next_ntiles, next_nsb, next_grid, next_warps, next_prefetch, next_uvec;
     unsigned long long *timeline;   // optional [grid][8] phase timestamps (ns) for tuning; null in normal use
     int dbg_mode;                   // tuning experiments: 1 = skip the unit arithmetic (memory only), 3 = recompute one resident unit (arithmetic only); results invalid
 };
@@ -402,19 +433,19 @@ __device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
 __device__ __forceinline__ void prefetch_next(const StreamPlan &p) {
     if (!p.next_units || (threadIdx.x & 31) != 0 || (int)blockIdx.x >= p.next_grid || (int)(threadIdx.x >> 5) >= p.next_warps) return;
     Cursor c; c.init(p.next_ntiles, p.next_nsb, blockIdx.x, p.next_grid, threadIdx.x >> 5, p.next_warps);
-    for (int i = 0; i < p.next_prefetch && c.valid(); ++i) { l2_prefetch(p.next_units + c.unit_index() * FK_UNIT_VEC, FK_UNIT_BYTES); c.advance(); }
+    for (int i = 0; i < p.next_prefetch && c.valid(); ++i) { l2_prefetch(p.next_units + c.unit_index() * p.next_uvec, (uint32_t)p.next_uvec * 16u); c.advance(); }
 }
 
 // Producer side of a warp's ring.  `consumed` counts the units this warp has taken out of the ring since its
 // barriers were initialised: it names the ring slot (consumed % stages) and the barrier phase to wait for.
 struct WarpStream {
-    uint64_t *bars; uint4 *ring; Cursor prod; int stages, consumed; const StreamPlan *plan; bool announced;
+    uint64_t *bars; uint4 *ring; Cursor prod; int stages, consumed, uvec; const StreamPlan *plan; bool announced;
     __device__ __forceinline__ bool valid() const { return prod.valid(); }
     __device__ __forceinline__ unsigned long long *tl() const { return plan->timeline; }
     __device__ __forceinline__ void issue(int stage) {
         if ((threadIdx.x & 31) == 0) {
-            mbar_expect_tx(bars + stage, FK_UNIT_BYTES);
-            bulk_g2s(ring + (size_t)stage * FK_UNIT_VEC, plan->W.units + prod.unit_index() * FK_UNIT_VEC, FK_UNIT_BYTES, bars + stage);
+            mbar_expect_tx(bars + stage, (uint32_t)uvec * 16u);
+            bulk_g2s(ring + (size_t)stage * FK_UNIT_VEC, plan->W.units + prod.unit_index() * uvec, (uint32_t)uvec * 16u, bars + stage);
         }
         prod.advance();
     }
@@ -428,7 +459,7 @@ struct WarpStream {
 __device__ __forceinline__ void stream_begin(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     ws.stages = p.stages; ws.bars = sm.bars + wid * p.stages; ws.ring = sm.ring + (size_t)wid * p.stages * FK_UNIT_VEC;
-    ws.consumed = 0; ws.plan = &p; ws.announced = false;
+    ws.consumed = 0; ws.plan = &p; ws.announced = false; ws.uvec = unit_vec(p.W.bits);
     ws.prod.init(p.W.ntiles, p.W.nsb, blockIdx.x, gridDim.x, wid, blockDim.x >> 5);
     if (lane == 0) { for (int s = 0; s < p.stages; ++s) mbar_init(ws.bars + s, 1); mbar_fence_init(); }
     for (int i = threadIdx.x; i < 2 * FK_CHUNK_TILES * FK_STREAM_MAXWARPS * 16; i += blockDim.x) sm.fold[i] = 0.0f;
@@ -535,6 +566,44 @@ __global__ void k_repack_tiled(SrcW a, SrcW bsrc, uint4 *dst, long long n_src, i
         out.x = sv[0] | (sv[1] << 16); out.y = sv[2] | (sv[3] << 16); out.z = bv[0] | (bv[1] << 16); out.w = bv[2] | (bv[3] << 16);
     }
     dst[idx] = out;
+}
+
+// bf16 rows [n_src][k] -> units of 16 rows x 128 activations as mma.m16n8k16 A fragments: vector (step s, lane (g, t)) =
+// {W[r0][k..k+1], W[r1][k..k+1], W[r0][k+8..k+9], W[r1][k+8..k+9]} with k = sb * 128 + 16 s + 2 t, r0/r1 = tile rows g, g + 8
+__global__ void k_repack_tiled16(const uint16_t *a, const uint16_t *bsrc, uint4 *dst, long long n_src, int k, int ntiles, int nsb,
+                                 int rows_kind, int hd, int n_rot) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)ntiles * nsb * 256) return;
+    const int e = (int)(idx & 255); const long long unit = idx >> 8;
+    const int tile = (int)(unit / nsb), sb = (int)(unit % nsb);
+    const int s8 = e >> 5, lane = e & 31, g = lane >> 2, t = lane & 3;
+    const long long r0 = tile_row(rows_kind, hd, n_rot, tile, g), r1 = tile_row(rows_kind, hd, n_rot, tile, g + 8);
+    const uint16_t *s0 = a, *s1 = (rows_kind == FK_ROWS_GATE_UP) ? bsrc : a;
+    const int kk = sb * 128 + s8 * 16 + 2 * t;
+    auto pair = [&](const uint16_t *src, long long r, int kq) -> uint32_t {
+        if (r >= n_src || kq >= k) return 0u;
+        return (uint32_t)src[r * k + kq] | ((uint32_t)src[r * k + kq + 1] << 16);
+    };
+    dst[idx] = make_uint4(pair(s0, r0, kk), pair(s1, r1, kk), pair(s0, r0, kk + 8), pair(s1, r1, kk + 8));
+}
+__global__ void k_dequant_tiled16(TiledW W, int which, long long row0, long long nrows, float *out) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)W.ntiles * W.nsb * 256) return;
+    const int e = (int)(idx & 255); const long long unit = idx >> 8;
+    const int tile = (int)(unit / W.nsb), sb = (int)(unit % W.nsb);
+    const int s8 = e >> 5, lane = e & 31, g = lane >> 2, t = lane & 3;
+    const uint4 w = W.units[(size_t)unit * 256 + e];
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int r = g + ((q & 1) ? 8 : 0);
+        if (W.rows_kind == FK_ROWS_GATE_UP && ((r >= 8) != (which == 1))) continue;
+        const long long src = tile_row(W.rows_kind, W.hd, W.n_rot, tile, r);
+        if (src < row0 || src >= row0 + nrows) continue;
+        const int kk = sb * 128 + s8 * 16 + 2 * t + ((q >= 2) ? 8 : 0);
+        if (kk < W.k) out[(src - row0) * W.k + kk] = bf_lo(words[q]);
+        if (kk + 1 < W.k) out[(src - row0) * W.k + kk + 1] = bf_hi(words[q]);
+    }
 }
 
 // fp32 dequantised values scattered back to source order: out[(row - row0) * k + col] for rows of matrix `which`

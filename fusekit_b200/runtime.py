@@ -104,7 +104,7 @@ class Runtime:
 
     @property
     def tiled(self) -> bool:
-        """True when 4/8-bit weights are repacked into the streaming layout (default)."""
+        """True when weights are repacked into the streaming layout (default)."""
         import os
         return os.environ.get("FK_LAYOUT", "") != "mlx"
 
@@ -276,7 +276,7 @@ class DecodeEngine:
     def _finish_weight(self, name: str, wid: int):
         """Choose the tile row order the consuming kernel wants, then freeze the weight."""
         s, rt = self.spec, self.rt
-        paired = rt.tiled and s.bits != 16
+        paired = rt.tiled
         if name.endswith(".qkv") and s.arch == "qwen2" and paired:
             rt.weight_set_rows(wid, 1, s.head_dim, (self.nq + self.nkv) * s.head_dim)
         if paired and (name.endswith(".gate") or name.endswith(".up")):

@@ -32,12 +32,12 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
          want_logits: bool = False) -> dict:
     """Build the v2 task graph of one decode step for `spec` (one tensor-parallel rank of it).
 
-    `fused_weights`: 4/8-bit weights in the streaming layout (gate/up paired, residual add after an all-reduce fused
-    into the next norm-first kernel); False describes the generic kernels (bf16 weights)."""
+    `fused_weights`: weights in the streaming layout (gate/up paired, residual add after an all-reduce fused into the next
+    norm-first kernel); False describes the generic kernels on MLX-layout rows."""
     s, hd, H = spec, spec.head_dim, spec.hidden
     nq, nkv, inter, vocab = s.n_q // tp_size, s.n_kv // tp_size, s.inter // tp_size, s.vocab // tp_size
     tp = tp_size > 1
-    fused = fused_weights and s.bits != 16
+    fused = fused_weights
     tasks: list[dict] = []
 
     def add(kind, layer, bufs, iargs, fargs=()):

@@ -21,7 +21,7 @@ def dev_weight(rt, w: O.QWeight, rope_rows=None, finalize=True) -> int:
         rt.weight_upload_rows(wid, 0, w.dense)
     else:
         rt.weight_upload_rows(wid, 0, w.packed, w.scales, w.biases)
-    if rope_rows and w.bits != 16 and rt.tiled:
+    if rope_rows and rt.tiled:
         rt.weight_set_rows(wid, 1, *rope_rows)
     if finalize:
         rt.weight_finalize(wid)
@@ -29,7 +29,7 @@ def dev_weight(rt, w: O.QWeight, rope_rows=None, finalize=True) -> int:
 
 
 def gateup_bufs(rt, wg: O.QWeight, wu: O.QWeight) -> dict:
-    if wg.bits != 16 and rt.tiled:
+    if rt.tiled:
         return {2: rt.weight_pair(dev_weight(rt, wg, finalize=False), dev_weight(rt, wu, finalize=False)), 3: 0}
     return {2: dev_weight(rt, wg), 3: dev_weight(rt, wu)}
 
@@ -134,9 +134,14 @@ def test_rmsnorm_qkv_rope_store(runtime, bits, h, nq, nkv, hd, pos, cap):
     assert_close_bf16(rt.download(ko, (nkv * hd,), np.uint16), y[nq * hd:(nq + nkv) * hd], "raw k")
 
 
-@pytest.mark.parametrize("nq,nkv,hd", [(14, 2, 64), (28, 4, 128), (8, 4, 256), (5, 1, 128), (1, 1, 64)])
-@pytest.mark.parametrize("pos,cap", [(0, 64), (62, 64), (63, 64), (64, 200), (136, 200), (199, 200), (1000, 96)])
-def test_sdpa_decode(runtime, nq, nkv, hd, pos, cap):
+@pytest.mark.parametrize("variant", [0, 2, 3])      # by shape (cluster / tiles), global partials + ticket, shared-memory tiles + ticket
+@pytest.mark.parametrize("nq,nkv,hd", [(14, 2, 64), (28, 4, 128), (8, 4, 256), (5, 1, 128), (1, 1, 64), (40, 8, 128)])
+@pytest.mark.parametrize("pos,cap", [(0, 64), (62, 64), (63, 64), (64, 200), (136, 200), (199, 200), (1000, 96), (1030, 2100), (3000, 2100)])
+def test_sdpa_decode(runtime, nq, nkv, hd, pos, cap, variant):
+    if variant == 3 and hd == 256:
+        pytest.skip("the tiled kernel covers head_dim 64 and 128")
+    if cap > 1000 and (nq, nkv) not in ((28, 4), (40, 8)):
+        pytest.skip("long caches are exercised on the benchmark shapes only")
     rt = runtime
     q = normal(f"sq{nq}", nq * hd)
     ck, cv = normal(f"sk{hd}", nkv * cap * hd), normal(f"sv{hd}", nkv * cap * hd)
@@ -146,11 +151,11 @@ def test_sdpa_decode(runtime, nq, nkv, hd, pos, cap):
     chunks = (cap + 31) // 32
     out, part, cnt = rt.alloc(nq * hd * 2), rt.alloc(nq * chunks * (hd + 2) * 4), rt.alloc(nkv * 4)
     task = T(N.TASK_SDPA_DECODE, 0, {0: rt.to_device(q), 1: rt.to_device(ck), 2: rt.to_device(cv), 3: out, 4: part, 5: cnt},
-             [nq, nkv, hd, cap], [scale])
+             [nq, nkv, hd, cap, variant], [scale])
     rt.state_set(0, pos)
     rt.launch(task)
     got = rt.download(out, (nq * hd,), np.uint16)
-    assert_close_bf16(got, want, f"sdpa kv_len {kv_len}")
+    assert_close_bf16(got, want, f"sdpa kv_len {kv_len} variant {variant}")
     rt.launch(task)                                                   # the ticket counters reset themselves
     assert np.array_equal(rt.download(out, (nq * hd,), np.uint16), got)
     assert not rt.download(cnt, (nkv,), np.uint32).any()

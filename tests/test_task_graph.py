@@ -31,7 +31,7 @@ def _fake_engine(spec, world=1, rank=0, fused=True):
     e = DecodeEngine.__new__(DecodeEngine)
     e.spec, e.capacity, e.rank, e.world, e.want_logits = spec, 1024, rank, world, False
     wn = {p[0] for p in linear_plan(spec, rank, world)}
-    if fused and spec.bits != 16:
+    if fused:
         wn = {n for n in wn if not n.endswith((".gate", ".up"))} | {f"layers.{l}.gateup" for l in range(spec.n_layers)}
     vn = {p[0] for p in vector_plan(spec, rank, world) if not p[0].endswith(("q_bias", "k_bias", "v_bias"))}
     if spec.arch == "qwen2":
