@@ -303,8 +303,8 @@ __device__ __noinline__ void sdpa_tiles_block(const FkState *st, const SdpaArgs 
 __host__ __device__ inline int sdpa_tiles_parts(int capacity) { const int p = (capacity + FK_MEGA_KEYBLOCK - 1) / FK_MEGA_KEYBLOCK; return p < FK_MEGA_PARTS ? p : FK_MEGA_PARTS; }
 template <int HD>
 __global__ void __launch_bounds__(FK_TILES_WARPS * 32) k_sdpa_tiles(const FkState *st, SdpaArgs a) {
-    extern __shared__ unsigned char smem_stream[];
-    unsigned char *scr = (unsigned char *)(((uintptr_t)smem_stream + 127) & ~(uintptr_t)127);
+    extern __shared__ __align__(128) unsigned char smem_stream[];
+    unsigned char *scr = smem_stream;
     const int parts = (int)gridDim.x, kvh = blockIdx.y, rank = blockIdx.x;
     pdl_launch_dependents();                     // attention leaves most SMs idle: the next projection may start prefetching now
     if (threadIdx.x == 0) {                      // every cache row but the newest was written by earlier tokens: pull this block's rows into L2
@@ -340,8 +340,8 @@ template <int BITS>
 __global__ void __launch_bounds__(FK_MEGA_WARPS * 32, 1)
 k_decode_token(FkState *st, const MegaSlot *ops, int nops, const MegaWeight *wtab_g, int nweights, MegaSync *sync, int max_nsb,
                int attn_bytes, int barriers_per_launch, unsigned long long *timeline) {
-    extern __shared__ unsigned char smem_stream[];
-    unsigned char *base = (unsigned char *)(((uintptr_t)smem_stream + 127) & ~(uintptr_t)127);
+    extern __shared__ __align__(128) unsigned char smem_stream[];
+    unsigned char *base = smem_stream;
     const MegaLayout L = mega_layout(nweights, max_nsb, BITS, (size_t)attn_bytes);
     MegaSlot *opbuf = reinterpret_cast<MegaSlot *>(base);
     volatile MegaCtl *ctl = reinterpret_cast<volatile MegaCtl *>(base + 2 * FK_MEGA_OP_BYTES);

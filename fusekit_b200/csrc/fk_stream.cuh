@@ -127,18 +127,20 @@ __host__ __device__ inline size_t stream_smem_bytes(int nsb, int stages, int war
     b += (size_t)warps * stages * FK_UNIT_BYTES;
     return b + 128;
 }
+// `base` is the kernel's dynamic shared memory (declared 128-byte aligned).  Offsets only, no integer casts: the compiler
+// must keep seeing shared-memory pointers, or every access becomes a generic load with 64-bit address arithmetic.
 __device__ __forceinline__ StreamSmem stream_carve(unsigned char *base, int nsb, int stages, int bits) {
     StreamSmem s;
-    base = (unsigned char *)(((uintptr_t)base + 127) & ~(uintptr_t)127);
-    s.bars = (uint64_t *)base; base += 512;
-    s.zero = (uint4 *)base; base += 256;
-    s.xsi = (float2 *)base; base += (size_t)stream_groups(nsb) * 8;
-    s.red = (float *)base; base += 192;
-    s.fold = (float *)base; base += 2 * 8 * FK_STREAM_MAXWARPS * 16 * 4;
-    base = (unsigned char *)(((uintptr_t)base + 15) & ~(uintptr_t)15);
-    s.xs = (uint2 *)base; base += (size_t)stream_groups(nsb) * xs_group_bytes(bits);
-    base = (unsigned char *)(((uintptr_t)base + 127) & ~(uintptr_t)127);
-    s.ring = (uint4 *)base;
+    size_t o = 0;
+    s.bars = (uint64_t *)(base + o); o += 512;
+    s.zero = (uint4 *)(base + o); o += 256;
+    s.xsi = (float2 *)(base + o); o += (size_t)stream_groups(nsb) * 8;
+    s.red = (float *)(base + o); o += 192;
+    s.fold = (float *)(base + o); o += 2 * 8 * FK_STREAM_MAXWARPS * 16 * 4;
+    o = (o + 15) & ~(size_t)15;
+    s.xs = (uint2 *)(base + o); o += (size_t)stream_groups(nsb) * xs_group_bytes(bits);
+    o = (o + 127) & ~(size_t)127;
+    s.ring = (uint4 *)(base + o);
     return s;
 }
 
@@ -316,23 +318,23 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
 }
 
 // ------------------------------------------------------------------ one unit: 16 rows x 8 groups
-template <int BITS>
-__device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
+// bf16 weights: eight k16 steps; the activations sit in B column 0 (lanes with g == 0), so D[:, 0] = W x lands in the lanes
+// with t == 0 and the other lanes add zeros
+__device__ __forceinline__ void unit_compute_bf16(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     const int g = lane >> 2, t = lane & 3;
-    if (BITS == 16) {
-        // bf16 weights: eight k16 steps; the activations sit in B column 0 (lanes with g == 0), so D[:, 0] = W x lands in the
-        // lanes with t == 0 and the other lanes add zeros
-        float c[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
-        const uint2 *z2 = reinterpret_cast<const uint2 *>(sm.zero);
+    float c[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+    const uint2 *z2 = reinterpret_cast<const uint2 *>(sm.zero);
 #pragma unroll
-        for (int s8 = 0; s8 < 8; ++s8) {
-            const uint4 w = u[s8 * 32 + lane];
-            const uint2 b = (g == 0) ? sm.xs[(size_t)(sb * 8 + s8) * 4 + t] : z2[t];
-            mma_bf16(c[s8 & 1], w.x, w.y, w.z, w.w, b.x, b.y);
-        }
-        acc_lo += c[0][0] + c[1][0]; acc_hi += c[0][2] + c[1][2];
-        return;
+    for (int s8 = 0; s8 < 8; ++s8) {
+        const uint4 w = u[s8 * 32 + lane];
+        const uint2 b = (g == 0) ? sm.xs[(size_t)(sb * 8 + s8) * 4 + t] : z2[t];
+        mma_bf16(c[s8 & 1], w.x, w.y, w.z, w.w, b.x, b.y);
     }
+    acc_lo += c[0][0] + c[1][0]; acc_hi += c[0][2] + c[1][2];
+}
+template <int BITS>
+__device__ __forceinline__ void unit_compute_q(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
+    const int g = lane >> 2, t = lane & 3;
     int cc[3][4];                                    // [digit][fragment]: three independent MMA chains
 #pragma unroll
     for (int d = 0; d < 3; ++d) { cc[d][0] = cc[d][1] = cc[d][2] = cc[d][3] = 0; }
@@ -369,6 +371,12 @@ __device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &s
     acc_lo = fmaf(s01, c[1] * i1, acc_lo); acc_lo = fmaf(b01, X1, acc_lo);
     acc_hi = fmaf(s10, c[2] * i0, acc_hi); acc_hi = fmaf(b10, X0, acc_hi);
     acc_hi = fmaf(s11, c[3] * i1, acc_hi); acc_hi = fmaf(b11, X1, acc_hi);
+}
+
+template <int BITS>
+__device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
+    if constexpr (BITS == 16) unit_compute_bf16(u, sm, sb, lane, acc_lo, acc_hi);
+    else unit_compute_q<BITS>(u, sm, sb, lane, acc_lo, acc_hi);
 }
 
 // ------------------------------------------------------------------ per-warp unit stream
@@ -666,7 +674,7 @@ struct EpiLinear {
 };
 template <int BITS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st, SLinArgs a) {
-    extern __shared__ unsigned char smem_stream[];
+    extern __shared__ __align__(128) unsigned char smem_stream[];
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
@@ -736,7 +744,7 @@ struct EpiQkv {
 };
 template <int BITS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkState *st, SQkvArgs a) {
-    extern __shared__ unsigned char smem_stream[];
+    extern __shared__ __align__(128) unsigned char smem_stream[];
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
@@ -780,7 +788,7 @@ struct EpiGateUp {
 };
 template <int BITS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st, SGateUpArgs a) {
-    extern __shared__ unsigned char smem_stream[];
+    extern __shared__ __align__(128) unsigned char smem_stream[];
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
@@ -827,7 +835,7 @@ struct EpiHead {
 // (final_rmsnorm_lm_head.rs:250-326; msl.rs:1805-1838); the last block folds the per-block keys and advances the state
 template <int BITS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, SHeadArgs a) {
-    extern __shared__ unsigned char smem_stream[];
+    extern __shared__ __align__(128) unsigned char smem_stream[];
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     __shared__ unsigned long long wbest[WARPS]; __shared__ int is_last;
     stamp(a.P, 0);
