@@ -400,20 +400,23 @@ __device__ __forceinline__ void stamp(const StreamPlan &p, int slot) {
 // of up to FK_CHUNK_TILES tiles whose units (tile, super-block) are dealt to the warps in contiguous runs, so every
 // warp gets the same number of units (+-1) and a tile's K range is shared by the warps of one block only.
 struct Cursor {
-    int nsb, ntl, nwarps, wid, block, grid, nb; // ntl: tiles of this block; nb: chunks of one tile per warp
+    int nsb, ntl, nwarps, lw, wid, block, grid, nb; // ntl: tiles of this block; lw: log2(nwarps); nb: chunks of one tile per warp
     int chunk, tq, sbv, left;                   // current chunk, tile inside the chunk, super-block, units left in the chunk
+    float inv_nsb;
     __device__ __forceinline__ void init(int ntiles, int nsb_, int block_, int grid_, int wid_, int nwarps_) {
         nsb = nsb_; nwarps = nwarps_; wid = wid_; block = block_; grid = grid_;
+        lw = 31 - __clz(nwarps_);               // blocks have 8 or 16 warps
+        inv_nsb = __frcp_rn((float)nsb_);
         ntl = block_ < ntiles ? (ntiles - block_ + grid_ - 1) / grid_ : 0;
-        nb = ntl / nwarps_;
+        nb = ntl >> lw;
         chunk = -1; left = 0;
         next_chunk();
     }
     __device__ __forceinline__ int nbig() const { return nb; }
-    __device__ __forceinline__ int nchunks() const { return nbig() + (ntl - nbig() * nwarps + FK_CHUNK_TILES - 1) / FK_CHUNK_TILES; }
-    __device__ __forceinline__ int chunk_start(int c) const { const int b = nbig(); return c < b ? c * nwarps : b * nwarps + (c - b) * FK_CHUNK_TILES; }
+    __device__ __forceinline__ int nchunks() const { return nb + (ntl - (nb << lw) + FK_CHUNK_TILES - 1) / FK_CHUNK_TILES; }
+    __device__ __forceinline__ int chunk_start(int c) const { return c < nb ? (c << lw) : (nb << lw) + (c - nb) * FK_CHUNK_TILES; }
     __device__ __forceinline__ int chunk_tiles(int c) const {
-        if (c < nbig()) return nwarps;
+        if (c < nb) return nwarps;
         const int r = ntl - chunk_start(c);
         return r < FK_CHUNK_TILES ? r : FK_CHUNK_TILES;
     }
@@ -421,14 +424,19 @@ struct Cursor {
     __device__ __forceinline__ void next_chunk() {
         const int nc = nchunks();
         while (left == 0 && ++chunk < nc) {
-            const int total = chunk_tiles(chunk) * nsb, u0 = wid * total / nwarps, u1 = (wid + 1) * total / nwarps;
-            left = u1 - u0; tq = u0 / nsb; sbv = u0 - tq * nsb;
+            if (chunk < nb) { left = nsb; tq = wid; sbv = 0; continue; }        // one whole tile per warp
+            const int total = chunk_tiles(chunk) * nsb, u0 = (wid * total) >> lw, u1 = ((wid + 1) * total) >> lw;
+            left = u1 - u0;
+            tq = (int)(((float)u0 + 0.5f) * inv_nsb);       // u0 / nsb, exact: u0 < 2^12 and the quotient is >= 0.5 / nsb away from an integer
+            sbv = u0 - tq * nsb;
         }
     }
     __device__ __forceinline__ bool valid() const { return left > 0; }
     __device__ __forceinline__ int tile_local() const { return chunk_start(chunk) + tq; }
     __device__ __forceinline__ int sb() const { return sbv; }
     __device__ __forceinline__ size_t unit_index() const { return (size_t)(block + tile_local() * grid) * nsb + sbv; }
+    // units of the current tile left in this warp's run
+    __device__ __forceinline__ int run() const { const int r = nsb - sbv; return r < left ? r : left; }
     __device__ __forceinline__ void advance() {
         if (++sbv >= nsb) { sbv = 0; ++tq; }
         if (--left == 0) next_chunk();
@@ -485,6 +493,12 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5, g = lane >> 2, t = lane & 3;
     Cursor cons; cons.init(W.ntiles, W.nsb, blockIdx.x, gridDim.x, wid, nw);
     bool ok = true;
+#ifdef FK_WARPSTAMP
+    unsigned long long *wtl = (pr.tl() && blockIdx.x < 32 && wid < 8) ? pr.tl() + 2560 + (blockIdx.x * 8 + wid) * 4 : nullptr;
+    auto wstamp = [&](int k) { if (wtl && lane == 0) { unsigned long long tt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tt)); wtl[k] = tt; } };
+    bool first_done = false;
+    wstamp(0);
+#endif
     if (!pr.valid()) pr.drained();
     const int nchunks = cons.nchunks();
     if (t == 0 && cons.ntl > 0) {
@@ -501,10 +515,13 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
         while (ok && cons.valid() && cons.chunk == c) {
             const int tl = cons.tile_local();
             float acc_lo = 0.0f, acc_hi = 0.0f;
-            while (ok && cons.valid() && cons.chunk == c && cons.tile_local() == tl) {
+            for (int n = cons.run(); n > 0 && ok; --n) {    // the units of tile tl in this warp's run
                 const int s = pr.consumed & (FK_STAGES - 1);
                 if (dbg_mode != 3 && !mbar_wait(pr.bars + s, (uint32_t)(pr.consumed >> 1) & 1u)) { ok = false; break; }
                 if (pr.consumed == 0) stamp_raw(pr.tl(), 6);
+#ifdef FK_WARPSTAMP
+                if (!first_done) { wstamp(1); first_done = true; }
+#endif
                 if (dbg_mode == 0) unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
                 else if (dbg_mode == 3) { if (pr.valid()) pr.prod.advance(); ++pr.consumed; cons.advance(); unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, 0, lane, acc_lo, acc_hi); continue; }
                 __syncwarp();
@@ -522,6 +539,9 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
         }
         if (whole) continue;
         if (c == 0) stamp_raw(pr.tl(), 7);
+#ifdef FK_WARPSTAMP
+        if (c == 0) wstamp(2);
+#endif
         __syncthreads();
         for (int q = wid; q < ct; q += nw) {                  // fold tile q of the chunk in warp order, then its epilogue
             if (t == 0) {
@@ -532,6 +552,9 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
             }
         }
         // the buffer of chunk c is cleared by its folding warps before chunk c+2 writes it: chunk c+1's barrier orders them
+#ifdef FK_WARPSTAMP
+        if (c == 0) wstamp(3);
+#endif
     }
     return ok;
 }
