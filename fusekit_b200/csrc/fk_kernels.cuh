@@ -589,6 +589,193 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_cluster(const FkState 
     sd_stamp(a.tl, 6);
 }
 
+// ---------------------------------------------------------------- tensor-core cluster SDPA
+// Same split as k_sdpa_cluster (cluster of 8 CTAs per kv head, contiguous key ranges, online softmax per warp, warp ->
+// CTA -> cluster fold), but a warp iteration takes 16 keys on mma.sync.m16n8k16 (bf16, fp32 accumulate):
+//   S[head][key]   = q K^T      -- A = q (heads padded to 16 rows, kept in registers), B = K rows straight from global
+//                                  (a lane owns 32 contiguous dims of its key; the dims are relabelled identically in A)
+//   O^T[dim][head] = V^T P^T    -- A = V^T through ldmatrix.trans from a per-warp shared-memory tile, B = P^T, which is
+//                                  exactly the layout S came out in; p is split into two bf16 terms (hi + lo), so the
+//                                  products carry 16 significant bits of p (sdpa_decode.rs:697-715 accumulates p*v in fp32)
+// A lane then handles one head instead of looping over the group: ~150 instructions per 16 keys instead of ~2200.
+#define FK_SDPA_MK 16
+__device__ __forceinline__ void mma_bf16_f32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return (uint32_t)f2bf(lo) | ((uint32_t)f2bf(hi) << 16); }
+template <int HD> struct SdpaMmaLayout {
+    static constexpr int QSTRIDE = HD * 2 + 16;                  // bytes per q row (bf16)
+    static constexpr int VSTRIDE = HD * 2 + 16;                  // bytes per V tile row: ldmatrix rows hit distinct banks
+    static constexpr int WTILE = FK_SDPA_MK * VSTRIDE;           // bytes of a warp's V tile; later its [G][HD+2] fp32 partial
+    __host__ __device__ static constexpr int q() { return 0; }
+    __host__ __device__ static constexpr int tiles() { return 8 * QSTRIDE; }
+    __host__ __device__ static constexpr int cpart() { return tiles() + FK_SDPA_CW * WTILE; }
+    __host__ __device__ static constexpr int wexp(int G) { return cpart() + G * (HD + 2) * 4; }
+    __host__ __device__ static constexpr int bytes(int G) { return wexp(G) + FK_SDPA_CW * G * 4 + 64; }
+};
+__host__ __device__ inline size_t sdpa_mma_smem_bytes(int G, int hd) { return hd == 128 ? SdpaMmaLayout<128>::bytes(G) : SdpaMmaLayout<64>::bytes(G); }
+template <int HD>
+__global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st, SdpaArgs a) {
+    extern __shared__ __align__(128) unsigned char smem_att[];
+    using L = SdpaMmaLayout<HD>;
+    cg::cluster_group cluster = cg::this_cluster();
+    constexpr int NT = FK_SDPA_CW * 32, KS = HD / 16, KV4 = HD / 32;      // k16 steps over head_dim; uint4 per lane per key row
+    const int G = a.n_q / a.n_kv, kvh = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int rank = (int)cluster.block_rank(), CL = (int)cluster.num_blocks();
+    const int stride = HD + 2;
+    unsigned char *qs = smem_att + L::q();
+    unsigned char *vt = smem_att + L::tiles() + wid * L::WTILE;                  // this warp's tile
+    float *cpart = reinterpret_cast<float *>(smem_att + L::cpart());          // [G][HD+2], read by the other CTAs of the cluster
+    float *wexp = reinterpret_cast<float *>(smem_att + L::wexp(G));           // [CW][G]
+    sd_stamp(a.tl, 0);
+    pdl_launch_dependents();
+    const uint32_t pos = a.pos_override >= 0 ? (uint32_t)a.pos_override : st->offset;
+    const int kv_len = (int)min(pos + 1u, (uint32_t)a.capacity);
+    const int kpc = ((kv_len + CL * FK_SDPA_MK - 1) / (CL * FK_SDPA_MK)) * FK_SDPA_MK;
+    const int k_begin = rank * kpc, k_end = min(kv_len, k_begin + kpc);
+    const uint16_t *K = a.ck + (size_t)kvh * a.capacity * HD, *V = a.cv + (size_t)kvh * a.capacity * HD;
+    if (tid == 0 && k_begin < k_end) {           // every row but the newest predates the QKV kernel in flight: warm L2 meanwhile
+        const uint32_t bytes = (uint32_t)(k_end - k_begin) * HD * 2;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(K + (size_t)k_begin * HD), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(V + (size_t)k_begin * HD), "r"(bytes) : "memory");
+    }
+    pdl_wait();
+    for (int i = tid; i < G * HD / 2; i += NT) {             // q as bf16 rows
+        const int gg = (2 * i) / HD, d = 2 * i - gg * HD;
+        *reinterpret_cast<uint32_t *>(qs + gg * L::QSTRIDE + d * 2) = __ldcg(reinterpret_cast<const uint32_t *>(a.q + kvh * G * HD) + i);
+    }
+    __syncthreads();
+    sd_stamp(a.tl, 1);
+    uint32_t aq[KS][2];                                      // A fragments of q: row g (rows >= G and 8..15 are zero)
+#pragma unroll
+    for (int s = 0; s < KS; ++s) {
+        const uint32_t *qp = reinterpret_cast<const uint32_t *>(qs + g * L::QSTRIDE + t * (HD / 2)) + 2 * s;      // the lane's HD/4 dims are contiguous
+        aq[s][0] = g < G ? qp[0] : 0u; aq[s][1] = g < G ? qp[1] : 0u;
+    }
+    float m = -INFINITY, l = 0.0f, oacc[KS][4];
+#pragma unroll
+    for (int mb = 0; mb < KS; ++mb) { oacc[mb][0] = oacc[mb][1] = oacc[mb][2] = oacc[mb][3] = 0.0f; }
+    for (int kb = k_begin + wid * FK_SDPA_MK; kb < k_end; kb += FK_SDPA_CW * FK_SDPA_MK) {
+        uint4 kr[2][KV4];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+            const int key = min(kb + 8 * nb + g, k_end - 1);                  // clamped: masked below
+            const uint4 *kp = reinterpret_cast<const uint4 *>(K + (size_t)key * HD + t * (HD / 4));
+#pragma unroll
+            for (int c = 0; c < KV4; ++c) kr[nb][c] = __ldcg(kp + c);
+        }
+        // V rows of the block into this warp's tile (rows past the end are zero)
+#pragma unroll
+        for (int i = 0; i < FK_SDPA_MK * (HD / 8) / 32; ++i) {
+            const int idx = lane + 32 * i, row = idx / (HD / 8), c = idx - row * (HD / 8);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (kb + row < k_end) v = __ldcg(reinterpret_cast<const uint4 *>(V + (size_t)(kb + row) * HD) + c);
+            *reinterpret_cast<uint4 *>(vt + row * L::VSTRIDE + c * 16) = v;
+        }
+        float sacc[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+            sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.0f;
+#pragma unroll
+            for (int s = 0; s < KS; ++s) {
+                const uint4 q4 = kr[nb][s >> 1];
+                const uint32_t w0 = (s & 1) ? q4.z : q4.x, w1 = (s & 1) ? q4.w : q4.y;
+                mma_bf16_f32(sacc[nb], aq[s][0], 0u, aq[s][1], 0u, w0, w1);
+            }
+        }
+        // lane (g, t): scores of head g for keys kb + {2t, 2t+1, 8+2t, 9+2t}
+        float sv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int key = kb + (i >> 1) * 8 + 2 * t + (i & 1);
+            sv[i] = key < k_end ? sacc[i >> 1][i & 1] * a.scale : -INFINITY;
+        }
+        float mb4 = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+        mb4 = fmaxf(mb4, __shfl_xor_sync(0xffffffffu, mb4, 1)); mb4 = fmaxf(mb4, __shfl_xor_sync(0xffffffffu, mb4, 2));
+        const float mn = fmaxf(m, mb4);                                       // finite: the block holds a valid key
+        const float alpha = expf(m - mn);
+        float p[4], ls = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { p[i] = sv[i] == -INFINITY ? 0.0f : expf(sv[i] - mn); ls += p[i]; }
+        ls += __shfl_xor_sync(0xffffffffu, ls, 1); ls += __shfl_xor_sync(0xffffffffu, ls, 2);
+        l = fmaf(l, alpha, ls); m = mn;
+        // the O^T accumulators of this lane belong to heads 2t and 2t+1
+        const float al0 = __shfl_sync(0xffffffffu, alpha, (2 * t) * 4), al1 = __shfl_sync(0xffffffffu, alpha, (2 * t + 1) * 4);
+#pragma unroll
+        for (int mb = 0; mb < KS; ++mb) { oacc[mb][0] *= al0; oacc[mb][1] *= al1; oacc[mb][2] *= al0; oacc[mb][3] *= al1; }
+        // P^T as the B operand (k = key, n = head): hi + lo bf16 terms of p
+        const uint32_t ph0 = pack_bf16(p[0], p[1]), ph1 = pack_bf16(p[2], p[3]);
+        const uint32_t pl0 = pack_bf16(p[0] - bf_lo(ph0), p[1] - bf_hi(ph0)), pl1 = pack_bf16(p[2] - bf_lo(ph1), p[3] - bf_hi(ph1));
+        __syncwarp();                                                         // the tile is written
+        const int mat = lane >> 3, r = lane & 7;
+        const uint32_t vaddr = (uint32_t)__cvta_generic_to_shared(vt + ((mat >> 1) * 8 + r) * L::VSTRIDE + (mat & 1) * 16);
+#pragma unroll
+        for (int mb = 0; mb < KS; ++mb) {
+            uint32_t a0, a1, a2, a3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(vaddr + mb * 32));
+            mma_bf16_f32(oacc[mb], a0, a1, a2, a3, ph0, ph1);
+            mma_bf16_f32(oacc[mb], a0, a1, a2, a3, pl0, pl1);
+        }
+        __syncwarp();                                                         // before the next block overwrites the tile
+    }
+    sd_stamp(a.tl, 2);
+    // the warp's partial (m, l, o[HD]) per head goes where its tile was
+    float *wp = reinterpret_cast<float *>(vt);
+    if (t == 0 && g < G) { wp[g * stride] = m; wp[g * stride + 1] = l; }
+#pragma unroll
+    for (int mb = 0; mb < KS; ++mb) {
+        const int h0 = 2 * t, h1 = 2 * t + 1, d = 16 * mb + g;
+        if (h0 < G) { wp[h0 * stride + 2 + d] = oacc[mb][0]; wp[h0 * stride + 2 + d + 8] = oacc[mb][2]; }
+        if (h1 < G) { wp[h1 * stride + 2 + d] = oacc[mb][1]; wp[h1 * stride + 2 + d + 8] = oacc[mb][3]; }
+    }
+    __syncthreads();
+    // fold the warps of this CTA (weights e^(m_w - M) once per (warp, head)), then the CTAs of the cluster
+    const unsigned char *tiles = smem_att + L::tiles();
+    const int nwp = min(FK_SDPA_CW, (k_end - k_begin + FK_SDPA_MK - 1) / FK_SDPA_MK);        // warps that saw keys
+    if (tid < G) {
+        float M = -INFINITY;
+        for (int w = 0; w < nwp; ++w) M = fmaxf(M, reinterpret_cast<const float *>(tiles + w * L::WTILE)[tid * stride]);
+        float Ls = 0.0f;
+        for (int w = 0; w < nwp; ++w) {
+            const float *pw = reinterpret_cast<const float *>(tiles + w * L::WTILE) + tid * stride;
+            const float e = pw[0] == -INFINITY ? 0.0f : expf(pw[0] - M);
+            wexp[w * G + tid] = e; Ls = fmaf(pw[1], e, Ls);
+        }
+        cpart[tid * stride] = M; cpart[tid * stride + 1] = Ls;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += NT) {
+        const int gg = i / HD, d = i - gg * HD;
+        float O = 0.0f;
+        for (int w = 0; w < nwp; ++w) O = fmaf(reinterpret_cast<const float *>(tiles + w * L::WTILE)[gg * stride + 2 + d], wexp[w * G + gg], O);
+        cpart[gg * stride + 2 + d] = O;
+    }
+    sd_stamp(a.tl, 3);
+    cluster.sync();
+    sd_stamp(a.tl, 4);
+    const int total = G * HD, per = (total + CL - 1) / CL;
+    for (int i = rank * per + tid; i < min(total, (rank + 1) * per); i += NT) {      // this CTA's slice of the outputs
+        const int gg = i / HD, d = i - gg * HD;
+        float mm[FK_SDPA_CL], ll[FK_SDPA_CL], oo[FK_SDPA_CL];
+#pragma unroll
+        for (int rr = 0; rr < FK_SDPA_CL; ++rr) {
+            if (rr < CL) { const float *rp = cluster.map_shared_rank(cpart, rr) + gg * stride; mm[rr] = rp[0]; ll[rr] = rp[1]; oo[rr] = rp[2 + d]; }
+            else { mm[rr] = -INFINITY; ll[rr] = 0.0f; oo[rr] = 0.0f; }
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int rr = 0; rr < FK_SDPA_CL; ++rr) M = fmaxf(M, mm[rr]);
+        float Ls = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int rr = 0; rr < FK_SDPA_CL; ++rr) { const float e = mm[rr] == -INFINITY ? 0.0f : expf(mm[rr] - M); Ls = fmaf(ll[rr], e, Ls); O = fmaf(oo[rr], e, O); }
+        a.out[(kvh * G + gg) * HD + d] = f2bf(O * __fdiv_rn(1.0f, Ls));
+    }
+    cluster.sync();                                      // peers may still be reading this CTA's partial
+    sd_stamp(a.tl, 6);
+}
+
 struct LinArgs { const uint16_t *x; WView W; const uint16_t *residual; uint16_t *y; float *y_f32; int k, n; };
 // y = T(acc + float(residual)), one rounding (src/codegen/msl.rs:2759-2775); residual optional
 template <int BITS>

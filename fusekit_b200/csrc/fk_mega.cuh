@@ -336,62 +336,6 @@ struct EpiAny {
     }
 };
 
-// One kernel for every streamed task kind (one kernel per task, programmatic dependent launch between them).  The tasks
-// of a token alternate between four kinds; with a kernel per kind every launch starts with cold instruction caches,
-// with one shared kernel the staging code, the streaming loop and the epilogues stay resident from launch to launch.
-template <int BITS, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_any(FkState *st, const __grid_constant__ MegaOp op) {
-    extern __shared__ __align__(128) unsigned char smem_stream[];
-    __shared__ unsigned long long wbest[WARPS]; __shared__ int is_last;
-    const int kind = op.kind;
-    const StreamPlan &P = kind == FK_TASK_LINEAR_RESIDUAL ? op.u.lin.P : kind == FK_TASK_RMSNORM_QKV ? op.u.qkv.P
-                          : kind == FK_TASK_RMSNORM_GATEUP_ACT ? op.u.gu.P : op.u.head.P;
-    const StreamSmem sm = stream_carve(smem_stream, P.W.nsb, P.stages, BITS);
-    stamp(P, 0);
-    WarpStream ws; stream_begin(ws, P, sm);
-    pdl_wait();
-    stamp(P, 1);
-    if (kind == FK_TASK_LINEAR_RESIDUAL) {
-        stage_plain<BITS>(sm, op.u.lin.x, op.u.lin.k, P.W.nsb);
-    } else {
-        const uint16_t *x, *nw, *pending, *pending_w; uint16_t *h_out; const float *pend_sum; int h; float eps;
-        if (kind == FK_TASK_RMSNORM_QKV) { const SQkvArgs &a = op.u.qkv; x = a.x; nw = a.norm_w; pending = a.pending; pending_w = a.pending_w; h_out = a.h_out; pend_sum = a.pend_sum; h = a.h; eps = a.eps; }
-        else if (kind == FK_TASK_RMSNORM_GATEUP_ACT) { const SGateUpArgs &a = op.u.gu; x = a.x; nw = a.norm_w; pending = a.pending; pending_w = a.pending_w; h_out = a.h_out; pend_sum = a.pend_sum; h = a.h; eps = a.eps; }
-        else { const SHeadArgs &a = op.u.head; x = a.x; nw = a.norm_w; pending = a.pending; pending_w = a.pending_w; h_out = a.h_out; pend_sum = a.pend_sum; h = a.h; eps = a.eps; }
-        stage_rmsnorm<BITS>(sm, x, nw, h, P.W.nsb, eps, pending, pending_w, h_out, P.timeline, pend_sum);
-    }
-    stamp(P, 2);
-    EpiAny epi(op, st->offset);
-    const bool ok = stream_run<BITS>(ws, P, sm, epi);
-    pdl_launch_dependents();
-    if (!ok) atomicOr(&st->error, 0x4000u);
-    if (kind != FK_TASK_FINAL_RMSNORM_LM_HEAD) { __syncthreads(); stamp(P, 3); return; }
-    // lm_head: per-block best key, the last block to arrive folds them and advances the decode state
-    const SHeadArgs &a = op.u.head;
-    stamp(P, 3);
-    unsigned long long best = warp_max_u64(epi.head.best);
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    if (lane == 0) wbest[wid] = best;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int i = 1; i < WARPS; ++i) best = wbest[i] > best ? wbest[i] : best;
-        a.scratch[blockIdx.x] = best;
-        __threadfence();
-        const uint32_t tk = atomicAdd(a.counter, 1u);
-        is_last = (tk == gridDim.x - 1);
-        if (is_last) *a.counter = 0u;
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    if (wid == 0) {
-        unsigned long long b = 0ull;
-        for (int i = lane; i < (int)gridDim.x; i += 32) { const unsigned long long v = __ldcg(a.scratch + i); b = v > b ? v : b; }
-        b = warp_max_u64(b);
-        if (lane == 0) { if (a.finalize) s_finalize_token(st, a.history, b); else a.scratch[0] = b; }
-    }
-}
-
 // The persistent kernel.  `ops` is the token's task list, `wtab` the streamed weights in task order.
 template <int BITS>
 __global__ void __launch_bounds__(FK_MEGA_WARPS * 32, 1)

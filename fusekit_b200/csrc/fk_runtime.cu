@@ -90,7 +90,7 @@ struct Ctx {
     uint32_t *pinned = nullptr;                 // host staging for state / history
     std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
     bool pending = false; bool pdl = true; int sm_count = 148;
-    bool use_tiled = true; int stages = FK_STAGES; int prefetch = 1; int force_warps = 0; bool sdpa_cluster = true; bool uber = false; int sdpa_tiles_from = 0; int dbg_mode = 0;
+    bool use_tiled = true; int stages = FK_STAGES; int prefetch = 1; int force_warps = 0; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_tiles_from = 0; int dbg_mode = 0;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
@@ -137,14 +137,15 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     const char *e = getenv("FK_PDL"); if (e && e[0] == '0') c->pdl = false;
     e = getenv("FK_LAYOUT"); if (e && !strcmp(e, "mlx")) c->use_tiled = false;
     e = getenv("FK_SDPA"); if (e && !strcmp(e, "ticket")) c->sdpa_cluster = false;
+    if (e && !strcmp(e, "mma")) c->sdpa_mma = true;
+    if (e && !strcmp(e, "fma")) c->sdpa_mma = false;
     e = getenv("FK_SDPA_TILES_FROM"); if (e) c->sdpa_tiles_from = atoi(e);      // capacity from which attention uses the tiled kernel (0 = never)
     e = getenv("FK_DBG"); if (e) c->dbg_mode = atoi(e);
-    e = getenv("FK_UBER"); if (e) c->uber = e[0] != '0';            // 1: every streamed task kind runs the shared kernel k_s_any
     e = getenv("FK_WARPS"); if (e) c->force_warps = atoi(e);
     e = getenv("FK_PREFETCH"); if (e && atoi(e) >= 0 && atoi(e) <= 64) c->prefetch = atoi(e);
 #define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>)); CU(big_smem(K<16, 8>)); CU(big_smem(K<16, 16>))
-    BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head); BIG4(k_s_any);
-    CU(big_smem(k_decode_token<4>)); CU(big_smem(k_decode_token<8>)); CU(big_smem(k_sdpa_tiles<64>)); CU(big_smem(k_sdpa_tiles<128>));
+    BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head);
+    CU(big_smem(k_decode_token<4>)); CU(big_smem(k_decode_token<8>)); CU(big_smem(k_sdpa_tiles<64>)); CU(big_smem(k_sdpa_tiles<128>)); CU(big_smem(k_sdpa_mma<64>)); CU(big_smem(k_sdpa_mma<128>));
     CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
     CU(big_smem(k_linear_residual<4>)); CU(big_smem(k_linear_residual<8>)); CU(big_smem(k_linear_residual<16>));
@@ -451,25 +452,16 @@ static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *nex
     }
     return sh;
 }
-// launch a streamed task: the shared kernel k_s_any<bits, warps> (default), or the kernel of its own kind (FK_UBER=0)
-#define ANY_LAUNCH(w, sh, OP)                                                                                           \
+// launch a streamed kernel template instance for (bits, warps).  (One kernel shared by all four task kinds was tried
+// to keep the code warm in the instruction caches between launches; it ran slower in the graph, 558 against 626 tok/s.)
+#define STREAM_LAUNCH(KERN, w, sh, ...)                                                                                  \
     do {                                                                                                                 \
-        if ((w)->bits == 4 && (sh).warps == 8) e = launch(c, k_s_any<4, 8>, dim3((sh).grid), dim3(256), (sh).smem, c->state, OP);            \
-        else if ((w)->bits == 4) e = launch(c, k_s_any<4, 16>, dim3((sh).grid), dim3(512), (sh).smem, c->state, OP);                         \
-        else if ((w)->bits == 8 && (sh).warps == 8) e = launch(c, k_s_any<8, 8>, dim3((sh).grid), dim3(256), (sh).smem, c->state, OP);       \
-        else if ((w)->bits == 8) e = launch(c, k_s_any<8, 16>, dim3((sh).grid), dim3(512), (sh).smem, c->state, OP);                         \
-        else if ((sh).warps == 8) e = launch(c, k_s_any<16, 8>, dim3((sh).grid), dim3(256), (sh).smem, c->state, OP);                        \
-        else e = launch(c, k_s_any<16, 16>, dim3((sh).grid), dim3(512), (sh).smem, c->state, OP);                                            \
-    } while (0)
-#define STREAM_LAUNCH(KERN, w, sh, FIELD, SA)                                                                            \
-    do {                                                                                                                 \
-        if (c->uber) { MegaOp op_; memset(&op_, 0, sizeof op_); op_.kind = t.kind; op_.widx = 0; op_.u.FIELD = SA; ANY_LAUNCH(w, sh, op_); break; } \
-        if ((w)->bits == 4 && (sh).warps == 8) e = launch(c, KERN<4, 8>, dim3((sh).grid), dim3(256), (sh).smem, c->state, SA);        \
-        else if ((w)->bits == 4) e = launch(c, KERN<4, 16>, dim3((sh).grid), dim3(512), (sh).smem, c->state, SA);                     \
-        else if ((w)->bits == 8 && (sh).warps == 8) e = launch(c, KERN<8, 8>, dim3((sh).grid), dim3(256), (sh).smem, c->state, SA);   \
-        else if ((w)->bits == 8) e = launch(c, KERN<8, 16>, dim3((sh).grid), dim3(512), (sh).smem, c->state, SA);                     \
-        else if ((sh).warps == 8) e = launch(c, KERN<16, 8>, dim3((sh).grid), dim3(256), (sh).smem, c->state, SA);                    \
-        else e = launch(c, KERN<16, 16>, dim3((sh).grid), dim3(512), (sh).smem, c->state, SA);                                        \
+        if ((w)->bits == 4 && (sh).warps == 8) e = launch(c, KERN<4, 8>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);        \
+        else if ((w)->bits == 4) e = launch(c, KERN<4, 16>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                     \
+        else if ((w)->bits == 8 && (sh).warps == 8) e = launch(c, KERN<8, 8>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);   \
+        else if ((w)->bits == 8) e = launch(c, KERN<8, 16>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                     \
+        else if ((sh).warps == 8) e = launch(c, KERN<16, 8>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);                    \
+        else e = launch(c, KERN<16, 16>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                                        \
     } while (0)
 #define BITS48(bits, CALL) do { if ((bits) == 4) { constexpr int B = 4; CALL; } else { constexpr int B = 8; CALL; } } while (0)
 
@@ -530,7 +522,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                 op.u.qkv = sa; rec_push(c, op); return FK_OK;
             }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
-            STREAM_LAUNCH(k_s_rmsnorm_qkv, w, sh, qkv, sa);
+            STREAM_LAUNCH(k_s_rmsnorm_qkv, w, sh, c->state, sa);
             break;
         }
         if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs 4/8-bit streamed weights");
@@ -580,6 +572,13 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             else e = launch(c, k_sdpa_tiles<128>, tgrid, tblock, smem, (const FkState *)c->state, a);
             break;
         }
+        if ((hd == 64 || hd == 128) && G <= 8 && (variant == 4 || (variant == 0 && c->sdpa_mma && c->sdpa_cluster))) {      // tensor-core cluster kernel
+            const size_t smem = sdpa_mma_smem_bytes(G, hd);
+            const dim3 cgrid(FK_SDPA_CL, nkv), cblock(FK_SDPA_CW * 32);
+            if (hd == 64) e = launch_cluster(c, k_sdpa_mma<64>, cgrid, cblock, smem, FK_SDPA_CL, (const FkState *)c->state, a);
+            else e = launch_cluster(c, k_sdpa_mma<128>, cgrid, cblock, smem, FK_SDPA_CL, (const FkState *)c->state, a);
+            break;
+        }
         if (variant != 2 && c->sdpa_cluster && (hd != 256 || G <= 2)) {
             const size_t smem = sdpa_cl_smem_bytes(G, hd);
             const dim3 cgrid(FK_SDPA_CL, nkv), cblock(FK_SDPA_CW * 32);
@@ -607,7 +606,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                 op.u.lin = sa; rec_push(c, op); return FK_OK;
             }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
-            STREAM_LAUNCH(k_s_linear, w, sh, lin, sa);
+            STREAM_LAUNCH(k_s_linear, w, sh, c->state, sa);
             break;
         }
         if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs 4/8-bit streamed weights");
@@ -629,7 +628,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                 op.u.gu = sa; rec_push(c, op); return FK_OK;
             }
             const Shape sh = make_plan(c, wg, &sa.P, nextw);
-            STREAM_LAUNCH(k_s_gateup, wg, sh, gu, sa);
+            STREAM_LAUNCH(k_s_gateup, wg, sh, c->state, sa);
             break;
         }
         if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs a paired 4/8-bit gate/up weight");
@@ -660,7 +659,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                 op.u.head = sa; rec_push(c, op); return FK_OK;
             }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
-            STREAM_LAUNCH(k_s_head, w, sh, head, sa);
+            STREAM_LAUNCH(k_s_head, w, sh, c->state, sa);
             break;
         }
         if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs 4/8-bit streamed weights");

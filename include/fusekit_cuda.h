@@ -75,7 +75,7 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      i0 n_q  i1 n_kv  i2 head_dim  i3 capacity   f0 eps  f1 rope_theta
  * SDPA_DECODE          buf0 q  buf1 cache_k  buf2 cache_v  buf3 out  buf4 partials(f32)  buf5 counter(u32)
  *                      i0 n_q  i1 n_kv  i2 head_dim  i3 capacity  i4 kernel choice (0 = by shape and capacity, 1 = cluster,
- *                      2 = global partials + ticket, 3 = shared-memory tiles + ticket)   f0 scale
+ *                      2 = global partials + ticket, 3 = shared-memory tiles + ticket, 4 = tensor-core cluster)   f0 scale
  *                      partials: n_q * ceil(capacity / 32) * (head_dim + 2) floats; counter: n_kv words, zero before first use
  * LINEAR_RESIDUAL      buf0 x T[K]  buf1 weight  buf2 residual|0  buf3 y_out T[N]  buf4 y_f32_out|0   i0 K  i1 N
  * RMSNORM_GATEUP_ACT   buf0 x  buf1 norm_w  buf2 weight(gate)  buf3 weight(up)  buf4 act_out T[I]
