@@ -614,7 +614,7 @@ template <int HD> struct SdpaMmaLayout {
     __host__ __device__ static constexpr int wexp(int G) { return cpart() + G * (HD + 2) * 4; }
     __host__ __device__ static constexpr int bytes(int G) { return wexp(G) + FK_SDPA_CW * G * 4 + 64; }
 };
-__host__ __device__ inline size_t sdpa_mma_smem_bytes(int G, int hd) { return hd == 128 ? SdpaMmaLayout<128>::bytes(G) : SdpaMmaLayout<64>::bytes(G); }
+__host__ __device__ inline size_t sdpa_mma_smem_bytes(int G, int hd) { return hd == 256 ? SdpaMmaLayout<256>::bytes(G) : hd == 128 ? SdpaMmaLayout<128>::bytes(G) : SdpaMmaLayout<64>::bytes(G); }
 template <int HD>
 __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st, SdpaArgs a) {
     extern __shared__ __align__(128) unsigned char smem_att[];
@@ -647,24 +647,18 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
     }
     __syncthreads();
     sd_stamp(a.tl, 1);
-    uint32_t aq[KS][2];                                      // A fragments of q: row g (rows >= G and 8..15 are zero)
+    // A fragments of q: row g (rows >= G and 8..15 are zero); in registers up to head_dim 128, re-read from shared memory above
+    constexpr bool QREG = HD <= 128;
+    uint32_t aq[QREG ? KS : 1][2];
+    const uint32_t *qrow = reinterpret_cast<const uint32_t *>(qs + g * L::QSTRIDE + t * (HD / 2));      // the lane's HD/4 dims are contiguous
+    if (QREG) {
 #pragma unroll
-    for (int s = 0; s < KS; ++s) {
-        const uint32_t *qp = reinterpret_cast<const uint32_t *>(qs + g * L::QSTRIDE + t * (HD / 2)) + 2 * s;      // the lane's HD/4 dims are contiguous
-        aq[s][0] = g < G ? qp[0] : 0u; aq[s][1] = g < G ? qp[1] : 0u;
+        for (int s = 0; s < (QREG ? KS : 1); ++s) { aq[s][0] = g < G ? qrow[2 * s] : 0u; aq[s][1] = g < G ? qrow[2 * s + 1] : 0u; }
     }
     float m = -INFINITY, l = 0.0f, oacc[KS][4];
 #pragma unroll
     for (int mb = 0; mb < KS; ++mb) { oacc[mb][0] = oacc[mb][1] = oacc[mb][2] = oacc[mb][3] = 0.0f; }
     for (int kb = k_begin + wid * FK_SDPA_MK; kb < k_end; kb += FK_SDPA_CW * FK_SDPA_MK) {
-        uint4 kr[2][KV4];
-#pragma unroll
-        for (int nb = 0; nb < 2; ++nb) {
-            const int key = min(kb + 8 * nb + g, k_end - 1);                  // clamped: masked below
-            const uint4 *kp = reinterpret_cast<const uint4 *>(K + (size_t)key * HD + t * (HD / 4));
-#pragma unroll
-            for (int c = 0; c < KV4; ++c) kr[nb][c] = __ldcg(kp + c);
-        }
         // V rows of the block into this warp's tile (rows past the end are zero)
 #pragma unroll
         for (int i = 0; i < FK_SDPA_MK * (HD / 8) / 32; ++i) {
@@ -673,15 +667,29 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
             if (kb + row < k_end) v = __ldcg(reinterpret_cast<const uint4 *>(V + (size_t)(kb + row) * HD) + c);
             *reinterpret_cast<uint4 *>(vt + row * L::VSTRIDE + c * 16) = v;
         }
+        // K rows of both 8-key halves are requested together up to head_dim 128 (one round trip), one half at a time above
+        constexpr int NKR = QREG ? 2 : 1;
+        uint4 kr[NKR][KV4];
+        auto load_k = [&](int nb, int slot) {
+            const int key = min(kb + 8 * nb + g, k_end - 1);                  // clamped: masked below
+            const uint4 *kp = reinterpret_cast<const uint4 *>(K + (size_t)key * HD + t * (HD / 4));
+#pragma unroll
+            for (int c = 0; c < KV4; ++c) kr[slot][c] = __ldcg(kp + c);
+        };
+        if (QREG) { load_k(0, 0); load_k(1, NKR - 1); }
         float sacc[2][4];
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) {
+            if (!QREG) load_k(nb, 0);
             sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.0f;
 #pragma unroll
             for (int s = 0; s < KS; ++s) {
-                const uint4 q4 = kr[nb][s >> 1];
+                const uint4 q4 = kr[QREG ? nb : 0][s >> 1];
                 const uint32_t w0 = (s & 1) ? q4.z : q4.x, w1 = (s & 1) ? q4.w : q4.y;
-                mma_bf16_f32(sacc[nb], aq[s][0], 0u, aq[s][1], 0u, w0, w1);
+                uint32_t x0, x1;
+                if (QREG) { x0 = aq[QREG ? s : 0][0]; x1 = aq[QREG ? s : 0][1]; }
+                else { x0 = g < G ? qrow[2 * s] : 0u; x1 = g < G ? qrow[2 * s + 1] : 0u; }
+                mma_bf16_f32(sacc[nb], x0, 0u, x1, 0u, w0, w1);
             }
         }
         // lane (g, t): scores of head g for keys kb + {2t, 2t+1, 8+2t, 9+2t}
