@@ -611,8 +611,8 @@ template <int HD> struct SdpaMmaLayout {
     __host__ __device__ static constexpr int q() { return 0; }
     __host__ __device__ static constexpr int tiles() { return 8 * QSTRIDE; }
     __host__ __device__ static constexpr int cpart() { return tiles() + FK_SDPA_CW * WTILE; }
-    __host__ __device__ static constexpr int wexp(int G) { return cpart() + G * (HD + 2) * 4; }
-    __host__ __device__ static constexpr int bytes(int G) { return wexp(G) + FK_SDPA_CW * G * 4 + 64; }
+    __host__ __device__ static constexpr int wexp(int G) { return cpart() + (G * HD + FK_SDPA_CL) * 4; }      // after the received o slices
+    __host__ __device__ static constexpr int bytes(int G) { return wexp(G) + FK_SDPA_CL * G * 2 * 4 + 64; }
 };
 __host__ __device__ inline size_t sdpa_mma_smem_bytes(int G, int hd) { return hd == 256 ? SdpaMmaLayout<256>::bytes(G) : hd == 128 ? SdpaMmaLayout<128>::bytes(G) : SdpaMmaLayout<64>::bytes(G); }
 template <int HD>
@@ -630,6 +630,7 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
     float *wexp = reinterpret_cast<float *>(smem_att + L::wexp(G));           // [CW][G]
     sd_stamp(a.tl, 0);
     pdl_launch_dependents();
+    auto started = cluster.barrier_arrive();     // waited for before the first remote store: every CTA of the cluster is running by then
     const uint32_t pos = a.pos_override >= 0 ? (uint32_t)a.pos_override : st->offset;
     const int kv_len = (int)min(pos + 1u, (uint32_t)a.capacity);
     const int kpc = ((kv_len + CL * FK_SDPA_MK - 1) / (CL * FK_SDPA_MK)) * FK_SDPA_MK;
@@ -739,48 +740,52 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
         if (h1 < G) { wp[h1 * stride + 2 + d] = oacc[mb][1]; wp[h1 * stride + 2 + d + 8] = oacc[mb][3]; }
     }
     __syncthreads();
-    // fold the warps of this CTA (weights e^(m_w - M) once per (warp, head)), then the CTAs of the cluster
+    // Fold the warps of this CTA and push the result to the CTA that owns the output: CTA r of the cluster writes outputs
+    // [r * per, (r + 1) * per) and receives, from every CTA, that slice of o plus (m, l) of every head (distributed shared
+    // memory stores).  One cluster barrier, then a local fold; nobody reads remote memory afterwards, so a CTA may exit as
+    // soon as its own outputs are written.
     const unsigned char *tiles = smem_att + L::tiles();
-    const int nwp = min(FK_SDPA_CW, (k_end - k_begin + FK_SDPA_MK - 1) / FK_SDPA_MK);        // warps that saw keys
-    if (tid < G) {
+    const int nwp = min(FK_SDPA_CW, max(0, (k_end - k_begin + FK_SDPA_MK - 1) / FK_SDPA_MK));        // warps that saw keys
+    const int total = G * HD, per = (total + CL - 1) / CL;
+    float *recv_o = cpart;                                   // [CL][per]
+    float *recv_ml = wexp;                                   // [CL][G][2]
+    cluster.barrier_wait(std::move(started));
+    for (int i = tid; i < total + G; i += NT) {              // i >= total: the (m, l) pair of head i - total
+        const int gg = i < total ? i / HD : i - total, d = i < total ? i - gg * HD : -1;
         float M = -INFINITY;
-        for (int w = 0; w < nwp; ++w) M = fmaxf(M, reinterpret_cast<const float *>(tiles + w * L::WTILE)[tid * stride]);
-        float Ls = 0.0f;
+        for (int w = 0; w < nwp; ++w) M = fmaxf(M, reinterpret_cast<const float *>(tiles + w * L::WTILE)[gg * stride]);
+        float acc = 0.0f;
         for (int w = 0; w < nwp; ++w) {
-            const float *pw = reinterpret_cast<const float *>(tiles + w * L::WTILE) + tid * stride;
+            const float *pw = reinterpret_cast<const float *>(tiles + w * L::WTILE) + gg * stride;
             const float e = pw[0] == -INFINITY ? 0.0f : expf(pw[0] - M);
-            wexp[w * G + tid] = e; Ls = fmaf(pw[1], e, Ls);
+            acc = fmaf(d < 0 ? pw[1] : pw[2 + d], e, acc);
         }
-        cpart[tid * stride] = M; cpart[tid * stride + 1] = Ls;
-    }
-    __syncthreads();
-    for (int i = tid; i < G * HD; i += NT) {
-        const int gg = i / HD, d = i - gg * HD;
-        float O = 0.0f;
-        for (int w = 0; w < nwp; ++w) O = fmaf(reinterpret_cast<const float *>(tiles + w * L::WTILE)[gg * stride + 2 + d], wexp[w * G + gg], O);
-        cpart[gg * stride + 2 + d] = O;
+        if (d >= 0) {
+            const int dst = i / per;
+            cluster.map_shared_rank(recv_o, dst)[rank * per + (i - dst * per)] = acc;
+        } else {
+            for (int dst = 0; dst < CL; ++dst) { float *q2 = cluster.map_shared_rank(recv_ml, dst) + (rank * G + gg) * 2; q2[0] = M; q2[1] = acc; }
+        }
     }
     sd_stamp(a.tl, 3);
     cluster.sync();
     sd_stamp(a.tl, 4);
-    const int total = G * HD, per = (total + CL - 1) / CL;
-    for (int i = rank * per + tid; i < min(total, (rank + 1) * per); i += NT) {      // this CTA's slice of the outputs
+    for (int il = tid; il < per; il += NT) {
+        const int i = rank * per + il;
+        if (i >= total) break;
         const int gg = i / HD, d = i - gg * HD;
-        float mm[FK_SDPA_CL], ll[FK_SDPA_CL], oo[FK_SDPA_CL];
-#pragma unroll
-        for (int rr = 0; rr < FK_SDPA_CL; ++rr) {
-            if (rr < CL) { const float *rp = cluster.map_shared_rank(cpart, rr) + gg * stride; mm[rr] = rp[0]; ll[rr] = rp[1]; oo[rr] = rp[2 + d]; }
-            else { mm[rr] = -INFINITY; ll[rr] = 0.0f; oo[rr] = 0.0f; }
-        }
         float M = -INFINITY;
 #pragma unroll
-        for (int rr = 0; rr < FK_SDPA_CL; ++rr) M = fmaxf(M, mm[rr]);
+        for (int rr = 0; rr < FK_SDPA_CL; ++rr) if (rr < CL) M = fmaxf(M, recv_ml[(rr * G + gg) * 2]);
         float Ls = 0.0f, O = 0.0f;
 #pragma unroll
-        for (int rr = 0; rr < FK_SDPA_CL; ++rr) { const float e = mm[rr] == -INFINITY ? 0.0f : expf(mm[rr] - M); Ls = fmaf(ll[rr], e, Ls); O = fmaf(oo[rr], e, O); }
+        for (int rr = 0; rr < FK_SDPA_CL; ++rr) if (rr < CL) {
+            const float mr = recv_ml[(rr * G + gg) * 2];
+            const float e = mr == -INFINITY ? 0.0f : expf(mr - M);
+            Ls = fmaf(recv_ml[(rr * G + gg) * 2 + 1], e, Ls); O = fmaf(recv_o[rr * per + il], e, O);
+        }
         a.out[(kvh * G + gg) * HD + d] = f2bf(O * __fdiv_rn(1.0f, Ls));
     }
-    cluster.sync();                                      // peers may still be reading this CTA's partial
     sd_stamp(a.tl, 6);
 }
 
