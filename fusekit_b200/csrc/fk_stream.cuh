@@ -493,12 +493,6 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5, g = lane >> 2, t = lane & 3;
     Cursor cons; cons.init(W.ntiles, W.nsb, blockIdx.x, gridDim.x, wid, nw);
     bool ok = true;
-#ifdef FK_WARPSTAMP
-    unsigned long long *wtl = (pr.tl() && blockIdx.x < 32 && wid < 8) ? pr.tl() + 2560 + (blockIdx.x * 8 + wid) * 4 : nullptr;
-    auto wstamp = [&](int k) { if (wtl && lane == 0) { unsigned long long tt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tt)); wtl[k] = tt; } };
-    bool first_done = false;
-    wstamp(0);
-#endif
     if (!pr.valid()) pr.drained();
     const int nchunks = cons.nchunks();
     if (t == 0 && cons.ntl > 0) {
@@ -519,9 +513,6 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
                 const int s = pr.consumed & (FK_STAGES - 1);
                 if (dbg_mode != 3 && !mbar_wait(pr.bars + s, (uint32_t)(pr.consumed >> 1) & 1u)) { ok = false; break; }
                 if (pr.consumed == 0) stamp_raw(pr.tl(), 6);
-#ifdef FK_WARPSTAMP
-                if (!first_done) { wstamp(1); first_done = true; }
-#endif
                 if (dbg_mode == 0) unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
                 else if (dbg_mode == 3) { if (pr.valid()) pr.prod.advance(); ++pr.consumed; cons.advance(); unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, 0, lane, acc_lo, acc_hi); continue; }
                 __syncwarp();
@@ -539,9 +530,6 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
         }
         if (whole) continue;
         if (c == 0) stamp_raw(pr.tl(), 7);
-#ifdef FK_WARPSTAMP
-        if (c == 0) wstamp(2);
-#endif
         __syncthreads();
         for (int q = wid; q < ct; q += nw) {                  // fold tile q of the chunk in warp order, then its epilogue
             if (t == 0) {
@@ -552,9 +540,6 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
             }
         }
         // the buffer of chunk c is cleared by its folding warps before chunk c+2 writes it: chunk c+1's barrier orders them
-#ifdef FK_WARPSTAMP
-        if (c == 0) wstamp(3);
-#endif
     }
     return ok;
 }
