@@ -188,6 +188,13 @@ def main():
         dist.broadcast_object_list(uid, src=0)
         eng = DecodeEngine(spec, cap, device=local, tp_rank=rank, tp_size=world)
         eng.comm_init(uid[0])
+        peer = False
+        # peer-memory all-reduce where the GPUs can map each other's arenas: measured faster than the library collective
+        # from 4 ranks up (FK_PEER=1 / 0 forces it on / off)
+        if os.environ.get("FK_PEER", "1" if world >= 4 else "0") != "0":
+            handles = [None] * world
+            dist.all_gather_object(handles, eng.peer_export())
+            peer = eng.peer_open(handles)
     else:
         eng = DecodeEngine(spec, cap, device=local)      # N > 1: N independent replicas, one per GPU
     eng.load_synthetic()
@@ -282,7 +289,7 @@ def main():
             "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "strong" if args.tp else "weak", "vs_baseline": None,
             "dtype": f"int{bits}" if bits != 16 else "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "tokens_per_step": CHUNK, "batch": 1, "ctx_start": ctx, "graph_nodes_per_token": nodes,
-                       "l2": "inputs (weights) larger than L2", "persistent_kernel": eng.persistent, "replicas": streams, "tensor_parallel": world if args.tp else 1, "pdl": eng.rt.info().get("pdl")},
+                       "l2": "inputs (weights) larger than L2", "persistent_kernel": eng.persistent, "replicas": streams, "tensor_parallel": world if args.tp else 1, "allreduce": ("peer" if (args.tp and world > 1 and peer) else "nccl") if args.tp and world > 1 else None, "pdl": eng.rt.info().get("pdl")},
             "e2e": {"value": tokens / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 80, "d2h_bytes_per_step": CHUNK * 4 + 80},
             "gpu_launches": nodes * CHUNK * args.steps,
             "clocks": clocks,

@@ -65,6 +65,7 @@ def lib():
         "fk_launch": [u64, P(Task)], "fk_launch_batch": [u64, P(Task), i32], "fk_smoke": [u64, vp, vp, vp, i32],
         "fk_state_set": [u64, u32, u32], "fk_state_get": [u64, P(u32), P(u32), P(u32)],
         "fk_program_build": [u64, P(Task), i32, P(u64)],
+        "fk_peer_arena_export": [u64, C.c_void_p, C.c_size_t], "fk_peer_arena_open": [u64, C.c_void_p, i32, i32],
         "fk_graph_capture": [u64, P(Task), i32, P(u64)], "fk_graph_launch": [u64, u64, P(C.c_double)],
         "fk_graph_launch_async": [u64, u64], "fk_wait": [u64, P(C.c_double)],
         "fk_graph_profile_nodes": [u64, u64, i32, P(C.c_double), i32, P(i32)], "fk_graph_node_count": [u64, u64, P(i32)],

@@ -789,6 +789,70 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
     sd_stamp(a.tl, 6);
 }
 
+// ---------------------------------------------------------------- peer-memory all-reduce (tensor parallel, one process per GPU)
+// The row-split projections of a tensor-parallel layer end in an all-reduce of one hidden vector (10-32 KB); a library
+// all-reduce costs ~23 us of latency for that, 129 times per token.  Here every rank owns an arena that its peers map
+// through CUDA IPC: a rank stores its partial into its slot of every peer's arena (plain peer stores over NVLink), then a
+// flag per (source rank, block); each rank polls its own arena only and sums the slots in rank order, so all ranks get
+// bit-identical results.  Slots and flags alternate by the parity of a per-block sequence number: a rank can be at most
+// one all-reduce ahead of a peer, because it needs that peer's push to finish the one in between.  Waits are bounded.
+#define FK_PEER_MAX 8
+#define FK_PEER_BLOCKS 8                    // blocks of an all-reduce; block b of every rank works on slice b
+#define FK_PEER_SLOT_BYTES (32 * 1024)      // payload limit per all-reduce
+#define FK_PEER_SPIN_LIMIT (1u << 22)
+struct PeerArena {
+    // byte offsets inside a rank's arena
+    __host__ __device__ static size_t slot(int parity, int src) { return ((size_t)parity * FK_PEER_MAX + src) * FK_PEER_SLOT_BYTES; }
+    __host__ __device__ static size_t flag(int parity, int src, int block) { return 2 * FK_PEER_MAX * FK_PEER_SLOT_BYTES + (((size_t)parity * FK_PEER_MAX + src) * FK_PEER_BLOCKS + block) * 128; }
+    __host__ __device__ static size_t counter(int block) { return flag(2, 0, 0) + (size_t)block * 128; }
+    __host__ __device__ static size_t bytes() { return counter(FK_PEER_BLOCKS); }
+};
+struct PeerMap { unsigned char *base[FK_PEER_MAX]; int rank, world; };     // base[r]: rank r's arena as mapped in this process
+template <typename T, bool IS_MAX>
+__global__ void __launch_bounds__(256) k_allreduce_peer(T *buf, int n, PeerMap P, FkState *st) {
+    __shared__ unsigned int seq_s; __shared__ int bad;
+    pdl_wait();                                  // buf is the previous kernel's output
+    unsigned char *own = P.base[P.rank];
+    const int b = blockIdx.x, nb = gridDim.x;
+    if (threadIdx.x == 0) {
+        unsigned int *cnt = reinterpret_cast<unsigned int *>(own + PeerArena::counter(b));
+        seq_s = *cnt + 1u; *cnt = seq_s; bad = 0;
+    }
+    __syncthreads();
+    const unsigned int seq = seq_s; const int par = (int)(seq & 1u);
+    const int per = (n + nb - 1) / nb, lo = b * per, hi = min(n, lo + per);
+    // 1. my slice into my slot of every rank's arena (my own included)
+    for (int i = lo + (int)threadIdx.x; i < hi; i += (int)blockDim.x) {
+        const T v = buf[i];
+        for (int p = 0; p < P.world; ++p) reinterpret_cast<T *>(P.base[p] + PeerArena::slot(par, P.rank))[i] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    // 2. tell every rank that slice b of this rank is in; 3. wait for slice b of every rank
+    if ((int)threadIdx.x < P.world) {
+        const int p = (int)threadIdx.x;
+        unsigned int *remote = reinterpret_cast<unsigned int *>(P.base[p] + PeerArena::flag(par, P.rank, b));
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(seq) : "memory");
+        const unsigned int *mine = reinterpret_cast<const unsigned int *>(own + PeerArena::flag(par, p, b));
+        unsigned int it = 0, v;
+        do {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        } while ((int)(v - seq) < 0 && ++it < FK_PEER_SPIN_LIMIT);
+        if ((int)(v - seq) < 0) { bad = 1; atomicOr(&st->error, 0x8000u); }
+    }
+    __syncthreads();
+    if (bad) return;
+    // 4. the slots in rank order
+    for (int i = lo + (int)threadIdx.x; i < hi; i += (int)blockDim.x) {
+        T acc = __ldcg(reinterpret_cast<const T *>(own + PeerArena::slot(par, 0)) + i);
+        for (int p = 1; p < P.world; ++p) {
+            const T v = __ldcg(reinterpret_cast<const T *>(own + PeerArena::slot(par, p)) + i);
+            acc = IS_MAX ? (v > acc ? v : acc) : (T)(acc + v);
+        }
+        buf[i] = acc;
+    }
+}
+
 struct LinArgs { const uint16_t *x; WView W; const uint16_t *residual; uint16_t *y; float *y_f32; int k, n; };
 // y = T(acc + float(residual)), one rounding (src/codegen/msl.rs:2759-2775); residual optional
 template <int BITS>

@@ -95,6 +95,7 @@ struct Ctx {
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
     std::vector<Program> programs; Recorder *rec = nullptr;
+    unsigned char *arena = nullptr; PeerMap peers; bool peer_ready = false;      // peer-memory all-reduce
 };
 static std::mutex g_mu;
 static std::vector<Ctx *> g_ctx;
@@ -679,6 +680,12 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
     }
     case FK_TASK_ALLREDUCE: {
         if (c->rec) return fail(FK_ERR_VALUE, "persistent program: collectives are not expressible");
+        if (c->peer_ready && i[0] > 0 && (size_t)i[0] * (i[1] == 1 ? 8 : 4) <= FK_PEER_SLOT_BYTES) {      // peer stores + flags instead of the library collective
+            const int nbk = i[0] >= 1024 ? FK_PEER_BLOCKS : 1;
+            if (i[1] == 1) e = launch(c, k_allreduce_peer<unsigned long long, true>, dim3(nbk), dim3(256), 0, (unsigned long long *)b[0], i[0], c->peers, c->state);
+            else e = launch(c, k_allreduce_peer<float, false>, dim3(nbk), dim3(256), 0, (float *)b[0], i[0], c->peers, c->state);
+            break;
+        }
         if (!c->comm) return fail(FK_ERR_STATE, "allreduce task without fk_comm_init");
         const int dtype = i[1] == 1 ? 5 /* ncclUint64 */ : 7 /* ncclFloat32 */, op = i[1] == 1 ? 2 /* ncclMax */ : 0 /* ncclSum */;
         int r = g_nccl.AllReduce((const void *)b[0], (void *)b[0], (size_t)i[0], dtype, op, c->comm, c->stream);
@@ -1005,6 +1012,35 @@ extern "C" fk_status fk_sdpa_decode_noalloc(const void *q, const void *cache_k, 
 extern "C" fk_status fk_debug_timeline(fk_handle h, fk_dptr dptr) { CTX(h); c->timeline = (unsigned long long *)dptr; return FK_OK; }
 
 // ------------------------------------------------------------------ tensor parallel
+extern "C" fk_status fk_peer_arena_export(fk_handle h, void *handle64, size_t cap) {
+    CTX(h);
+    if (!handle64 || cap < sizeof(cudaIpcMemHandle_t)) return fail(FK_ERR_VALUE, "handle buffer must hold 64 bytes");
+    if (!c->arena) {
+        CU(cudaMalloc(&c->arena, PeerArena::bytes()));
+        CU(cudaMemset(c->arena, 0, PeerArena::bytes()));
+        CU(cudaDeviceSynchronize());
+    }
+    cudaIpcMemHandle_t hd; CU(cudaIpcGetMemHandle(&hd, c->arena));
+    memcpy(handle64, &hd, sizeof hd);
+    return FK_OK;
+}
+extern "C" fk_status fk_peer_arena_open(fk_handle h, const void *handles, int rank, int world) {
+    CTX(h);
+    if (!handles || world < 2 || world > FK_PEER_MAX || rank < 0 || rank >= world) return fail(FK_ERR_VALUE, "fk_peer_arena_open: 2..%d ranks", FK_PEER_MAX);
+    if (!c->arena) return fail(FK_ERR_STATE, "call fk_peer_arena_export first");
+    memset(&c->peers, 0, sizeof c->peers);
+    c->peers.rank = rank; c->peers.world = world;
+    for (int r = 0; r < world; ++r) {
+        if (r == rank) { c->peers.base[r] = c->arena; continue; }
+        cudaIpcMemHandle_t hd; memcpy(&hd, (const unsigned char *)handles + (size_t)r * sizeof hd, sizeof hd);
+        void *p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, hd, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) { cudaGetLastError(); return fail(FK_ERR_CUDA, "cudaIpcOpenMemHandle for rank %d: %s", r, cudaGetErrorString(e)); }
+        c->peers.base[r] = (unsigned char *)p;
+    }
+    c->rank = rank; c->world = world; c->peer_ready = true;
+    return FK_OK;
+}
 extern "C" fk_status fk_comm_unique_id(void *id128, size_t cap) {
     if (!id128 || cap < sizeof(ncclUniqueId)) return fail(FK_ERR_VALUE, "id buffer must hold 128 bytes");
     fk_status s = nccl_load(); if (s) return s;

@@ -486,6 +486,22 @@ class DecodeEngine:
         buf = C.create_string_buffer(unique_id, 128)
         N.check(self.rt.L.fk_comm_init(self.rt.h, buf, self.rank, self.world), "fk_comm_init")
 
+    def peer_export(self) -> bytes:
+        """This rank's arena for the peer-memory all-reduce as a 64-byte IPC handle (gather them in rank order)."""
+        buf = C.create_string_buffer(64)
+        N.check(self.rt.L.fk_peer_arena_export(self.rt.h, buf, 64), "fk_peer_arena_export")
+        return buf.raw
+
+    def peer_open(self, handles) -> bool:
+        """Map the peers' arenas (`handles`: one 64-byte handle per rank, in rank order).  Returns False, leaving the
+        library collective in charge, where peer mapping is not possible."""
+        blob = C.create_string_buffer(b"".join(handles), 64 * len(handles))
+        try:
+            N.check(self.rt.L.fk_peer_arena_open(self.rt.h, blob, self.rank, self.world), "fk_peer_arena_open")
+        except N.FusekitError:
+            return False
+        return True
+
     def close(self):
         self.rt.close()
 

@@ -207,6 +207,13 @@ fk_status fk_sdpa_decode_noalloc(const void *q, const void *cache_k, const void 
  * `python -m fusekit_b200.timeline` prints both forms. */
 fk_status fk_debug_timeline(fk_handle h, fk_dptr buf);
 
+/* ---- peer-memory all-reduce for tensor parallelism (no reference counterpart).  Every rank exports a small arena as a
+ *      64-byte CUDA IPC handle, the host gathers the handles (any transport) and every rank opens them in rank order;
+ *      from then on FK_TASK_ALLREDUCE payloads of up to 32 KB are exchanged by peer stores and flags inside one small
+ *      kernel (bit-identical on all ranks) instead of the library collective, which stays the fallback. ------------- */
+fk_status fk_peer_arena_export(fk_handle h, void *handle64, size_t cap);
+fk_status fk_peer_arena_open(fk_handle h, const void *handles /* world x 64 bytes */, int rank, int world);
+
 /* ---- tensor parallelism (no reference counterpart; NCCL over NVLink) ------ */
 fk_status fk_comm_unique_id(void *id128, size_t cap);          /* rank 0 makes the 128-byte id */
 fk_status fk_comm_init(fk_handle h, const void *id128, int rank, int world);

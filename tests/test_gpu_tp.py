@@ -1,5 +1,5 @@
-"""Tensor-parallel decode on 2 GPUs (NCCL all-reduce captured in the graph) against the single-rank oracle.
-Skipped where fewer than two CUDA devices are visible."""
+"""Tensor-parallel decode on 2 GPUs against the single-rank oracle, once with the library all-reduce (NCCL, captured in
+the graph) and once with the peer-memory all-reduce kernel.  Skipped where fewer than two CUDA devices are visible."""
 import os
 import subprocess
 import sys
@@ -16,7 +16,7 @@ WORKER = textwrap.dedent("""
     import torch, torch.distributed as dist
     sys.path.insert(0, {root!r})
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    rank, world = int(sys.argv[1]), int(sys.argv[2])
+    rank, world, mode = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
     dist.init_process_group("gloo", init_method="tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     from fusekit_b200.model_spec import CONFIGS
     from fusekit_b200.runtime import DecodeEngine, comm_unique_id
@@ -25,6 +25,10 @@ WORKER = textwrap.dedent("""
     dist.broadcast_object_list(uid, src=0)
     eng = DecodeEngine(spec, 64, device=rank, tp_rank=rank, tp_size=world)
     eng.comm_init(uid[0])
+    if mode == "peer":
+        handles = [None] * world
+        dist.all_gather_object(handles, eng.peer_export())
+        assert eng.peer_open(handles), "peer arenas could not be mapped"
     eng.load_synthetic(); eng.prefill_kv_synthetic(ctx)
     toks, secs = eng.decode_chunk(ctx, 3, steps)
     gathered = [None] * world
@@ -41,14 +45,15 @@ WORKER = textwrap.dedent("""
 """)
 
 
-def test_two_rank_tensor_parallel_decode(tmp_path):
+@pytest.mark.parametrize("mode", ["nccl", "peer"])
+def test_two_rank_tensor_parallel_decode(tmp_path, mode):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
-    port = 29700 + os.getpid() % 2000
+    port = 29700 + os.getpid() % 2000 + (1 if mode == "peer" else 0)
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER.format(root=ROOT, port=port))
-    procs = [subprocess.Popen([sys.executable, str(script), str(r), "2"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), "2", mode], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
              for r in range(2)]
     outs = [p.communicate(timeout=600)[0] for p in procs]
     for r, (p, out) in enumerate(zip(procs, outs)):
