@@ -409,14 +409,14 @@ k_decode_token(FkState *st, const MegaSlot *ops, int nops, const MegaWeight *wta
             if (kind == FK_TASK_LINEAR_RESIDUAL) {
                 const SLinArgs &a = op.u.lin;
                 W = &a.P.W;
-                stage_plain<BITS>(sm, a.x, a.k, a.P.W.nsb);
+                stage_plain<BITS, 5>(sm, a.x, a.k, a.P.W.nsb);
             } else {
                 // the three norm-first tasks differ only in where their arguments sit
                 const uint16_t *x, *nw; int h; float eps;
                 if (kind == FK_TASK_RMSNORM_QKV) { const SQkvArgs &a = op.u.qkv; W = &a.P.W; x = a.x; nw = a.norm_w; h = a.h; eps = a.eps; }
                 else if (kind == FK_TASK_RMSNORM_GATEUP_ACT) { const SGateUpArgs &a = op.u.gu; W = &a.P.W; x = a.x; nw = a.norm_w; h = a.h; eps = a.eps; }
                 else { const SHeadArgs &a = op.u.head; W = &a.P.W; x = a.x; nw = a.norm_w; h = a.h; eps = a.eps; }
-                stage_rmsnorm<BITS>(sm, x, nw, h, W->nsb, eps, nullptr, nullptr, nullptr, nullptr, nullptr);     // lists with pending norms or all-reduce inputs are refused at build time
+                stage_rmsnorm<BITS, false>(sm, x, nw, h, W->nsb, eps, nullptr, nullptr, nullptr, nullptr, nullptr);     // lists with pending norms or all-reduce inputs are refused at build time
             }
             mega_stamp(timeline, i, 1);
             if (kind == FK_TASK_RMSNORM_QKV && threadIdx.x == 0 && i + 1 < nops) {      // the staging above synchronised the block: the next record is in

@@ -90,7 +90,7 @@ struct Ctx {
     uint32_t *pinned = nullptr;                 // host staging for state / history
     std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
     bool pending = false; bool pdl = true; int sm_count = 148;
-    bool use_tiled = true; int stages = FK_STAGES; int prefetch = 1; int force_warps = 0; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_tiles_from = 0; int dbg_mode = 0;
+    bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_tiles_from = 0; int dbg_mode = 0;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
@@ -143,9 +143,9 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     e = getenv("FK_SDPA_TILES_FROM"); if (e) c->sdpa_tiles_from = atoi(e);      // capacity from which attention uses the tiled kernel (0 = never)
     e = getenv("FK_DBG"); if (e) c->dbg_mode = atoi(e);
     e = getenv("FK_WARPS"); if (e) c->force_warps = atoi(e);
-    e = getenv("FK_PREFETCH"); if (e && atoi(e) >= 0 && atoi(e) <= 64) c->prefetch = atoi(e);
 #define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>)); CU(big_smem(K<16, 8>)); CU(big_smem(K<16, 16>))
-    BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head);
+#define BIG4P(K) CU(big_smem(K<4, 8, true>)); CU(big_smem(K<4, 16, true>)); CU(big_smem(K<8, 8, true>)); CU(big_smem(K<8, 16, true>)); CU(big_smem(K<16, 8, true>)); CU(big_smem(K<16, 16, true>))
+    BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head); BIG4P(k_s_rmsnorm_qkv); BIG4P(k_s_gateup); BIG4P(k_s_head);
     CU(big_smem(k_decode_token<4>)); CU(big_smem(k_decode_token<8>)); CU(big_smem(k_sdpa_tiles<64>)); CU(big_smem(k_sdpa_tiles<128>)); CU(big_smem(k_sdpa_mma<64>)); CU(big_smem(k_sdpa_mma<128>)); CU(big_smem(k_sdpa_mma<256>));
     CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
@@ -445,12 +445,6 @@ static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *nex
     const Shape sh = plan_shape(c, w);
     p->W = w->tview(); p->stages = c->stages; p->dbg_mode = c->dbg_mode;
     p->timeline = c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr;
-    p->next_units = nullptr; p->next_ntiles = p->next_nsb = p->next_grid = p->next_warps = p->next_prefetch = 0; p->next_uvec = FK_UNIT_VEC;
-    if (next && c->prefetch > 0) {
-        const Shape ns = plan_shape(c, next);
-        p->next_units = next->units; p->next_ntiles = next->ntiles; p->next_nsb = next->nsb;
-        p->next_grid = ns.grid; p->next_warps = ns.warps; p->next_prefetch = c->prefetch; p->next_uvec = unit_vec(next->bits);
-    }
     return sh;
 }
 // launch a streamed kernel template instance for (bits, warps).  (One kernel shared by all four task kinds was tried
@@ -464,6 +458,25 @@ static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *nex
         else if ((sh).warps == 8) e = launch(c, KERN<16, 8>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);                    \
         else e = launch(c, KERN<16, 16>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                                        \
     } while (0)
+// norm-first kernels: the variant with the pending-norm / all-reduce prologue is a kernel of its own
+#define STREAM_LAUNCH_P(KERN, pend, w, sh, ...)                                                                          \
+    do {                                                                                                                 \
+        if (pend) {                                                                                                      \
+            if ((w)->bits == 4 && (sh).warps == 8) e = launch(c, KERN<4, 8, true>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);        \
+            else if ((w)->bits == 4) e = launch(c, KERN<4, 16, true>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                     \
+            else if ((w)->bits == 8 && (sh).warps == 8) e = launch(c, KERN<8, 8, true>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);   \
+            else if ((w)->bits == 8) e = launch(c, KERN<8, 16, true>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                     \
+            else if ((sh).warps == 8) e = launch(c, KERN<16, 8, true>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);                    \
+            else e = launch(c, KERN<16, 16, true>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                                        \
+        } else {                                                                                                         \
+            if ((w)->bits == 4 && (sh).warps == 8) e = launch(c, KERN<4, 8, false>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);       \
+            else if ((w)->bits == 4) e = launch(c, KERN<4, 16, false>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                    \
+            else if ((w)->bits == 8 && (sh).warps == 8) e = launch(c, KERN<8, 8, false>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);  \
+            else if ((w)->bits == 8) e = launch(c, KERN<8, 16, false>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                    \
+            else if ((sh).warps == 8) e = launch(c, KERN<16, 8, false>, dim3((sh).grid), dim3(256), (sh).smem, __VA_ARGS__);                   \
+            else e = launch(c, KERN<16, 16, false>, dim3((sh).grid), dim3(512), (sh).smem, __VA_ARGS__);                                       \
+        }                                                                                                                \
+    } while (0)
 #define BITS48(bits, CALL) do { if ((bits) == 4) { constexpr int B = 4; CALL; } else { constexpr int B = 8; CALL; } } while (0)
 
 
@@ -473,8 +486,7 @@ static fk_status rec_stream(Ctx *c, MegaOp &op, StreamPlan &P, const Weight *w) 
     if (w->bits == 16) return fail(FK_ERR_VALUE, "persistent program: 4- or 8-bit weights only");
     if (r->bits && r->bits != w->bits) return fail(FK_ERR_VALUE, "persistent program: all streamed weights must share one bit width");
     r->bits = w->bits;
-    P.W = w->tview(); P.stages = FK_STAGES; P.dbg_mode = 0; P.timeline = nullptr; P.next_units = nullptr;
-    P.next_ntiles = P.next_nsb = P.next_grid = P.next_warps = P.next_prefetch = 0;
+    P.W = w->tview(); P.stages = FK_STAGES; P.dbg_mode = 0; P.timeline = nullptr;
     op.widx = (int)r->wtab.size();
     MegaWeight mw; mw.units = w->units; mw.ntiles = w->ntiles; mw.nsb = w->nsb;
     r->wtab.push_back(mw);
@@ -523,7 +535,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                 op.u.qkv = sa; rec_push(c, op); return FK_OK;
             }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
-            STREAM_LAUNCH(k_s_rmsnorm_qkv, w, sh, c->state, sa);
+            STREAM_LAUNCH_P(k_s_rmsnorm_qkv, (sa.pending || sa.pend_sum), w, sh, c->state, sa);
             break;
         }
         if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs 4/8-bit streamed weights");
@@ -632,7 +644,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                 op.u.gu = sa; rec_push(c, op); return FK_OK;
             }
             const Shape sh = make_plan(c, wg, &sa.P, nextw);
-            STREAM_LAUNCH(k_s_gateup, wg, sh, c->state, sa);
+            STREAM_LAUNCH_P(k_s_gateup, (sa.pending || sa.pend_sum), wg, sh, c->state, sa);
             break;
         }
         if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs a paired 4/8-bit gate/up weight");
@@ -663,7 +675,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                 op.u.head = sa; rec_push(c, op); return FK_OK;
             }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
-            STREAM_LAUNCH(k_s_head, w, sh, c->state, sa);
+            STREAM_LAUNCH_P(k_s_head, (sa.pending || sa.pend_sum), w, sh, c->state, sa);
             break;
         }
         if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs 4/8-bit streamed weights");

@@ -23,8 +23,8 @@
 // of the block's tile and fold their sums through shared memory in warp order (deterministic, no global
 // round trip).  Rings are filled before griddepcontrol.wait: weights do not depend on the previous kernel,
 // so under programmatic dependent launch a block of the next kernel that lands on an SM slot freed by this
-// one streams its weights while this kernel finishes; each warp also pulls the first units its slot will
-// need in the next kernel into L2 once its own loads are all in flight.
+// one streams its weights while this kernel finishes.  (An L2 prefetch of the next kernel's first units was
+// measured and dropped: no gain.)
 #pragma once
 #include "fk_common.cuh"
 
@@ -217,20 +217,21 @@ __device__ __forceinline__ void stamp_raw(unsigned long long *tl, int slot) {
     if (tl && threadIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tl[blockIdx.x * 8 + slot] = t; }
 }
 #define FK_STAGE_MAXB 4          // 8-blocks per thread held in registers during staging (h <= 8 * 256 * 4)
-#define FK_PLAIN_MAXB 8          // 8-blocks per thread requested together by the plain staging
-template <int BITS>
+// MAXB: 8-blocks per thread requested together (one round trip); longer inputs take more rounds.  Small on purpose:
+// every unrolled copy is code the kernel carries, and a kernel's launch-to-launch cost grows with its size.
+template <int BITS, int MAXB>
 __device__ __forceinline__ void stage_plain(const StreamSmem &sm, const uint16_t *x, int k, int nsb) {
     stage_pad<BITS>(sm, k, nsb);
     const int nblk = k >> 3;
-    for (int b0 = 0; b0 < nblk; b0 += FK_PLAIN_MAXB * blockDim.x) {
-        uint4 v[FK_PLAIN_MAXB];
+    for (int b0 = 0; b0 < nblk; b0 += MAXB * blockDim.x) {
+        uint4 v[MAXB];
 #pragma unroll
-        for (int i = 0; i < FK_PLAIN_MAXB; ++i) {          // all loads in flight before the first use
+        for (int i = 0; i < MAXB; ++i) {          // all loads in flight before the first use
             const int blk = b0 + i * blockDim.x + threadIdx.x;
             v[i] = blk < nblk ? __ldcg(reinterpret_cast<const uint4 *>(x + (size_t)blk * 8)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int i = 0; i < FK_PLAIN_MAXB; ++i) {
+        for (int i = 0; i < MAXB; ++i) {
             const int blk = b0 + i * blockDim.x + threadIdx.x;
             if (b0 + i * (int)blockDim.x >= nblk) break;   // uniform across the block
             float f[8]; unpack8(v[i], f);
@@ -242,7 +243,7 @@ __device__ __forceinline__ void stage_plain(const StreamSmem &sm, const uint16_t
 // RMSNorm (two roundings to T, src/codegen/kernels/mod.rs:4464-4472; rmsnorm_qkv.rs:325), optionally after advancing the
 // residual stream with a pending post-norm, x' = T(x + rmsnorm(pending) * w_p) (Gemma-shaped layers); block 0
 // publishes x' to h_out.  One round of global loads: x, w (and the pending pair) stay in registers.
-template <int BITS>
+template <int BITS, bool PEND = true>
 __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16_t *x, const uint16_t *w, int h, int nsb, float eps,
                                               const uint16_t *pending, const uint16_t *pending_w, uint16_t *h_out,
                                               unsigned long long *tl = nullptr, const float *pend_sum = nullptr) {
@@ -255,7 +256,7 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
         xv[i] = wv[i] = make_uint4(0, 0, 0, 0);
         if (blk < nblk) { xv[i] = __ldcg(reinterpret_cast<const uint4 *>(x + (size_t)blk * 8)); wv[i] = *reinterpret_cast<const uint4 *>(w + (size_t)blk * 8); }
     }
-    if (pend_sum) {     // tensor parallel: x' = T(all-reduced projection + residual x); block 0 publishes it
+    if (PEND && pend_sum) {     // tensor parallel: x' = T(all-reduced projection + residual x); block 0 publishes it
 #pragma unroll
         for (int i = 0; i < FK_STAGE_MAXB; ++i) {
             const int blk = i * blockDim.x + threadIdx.x;
@@ -269,7 +270,7 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
             }
         }
     }
-    if (pending) {
+    if (PEND && pending) {
         uint4 pv[FK_STAGE_MAXB], pw[FK_STAGE_MAXB];
         float ss = 0.0f;
 #pragma unroll
@@ -384,8 +385,7 @@ __device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &s
 struct StreamPlan {
     TiledW W;
     int stages;             // ring depth per warp
-    // the streamed kernel that runs next: its first units are pulled into L2 while this kernel drains
-    const uint4 *next_units; int next_ntiles, next_nsb, next_grid, next_warps, next_prefetch, next_uvec;
+
     unsigned long long *timeline;   // optional [grid][8] phase timestamps (ns) for tuning; null in normal use
     int dbg_mode;                   // tuning experiments: 1 = skip the unit arithmetic (memory only), 3 = recompute one resident unit (arithmetic only); results invalid
 };
@@ -445,13 +445,6 @@ struct Cursor {
 __device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
-// L2 prefetch of the units this (block, warp) slot will consume first in the next streamed kernel
-__device__ __forceinline__ void prefetch_next(const StreamPlan &p) {
-    if (!p.next_units || (threadIdx.x & 31) != 0 || (int)blockIdx.x >= p.next_grid || (int)(threadIdx.x >> 5) >= p.next_warps) return;
-    Cursor c; c.init(p.next_ntiles, p.next_nsb, blockIdx.x, p.next_grid, threadIdx.x >> 5, p.next_warps);
-    for (int i = 0; i < p.next_prefetch && c.valid(); ++i) { l2_prefetch(p.next_units + c.unit_index() * p.next_uvec, (uint32_t)p.next_uvec * 16u); c.advance(); }
-}
-
 // Producer side of a warp's ring.  `consumed` counts the units this warp has taken out of the ring since its
 // barriers were initialised: it names the ring slot (consumed % stages) and the barrier phase to wait for.
 struct WarpStream {
@@ -465,10 +458,10 @@ struct WarpStream {
         }
         prod.advance();
     }
-    // everything this warp needs is in flight: let the next kernel start and warm L2 with its first units
+    // everything this warp needs is in flight: let the next kernel start
     __device__ __forceinline__ void drained() {
         if (announced) return;
-        announced = true; pdl_launch_dependents(); prefetch_next(*plan);
+        announced = true; pdl_launch_dependents();
     }
 };
 // before griddepcontrol.wait: barriers up, ring filled with the warp's first units, fold buffer cleared
@@ -688,7 +681,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st
     WarpStream ws; stream_begin(ws, a.P, sm);
     pdl_wait();
     stamp(a.P, 1);
-    stage_plain<BITS>(sm, a.x, a.k, a.P.W.nsb);
+    stage_plain<BITS, (WARPS == 16 ? 5 : 2)>(sm, a.x, a.k, a.P.W.nsb);
     stamp(a.P, 2);
     EpiLinear epi(a);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x100u);
@@ -750,7 +743,7 @@ struct EpiQkv {
         } else { store(r0, f2bf(lo)); store(r1, f2bf(hi)); }
     }
 };
-template <int BITS, int WARPS>
+template <int BITS, int WARPS, bool PEND = false>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkState *st, SQkvArgs a) {
     extern __shared__ __align__(128) unsigned char smem_stream[];
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
@@ -758,7 +751,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkStat
     WarpStream ws; stream_begin(ws, a.P, sm);
     pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
+    stage_rmsnorm<BITS, PEND>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
     EpiQkv epi(a, st->offset);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x200u);
@@ -794,7 +787,7 @@ struct EpiGateUp {
         if (r < a.inter) a.act_out[r] = a.act == 1 ? s_act_geglu(gate, up) : s_act_swiglu(gate, up);
     }
 };
-template <int BITS, int WARPS>
+template <int BITS, int WARPS, bool PEND = false>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st, SGateUpArgs a) {
     extern __shared__ __align__(128) unsigned char smem_stream[];
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
@@ -802,7 +795,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st
     WarpStream ws; stream_begin(ws, a.P, sm);
     pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
+    stage_rmsnorm<BITS, PEND>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
     EpiGateUp epi(a);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x400u);
@@ -841,7 +834,7 @@ struct EpiHead {
 };
 // final RMSNorm -> lm_head -> argmax on T-rounded logits, ties to the lowest index, no logits round trip
 // (final_rmsnorm_lm_head.rs:250-326; msl.rs:1805-1838); the last block folds the per-block keys and advances the state
-template <int BITS, int WARPS>
+template <int BITS, int WARPS, bool PEND = false>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, SHeadArgs a) {
     extern __shared__ __align__(128) unsigned char smem_stream[];
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
@@ -850,7 +843,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, 
     WarpStream ws; stream_begin(ws, a.P, sm);
     pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
+    stage_rmsnorm<BITS, PEND>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
     EpiHead epi(a);
     const bool ok = stream_run<BITS>(ws, a.P, sm, epi);
