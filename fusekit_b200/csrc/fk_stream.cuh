@@ -504,10 +504,15 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
             float acc_lo = 0.0f, acc_hi = 0.0f;
             for (int n = cons.run(); n > 0 && ok; --n) {    // the units of tile tl in this warp's run
                 const int s = pr.consumed & (FK_STAGES - 1);
+#ifdef FK_TUNING          // FK_DBG=1: memory only, FK_DBG=3: arithmetic only (results invalid); compiled in with -DFK_TUNING only
                 if (dbg_mode != 3 && !mbar_wait(pr.bars + s, (uint32_t)(pr.consumed >> 1) & 1u)) { ok = false; break; }
                 if (pr.consumed == 0) stamp_raw(pr.tl(), 6);
                 if (dbg_mode == 0) unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
                 else if (dbg_mode == 3) { if (pr.valid()) pr.prod.advance(); ++pr.consumed; cons.advance(); unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, 0, lane, acc_lo, acc_hi); continue; }
+#else
+                if (!mbar_wait(pr.bars + s, (uint32_t)(pr.consumed >> 1) & 1u)) { ok = false; break; }
+                unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
+#endif
                 __syncwarp();
                 if (pr.valid()) pr.issue(s);              // refill the stage just drained
                 if (!pr.valid()) pr.drained();
@@ -522,7 +527,9 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
             }
         }
         if (whole) continue;
+#ifdef FK_TUNING
         if (c == 0) stamp_raw(pr.tl(), 7);
+#endif
         __syncthreads();
         for (int q = wid; q < ct; q += nw) {                  // fold tile q of the chunk in warp order, then its epilogue
             if (t == 0) {
