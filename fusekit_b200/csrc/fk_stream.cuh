@@ -106,6 +106,15 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// shared-memory loads by 32-bit address: the choice between a group's digits and the zero vectors is then a SEL on an
+// address, where a choice between two generic pointers compiled to a divergent branch per group
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr)); return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr)); return v;
+}
+
 // ------------------------------------------------------------------ shared-memory plan of a streamed kernel
 struct StreamSmem {
     uint64_t *bars;     // [warps * stages]
@@ -339,21 +348,23 @@ __device__ __forceinline__ void unit_compute_q(const uint4 *u, const StreamSmem 
     int cc[3][4];                                    // [digit][fragment]: three independent MMA chains
 #pragma unroll
     for (int d = 0; d < 3; ++d) { cc[d][0] = cc[d][1] = cc[d][2] = cc[d][3] = 0; }
-    const uint2 *zero2 = reinterpret_cast<const uint2 *>(sm.zero);
+    // per group: 3 digits x 4 lanes x {16 or 8} bytes; lane t reads its vector of each digit, or zeros when the group is not its own
+    constexpr uint32_t GB = BITS == 4 ? 192u : 96u, DB = BITS == 4 ? 64u : 32u, LB = BITS == 4 ? 16u : 8u;
+    const uint32_t zaddr = smem_u32(sm.zero) + (uint32_t)t * LB;
+    const uint32_t xaddr = smem_u32(sm.xs) + (uint32_t)(sb * 8) * GB + (uint32_t)t * LB;
     FK_UNROLL(FK_J_UNROLL)
     for (int j = 0; j < 8; ++j) {
         const uint4 w = u[j * 32 + lane];
+        const uint32_t xa = (g == j) ? xaddr + (uint32_t)j * GB : zaddr;
         if (BITS == 4) {
-            const uint4 *xp = (g == j) ? reinterpret_cast<const uint4 *>(sm.xs + (size_t)(sb * 8 + j) * 24) : reinterpret_cast<const uint4 *>(sm.zero);
             // rows g (w.x word A, w.y word B) and g+8 (w.z, w.w): even nibbles -> k-slots 4t.., odd nibbles -> 4t+16..
             const uint32_t ea = w.x & 0x0F0F0F0Fu, oa = (w.x >> 4) & 0x0F0F0F0Fu, ea8 = w.z & 0x0F0F0F0Fu, oa8 = (w.z >> 4) & 0x0F0F0F0Fu;
             const uint32_t eb = w.y & 0x0F0F0F0Fu, ob = (w.y >> 4) & 0x0F0F0F0Fu, eb8 = w.w & 0x0F0F0F0Fu, ob8 = (w.w >> 4) & 0x0F0F0F0Fu;
-            const uint4 x0 = xp[t], x1 = xp[4 + t], x2 = xp[8 + t];     // digits 0..2: {A even, A odd, B even, B odd}
+            const uint4 x0 = lds128(xa), x1 = lds128(xa + DB), x2 = lds128(xa + 2 * DB);     // digits 0..2: {A even, A odd, B even, B odd}
             imma_uu(cc[0], ea, ea8, oa, oa8, x0.x, x0.y); imma_uu(cc[1], ea, ea8, oa, oa8, x1.x, x1.y); imma_us(cc[2], ea, ea8, oa, oa8, x2.x, x2.y);
             imma_uu(cc[0], eb, eb8, ob, ob8, x0.z, x0.w); imma_uu(cc[1], eb, eb8, ob, ob8, x1.z, x1.w); imma_us(cc[2], eb, eb8, ob, ob8, x2.z, x2.w);
         } else {
-            const uint2 *xp = (g == j) ? sm.xs + (size_t)(sb * 8 + j) * 12 : zero2;
-            const uint2 x0 = xp[t], x1 = xp[4 + t], x2 = xp[8 + t];     // digits 0..2: {word A, word B}
+            const uint2 x0 = lds64(xa), x1 = lds64(xa + DB), x2 = lds64(xa + 2 * DB);     // digits 0..2: {word A, word B}
             imma_uu(cc[0], w.x, w.z, w.y, w.w, x0.x, x0.y);
             imma_uu(cc[1], w.x, w.z, w.y, w.w, x1.x, x1.y);
             imma_us(cc[2], w.x, w.z, w.y, w.w, x2.x, x2.y);
