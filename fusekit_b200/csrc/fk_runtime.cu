@@ -90,7 +90,7 @@ struct Ctx {
     uint32_t *pinned = nullptr;                 // host staging for state / history
     std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
     bool pending = false; bool pdl = true; int sm_count = 148;
-    bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_tiles_from = 0; int dbg_mode = 0;
+    bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_cl = 0; int sdpa_tiles_from = 0; int dbg_mode = 0;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
@@ -140,6 +140,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     e = getenv("FK_SDPA"); if (e && !strcmp(e, "ticket")) c->sdpa_cluster = false;
     if (e && !strcmp(e, "mma")) c->sdpa_mma = true;
     if (e && !strcmp(e, "fma")) c->sdpa_mma = false;
+    e = getenv("FK_SDPA_CL"); if (e && (atoi(e) == 1 || atoi(e) == 2 || atoi(e) == 4 || atoi(e) == 8)) c->sdpa_cl = atoi(e);      // CTAs per kv head of the tensor-core attention
     e = getenv("FK_SDPA_TILES_FROM"); if (e) c->sdpa_tiles_from = atoi(e);      // capacity from which attention uses the tiled kernel (0 = never)
     e = getenv("FK_DBG"); if (e) c->dbg_mode = atoi(e);
     e = getenv("FK_WARPS"); if (e) c->force_warps = atoi(e);
@@ -589,10 +590,12 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         // the FMA kernel below is faster (11.0 against 12.1 us), so it runs only when asked for
         if (G <= 8 && (variant == 4 || (variant == 0 && hd <= 128 && c->sdpa_mma && c->sdpa_cluster))) {
             const size_t smem = sdpa_mma_smem_bytes(G, hd);
-            const dim3 cgrid(FK_SDPA_CL, nkv), cblock(FK_SDPA_CW * 32);
-            if (hd == 64) e = launch_cluster(c, k_sdpa_mma<64>, cgrid, cblock, smem, FK_SDPA_CL, (const FkState *)c->state, a);
-            else if (hd == 128) e = launch_cluster(c, k_sdpa_mma<128>, cgrid, cblock, smem, FK_SDPA_CL, (const FkState *)c->state, a);
-            else e = launch_cluster(c, k_sdpa_mma<256>, cgrid, cblock, smem, FK_SDPA_CL, (const FkState *)c->state, a);
+            // CTAs per kv head: 8 even for short caches (measured at 513 keys: 6.9 us with 8, 7.7 with 4, 10.6 with 2, 13.1 with 1)
+            const int cl = c->sdpa_cl > 0 ? c->sdpa_cl : FK_SDPA_CL;
+            const dim3 cgrid(cl, nkv), cblock(FK_SDPA_CW * 32);
+            if (hd == 64) e = launch_cluster(c, k_sdpa_mma<64>, cgrid, cblock, smem, cl, (const FkState *)c->state, a);
+            else if (hd == 128) e = launch_cluster(c, k_sdpa_mma<128>, cgrid, cblock, smem, cl, (const FkState *)c->state, a);
+            else e = launch_cluster(c, k_sdpa_mma<256>, cgrid, cblock, smem, cl, (const FkState *)c->state, a);
             break;
         }
         if (variant != 2 && c->sdpa_cluster && (hd != 256 || G <= 2)) {
