@@ -10,9 +10,10 @@
 // Arithmetic: integer tensor cores, exact.  The activations of a quantisation group (bf16, 8 significant bits)
 // are scaled by a power of two so the largest lands in [2^20, 2^21), rounded to integers (exact for everything
 // within 2^-13 of the group maximum, +-2^-21 of it below) and split into three 7-bit digits d0, d1 (unsigned) and
-// d2 (signed).  Packed nibbles become bytes four at a time (w & 0x0F0F0F0F and (w >> 4) & 0x0F0F0F0F: three ALU
-// ops per eight weights), 8-bit weights are used as stored, and mma.sync.m16n8k32 (u8 x u8/s8, s32 accumulate)
-// forms sum(q * digit) exactly; the three digit sums are recombined in fp32.  The tensor pipe is the dot-product
+// d2 (signed).  Packed nibbles become bytes four at a time with one AND each: w & 0x0F0F0F0F are the even nibbles,
+// w & 0xF0F0F0F0 the odd ones left in place as 16 q (two ALU ops per eight weights; their MMA chains are shifted back
+// by 4 when the digits are recombined); 8-bit weights are used as stored.  mma.sync.m16n8k32 (u8 x u8/s8, s32
+// accumulate) forms sum(q * digit) exactly; the digit sums are recombined in s32 (4 bit) or fp32 (8 bit).  The tensor pipe is the dot-product
 // unit because unpack + convert + FMA on the CUDA cores costs >2 issue slots per weight, more than an SM has at
 // HBM speed.  The eight groups of a unit go to the eight accumulator columns (the activations of group j sit in
 // B column j, zeros elsewhere), so after a unit every lane owns four (row, group) sums and applies
@@ -194,11 +195,13 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
     for (int i = 0; i < 8; ++i) xi[i] = __float2int_rn(f[i] * scale);
     if (BITS == 4) {
         const int grp = blk >> 3, bb = blk & 7;
-        uint2 *dst = sm.xs + (size_t)grp * 24 + (bb & 3) * 2 + (bb >> 2);        // [digit][lane][A|B], 8 uint2 per digit
-        dst[0] = make_uint2(pack4(xi[0] & 127, xi[2] & 127, xi[4] & 127, xi[6] & 127), pack4(xi[1] & 127, xi[3] & 127, xi[5] & 127, xi[7] & 127));
-        dst[8] = make_uint2(pack4((xi[0] >> 7) & 127, (xi[2] >> 7) & 127, (xi[4] >> 7) & 127, (xi[6] >> 7) & 127),
-                            pack4((xi[1] >> 7) & 127, (xi[3] >> 7) & 127, (xi[5] >> 7) & 127, (xi[7] >> 7) & 127));
-        dst[16] = make_uint2(pack4(xi[0] >> 14, xi[2] >> 14, xi[4] >> 14, xi[6] >> 14), pack4(xi[1] >> 14, xi[3] >> 14, xi[5] >> 14, xi[7] >> 14));
+        // [digit][lane t = bb & 3]{word A even, word B even, word A odd, word B odd}: the even nibbles of both words feed one MMA,
+        // the odd nibbles (used unshifted, as 16 q) the other
+        uint32_t *dst = reinterpret_cast<uint32_t *>(sm.xs) + (size_t)grp * 48 + (bb & 3) * 4 + (bb >> 2);
+        dst[0] = pack4(xi[0] & 127, xi[2] & 127, xi[4] & 127, xi[6] & 127); dst[2] = pack4(xi[1] & 127, xi[3] & 127, xi[5] & 127, xi[7] & 127);
+        dst[16] = pack4((xi[0] >> 7) & 127, (xi[2] >> 7) & 127, (xi[4] >> 7) & 127, (xi[6] >> 7) & 127);
+        dst[18] = pack4((xi[1] >> 7) & 127, (xi[3] >> 7) & 127, (xi[5] >> 7) & 127, (xi[7] >> 7) & 127);
+        dst[32] = pack4(xi[0] >> 14, xi[2] >> 14, xi[4] >> 14, xi[6] >> 14); dst[34] = pack4(xi[1] >> 14, xi[3] >> 14, xi[5] >> 14, xi[7] >> 14);
         if (bb == 0) sm.xsi[grp] = make_float2(s8, inv);
     } else {
         const int k0 = blk * 8, grp = k0 >> 5, o = k0 & 31, half = o >> 4, t = (o >> 2) & 3;
@@ -345,9 +348,12 @@ __device__ __forceinline__ void unit_compute_bf16(const uint4 *u, const StreamSm
 template <int BITS>
 __device__ __forceinline__ void unit_compute_q(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     const int g = lane >> 2, t = lane & 3;
-    int cc[3][4];                                    // [digit][fragment]: three independent MMA chains
+    // [digit][fragment] MMA chains; at 4 bits the odd nibbles are used in place (bytes 16 q) and accumulate in chains of their own
+    int cc[3][4], co[BITS == 4 ? 3 : 1][4];
 #pragma unroll
     for (int d = 0; d < 3; ++d) { cc[d][0] = cc[d][1] = cc[d][2] = cc[d][3] = 0; }
+#pragma unroll
+    for (int d = 0; d < (BITS == 4 ? 3 : 1); ++d) { co[d][0] = co[d][1] = co[d][2] = co[d][3] = 0; }
     // per group: 3 digits x 4 lanes x {16 or 8} bytes; lane t reads its vector of each digit, or zeros when the group is not its own
     constexpr uint32_t GB = BITS == 4 ? 192u : 96u, DB = BITS == 4 ? 64u : 32u, LB = BITS == 4 ? 16u : 8u;
     const uint32_t zaddr = smem_u32(sm.zero) + (uint32_t)t * LB;
@@ -357,12 +363,13 @@ __device__ __forceinline__ void unit_compute_q(const uint4 *u, const StreamSmem 
         const uint4 w = u[j * 32 + lane];
         const uint32_t xa = (g == j) ? xaddr + (uint32_t)j * GB : zaddr;
         if (BITS == 4) {
-            // rows g (w.x word A, w.y word B) and g+8 (w.z, w.w): even nibbles -> k-slots 4t.., odd nibbles -> 4t+16..
-            const uint32_t ea = w.x & 0x0F0F0F0Fu, oa = (w.x >> 4) & 0x0F0F0F0Fu, ea8 = w.z & 0x0F0F0F0Fu, oa8 = (w.z >> 4) & 0x0F0F0F0Fu;
-            const uint32_t eb = w.y & 0x0F0F0F0Fu, ob = (w.y >> 4) & 0x0F0F0F0Fu, eb8 = w.w & 0x0F0F0F0Fu, ob8 = (w.w >> 4) & 0x0F0F0F0Fu;
-            const uint4 x0 = lds128(xa), x1 = lds128(xa + DB), x2 = lds128(xa + 2 * DB);     // digits 0..2: {A even, A odd, B even, B odd}
-            imma_uu(cc[0], ea, ea8, oa, oa8, x0.x, x0.y); imma_uu(cc[1], ea, ea8, oa, oa8, x1.x, x1.y); imma_us(cc[2], ea, ea8, oa, oa8, x2.x, x2.y);
-            imma_uu(cc[0], eb, eb8, ob, ob8, x0.z, x0.w); imma_uu(cc[1], eb, eb8, ob, ob8, x1.z, x1.w); imma_us(cc[2], eb, eb8, ob, ob8, x2.z, x2.w);
+            // rows g (w.x word A, w.y word B) and g+8 (w.z, w.w).  Even MMA: k-slots 4t.. = word A even nibbles, 4t+16.. = word B even
+            // nibbles; odd MMA the same with the odd nibbles left in the high half of each byte (16 q, exact in u8 and in s32)
+            const uint32_t ea = w.x & 0x0F0F0F0Fu, oa = w.x & 0xF0F0F0F0u, ea8 = w.z & 0x0F0F0F0Fu, oa8 = w.z & 0xF0F0F0F0u;
+            const uint32_t eb = w.y & 0x0F0F0F0Fu, ob = w.y & 0xF0F0F0F0u, eb8 = w.w & 0x0F0F0F0Fu, ob8 = w.w & 0xF0F0F0F0u;
+            const uint4 x0 = lds128(xa), x1 = lds128(xa + DB), x2 = lds128(xa + 2 * DB);     // digits 0..2: {A even, B even, A odd, B odd}
+            imma_uu(cc[0], ea, ea8, eb, eb8, x0.x, x0.y); imma_uu(cc[1], ea, ea8, eb, eb8, x1.x, x1.y); imma_us(cc[2], ea, ea8, eb, eb8, x2.x, x2.y);
+            imma_uu(co[0], oa, oa8, ob, ob8, x0.z, x0.w); imma_uu(co[1], oa, oa8, ob, ob8, x1.z, x1.w); imma_us(co[2], oa, oa8, ob, ob8, x2.z, x2.w);
         } else {
             const uint2 x0 = lds64(xa), x1 = lds64(xa + DB), x2 = lds64(xa + 2 * DB);     // digits 0..2: {word A, word B}
             imma_uu(cc[0], w.x, w.z, w.y, w.w, x0.x, x0.y);
@@ -377,8 +384,12 @@ __device__ __forceinline__ void unit_compute_q(const uint4 *u, const StreamSmem 
     const float b00 = bf_lo(sb4.z), b01 = bf_hi(sb4.z), b10 = bf_lo(sb4.w), b11 = bf_hi(sb4.w);
     float c[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)      // digits recombined: (d0 + 128 d1) in s32, + 16384 d2 in fp32 (each part exact)
-        c[i] = fmaf(16384.0f, (float)cc[2][i], (float)(cc[0][i] + (cc[1][i] << 7)));
+    for (int i = 0; i < 4; ++i) {
+        if (BITS == 4)   // all six chains in s32 (|sum| < 2^31: 15 * 64 * 32 * 2^14 twice), one conversion: the same single rounding as below
+            c[i] = (float)(cc[0][i] + (cc[1][i] << 7) + (cc[2][i] << 14) + (co[0][i] >> 4) + (co[1][i] << 3) + (co[2][i] << 10));
+        else             // digits recombined: (d0 + 128 d1) in s32, + 16384 d2 in fp32 (each part exact)
+            c[i] = fmaf(16384.0f, (float)cc[2][i], (float)(cc[0][i] + (cc[1][i] << 7)));
+    }
     acc_lo = fmaf(s00, c[0] * i0, acc_lo); acc_lo = fmaf(b00, X0, acc_lo);
     acc_lo = fmaf(s01, c[1] * i1, acc_lo); acc_lo = fmaf(b01, X1, acc_lo);
     acc_hi = fmaf(s10, c[2] * i0, acc_hi); acc_hi = fmaf(b10, X0, acc_hi);
