@@ -7,6 +7,7 @@
 #include "fk_synth.cuh"
 #include "fk_stream.cuh"
 #include "fk_mega.cuh"
+#include "fk_qmm.cuh"
 
 #include <dlfcn.h>
 #include <math.h>
@@ -148,6 +149,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
 #define BIG4P(K) CU(big_smem(K<4, 8, true>)); CU(big_smem(K<4, 16, true>)); CU(big_smem(K<8, 8, true>)); CU(big_smem(K<8, 16, true>)); CU(big_smem(K<16, 8, true>)); CU(big_smem(K<16, 16, true>))
     BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head); BIG4P(k_s_rmsnorm_qkv); BIG4P(k_s_gateup); BIG4P(k_s_head);
     CU(big_smem(k_decode_token<4>)); CU(big_smem(k_decode_token<8>)); CU(big_smem(k_sdpa_tiles<64>)); CU(big_smem(k_sdpa_tiles<128>)); CU(big_smem(k_sdpa_mma<64>)); CU(big_smem(k_sdpa_mma<128>)); CU(big_smem(k_sdpa_mma<256>));
+    CU(big_smem(k_qmm4<1>)); CU(big_smem(k_qmm4<2>)); CU(big_smem(k_qmm4<4>)); CU(big_smem(k_qmm4<8>));
     CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
     CU(big_smem(k_linear_residual<4>)); CU(big_smem(k_linear_residual<8>)); CU(big_smem(k_linear_residual<16>));
@@ -615,6 +617,24 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         Weight *w = get_w(c, b[1]);
         if (!w || !w->finalized) return fail(FK_ERR_VALUE, "linear_residual: weight missing or not finalized");
         if (w->k != i[0] || w->n != i[1] || !b[0] || (!b[3] && !b[4])) return fail(FK_ERR_VALUE, "linear_residual: shape mismatch");
+        if (i[2] > 1) {                                    // 2..16 activation rows: the quantised matrix product
+            if (c->rec) return fail(FK_ERR_VALUE, "persistent program: one activation row only");
+            if (i[2] > FK_QMM_MAXM) return fail(FK_ERR_VALUE, "linear_residual: at most %d activation rows", FK_QMM_MAXM);
+            if (!w->tiled || w->bits != 4 || w->rows_kind != FK_ROWS_PLAIN || !b[3] || b[4])
+                return fail(FK_ERR_VALUE, "linear_residual with several rows takes streamed 4-bit weights in plain row order and a T output");
+            QmmArgs qa{(const uint16_t *)b[0], w->tview(), (const uint16_t *)b[2], (uint16_t *)b[3], i[2], i[0], i[1]};
+            // warps per tile: the smallest of 1, 2, 4, 8 whose block count covers (nearly) every block slot of the GPU
+            // (two blocks per SM fit up to 2 warps per tile, one beyond)
+            int wpt = 1;
+            while (wpt < 8 && ((long long)w->ntiles * wpt + 7) / 8 < (long long)c->sm_count * (wpt <= 2 ? 2 : 1) * 9 / 10) wpt *= 2;
+            const int want = (int)(((long long)w->ntiles * wpt + 7) / 8), slots = (wpt <= 2 ? 2 : 1) * c->sm_count;
+            const dim3 qgrid(want < slots ? want : slots), qblock(FK_QMM_WARPS * 32);
+            if (wpt == 1) e = launch(c, k_qmm4<1>, qgrid, qblock, qmm_smem_bytes(1), c->state, qa);
+            else if (wpt == 2) e = launch(c, k_qmm4<2>, qgrid, qblock, qmm_smem_bytes(2), c->state, qa);
+            else if (wpt == 4) e = launch(c, k_qmm4<4>, qgrid, qblock, qmm_smem_bytes(4), c->state, qa);
+            else e = launch(c, k_qmm4<8>, qgrid, qblock, qmm_smem_bytes(8), c->state, qa);
+            break;
+        }
         LinArgs a{(const uint16_t *)b[0], w->view(), (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], i[0], i[1]};
         if (w->tiled) {
             if (w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "linear_residual takes plain row order");

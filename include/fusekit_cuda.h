@@ -78,6 +78,9 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      2 = global partials + ticket, 3 = shared-memory tiles + ticket, 4 = tensor-core cluster)   f0 scale
  *                      partials: n_q * ceil(capacity / 32) * (head_dim + 2) floats; counter: n_kv words, zero before first use
  * LINEAR_RESIDUAL      buf0 x T[K]  buf1 weight  buf2 residual|0  buf3 y_out T[N]  buf4 y_f32_out|0   i0 K  i1 N
+ *                      i2 activation rows M (0 or 1: one row).  M = 2..16: x is T[M, K], residual and y_out are T[M, N], row m
+ *                      is the result the one-row task gives for x[m] (reference: the fusekit_qmm tiles for M > 1,
+ *                      src/codegen/msl.rs:2318-2439, chosen in kernels/mod.rs:1442-1473); streamed 4-bit weights only
  * RMSNORM_GATEUP_ACT   buf0 x  buf1 norm_w  buf2 weight(gate)  buf3 weight(up)  buf4 act_out T[I]
  *                      buf9..11 pending (as RMSNORM_QKV)     i0 H  i1 I  i2 act   f0 eps
  * FINAL_RMSNORM_LM_HEAD buf0 x  buf1 norm_w  buf2 weight(head)  buf3 logits_out|0  buf4 argmax scratch(u64)

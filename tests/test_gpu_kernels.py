@@ -99,6 +99,33 @@ def test_linear_residual(runtime, bits, k, n, residual):
     assert_close_bf16(runtime.download(yd, (n,), np.uint16), want, f"linear q{bits} {k}->{n}")
 
 
+@pytest.mark.parametrize("m", [2, 5, 8, 13, 16])
+@pytest.mark.parametrize("k,n", [(896, 1152), (896, 100), (4864, 896), (3584, 4736), (18944, 96), (64, 8), (512, 4800), (256, 9600), (320, 17088), (128, 34304)])
+@pytest.mark.parametrize("residual", [False, True])
+def test_linear_residual_rows(runtime, m, k, n, residual):
+    """2..16 activation rows through one weight: row i equals the one-row task's result for x[i] (the oracle of a batch)."""
+    w = O.gen_weight(stream_id(1, f"qmm.{k}.{n}"), n, k, 4)
+    x, res = normal(f"qx{k}.{m}", m * k).reshape(m, k), normal(f"qr{n}.{m}", m * n).reshape(m, n)
+    want = np.stack([O.qmatvec(w, x[i], res[i] if residual else None) for i in range(m)])
+    xd, yd = runtime.to_device(x), runtime.alloc(m * n * 2)
+    rd = runtime.to_device(res) if residual else 0
+    runtime.launch(T(N.TASK_LINEAR_RESIDUAL, 0, {0: xd, 1: dev_weight(runtime, w), 2: rd, 3: yd}, [k, n, m]))
+    got = runtime.download(yd, (m, n), np.uint16)
+    for i in range(m):
+        assert_close_bf16(got[i], want[i], f"qmm row {i}/{m} {k}->{n}")
+    assert runtime.state_get()[2] == 0
+
+
+def test_linear_residual_rows_refusals(runtime):
+    rt = runtime
+    w8 = O.gen_weight(stream_id(1, "qmm8"), 16, 64, 8)
+    with pytest.raises(N.FusekitError, match="4-bit"):
+        rt.launch(T(N.TASK_LINEAR_RESIDUAL, 0, {0: rt.alloc(4 * 64 * 2), 1: dev_weight(rt, w8), 3: rt.alloc(4 * 16 * 2)}, [64, 16, 4]))
+    w4 = O.gen_weight(stream_id(1, "qmm4"), 16, 64, 4)
+    with pytest.raises(N.FusekitError, match="at most 16"):
+        rt.launch(T(N.TASK_LINEAR_RESIDUAL, 0, {0: rt.alloc(17 * 64 * 2), 1: dev_weight(rt, w4), 3: rt.alloc(17 * 16 * 2)}, [64, 16, 17]))
+
+
 @pytest.mark.parametrize("bits", [4, 8, 16])
 @pytest.mark.parametrize("h,nq,nkv,hd,pos,cap", [(896, 14, 2, 64, 37, 64), (512, 4, 2, 128, 700, 512), (256, 2, 1, 256, 5, 16)])
 def test_rmsnorm_qkv_rope_store(runtime, bits, h, nq, nkv, hd, pos, cap):
