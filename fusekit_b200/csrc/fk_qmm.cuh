@@ -2,7 +2,7 @@
 //
 // Reference: the M > 1 tiles `fusekit_qmm_*` (src/codegen/msl.rs:2318-2439, 3821-4332; selection kernels/mod.rs:1442-1473),
 // used by the reference for prefill chunks and multi-token verify rows; a batch of independent decode rows has no
-// reference implementation, its oracle is M independent batch-1 matvecs.
+// reference implementation: row m of the result is checked against the batch-1 matvec of x[m].
 //
 // The weights stream exactly as in the batch-1 engine (same units of 16 rows x 8 groups, one TMA copy each, a ring per
 // warp).  The arithmetic is mma.sync.m16n8k16 on bf16 with exact products: a nibble q becomes the bf16 number 128 + q
