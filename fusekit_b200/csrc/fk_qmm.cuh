@@ -13,12 +13,10 @@
 // warps of a block: the chunk's activations sit in shared memory in B-operand order (a lane's eight k values permuted
 // 0,4,1,5,2,6,3,7 to match the nibble pairs above) with the per-group sums beside them.
 //
-// WPT warps share a tile and split its units between them (unit sb goes to warp sb % WPT), so that a weight of few
-// tiles still fills the GPU; their partial sums are folded through shared memory.  WPT = 1: 8 tiles per block, chunks
-// double buffered, two blocks per SM.  WPT = 2, 4, 8: 4, 2, 1 tiles per block, WPT chunks staged per step, two blocks per SM
-// for WPT = 2 and one beyond.
-// The fewer tiles a block holds the more often the activations are re-read from L2 (WPT = 8: 32 B of activations per
-// 8 B of weights), which is what bounds the small-N shapes.
+// A block holds 8 tiles (one per warp), so a chunk of activations staged once serves 128 weight rows.  A weight of few
+// tiles is split along K instead: `kparts` blocks share a set of 8 tiles, each walks its share of the chunks, writes its
+// fp32 partial sums to a scratch area and takes a ticket; the block that draws the last ticket adds the partials in
+// part order (the same order whichever block that is) and writes the rows.
 #pragma once
 #include "fk_stream.cuh"
 
@@ -27,36 +25,34 @@
 #define FK_QMM_KC 512                               // activations per chunk = per unit at 4 bits
 #define FK_QMM_XSTRIDE (FK_QMM_KC * 2 + 64)         // bytes per activation row of a chunk: 16-byte reads of a quarter warp hit distinct banks
 #define FK_QMM_CHUNK (FK_QMM_MAXM * FK_QMM_XSTRIDE) // bytes per staged chunk
+#define FK_QMM_PART_FLOATS (FK_QMM_WARPS * 8 * 32)  // partial sums one block leaves in the scratch area
 
-struct QmmArgs { const uint16_t *x; TiledW W; const uint16_t *residual; uint16_t *y; int m, k, n; };
+// scratch: gridDim.x * FK_QMM_PART_FLOATS floats; counters: one per set of 8 tiles, zero before the launch and after it
+struct QmmArgs { const uint16_t *x; TiledW W; const uint16_t *residual; uint16_t *y; float *scratch; unsigned int *counters; int m, k, n, kparts; };
 
-__host__ __device__ inline int qmm_xbufs(int wpt) { return wpt == 1 ? 2 : 1; }
-__host__ __device__ inline size_t qmm_smem_bytes(int wpt) {
-    return 256 /*bars*/ + (size_t)qmm_xbufs(wpt) * wpt * (FK_QMM_CHUNK + FK_QMM_MAXM * 8 * 4 /*group sums*/) +
-           (size_t)FK_QMM_WARPS * FK_STAGES * FK_UNIT_BYTES + 128;
+__host__ __device__ inline size_t qmm_smem_bytes() {
+    return 256 /*bars*/ + 2 * (size_t)(FK_QMM_CHUNK + FK_QMM_MAXM * 8 * 4 /*group sums*/) + (size_t)FK_QMM_WARPS * FK_STAGES * FK_UNIT_BYTES + 128;
 }
 
-template <int WPT>
-__global__ void __launch_bounds__(FK_QMM_WARPS * 32, WPT <= 2 ? 2 : 1) k_qmm4(FkState *st, QmmArgs a) {
-    constexpr int TPB = FK_QMM_WARPS / WPT, XBUFS = WPT == 1 ? 2 : 1;
+__global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmArgs a) {
     extern __shared__ __align__(128) unsigned char smem_stream[];
+    __shared__ int s_last;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_stream);
-    unsigned char *xs = smem_stream + 256;                                             // [XBUFS][WPT][16][XSTRIDE]
-    float *sx = reinterpret_cast<float *>(xs + (size_t)XBUFS * WPT * FK_QMM_CHUNK);     // [XBUFS][WPT][16][8]
-    uint4 *ring = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(sx) + XBUFS * WPT * FK_QMM_MAXM * 8 * 4);
+    unsigned char *xs = smem_stream + 256;                                             // [2][16][XSTRIDE]
+    float *sx = reinterpret_cast<float *>(xs + 2 * (size_t)FK_QMM_CHUNK);               // [2][16][8]
+    uint4 *ring = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(sx) + 2 * FK_QMM_MAXM * 8 * 4);
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, g = lane >> 2, t = lane & 3;
-    const int slot = wid / WPT, part = wid % WPT;                            // which of the block's tiles, which share of its units
-    const int nsb = a.W.nsb, ntiles = a.W.ntiles, nbs = a.m > 8 ? 2 : 1, rows = nbs * 8;
+    const int nsb = a.W.nsb, ntiles = a.W.ntiles, nbs = a.m > 8 ? 2 : 1;
+    const int S = a.kparts, kp = (int)blockIdx.x % S, bset = (int)blockIdx.x / S, nsets = (int)gridDim.x / S;
     uint64_t *wbar = bars + wid * FK_STAGES;
     uint4 *wring = ring + (size_t)wid * FK_STAGES * FK_UNIT_VEC;
     if (lane == 0) { for (int s = 0; s < FK_STAGES; ++s) mbar_init(wbar + s, 1); mbar_fence_init(); }
     __syncwarp();
-    const int stride = (int)gridDim.x * TPB, first = (int)blockIdx.x * TPB + slot;
-    const int rounds = (ntiles + stride - 1) / stride;                       // of the block: every warp walks them all
-    const int nss = (nsb + WPT - 1) / WPT;                                   // steps per round: WPT units of each tile per step
-    const int per_tile = part < nsb ? (nsb - part + WPT - 1) / WPT : 0;
-    const int total = first < ntiles ? ((ntiles - 1 - first) / stride + 1) * per_tile : 0;   // units of this warp
-    int issued = 0, consumed = 0, ptile = first, psb = part;
+    const int stride = nsets * FK_QMM_WARPS, first = bset * FK_QMM_WARPS + wid;
+    const int rounds = (ntiles + stride - 1) / stride;                       // of the block (1 when K is split): every warp walks them all
+    const int ss0 = (int)((long long)kp * nsb / S), ss1 = (int)((long long)(kp + 1) * nsb / S);   // this block's chunks of K
+    const int total = first < ntiles ? ((ntiles - 1 - first) / stride + 1) * (ss1 - ss0) : 0;      // units of this warp
+    int issued = 0, consumed = 0, ptile = first, psb = ss0;
     bool ok = true;
     auto issue = [&]() {
         if (lane == 0) {
@@ -64,31 +60,27 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, WPT <= 2 ? 2 : 1) k_qmm4(Fk
             mbar_expect_tx(wbar + s, FK_UNIT_BYTES);
             bulk_g2s(wring + (size_t)s * FK_UNIT_VEC, a.W.units + ((size_t)ptile * nsb + psb) * FK_UNIT_VEC, FK_UNIT_BYTES, wbar + s);
         }
-        psb += WPT;
-        if (psb >= nsb) { psb = part; ptile += stride; }
+        if (++psb == ss1) { psb = ss0; ptile += stride; }
         ++issued;
     };
     while (issued < FK_STAGES && issued < total) issue();                    // weights are constants: fetched before the wait below
     pdl_wait();
-    // Staging of the WPT chunks of step `ss`: item = 8 consecutive k of one row.  Loads (four items per thread and batch)
-    // are separate from the permute + store, so that several loads are in flight and the arithmetic of a step can sit
-    // between the two.
-    const int pc_shift = nbs == 2 ? 10 : 9, per_chunk = 1 << pc_shift /* rows * 64 items */, items = WPT * per_chunk, nbatch = (items + FK_QMM_WARPS * 32 * 4 - 1) / (FK_QMM_WARPS * 32 * 4);
-    auto stage_load = [&](int ss, int batch, uint4 (&v)[4]) {
+    // Staging of chunk `ss`: item = 8 consecutive k of one row, four items per thread (two when 8 rows are enough).  The
+    // loads are separate from the permute + store so that the arithmetic of a step sits between the two.
+    const int items = nbs * 8 * (FK_QMM_KC / 8);
+    auto stage_load = [&](int ss, uint4 (&v)[4]) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const int idx = tid + (batch * 4 + q) * FK_QMM_WARPS * 32;
-            const int c = idx >> pc_shift, rem = idx & (per_chunk - 1), m = rem >> 6, item = rem & 63;
-            const int k0 = (ss * WPT + c) * FK_QMM_KC + item * 8;
+            const int idx = tid + q * FK_QMM_WARPS * 32, m = idx >> 6, item = idx & 63;
+            const int k0 = ss * FK_QMM_KC + item * 8;
             v[q] = make_uint4(0, 0, 0, 0);
             if (idx < items && m < a.m && k0 < a.k) v[q] = __ldcg(reinterpret_cast<const uint4 *>(a.x + (size_t)m * a.k + k0));
         }
     };
-    auto stage_store = [&](int buf, int batch, const uint4 (&v)[4]) {
+    auto stage_store = [&](int buf, const uint4 (&v)[4]) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const int idx = tid + (batch * 4 + q) * FK_QMM_WARPS * 32;
-            const int c = idx >> pc_shift, rem = idx & (per_chunk - 1), m = rem >> 6, item = rem & 63;
+            const int idx = tid + q * FK_QMM_WARPS * 32, m = idx >> 6, item = idx & 63;
             const uint32_t h[4] = {v[q].x, v[q].y, v[q].z, v[q].w};      // (x0,x1) (x2,x3) (x4,x5) (x6,x7)
             float s8 = bf_lo(h[0]) + bf_hi(h[0]) + bf_lo(h[1]) + bf_hi(h[1]) + bf_lo(h[2]) + bf_hi(h[2]) + bf_lo(h[3]) + bf_hi(h[3]);
             s8 += __shfl_xor_sync(0xffffffffu, s8, 1); s8 += __shfl_xor_sync(0xffffffffu, s8, 2); s8 += __shfl_xor_sync(0xffffffffu, s8, 4);
@@ -96,16 +88,9 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, WPT <= 2 ? 2 : 1) k_qmm4(Fk
                 uint4 o;                                                 // B-operand order 0,4 | 1,5 | 2,6 | 3,7
                 o.x = (h[0] & 0xffffu) | (h[2] << 16); o.y = (h[0] >> 16) | (h[2] & 0xffff0000u);
                 o.z = (h[1] & 0xffffu) | (h[3] << 16); o.w = (h[1] >> 16) | (h[3] & 0xffff0000u);
-                *reinterpret_cast<uint4 *>(xs + (size_t)(buf * WPT + c) * FK_QMM_CHUNK + (size_t)m * FK_QMM_XSTRIDE + item * 16) = o;
-                if ((item & 7) == 0) sx[((buf * WPT + c) * FK_QMM_MAXM + m) * 8 + (item >> 3)] = s8;
+                *reinterpret_cast<uint4 *>(xs + (size_t)buf * FK_QMM_CHUNK + (size_t)m * FK_QMM_XSTRIDE + item * 16) = o;
+                if ((item & 7) == 0) sx[(buf * FK_QMM_MAXM + m) * 8 + (item >> 3)] = s8;
             }
-        }
-    };
-    auto stage_all = [&](int ss, int buf) {                                  // eight loads in flight per thread
-        for (int bt = 0; bt < nbatch; bt += 2) {
-            uint4 va[4], vb[4];
-            stage_load(ss, bt, va); stage_load(ss, bt + 1, vb);
-            stage_store(buf, bt, va); stage_store(buf, bt + 1, vb);
         }
     };
     for (int r = 0; r < rounds; ++r) {
@@ -114,19 +99,19 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, WPT <= 2 ? 2 : 1) k_qmm4(Fk
         float acc[2][4];
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) { acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.0f; }
-        uint4 nxt[4];                                                    // WPT = 1: the next chunk on its way (one batch: 16 rows x 64 items)
-        if (XBUFS == 2) { stage_all(0, 0); __syncthreads(); }
-        for (int ss = 0; ss < nss; ++ss) {
-            const int buf = XBUFS == 2 ? (ss & 1) : 0;
-            if (XBUFS == 2) { if (ss + 1 < nss) stage_load(ss + 1, 0, nxt); }  // loaded under this step's arithmetic, stored after it
-            else { stage_all(ss, 0); __syncthreads(); }
-            if (have && ok && ss * WPT + part < nsb) {
+        uint4 nxt[4];                                                    // the next chunk on its way
+        stage_load(ss0, nxt); stage_store(0, nxt);
+        __syncthreads();
+        for (int ss = ss0; ss < ss1; ++ss) {
+            const int buf = (ss - ss0) & 1;
+            if (ss + 1 < ss1) stage_load(ss + 1, nxt);                   // loaded under this step's arithmetic, stored after it
+            if (have && ok) {
                 const int s = consumed & (FK_STAGES - 1);
                 if (!mbar_wait(wbar + s, (uint32_t)(consumed >> 1) & 1u)) ok = false;
                 if (ok) {
                     const uint4 *u = wring + (size_t)s * FK_UNIT_VEC;
-                    const unsigned char *xb = xs + (size_t)(buf * WPT + part) * FK_QMM_CHUNK;
-                    const float *sums = sx + (buf * WPT + part) * FK_QMM_MAXM * 8;
+                    const unsigned char *xb = xs + (size_t)buf * FK_QMM_CHUNK;
+                    const float *sums = sx + buf * FK_QMM_MAXM * 8;
 #pragma unroll 2
                     for (int j = 0; j < 8; ++j) {
                         const uint4 w = u[j * 32 + lane];                // {word A row g, word B row g, word A row g+8, word B row g+8}
@@ -169,8 +154,8 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, WPT <= 2 ? 2 : 1) k_qmm4(Fk
                     ++consumed;
                 }
             }
-            if (XBUFS == 2 && ss + 1 < nss) stage_store(buf ^ 1, 0, nxt);      // the other buffer was last read in step ss - 1
-            __syncthreads();                                             // the chunks of this step are no longer read
+            if (ss + 1 < ss1) stage_store(buf ^ 1, nxt);                  // the other buffer was last read in step ss - 1
+            __syncthreads();                                             // chunk ss is no longer read, chunk ss + 1 is in place
         }
         auto emit = [&](int v, float val) {                              // value v = nb * 4 + i of this lane's fragment
             const int row = tile * 16 + g + ((v & 2) ? 8 : 0), m = (v >> 2) * 8 + 2 * t + (v & 1);
@@ -179,25 +164,36 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, WPT <= 2 ? 2 : 1) k_qmm4(Fk
                 a.y[(size_t)m * a.n + row] = f2bf(val);
             }
         };
-        if (WPT == 1) {
+        if (S == 1) {
             if (have) {
 #pragma unroll
                 for (int v = 0; v < 8; ++v) emit(v, acc[v >> 2][v & 3]);
             }
-        } else {
-            float *fold = reinterpret_cast<float *>(xs);                 // [warp][8 values][32 lanes], in the chunk area (idle now)
+        } else {                                                         // K split over S blocks (one round)
+            float *mine = a.scratch + ((size_t)blockIdx.x * FK_QMM_WARPS + wid) * 256;
 #pragma unroll
-            for (int v = 0; v < 8; ++v) fold[(wid * 8 + v) * 32 + lane] = acc[v >> 2][v & 3];
+            for (int v = 0; v < 8; ++v) __stcg(mine + v * 32 + lane, acc[v >> 2][v & 3]);
+            __threadfence();
             __syncthreads();
-            if (have) {
-                for (int v = part; v < 8; v += WPT) {                    // the tile's WPT warps share the 8 values per lane
-                    float sum = 0.0f;
-#pragma unroll
-                    for (int p = 0; p < WPT; ++p) sum += fold[((slot * WPT + p) * 8 + v) * 32 + lane];
-                    emit(v, sum);
-                }
+            if (tid == 0) {
+                const unsigned int ticket = atomicAdd(a.counters + bset, 1u);
+                s_last = ticket == (unsigned int)(S - 1);
+                if (s_last) a.counters[bset] = 0u;                       // every block of the set has arrived: ready for the next launch
             }
-            __syncthreads();                                             // before the next round stages over the fold area
+            __syncthreads();
+            if (s_last && have) {
+                __threadfence();
+                float sum[8];
+#pragma unroll
+                for (int v = 0; v < 8; ++v) sum[v] = 0.0f;
+                for (int p = 0; p < S; ++p) {                            // part order, whichever block does the adding
+                    const float *src = a.scratch + ((size_t)(bset * S + p) * FK_QMM_WARPS + wid) * 256;
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) sum[v] += __ldcg(src + v * 32 + lane);
+                }
+#pragma unroll
+                for (int v = 0; v < 8; ++v) emit(v, sum[v]);
+            }
         }
     }
     if (!ok) {                                                               // a wait ran out: give the copies in flight one more bounded wait each

@@ -91,6 +91,7 @@ struct Ctx {
     uint32_t *pinned = nullptr;                 // host staging for state / history
     std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
     bool pending = false; bool pdl = true; int sm_count = 148;
+    float *qmm_scratch = nullptr; unsigned int *qmm_counters = nullptr;   // K-split partial sums and tickets of the several-row projection
     bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_cl = 0; int sdpa_tiles_from = 0; int dbg_mode = 0;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
@@ -134,6 +135,8 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     CU(cudaEventCreate(&c->ev0)); CU(cudaEventCreate(&c->ev1));
     CU(cudaMalloc(&c->state, sizeof(FkState))); CU(cudaMemset(c->state, 0, sizeof(FkState)));
     c->hist_cap = FK_HIST_CAP;
+    CU(cudaMalloc(&c->qmm_scratch, sizeof(float) * 2 * c->sm_count * FK_QMM_PART_FLOATS));
+    CU(cudaMalloc(&c->qmm_counters, sizeof(unsigned int) * 2 * c->sm_count)); CU(cudaMemset(c->qmm_counters, 0, sizeof(unsigned int) * 2 * c->sm_count));
     CU(cudaMalloc(&c->history, sizeof(uint32_t) * c->hist_cap)); CU(cudaMemset(c->history, 0, sizeof(uint32_t) * c->hist_cap));
     CU(cudaMallocHost(&c->pinned, sizeof(uint32_t) * (c->hist_cap + 64)));
     const char *e = getenv("FK_PDL"); if (e && e[0] == '0') c->pdl = false;
@@ -149,7 +152,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
 #define BIG4P(K) CU(big_smem(K<4, 8, true>)); CU(big_smem(K<4, 16, true>)); CU(big_smem(K<8, 8, true>)); CU(big_smem(K<8, 16, true>)); CU(big_smem(K<16, 8, true>)); CU(big_smem(K<16, 16, true>))
     BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head); BIG4P(k_s_rmsnorm_qkv); BIG4P(k_s_gateup); BIG4P(k_s_head);
     CU(big_smem(k_decode_token<4>)); CU(big_smem(k_decode_token<8>)); CU(big_smem(k_sdpa_tiles<64>)); CU(big_smem(k_sdpa_tiles<128>)); CU(big_smem(k_sdpa_mma<64>)); CU(big_smem(k_sdpa_mma<128>)); CU(big_smem(k_sdpa_mma<256>));
-    CU(big_smem(k_qmm4<1>)); CU(big_smem(k_qmm4<2>)); CU(big_smem(k_qmm4<4>)); CU(big_smem(k_qmm4<8>));
+    CU(big_smem(k_qmm4));
     CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
     CU(big_smem(k_linear_residual<4>)); CU(big_smem(k_linear_residual<8>)); CU(big_smem(k_linear_residual<16>));
@@ -168,6 +171,7 @@ extern "C" fk_status fk_close(fk_handle h) {
     for (auto &w : c->weights) { cudaFree(w.w); cudaFree(w.s); cudaFree(w.b); cudaFree(w.units); }
     for (void *p : c->allocs) cudaFree(p);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
+    cudaFree(c->qmm_scratch); cudaFree(c->qmm_counters);
     cudaFree(c->state); cudaFree(c->history); cudaFreeHost(c->pinned);
     cudaEventDestroy(c->ev0); cudaEventDestroy(c->ev1); cudaStreamDestroy(c->stream);
     c->graphs.clear(); c->weights.clear(); c->allocs.clear(); c->open = false;
@@ -622,17 +626,13 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             if (i[2] > FK_QMM_MAXM) return fail(FK_ERR_VALUE, "linear_residual: at most %d activation rows", FK_QMM_MAXM);
             if (!w->tiled || w->bits != 4 || w->rows_kind != FK_ROWS_PLAIN || !b[3] || b[4])
                 return fail(FK_ERR_VALUE, "linear_residual with several rows takes streamed 4-bit weights in plain row order and a T output");
-            QmmArgs qa{(const uint16_t *)b[0], w->tview(), (const uint16_t *)b[2], (uint16_t *)b[3], i[2], i[0], i[1]};
-            // warps per tile: the smallest of 1, 2, 4, 8 whose block count covers (nearly) every block slot of the GPU
-            // (two blocks per SM fit up to 2 warps per tile, one beyond)
-            int wpt = 1;
-            while (wpt < 8 && ((long long)w->ntiles * wpt + 7) / 8 < (long long)c->sm_count * (wpt <= 2 ? 2 : 1) * 9 / 10) wpt *= 2;
-            const int want = (int)(((long long)w->ntiles * wpt + 7) / 8), slots = (wpt <= 2 ? 2 : 1) * c->sm_count;
-            const dim3 qgrid(want < slots ? want : slots), qblock(FK_QMM_WARPS * 32);
-            if (wpt == 1) e = launch(c, k_qmm4<1>, qgrid, qblock, qmm_smem_bytes(1), c->state, qa);
-            else if (wpt == 2) e = launch(c, k_qmm4<2>, qgrid, qblock, qmm_smem_bytes(2), c->state, qa);
-            else if (wpt == 4) e = launch(c, k_qmm4<4>, qgrid, qblock, qmm_smem_bytes(4), c->state, qa);
-            else e = launch(c, k_qmm4<8>, qgrid, qblock, qmm_smem_bytes(8), c->state, qa);
+            // 8 tiles per block; a weight with fewer sets of 8 tiles than block slots has K split over several blocks per set
+            const int sets = (w->ntiles + FK_QMM_WARPS - 1) / FK_QMM_WARPS, slots = 2 * c->sm_count;
+            int kparts = 1, qg = sets < slots ? sets : slots;
+            if (sets * 10 < slots * 9) { kparts = slots / sets; if (kparts > w->nsb) kparts = w->nsb; qg = sets * kparts; }
+            QmmArgs qa{(const uint16_t *)b[0], w->tview(), (const uint16_t *)b[2], (uint16_t *)b[3], c->qmm_scratch, c->qmm_counters,
+                       i[2], i[0], i[1], kparts};
+            e = launch(c, k_qmm4, dim3(qg), dim3(FK_QMM_WARPS * 32), qmm_smem_bytes(), c->state, qa);
             break;
         }
         LinArgs a{(const uint16_t *)b[0], w->view(), (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], i[0], i[1]};
