@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmA
     const int ss0 = (int)((long long)kp * nsb / S), ss1 = (int)((long long)(kp + 1) * nsb / S);   // this block's chunks of K
     const int total = first < ntiles ? ((ntiles - 1 - first) / stride + 1) * (ss1 - ss0) : 0;      // units of this warp
     int issued = 0, consumed = 0, ptile = first, psb = ss0;
-    bool ok = true;
+    bool ok = true, announced = false;
     auto issue = [&]() {
         if (lane == 0) {
             const int s = issued & (FK_STAGES - 1);
@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmA
                     }
                     __syncwarp();
                     if (issued < total) issue();                         // refill the stage just drained
+                    else if (!announced) { announced = true; pdl_launch_dependents(); }   // all of this warp's units are on their way
                     ++consumed;
                 }
             }
