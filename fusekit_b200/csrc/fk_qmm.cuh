@@ -28,15 +28,20 @@
 #define FK_QMM_PART_FLOATS (FK_QMM_WARPS * 8 * 32)  // partial sums one block leaves in the scratch area
 
 // scratch: gridDim.x * FK_QMM_PART_FLOATS floats; counters: one per set of 8 tiles, zero before the launch and after it
-struct QmmArgs { const uint16_t *x; TiledW W; const uint16_t *residual; uint16_t *y; float *scratch; unsigned int *counters; int m, k, n, kparts; };
+// GATEUP form: W holds gate/up row pairs (tile rows g = gate, g + 8 = up of output tile * 8 + g), x is normalised on the
+// way into shared memory (norm_w, eps), y[m][n] takes the activation (act: 0 SwiGLU, 1 GeGLU-tanh); n = outputs per row.
+struct QmmArgs { const uint16_t *x; TiledW W; const uint16_t *residual; uint16_t *y; float *scratch; unsigned int *counters; int m, k, n, kparts;
+                 const uint16_t *norm_w; float eps; int act; };
 
 __host__ __device__ inline size_t qmm_smem_bytes() {
     return 256 /*bars*/ + 2 * (size_t)(FK_QMM_CHUNK + FK_QMM_MAXM * 8 * 4 /*group sums*/) + (size_t)FK_QMM_WARPS * FK_STAGES * FK_UNIT_BYTES + 128;
 }
 
+template <bool GATEUP>
 __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmArgs a) {
     extern __shared__ __align__(128) unsigned char smem_stream[];
     __shared__ int s_last;
+    __shared__ float s_r[FK_QMM_MAXM];                                      // GATEUP: 1 / rms of each activation row
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_stream);
     unsigned char *xs = smem_stream + 256;                                             // [2][16][XSTRIDE]
     float *sx = reinterpret_cast<float *>(xs + 2 * (size_t)FK_QMM_CHUNK);               // [2][16][8]
@@ -65,10 +70,36 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmA
     };
     while (issued < FK_STAGES && issued < total) issue();                    // weights are constants: fetched before the wait below
     pdl_wait();
+    if (GATEUP) {                                                            // RMSNorm scale of every row, over the whole of K
+        if (tid < FK_QMM_MAXM && tid >= a.m) s_r[tid] = 0.0f;
+        for (int mm = wid; mm < a.m; mm += FK_QMM_WARPS) {
+            float ss = 0.0f;
+            const uint4 *xr = reinterpret_cast<const uint4 *>(a.x + (size_t)mm * a.k);
+            for (int v0 = lane; v0 < (a.k >> 3); v0 += 32 * 8) {         // eight loads in flight per lane
+                uint4 xv[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) xv[u] = v0 + 32 * u < (a.k >> 3) ? __ldcg(xr + v0 + 32 * u) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    float f[8]; unpack8(xv[u], f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) s_r[mm] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.k), a.eps)));
+        }
+        __syncthreads();
+    }
     // Staging of chunk `ss`: item = 8 consecutive k of one row, four items per thread (two when 8 rows are enough).  The
     // loads are separate from the permute + store so that the arithmetic of a step sits between the two.
     const int items = nbs * 8 * (FK_QMM_KC / 8);
-    auto stage_load = [&](int ss, uint4 (&v)[4]) {
+    auto stage_load = [&](int ss, uint4 (&v)[4], uint4 &wv) {
+        if (GATEUP) {                                                        // a thread's four items share their k range: one vector of norm weights
+            const int k0 = ss * FK_QMM_KC + (tid & 63) * 8;
+            wv = k0 < a.k ? __ldg(reinterpret_cast<const uint4 *>(a.norm_w + k0)) : make_uint4(0, 0, 0, 0);
+        }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int idx = tid + q * FK_QMM_WARPS * 32, m = idx >> 6, item = idx & 63;
@@ -77,11 +108,17 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmA
             if (idx < items && m < a.m && k0 < a.k) v[q] = __ldcg(reinterpret_cast<const uint4 *>(a.x + (size_t)m * a.k + k0));
         }
     };
-    auto stage_store = [&](int buf, const uint4 (&v)[4]) {
+    auto stage_store = [&](int buf, const uint4 (&v)[4], const uint4 &wv) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int idx = tid + q * FK_QMM_WARPS * 32, m = idx >> 6, item = idx & 63;
-            const uint32_t h[4] = {v[q].x, v[q].y, v[q].z, v[q].w};      // (x0,x1) (x2,x3) (x4,x5) (x6,x7)
+            uint32_t h[4] = {v[q].x, v[q].y, v[q].z, v[q].w};            // (x0,x1) (x2,x3) (x4,x5) (x6,x7)
+            if (GATEUP) {                                                // y = T(w * T(x * r)), two roundings as in the one-row kernel
+                float f[8], wf[8]; unpack8(v[q], f); unpack8(wv, wf);
+                const float r = s_r[m & (FK_QMM_MAXM - 1)];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = (uint32_t)f2bf(wf[2 * j] * rT(f[2 * j] * r)) | ((uint32_t)f2bf(wf[2 * j + 1] * rT(f[2 * j + 1] * r)) << 16);
+            }
             float s8 = bf_lo(h[0]) + bf_hi(h[0]) + bf_lo(h[1]) + bf_hi(h[1]) + bf_lo(h[2]) + bf_hi(h[2]) + bf_lo(h[3]) + bf_hi(h[3]);
             s8 += __shfl_xor_sync(0xffffffffu, s8, 1); s8 += __shfl_xor_sync(0xffffffffu, s8, 2); s8 += __shfl_xor_sync(0xffffffffu, s8, 4);
             if (idx < items) {
@@ -99,12 +136,12 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmA
         float acc[2][4];
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) { acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.0f; }
-        uint4 nxt[4];                                                    // the next chunk on its way
-        stage_load(ss0, nxt); stage_store(0, nxt);
+        uint4 nxt[4], nxw = make_uint4(0, 0, 0, 0);                      // the next chunk on its way
+        stage_load(ss0, nxt, nxw); stage_store(0, nxt, nxw);
         __syncthreads();
         for (int ss = ss0; ss < ss1; ++ss) {
             const int buf = (ss - ss0) & 1;
-            if (ss + 1 < ss1) stage_load(ss + 1, nxt);                   // loaded under this step's arithmetic, stored after it
+            if (ss + 1 < ss1) stage_load(ss + 1, nxt, nxw);                   // loaded under this step's arithmetic, stored after it
             if (have && ok) {
                 const int s = consumed & (FK_STAGES - 1);
                 if (!mbar_wait(wbar + s, (uint32_t)(consumed >> 1) & 1u)) ok = false;
@@ -155,20 +192,32 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmA
                     ++consumed;
                 }
             }
-            if (ss + 1 < ss1) stage_store(buf ^ 1, nxt);                  // the other buffer was last read in step ss - 1
+            if (ss + 1 < ss1) stage_store(buf ^ 1, nxt, nxw);                  // the other buffer was last read in step ss - 1
             __syncthreads();                                             // chunk ss is no longer read, chunk ss + 1 is in place
         }
-        auto emit = [&](int v, float val) {                              // value v = nb * 4 + i of this lane's fragment
-            const int row = tile * 16 + g + ((v & 2) ? 8 : 0), m = (v >> 2) * 8 + 2 * t + (v & 1);
-            if (row < a.n && m < a.m) {
-                if (a.residual) val += bf2f(__ldcg(a.residual + (size_t)m * a.n + row));
-                a.y[(size_t)m * a.n + row] = f2bf(val);
+        // val[nb * 4 + i]: rows g (i = 0, 1) and g + 8 (i = 2, 3) of the tile against activation rows nb * 8 + 2 t + (i & 1)
+        auto finish = [&](const float (&val)[8]) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                const int m = (v >> 2) * 8 + 2 * t + (v & 1);
+                if (GATEUP) {
+                    const int out = tile * 8 + g;
+                    if (!(v & 2) && out < a.n && m < a.m)
+                        a.y[(size_t)m * a.n + out] = a.act == 1 ? s_act_geglu(val[v], val[v + 2]) : s_act_swiglu(val[v], val[v + 2]);
+                } else {
+                    const int row = tile * 16 + g + ((v & 2) ? 8 : 0);
+                    if (row < a.n && m < a.m) {
+                        float o = val[v];
+                        if (a.residual) o += bf2f(__ldcg(a.residual + (size_t)m * a.n + row));
+                        a.y[(size_t)m * a.n + row] = f2bf(o);
+                    }
+                }
             }
         };
         if (S == 1) {
             if (have) {
-#pragma unroll
-                for (int v = 0; v < 8; ++v) emit(v, acc[v >> 2][v & 3]);
+                const float val[8] = {acc[0][0], acc[0][1], acc[0][2], acc[0][3], acc[1][0], acc[1][1], acc[1][2], acc[1][3]};
+                finish(val);
             }
         } else {                                                         // K split over S blocks (one round)
             float *mine = a.scratch + ((size_t)blockIdx.x * FK_QMM_WARPS + wid) * 256;
@@ -192,8 +241,7 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmA
 #pragma unroll
                     for (int v = 0; v < 8; ++v) sum[v] += __ldcg(src + v * 32 + lane);
                 }
-#pragma unroll
-                for (int v = 0; v < 8; ++v) emit(v, sum[v]);
+                finish(sum);
             }
         }
     }

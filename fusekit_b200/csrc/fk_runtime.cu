@@ -152,7 +152,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
 #define BIG4P(K) CU(big_smem(K<4, 8, true>)); CU(big_smem(K<4, 16, true>)); CU(big_smem(K<8, 8, true>)); CU(big_smem(K<8, 16, true>)); CU(big_smem(K<16, 8, true>)); CU(big_smem(K<16, 16, true>))
     BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head); BIG4P(k_s_rmsnorm_qkv); BIG4P(k_s_gateup); BIG4P(k_s_head);
     CU(big_smem(k_decode_token<4>)); CU(big_smem(k_decode_token<8>)); CU(big_smem(k_sdpa_tiles<64>)); CU(big_smem(k_sdpa_tiles<128>)); CU(big_smem(k_sdpa_mma<64>)); CU(big_smem(k_sdpa_mma<128>)); CU(big_smem(k_sdpa_mma<256>));
-    CU(big_smem(k_qmm4));
+    CU(big_smem(k_qmm4<false>)); CU(big_smem(k_qmm4<true>));
     CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
     CU(big_smem(k_linear_residual<4>)); CU(big_smem(k_linear_residual<8>)); CU(big_smem(k_linear_residual<16>));
@@ -403,6 +403,16 @@ static cudaError_t launch_cluster(Ctx *c, void (*kern)(KA...), dim3 grid, dim3 b
     c->launches++;
     return cudaLaunchKernelEx(&cfg, kern, KA(args)...);
 }
+// the several-row projection: 8 tiles per block; a weight with fewer sets of 8 tiles than block slots has K split over
+// several blocks per set
+static cudaError_t launch_qmm(Ctx *c, const Weight *w, QmmArgs &qa, bool gateup) {
+    const int sets = (w->ntiles + FK_QMM_WARPS - 1) / FK_QMM_WARPS, slots = 2 * c->sm_count;
+    int kparts = 1, qg = sets < slots ? sets : slots;
+    if (sets * 10 < slots * 9) { kparts = slots / sets; if (kparts > w->nsb) kparts = w->nsb; qg = sets * kparts; }
+    qa.kparts = kparts;
+    if (gateup) return launch(c, k_qmm4<true>, dim3(qg), dim3(FK_QMM_WARPS * 32), qmm_smem_bytes(), c->state, qa);
+    return launch(c, k_qmm4<false>, dim3(qg), dim3(FK_QMM_WARPS * 32), qmm_smem_bytes(), c->state, qa);
+}
 #define BITS_SWITCH(bits, CALL)                  \
     switch (bits) {                              \
         case 4: { constexpr int B = 4; CALL; break; }   \
@@ -626,13 +636,9 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             if (i[2] > FK_QMM_MAXM) return fail(FK_ERR_VALUE, "linear_residual: at most %d activation rows", FK_QMM_MAXM);
             if (!w->tiled || w->bits != 4 || w->rows_kind != FK_ROWS_PLAIN || !b[3] || b[4])
                 return fail(FK_ERR_VALUE, "linear_residual with several rows takes streamed 4-bit weights in plain row order and a T output");
-            // 8 tiles per block; a weight with fewer sets of 8 tiles than block slots has K split over several blocks per set
-            const int sets = (w->ntiles + FK_QMM_WARPS - 1) / FK_QMM_WARPS, slots = 2 * c->sm_count;
-            int kparts = 1, qg = sets < slots ? sets : slots;
-            if (sets * 10 < slots * 9) { kparts = slots / sets; if (kparts > w->nsb) kparts = w->nsb; qg = sets * kparts; }
             QmmArgs qa{(const uint16_t *)b[0], w->tview(), (const uint16_t *)b[2], (uint16_t *)b[3], c->qmm_scratch, c->qmm_counters,
-                       i[2], i[0], i[1], kparts};
-            e = launch(c, k_qmm4, dim3(qg), dim3(FK_QMM_WARPS * 32), qmm_smem_bytes(), c->state, qa);
+                       i[2], i[0], i[1], 1, nullptr, 0.0f, 0};
+            e = launch_qmm(c, w, qa, false);
             break;
         }
         LinArgs a{(const uint16_t *)b[0], w->view(), (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], i[0], i[1]};
@@ -657,6 +663,15 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         Weight *wg = get_w(c, b[2]), *wu = get_w(c, b[3]);
         if (wg && wg->tiled && wg->rows_kind == FK_ROWS_GATE_UP) {       // paired gate/up weight (fk_weight_pair)
             if (wg->k != i[0] || wg->n != 2LL * i[1] || !b[4]) return fail(FK_ERR_VALUE, "gateup: shape mismatch");
+            if (i[3] > 1) {                                // 2..16 activation rows
+                if (c->rec) return fail(FK_ERR_VALUE, "persistent program: one activation row only");
+                if (i[3] > FK_QMM_MAXM) return fail(FK_ERR_VALUE, "gateup: at most %d activation rows", FK_QMM_MAXM);
+                if (wg->bits != 4 || b[9] || b[10] || b[11]) return fail(FK_ERR_VALUE, "gateup with several rows takes 4-bit weights and no pending inputs");
+                QmmArgs qa{(const uint16_t *)b[0], wg->tview(), nullptr, (uint16_t *)b[4], c->qmm_scratch, c->qmm_counters,
+                           i[3], i[0], i[1], 1, (const uint16_t *)b[1], f[0], i[2]};
+                e = launch_qmm(c, wg, qa, true);
+                break;
+            }
             SGateUpArgs sa{(const uint16_t *)b[0], (const uint16_t *)b[1], StreamPlan(), (uint16_t *)b[4],
                            (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0], nullptr};
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }

@@ -83,6 +83,8 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      src/codegen/msl.rs:2318-2439, chosen in kernels/mod.rs:1442-1473); streamed 4-bit weights only
  * RMSNORM_GATEUP_ACT   buf0 x  buf1 norm_w  buf2 weight(gate)  buf3 weight(up)  buf4 act_out T[I]
  *                      buf9..11 pending (as RMSNORM_QKV)     i0 H  i1 I  i2 act   f0 eps
+ *                      i3 activation rows M (0 or 1: one row).  M = 2..16: x is T[M, H], act_out is T[M, I], every row normalised
+ *                      by its own RMS; paired 4-bit weights, no pending inputs (reference: fusekit_qmm_t_swiglu_pair_impl, msl.rs:2489)
  * FINAL_RMSNORM_LM_HEAD buf0 x  buf1 norm_w  buf2 weight(head)  buf3 logits_out|0  buf4 argmax scratch(u64)
  *                      buf5 counter(u32)  buf9..11 pending     i0 H  i1 V(local)  i2 vocab_offset  i3 finalize(1/0)   f0 eps
  * ARGMAX_FINALIZE      buf4 argmax scratch  i0 entries

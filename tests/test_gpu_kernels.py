@@ -116,6 +116,38 @@ def test_linear_residual_rows(runtime, m, k, n, residual):
     assert runtime.state_get()[2] == 0
 
 
+@pytest.mark.parametrize("m", [2, 7, 16])
+@pytest.mark.parametrize("act", [0, 1])
+@pytest.mark.parametrize("h,inter", [(896, 4864), (256, 100), (3584, 1024), (512, 19200)])
+def test_rmsnorm_gateup_act_rows(runtime, m, act, h, inter):
+    """2..16 activation rows through the norm-first gate/up task: row i equals the one-row task's result for x[i]."""
+    rt = runtime
+    if not rt.tiled:
+        pytest.skip("streamed weight layout only")
+    wg = O.gen_weight(stream_id(3, f"qg.{h}.{inter}"), inter, h, 4)
+    wu = O.gen_weight(stream_id(3, f"qu.{h}.{inter}"), inter, h, 4)
+    x, nw = normal(f"qgx{m}", m * h, 40.0).reshape(m, h), normal("qgnw", h, 0.02, 1.0)
+    want = []
+    for i in range(m):
+        nf = O.rmsnorm(x[i], nw, 1e-6)
+        want.append(O.act(O.linear_acc(wg, nf), O.linear_acc(wu, nf), act))
+    out = rt.alloc(m * inter * 2)
+    rt.launch(T(N.TASK_RMSNORM_GATEUP_ACT, 0, {0: rt.to_device(x), 1: rt.to_device(nw), **gateup_bufs(rt, wg, wu), 4: out},
+                [h, inter, act, m], [1e-6]))
+    got = rt.download(out, (m, inter), np.uint16)
+    bufs = {1: rt.to_device(nw), **gateup_bufs(rt, wg, wu)}
+    one = rt.alloc(inter * 2)
+    for i in range(m):
+        # The sum of squares is added in another order than the oracle's, so 1/rms can differ in its last bit; now and then
+        # that flips one normalised activation by a bf16 ulp, which moves every output a little and a third of them across
+        # a rounding boundary (seen at H = 3584: relative RMS 2.2e-3, the one-row kernel showing the very same deviation).
+        # Hence the wider bound against the oracle, and the tight one against the one-row kernel, which shares the order.
+        assert_close_bf16(got[i], want[i], f"gateup rows {i}/{m} act{act} {h}->{inter}", rel_rms_tol=4e-3)
+        rt.launch(T(N.TASK_RMSNORM_GATEUP_ACT, 0, {0: rt.to_device(x[i].copy()), **bufs, 4: one}, [h, inter, act], [1e-6]))
+        assert_close_bf16(got[i], rt.download(one, (inter,), np.uint16), f"gateup rows {i}/{m} against the one-row kernel")
+    assert rt.state_get()[2] == 0
+
+
 def test_linear_residual_rows_refusals(runtime):
     rt = runtime
     w8 = O.gen_weight(stream_id(1, "qmm8"), 16, 64, 8)
