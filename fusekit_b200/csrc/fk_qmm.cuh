@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmA
                     const uint4 *u = wring + (size_t)s * FK_UNIT_VEC;
                     const unsigned char *xb = xs + (size_t)buf * FK_QMM_CHUNK;
                     const float *sums = sx + buf * FK_QMM_MAXM * 8;
-#pragma unroll 2
+#pragma unroll 4
                     for (int j = 0; j < 8; ++j) {
                         const uint4 w = u[j * 32 + lane];                // {word A row g, word B row g, word A row g+8, word B row g+8}
                         float d[2][4];
