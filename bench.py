@@ -2,8 +2,9 @@
 """Headline benchmark: batch-1 greedy decode tokens/s of the Qwen2.5-7B-shaped 4-bit (group 64)
 decoder at context 512, through the captured CUDA graph of libfusekit_cuda.so.
 
-    python bench.py --gpus N --steps K --warmup W            (N > 1 under torchrun: N replicas)
+    python bench.py --gpus N --steps K --warmup W            (N > 1 under torchrun: N replicas + the 32B tensor-parallel run)
     python bench.py --impl reference ...                      (CPU oracle port on the host cores)
+    python bench.py --workload qwen32b-q4-ctx4096 --tp        (N ranks form one tensor-parallel group)
 
 A step is one decode chunk of 64 tokens (the reference's FK_CHUNK) with on-device token feedback.
 `value` is device-timed (CUDA events on the library's stream, weights/KV resident in HBM); `e2e` is
@@ -11,6 +12,11 @@ wall-clock through DecodeEngine.decode_chunk with the seed token uploaded from p
 and the token history read back every chunk.  Synthetic data: seeded random-init weights and an
 N(0,1) KV pre-fill, as the benchmark configs define.  Inputs (4 GB of weights) exceed the 126 MB L2,
 so no explicit flush is needed between iterations.
+
+With more than one rank the headline line stays the replica measurement (batch-1 decode does not
+shard into independent units); the ranks then also run the 32B-shaped model tensor-parallel over all
+of them and the line carries that as `tp` (tok/s of the one stream, roofline fraction, whether every
+rank produced the same tokens).
 """
 from __future__ import annotations
 
@@ -29,7 +35,7 @@ import numpy as np  # noqa: E402
 
 CHUNK = 64
 WORKLOADS = {
-    # name: (config, bits, ctx, metric tag)
+    # name: (config, bits, ctx)
     "qwen7b-q4-ctx512": ("qwen2.5-7b", 4, 512),
     "qwen7b-q4-ctx32": ("qwen2.5-7b", 4, 32),
     "qwen7b-q8-ctx512": ("qwen2.5-7b", 8, 512),
@@ -38,11 +44,25 @@ WORKLOADS = {
     "qwen32b-q4-ctx4096": ("qwen2.5-32b", 4, 4096),
     "qwen0.5b-q4-ctx32": ("qwen2.5-0.5b", 4, 32),
 }
-METRIC = "batch-1 decode tok/s, 7B-shaped int4 ctx512"      # BASELINE.json metric; other --workload values are named in config.workload
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
-NCU_TRAFFIC = {"fusekit_rmsnorm_gateup_act": 81.8e6 + 2.2e6, "fusekit_final_rmsnorm_lm_head": 315.9e6 + 0.4e6}
+TP_WORKLOAD = "qwen32b-q4-ctx4096"
+METRIC = "batch-1 decode tok/s, 7B-shaped int4 ctx512"      # other --workload values are named in config.workload
 KIND_NAMES = ["step_init", "embed_lookup_decode", "rmsnorm_qkv", "qk_norm_rope_store", "sdpa_decode", "linear_residual",
               "rmsnorm_gateup_act", "final_rmsnorm_lm_head", "argmax_finalize", "allreduce", "residual_add"]
+
+
+def ncu_traffic() -> dict:
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel kind, from the ncu captures summarised
+    under profiles/ (one `kernel_name bytes` pair per line)."""
+    out, p = {}, os.path.join(ROOT, "profiles", "dram_traffic_per_launch.txt")
+    if os.path.exists(p):
+        for ln in open(p):
+            f = ln.split()
+            if len(f) >= 2 and not ln.startswith("#"):
+                try:
+                    out[f[0]] = float(f[1])
+                except ValueError:
+                    pass
+    return out
 
 
 def measured_peak():
@@ -100,19 +120,32 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_oracle_rate(config: str, bits: int, ctx: int, budget_s: float, tokens: int | None = None):
-    """Tokens/s of the CPU oracle port (all host threads) on a bounded sample of the same workload."""
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_oracle_check(config: str, bits: int, ctx: int, gpu_tokens, seed_token: int, budget_s: float):
+    """The CPU oracle port (all host threads) walked along the GPU's own first tokens of the same workload: its rate is
+    the CPU baseline, and every token is compared with the GPU's (a flip inside two bf16 ulps of the oracle's winning
+    logit counts as a near-tie, anything wider as a mismatch)."""
     from fusekit_b200.model_spec import CONFIGS
     from oracle import oracle as O
-    from tests.helpers import oracle_config
+    cores = O.set_num_threads(host_cores())
     spec = CONFIGS[config].with_bits(bits)
-    m = O.Model(oracle_config(spec, ctx + 64))
+    m = O.Model(O.model_config(spec, ctx + 64))
     m.prefill_kv(ctx)
-    _, t1 = m.greedy(3, ctx, 1)
-    n = tokens if tokens is not None else int(max(1, min(16, budget_s / max(t1, 1e-3))))
-    toks, secs = m.greedy(3, ctx + 1, n)
+    t0 = time.perf_counter()
+    m.step(seed_token, ctx)                      # one token to size the sample (its KV row is rewritten below)
+    t1 = time.perf_counter() - t0
+    n = int(max(1, min(len(gpu_tokens), budget_s / max(t1, 1e-3))))
+    t0 = time.perf_counter()
+    mism, ties = O.compare_greedy(gpu_tokens[:n], m, seed_token, ctx)
+    secs = time.perf_counter() - t0
     m.close()
-    return n / secs, n, O.num_threads()
+    return n / secs, n, cores, mism, ties
 
 
 def run_reference(args, rank: int):
@@ -123,9 +156,9 @@ def run_reference(args, rank: int):
     config, bits, ctx = WORKLOADS[args.workload]
     from fusekit_b200.model_spec import CONFIGS
     from oracle import oracle as O
-    from tests.helpers import oracle_config
+    cores = O.set_num_threads(host_cores())      # all host cores, whatever OMP_NUM_THREADS the launcher exported
     spec = CONFIGS[config].with_bits(bits)
-    m = O.Model(oracle_config(spec, ctx + args.steps + args.warmup + 8))
+    m = O.Model(O.model_config(spec, ctx + args.steps + args.warmup + 8))
     m.prefill_kv(ctx)
     tok, pos = 3, ctx
     for _ in range(args.warmup):
@@ -135,16 +168,57 @@ def run_reference(args, rank: int):
         tok, _, _ = m.step(tok, pos); pos += 1
     dt = time.perf_counter() - t0
     val = args.steps / dt
-    cores = O.num_threads()
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": f"int{bits}" if bits != 16 else "bf16", "data": "synthetic",
         "config": {"workload": args.workload, "step": "1 decoded token on the CPU"},
         "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port",
-                         "sample": f"{args.steps} greedy tokens of {args.workload} after {args.warmup} warm-up tokens, OpenMP over output rows"},
+                         "sample": f"{args.steps} greedy tokens of {args.workload} after {args.warmup} warm-up tokens, OpenMP over output rows on {cores} threads"},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
+
+
+def make_tp_engine(spec, cap, local, rank, world, dist):
+    """One tensor-parallel slice per rank, with the exchange the library offers: peer-memory (CUDA IPC arenas, default
+    where the GPUs can map each other) or the NCCL all-reduce captured in the graph (FK_PEER=0)."""
+    from fusekit_b200.runtime import DecodeEngine, comm_unique_id
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    eng = DecodeEngine(spec, cap, device=local, tp_rank=rank, tp_size=world)
+    peer = False
+    if os.environ.get("FK_PEER", "1") != "0":
+        handles = [None] * world
+        dist.all_gather_object(handles, eng.peer_export())
+        peer = eng.peer_open(handles)
+        flags = [None] * world
+        dist.all_gather_object(flags, bool(peer))
+        peer = all(flags)
+    if not peer:
+        uid = [comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        eng.comm_init(uid[0])
+        eng.peer_disable()
+    return eng, peer
+
+
+def timed_chunks(eng, ctx, warmup, steps, barrier, sampler=None):
+    tok, first = 3, None
+    for i in range(warmup):
+        out, _ = eng.decode_chunk(ctx + i * CHUNK, tok, CHUNK)
+        if first is None:
+            first = out.copy()
+    if sampler:
+        sampler.start()
+    barrier()
+    dev_s, t0 = 0.0, time.perf_counter()
+    last = None
+    for i in range(steps):
+        out, s = eng.decode_chunk(ctx + i * CHUNK, tok, CHUNK)
+        tok = int(out[-1]); dev_s += s; last = out
+    eng.rt.sync()
+    wall_s = time.perf_counter() - t0
+    barrier()
+    return dev_s, wall_s, first, last, tok
 
 
 def main():
@@ -157,7 +231,7 @@ def main():
     ap.add_argument("--workload", default="qwen7b-q4-ctx512", choices=sorted(WORKLOADS))
     ap.add_argument("--chunk", type=int, default=CHUNK, help="tokens per step (64 = the reference's FK_CHUNK); smaller for profiler captures")
     ap.add_argument("--tp", action="store_true", help="N ranks form one tensor-parallel group (one stream) instead of N replicas")
-    ap.add_argument("--persistent", default="auto", choices=["auto", "on", "off"], help="run a token as one persistent kernel (auto: when the task list allows)")
+    ap.add_argument("--no-tp-extra", action="store_true", help="with N > 1 replicas, skip the additional 32B tensor-parallel run")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--profile-nodes", type=int, default=5, help="repeats of the per-kernel timing pass (0 = skip)")
@@ -181,25 +255,14 @@ def main():
     config, bits, ctx = WORKLOADS[args.workload]
     spec = CONFIGS[config].with_bits(bits)
     cap = ctx + CHUNK * max(args.steps, args.warmup) + 8
+    peer = False
     if args.tp and world > 1:
-        from fusekit_b200.runtime import comm_unique_id
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        uid = [comm_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(uid, src=0)
-        eng = DecodeEngine(spec, cap, device=local, tp_rank=rank, tp_size=world)
-        eng.comm_init(uid[0])
-        peer = False
-        # peer-memory all-reduce where the GPUs can map each other's arenas: measured faster than the library collective
-        # from 4 ranks up (FK_PEER=1 / 0 forces it on / off)
-        if os.environ.get("FK_PEER", "1" if world >= 4 else "0") != "0":
-            handles = [None] * world
-            dist.all_gather_object(handles, eng.peer_export())
-            peer = eng.peer_open(handles)
+        eng, peer = make_tp_engine(spec, cap, local, rank, world, dist)
     else:
         eng = DecodeEngine(spec, cap, device=local)      # N > 1: N independent replicas, one per GPU
     eng.load_synthetic()
     eng.prefill_kv_synthetic(ctx)
-    eng.capture({"auto": None, "on": True, "off": False}[args.persistent])
+    eng.capture()
     nodes = len(eng.replay)
 
     def barrier():
@@ -208,24 +271,16 @@ def main():
         torch.cuda.synchronize()
         eng.rt.sync()
 
-    tok = 3
-    for i in range(args.warmup):
-        out, _ = eng.decode_chunk(ctx + i * CHUNK, tok, CHUNK)
+    def max_over_ranks(*vals):
+        t = torch.tensor(list(vals), dtype=torch.float64, device=f"cuda:{local}")
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t]
+
     sampler = ClockSampler(local)
-    sampler.start()
-    barrier()
-    dev_s, t0 = 0.0, time.perf_counter()
-    for i in range(args.steps):
-        out, s = eng.decode_chunk(ctx + i * CHUNK, tok, CHUNK)
-        tok = int(out[-1]); dev_s += s
-    eng.rt.sync()
-    wall_s = time.perf_counter() - t0
-    barrier()
+    dev_s, wall_s, first_chunk, _, tok = timed_chunks(eng, ctx, max(args.warmup, 1), args.steps, barrier, sampler)
     clocks = sampler.stop()
-    times = torch.tensor([dev_s, wall_s], dtype=torch.float64, device=f"cuda:{local}")
-    if dist is not None:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_s, wall_s = float(times[0]), float(times[1])
+    dev_s, wall_s = max_over_ranks(dev_s, wall_s)
     streams = 1 if args.tp else world
     tokens = args.steps * CHUNK * streams
     peak, peak_kind = measured_peak()
@@ -234,7 +289,8 @@ def main():
     # every launch reads cold data) back to back between two CUDA events on the library's stream
     roofline = None
     shares = {}
-    if args.profile_nodes > 0 and rank == 0:
+    if args.profile_nodes > 0 and rank == 0 and not (args.tp and world > 1):
+        traffic = ncu_traffic()
         eng.rt.state_set(tok, ctx + CHUNK)
         by_kind = {}
         for t in eng.tasks:
@@ -247,13 +303,19 @@ def main():
             subs.setdefault((t.iarg[0], t.iarg[1]), []).append(t)
         lin_times = {shape: eng.time_tasks(v, args.profile_nodes) / len(v) for shape, v in subs.items()}
         tot = sum(per_kind[k] * len(v) for k, v in by_kind.items())
-        shares = {KIND_NAMES[k]: {"launches": len(v), "avg_us": 1e6 * per_kind[k], "share": per_kind[k] * len(v) / tot} for k, v in by_kind.items()}
-        for (kk, nn), tsec in lin_times.items():
-            shares[f"linear_residual[{kk}->{nn}]"] = {"launches": len(subs[(kk, nn)]), "avg_us": 1e6 * tsec}
         H, I = spec.hidden, spec.inter
         algo_by_kind = {6: 2 * spec.linear_bytes(H, I) - 2 * H - 2 * I,            # gate+up weights, x once, one T[I] out
                         7: spec.linear_bytes(H, spec.vocab) - 2 * spec.vocab,      # no logits are written
                         2: spec.linear_bytes(H, (spec.n_q + 2 * spec.n_kv) * spec.head_dim)}
+        shares = {}
+        for k, v in by_kind.items():
+            e = {"launches": len(v), "avg_us": 1e6 * per_kind[k], "share": per_kind[k] * len(v) / tot}
+            if k in algo_by_kind:
+                e["gbs"] = algo_by_kind[k] / per_kind[k] / 1e9; e["frac_of_peak"] = e["gbs"] / peak
+            shares[KIND_NAMES[k]] = e
+        for (kk, nn), tsec in lin_times.items():
+            gbs = spec.linear_bytes(kk, nn, True) / tsec / 1e9
+            shares[f"linear_residual[{kk}->{nn}]"] = {"launches": len(subs[(kk, nn)]), "avg_us": 1e6 * tsec, "gbs": gbs, "frac_of_peak": gbs / peak}
         cands = {k: per_kind[k] * len(by_kind[k]) for k in algo_by_kind if k in per_kind}
         for (kk, nn), tsec in lin_times.items():
             cands[("lin", kk, nn)] = tsec * len(subs[(kk, nn)])
@@ -265,40 +327,66 @@ def main():
         ach = algo / avg / 1e9
         roofline = {"bound": "hbm", "kernel": name, "achieved": ach, "peak": peak, "peak_kind": peak_kind,
                     "unit": "GB/s", "frac": ach / peak, "bytes_per_launch": algo, "avg_launch_us": avg * 1e6,
-                    "traffic": NCU_TRAFFIC.get(name)}
-        if eng.persistent:
-            # the timed region is launches of one kernel, the persistent token kernel: its roofline is the token's.  The
-            # per-task figures above (same tasks, one kernel each) stay in kernel_shares as the breakdown.
-            bpl = spec.bytes_per_token(ctx + CHUNK * args.steps // 2)
-            avg = dev_s / (args.steps * CHUNK)
-            roofline = {"bound": "hbm", "kernel": "fusekit_decode_token", "achieved": bpl / avg / 1e9, "peak": peak, "peak_kind": peak_kind,
-                        "unit": "GB/s", "frac": bpl / avg / 1e9 / peak, "bytes_per_launch": bpl, "avg_launch_us": avg * 1e6,
-                        "traffic": NCU_TRAFFIC.get("fusekit_decode_token"), "per_task_dominant": roofline}
+                    "traffic": traffic.get(name) if args.workload == "qwen7b-q4-ctx512" else None}
 
-    cpu_baseline = None
+    cpu_baseline, parity = None, None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        rate, n, cores = cpu_oracle_rate(config, bits, ctx, args.cpu_budget)
+        rate, n, cores, mism, ties = cpu_oracle_check(config, bits, ctx, first_chunk, 3, args.cpu_budget)
         cpu_baseline = {"value": rate, "unit": "tok/s", "cores": cores, "kind": "port",
-                        "sample": f"{n} greedy tokens of {args.workload} on the CPU oracle (OpenMP over output rows)"}
+                        "sample": f"{n} tokens of {args.workload} on the CPU oracle (OpenMP over output rows, {cores} threads), walked along the GPU's token stream"}
+        parity = {"tokens_compared": n, "mismatches": len(mism), "near_ties": len(ties)}
+        if mism:
+            raise SystemExit(f"bench: GPU tokens differ from the CPU oracle beyond a near-tie: {mism}")
+
+    info = eng.rt.info()
+    eng.close()
+
+    # ---- N > 1 replicas: the same ranks also run the 32B-shaped model tensor-parallel over all of them
+    tp = None
+    if dist is not None and not args.tp and not args.no_tp_extra:
+        tcfg, tbits, tctx = WORKLOADS[TP_WORKLOAD]
+        tspec = CONFIGS[tcfg].with_bits(tbits)
+        tsteps, twarm = max(2, min(args.steps, 4)), 2
+        teng, tpeer = make_tp_engine(tspec, tctx + CHUNK * max(tsteps, twarm) + 8, local, rank, world, dist)
+        teng.load_synthetic(); teng.prefill_kv_synthetic(tctx); teng.capture()
+
+        def tbarrier():
+            dist.barrier(); torch.cuda.synchronize(); teng.rt.sync()
+
+        tdev, twall, _, tlast, _ = timed_chunks(teng, tctx, twarm, tsteps, tbarrier)
+        tdev, twall = max_over_ranks(tdev, twall)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, [int(v) for v in tlast])
+        tnodes = len(teng.replay)
+        teng.close()
+        tps = tsteps * CHUNK / tdev
+        bpt = tspec.bytes_per_token(tctx + CHUNK * tsteps // 2)
+        tp = {"workload": TP_WORKLOAD, "tensor_parallel": world, "tok_s": tps, "e2e_tok_s": tsteps * CHUNK / twall, "steps": tsteps, "warmup": twarm,
+              "roofline_frac": bpt * tps / 1e9 / peak / world, "bytes_per_token": bpt, "allreduce": "peer" if tpeer else "nccl",
+              "graph_nodes_per_token": tnodes, "tokens_equal_across_ranks": all(g == gathered[0] for g in gathered)}
 
     if rank == 0:
         tps = tokens / dev_s
         bpt = spec.bytes_per_token(ctx + CHUNK * args.steps // 2)
+        tpd = world if args.tp else 1
         line = {
             "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "strong" if args.tp else "weak", "vs_baseline": None,
             "dtype": f"int{bits}" if bits != 16 else "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "tokens_per_step": CHUNK, "batch": 1, "ctx_start": ctx, "graph_nodes_per_token": nodes,
-                       "l2": "inputs (weights) larger than L2", "persistent_kernel": eng.persistent, "replicas": streams, "tensor_parallel": world if args.tp else 1, "allreduce": ("peer" if (args.tp and world > 1 and peer) else "nccl") if args.tp and world > 1 else None, "pdl": eng.rt.info().get("pdl")},
+                       "l2": "inputs (weights) larger than L2", "replicas": streams, "tensor_parallel": tpd,
+                       "allreduce": ("peer" if peer else "nccl") if args.tp and world > 1 else None, "pdl": info.get("pdl")},
             "e2e": {"value": tokens / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 80, "d2h_bytes_per_step": CHUNK * 4 + 80},
             "gpu_launches": nodes * CHUNK * args.steps,
             "clocks": clocks,
             "token_roofline": {"bytes_per_token": bpt, "achieved_gbs": bpt * (tps / streams) / 1e9, "peak": peak, "peak_kind": peak_kind,
-                               "frac": bpt * (tps / streams) / 1e9 / peak / (world if args.tp else 1), "frac_of_8tbs": bpt * (tps / streams) / 8e12 / (world if args.tp else 1)},
+                               "frac": bpt * (tps / streams) / 1e9 / peak / tpd, "frac_of_8tbs": bpt * (tps / streams) / 8e12 / tpd},
             "roofline": roofline, "kernel_shares": shares, "cpu_baseline": cpu_baseline,
+            "parity_checked": parity is not None and not parity["mismatches"], "parity": parity,
         }
+        if tp is not None:
+            line["tp"] = tp
         print(json.dumps(line), flush=True)
-    eng.close()
     if dist is not None:
         dist.destroy_process_group()
 

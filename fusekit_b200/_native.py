@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("FUSEKIT_CUDA_LIB") or os.path.join(_HERE, "libfusekit
 
 (TASK_STEP_INIT, TASK_EMBED_LOOKUP_DECODE, TASK_RMSNORM_QKV, TASK_QK_NORM_ROPE_STORE, TASK_SDPA_DECODE,
  TASK_LINEAR_RESIDUAL, TASK_RMSNORM_GATEUP_ACT, TASK_FINAL_RMSNORM_LM_HEAD, TASK_ARGMAX_FINALIZE,
- TASK_ALLREDUCE, TASK_RESIDUAL_ADD, TASK_DECODE_TOKEN) = range(12)
+ TASK_ALLREDUCE, TASK_RESIDUAL_ADD) = range(11)
 ACT_SWIGLU, ACT_GEGLU_TANH = 0, 1
 
 
@@ -64,8 +64,8 @@ def lib():
         "fk_synth_normal_bf16": [u64, u64, u64, u64, u64, f32, f32],
         "fk_launch": [u64, P(Task)], "fk_launch_batch": [u64, P(Task), i32], "fk_smoke": [u64, vp, vp, vp, i32],
         "fk_state_set": [u64, u32, u32], "fk_state_get": [u64, P(u32), P(u32), P(u32)],
-        "fk_program_build": [u64, P(Task), i32, P(u64)],
         "fk_peer_arena_export": [u64, C.c_void_p, C.c_size_t], "fk_peer_arena_open": [u64, C.c_void_p, i32, i32],
+        "fk_peer_arena_loopback": [u64, i32, i32, u32], "fk_peer_arena_close": [u64],
         "fk_graph_capture": [u64, P(Task), i32, P(u64)], "fk_graph_launch": [u64, u64, P(C.c_double)],
         "fk_graph_launch_async": [u64, u64], "fk_wait": [u64, P(C.c_double)],
         "fk_graph_profile_nodes": [u64, u64, i32, P(C.c_double), i32, P(i32)], "fk_graph_node_count": [u64, u64, P(i32)],

@@ -2,6 +2,11 @@
 // loads, in-register dequant with the group-factored form  s * sum(x*q) + b * sum(x), fp32
 // accumulation, warp-shuffle reduction.  These are the parity baseline and the fallback for
 // shapes the streamed kernels (fk_stream.cuh) do not take.
+//
+// Programmatic dependent launch order: the projection kernels here wait for their predecessor first and only then let
+// their successor start.  A kernel that triggers after its own wait guarantees that everything before it in the stream
+// has completed by the time its successor is launched, which is what lets the attention kernels read the decode
+// position and prefetch old cache rows ahead of their own wait.
 #pragma once
 #include "fk_common.cuh"
 #include <cooperative_groups.h>
@@ -169,14 +174,18 @@ __device__ __forceinline__ void rope_pair(float lo, float hi, int d, int half, u
 }
 
 // ================================================================ kernels
-struct EmbedArgs { const uint16_t *table; uint16_t *x; int h, rows; float scale; };
-// x[row,:] = T(embed[token[row],:] * scale) (src/codegen/kernels/embed_lookup_decode.rs:95-98)
-__global__ void k_embed_lookup(const FkState *st, EmbedArgs a) {
+struct EmbedArgs { const uint16_t *table; uint16_t *x; int h, rows; float scale; int vocab; };
+// x[row,:] = T(embed[token[row],:] * scale) (src/codegen/kernels/embed_lookup_decode.rs:95-98).  A token id outside the
+// table (vocab > 0) reads row 0 instead and raises error bit 0x20000: the host refuses such seeds, this guards the ids
+// that arrive through the device-side feedback.
+__global__ void k_embed_lookup(FkState *st, EmbedArgs a) {
     pdl_launch_dependents(); pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= a.h * a.rows) return;
     const int row = i / a.h, d = i - row * a.h;
-    a.x[i] = f2bf(__fmul_rn(bf2f(a.table[(size_t)st->token[row] * a.h + d]), a.scale));
+    uint32_t tok = st->token[row];
+    if (a.vocab > 0 && tok >= (uint32_t)a.vocab) { if (d == 0) atomicOr(&st->error, 0x20000u); tok = 0; }
+    a.x[i] = f2bf(__fmul_rn(bf2f(a.table[(size_t)tok * a.h + d]), a.scale));
 }
 
 struct QkvArgs {
@@ -191,7 +200,7 @@ template <int BITS>
 __global__ void __launch_bounds__(256) k_rmsnorm_qkv(const FkState *st, QkvArgs a) {
     extern __shared__ float smem_raw[];
     const Smem sm = carve(smem_raw, a.h);
-    pdl_launch_dependents(); pdl_wait();
+    pdl_wait(); pdl_launch_dependents();
     stage_norm(sm, a.x, a.norm_w, a.h, a.eps, a.pending, a.pending_w, a.h_out);
     const int lane = threadIdx.x & 31, half = a.hd >> 1;
     const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nw = gridDim.x * (blockDim.x >> 5);
@@ -807,7 +816,7 @@ struct PeerArena {
     __host__ __device__ static size_t counter(int block) { return flag(2, 0, 0) + (size_t)block * 128; }
     __host__ __device__ static size_t bytes() { return counter(FK_PEER_BLOCKS); }
 };
-struct PeerMap { unsigned char *base[FK_PEER_MAX]; int rank, world; };     // base[r]: rank r's arena as mapped in this process
+struct PeerMap { unsigned char *base[FK_PEER_MAX]; int rank, world; unsigned int spin_limit; };     // base[r]: rank r's arena as mapped in this process; spin_limit: polls before a wait gives up
 template <typename T, bool IS_MAX>
 __global__ void __launch_bounds__(256) k_allreduce_peer(T *buf, int n, PeerMap P, FkState *st) {
     __shared__ unsigned int seq_s; __shared__ int bad;
@@ -837,7 +846,7 @@ __global__ void __launch_bounds__(256) k_allreduce_peer(T *buf, int n, PeerMap P
         unsigned int it = 0, v;
         do {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-        } while ((int)(v - seq) < 0 && ++it < FK_PEER_SPIN_LIMIT);
+        } while ((int)(v - seq) < 0 && ++it < P.spin_limit);
         if ((int)(v - seq) < 0) { bad = 1; atomicOr(&st->error, 0x8000u); }
     }
     __syncthreads();
@@ -859,7 +868,7 @@ template <int BITS>
 __global__ void __launch_bounds__(256) k_linear_residual(const FkState *st, LinArgs a) {
     extern __shared__ float smem_raw[];
     const Smem sm = carve(smem_raw, a.k);
-    pdl_launch_dependents(); pdl_wait();
+    pdl_wait(); pdl_launch_dependents();
     stage_x(sm, a.x, a.k);
     const int lane = threadIdx.x & 31;
     const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nw = gridDim.x * (blockDim.x >> 5);
@@ -883,7 +892,7 @@ template <int BITS>
 __global__ void __launch_bounds__(256) k_rmsnorm_gateup_act(const FkState *st, GateUpArgs a) {
     extern __shared__ float smem_raw[];
     const Smem sm = carve(smem_raw, a.h);
-    pdl_launch_dependents(); pdl_wait();
+    pdl_wait(); pdl_launch_dependents();
     stage_norm(sm, a.x, a.norm_w, a.h, a.eps, a.pending, a.pending_w, a.h_out);
     const int lane = threadIdx.x & 31;
     const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nw = gridDim.x * (blockDim.x >> 5);
@@ -916,7 +925,7 @@ __global__ void __launch_bounds__(256) k_final_head(FkState *st, HeadArgs a) {
     extern __shared__ float smem_raw[];
     const Smem sm = carve(smem_raw, a.h);
     __shared__ unsigned long long wbest[8]; __shared__ int is_last;
-    pdl_launch_dependents(); pdl_wait();
+    pdl_wait(); pdl_launch_dependents();
     stage_norm(sm, a.x, a.norm_w, a.h, a.eps, a.pending, a.pending_w, a.h_out);
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int gw = blockIdx.x * (blockDim.x >> 5) + wid, nw = gridDim.x * (blockDim.x >> 5);
@@ -954,7 +963,7 @@ __global__ void __launch_bounds__(256) k_final_head(FkState *st, HeadArgs a) {
 
 // fold `entries` per-block (or per-rank) keys and advance the state (argmax_logits_finalize.rs:68-105)
 __global__ void k_argmax_finalize(FkState *st, const unsigned long long *scratch, int entries, uint32_t *history) {
-    pdl_launch_dependents(); pdl_wait();
+    pdl_wait(); pdl_launch_dependents();
     unsigned long long b = 0ull;
     for (int i = threadIdx.x; i < entries; i += 32) { const unsigned long long v = scratch[i]; b = v > b ? v : b; }
     b = warp_max_u64(b);
@@ -963,7 +972,7 @@ __global__ void k_argmax_finalize(FkState *st, const unsigned long long *scratch
 
 // y = T(sum + float(residual)) after a tensor-parallel all-reduce
 __global__ void k_residual_add(const float *sum, const uint16_t *residual, uint16_t *y, int n) {
-    pdl_launch_dependents(); pdl_wait();
+    pdl_wait(); pdl_launch_dependents();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) y[i] = f2bf(sum[i] + (residual ? bf2f(residual[i]) : 0.0f));
 }

@@ -6,7 +6,6 @@
 #include "fk_kernels.cuh"
 #include "fk_synth.cuh"
 #include "fk_stream.cuh"
-#include "fk_mega.cuh"
 #include "fk_qmm.cuh"
 
 #include <dlfcn.h>
@@ -68,18 +67,6 @@ struct Weight {
     TiledW tview() const { TiledW t; t.units = units; t.ntiles = ntiles; t.nsb = nsb; t.n = (int)n; t.k = (int)k; t.bits = bits;
                            t.rows_kind = rows_kind; t.hd = hd; t.n_rot = n_rot; return t; }
 };
-// a task list compiled for the persistent kernel (fk_mega.cuh)
-struct Program {
-    MegaSlot *ops = nullptr; MegaWeight *wtab = nullptr; MegaSync *sync = nullptr; float *part = nullptr;
-    int nops = 0, nweights = 0, max_nsb = 0, bits = 0, attn_bytes = 0, barriers = 0; size_t smem = 0;
-    std::vector<std::pair<void *, size_t>> zero;
-};
-struct Recorder {               // filled by run_task instead of launching while a program is being built
-    std::vector<MegaSlot> ops; std::vector<MegaWeight> wtab;
-    int bits = 0, max_nsb = 0, attn_bytes = 0, barriers = 0, min_grid = 1;
-    float *part = nullptr; size_t part_floats = 0;
-    std::vector<std::pair<void *, size_t>> zero;      // ticket counters to clear whenever the decode state is reset
-};
 struct Graph {
     std::vector<fk_task> tasks;
     cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
@@ -92,11 +79,12 @@ struct Ctx {
     std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
     bool pending = false; bool pdl = true; int sm_count = 148;
     float *qmm_scratch = nullptr; unsigned int *qmm_counters = nullptr;   // K-split partial sums and tickets of the several-row projection
-    bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_cl = 0; int sdpa_tiles_from = 0; int dbg_mode = 0;
+    bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_cl = 0;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
-    std::vector<Program> programs; Recorder *rec = nullptr;
+    uint32_t vocab = 0;                         // rows of the embedding table of the last embed task seen (0 = unknown)
+    std::vector<void *> ipc_open; std::vector<unsigned char *> loop_arenas;      // peer mappings / loopback arenas to release
     unsigned char *arena = nullptr; PeerMap peers; bool peer_ready = false;      // peer-memory all-reduce
 };
 static std::mutex g_mu;
@@ -145,13 +133,11 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     if (e && !strcmp(e, "mma")) c->sdpa_mma = true;
     if (e && !strcmp(e, "fma")) c->sdpa_mma = false;
     e = getenv("FK_SDPA_CL"); if (e && (atoi(e) == 1 || atoi(e) == 2 || atoi(e) == 4 || atoi(e) == 8)) c->sdpa_cl = atoi(e);      // CTAs per kv head of the tensor-core attention
-    e = getenv("FK_SDPA_TILES_FROM"); if (e) c->sdpa_tiles_from = atoi(e);      // capacity from which attention uses the tiled kernel (0 = never)
-    e = getenv("FK_DBG"); if (e) c->dbg_mode = atoi(e);
     e = getenv("FK_WARPS"); if (e) c->force_warps = atoi(e);
 #define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>)); CU(big_smem(K<16, 8>)); CU(big_smem(K<16, 16>))
 #define BIG4P(K) CU(big_smem(K<4, 8, true>)); CU(big_smem(K<4, 16, true>)); CU(big_smem(K<8, 8, true>)); CU(big_smem(K<8, 16, true>)); CU(big_smem(K<16, 8, true>)); CU(big_smem(K<16, 16, true>))
     BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head); BIG4P(k_s_rmsnorm_qkv); BIG4P(k_s_gateup); BIG4P(k_s_head);
-    CU(big_smem(k_decode_token<4>)); CU(big_smem(k_decode_token<8>)); CU(big_smem(k_sdpa_tiles<64>)); CU(big_smem(k_sdpa_tiles<128>)); CU(big_smem(k_sdpa_mma<64>)); CU(big_smem(k_sdpa_mma<128>)); CU(big_smem(k_sdpa_mma<256>));
+    CU(big_smem(k_sdpa_mma<64>)); CU(big_smem(k_sdpa_mma<128>)); CU(big_smem(k_sdpa_mma<256>));
     CU(big_smem(k_qmm4<false>)); CU(big_smem(k_qmm4<true>));
     CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
@@ -171,6 +157,10 @@ extern "C" fk_status fk_close(fk_handle h) {
     for (auto &w : c->weights) { cudaFree(w.w); cudaFree(w.s); cudaFree(w.b); cudaFree(w.units); }
     for (void *p : c->allocs) cudaFree(p);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
+    for (void *p : c->ipc_open) cudaIpcCloseMemHandle(p);
+    for (unsigned char *p : c->loop_arenas) cudaFree(p);
+    if (c->arena) cudaFree(c->arena);
+    c->ipc_open.clear(); c->loop_arenas.clear(); c->arena = nullptr; c->peer_ready = false; c->comm = nullptr;
     cudaFree(c->qmm_scratch); cudaFree(c->qmm_counters);
     cudaFree(c->state); cudaFree(c->history); cudaFreeHost(c->pinned);
     cudaEventDestroy(c->ev0); cudaEventDestroy(c->ev1); cudaStreamDestroy(c->stream);
@@ -192,7 +182,7 @@ extern "C" fk_status fk_info(fk_handle h, char *buf, size_t cap) {
 static const char *kKernelNames[FK_TASK_KIND_COUNT] = {
     "fusekit_step_init", "fusekit_embed_lookup_decode", "fusekit_rmsnorm_qkv", "fusekit_qk_norm_rope_store",
     "fusekit_sdpa_decode", "fusekit_linear_residual", "fusekit_rmsnorm_gateup_act", "fusekit_final_rmsnorm_lm_head",
-    "fusekit_argmax_finalize", "fusekit_allreduce", "fusekit_residual_add", "fusekit_decode_token"};
+    "fusekit_argmax_finalize", "fusekit_allreduce", "fusekit_residual_add"};
 extern "C" fk_status fk_kernel_names(char *buf, size_t cap) {
     if (!buf || cap == 0) return fail(FK_ERR_VALUE, "buf is null");
     std::string s;
@@ -460,7 +450,7 @@ static Weight *task_stream_weight(Ctx *c, const fk_task *t) {
 }
 static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *next) {
     const Shape sh = plan_shape(c, w);
-    p->W = w->tview(); p->stages = c->stages; p->dbg_mode = c->dbg_mode;
+    p->W = w->tview(); p->stages = c->stages;
     p->timeline = c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr;
     return sh;
 }
@@ -497,24 +487,6 @@ static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *nex
 #define BITS48(bits, CALL) do { if ((bits) == 4) { constexpr int B = 4; CALL; } else { constexpr int B = 8; CALL; } } while (0)
 
 
-// ---- recording a task for the persistent kernel instead of launching it
-static fk_status rec_stream(Ctx *c, MegaOp &op, StreamPlan &P, const Weight *w) {
-    Recorder *r = c->rec;
-    if (w->bits == 16) return fail(FK_ERR_VALUE, "persistent program: 4- or 8-bit weights only");
-    if (r->bits && r->bits != w->bits) return fail(FK_ERR_VALUE, "persistent program: all streamed weights must share one bit width");
-    r->bits = w->bits;
-    P.W = w->tview(); P.stages = FK_STAGES; P.dbg_mode = 0; P.timeline = nullptr;
-    op.widx = (int)r->wtab.size();
-    MegaWeight mw; mw.units = w->units; mw.ntiles = w->ntiles; mw.nsb = w->nsb;
-    r->wtab.push_back(mw);
-    if (w->nsb > r->max_nsb) r->max_nsb = w->nsb;
-    r->barriers++;
-    return FK_OK;
-}
-static void rec_push(Ctx *c, const MegaOp &op) { MegaSlot sl; memset(&sl, 0, sizeof sl); sl.op = op; c->rec->ops.push_back(sl); }
-static MegaOp rec_op(int kind) { MegaOp op; memset(&op, 0, sizeof op); op.kind = kind; op.widx = -1; return op; }
-
-static fk_status launch_program(Ctx *c, uint64_t id);
 static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullptr) {
     const uint64_t *b = t.buf; const int32_t *i = t.iarg; const float *f = t.farg;
     cudaError_t e = cudaSuccess;
@@ -522,12 +494,10 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
     case FK_TASK_STEP_INIT: return FK_OK;     // offset/token advance is fused into the argmax finalisation
     case FK_TASK_EMBED_LOOKUP_DECODE: {
         if (!b[0] || !b[1] || i[0] <= 0 || i[1] <= 0 || i[1] > FK_MAX_ROWS) return fail(FK_ERR_VALUE, "embed: bad arguments");
-        EmbedArgs a{(const uint16_t *)b[0], (uint16_t *)b[1], i[0], i[1], f[0]};
-        if (c->rec) {
-            if (i[1] != 1) return fail(FK_ERR_VALUE, "persistent program: one row per step");
-            MegaOp op = rec_op(t.kind); op.u.emb = a; rec_push(c, op); return FK_OK;
-        }
-        e = launch(c, k_embed_lookup, dim3((i[0] * i[1] + 255) / 256), dim3(256), 0, (const FkState *)c->state, a);
+        if (i[2] < 0) return fail(FK_ERR_VALUE, "embed: negative vocabulary size");
+        EmbedArgs a{(const uint16_t *)b[0], (uint16_t *)b[1], i[0], i[1], f[0], i[2]};
+        if (i[2] > 0) c->vocab = (uint32_t)i[2];        // seeds are checked against it in fk_state_set / fk_decode_chunk
+        e = launch(c, k_embed_lookup, dim3((i[0] * i[1] + 255) / 256), dim3(256), 0, c->state, a);
         break;
     }
     case FK_TASK_RMSNORM_QKV: {
@@ -546,16 +516,10 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                         H, nq, nkv, hd, cap, sinks, a.eps, a.log2theta, nullptr};
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }      // fp32 all-reduced projection + residual
             if (H > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "rmsnorm_qkv: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
-            if (c->rec) {
-                if (!sinks || sa.pend_sum || sa.pending) return fail(FK_ERR_VALUE, "persistent program: rmsnorm_qkv needs the fused RoPE + cache store and no pending norm or all-reduce input");
-                MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, w); if (rs) return rs;
-                op.u.qkv = sa; rec_push(c, op); return FK_OK;
-            }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
             STREAM_LAUNCH_P(k_s_rmsnorm_qkv, (sa.pending || sa.pend_sum), w, sh, c->state, sa);
             break;
         }
-        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs 4/8-bit streamed weights");
         if (b[9] && !b[10]) return fail(FK_ERR_VALUE, "rmsnorm_qkv: the fused all-reduce residual needs 4/8-bit streamed weights");
         const int grid = grid_for(c, w->n / 2, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_rmsnorm_qkv<B>, dim3(grid), dim3(256), smem_bytes_for(H), (const FkState *)c->state, a));
@@ -563,7 +527,6 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
     }
     case FK_TASK_QK_NORM_ROPE_STORE: {
         const int nq = i[0], nkv = i[1], hd = i[2], cap = i[3];
-        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: qk_norm_rope_store is not expressible yet");
         if (hd > 512 || (hd & 1) || !b[0] || !b[1] || !b[2] || !b[5] || !b[6]) return fail(FK_ERR_VALUE, "qk_norm_rope_store: bad arguments");
         QkNormArgs a{(uint16_t *)b[0], (const uint16_t *)b[1], (const uint16_t *)b[2], (const uint16_t *)b[3], (const uint16_t *)b[4],
                      (uint16_t *)b[5], (uint16_t *)b[6], nq, nkv, hd, cap, f[0], (float)log2((double)f[1])};
@@ -576,32 +539,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         const int chunks = (cap + FK_SDPA_KEYS - 1) / FK_SDPA_KEYS, G = nq / nkv;
         SdpaArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], (uint32_t *)b[5],
                    nq, nkv, hd, cap, chunks, f[0], c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr, -1};
-        if (c->rec) {
-            Recorder *r = c->rec;
-            if (hd != 64 && hd != 128) return fail(FK_ERR_VALUE, "persistent program: head_dim must be 64 or 128");
-            if ((size_t)nq * FK_MEGA_PARTS * (hd + 2) > r->part_floats) return fail(FK_ERR_VALUE, "persistent program: attention partial buffer too small");
-            if (G * 2 > FK_MEGA_WARPS) return fail(FK_ERR_VALUE, "persistent program: at most %d q heads per kv head", FK_MEGA_WARPS / 2);
-            a.part = r->part; a.tl = nullptr;
-            const int ab = (int)mega_attn2_bytes(G, hd);
-            if (ab > r->attn_bytes) r->attn_bytes = ab;
-            if (nkv * FK_MEGA_PARTS > r->min_grid) r->min_grid = nkv * FK_MEGA_PARTS;
-            MegaOp op = rec_op(t.kind); op.u.sdpa = a; rec_push(c, op);
-            r->barriers++;
-            r->zero.push_back({(void *)a.counter, sizeof(uint32_t) * (size_t)nkv});
-            return FK_OK;
-        }
-        // shared-memory tiles over up to 16 blocks per kv head with a ticket fold: i4 = 3 asks for it (1 = cluster kernel,
-        // 2 = global-partials kernel, 0 = by shape); measured slower than the cluster kernel at 512 and at 4096 keys, so it
-        // is never chosen by default (FK_SDPA_TILES_FROM=<capacity> enables it from that capacity on)
-        const int variant = i[4];
-        if ((hd == 64 || hd == 128) && G * 2 <= FK_TILES_WARPS && (variant == 3 || (variant == 0 && c->sdpa_tiles_from > 0 && cap >= c->sdpa_tiles_from))) {
-            const int parts = sdpa_tiles_parts(cap);
-            const size_t smem = mega_attn2_bytes(G, hd) + 128;
-            const dim3 tgrid(parts, nkv), tblock(FK_TILES_WARPS * 32);
-            if (hd == 64) e = launch(c, k_sdpa_tiles<64>, tgrid, tblock, smem, (const FkState *)c->state, a);
-            else e = launch(c, k_sdpa_tiles<128>, tgrid, tblock, smem, (const FkState *)c->state, a);
-            break;
-        }
+        const int variant = i[4];      // 0 = by shape, 1 = FMA cluster kernel, 2 = global-partials kernel, 4 = tensor-core cluster kernel
         // tensor-core cluster kernel: the default up to head_dim 128; at 256 (two q heads per kv head in the Gemma shape)
         // the FMA kernel below is faster (11.0 against 12.1 us), so it runs only when asked for
         if (G <= 8 && (variant == 4 || (variant == 0 && hd <= 128 && c->sdpa_mma && c->sdpa_cluster))) {
@@ -632,7 +570,6 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (!w || !w->finalized) return fail(FK_ERR_VALUE, "linear_residual: weight missing or not finalized");
         if (w->k != i[0] || w->n != i[1] || !b[0] || (!b[3] && !b[4])) return fail(FK_ERR_VALUE, "linear_residual: shape mismatch");
         if (i[2] > 1) {                                    // 2..16 activation rows: the quantised matrix product
-            if (c->rec) return fail(FK_ERR_VALUE, "persistent program: one activation row only");
             if (i[2] > FK_QMM_MAXM) return fail(FK_ERR_VALUE, "linear_residual: at most %d activation rows", FK_QMM_MAXM);
             if (!w->tiled || w->bits != 4 || w->rows_kind != FK_ROWS_PLAIN || !b[3] || b[4])
                 return fail(FK_ERR_VALUE, "linear_residual with several rows takes streamed 4-bit weights in plain row order and a T output");
@@ -645,16 +582,10 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (w->tiled) {
             if (w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "linear_residual takes plain row order");
             SLinArgs sa{a.x, StreamPlan(), a.residual, a.y, a.y_f32, i[0], i[1]};
-            if (c->rec) {
-                if (sa.y_f32 || !sa.y) return fail(FK_ERR_VALUE, "persistent program: linear_residual writes T outputs only");
-                MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, w); if (rs) return rs;
-                op.u.lin = sa; rec_push(c, op); return FK_OK;
-            }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
             STREAM_LAUNCH(k_s_linear, w, sh, c->state, sa);
             break;
         }
-        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs 4/8-bit streamed weights");
         const int grid = grid_for(c, w->n, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_linear_residual<B>, dim3(grid), dim3(256), smem_bytes_for(i[0]), (const FkState *)c->state, a));
         break;
@@ -664,7 +595,6 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (wg && wg->tiled && wg->rows_kind == FK_ROWS_GATE_UP) {       // paired gate/up weight (fk_weight_pair)
             if (wg->k != i[0] || wg->n != 2LL * i[1] || !b[4]) return fail(FK_ERR_VALUE, "gateup: shape mismatch");
             if (i[3] > 1) {                                // 2..16 activation rows
-                if (c->rec) return fail(FK_ERR_VALUE, "persistent program: one activation row only");
                 if (i[3] > FK_QMM_MAXM) return fail(FK_ERR_VALUE, "gateup: at most %d activation rows", FK_QMM_MAXM);
                 if (wg->bits != 4 || b[9] || b[10] || b[11]) return fail(FK_ERR_VALUE, "gateup with several rows takes 4-bit weights and no pending inputs");
                 QmmArgs qa{(const uint16_t *)b[0], wg->tview(), nullptr, (uint16_t *)b[4], c->qmm_scratch, c->qmm_counters,
@@ -676,16 +606,10 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                            (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0], nullptr};
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "gateup: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
-            if (c->rec) {
-                if (sa.pend_sum || sa.pending) return fail(FK_ERR_VALUE, "persistent program: no pending norm or all-reduce inputs");
-                MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, wg); if (rs) return rs;
-                op.u.gu = sa; rec_push(c, op); return FK_OK;
-            }
             const Shape sh = make_plan(c, wg, &sa.P, nextw);
             STREAM_LAUNCH_P(k_s_gateup, (sa.pending || sa.pend_sum), wg, sh, c->state, sa);
             break;
         }
-        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs a paired 4/8-bit gate/up weight");
         if (!wg || !wu || !wg->finalized || !wu->finalized) return fail(FK_ERR_VALUE, "gateup: weights missing or not finalized");
         if (wg->tiled || wu->tiled) return fail(FK_ERR_VALUE, "gateup: pair the gate and up weights with fk_weight_pair");
         if (wg->k != i[0] || wu->k != i[0] || wg->n != i[1] || wu->n != i[1] || wg->bits != wu->bits) return fail(FK_ERR_VALUE, "gateup: shape mismatch");
@@ -707,31 +631,22 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                          a.h, a.v, a.vocab_offset, a.finalize, a.eps, nullptr};
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "lm_head: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
-            if (c->rec) {
-                if (sa.pend_sum || sa.pending || !sa.finalize) return fail(FK_ERR_VALUE, "persistent program: the head must finalise the token itself and takes no pending norm");
-                MegaOp op = rec_op(t.kind); fk_status rs = rec_stream(c, op, sa.P, w); if (rs) return rs;
-                op.u.head = sa; rec_push(c, op); return FK_OK;
-            }
             const Shape sh = make_plan(c, w, &sa.P, nextw);
             STREAM_LAUNCH_P(k_s_head, (sa.pending || sa.pend_sum), w, sh, c->state, sa);
             break;
         }
-        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: needs 4/8-bit streamed weights");
         const int grid = grid_for(c, w->n, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_final_head<B>, dim3(grid), dim3(256), smem_bytes_for(i[0]), c->state, a));
         break;
     }
-    case FK_TASK_DECODE_TOKEN: return c->rec ? fail(FK_ERR_VALUE, "persistent program: programs do not nest") : launch_program(c, b[0]);
     case FK_TASK_ARGMAX_FINALIZE: {
-        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: argmax_finalize is not expressible");
         if (!b[4] || i[0] <= 0) return fail(FK_ERR_VALUE, "argmax_finalize: bad arguments");
         e = launch(c, k_argmax_finalize, dim3(1), dim3(32), 0, c->state, (const unsigned long long *)b[4], i[0], c->history);
         break;
     }
     case FK_TASK_ALLREDUCE: {
-        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: collectives are not expressible");
         if (c->peer_ready && i[0] > 0 && (size_t)i[0] * (i[1] == 1 ? 8 : 4) <= FK_PEER_SLOT_BYTES) {      // peer stores + flags instead of the library collective
-            const int nbk = i[0] >= 1024 ? FK_PEER_BLOCKS : 1;
+            const int nbk = FK_PEER_BLOCKS;         // every call uses all blocks: one sequence number per block stays in step on all ranks
             if (i[1] == 1) e = launch(c, k_allreduce_peer<unsigned long long, true>, dim3(nbk), dim3(256), 0, (unsigned long long *)b[0], i[0], c->peers, c->state);
             else e = launch(c, k_allreduce_peer<float, false>, dim3(nbk), dim3(256), 0, (float *)b[0], i[0], c->peers, c->state);
             break;
@@ -743,7 +658,6 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         break;
     }
     case FK_TASK_RESIDUAL_ADD: {
-        if (c->rec) return fail(FK_ERR_VALUE, "persistent program: residual_add is not expressible");
         if (!b[0] || !b[2] || i[0] <= 0) return fail(FK_ERR_VALUE, "residual_add: bad arguments");
         e = launch(c, k_residual_add, dim3((i[0] + 255) / 256), dim3(256), 0, (const float *)b[0], (const uint16_t *)b[1], (uint16_t *)b[2], i[0]);
         break;
@@ -754,64 +668,6 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
     return FK_OK;
 }
 
-
-// ------------------------------------------------------------------ persistent programs
-extern "C" fk_status fk_program_build(fk_handle h, const fk_task *tasks, int n, uint64_t *out) {
-    CTX(h);
-    if (!tasks || n <= 0 || !out) return fail(FK_ERR_VALUE, "empty task list");
-    if (!c->use_tiled) return fail(FK_ERR_VALUE, "persistent program: needs the streamed weight layout");
-    Recorder r;
-    for (int j = 0; j < n; ++j) if (tasks[j].kind == FK_TASK_SDPA_DECODE) {
-        const size_t need = (size_t)tasks[j].iarg[0] * FK_MEGA_PARTS * (tasks[j].iarg[2] + 2);
-        if (need > r.part_floats) r.part_floats = need;
-    }
-    if (r.part_floats) CU(cudaMalloc(&r.part, r.part_floats * sizeof(float)));
-    c->rec = &r;
-    fk_status s = FK_OK;
-    for (int j = 0; j < n && s == FK_OK; ++j) s = run_task(c, tasks[j]);
-    c->rec = nullptr;
-    if (s == FK_OK && (r.ops.empty() || r.wtab.empty() || r.ops.back().op.kind != FK_TASK_FINAL_RMSNORM_LM_HEAD))
-        s = fail(FK_ERR_VALUE, "persistent program: the list must end with the lm_head task");
-    if (s == FK_OK && r.min_grid > c->sm_count) s = fail(FK_ERR_VALUE, "persistent program: %d kv heads x %d key blocks exceed the %d resident blocks", r.min_grid / FK_MEGA_PARTS, FK_MEGA_PARTS, c->sm_count);
-    Program p;
-    if (s == FK_OK) {
-        p.nops = (int)r.ops.size(); p.nweights = (int)r.wtab.size(); p.max_nsb = r.max_nsb; p.bits = r.bits; p.attn_bytes = r.attn_bytes; p.barriers = r.barriers;
-        p.smem = mega_layout(p.nweights, p.max_nsb, p.bits, (size_t)p.attn_bytes).total;
-        if (p.smem > 227 * 1024) s = fail(FK_ERR_VALUE, "persistent program: %zu bytes of shared memory needed, 232448 available", p.smem);
-    }
-    if (s != FK_OK) { cudaFree(r.part); return s; }
-    p.part = r.part; p.zero = r.zero;
-    CU(cudaMalloc(&p.ops, r.ops.size() * sizeof(MegaSlot)));
-    CU(cudaMalloc(&p.wtab, r.wtab.size() * sizeof(MegaWeight)));
-    CU(cudaMalloc(&p.sync, sizeof(MegaSync)));
-    CU(cudaMemcpyAsync(p.ops, r.ops.data(), r.ops.size() * sizeof(MegaSlot), cudaMemcpyHostToDevice, c->stream));
-    CU(cudaMemcpyAsync(p.wtab, r.wtab.data(), r.wtab.size() * sizeof(MegaWeight), cudaMemcpyHostToDevice, c->stream));
-    CU(cudaMemsetAsync(p.sync, 0, sizeof(MegaSync), c->stream));
-    CU(cudaStreamSynchronize(c->stream));
-    // the whole grid must be resident at once
-    int per_sm = 0;
-    if (p.bits == 4) CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_token<4>, FK_MEGA_WARPS * 32, p.smem));
-    else CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_token<8>, FK_MEGA_WARPS * 32, p.smem));
-    if (per_sm < 1) { cudaFree(p.ops); cudaFree(p.wtab); cudaFree(p.sync); cudaFree(p.part); return fail(FK_ERR_VALUE, "persistent program: a block does not fit on an SM"); }
-    c->programs.push_back(p); *out = c->programs.size();
-    return FK_OK;
-}
-static fk_status launch_program(Ctx *c, uint64_t id) {
-    if (id == 0 || id > c->programs.size()) return fail(FK_ERR_VALUE, "bad program id");
-    const Program &p = c->programs[id - 1];
-    cudaLaunchConfig_t cfg; memset(&cfg, 0, sizeof cfg);
-    cfg.gridDim = dim3(c->sm_count); cfg.blockDim = dim3(FK_MEGA_WARPS * 32); cfg.dynamicSmemBytes = p.smem; cfg.stream = c->stream;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeCooperative; at[0].val.cooperative = 1;        // all blocks resident, or the launch fails
-    cfg.attrs = at; cfg.numAttrs = 1;
-    c->launches++;
-    unsigned long long *tl = c->timeline;
-    cudaError_t e;
-    if (p.bits == 4) e = cudaLaunchKernelEx(&cfg, k_decode_token<4>, c->state, (const MegaSlot *)p.ops, p.nops, (const MegaWeight *)p.wtab, p.nweights, p.sync, p.max_nsb, p.attn_bytes, p.barriers, tl);
-    else e = cudaLaunchKernelEx(&cfg, k_decode_token<8>, c->state, (const MegaSlot *)p.ops, p.nops, (const MegaWeight *)p.wtab, p.nweights, p.sync, p.max_nsb, p.attn_bytes, p.barriers, tl);
-    if (e != cudaSuccess) return fail(FK_ERR_CUDA, "launch of fusekit_decode_token failed: %s", cudaGetErrorString(e));
-    return FK_OK;
-}
 
 // the next streamed weight after task j (looking a few tasks ahead; wrapping to the start of the list when the
 // list is replayed token after token)
@@ -855,13 +711,10 @@ extern "C" fk_status fk_smoke(fk_handle h, const uint16_t *a, const uint16_t *b,
 
 // ------------------------------------------------------------------ state
 static fk_status set_state(Ctx *c, uint32_t token, uint32_t offset) {
+    if (c->vocab && token >= c->vocab) return fail(FK_ERR_VALUE, "token id %u is outside the embedding table (%u rows)", token, c->vocab);
     FkState *s = (FkState *)c->pinned; memset(s, 0, sizeof(FkState));
     s->token[0] = token; s->offset = offset; s->hist_counter = 0; s->error = 0; s->hist_cap = c->hist_cap;
     CU(cudaMemcpyAsync(c->state, s, sizeof(FkState), cudaMemcpyHostToDevice, c->stream));
-    for (Program &p : c->programs) {        // barrier and ticket counters restart with the state
-        CU(cudaMemsetAsync(p.sync, 0, sizeof(MegaSync), c->stream));
-        for (auto &z : p.zero) CU(cudaMemsetAsync(z.first, 0, z.second, c->stream));
-    }
     return FK_OK;
 }
 extern "C" fk_status fk_state_set(fk_handle h, uint32_t token, uint32_t offset) {
@@ -1025,6 +878,7 @@ extern "C" fk_status fk_sdpa_decode_noalloc(const void *q, const void *cache_k, 
     if (!q || !cache_k || !cache_v || !out) return fail(FK_ERR_VALUE, "fk_sdpa_decode_noalloc: null pointer");
     if (n_kv <= 0 || n_q <= 0 || n_q % n_kv || n_q / n_kv > FK_SDPA_MAXG || (head_dim != 64 && head_dim != 128 && head_dim != 256) || capacity <= 0)
         return fail(FK_ERR_VALUE, "fk_sdpa_decode_noalloc: unsupported shape (group <= 8, head_dim in {64,128,256})");
+    if (pos > 0x7fffffffu) return fail(FK_ERR_VALUE, "fk_sdpa_decode_noalloc: pos %u exceeds 2^31 - 1", pos);
     const int chunks = (capacity + FK_SDPA_KEYS - 1) / FK_SDPA_KEYS, G = n_q / n_kv;
     const size_t need = (size_t)n_q * chunks * (head_dim + 2);
     if (need > FK_NOALLOC_PART_FLOATS || n_kv > FK_NOALLOC_MAX_KV)
@@ -1079,15 +933,48 @@ extern "C" fk_status fk_peer_arena_open(fk_handle h, const void *handles, int ra
     if (!handles || world < 2 || world > FK_PEER_MAX || rank < 0 || rank >= world) return fail(FK_ERR_VALUE, "fk_peer_arena_open: 2..%d ranks", FK_PEER_MAX);
     if (!c->arena) return fail(FK_ERR_STATE, "call fk_peer_arena_export first");
     memset(&c->peers, 0, sizeof c->peers);
-    c->peers.rank = rank; c->peers.world = world;
+    c->peers.rank = rank; c->peers.world = world; c->peers.spin_limit = FK_PEER_SPIN_LIMIT;
     for (int r = 0; r < world; ++r) {
         if (r == rank) { c->peers.base[r] = c->arena; continue; }
         cudaIpcMemHandle_t hd; memcpy(&hd, (const unsigned char *)handles + (size_t)r * sizeof hd, sizeof hd);
         void *p = nullptr;
         cudaError_t e = cudaIpcOpenMemHandle(&p, hd, cudaIpcMemLazyEnablePeerAccess);
-        if (e != cudaSuccess) { cudaGetLastError(); return fail(FK_ERR_CUDA, "cudaIpcOpenMemHandle for rank %d: %s", r, cudaGetErrorString(e)); }
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            for (void *q : c->ipc_open) cudaIpcCloseMemHandle(q);       // nothing stays mapped after a failed open
+            c->ipc_open.clear(); memset(&c->peers, 0, sizeof c->peers);
+            return fail(FK_ERR_CUDA, "cudaIpcOpenMemHandle for rank %d: %s", r, cudaGetErrorString(e));
+        }
+        c->ipc_open.push_back(p);
         c->peers.base[r] = (unsigned char *)p;
     }
+    c->rank = rank; c->world = world; c->peer_ready = true;
+    return FK_OK;
+}
+extern "C" fk_status fk_peer_arena_close(fk_handle h) {
+    CTX(h);
+    CU(cudaStreamSynchronize(c->stream));
+    for (void *p : c->ipc_open) cudaIpcCloseMemHandle(p);
+    for (unsigned char *p : c->loop_arenas) cudaFree(p);
+    c->ipc_open.clear(); c->loop_arenas.clear(); c->peer_ready = false; memset(&c->peers, 0, sizeof c->peers);
+    return FK_OK;
+}
+// Diagnostic form of the peer exchange on ONE GPU: every "rank" gets an arena of its own in this device's memory, so an
+// all-reduce task runs with ranks that never write.  With a small spin_limit the bounded wait of the exchange gives up
+// after that many polls, the kernel sets error bit 0x8000 and returns; nothing hangs.
+extern "C" fk_status fk_peer_arena_loopback(fk_handle h, int rank, int world, uint32_t spin_limit) {
+    CTX(h);
+    if (world < 2 || world > FK_PEER_MAX || rank < 0 || rank >= world || spin_limit == 0) return fail(FK_ERR_VALUE, "fk_peer_arena_loopback: 2..%d ranks, spin_limit > 0", FK_PEER_MAX);
+    if (c->peer_ready) return fail(FK_ERR_STATE, "peer arenas are already open on this handle");
+    memset(&c->peers, 0, sizeof c->peers);
+    c->peers.rank = rank; c->peers.world = world; c->peers.spin_limit = spin_limit;
+    for (int r = 0; r < world; ++r) {
+        unsigned char *p = nullptr;
+        CU(cudaMalloc(&p, PeerArena::bytes())); c->loop_arenas.push_back(p);
+        CU(cudaMemset(p, 0, PeerArena::bytes()));
+        c->peers.base[r] = p;
+    }
+    CU(cudaDeviceSynchronize());
     c->rank = rank; c->world = world; c->peer_ready = true;
     return FK_OK;
 }

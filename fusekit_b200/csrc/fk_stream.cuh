@@ -409,7 +409,6 @@ struct StreamPlan {
     int stages;             // ring depth per warp
 
     unsigned long long *timeline;   // optional [grid][8] phase timestamps (ns) for tuning; null in normal use
-    int dbg_mode;                   // tuning experiments: 1 = skip the unit arithmetic (memory only), 3 = recompute one resident unit (arithmetic only); results invalid
 };
 __device__ __forceinline__ void stamp(const StreamPlan &p, int slot) {
     if (p.timeline && threadIdx.x == 0) {
@@ -504,7 +503,7 @@ __device__ __forceinline__ void stream_begin(WarpStream &ws, const StreamPlan &p
 // Returns false if a barrier wait expired.  Every warp of the block must call this (it synchronises the block once per
 // chunk), after a block-wide synchronisation that follows the clearing of the fold buffer.
 template <int BITS, class Prod, class Epi>
-__device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int dbg_mode, const StreamSmem &sm, Epi &epi) {
+__device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, const StreamSmem &sm, Epi &epi) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5, g = lane >> 2, t = lane & 3;
     Cursor cons; cons.init(W.ntiles, W.nsb, blockIdx.x, gridDim.x, wid, nw);
     bool ok = true;
@@ -526,15 +525,8 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
             float acc_lo = 0.0f, acc_hi = 0.0f;
             for (int n = cons.run(); n > 0 && ok; --n) {    // the units of tile tl in this warp's run
                 const int s = pr.consumed & (FK_STAGES - 1);
-#ifdef FK_TUNING          // FK_DBG=1: memory only, FK_DBG=3: arithmetic only (results invalid); compiled in with -DFK_TUNING only
-                if (dbg_mode != 3 && !mbar_wait(pr.bars + s, (uint32_t)(pr.consumed >> 1) & 1u)) { ok = false; break; }
-                if (pr.consumed == 0) stamp_raw(pr.tl(), 6);
-                if (dbg_mode == 0) unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
-                else if (dbg_mode == 3) { if (pr.valid()) pr.prod.advance(); ++pr.consumed; cons.advance(); unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, 0, lane, acc_lo, acc_hi); continue; }
-#else
                 if (!mbar_wait(pr.bars + s, (uint32_t)(pr.consumed >> 1) & 1u)) { ok = false; break; }
                 unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
-#endif
                 __syncwarp();
                 if (pr.valid()) pr.issue(s);              // refill the stage just drained
                 if (!pr.valid()) pr.drained();
@@ -549,9 +541,6 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
             }
         }
         if (whole) continue;
-#ifdef FK_TUNING
-        if (c == 0) stamp_raw(pr.tl(), 7);
-#endif
         __syncthreads();
         for (int q = wid; q < ct; q += nw) {                  // fold tile q of the chunk in warp order, then its epilogue
             if (t == 0) {
@@ -567,7 +556,7 @@ __device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, int db
 }
 template <int BITS, class Epi>
 __device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm, Epi &epi) {
-    return stream_consume<BITS>(ws, p.W, p.dbg_mode, sm, epi);
+    return stream_consume<BITS>(ws, p.W, sm, epi);
 }
 
 // ------------------------------------------------------------------ repack / probe kernels

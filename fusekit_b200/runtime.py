@@ -390,39 +390,12 @@ class DecodeEngine:
         return self.dispatches_from(self.task_graph())
 
     # ------------------------------------------------------------------ replay
-    def program_build(self, tasks) -> int:
-        """Compile a task list for the persistent kernel; raises FusekitError when the list is not expressible."""
-        arr = (N.Task * len(tasks))(*tasks)
-        pid = C.c_uint64()
-        N.check(self.rt.L.fk_program_build(self.rt.h, arr, len(tasks), C.byref(pid)), "fk_program_build")
-        return pid.value
-
-    def replay_list(self, persistent: bool | None = None) -> list:
-        """What a token replays: the task list itself, or -- when it can be compiled for the persistent kernel --
-        the single FK_TASK_DECODE_TOKEN task that runs it.  `persistent`: None = follow FK_PERSISTENT (default 0: one
-        kernel per task, which is the faster path today), True = require the persistent kernel, False = never."""
-        import os
-        tasks = self.build_dispatches()
-        self.tasks, self.persistent = tasks, False
-        if persistent is None and os.environ.get("FK_PERSISTENT", "0") == "0":
-            persistent = False
-        if persistent is False:
-            return tasks
-        try:
-            pid = self.program_build(tasks)
-        except N.FusekitError:
-            if persistent:
-                raise
-            return tasks
-        self.persistent = True
-        return [N.Task.make(N.TASK_DECODE_TOKEN, -1, {0: pid})]
-
-    def capture(self, persistent: bool | None = None) -> int:
-        replay = self.replay_list(persistent)
-        self.replay = replay
-        arr = (N.Task * len(replay))(*replay)
+    def capture(self) -> int:
+        """Capture the per-token task list once as a CUDA graph (reference: build_icb, lib.rs:459-570)."""
+        self.tasks = self.replay = self.build_dispatches()
+        arr = (N.Task * len(self.replay))(*self.replay)
         g = C.c_uint64()
-        N.check(self.rt.L.fk_graph_capture(self.rt.h, arr, len(replay), C.byref(g)), "fk_graph_capture")
+        N.check(self.rt.L.fk_graph_capture(self.rt.h, arr, len(self.replay), C.byref(g)), "fk_graph_capture")
         self.graph = g.value
         return self.graph
 
@@ -501,6 +474,10 @@ class DecodeEngine:
         except N.FusekitError:
             return False
         return True
+
+    def peer_disable(self):
+        """Drop the peer mappings (some rank could not map them): the library collective takes over."""
+        N.check(self.rt.L.fk_peer_arena_close(self.rt.h), "fk_peer_arena_close")
 
     def close(self):
         self.rt.close()

@@ -49,7 +49,7 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
     lp = lambda l, rel: f"layer_param.{l}.{rel}"
     gateup = (lambda l: {2: lp(l, "mlp.gate_up_proj")}) if fused else (lambda l: {2: lp(l, "mlp.gate_proj"), 3: lp(l, "mlp.up_proj")})
     emb_scale = _bf16_round(math.sqrt(H)) if s.arch == "gemma3" else 1.0      # embed_lookup_decode.rs OUTPUT_SCALE
-    add(K_EMBED, -1, {0: "param.embed_tokens", 1: x(0)}, [H, 1], [emb_scale])
+    add(K_EMBED, -1, {0: "param.embed_tokens", 1: x(0)}, [H, 1, s.vocab], [emb_scale])
     scale = 1.0 / math.sqrt(hd)
     for l in range(s.n_layers):
         cap, theta = s.layer_capacity(l, capacity), s.layer_theta(l)

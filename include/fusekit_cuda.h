@@ -49,10 +49,7 @@ enum {
     FK_TASK_ARGMAX_FINALIZE = 8,       /* argmax_logits_finalize.rs:16-115 (+ history capture) */
     FK_TASK_ALLREDUCE = 9,             /* no reference counterpart: tensor-parallel sum over ranks */
     FK_TASK_RESIDUAL_ADD = 10,         /* no reference counterpart: y = T(sum + residual) after FK_TASK_ALLREDUCE */
-    FK_TASK_DECODE_TOKEN = 11,         /* a whole token's task list run by one persistent kernel (fk_program_build); the
-                                          reference's counterpart is the replay of its event-ordered task graph,
-                                          src/codegen/task_graph_json.rs:33-226 */
-    FK_TASK_KIND_COUNT = 12
+    FK_TASK_KIND_COUNT = 11
 };
 
 /* activation selector for FK_TASK_RMSNORM_GATEUP_ACT */
@@ -64,7 +61,9 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  * encodes).  `buf` holds device addresses from fk_alloc / fk_kv_cache_alloc or
  * fk_weight ids; unused slots are 0.  Slot meaning per kind:
  *
- * EMBED_LOOKUP_DECODE  buf0 table T[V,H]  buf1 x_out T[rows,H]            i0 H  i1 rows         f0 scale
+ * EMBED_LOOKUP_DECODE  buf0 table T[V,H]  buf1 x_out T[rows,H]            i0 H  i1 rows  i2 V (rows of the table; 0 = unchecked)   f0 scale
+ *                      with V given, fk_state_set / fk_decode_chunk refuse a seed token >= V and an id >= V arriving on the
+ *                      device reads row 0 and sets error bit 0x20000
  * RMSNORM_QKV          buf0 x T[H]  buf1 norm_w  buf2 weight(qkv rows: q|k|v)  buf3 lin_bias|0
  *                      buf4 q_out  buf5 cache_k  buf6 cache_v  buf7 k_out|0  buf8 v_out|0
  *                      buf9 pending_y|0  buf10 pending_norm_w  buf11 h_out   (Gemma: x <- T(x + rmsnorm(pending_y)));
@@ -75,7 +74,7 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      i0 n_q  i1 n_kv  i2 head_dim  i3 capacity   f0 eps  f1 rope_theta
  * SDPA_DECODE          buf0 q  buf1 cache_k  buf2 cache_v  buf3 out  buf4 partials(f32)  buf5 counter(u32)
  *                      i0 n_q  i1 n_kv  i2 head_dim  i3 capacity  i4 kernel choice (0 = by shape and capacity, 1 = cluster,
- *                      2 = global partials + ticket, 3 = shared-memory tiles + ticket, 4 = tensor-core cluster)   f0 scale
+ *                      2 = global partials + ticket, 4 = tensor-core cluster)   f0 scale
  *                      partials: n_q * ceil(capacity / 32) * (head_dim + 2) floats; counter: n_kv words, zero before first use
  * LINEAR_RESIDUAL      buf0 x T[K]  buf1 weight  buf2 residual|0  buf3 y_out T[N]  buf4 y_f32_out|0   i0 K  i1 N
  *                      i2 activation rows M (0 or 1: one row).  M = 2..16: x is T[M, K], residual and y_out are T[M, N], row m
@@ -90,7 +89,6 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  * ARGMAX_FINALIZE      buf4 argmax scratch  i0 entries
  * ALLREDUCE            buf0 f32 buffer   i0 count
  * RESIDUAL_ADD         buf0 sum f32[N]  buf1 residual T[N]  buf2 y_out T[N]   i0 N
- * DECODE_TOKEN         buf0 program id from fk_program_build
  */
 typedef struct fk_task {
     int32_t  kind;
@@ -159,14 +157,6 @@ fk_status fk_smoke(fk_handle h, const uint16_t *a, const uint16_t *b, uint16_t *
 fk_status fk_state_set(fk_handle h, uint32_t token, uint32_t offset);
 fk_status fk_state_get(fk_handle h, uint32_t *token, uint32_t *offset, uint32_t *error_word);
 
-/* ---- persistent program: compile a token's task list (embed, rmsnorm_qkv with sinks, sdpa, linear_residual,
- *      rmsnorm_gateup_act, final_rmsnorm_lm_head; 4/8-bit streamed weights of one width) into records that one
- *      resident cooperative kernel walks, with grid barriers where the reference's task graph has events
- *      (src/codegen/task_graph_json.rs:33-226 `events`/`num_triggers`; replay order dispatch.py:3163-3611).
- *      Launch it as a single FK_TASK_DECODE_TOKEN task, eagerly or captured by fk_graph_capture.  Lists it cannot
- *      express are refused with FK_ERR_VALUE and the caller keeps the one-kernel-per-task path. ------------------- */
-fk_status fk_program_build(fk_handle h, const fk_task *tasks, int n, uint64_t *program_out);
-
 /* ---- per-token graph (reference: build_icb lib.rs:459-570, execute_icb lib.rs:718-760,
  *      submit_icb_async / wait_pending_icb lib.rs:659-715, profile_icb_commands lib.rs:821-869) - */
 fk_status fk_graph_capture(fk_handle h, const fk_task *tasks, int n, fk_graph *out);
@@ -195,7 +185,7 @@ fk_status fk_decode_chunk_host(fk_handle h, fk_graph g, uint32_t base_offset, ui
  * memory at start-up and forbids later cudaMalloc calls (they synchronise the device and can fail under memory
  * pressure), or a host that only holds buffers handed to it by another framework.  q [n_q*head_dim], cache_k /
  * cache_v [n_kv, capacity, head_dim] and out [n_q*head_dim] are bf16 device buffers of the caller; `pos` is the
- * position being decoded (keys 0..min(pos+1, capacity)-1 are attended); `stream` is a cudaStream_t (0 = default)
+ * position being decoded (keys 0..min(pos+1, capacity)-1 are attended; pos > 2^31 - 1 is refused); `stream` is a cudaStream_t (0 = default)
  * and the call returns once the work is queued.  The split-K partial sums live in a fixed 4 MiB array inside the
  * library image, so the shape is limited to  n_q * ceil(capacity/32) * (head_dim+2) <= 1048576 floats  and at most
  * 64 kv heads; larger shapes are refused with FK_ERR_VALUE.  The first call on a device looks up the array's device
@@ -207,9 +197,9 @@ fk_status fk_sdpa_decode_noalloc(const void *q, const void *cache_k, const void 
 
 /* tuning aid (no reference counterpart): while `buf` is non-zero the streamed kernels write per-block phase
  * timestamps ([grid][8] u64 nanoseconds: start, dependency met, activations staged, rows done) into it; a graph
- * captured while it is set gives task j the slice starting at entry j * 4096.  A persistent program launched while it
- * is set writes [task][block][8] instead (task start, activations staged, body done, grid barrier passed).
- * `python -m fusekit_b200.timeline` prints both forms. */
+ * captured while it is set gives task j the slice starting at entry j * 4096 (reference: profile_icb_commands,
+ * lib.rs:821-869, times each command; this shows where inside a command the time goes).
+ * `python -m fusekit_b200.timeline` prints it. */
 fk_status fk_debug_timeline(fk_handle h, fk_dptr buf);
 
 /* ---- peer-memory all-reduce for tensor parallelism (no reference counterpart).  Every rank exports a small arena as a
@@ -218,6 +208,13 @@ fk_status fk_debug_timeline(fk_handle h, fk_dptr buf);
  *      kernel (bit-identical on all ranks) instead of the library collective, which stays the fallback. ------------- */
 fk_status fk_peer_arena_export(fk_handle h, void *handle64, size_t cap);
 fk_status fk_peer_arena_open(fk_handle h, const void *handles /* world x 64 bytes */, int rank, int world);
+/* unmaps the peers' arenas; all-reduce tasks launched afterwards use the library collective again (graphs captured
+ * before keep the kernels they were captured with and must not be replayed) */
+fk_status fk_peer_arena_close(fk_handle h);
+/* diagnostic (no reference counterpart): the same exchange with all `world` arenas on this one GPU and the given number
+ * of polls per wait; the other ranks never write, so an all-reduce task gives up after spin_limit polls and sets error
+ * bit 0x8000 in the device state (fk_decode_chunk then returns FK_ERR_DEVICE; fk_state_set clears the word) */
+fk_status fk_peer_arena_loopback(fk_handle h, int rank, int world, uint32_t spin_limit);
 
 /* ---- tensor parallelism (no reference counterpart; NCCL over NVLink) ------ */
 fk_status fk_comm_unique_id(void *id128, size_t cap);          /* rank 0 makes the 128-byte id */

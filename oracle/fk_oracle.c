@@ -577,6 +577,14 @@ double fko_decode_greedy(fko_model *M, uint32_t first_tok, uint32_t pos0, int st
 #endif
     return t1 - t0;
 }
+/* thread count of the OpenMP loops, whatever OMP_NUM_THREADS said at start-up (results do not depend on it) */
+void fko_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
 int fko_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

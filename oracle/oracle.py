@@ -86,6 +86,7 @@ def lib():
     L.fko_head_step.restype = u32; L.fko_head_step.argtypes = [vp, vp, vp]
     L.fko_decode_greedy.restype = C.c_double; L.fko_decode_greedy.argtypes = [vp, u32, u32, i32, vp]
     L.fko_num_threads.restype = i32
+    L.fko_set_num_threads.restype = None; L.fko_set_num_threads.argtypes = [i32]
     L.fko_f32_to_bf16.restype = C.c_uint16; L.fko_f32_to_bf16.argtypes = [f32]
     L.fko_bf16_to_f32.restype = f32; L.fko_bf16_to_f32.argtypes = [C.c_uint16]
     _lib = L
@@ -216,6 +217,20 @@ def num_threads() -> int:
     return int(lib().fko_num_threads())
 
 
+def set_num_threads(n: int) -> int:
+    """Pin the OpenMP thread count of the oracle (launchers such as torchrun export OMP_NUM_THREADS=1)."""
+    lib().fko_set_num_threads(int(n))
+    return num_threads()
+
+
+def model_config(spec, capacity: int, tp_rank: int = 0, tp_size: int = 1) -> "Config":
+    """Oracle configuration of a model shape (any object with the fields of fusekit_b200.model_spec.ModelSpec)."""
+    return Config(arch=1 if spec.arch == "gemma3" else 0, n_layers=spec.n_layers, hidden=spec.hidden, n_q=spec.n_q,
+                  n_kv=spec.n_kv, head_dim=spec.head_dim, inter=spec.inter, vocab=spec.vocab, bits=spec.bits,
+                  eps=spec.eps, theta=spec.theta, theta_local=spec.theta_local, window=spec.window,
+                  global_every=spec.global_every, capacity=capacity, seed=spec.seed, tp_rank=tp_rank, tp_size=tp_size)
+
+
 class Model:
     """Whole-model oracle: seeded weights + a greedy decode loop on the CPU."""
 
@@ -291,6 +306,24 @@ class Model:
         out = np.empty(steps, np.uint32)
         secs = lib().fko_decode_greedy(self._h, first_tok, pos0, steps, _p(out))
         return out, float(secs)
+
+
+def compare_greedy(got_tokens, oracle_model, first_tok: int, pos0: int, tie_ulps: float = 2.0):
+    """Walk the oracle along the GPU's token stream.  Returns (mismatches, ties): a mismatch where the
+    oracle's own margin between its winner and the GPU's token is at most `tie_ulps` bf16 ulps of the logit
+    is a near-tie (random-init logits are almost flat; the reference itself documents token flips
+    from reordered fp32 sums); anything larger is a real mismatch."""
+    tok, mism, ties = first_tok, [], []
+    for i, g in enumerate(int(t) for t in got_tokens):
+        want, _, lg = oracle_model.step(tok, pos0 + i, want_logits=True)
+        if want != g:
+            l = bf16_to_f32(np.asarray(lg, np.uint16))
+            margin = float(l[want] - l[g])
+            ulp = 2.0 ** (np.floor(np.log2(max(abs(float(l[want])), 1e-30))) - 7)
+            (ties if margin <= tie_ulps * ulp else mism).append((i, want, g, margin, ulp))
+        tok = g
+    return mism, ties
+
 
 
 # ====================================================== NumPy restatement ==

@@ -11,11 +11,7 @@ MAX_ABS_TOL = 1e-2
 REL_RMS_TOL = 1e-3
 
 
-def oracle_config(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1) -> O.Config:
-    return O.Config(arch=1 if spec.arch == "gemma3" else 0, n_layers=spec.n_layers, hidden=spec.hidden, n_q=spec.n_q,
-                    n_kv=spec.n_kv, head_dim=spec.head_dim, inter=spec.inter, vocab=spec.vocab, bits=spec.bits,
-                    eps=spec.eps, theta=spec.theta, theta_local=spec.theta_local, window=spec.window,
-                    global_every=spec.global_every, capacity=capacity, seed=spec.seed, tp_rank=tp_rank, tp_size=tp_size)
+oracle_config = O.model_config
 
 
 def weight_provider(spec: ModelSpec):
@@ -55,18 +51,4 @@ def assert_close_bf16(got_bits, want_bits, what="", max_abs_tol=MAX_ABS_TOL, rel
     assert rr <= rel_rms_tol, f"{what}: relative RMS {rr:.4g} > {rel_rms_tol}"
 
 
-def compare_greedy(got_tokens, oracle_model, first_tok: int, pos0: int, tie_ulps: float = 2.0):
-    """Walk the oracle along the GPU's token stream.  Returns (mismatches, ties): a mismatch where the
-    oracle's own margin between its winner and the GPU's token is at most `tie_ulps` bf16 ulps of the logit
-    is a near-tie (random-init logits are almost flat; the reference itself documents token flips
-    from reordered fp32 sums); anything larger is a real mismatch."""
-    tok, mism, ties = first_tok, [], []
-    for i, g in enumerate(int(t) for t in got_tokens):
-        want, _, lg = oracle_model.step(tok, pos0 + i, want_logits=True)
-        if want != g:
-            l = bf(lg)
-            margin = float(l[want] - l[g])
-            ulp = 2.0 ** (np.floor(np.log2(max(abs(float(l[want])), 1e-30))) - 7)
-            (ties if margin <= tie_ulps * ulp else mism).append((i, want, g, margin, ulp))
-        tok = g
-    return mism, ties
+compare_greedy = O.compare_greedy

@@ -193,12 +193,12 @@ def test_rmsnorm_qkv_rope_store(runtime, bits, h, nq, nkv, hd, pos, cap):
     assert_close_bf16(rt.download(ko, (nkv * hd,), np.uint16), y[nq * hd:(nq + nkv) * hd], "raw k")
 
 
-@pytest.mark.parametrize("variant", [0, 2, 3, 4])   # by shape, global partials + ticket, shared-memory tiles + ticket, tensor-core cluster
+@pytest.mark.parametrize("variant", [0, 1, 2, 4])   # by shape, FMA cluster, global partials + ticket, tensor-core cluster
 @pytest.mark.parametrize("nq,nkv,hd", [(14, 2, 64), (28, 4, 128), (8, 4, 256), (5, 1, 128), (1, 1, 64), (40, 8, 128)])
 @pytest.mark.parametrize("pos,cap", [(0, 64), (62, 64), (63, 64), (64, 200), (136, 200), (199, 200), (1000, 96), (1030, 2100), (3000, 2100)])
 def test_sdpa_decode(runtime, nq, nkv, hd, pos, cap, variant):
-    if variant == 3 and hd == 256:
-        pytest.skip("the tiled kernel covers head_dim 64 and 128")
+    if variant == 1 and hd == 256 and nq // nkv > 2:
+        pytest.skip("the FMA cluster kernel takes at most two q heads per kv head at head_dim 256")
     if cap > 1000 and (nq, nkv) not in ((28, 4), (40, 8)):
         pytest.skip("long caches are exercised on the benchmark shapes only")
     rt = runtime
@@ -218,6 +218,29 @@ def test_sdpa_decode(runtime, nq, nkv, hd, pos, cap, variant):
     rt.launch(task)                                                   # the ticket counters reset themselves
     assert np.array_equal(rt.download(out, (nq * hd,), np.uint16), got)
     assert not rt.download(cnt, (nkv,), np.uint32).any()
+
+
+@pytest.mark.parametrize("variant", [0, 2, 4])
+@pytest.mark.parametrize("nq,nkv,hd", [(28, 4, 128), (40, 8, 128), (8, 4, 256)])
+@pytest.mark.parametrize("pos", [4095, 4096, 4351, 5000])
+def test_sdpa_decode_at_benchmark_capacity(runtime, nq, nkv, hd, pos, variant):
+    """The capacities the 4096-token benchmark configurations run at (4096 + decoded tokens; the reference's own kernel
+    stopped at 4096 keys, sdpa_decode.rs:76): last position before 4096, the first after, the last row of the cache and
+    a wrapped ring position."""
+    rt, cap = runtime, 4352
+    q = normal(f"bq{nq}", nq * hd)
+    ck, cv = normal(f"bk{hd}", nkv * cap * hd), normal(f"bv{hd}", nkv * cap * hd)
+    kv_len, scale = min(pos + 1, cap), 1.0 / math.sqrt(hd)
+    want = O.sdpa_decode(q, ck, cv, nq, nkv, hd, cap, kv_len, scale)
+    chunks = (cap + 31) // 32
+    out, part, cnt = rt.alloc(nq * hd * 2), rt.alloc(nq * chunks * (hd + 2) * 4), rt.alloc(nkv * 4)
+    bufs = [rt.to_device(q), rt.to_device(ck), rt.to_device(cv)]
+    task = T(N.TASK_SDPA_DECODE, 0, {0: bufs[0], 1: bufs[1], 2: bufs[2], 3: out, 4: part, 5: cnt}, [nq, nkv, hd, cap, variant], [scale])
+    rt.state_set(0, pos)
+    rt.launch(task)
+    assert_close_bf16(rt.download(out, (nq * hd,), np.uint16), want, f"sdpa capacity {cap} kv_len {kv_len} variant {variant}")
+    for p in bufs + [out, part, cnt]:
+        N.check(rt.L.fk_free(rt.h, p), "fk_free")
 
 
 @pytest.mark.parametrize("bits", [4, 8, 16])

@@ -1,0 +1,74 @@
+"""Whole-model parity on the configurations that are benchmarked: the CPU oracle is walked along the GPU's greedy token
+stream (reference: scripts/check_correctness.py:28-172 compares argmax, top-5 and max/mean logit differences between the
+fused path and plain mlx-lm), hidden states are checked per layer on identical layer inputs, and the measured worst
+values are appended to gpurun_out/parity_measured.jsonl when that folder exists."""
+import dataclasses
+import json
+import os
+
+import numpy as np
+import pytest
+
+from fusekit_b200.model_spec import CONFIGS
+from fusekit_b200.runtime import DecodeEngine
+from oracle import oracle as O
+from tests.helpers import REL_RMS_TOL, compare_greedy, oracle_config
+from tests.test_gpu_model import check_layers_teacher_forced, check_stages_qwen
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def record(**kw):
+    d = os.path.join(ROOT, "gpurun_out")
+    if os.path.isdir(d):
+        with open(os.path.join(d, "parity_measured.jsonl"), "a") as f:
+            f.write(json.dumps(kw) + "\n")
+    print("parity:", kw)
+
+
+def run_config(spec, ctx, steps, what, stage_layers=None, forced_layers=None, max_ties=4):
+    cap = ctx + steps + 8
+    O.set_num_threads(len(os.sched_getaffinity(0)))
+    m = O.Model(oracle_config(spec, cap)); m.prefill_kv(ctx)
+    eng = DecodeEngine(spec, cap)
+    try:
+        eng.load_synthetic(); eng.prefill_kv_synthetic(ctx)
+        got, _ = eng.decode_chunk(ctx, 3, steps)
+        mism, ties = compare_greedy(got, m, 3, ctx)
+        # hidden states of the token after the chunk: whole layers on the GPU's own layer inputs and caches
+        pos, tok = ctx + steps, int(got[-1])
+        eng.decode_chunk(pos, tok, 1)
+        worst = check_layers_teacher_forced(eng, m, pos, what, rel_tol=5e-3, layers=forced_layers)
+        stage = None
+        if stage_layers is not None:
+            stage = check_stages_qwen(eng, m, tok, pos, what, layers=stage_layers)
+        record(config=what, ctx=ctx, tokens=steps, mismatches=len(mism), near_ties=[(t[0], round(t[3], 5), round(t[4], 5)) for t in ties],
+               whole_layer_worst_max_abs=worst[0], whole_layer_worst_rel_rms=worst[1], stage_worst_rel_rms=stage)
+        assert not mism, f"{what}: greedy tokens differ beyond a near-tie: {mism}"
+        assert len(ties) <= max_ties, f"{what}: too many near-tie flips in {steps} steps: {ties}"
+    finally:
+        eng.close(); m.close()
+
+
+def test_config2_qwen7b_q4_ctx512_first_64_tokens():
+    """The headline configuration: 7B-shaped q4, KV pre-filled to 512, 64 greedy steps against the oracle; every stage of
+    layers 0 and 27 within the 1e-2 / 1e-3 bar, whole layers on identical inputs within 1e-2 / 5e-3."""
+    run_config(CONFIGS["qwen2.5-7b"].with_bits(4), 512, 64, "qwen7b-q4-ctx512", stage_layers=(0, 27))
+
+
+@pytest.mark.parametrize("bits", [8, 16])
+def test_config3_qwen7b_q8_and_bf16_ctx512_16_tokens(bits):
+    run_config(CONFIGS["qwen2.5-7b"].with_bits(bits), 512, 16, f"qwen7b-{'q8' if bits == 8 else 'bf16'}-ctx512", forced_layers=(0, 13, 27), max_ties=2)
+
+
+def test_config4_gemma4b_q4_ctx4096_16_tokens():
+    """All 34 Gemma-shaped layers at context 4096 (sliding rings wrapped four times, global layers at capacity > 4096);
+    the vocabulary is cut to 16k rows so the CPU head stays cheap."""
+    spec = dataclasses.replace(CONFIGS["gemma3-4b"], name="gemma3-4b-16kvocab", vocab=16384)
+    run_config(spec, 4096, 16, "gemma4b-q4-ctx4096", forced_layers=(0, 5, 17, 33), max_ties=2)
+
+
+def test_config5_qwen32b_q4_ctx4096_on_four_layers():
+    spec = dataclasses.replace(CONFIGS["qwen2.5-32b"], name="qwen32b-4layers", n_layers=4, vocab=16384)
+    run_config(spec, 4096, 8, "qwen32b-q4-ctx4096-4layers", stage_layers=(0, 3), max_ties=2)
