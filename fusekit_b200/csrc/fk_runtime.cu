@@ -79,7 +79,7 @@ struct Ctx {
     std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
     bool pending = false; bool pdl = true; int sm_count = 148;
     float *qmm_scratch = nullptr; unsigned int *qmm_counters = nullptr;   // K-split partial sums and tickets of the several-row projection
-    bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_cl = 0;
+    bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; int force_split = -1; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_cl = 0;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
@@ -134,6 +134,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     if (e && !strcmp(e, "fma")) c->sdpa_mma = false;
     e = getenv("FK_SDPA_CL"); if (e && (atoi(e) == 1 || atoi(e) == 2 || atoi(e) == 4 || atoi(e) == 8)) c->sdpa_cl = atoi(e);      // CTAs per kv head of the tensor-core attention
     e = getenv("FK_WARPS"); if (e) c->force_warps = atoi(e);
+    e = getenv("FK_SPLIT"); if (e) c->force_split = atoi(e);        // log2 of the warps sharing a row tile (tuning)
 #define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>)); CU(big_smem(K<16, 8>)); CU(big_smem(K<16, 16>))
 #define BIG4P(K) CU(big_smem(K<4, 8, true>)); CU(big_smem(K<4, 16, true>)); CU(big_smem(K<8, 8, true>)); CU(big_smem(K<8, 16, true>)); CU(big_smem(K<16, 8, true>)); CU(big_smem(K<16, 16, true>))
     BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head); BIG4P(k_s_rmsnorm_qkv); BIG4P(k_s_gateup); BIG4P(k_s_head);
@@ -418,9 +419,10 @@ static int grid_for(Ctx *c, long long units, int warps_per_block) {
 }
 
 // Work split of a streamed kernel.  Blocks have 8 warps and sit two to an SM when their shared memory (ring +
-// staged activations) allows, else 16 warps and one per SM.  A block owns the row tiles block, block+grid, ... and
-// deals their units to its warps in chunks of 8 tiles (fk_stream.cuh).
-struct Shape { int grid, warps; size_t smem; };
+// staged activations) allows, else 16 warps and one per SM.  While there are fewer row tiles than warps in the grid, the
+// K range of a tile is split over 2, 4, ... warps of one block (never more parts than super-blocks, rounded up to a power
+// of two); a block then works on warps / parts tiles per round (fk_stream.cuh).
+struct Shape { int grid, warps, lsplit; size_t smem; };
 static Shape plan_shape(Ctx *c, const Weight *w) {
     Shape s;
     s.warps = 8;
@@ -432,7 +434,13 @@ static Shape plan_shape(Ctx *c, const Weight *w) {
         if (wide <= 226 * 1024) { s.warps = 16; s.smem = wide; }          // else: 8 warps, one block per SM (very long K)
     }
     const int slots = c->sm_count * per_sm;
-    s.grid = w->ntiles < slots ? w->ntiles : slots;
+    const long long total_warps = (long long)slots * s.warps;
+    int ls = 0;
+    while ((2 << ls) <= s.warps && (long long)w->ntiles * (2 << ls) <= total_warps && (1 << ls) < w->nsb) ++ls;
+    if (c->force_split >= 0) { ls = c->force_split; while ((1 << ls) > s.warps) --ls; }
+    s.lsplit = ls;
+    const int tpb = s.warps >> ls, rounds = (w->ntiles + tpb - 1) / tpb;
+    s.grid = rounds < slots ? rounds : slots;
     if (s.grid < 1) s.grid = 1;
     return s;
 }
@@ -450,7 +458,7 @@ static Weight *task_stream_weight(Ctx *c, const fk_task *t) {
 }
 static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *next) {
     const Shape sh = plan_shape(c, w);
-    p->W = w->tview(); p->stages = c->stages;
+    p->W = w->tview(); p->stages = c->stages; p->lsplit = sh.lsplit;
     p->timeline = c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr;
     return sh;
 }

@@ -37,6 +37,7 @@ __host__ __device__ inline int unit_vec(int bits) { return bits == 16 ? 256 : FK
 __host__ __device__ inline int unit_k(int bits) { return bits == 4 ? 512 : bits == 8 ? 256 : 128; }      // activations covered by a unit
 #define FK_STREAM_MAXWARPS 16         // blocks run 8 warps (two blocks per SM) or 16 (one per SM, large activations)
 #define FK_STAGES 2                     // ring depth per warp
+#define FK_ZERO_BYTES 2048              // zero region: 8 groups x 192 bytes of digits and some slack
 #define FK_WAIT_LIMIT (1u << 24)        // bounded mbarrier wait; on expiry the kernel flags an error and leaves
 #ifndef FK_J_UNROLL
 #define FK_J_UNROLL 8                   // unroll factor of the group loop inside a unit (code size against scheduling freedom)
@@ -119,10 +120,10 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 // ------------------------------------------------------------------ shared-memory plan of a streamed kernel
 struct StreamSmem {
     uint64_t *bars;     // [warps * stages]
-    uint4 *zero;        // 16 zero vectors (what a lane reads for the groups that are not its own)
+    uint4 *zero;        // FK_ZERO_BYTES of zeros: a super-block of digits for the lanes whose group is not the one being multiplied
     float2 *xsi;        // [groups] (sum of the group's activations, 1 / power-of-two scale of its integer digits)
     float *red;         // [48]
-    float *fold;        // [2][FK_CHUNK_TILES][16 warps][16] per-warp row sums of the tiles of a chunk
+    float *fold;        // [2][16 warps][16] per-warp row sums of a round
     uint2 *xs;          // [groups][3 digits][4 lanes][1 or 2] activation digits in MMA B-operand order
     uint4 *ring;        // [warps * stages * FK_UNIT_VEC]
 };
@@ -130,7 +131,7 @@ __host__ __device__ inline int stream_groups(int nsb) { return nsb * 8; }
 // bytes of staged activations per group: 4-bit 3 digits x 4 x 16, 8-bit 3 x 4 x 8, bf16 weights: the bf16 values themselves
 __host__ __device__ inline int xs_group_bytes(int bits) { return bits == 4 ? 192 : bits == 8 ? 96 : 32; }      // bf16: a group is one k16 step, 4 lanes x {b0, b1}
 __host__ __device__ inline size_t stream_smem_bytes(int nsb, int stages, int warps, int bits) {
-    size_t b = 512 /*bars*/ + 256 /*zero*/ + (size_t)stream_groups(nsb) * 8 + 192 /*red*/ + 2 * 8 * FK_STREAM_MAXWARPS * 16 * 4 /*fold: 2 x FK_CHUNK_TILES tiles*/;
+    size_t b = 512 /*bars*/ + FK_ZERO_BYTES + (size_t)stream_groups(nsb) * 8 + 192 /*red*/ + 2 * FK_STREAM_MAXWARPS * 16 * 4 /*fold: two rounds of per-warp row sums*/;
     b = (b + 15) & ~(size_t)15;
     b += (size_t)stream_groups(nsb) * xs_group_bytes(bits);    // xs
     b = (b + 127) & ~(size_t)127;
@@ -143,10 +144,10 @@ __device__ __forceinline__ StreamSmem stream_carve(unsigned char *base, int nsb,
     StreamSmem s;
     size_t o = 0;
     s.bars = (uint64_t *)(base + o); o += 512;
-    s.zero = (uint4 *)(base + o); o += 256;
+    s.zero = (uint4 *)(base + o); o += FK_ZERO_BYTES;
     s.xsi = (float2 *)(base + o); o += (size_t)stream_groups(nsb) * 8;
     s.red = (float *)(base + o); o += 192;
-    s.fold = (float *)(base + o); o += 2 * 8 * FK_STREAM_MAXWARPS * 16 * 4;
+    s.fold = (float *)(base + o); o += 2 * FK_STREAM_MAXWARPS * 16 * 4;
     o = (o + 15) & ~(size_t)15;
     s.xs = (uint2 *)(base + o); o += (size_t)stream_groups(nsb) * xs_group_bytes(bits);
     o = (o + 127) & ~(size_t)127;
@@ -221,7 +222,7 @@ template <int BITS>
 __device__ __forceinline__ void stage_pad(const StreamSmem &sm, int k, int nsb) {
     const int per_group = BITS == 4 ? 64 : BITS == 8 ? 32 : 16, groups = stream_groups(nsb), g0 = k / per_group;
     constexpr int V = BITS == 4 ? 24 : BITS == 8 ? 12 : 4;          // uint2 per group
-    if (threadIdx.x < 16) sm.zero[threadIdx.x] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < FK_ZERO_BYTES / 16; i += blockDim.x) sm.zero[i] = make_uint4(0, 0, 0, 0);
     for (int i = g0 * V + threadIdx.x; i < groups * V; i += blockDim.x) sm.xs[i] = make_uint2(0, 0);
     for (int i = g0 + threadIdx.x; i < groups; i += blockDim.x) sm.xsi[i] = make_float2(0.0f, 0.0f);
 }
@@ -331,53 +332,77 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
 }
 
 // ------------------------------------------------------------------ one unit: 16 rows x 8 groups
+// Shared-memory loads at [address + immediate]: the unit loop is fully unrolled, so every offset inside a ring slot or a
+// super-block of digits is a compile-time constant and costs no address arithmetic.
+template <int OFF> __device__ __forceinline__ uint4 lds128o(uint32_t addr) {
+    uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF)); return v;
+}
+template <int OFF> __device__ __forceinline__ uint2 lds64o(uint32_t addr) {
+    uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF)); return v;
+}
+// first MMA of a chain: the accumulator starts at zero (constant-zero inputs instead of cleared registers)
+__device__ __forceinline__ void imma_uu0(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void imma_us0(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
 // bf16 weights: eight k16 steps; the activations sit in B column 0 (lanes with g == 0), so D[:, 0] = W x lands in the lanes
-// with t == 0 and the other lanes add zeros
-__device__ __forceinline__ void unit_compute_bf16(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
+// with t == 0 and the other lanes add zeros.  `ub`: shared address of this lane's first vector of the unit.
+__device__ __forceinline__ void unit_compute_bf16(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     const int g = lane >> 2, t = lane & 3;
     float c[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
     const uint2 *z2 = reinterpret_cast<const uint2 *>(sm.zero);
 #pragma unroll
     for (int s8 = 0; s8 < 8; ++s8) {
-        const uint4 w = u[s8 * 32 + lane];
+        const uint4 w = lds128(ub + (uint32_t)s8 * 512u);
         const uint2 b = (g == 0) ? sm.xs[(size_t)(sb * 8 + s8) * 4 + t] : z2[t];
         mma_bf16(c[s8 & 1], w.x, w.y, w.z, w.w, b.x, b.y);
     }
     acc_lo += c[0][0] + c[1][0]; acc_hi += c[0][2] + c[1][2];
 }
-template <int BITS>
-__device__ __forceinline__ void unit_compute_q(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
-    const int g = lane >> 2, t = lane & 3;
-    // [digit][fragment] MMA chains; at 4 bits the odd nibbles are used in place (bytes 16 q) and accumulate in chains of their own
-    int cc[3][4], co[BITS == 4 ? 3 : 1][4];
-#pragma unroll
-    for (int d = 0; d < 3; ++d) { cc[d][0] = cc[d][1] = cc[d][2] = cc[d][3] = 0; }
-#pragma unroll
-    for (int d = 0; d < (BITS == 4 ? 3 : 1); ++d) { co[d][0] = co[d][1] = co[d][2] = co[d][3] = 0; }
-    // per group: 3 digits x 4 lanes x {16 or 8} bytes; lane t reads its vector of each digit, or zeros when the group is not its own
-    constexpr uint32_t GB = BITS == 4 ? 192u : 96u, DB = BITS == 4 ? 64u : 32u, LB = BITS == 4 ? 16u : 8u;
-    const uint32_t zaddr = smem_u32(sm.zero) + (uint32_t)t * LB;
-    const uint32_t xaddr = smem_u32(sm.xs) + (uint32_t)(sb * 8) * GB + (uint32_t)t * LB;
-    FK_UNROLL(FK_J_UNROLL)
-    for (int j = 0; j < 8; ++j) {
-        const uint4 w = u[j * 32 + lane];
-        const uint32_t xa = (g == j) ? xaddr + (uint32_t)j * GB : zaddr;
-        if (BITS == 4) {
-            // rows g (w.x word A, w.y word B) and g+8 (w.z, w.w).  Even MMA: k-slots 4t.. = word A even nibbles, 4t+16.. = word B even
-            // nibbles; odd MMA the same with the odd nibbles left in the high half of each byte (16 q, exact in u8 and in s32)
-            const uint32_t ea = w.x & 0x0F0F0F0Fu, oa = w.x & 0xF0F0F0F0u, ea8 = w.z & 0x0F0F0F0Fu, oa8 = w.z & 0xF0F0F0F0u;
-            const uint32_t eb = w.y & 0x0F0F0F0Fu, ob = w.y & 0xF0F0F0F0u, eb8 = w.w & 0x0F0F0F0Fu, ob8 = w.w & 0xF0F0F0F0u;
-            const uint4 x0 = lds128(xa), x1 = lds128(xa + DB), x2 = lds128(xa + 2 * DB);     // digits 0..2: {A even, B even, A odd, B odd}
+// one group of a 4- or 8-bit unit: rows g (w.x word A, w.y word B) and g + 8 (w.z, w.w) against the group's three digits
+template <int BITS, int J>
+__device__ __forceinline__ void group_compute(uint32_t ub, uint32_t xsel, int (&cc)[3][4], int (&co)[3][4]) {
+    constexpr int GB = BITS == 4 ? 192 : 96, DB = BITS == 4 ? 64 : 32;
+    const uint4 w = lds128o<J * 512>(ub);
+    if (BITS == 4) {
+        // Even MMA: k-slots 4t.. = word A even nibbles, 4t+16.. = word B even nibbles; odd MMA the same with the odd nibbles
+        // left in the high half of each byte (16 q, exact in u8 and in s32)
+        const uint32_t ea = w.x & 0x0F0F0F0Fu, oa = w.x & 0xF0F0F0F0u, ea8 = w.z & 0x0F0F0F0Fu, oa8 = w.z & 0xF0F0F0F0u;
+        const uint32_t eb = w.y & 0x0F0F0F0Fu, ob = w.y & 0xF0F0F0F0u, eb8 = w.w & 0x0F0F0F0Fu, ob8 = w.w & 0xF0F0F0F0u;
+        const uint4 x0 = lds128o<J * GB>(xsel), x1 = lds128o<J * GB + DB>(xsel), x2 = lds128o<J * GB + 2 * DB>(xsel);     // digits 0..2: {A even, B even, A odd, B odd}
+        if (J == 0) {
+            imma_uu0(cc[0], ea, ea8, eb, eb8, x0.x, x0.y); imma_uu0(cc[1], ea, ea8, eb, eb8, x1.x, x1.y); imma_us0(cc[2], ea, ea8, eb, eb8, x2.x, x2.y);
+            imma_uu0(co[0], oa, oa8, ob, ob8, x0.z, x0.w); imma_uu0(co[1], oa, oa8, ob, ob8, x1.z, x1.w); imma_us0(co[2], oa, oa8, ob, ob8, x2.z, x2.w);
+        } else {
             imma_uu(cc[0], ea, ea8, eb, eb8, x0.x, x0.y); imma_uu(cc[1], ea, ea8, eb, eb8, x1.x, x1.y); imma_us(cc[2], ea, ea8, eb, eb8, x2.x, x2.y);
             imma_uu(co[0], oa, oa8, ob, ob8, x0.z, x0.w); imma_uu(co[1], oa, oa8, ob, ob8, x1.z, x1.w); imma_us(co[2], oa, oa8, ob, ob8, x2.z, x2.w);
-        } else {
-            const uint2 x0 = lds64(xa), x1 = lds64(xa + DB), x2 = lds64(xa + 2 * DB);     // digits 0..2: {word A, word B}
-            imma_uu(cc[0], w.x, w.z, w.y, w.w, x0.x, x0.y);
-            imma_uu(cc[1], w.x, w.z, w.y, w.w, x1.x, x1.y);
-            imma_us(cc[2], w.x, w.z, w.y, w.w, x2.x, x2.y);
         }
+    } else {
+        const uint2 x0 = lds64o<J * GB>(xsel), x1 = lds64o<J * GB + DB>(xsel), x2 = lds64o<J * GB + 2 * DB>(xsel);     // digits 0..2: {word A, word B}
+        if (J == 0) { imma_uu0(cc[0], w.x, w.z, w.y, w.w, x0.x, x0.y); imma_uu0(cc[1], w.x, w.z, w.y, w.w, x1.x, x1.y); imma_us0(cc[2], w.x, w.z, w.y, w.w, x2.x, x2.y); }
+        else { imma_uu(cc[0], w.x, w.z, w.y, w.w, x0.x, x0.y); imma_uu(cc[1], w.x, w.z, w.y, w.w, x1.x, x1.y); imma_us(cc[2], w.x, w.z, w.y, w.w, x2.x, x2.y); }
     }
-    const uint4 sb4 = u[256 + lane];
+}
+// `ub`: shared address of this lane's first vector of the unit; `xb`: shared address of the lane's 16 (8) bytes of digit 0 of
+// the super-block's first group; `zb`: the same inside the zero region, which spans a whole super-block of digits, so the
+// choice between a group's digits and zeros is one select on the base address and every load keeps its immediate offset.
+template <int BITS>
+__device__ __forceinline__ void unit_compute_q(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
+    const int g = lane >> 2, t = lane & 3;
+    // [digit][fragment] MMA chains; at 4 bits the odd nibbles are used in place (bytes 16 q) and accumulate in chains of their own
+    int cc[3][4], co[3][4];
+    constexpr uint32_t GB = BITS == 4 ? 192u : 96u, LB = BITS == 4 ? 16u : 8u;
+    const uint32_t zb = smem_u32(sm.zero) + (uint32_t)t * LB;
+    const uint32_t xb = smem_u32(sm.xs) + (uint32_t)(sb * 8) * GB + (uint32_t)t * LB;
+    group_compute<BITS, 0>(ub, g == 0 ? xb : zb, cc, co); group_compute<BITS, 1>(ub, g == 1 ? xb : zb, cc, co);
+    group_compute<BITS, 2>(ub, g == 2 ? xb : zb, cc, co); group_compute<BITS, 3>(ub, g == 3 ? xb : zb, cc, co);
+    group_compute<BITS, 4>(ub, g == 4 ? xb : zb, cc, co); group_compute<BITS, 5>(ub, g == 5 ? xb : zb, cc, co);
+    group_compute<BITS, 6>(ub, g == 6 ? xb : zb, cc, co); group_compute<BITS, 7>(ub, g == 7 ? xb : zb, cc, co);
+    const uint4 sb4 = lds128o<4096>(ub);
     const float2 xi0 = sm.xsi[sb * 8 + 2 * t], xi1 = sm.xsi[sb * 8 + 2 * t + 1];      // (group sum, 1/scale)
     const float X0 = xi0.x, X1 = xi1.x, i0 = xi0.y, i1 = xi1.y;
     const float s00 = bf_lo(sb4.x), s01 = bf_hi(sb4.x), s10 = bf_lo(sb4.y), s11 = bf_hi(sb4.y);
@@ -397,17 +422,21 @@ __device__ __forceinline__ void unit_compute_q(const uint4 *u, const StreamSmem 
 }
 
 template <int BITS>
-__device__ __forceinline__ void unit_compute(const uint4 *u, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
-    if constexpr (BITS == 16) unit_compute_bf16(u, sm, sb, lane, acc_lo, acc_hi);
-    else unit_compute_q<BITS>(u, sm, sb, lane, acc_lo, acc_hi);
+__device__ __forceinline__ void unit_compute(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
+    if constexpr (BITS == 16) unit_compute_bf16(ub, sm, sb, lane, acc_lo, acc_hi);
+    else unit_compute_q<BITS>(ub, sm, sb, lane, acc_lo, acc_hi);
 }
 
 // ------------------------------------------------------------------ per-warp unit stream
-#define FK_CHUNK_TILES 8            // row tiles a block works on at a time
+// Work split.  The host picks `lsplit`: S = 2^lsplit warps of a block share one row tile and split its K range (S = 1: a
+// warp owns whole tiles).  A block of W warps works on W / S tiles per round: block b, round r takes tiles
+// (r * grid + b) * (W / S) + [0, W / S); warp w handles tile slot w / S, part w % S, i.e. super-blocks
+// [part * nsb / S, (part + 1) * nsb / S) of that tile -- a run of units that is contiguous in memory.  The parts of a tile
+// are summed in part order through shared memory by the part-0 warp (deterministic), which then runs the epilogue.
 struct StreamPlan {
     TiledW W;
-    int stages;             // ring depth per warp
-
+    int stages;             // ring depth per warp (FK_STAGES)
+    int lsplit;             // log2 of the warps sharing a tile
     unsigned long long *timeline;   // optional [grid][8] phase timestamps (ns) for tuning; null in normal use
 };
 __device__ __forceinline__ void stamp(const StreamPlan &p, int slot) {
@@ -416,68 +445,46 @@ __device__ __forceinline__ void stamp(const StreamPlan &p, int slot) {
         p.timeline[blockIdx.x * 8 + slot] = t;
     }
 }
-// Work of a block: its row tiles are block, block+grid, block+2*grid, ... taken in chunks.  While at least one tile per
-// warp is left a chunk is `nwarps` tiles and every warp owns whole tiles of it (no fold); the remainder goes in chunks
-// of up to FK_CHUNK_TILES tiles whose units (tile, super-block) are dealt to the warps in contiguous runs, so every
-// warp gets the same number of units (+-1) and a tile's K range is shared by the warps of one block only.
-struct Cursor {
-    int nsb, ntl, nwarps, lw, wid, block, grid, nb; // ntl: tiles of this block; lw: log2(nwarps); nb: chunks of one tile per warp
-    int chunk, tq, sbv, left;                   // current chunk, tile inside the chunk, super-block, units left in the chunk
-    float inv_nsb;
-    __device__ __forceinline__ void init(int ntiles, int nsb_, int block_, int grid_, int wid_, int nwarps_) {
-        nsb = nsb_; nwarps = nwarps_; wid = wid_; block = block_; grid = grid_;
-        lw = 31 - __clz(nwarps_);               // blocks have 8 or 16 warps
-        inv_nsb = __frcp_rn((float)nsb_);
-        ntl = block_ < ntiles ? (ntiles - block_ + grid_ - 1) / grid_ : 0;
-        nb = ntl >> lw;
-        chunk = -1; left = 0;
-        next_chunk();
-    }
-    __device__ __forceinline__ int nbig() const { return nb; }
-    __device__ __forceinline__ int nchunks() const { return nb + (ntl - (nb << lw) + FK_CHUNK_TILES - 1) / FK_CHUNK_TILES; }
-    __device__ __forceinline__ int chunk_start(int c) const { return c < nb ? (c << lw) : (nb << lw) + (c - nb) * FK_CHUNK_TILES; }
-    __device__ __forceinline__ int chunk_tiles(int c) const {
-        if (c < nb) return nwarps;
-        const int r = ntl - chunk_start(c);
-        return r < FK_CHUNK_TILES ? r : FK_CHUNK_TILES;
-    }
-    // a warp takes a contiguous run of the chunk's units (tile-major), so it rarely changes tile
-    __device__ __forceinline__ void next_chunk() {
-        const int nc = nchunks();
-        while (left == 0 && ++chunk < nc) {
-            if (chunk < nb) { left = nsb; tq = wid; sbv = 0; continue; }        // one whole tile per warp
-            const int total = chunk_tiles(chunk) * nsb, u0 = (wid * total) >> lw, u1 = ((wid + 1) * total) >> lw;
-            left = u1 - u0;
-            tq = (int)(((float)u0 + 0.5f) * inv_nsb);       // u0 / nsb, exact: u0 < 2^12 and the quotient is >= 0.5 / nsb away from an integer
-            sbv = u0 - tq * nsb;
-        }
-    }
-    __device__ __forceinline__ bool valid() const { return left > 0; }
-    __device__ __forceinline__ int tile_local() const { return chunk_start(chunk) + tq; }
-    __device__ __forceinline__ int sb() const { return sbv; }
-    __device__ __forceinline__ size_t unit_index() const { return (size_t)(block + tile_local() * grid) * nsb + sbv; }
-    // units of the current tile left in this warp's run
-    __device__ __forceinline__ int run() const { const int r = nsb - sbv; return r < left ? r : left; }
-    __device__ __forceinline__ void advance() {
-        if (++sbv >= nsb) { sbv = 0; ++tq; }
-        if (--left == 0) next_chunk();
-    }
-};
 __device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
-// Producer side of a warp's ring.  `consumed` counts the units this warp has taken out of the ring since its
-// barriers were initialised: it names the ring slot (consumed % stages) and the barrier phase to wait for.
+__device__ __forceinline__ void mbar_expect_tx_a(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s_a(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// bounded wait on a barrier given by shared address: returns false if it never completed
+__device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < FK_WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+// A warp's ring and its walk over the runs: the producer fetches the same sequence of units the consumer takes, FK_STAGES
+// units ahead.  `fetched` / `consumed` count units since the barriers were initialised: they name the ring slot
+// (count % FK_STAGES) and the barrier phase.
 struct WarpStream {
-    uint64_t *bars; uint4 *ring; Cursor prod; int stages, consumed, uvec; const StreamPlan *plan; bool announced;
-    __device__ __forceinline__ bool valid() const { return prod.valid(); }
-    __device__ __forceinline__ unsigned long long *tl() const { return plan->timeline; }
-    __device__ __forceinline__ void issue(int stage) {
+    const uint4 *src;           // next unit to fetch
+    size_t jump;                // vectors from the end of a run to the start of the next run of this warp
+    uint32_t bar, ring;         // shared addresses of stage 0's barrier and slot
+    int p_tile, p_left;         // producer: tile of the run being fetched (>= ntiles: nothing left), units left in it
+    int cnt, tstep, ntiles;     // units per run, tile stride between rounds
+    int uvec, fetched, consumed;
+    bool announced;
+    __device__ __forceinline__ bool valid() const { return p_tile < ntiles; }
+    __device__ __forceinline__ void issue() {
+        const uint32_t s = (uint32_t)fetched & (FK_STAGES - 1);
         if ((threadIdx.x & 31) == 0) {
-            mbar_expect_tx(bars + stage, (uint32_t)uvec * 16u);
-            bulk_g2s(ring + (size_t)stage * FK_UNIT_VEC, plan->W.units + prod.unit_index() * uvec, (uint32_t)uvec * 16u, bars + stage);
+            mbar_expect_tx_a(bar + s * 8u, (uint32_t)uvec * 16u);
+            bulk_g2s_a(ring + s * (uint32_t)FK_UNIT_BYTES, src, (uint32_t)uvec * 16u, bar + s * 8u);
         }
-        prod.advance();
+        ++fetched; src += uvec;
+        if (--p_left == 0) { p_tile += tstep; p_left = cnt; src += jump; }
     }
     // everything this warp needs is in flight: let the next kernel start
     __device__ __forceinline__ void drained() {
@@ -485,78 +492,67 @@ struct WarpStream {
         announced = true; pdl_launch_dependents();
     }
 };
-// before griddepcontrol.wait: barriers up, ring filled with the warp's first units, fold buffer cleared
+// before griddepcontrol.wait: barriers up, ring filled with the warp's first units
 __device__ __forceinline__ void stream_begin(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm) {
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    ws.stages = p.stages; ws.bars = sm.bars + wid * p.stages; ws.ring = sm.ring + (size_t)wid * p.stages * FK_UNIT_VEC;
-    ws.consumed = 0; ws.plan = &p; ws.announced = false; ws.uvec = unit_vec(p.W.bits);
-    ws.prod.init(p.W.ntiles, p.W.nsb, blockIdx.x, gridDim.x, wid, blockDim.x >> 5);
-    if (lane == 0) { for (int s = 0; s < p.stages; ++s) mbar_init(ws.bars + s, 1); mbar_fence_init(); }
-    for (int i = threadIdx.x; i < 2 * FK_CHUNK_TILES * FK_STREAM_MAXWARPS * 16; i += blockDim.x) sm.fold[i] = 0.0f;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int ls = p.lsplit, part = wid & ((1 << ls) - 1), slot = wid >> ls, tpb = nw >> ls, nsb = p.W.nsb;
+    const int sb0 = (part * nsb) >> ls, sb1 = ((part + 1) * nsb) >> ls;
+    ws.uvec = unit_vec(p.W.bits); ws.cnt = sb1 - sb0; ws.ntiles = p.W.ntiles; ws.tstep = (int)gridDim.x * tpb;
+    ws.p_tile = ws.cnt > 0 ? (int)blockIdx.x * tpb + slot : ws.ntiles; ws.p_left = ws.cnt;
+    if (ws.p_tile > ws.ntiles) ws.p_tile = ws.ntiles;
+    ws.src = p.W.units + ((size_t)ws.p_tile * nsb + sb0) * ws.uvec;
+    ws.jump = ((size_t)ws.tstep * nsb - (size_t)ws.cnt) * ws.uvec;
+    ws.bar = smem_u32(sm.bars + wid * FK_STAGES); ws.ring = smem_u32(sm.ring + (size_t)wid * FK_STAGES * FK_UNIT_VEC);
+    ws.fetched = ws.consumed = 0; ws.announced = false;
+    if (lane == 0) { for (int s = 0; s < FK_STAGES; ++s) mbar_init(sm.bars + wid * FK_STAGES + s, 1); mbar_fence_init(); }
     __syncwarp();
-    for (int s = 0; s < p.stages && ws.valid(); ++s) ws.issue(s);
+#pragma unroll
+    for (int s = 0; s < FK_STAGES; ++s) if (ws.valid()) ws.issue();
 }
 
-// Walk the block's chunks of the weight W; `epi(tile, g, v_lo, v_hi)` receives the finished sums of tile rows g and g+8 on
-// lanes with (lane & 3) == 0 of the warp that folds the tile.  `pr` is the warp's producer (valid / issue / drained,
-// bars, ring, consumed): it must hand out W's units in Cursor order, and may run on into whatever is streamed next.
-// Returns false if a barrier wait expired.  Every warp of the block must call this (it synchronises the block once per
-// chunk), after a block-wide synchronisation that follows the clearing of the fold buffer.
-template <int BITS, class Prod, class Epi>
-__device__ __forceinline__ bool stream_consume(Prod &pr, const TiledW &W, const StreamSmem &sm, Epi &epi) {
+// Walk the block's rounds of the weight; `epi(tile, g, v_lo, v_hi)` receives the finished sums of tile rows g and g + 8 on
+// lanes with (lane & 3) == 0 of the warp that owns (or folds) the tile.  Returns false if a barrier wait expired.
+// Every warp of the block must call this: the warps sharing a tile meet at a named barrier once per round.
+template <int BITS, class Epi>
+__device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm, Epi &epi) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5, g = lane >> 2, t = lane & 3;
-    Cursor cons; cons.init(W.ntiles, W.nsb, blockIdx.x, gridDim.x, wid, nw);
+    const int ls = p.lsplit, S = 1 << ls, part = wid & (S - 1), slot = wid >> ls, tpb = nw >> ls, nsb = p.W.nsb;
+    const int sb0 = (part * nsb) >> ls, ntiles = p.W.ntiles;
+    const uint32_t lane_off = (uint32_t)lane * 16u;
     bool ok = true;
-    if (!pr.valid()) pr.drained();
-    const int nchunks = cons.nchunks();
-    if (t == 0 && cons.ntl > 0) {
-        // what the epilogue of this lane's first tile needs from global memory (residual, bias) or from slow math (RoPE
-        // angle) is fetched now, under the wait for the first unit, instead of after the last one
-        const int ct0 = cons.chunk_tiles(0);
-        const int first = ct0 == nw ? (cons.valid() ? cons.tile_local() : -1) : (wid < ct0 ? wid : -1);
-        if (first >= 0) epi.prefetch((int)blockIdx.x + first * (int)gridDim.x, g);
-    }
-    for (int c = 0; c < nchunks; ++c) {
-        float *fold = sm.fold + (c & 1) * FK_CHUNK_TILES * FK_STREAM_MAXWARPS * 16;
-        const int ct = cons.chunk_tiles(c), cs = cons.chunk_start(c);
-        const bool whole = ct == nw;                // every warp owns one whole tile of this chunk: no fold, no barrier
-        while (ok && cons.valid() && cons.chunk == c) {
-            const int tl = cons.tile_local();
-            float acc_lo = 0.0f, acc_hi = 0.0f;
-            for (int n = cons.run(); n > 0 && ok; --n) {    // the units of tile tl in this warp's run
-                const int s = pr.consumed & (FK_STAGES - 1);
-                if (!mbar_wait(pr.bars + s, (uint32_t)(pr.consumed >> 1) & 1u)) { ok = false; break; }
-                unit_compute<BITS>(pr.ring + (size_t)s * FK_UNIT_VEC, sm, cons.sb(), lane, acc_lo, acc_hi);
+    if (!ws.valid()) ws.drained();
+    // what the epilogue of this lane's first tile needs from global memory (residual, bias) or from slow math (RoPE
+    // angle) is fetched now, under the wait for the first unit, instead of after the last one
+    if (t == 0 && part == 0 && (int)blockIdx.x * tpb + slot < ntiles) epi.prefetch((int)blockIdx.x * tpb + slot, g);
+    int round = 0;
+    for (int tb = (int)blockIdx.x * tpb; tb < ntiles; tb += ws.tstep, ++round) {
+        const int tile = tb + slot;
+        float acc_lo = 0.0f, acc_hi = 0.0f;
+        if (tile < ntiles && ok) {
+            int sb = sb0;
+            for (int n = ws.cnt; n > 0; --n, ++sb) {
+                const uint32_t s = (uint32_t)ws.consumed & (FK_STAGES - 1);
+                if (!mbar_wait_a(ws.bar + s * 8u, ((uint32_t)ws.consumed / FK_STAGES) & 1u)) { ok = false; break; }
+                unit_compute<BITS>(ws.ring + s * (uint32_t)FK_UNIT_BYTES + lane_off, sm, sb, lane, acc_lo, acc_hi);
                 __syncwarp();
-                if (pr.valid()) pr.issue(s);              // refill the stage just drained
-                if (!pr.valid()) pr.drained();
-                ++pr.consumed;
-                cons.advance();
+                ++ws.consumed;
+                if (ws.valid()) { ws.issue(); if (!ws.valid()) ws.drained(); }      // refill the stage just drained
             }
             acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 1); acc_lo += __shfl_xor_sync(0xffffffffu, acc_lo, 2);
             acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 1); acc_hi += __shfl_xor_sync(0xffffffffu, acc_hi, 2);
-            if (t == 0) {
-                if (whole) epi((int)blockIdx.x + tl * (int)gridDim.x, g, acc_lo, acc_hi);
-                else { float *f = fold + ((tl - cs) * FK_STREAM_MAXWARPS + wid) * 16; f[g] = acc_lo; f[8 + g] = acc_hi; }
-            }
         }
-        if (whole) continue;
-        __syncthreads();
-        for (int q = wid; q < ct; q += nw) {                  // fold tile q of the chunk in warp order, then its epilogue
-            if (t == 0) {
-                float *f = fold + q * FK_STREAM_MAXWARPS * 16;
-                float lo = 0.0f, hi = 0.0f;
-                for (int w = 0; w < nw; ++w) { lo += f[w * 16 + g]; hi += f[w * 16 + 8 + g]; f[w * 16 + g] = 0.0f; f[w * 16 + 8 + g] = 0.0f; }
-                epi((int)blockIdx.x + (cs + q) * (int)gridDim.x, g, lo, hi);
-            }
+        if (S == 1) { if (t == 0 && tile < ntiles) epi(tile, g, acc_lo, acc_hi); continue; }
+        // the parts of a tile through shared memory (two buffers: a warp may be one round ahead of the folding warp)
+        float *fold = sm.fold + ((round & 1) * FK_STREAM_MAXWARPS + slot * S) * 16;
+        if (t == 0) { fold[part * 16 + g] = acc_lo; fold[part * 16 + 8 + g] = acc_hi; }
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(S * 32) : "memory");
+        if (part == 0 && t == 0 && tile < ntiles) {
+            float lo = 0.0f, hi = 0.0f;
+            for (int q = 0; q < S; ++q) { lo += fold[q * 16 + g]; hi += fold[q * 16 + 8 + g]; }
+            epi(tile, g, lo, hi);
         }
-        // the buffer of chunk c is cleared by its folding warps before chunk c+2 writes it: chunk c+1's barrier orders them
     }
     return ok;
-}
-template <int BITS, class Epi>
-__device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, const StreamSmem &sm, Epi &epi) {
-    return stream_consume<BITS>(ws, p.W, sm, epi);
 }
 
 // ------------------------------------------------------------------ repack / probe kernels
