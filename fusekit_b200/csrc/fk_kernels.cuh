@@ -650,7 +650,33 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(K + (size_t)k_begin * HD), "r"(bytes) : "memory");
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(V + (size_t)k_begin * HD), "r"(bytes) : "memory");
     }
+    // K rows of both 8-key halves are requested together up to head_dim 128 (one round trip), one half at a time above
+    constexpr bool QREG = HD <= 128;
+    constexpr int NKR = QREG ? 2 : 1;
+    uint4 kr[NKR][KV4];
+    auto load_v_tile = [&](int kb) {             // V rows of a 16-key block into this warp's tile (rows past the end are zero)
+#pragma unroll
+        for (int i = 0; i < FK_SDPA_MK * (HD / 8) / 32; ++i) {
+            const int idx = lane + 32 * i, row = idx / (HD / 8), c = idx - row * (HD / 8);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (kb + row < k_end) v = __ldcg(reinterpret_cast<const uint4 *>(V + (size_t)(kb + row) * HD) + c);
+            *reinterpret_cast<uint4 *>(vt + row * L::VSTRIDE + c * 16) = v;
+        }
+    };
+    auto load_k = [&](int kb, int nb, int slot) {
+        const int key = min(kb + 8 * nb + g, k_end - 1);                  // clamped: masked below
+        const uint4 *kp = reinterpret_cast<const uint4 *>(K + (size_t)key * HD + t * (HD / 4));
+#pragma unroll
+        for (int c = 0; c < KV4; ++c) kr[slot][c] = __ldcg(kp + c);
+    };
+    // The warp's first key block is fetched before the dependency wait: every cache row but the one of the token being
+    // decoded was written by earlier tokens.  The block that holds that newest row is fetched again after the wait.
+    const int kb0 = k_begin + wid * FK_SDPA_MK;
+    const int newest = (int)(pos % (uint32_t)a.capacity);
+    const bool pre = QREG && kb0 < k_end;
+    if (pre) { load_v_tile(kb0); load_k(kb0, 0, 0); load_k(kb0, 1, NKR - 1); }
     pdl_wait();
+    if (pre && newest >= kb0 && newest < kb0 + FK_SDPA_MK) { load_v_tile(kb0); load_k(kb0, 0, 0); load_k(kb0, 1, NKR - 1); }
     for (int i = tid; i < G * HD / 2; i += NT) {             // q as bf16 rows
         const int gg = (2 * i) / HD, d = 2 * i - gg * HD;
         *reinterpret_cast<uint32_t *>(qs + gg * L::QSTRIDE + d * 2) = __ldcg(reinterpret_cast<const uint32_t *>(a.q + kvh * G * HD) + i);
@@ -658,7 +684,6 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
     __syncthreads();
     sd_stamp(a.tl, 1);
     // A fragments of q: row g (rows >= G and 8..15 are zero); in registers up to head_dim 128, re-read from shared memory above
-    constexpr bool QREG = HD <= 128;
     uint32_t aq[QREG ? KS : 1][2];
     const uint32_t *qrow = reinterpret_cast<const uint32_t *>(qs + g * L::QSTRIDE + t * (HD / 2));      // the lane's HD/4 dims are contiguous
     if (QREG) {
@@ -668,29 +693,15 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
     float m = -INFINITY, l = 0.0f, oacc[KS][4];
 #pragma unroll
     for (int mb = 0; mb < KS; ++mb) { oacc[mb][0] = oacc[mb][1] = oacc[mb][2] = oacc[mb][3] = 0.0f; }
-    for (int kb = k_begin + wid * FK_SDPA_MK; kb < k_end; kb += FK_SDPA_CW * FK_SDPA_MK) {
-        // V rows of the block into this warp's tile (rows past the end are zero)
-#pragma unroll
-        for (int i = 0; i < FK_SDPA_MK * (HD / 8) / 32; ++i) {
-            const int idx = lane + 32 * i, row = idx / (HD / 8), c = idx - row * (HD / 8);
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (kb + row < k_end) v = __ldcg(reinterpret_cast<const uint4 *>(V + (size_t)(kb + row) * HD) + c);
-            *reinterpret_cast<uint4 *>(vt + row * L::VSTRIDE + c * 16) = v;
+    for (int kb = kb0; kb < k_end; kb += FK_SDPA_CW * FK_SDPA_MK) {
+        if (!(pre && kb == kb0)) {
+            load_v_tile(kb);
+            if (QREG) { load_k(kb, 0, 0); load_k(kb, 1, NKR - 1); }
         }
-        // K rows of both 8-key halves are requested together up to head_dim 128 (one round trip), one half at a time above
-        constexpr int NKR = QREG ? 2 : 1;
-        uint4 kr[NKR][KV4];
-        auto load_k = [&](int nb, int slot) {
-            const int key = min(kb + 8 * nb + g, k_end - 1);                  // clamped: masked below
-            const uint4 *kp = reinterpret_cast<const uint4 *>(K + (size_t)key * HD + t * (HD / 4));
-#pragma unroll
-            for (int c = 0; c < KV4; ++c) kr[slot][c] = __ldcg(kp + c);
-        };
-        if (QREG) { load_k(0, 0); load_k(1, NKR - 1); }
         float sacc[2][4];
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) {
-            if (!QREG) load_k(nb, 0);
+            if (!QREG) load_k(kb, nb, 0);
             sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.0f;
 #pragma unroll
             for (int s = 0; s < KS; ++s) {

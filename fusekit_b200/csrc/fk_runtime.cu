@@ -79,7 +79,7 @@ struct Ctx {
     std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
     bool pending = false; bool pdl = true; int sm_count = 148;
     float *qmm_scratch = nullptr; unsigned int *qmm_counters = nullptr;   // K-split partial sums and tickets of the several-row projection
-    bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; int force_split = -1; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_cl = 0;
+    bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; int force_split = -1; int wide_upto = 3; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_cl = 0;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
@@ -134,6 +134,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     if (e && !strcmp(e, "fma")) c->sdpa_mma = false;
     e = getenv("FK_SDPA_CL"); if (e && (atoi(e) == 1 || atoi(e) == 2 || atoi(e) == 4 || atoi(e) == 8)) c->sdpa_cl = atoi(e);      // CTAs per kv head of the tensor-core attention
     e = getenv("FK_WARPS"); if (e) c->force_warps = atoi(e);
+    e = getenv("FK_WIDE_UPTO"); if (e) c->wide_upto = atoi(e);      // 16-warp blocks for weights of up to this many tiles per warp of the machine
     e = getenv("FK_SPLIT"); if (e) c->force_split = atoi(e);        // log2 of the warps sharing a row tile (tuning)
 #define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>)); CU(big_smem(K<16, 8>)); CU(big_smem(K<16, 16>))
 #define BIG4P(K) CU(big_smem(K<4, 8, true>)); CU(big_smem(K<4, 16, true>)); CU(big_smem(K<8, 8, true>)); CU(big_smem(K<8, 16, true>)); CU(big_smem(K<16, 8, true>)); CU(big_smem(K<16, 16, true>))
@@ -428,7 +429,10 @@ static Shape plan_shape(Ctx *c, const Weight *w) {
     s.warps = 8;
     s.smem = stream_smem_bytes(w->nsb, c->stages, 8, w->bits);
     int per_sm = 2;
-    if (s.smem > 113 * 1024 || c->force_warps == 16) {
+    // 16-warp blocks (one per SM) stage the activations once per SM instead of twice; weights with many rounds of tiles per
+    // block (the lm_head) run faster with two 8-warp blocks per SM
+    const bool few_rounds = (long long)w->ntiles <= (long long)c->wide_upto * c->sm_count * 16;
+    if (s.smem > 113 * 1024 || c->force_warps == 16 || (c->force_warps == 0 && few_rounds)) {
         per_sm = 1;
         const size_t wide = stream_smem_bytes(w->nsb, c->stages, 16, w->bits);
         if (wide <= 226 * 1024) { s.warps = 16; s.smem = wide; }          // else: 8 warps, one block per SM (very long K)

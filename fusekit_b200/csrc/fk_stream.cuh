@@ -234,7 +234,6 @@ __device__ __forceinline__ void stamp_raw(unsigned long long *tl, int slot) {
 // every unrolled copy is code the kernel carries, and a kernel's launch-to-launch cost grows with its size.
 template <int BITS, int MAXB>
 __device__ __forceinline__ void stage_plain(const StreamSmem &sm, const uint16_t *x, int k, int nsb) {
-    stage_pad<BITS>(sm, k, nsb);
     const int nblk = k >> 3;
     for (int b0 = 0; b0 < nblk; b0 += MAXB * blockDim.x) {
         uint4 v[MAXB];
@@ -256,18 +255,28 @@ __device__ __forceinline__ void stage_plain(const StreamSmem &sm, const uint16_t
 // RMSNorm (two roundings to T, src/codegen/kernels/mod.rs:4464-4472; rmsnorm_qkv.rs:325), optionally after advancing the
 // residual stream with a pending post-norm, x' = T(x + rmsnorm(pending) * w_p) (Gemma-shaped layers); block 0
 // publishes x' to h_out.  One round of global loads: x, w (and the pending pair) stay in registers.
-template <int BITS, bool PEND = true>
-__device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16_t *x, const uint16_t *w, int h, int nsb, float eps,
-                                              const uint16_t *pending, const uint16_t *pending_w, uint16_t *h_out,
-                                              unsigned long long *tl = nullptr, const float *pend_sum = nullptr) {
-    stage_pad<BITS>(sm, h, nsb);
+// The norm weights are constants: a kernel fetches its thread's share before griddepcontrol.wait (a first touch per token
+// comes from HBM), so only the activations are loaded on the critical path after it.
+struct NormW { uint4 v[FK_STAGE_MAXB]; };
+__device__ __forceinline__ void norm_w_load(NormW &nw, const uint16_t *w, int h) {
     const int nblk = h >> 3;
-    uint4 xv[FK_STAGE_MAXB], wv[FK_STAGE_MAXB];
 #pragma unroll
     for (int i = 0; i < FK_STAGE_MAXB; ++i) {
         const int blk = i * blockDim.x + threadIdx.x;
-        xv[i] = wv[i] = make_uint4(0, 0, 0, 0);
-        if (blk < nblk) { xv[i] = __ldcg(reinterpret_cast<const uint4 *>(x + (size_t)blk * 8)); wv[i] = *reinterpret_cast<const uint4 *>(w + (size_t)blk * 8); }
+        nw.v[i] = blk < nblk ? __ldg(reinterpret_cast<const uint4 *>(w + (size_t)blk * 8)) : make_uint4(0, 0, 0, 0);
+    }
+}
+template <int BITS, bool PEND = true>
+__device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16_t *x, const NormW &nwv, int h, int nsb, float eps,
+                                              const uint16_t *pending, const uint16_t *pending_w, uint16_t *h_out,
+                                              unsigned long long *tl = nullptr, const float *pend_sum = nullptr) {
+    const int nblk = h >> 3;
+    uint4 xv[FK_STAGE_MAXB];
+    const uint4 (&wv)[FK_STAGE_MAXB] = nwv.v;
+#pragma unroll
+    for (int i = 0; i < FK_STAGE_MAXB; ++i) {
+        const int blk = i * blockDim.x + threadIdx.x;
+        xv[i] = blk < nblk ? __ldcg(reinterpret_cast<const uint4 *>(x + (size_t)blk * 8)) : make_uint4(0, 0, 0, 0);
     }
     if (PEND && pend_sum) {     // tensor parallel: x' = T(all-reduced projection + residual x); block 0 publishes it
 #pragma unroll
@@ -693,6 +702,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
+    stage_pad<BITS>(sm, a.k, a.P.W.nsb);
     pdl_wait();
     stamp(a.P, 1);
     stage_plain<BITS, (WARPS == 16 ? 5 : 2)>(sm, a.x, a.k, a.P.W.nsb);
@@ -763,9 +773,11 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkStat
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
+    stage_pad<BITS>(sm, a.h, a.P.W.nsb);
+    NormW nwv; norm_w_load(nwv, a.norm_w, a.h);
     pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS, PEND>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
+    stage_rmsnorm<BITS, PEND>(sm, a.x, nwv, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
     EpiQkv epi(a, st->offset);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x200u);
@@ -807,9 +819,11 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
+    stage_pad<BITS>(sm, a.h, a.P.W.nsb);
+    NormW nwv; norm_w_load(nwv, a.norm_w, a.h);
     pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS, PEND>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
+    stage_rmsnorm<BITS, PEND>(sm, a.x, nwv, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
     EpiGateUp epi(a);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x400u);
@@ -855,9 +869,11 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, 
     __shared__ unsigned long long wbest[WARPS]; __shared__ int is_last;
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
+    stage_pad<BITS>(sm, a.h, a.P.W.nsb);
+    NormW nwv; norm_w_load(nwv, a.norm_w, a.h);
     pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS, PEND>(sm, a.x, a.norm_w, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
+    stage_rmsnorm<BITS, PEND>(sm, a.x, nwv, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
     stamp(a.P, 2);
     EpiHead epi(a);
     const bool ok = stream_run<BITS>(ws, a.P, sm, epi);
