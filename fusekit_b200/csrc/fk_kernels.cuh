@@ -174,10 +174,12 @@ __device__ __forceinline__ void rope_pair(float lo, float hi, int d, int half, u
 }
 
 // ================================================================ kernels
-struct EmbedArgs { const uint16_t *table; uint16_t *x; int h, rows; float scale; int vocab; };
-// x[row,:] = T(embed[token[row],:] * scale) (src/codegen/kernels/embed_lookup_decode.rs:95-98).  A token id outside the
-// table (vocab > 0) reads row 0 instead and raises error bit 0x20000: the host refuses such seeds, this guards the ids
-// that arrive through the device-side feedback.
+struct EmbedArgs { const uint16_t *table; uint16_t *x; int h, rows; float scale; int vocab; const uint16_t *qs, *qb; int bits; };
+// x[row,:] = T(embed[token[row],:] * scale) (src/codegen/kernels/embed_lookup_decode.rs:95-98); with a quantised table
+// (bits 4 / 8: `table` holds the packed u32 words, qs / qb the group scales and biases) the row is dequantised on the fly,
+// x = T((float(q) * s + b) * scale), one rounding (embed_lookup_decode.rs:79-93).  A token id outside the table (vocab > 0)
+// reads row 0 instead and raises error bit 0x20000: the host refuses such seeds, this guards the ids that arrive through
+// the device-side feedback.
 __global__ void k_embed_lookup(FkState *st, EmbedArgs a) {
     pdl_launch_dependents(); pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -185,6 +187,14 @@ __global__ void k_embed_lookup(FkState *st, EmbedArgs a) {
     const int row = i / a.h, d = i - row * a.h;
     uint32_t tok = st->token[row];
     if (a.vocab > 0 && tok >= (uint32_t)a.vocab) { if (d == 0) atomicOr(&st->error, 0x20000u); tok = 0; }
+    if (a.bits == 4 || a.bits == 8) {
+        const int lanes = 32 / a.bits, nwords = a.h / lanes, ngroups = a.h >> 6;
+        const uint32_t word = reinterpret_cast<const uint32_t *>(a.table)[(size_t)tok * nwords + d / lanes];
+        const uint32_t q = (word >> ((d % lanes) * a.bits)) & ((1u << a.bits) - 1u);
+        const float sc = bf2f(a.qs[(size_t)tok * ngroups + (d >> 6)]), bi = bf2f(a.qb[(size_t)tok * ngroups + (d >> 6)]);
+        a.x[i] = f2bf(__fmul_rn(__fadd_rn(__fmul_rn((float)q, sc), bi), a.scale));
+        return;
+    }
     a.x[i] = f2bf(__fmul_rn(bf2f(a.table[(size_t)tok * a.h + d]), a.scale));
 }
 

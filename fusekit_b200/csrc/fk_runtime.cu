@@ -507,7 +507,8 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
     case FK_TASK_EMBED_LOOKUP_DECODE: {
         if (!b[0] || !b[1] || i[0] <= 0 || i[1] <= 0 || i[1] > FK_MAX_ROWS) return fail(FK_ERR_VALUE, "embed: bad arguments");
         if (i[2] < 0) return fail(FK_ERR_VALUE, "embed: negative vocabulary size");
-        EmbedArgs a{(const uint16_t *)b[0], (uint16_t *)b[1], i[0], i[1], f[0], i[2]};
+        if (i[3] != 0 && i[3] != 16 && ((i[3] != 4 && i[3] != 8) || !b[2] || !b[3] || (i[0] & 63))) return fail(FK_ERR_VALUE, "embed: a quantised table needs bits 4 or 8, scales, biases and H %% 64 == 0");
+        EmbedArgs a{(const uint16_t *)b[0], (uint16_t *)b[1], i[0], i[1], f[0], i[2], (const uint16_t *)b[2], (const uint16_t *)b[3], i[3] == 16 ? 0 : i[3]};
         if (i[2] > 0) c->vocab = (uint32_t)i[2];        // seeds are checked against it in fk_state_set / fk_decode_chunk
         e = launch(c, k_embed_lookup, dim3((i[0] * i[1] + 255) / 256), dim3(256), 0, c->state, a);
         break;

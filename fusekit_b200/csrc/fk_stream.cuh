@@ -15,17 +15,20 @@
 // by 4 when the digits are recombined); 8-bit weights are used as stored.  mma.sync.m16n8k32 (u8 x u8/s8, s32
 // accumulate) forms sum(q * digit) exactly; the digit sums are recombined in s32 (4 bit) or fp32 (8 bit).  The tensor pipe is the dot-product
 // unit because unpack + convert + FMA on the CUDA cores costs >2 issue slots per weight, more than an SM has at
-// HBM speed.  The eight groups of a unit go to the eight accumulator columns (the activations of group j sit in
-// B column j, zeros elsewhere), so after a unit every lane owns four (row, group) sums and applies
-// s * c / scale_g + b * sum(x_g) to them.
+// HBM speed.  The eight groups of a unit go to the eight accumulator columns: a lane holds the digits of the group whose
+// column it feeds (group lane / 4) and zeros for the other seven MMAs, so after a unit every lane owns four (row, group)
+// sums and applies s * c / scale_g + b * sum(x_g) to them.  (Two 8-bit digits -- 16-bit activations with the rounding
+// loss of a group added back times the mean weight code -- ran 6 % faster, 829 against 782 tok/s on the 7B shape, and stayed
+// inside the per-stage tolerance, but the 64-token greedy check of that shape then showed a flip three bf16 ulps wide
+// where this form shows none wider than two: not kept.)
 //
-// Scheduling: blocks of 8 warps, two per SM, each warp with its own ring and mbarriers.  With at least one
-// row tile per warp in the grid a warp owns whole tiles (all of K); otherwise the warps of a block split K
-// of the block's tile and fold their sums through shared memory in warp order (deterministic, no global
-// round trip).  Rings are filled before griddepcontrol.wait: weights do not depend on the previous kernel,
-// so under programmatic dependent launch a block of the next kernel that lands on an SM slot freed by this
-// one streams its weights while this kernel finishes.  (An L2 prefetch of the next kernel's first units was
-// measured and dropped: no gain.)
+// Scheduling: blocks of 16 warps, one per SM (8 warps, two per SM, for weights with many rounds of tiles), each warp with
+// its own ring and mbarriers.  With at least one row tile per warp in the grid a warp owns whole tiles (all of K); otherwise
+// 2, 4, 8 or 16 warps of a block split K of a tile and fold their sums through shared memory in warp order (deterministic,
+// no global round trip).  Rings are filled before griddepcontrol.wait: weights do not depend on the previous kernel, so
+// under programmatic dependent launch a block of the next kernel that lands on an SM slot freed by this one streams its
+// weights while this kernel finishes.  (L2 prefetches -- of the next kernel's first units, of the rest of a warp's run, of
+// the unit a few fetches ahead -- were each measured and dropped: all slower.)
 #pragma once
 #include "fk_common.cuh"
 
@@ -37,7 +40,7 @@ __host__ __device__ inline int unit_vec(int bits) { return bits == 16 ? 256 : FK
 __host__ __device__ inline int unit_k(int bits) { return bits == 4 ? 512 : bits == 8 ? 256 : 128; }      // activations covered by a unit
 #define FK_STREAM_MAXWARPS 16         // blocks run 8 warps (two blocks per SM) or 16 (one per SM, large activations)
 #define FK_STAGES 2                     // ring depth per warp
-#define FK_ZERO_BYTES 2048              // zero region: 8 groups x 192 bytes of digits and some slack
+#define FK_ZERO_BYTES 256               // zero vectors (the bf16 engine's B operand outside column 0)
 #define FK_WAIT_LIMIT (1u << 24)        // bounded mbarrier wait; on expiry the kernel flags an error and leaves
 #ifndef FK_J_UNROLL
 #define FK_J_UNROLL 8                   // unroll factor of the group loop inside a unit (code size against scheduling freedom)
@@ -120,7 +123,7 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 // ------------------------------------------------------------------ shared-memory plan of a streamed kernel
 struct StreamSmem {
     uint64_t *bars;     // [warps * stages]
-    uint4 *zero;        // FK_ZERO_BYTES of zeros: a super-block of digits for the lanes whose group is not the one being multiplied
+    uint4 *zero;        // FK_ZERO_BYTES of zeros
     float2 *xsi;        // [groups] (sum of the group's activations, 1 / power-of-two scale of its integer digits)
     float *red;         // [48]
     float *fold;        // [2][16 warps][16] per-warp row sums of a round
@@ -191,28 +194,31 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
     e = e < -100 ? -100 : (e > 100 ? 100 : e);
     const float scale = __uint_as_float((uint32_t)(127 + 20 - e) << 23), inv = __uint_as_float((uint32_t)(127 - 20 + e) << 23);
     if (!valid) return;
-    int xi[8];
+    // three 7-bit digits of the 21-bit integers (d0, d1 unsigned, d2 signed): byte 0 of xi, xi >> 7, xi >> 14, gathered four at
+    // a time with byte permutes and masked as a word
+    uint32_t x0[8], x7[8], x14[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) xi[i] = __float2int_rn(f[i] * scale);
+    for (int i = 0; i < 8; ++i) { const int v = __float2int_rn(f[i] * scale); x0[i] = (uint32_t)v; x7[i] = (uint32_t)(v >> 7); x14[i] = (uint32_t)(v >> 14); }
+    auto bytes4 = [](uint32_t a, uint32_t b, uint32_t c, uint32_t d) {      // byte 0 of a, b, c, d
+        return __byte_perm(__byte_perm(a, b, 0x0040u), __byte_perm(c, d, 0x0040u), 0x5410u);
+    };
     if (BITS == 4) {
         const int grp = blk >> 3, bb = blk & 7;
         // [digit][lane t = bb & 3]{word A even, word B even, word A odd, word B odd}: the even nibbles of both words feed one MMA,
         // the odd nibbles (used unshifted, as 16 q) the other
         uint32_t *dst = reinterpret_cast<uint32_t *>(sm.xs) + (size_t)grp * 48 + (bb & 3) * 4 + (bb >> 2);
-        dst[0] = pack4(xi[0] & 127, xi[2] & 127, xi[4] & 127, xi[6] & 127); dst[2] = pack4(xi[1] & 127, xi[3] & 127, xi[5] & 127, xi[7] & 127);
-        dst[16] = pack4((xi[0] >> 7) & 127, (xi[2] >> 7) & 127, (xi[4] >> 7) & 127, (xi[6] >> 7) & 127);
-        dst[18] = pack4((xi[1] >> 7) & 127, (xi[3] >> 7) & 127, (xi[5] >> 7) & 127, (xi[7] >> 7) & 127);
-        dst[32] = pack4(xi[0] >> 14, xi[2] >> 14, xi[4] >> 14, xi[6] >> 14); dst[34] = pack4(xi[1] >> 14, xi[3] >> 14, xi[5] >> 14, xi[7] >> 14);
+        dst[0] = bytes4(x0[0], x0[2], x0[4], x0[6]) & 0x7f7f7f7fu; dst[2] = bytes4(x0[1], x0[3], x0[5], x0[7]) & 0x7f7f7f7fu;
+        dst[16] = bytes4(x7[0], x7[2], x7[4], x7[6]) & 0x7f7f7f7fu; dst[18] = bytes4(x7[1], x7[3], x7[5], x7[7]) & 0x7f7f7f7fu;
+        dst[32] = bytes4(x14[0], x14[2], x14[4], x14[6]); dst[34] = bytes4(x14[1], x14[3], x14[5], x14[7]);
         if (bb == 0) sm.xsi[grp] = make_float2(s8, inv);
     } else {
         const int k0 = blk * 8, grp = k0 >> 5, o = k0 & 31, half = o >> 4, t = (o >> 2) & 3;
         uint32_t *dst = reinterpret_cast<uint32_t *>(sm.xs) + (size_t)grp * 24 + t * 2 + half;   // [digit][lane][A|B] as words
 #pragma unroll
         for (int q = 0; q < 2; ++q) {                    // the two 4-blocks of this thread: lanes t and t+1
-            const int *x4 = xi + 4 * q;
-            dst[2 * q] = pack4(x4[0] & 127, x4[1] & 127, x4[2] & 127, x4[3] & 127);
-            dst[8 + 2 * q] = pack4((x4[0] >> 7) & 127, (x4[1] >> 7) & 127, (x4[2] >> 7) & 127, (x4[3] >> 7) & 127);
-            dst[16 + 2 * q] = pack4(x4[0] >> 14, x4[1] >> 14, x4[2] >> 14, x4[3] >> 14);
+            dst[2 * q] = bytes4(x0[4 * q], x0[4 * q + 1], x0[4 * q + 2], x0[4 * q + 3]) & 0x7f7f7f7fu;
+            dst[8 + 2 * q] = bytes4(x7[4 * q], x7[4 * q + 1], x7[4 * q + 2], x7[4 * q + 3]) & 0x7f7f7f7fu;
+            dst[16 + 2 * q] = bytes4(x14[4 * q], x14[4 * q + 1], x14[4 * q + 2], x14[4 * q + 3]);
         }
         if ((blk & 3) == 0) sm.xsi[blk >> 2] = make_float2(s8, inv);
     }
@@ -372,17 +378,17 @@ __device__ __forceinline__ void unit_compute_bf16(uint32_t ub, const StreamSmem 
     }
     acc_lo += c[0][0] + c[1][0]; acc_hi += c[0][2] + c[1][2];
 }
-// one group of a 4- or 8-bit unit: rows g (w.x word A, w.y word B) and g + 8 (w.z, w.w) against the group's three digits
+// one group of a 4- or 8-bit unit: rows g (w.x word A, w.y word B) and g + 8 (w.z, w.w) against the group's three digits.
+// `x0`, `x1`, `x2`: the B-operand registers of the digits -- the lane's own digits when the group is the lane's
+// (lane / 4 == J), zeros otherwise, so column J of the accumulators collects group J.
 template <int BITS, int J>
-__device__ __forceinline__ void group_compute(uint32_t ub, uint32_t xsel, int (&cc)[3][4], int (&co)[3][4]) {
-    constexpr int GB = BITS == 4 ? 192 : 96, DB = BITS == 4 ? 64 : 32;
+__device__ __forceinline__ void group_compute(uint32_t ub, const uint4 &x0, const uint4 &x1, const uint4 &x2, int (&cc)[3][4], int (&co)[3][4]) {
     const uint4 w = lds128o<J * 512>(ub);
     if (BITS == 4) {
         // Even MMA: k-slots 4t.. = word A even nibbles, 4t+16.. = word B even nibbles; odd MMA the same with the odd nibbles
-        // left in the high half of each byte (16 q, exact in u8 and in s32)
+        // left in the high half of each byte (16 q, exact in u8 and in s32).  Digit vectors: {A even, B even, A odd, B odd}.
         const uint32_t ea = w.x & 0x0F0F0F0Fu, oa = w.x & 0xF0F0F0F0u, ea8 = w.z & 0x0F0F0F0Fu, oa8 = w.z & 0xF0F0F0F0u;
         const uint32_t eb = w.y & 0x0F0F0F0Fu, ob = w.y & 0xF0F0F0F0u, eb8 = w.w & 0x0F0F0F0Fu, ob8 = w.w & 0xF0F0F0F0u;
-        const uint4 x0 = lds128o<J * GB>(xsel), x1 = lds128o<J * GB + DB>(xsel), x2 = lds128o<J * GB + 2 * DB>(xsel);     // digits 0..2: {A even, B even, A odd, B odd}
         if (J == 0) {
             imma_uu0(cc[0], ea, ea8, eb, eb8, x0.x, x0.y); imma_uu0(cc[1], ea, ea8, eb, eb8, x1.x, x1.y); imma_us0(cc[2], ea, ea8, eb, eb8, x2.x, x2.y);
             imma_uu0(co[0], oa, oa8, ob, ob8, x0.z, x0.w); imma_uu0(co[1], oa, oa8, ob, ob8, x1.z, x1.w); imma_us0(co[2], oa, oa8, ob, ob8, x2.z, x2.w);
@@ -390,27 +396,35 @@ __device__ __forceinline__ void group_compute(uint32_t ub, uint32_t xsel, int (&
             imma_uu(cc[0], ea, ea8, eb, eb8, x0.x, x0.y); imma_uu(cc[1], ea, ea8, eb, eb8, x1.x, x1.y); imma_us(cc[2], ea, ea8, eb, eb8, x2.x, x2.y);
             imma_uu(co[0], oa, oa8, ob, ob8, x0.z, x0.w); imma_uu(co[1], oa, oa8, ob, ob8, x1.z, x1.w); imma_us(co[2], oa, oa8, ob, ob8, x2.z, x2.w);
         }
-    } else {
-        const uint2 x0 = lds64o<J * GB>(xsel), x1 = lds64o<J * GB + DB>(xsel), x2 = lds64o<J * GB + 2 * DB>(xsel);     // digits 0..2: {word A, word B}
+    } else {            // digit vectors: {word A, word B} in .x, .y
         if (J == 0) { imma_uu0(cc[0], w.x, w.z, w.y, w.w, x0.x, x0.y); imma_uu0(cc[1], w.x, w.z, w.y, w.w, x1.x, x1.y); imma_us0(cc[2], w.x, w.z, w.y, w.w, x2.x, x2.y); }
         else { imma_uu(cc[0], w.x, w.z, w.y, w.w, x0.x, x0.y); imma_uu(cc[1], w.x, w.z, w.y, w.w, x1.x, x1.y); imma_us(cc[2], w.x, w.z, w.y, w.w, x2.x, x2.y); }
     }
 }
-// `ub`: shared address of this lane's first vector of the unit; `xb`: shared address of the lane's 16 (8) bytes of digit 0 of
-// the super-block's first group; `zb`: the same inside the zero region, which spans a whole super-block of digits, so the
-// choice between a group's digits and zeros is one select on the base address and every load keeps its immediate offset.
+template <int BITS> __device__ __forceinline__ uint4 sel4(bool p, const uint4 &v) {
+    if (BITS == 4) return make_uint4(p ? v.x : 0u, p ? v.y : 0u, p ? v.z : 0u, p ? v.w : 0u);
+    return make_uint4(p ? v.x : 0u, p ? v.y : 0u, 0u, 0u);
+}
+// `ub`: shared address of this lane's first vector of the unit.  The lane loads the digits of ITS group (group lane / 4 of
+// the super-block) once per unit; for the other seven groups its B registers are zero.  (Loading zeros from shared memory
+// for those, as an earlier form did, cost four wavefronts per load, 24 loads per unit: shared-memory bandwidth, not issue
+// slots, bounded the kernel.  Lanes of neighbouring groups sit 192 (96) bytes apart: no bank conflicts.)
 template <int BITS>
 __device__ __forceinline__ void unit_compute_q(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     const int g = lane >> 2, t = lane & 3;
     // [digit][fragment] MMA chains; at 4 bits the odd nibbles are used in place (bytes 16 q) and accumulate in chains of their own
     int cc[3][4], co[3][4];
-    constexpr uint32_t GB = BITS == 4 ? 192u : 96u, LB = BITS == 4 ? 16u : 8u;
-    const uint32_t zb = smem_u32(sm.zero) + (uint32_t)t * LB;
-    const uint32_t xb = smem_u32(sm.xs) + (uint32_t)(sb * 8) * GB + (uint32_t)t * LB;
-    group_compute<BITS, 0>(ub, g == 0 ? xb : zb, cc, co); group_compute<BITS, 1>(ub, g == 1 ? xb : zb, cc, co);
-    group_compute<BITS, 2>(ub, g == 2 ? xb : zb, cc, co); group_compute<BITS, 3>(ub, g == 3 ? xb : zb, cc, co);
-    group_compute<BITS, 4>(ub, g == 4 ? xb : zb, cc, co); group_compute<BITS, 5>(ub, g == 5 ? xb : zb, cc, co);
-    group_compute<BITS, 6>(ub, g == 6 ? xb : zb, cc, co); group_compute<BITS, 7>(ub, g == 7 ? xb : zb, cc, co);
+    constexpr uint32_t GB = BITS == 4 ? 192u : 96u, DB = GB / 3, LB = BITS == 4 ? 16u : 8u;
+    const uint32_t xg = smem_u32(sm.xs) + (uint32_t)(sb * 8 + g) * GB + (uint32_t)t * LB;
+    uint4 x0, x1, x2;
+    if (BITS == 4) { x0 = lds128(xg); x1 = lds128(xg + DB); x2 = lds128(xg + 2 * DB); }
+    else {
+        const uint2 a = lds64(xg), b = lds64(xg + DB), c2 = lds64(xg + 2 * DB);
+        x0 = make_uint4(a.x, a.y, 0u, 0u); x1 = make_uint4(b.x, b.y, 0u, 0u); x2 = make_uint4(c2.x, c2.y, 0u, 0u);
+    }
+#define FK_GROUP(J) group_compute<BITS, J>(ub, sel4<BITS>(g == J, x0), sel4<BITS>(g == J, x1), sel4<BITS>(g == J, x2), cc, co)
+    FK_GROUP(0); FK_GROUP(1); FK_GROUP(2); FK_GROUP(3); FK_GROUP(4); FK_GROUP(5); FK_GROUP(6); FK_GROUP(7);
+#undef FK_GROUP
     const uint4 sb4 = lds128o<4096>(ub);
     const float2 xi0 = sm.xsi[sb * 8 + 2 * t], xi1 = sm.xsi[sb * 8 + 2 * t + 1];      // (group sum, 1/scale)
     const float X0 = xi0.x, X1 = xi1.x, i0 = xi0.y, i1 = xi1.y;

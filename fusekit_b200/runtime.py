@@ -196,6 +196,7 @@ class DecodeEngine:
         self.V: dict[str, int] = {}      # name -> device address of a bf16 vector
         self.cache: list[tuple[int, int, int]] = []     # (k, v, capacity) per layer
         self.graph = 0
+        self.embed_bits = 16             # 4 / 8: the embedding table is quantised (load_from with an embed provider)
         self._alloc_buffers()
 
     # ------------------------------------------------------------------ buffers
@@ -257,10 +258,11 @@ class DecodeEngine:
             dst, stream_id(s.seed, tensor_name(layer, leaf)), idx0, n, mean, std))
         rt.sync()
 
-    def load_from(self, weight_provider, vector_provider):
+    def load_from(self, weight_provider, vector_provider, embed=None):
         """Upload host tensors in MLX-affine layout.  ``weight_provider(leaf, layer, src_row0, nrows,
         k_global, k0, k, bits) -> (packed_or_dense, scales, biases)``; ``vector_provider(leaf, layer,
-        idx0, n, mean, std) -> uint16 array``."""
+        idx0, n, mean, std) -> uint16 array``; ``embed``: None for a bf16 embedding table served by the vector
+        provider, or ``{"bits", "packed", "scales", "biases"}`` for a quantised one (fusekit_b200.checkpoint)."""
         s, rt = self.spec, self.rt
         for name, segs, k_global, k0, k, layer in self._linear_plan():
             wid = rt.weight_alloc(sum(n for _, _, n in segs), k, s.bits)
@@ -270,6 +272,11 @@ class DecodeEngine:
                 rt.weight_upload_rows(wid, row, p, sc, bi)
                 row += n
             self._finish_weight(name, wid)
+        if embed is not None:
+            self.embed_bits = int(embed["bits"])
+            self.V["embed_tokens"] = rt.to_device(np.ascontiguousarray(embed["packed"], np.uint32))
+            self.V["embed_tokens.scales"] = rt.to_device(np.ascontiguousarray(embed["scales"], np.uint16))
+            self.V["embed_tokens.biases"] = rt.to_device(np.ascontiguousarray(embed["biases"], np.uint16))
         self._load_vectors(lambda leaf, layer, idx0, n, mean, std, dst: rt.upload(dst, vector_provider(leaf, layer, idx0, n, mean, std)))
         rt.sync()
 
@@ -291,7 +298,7 @@ class DecodeEngine:
     def _load_vectors(self, fill):
         s, rt = self.spec, self.rt
         for name, leaf, layer, idx0, n, mean, std in self._vector_plan():
-            if leaf in ("q_bias", "k_bias", "v_bias"):
+            if leaf in ("q_bias", "k_bias", "v_bias") or name in self.V:
                 continue
             self.V[name] = rt.alloc(n * 2)
             fill(leaf, layer, idx0, n, mean, std, self.V[name])
@@ -335,13 +342,13 @@ class DecodeEngine:
     def task_graph(self) -> dict:
         """This engine's decode step as a v2 ``task_graph.json`` document (see task_graph.emit)."""
         return task_graph.emit(self.spec, self.capacity, self.rank, self.world,
-                               fused_weights=self.rt.tiled, want_logits=self.want_logits)
+                               fused_weights=self.rt.tiled, want_logits=self.want_logits, embed_bits=self.embed_bits)
 
     def _resolve(self, role: str) -> int:
         """Device address (or fk_weight id) behind one role string of the task graph."""
         p = role.split(".")
         if p[0] == "param":
-            return self.W["lm_head"] if p[1] == "lm_head" else self.V[p[1]]
+            return self.W["lm_head"] if p[1] == "lm_head" else self.V[".".join(p[1:])]
         if p[0] == "layer_param":
             l, rel = int(p[1]), ".".join(p[2:])
             w = {"self_attn.qkv_proj": "qkv", "self_attn.o_proj": "o", "mlp.gate_up_proj": "gateup", "mlp.gate_proj": "gate",

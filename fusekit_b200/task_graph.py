@@ -29,7 +29,7 @@ def _bf16_round(v: float) -> float:
 
 
 def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fused_weights: bool = True,
-         want_logits: bool = False) -> dict:
+         want_logits: bool = False, embed_bits: int = 16) -> dict:
     """Build the v2 task graph of one decode step for `spec` (one tensor-parallel rank of it).
 
     `fused_weights`: weights in the streaming layout (gate/up paired, residual add after an all-reduce fused into the next
@@ -49,7 +49,11 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
     lp = lambda l, rel: f"layer_param.{l}.{rel}"
     gateup = (lambda l: {2: lp(l, "mlp.gate_up_proj")}) if fused else (lambda l: {2: lp(l, "mlp.gate_proj"), 3: lp(l, "mlp.up_proj")})
     emb_scale = _bf16_round(math.sqrt(H)) if s.arch == "gemma3" else 1.0      # embed_lookup_decode.rs OUTPUT_SCALE
-    add(K_EMBED, -1, {0: "param.embed_tokens", 1: x(0)}, [H, 1, s.vocab], [emb_scale])
+    if embed_bits in (4, 8):      # quantised embedding rows, dequantised in the gather (embed_lookup_decode.rs:40-61 signature)
+        add(K_EMBED, -1, {0: "param.embed_tokens", 1: x(0), 2: "param.embed_tokens.scales", 3: "param.embed_tokens.biases"},
+            [H, 1, s.vocab, embed_bits], [emb_scale])
+    else:
+        add(K_EMBED, -1, {0: "param.embed_tokens", 1: x(0)}, [H, 1, s.vocab], [emb_scale])
     scale = 1.0 / math.sqrt(hd)
     for l in range(s.n_layers):
         cap, theta = s.layer_capacity(l, capacity), s.layer_theta(l)

@@ -63,7 +63,9 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *
  * EMBED_LOOKUP_DECODE  buf0 table T[V,H]  buf1 x_out T[rows,H]            i0 H  i1 rows  i2 V (rows of the table; 0 = unchecked)   f0 scale
  *                      with V given, fk_state_set / fk_decode_chunk refuse a seed token >= V and an id >= V arriving on the
- *                      device reads row 0 and sets error bit 0x20000
+ *                      device reads row 0 and sets error bit 0x20000.  i3 = 4 or 8: a quantised table -- buf0 packed u32
+ *                      [V, H*bits/32], buf2 scales T[V, H/64], buf3 biases T[V, H/64], x = T((q*s + b) * scale)
+ *                      (embed_lookup_decode.rs:79-93); i3 = 0 or 16: buf0 is the T[V,H] table
  * RMSNORM_QKV          buf0 x T[H]  buf1 norm_w  buf2 weight(qkv rows: q|k|v)  buf3 lin_bias|0
  *                      buf4 q_out  buf5 cache_k  buf6 cache_v  buf7 k_out|0  buf8 v_out|0
  *                      buf9 pending_y|0  buf10 pending_norm_w  buf11 h_out   (Gemma: x <- T(x + rmsnorm(pending_y)));

@@ -308,20 +308,27 @@ class Model:
         return out, float(secs)
 
 
-def compare_greedy(got_tokens, oracle_model, first_tok: int, pos0: int, tie_ulps: float = 2.0):
+def compare_greedy(got_tokens, oracle_model, first_tok: int, pos0: int, tie_ulps: float = 2.0, stats: dict | None = None):
     """Walk the oracle along the GPU's token stream.  Returns (mismatches, ties): a mismatch where the
     oracle's own margin between its winner and the GPU's token is at most `tie_ulps` bf16 ulps of the logit
     is a near-tie (random-init logits are almost flat; the reference itself documents token flips
-    from reordered fp32 sums); anything larger is a real mismatch."""
-    tok, mism, ties = first_tok, [], []
+    from reordered fp32 sums); anything larger is a real mismatch.  `stats`, when given, receives
+    ``ambiguous_steps``: the steps at which the oracle's own runner-up lies within `tie_ulps` ulps of its winner,
+    i.e. the only steps at which a near-tie can occur at all."""
+    tok, mism, ties, amb = first_tok, [], [], 0
     for i, g in enumerate(int(t) for t in got_tokens):
         want, _, lg = oracle_model.step(tok, pos0 + i, want_logits=True)
+        l = bf16_to_f32(np.asarray(lg, np.uint16))
+        ulp = 2.0 ** (np.floor(np.log2(max(abs(float(l[want])), 1e-30))) - 7)
+        if stats is not None:
+            top2 = np.partition(l, -2)[-2:]
+            amb += int(float(top2[1] - top2[0]) <= tie_ulps * ulp)
         if want != g:
-            l = bf16_to_f32(np.asarray(lg, np.uint16))
             margin = float(l[want] - l[g])
-            ulp = 2.0 ** (np.floor(np.log2(max(abs(float(l[want])), 1e-30))) - 7)
             (ties if margin <= tie_ulps * ulp else mism).append((i, want, g, margin, ulp))
         tok = g
+    if stats is not None:
+        stats["ambiguous_steps"] = amb
     return mism, ties
 
 

@@ -27,7 +27,11 @@ def record(**kw):
     print("parity:", kw)
 
 
-def run_config(spec, ctx, steps, what, stage_layers=None, forced_layers=None, max_ties=4, forced_rel_tol=5e-3):
+def run_config(spec, ctx, steps, what, stage_layers=None, forced_layers=None, max_ties=8, forced_rel_tol=5e-3):
+    """`max_ties`: near-tie flips allowed (each at most two bf16 ulps wide by the oracle's own margin; wider is a mismatch
+    and fails).  Their number moves with the summation order of the kernels -- 3 to 5 of 64 steps were seen on the 7B shape
+    across work splits, with 15 or 16 steps whose two best oracle logits lie within two ulps -- so the bound is a sanity
+    limit, half of the ambiguous steps, and the measured count is recorded."""
     cap = ctx + steps + 8
     O.set_num_threads(len(os.sched_getaffinity(0)))
     m = O.Model(oracle_config(spec, cap)); m.prefill_kv(ctx)
@@ -35,7 +39,8 @@ def run_config(spec, ctx, steps, what, stage_layers=None, forced_layers=None, ma
     try:
         eng.load_synthetic(); eng.prefill_kv_synthetic(ctx)
         got, _ = eng.decode_chunk(ctx, 3, steps)
-        mism, ties = compare_greedy(got, m, 3, ctx)
+        st = {}
+        mism, ties = compare_greedy(got, m, 3, ctx, stats=st)
         # hidden states of the token after the chunk: whole layers on the GPU's own layer inputs and caches
         pos, tok = ctx + steps, int(got[-1])
         eng.decode_chunk(pos, tok, 1)
@@ -46,7 +51,7 @@ def run_config(spec, ctx, steps, what, stage_layers=None, forced_layers=None, ma
         # whole layers: one-ulp flips of a stage's bf16 outputs pass through the next projections, so a whole layer is held
         # to a wider relative-RMS bound (the measured values are recorded)
         worst = check_layers_teacher_forced(eng, m, pos, what, rel_tol=forced_rel_tol, layers=forced_layers)
-        record(config=what, ctx=ctx, tokens=steps, mismatches=len(mism), near_ties=[(t[0], round(t[3], 5), round(t[4], 5)) for t in ties],
+        record(config=what, ctx=ctx, tokens=steps, mismatches=len(mism), ambiguous_steps=st["ambiguous_steps"], near_ties=[(t[0], round(t[3], 5), round(t[4], 5)) for t in ties],
                whole_layer_worst_max_abs=worst[0], whole_layer_worst_rel_rms=worst[1], stage_worst_rel_rms=stage)
         assert not mism, f"{what}: greedy tokens differ beyond a near-tie: {mism}"
         assert len(ties) <= max_ties, f"{what}: too many near-tie flips in {steps} steps: {ties}"
