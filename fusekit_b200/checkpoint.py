@@ -79,7 +79,7 @@ class SafetensorsFile:
 
 def write_safetensors(path: str, tensors: dict, metadata: dict | None = None):
     """Write ``{name: (array, dtype_tag)}`` as one safetensors file; ``dtype_tag`` names the stored type ("BF16" for uint16
-    bit patterns of bf16 values).  Used by the tests and by tools that export synthetic models."""
+    bit patterns of bf16 values).  Used by the tests and by tools that export models."""
     header, off, blobs = {}, 0, []
     for name, (arr, tag) in tensors.items():
         a = np.ascontiguousarray(arr)
@@ -284,53 +284,3 @@ def load_engine(path: str, capacity: int, device: int = 0, tp_rank: int = 0, tp_
     eng = DecodeEngine(ck.spec, capacity, device=device, tp_rank=tp_rank, tp_size=tp_size, **kw)
     eng.load_from(ck.weight_provider(), ck.vector_provider(), ck.embed_provider())
     return eng, ck
-
-
-def export_oracle_model(model, spec: ModelSpec, path: str, quantised_embedding: bool = False):
-    """Write the tensors of a CPU oracle model as an mlx-lm style checkpoint directory (config.json + model.safetensors):
-    the fixture generator of the ingestion tests, and a way to hand a synthetic model to other tools."""
-    os.makedirs(path, exist_ok=True)
-    H, hd = spec.hidden, spec.head_dim
-    t: dict = {}
-    pre = "model."
-
-    def put_linear(base, w):
-        if w.bits == 16:
-            t[base + ".weight"] = (w.dense, "BF16")
-        else:
-            t[base + ".weight"] = (w.packed, "U32"); t[base + ".scales"] = (w.scales, "BF16"); t[base + ".biases"] = (w.biases, "BF16")
-
-    def norm(v):
-        if spec.arch != "gemma3":
-            return v
-        f = (np.asarray(v, np.uint16).astype(np.uint32) << 16).view(np.float32) - np.float32(1.0)     # stored weight = effective - 1
-        return f32_to_bf16_bits(f)
-
-    t[pre + "embed_tokens.weight"] = (model.vec(-1, 0, spec.vocab * H).reshape(spec.vocab, H), "BF16")
-    t[pre + "norm.weight"] = (norm(model.vec(-1, 1, H)), "BF16")
-    put_linear("lm_head", model.linear(-1, 0))
-    names = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
-    for l in range(spec.n_layers):
-        for i, leaf in enumerate(names):
-            w = model.linear(l, i)
-            put_linear(f"{pre}layers.{l}.{_W[leaf]}", w)
-            if spec.qkv_bias and i < 3:
-                t[f"{pre}layers.{l}.{_W[leaf]}.bias"] = (w.lin_bias, "BF16")
-        t[f"{pre}layers.{l}.input_layernorm.weight"] = (norm(model.vec(l, 0, H)), "BF16")
-        if spec.arch == "qwen2":
-            t[f"{pre}layers.{l}.post_attention_layernorm.weight"] = (norm(model.vec(l, 1, H)), "BF16")
-        else:
-            for which, leaf, n in ((2, "post_attention_norm", H), (3, "pre_feedforward_norm", H), (4, "post_feedforward_norm", H),
-                                   (5, "q_norm", hd), (6, "k_norm", hd)):
-                t[f"{pre}layers.{l}.{_V[leaf]}"] = (norm(model.vec(l, which, n)), "BF16")
-    cfg = {"model_type": "qwen2" if spec.arch == "qwen2" else "gemma3_text", "hidden_size": H, "num_hidden_layers": spec.n_layers,
-           "num_attention_heads": spec.n_q, "num_key_value_heads": spec.n_kv, "head_dim": hd, "intermediate_size": spec.inter,
-           "vocab_size": spec.vocab, "rms_norm_eps": spec.eps, "rope_theta": spec.theta, "tie_word_embeddings": False,
-           "torch_dtype": "bfloat16"}
-    if spec.arch == "gemma3":
-        cfg.update({"sliding_window": spec.window, "sliding_window_pattern": spec.global_every, "rope_local_base_freq": spec.theta_local})
-    if spec.bits != 16:
-        cfg["quantization"] = {"group_size": 64, "bits": spec.bits}
-    with open(os.path.join(path, "config.json"), "w") as f:
-        json.dump(cfg, f, indent=2)
-    write_safetensors(os.path.join(path, "model.safetensors"), t, {"format": "mlx"})

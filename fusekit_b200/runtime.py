@@ -342,7 +342,7 @@ class DecodeEngine:
     def task_graph(self) -> dict:
         """This engine's decode step as a v2 ``task_graph.json`` document (see task_graph.emit)."""
         return task_graph.emit(self.spec, self.capacity, self.rank, self.world,
-                               fused_weights=self.rt.tiled, want_logits=self.want_logits, embed_bits=self.embed_bits)
+                               fused_weights=self.rt.tiled, want_logits=self.want_logits, embed_bits=getattr(self, "embed_bits", 16))
 
     def _resolve(self, role: str) -> int:
         """Device address (or fk_weight id) behind one role string of the task graph."""

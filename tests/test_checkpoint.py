@@ -9,7 +9,7 @@ import pytest
 from fusekit_b200 import checkpoint as CK
 from fusekit_b200.model_spec import CONFIGS
 from oracle import oracle as O
-from tests.helpers import compare_greedy, oracle_config
+from tests.helpers import compare_greedy, export_oracle_model, oracle_config
 
 
 def test_reader_agrees_with_the_safetensors_library(tmp_path):
@@ -78,7 +78,7 @@ def _export(tmp_path, name, bits):
     spec = CONFIGS[name].with_bits(bits)
     m = O.Model(oracle_config(spec, 64))
     d = str(tmp_path / f"{name}-q{bits}")
-    CK.export_oracle_model(m, spec, d)
+    export_oracle_model(m, spec, d)
     return spec, m, d
 
 
