@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stddef.h>
 
 #define FK_MAX_ROWS 16          // independent sequences decoded together (batch rows)
 #define FK_WARP 32
@@ -17,7 +18,10 @@ struct FkState {
     uint32_t hist_counter;      // tokens appended to history so far
     uint32_t error;             // non-zero: a kernel refused its arguments
     uint32_t hist_cap;
+    uint32_t epoch;             // tokens finalised since the handle was opened; never reset (fk_state_set keeps it), so all
+                                // tensor-parallel ranks agree on it: the sequence number of the fused peer exchanges
 };
+#define FK_STATE_SET_BYTES offsetof(FkState, epoch)      // what fk_state_set overwrites
 
 // A linear layer's weights as the kernels see them (MLX-affine rows, group 64).
 struct WView {
@@ -76,4 +80,51 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ unsigned long long argmax_key(uint16_t bits, uint32_t idx) {
     uint32_t k = (bits & 0x8000u) ? (uint32_t)(uint16_t)~bits : (uint32_t)(bits ^ 0x8000u);
     return ((unsigned long long)k << 32) | (unsigned long long)(0xffffffffu - idx);
+}
+
+// ---------------------------------------------------------------- peer arenas of the tensor-parallel exchange
+#define FK_PEER_MAX 8
+#define FK_PEER_BLOCKS 8                    // blocks of an all-reduce; block b of every rank works on slice b
+#define FK_PEER_SLOT_BYTES (32 * 1024)      // payload limit per all-reduce
+#define FK_PEER_SITES 162                   // 2 parities of the all-reduce kernel + up to 160 fused exchange sites (2 per layer + argmax)
+#define FK_PEER_SITE0 2
+#define FK_PEER_SPIN_LIMIT (1u << 22)
+struct PeerArena {
+    // byte offsets inside a rank's arena.  Sites 0 and 1 are the two parities of the stand-alone all-reduce kernel; sites
+    // from FK_PEER_SITE0 on belong to the exchanges fused into the projection kernels (one site per row-split projection of
+    // the task list plus one for the argmax), so a site is written once per token and needs no parity.
+    __host__ __device__ static size_t slot(int site, int src) { return ((size_t)site * FK_PEER_MAX + src) * FK_PEER_SLOT_BYTES; }
+    __host__ __device__ static size_t flags0() { return (size_t)FK_PEER_SITES * FK_PEER_MAX * FK_PEER_SLOT_BYTES; }
+    __host__ __device__ static size_t flag(int site, int src, int block) { return flags0() + (((size_t)site * FK_PEER_MAX + src) * FK_PEER_BLOCKS + block) * 128; }
+    __host__ __device__ static size_t counter(int block) { return flag(FK_PEER_SITES, 0, 0) + (size_t)block * 128; }
+    __host__ __device__ static size_t ticket(int site) { return counter(FK_PEER_BLOCKS) + (size_t)site * 128; }
+    __host__ __device__ static size_t bytes() { return ticket(FK_PEER_SITES); }
+};
+struct PeerMap { unsigned char *base[FK_PEER_MAX]; int rank, world; unsigned int spin_limit; };     // base[r]: rank r's arena as mapped in this process; spin_limit: polls before a wait gives up
+
+// One fused exchange as a kernel sees it.  Producer side (a row-split projection): every finished fp32 partial row goes
+// into this rank's slot of `site` in every rank's arena (plain peer stores); the block that takes the last ticket of the
+// grid publishes flag = sequence number to every rank with a system-scope release.  Consumer side (the next norm-first
+// kernel): poll this rank's own arena until every source rank's flag has reached the sequence number (bounded), then add
+// the slots in rank order -- the same order on every rank, so all ranks hold bit-identical sums.
+struct PeerXchg { PeerMap map; int site; };      // site < 0: no exchange
+__device__ __forceinline__ void peer_publish(const PeerXchg &x, uint32_t seq) {      // one thread, after the ticket says "last"
+    __threadfence_system();
+    for (int p = 0; p < x.map.world; ++p) {
+        unsigned int *f = reinterpret_cast<unsigned int *>(x.map.base[p] + PeerArena::flag(x.site, x.map.rank, 0));
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
+    }
+}
+// threads 0 .. world-1 of a block each wait for one source rank; returns false (on those threads) if the wait ran out
+__device__ __forceinline__ bool peer_wait(const PeerXchg &x, uint32_t seq) {
+    bool ok = true;
+    if ((int)threadIdx.x < x.map.world) {
+        const unsigned int *f = reinterpret_cast<const unsigned int *>(x.map.base[x.map.rank] + PeerArena::flag(x.site, (int)threadIdx.x, 0));
+        unsigned int it = 0, v;
+        do {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+        } while ((int)(v - seq) < 0 && ++it < x.map.spin_limit);
+        ok = (int)(v - seq) >= 0;
+    }
+    return ok;
 }

@@ -826,18 +826,6 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
 // flag per (source rank, block); each rank polls its own arena only and sums the slots in rank order, so all ranks get
 // bit-identical results.  Slots and flags alternate by the parity of a per-block sequence number: a rank can be at most
 // one all-reduce ahead of a peer, because it needs that peer's push to finish the one in between.  Waits are bounded.
-#define FK_PEER_MAX 8
-#define FK_PEER_BLOCKS 8                    // blocks of an all-reduce; block b of every rank works on slice b
-#define FK_PEER_SLOT_BYTES (32 * 1024)      // payload limit per all-reduce
-#define FK_PEER_SPIN_LIMIT (1u << 22)
-struct PeerArena {
-    // byte offsets inside a rank's arena
-    __host__ __device__ static size_t slot(int parity, int src) { return ((size_t)parity * FK_PEER_MAX + src) * FK_PEER_SLOT_BYTES; }
-    __host__ __device__ static size_t flag(int parity, int src, int block) { return 2 * FK_PEER_MAX * FK_PEER_SLOT_BYTES + (((size_t)parity * FK_PEER_MAX + src) * FK_PEER_BLOCKS + block) * 128; }
-    __host__ __device__ static size_t counter(int block) { return flag(2, 0, 0) + (size_t)block * 128; }
-    __host__ __device__ static size_t bytes() { return counter(FK_PEER_BLOCKS); }
-};
-struct PeerMap { unsigned char *base[FK_PEER_MAX]; int rank, world; unsigned int spin_limit; };     // base[r]: rank r's arena as mapped in this process; spin_limit: polls before a wait gives up
 template <typename T, bool IS_MAX>
 __global__ void __launch_bounds__(256) k_allreduce_peer(T *buf, int n, PeerMap P, FkState *st) {
     __shared__ unsigned int seq_s; __shared__ int bad;
@@ -937,6 +925,7 @@ __device__ __forceinline__ void finalize_token(FkState *st, uint32_t *history, u
     if (history && st->hist_counter < st->hist_cap) history[st->hist_counter] = next;
     st->hist_counter += 1;
     st->offset += 1;
+    st->epoch += 1;
 }
 // final RMSNorm -> lm_head matvec -> argmax without a logits round trip: values are rounded to T
 // before the compare and ties go to the lowest index (final_rmsnorm_lm_head.rs:250-326;

@@ -499,6 +499,15 @@ static Shape make_plan(Ctx *c, const Weight *w, StreamPlan *p, const Weight *nex
 #define BITS48(bits, CALL) do { if ((bits) == 4) { constexpr int B = 4; CALL; } else { constexpr int B = 8; CALL; } } while (0)
 
 
+// the fused peer exchange named by a task argument (0 = none, n > 0 = exchange site n - 1 of the task list)
+static fk_status make_xchg(Ctx *c, int site_plus1, PeerXchg *x, const char *what) {
+    memset(x, 0, sizeof *x); x->site = -1;
+    if (site_plus1 <= 0) return FK_OK;
+    if (!c->peer_ready) return fail(FK_ERR_STATE, "%s: a peer exchange site needs fk_peer_arena_open first", what);
+    if (FK_PEER_SITE0 + site_plus1 - 1 >= FK_PEER_SITES) return fail(FK_ERR_VALUE, "%s: exchange site %d beyond the %d sites of an arena", what, site_plus1 - 1, FK_PEER_SITES - FK_PEER_SITE0);
+    x->map = c->peers; x->site = FK_PEER_SITE0 + site_plus1 - 1;
+    return FK_OK;
+}
 static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullptr) {
     const uint64_t *b = t.buf; const int32_t *i = t.iarg; const float *f = t.farg;
     cudaError_t e = cudaSuccess;
@@ -526,11 +535,13 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             if (sinks && (w->rows_kind != FK_ROWS_ROPE_PAIRS || w->hd != hd || w->n_rot != (nq + nkv) * hd)) return fail(FK_ERR_VALUE, "rmsnorm_qkv: weight rows must be laid out as RoPE pairs (fk_weight_set_rows)");
             if (!sinks && w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "rmsnorm_qkv without sinks takes plain row order");
             SQkvArgs sa{a.x, a.norm_w, StreamPlan(), a.lin_bias, a.q_out, a.cache_k, a.cache_v, a.k_out, a.v_out, a.pending, a.pending_w, a.h_out,
-                        H, nq, nkv, hd, cap, sinks, a.eps, a.log2theta, nullptr};
+                        H, nq, nkv, hd, cap, sinks, a.eps, a.log2theta, nullptr, PeerXchg()};
+            { fk_status xs = make_xchg(c, i[6], &sa.pull, "rmsnorm_qkv"); if (xs) return xs; }
+            if (sa.pull.site >= 0 && (b[9] || b[10] || H * 4 > FK_PEER_SLOT_BYTES)) return fail(FK_ERR_VALUE, "rmsnorm_qkv: a pulled exchange excludes pending inputs and needs H <= %d", FK_PEER_SLOT_BYTES / 4);
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }      // fp32 all-reduced projection + residual
             if (H > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "rmsnorm_qkv: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             const Shape sh = make_plan(c, w, &sa.P, nextw);
-            STREAM_LAUNCH_P(k_s_rmsnorm_qkv, (sa.pending || sa.pend_sum), w, sh, c->state, sa);
+            STREAM_LAUNCH_P(k_s_rmsnorm_qkv, (sa.pending || sa.pend_sum || sa.pull.site >= 0), w, sh, c->state, sa);
             break;
         }
         if (b[9] && !b[10]) return fail(FK_ERR_VALUE, "rmsnorm_qkv: the fused all-reduce residual needs 4/8-bit streamed weights");
@@ -581,7 +592,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
     case FK_TASK_LINEAR_RESIDUAL: {
         Weight *w = get_w(c, b[1]);
         if (!w || !w->finalized) return fail(FK_ERR_VALUE, "linear_residual: weight missing or not finalized");
-        if (w->k != i[0] || w->n != i[1] || !b[0] || (!b[3] && !b[4])) return fail(FK_ERR_VALUE, "linear_residual: shape mismatch");
+        if (w->k != i[0] || w->n != i[1] || !b[0] || (!b[3] && !b[4] && i[3] <= 0)) return fail(FK_ERR_VALUE, "linear_residual: shape mismatch");
         if (i[2] > 1) {                                    // 2..16 activation rows: the quantised matrix product
             if (i[2] > FK_QMM_MAXM) return fail(FK_ERR_VALUE, "linear_residual: at most %d activation rows", FK_QMM_MAXM);
             if (!w->tiled || w->bits != 4 || w->rows_kind != FK_ROWS_PLAIN || !b[3] || b[4])
@@ -594,11 +605,14 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         LinArgs a{(const uint16_t *)b[0], w->view(), (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], i[0], i[1]};
         if (w->tiled) {
             if (w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "linear_residual takes plain row order");
-            SLinArgs sa{a.x, StreamPlan(), a.residual, a.y, a.y_f32, i[0], i[1]};
+            SLinArgs sa{a.x, StreamPlan(), a.residual, a.y, a.y_f32, i[0], i[1], PeerXchg()};
+            { fk_status xs = make_xchg(c, i[3], &sa.push, "linear_residual"); if (xs) return xs; }
+            if (sa.push.site >= 0 && i[1] * 4 > FK_PEER_SLOT_BYTES) return fail(FK_ERR_VALUE, "linear_residual: a pushed exchange needs N <= %d", FK_PEER_SLOT_BYTES / 4);
             const Shape sh = make_plan(c, w, &sa.P, nextw);
             STREAM_LAUNCH(k_s_linear, w, sh, c->state, sa);
             break;
         }
+        if (i[3] > 0) return fail(FK_ERR_VALUE, "linear_residual: the fused peer exchange needs streamed weights");
         const int grid = grid_for(c, w->n, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_linear_residual<B>, dim3(grid), dim3(256), smem_bytes_for(i[0]), (const FkState *)c->state, a));
         break;
@@ -616,11 +630,13 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                 break;
             }
             SGateUpArgs sa{(const uint16_t *)b[0], (const uint16_t *)b[1], StreamPlan(), (uint16_t *)b[4],
-                           (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0], nullptr};
+                           (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0], nullptr, PeerXchg()};
+            { fk_status xs = make_xchg(c, i[4], &sa.pull, "gateup"); if (xs) return xs; }
+            if (sa.pull.site >= 0 && (b[9] || b[10] || i[0] * 4 > FK_PEER_SLOT_BYTES)) return fail(FK_ERR_VALUE, "gateup: a pulled exchange excludes pending inputs and needs H <= %d", FK_PEER_SLOT_BYTES / 4);
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "gateup: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             const Shape sh = make_plan(c, wg, &sa.P, nextw);
-            STREAM_LAUNCH_P(k_s_gateup, (sa.pending || sa.pend_sum), wg, sh, c->state, sa);
+            STREAM_LAUNCH_P(k_s_gateup, (sa.pending || sa.pend_sum || sa.pull.site >= 0), wg, sh, c->state, sa);
             break;
         }
         if (!wg || !wu || !wg->finalized || !wu->finalized) return fail(FK_ERR_VALUE, "gateup: weights missing or not finalized");
@@ -641,11 +657,13 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (w->tiled) {
             if (w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "lm_head takes plain row order");
             SHeadArgs sa{a.x, a.norm_w, StreamPlan(), a.logits, a.scratch, a.counter, a.pending, a.pending_w, a.h_out, a.history,
-                         a.h, a.v, a.vocab_offset, a.finalize, a.eps, nullptr};
+                         a.h, a.v, a.vocab_offset, a.finalize, a.eps, nullptr, PeerXchg(), PeerXchg()};
+            { fk_status xs = make_xchg(c, i[4], &sa.pull, "lm_head"); if (xs) return xs; xs = make_xchg(c, i[5], &sa.amax, "lm_head"); if (xs) return xs; }
+            if (sa.pull.site >= 0 && (b[9] || b[10] || i[0] * 4 > FK_PEER_SLOT_BYTES)) return fail(FK_ERR_VALUE, "lm_head: a pulled exchange excludes pending inputs and needs H <= %d", FK_PEER_SLOT_BYTES / 4);
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "lm_head: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             const Shape sh = make_plan(c, w, &sa.P, nextw);
-            STREAM_LAUNCH_P(k_s_head, (sa.pending || sa.pend_sum), w, sh, c->state, sa);
+            STREAM_LAUNCH_P(k_s_head, (sa.pending || sa.pend_sum || sa.pull.site >= 0), w, sh, c->state, sa);
             break;
         }
         const int grid = grid_for(c, w->n, 8);
@@ -727,7 +745,7 @@ static fk_status set_state(Ctx *c, uint32_t token, uint32_t offset) {
     if (c->vocab && token >= c->vocab) return fail(FK_ERR_VALUE, "token id %u is outside the embedding table (%u rows)", token, c->vocab);
     FkState *s = (FkState *)c->pinned; memset(s, 0, sizeof(FkState));
     s->token[0] = token; s->offset = offset; s->hist_counter = 0; s->error = 0; s->hist_cap = c->hist_cap;
-    CU(cudaMemcpyAsync(c->state, s, sizeof(FkState), cudaMemcpyHostToDevice, c->stream));
+    CU(cudaMemcpyAsync(c->state, s, FK_STATE_SET_BYTES, cudaMemcpyHostToDevice, c->stream));      // the epoch counter stays
     return FK_OK;
 }
 extern "C" fk_status fk_state_set(fk_handle h, uint32_t token, uint32_t offset) {

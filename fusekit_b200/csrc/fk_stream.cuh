@@ -275,7 +275,8 @@ __device__ __forceinline__ void norm_w_load(NormW &nw, const uint16_t *w, int h)
 template <int BITS, bool PEND = true>
 __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16_t *x, const NormW &nwv, int h, int nsb, float eps,
                                               const uint16_t *pending, const uint16_t *pending_w, uint16_t *h_out,
-                                              unsigned long long *tl = nullptr, const float *pend_sum = nullptr) {
+                                              unsigned long long *tl = nullptr, const float *pend_sum = nullptr,
+                                              const PeerXchg *pull = nullptr, FkState *st = nullptr) {
     const int nblk = h >> 3;
     uint4 xv[FK_STAGE_MAXB];
     const uint4 (&wv)[FK_STAGE_MAXB] = nwv.v;
@@ -284,7 +285,29 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
         const int blk = i * blockDim.x + threadIdx.x;
         xv[i] = blk < nblk ? __ldcg(reinterpret_cast<const uint4 *>(x + (size_t)blk * 8)) : make_uint4(0, 0, 0, 0);
     }
-    if (PEND && pend_sum) {     // tensor parallel: x' = T(all-reduced projection + residual x); block 0 publishes it
+    if (PEND && pull && pull->site >= 0) {      // tensor parallel, fused exchange: x' = T(sum over ranks of the partial rows + residual x)
+        const uint32_t seq = st->epoch + 1u;
+        if (!peer_wait(*pull, seq)) atomicOr(&st->error, 0x8000u);      // bounded: on expiry the sums are wrong, nothing hangs
+        __syncthreads();
+        const unsigned char *own = pull->map.base[pull->map.rank];
+#pragma unroll
+        for (int i = 0; i < FK_STAGE_MAXB; ++i) {
+            const int blk = i * blockDim.x + threadIdx.x;
+            if (blk < nblk) {
+                float4 s0 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), s1 = s0;
+                for (int p = 0; p < pull->map.world; ++p) {
+                    const float *src = reinterpret_cast<const float *>(own + PeerArena::slot(pull->site, p)) + (size_t)blk * 8;
+                    const float4 a0 = __ldcg(reinterpret_cast<const float4 *>(src)), a1 = __ldcg(reinterpret_cast<const float4 *>(src + 4));
+                    s0.x += a0.x; s0.y += a0.y; s0.z += a0.z; s0.w += a0.w; s1.x += a1.x; s1.y += a1.y; s1.z += a1.z; s1.w += a1.w;
+                }
+                float f[8]; unpack8(xv[i], f);
+                const uint16_t o0 = f2bf(s0.x + f[0]), o1 = f2bf(s0.y + f[1]), o2 = f2bf(s0.z + f[2]), o3 = f2bf(s0.w + f[3]);
+                const uint16_t o4 = f2bf(s1.x + f[4]), o5 = f2bf(s1.y + f[5]), o6 = f2bf(s1.z + f[6]), o7 = f2bf(s1.w + f[7]);
+                xv[i] = make_uint4(o0 | ((uint32_t)o1 << 16), o2 | ((uint32_t)o3 << 16), o4 | ((uint32_t)o5 << 16), o6 | ((uint32_t)o7 << 16));
+                if (blockIdx.x == 0 && h_out) *reinterpret_cast<uint4 *>(h_out + (size_t)blk * 8) = xv[i];
+            }
+        }
+    } else if (PEND && pend_sum) {     // tensor parallel: x' = T(all-reduced projection + residual x); block 0 publishes it
 #pragma unroll
         for (int i = 0; i < FK_STAGE_MAXB; ++i) {
             const int blk = i * blockDim.x + threadIdx.x;
@@ -685,7 +708,7 @@ __global__ void k_dequant_tiled(TiledW W, int which, long long row0, long long n
 
 // ================================================================ streamed kernels
 
-struct SLinArgs { const uint16_t *x; StreamPlan P; const uint16_t *residual; uint16_t *y; float *y_f32; int k, n; };
+struct SLinArgs { const uint16_t *x; StreamPlan P; const uint16_t *residual; uint16_t *y; float *y_f32; int k, n; PeerXchg push; };
 // Epilogues are functors: prefetch(tile, g) is called once per lane (lanes with (lane & 3) == 0) for the first tile the
 // lane will finish, before the streaming loop; operator() gets the finished sums of tile rows g and g + 8.
 
@@ -707,6 +730,9 @@ struct EpiLinear {
             if (r >= a.n) continue;
             if (a.y_f32) a.y_f32[r] = v[q];
             if (a.y) a.y[r] = f2bf(v[q] + res[q]);
+            if (a.push.site >= 0)           // row-split projection of a tensor-parallel layer: the fp32 partial goes to every rank
+                for (int p = 0; p < a.push.map.world; ++p)
+                    reinterpret_cast<float *>(a.push.map.base[p] + PeerArena::slot(a.push.site, a.push.map.rank))[r] = v[q];
         }
     }
 };
@@ -724,6 +750,14 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st
     EpiLinear epi(a);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x100u);
     pdl_launch_dependents();
+    if (a.push.site >= 0) {             // the block that takes the grid's last ticket tells every rank that this rank's rows are in
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned int *ticket = reinterpret_cast<unsigned int *>(a.push.map.base[a.push.map.rank] + PeerArena::ticket(a.push.site));
+            if (atomicAdd(ticket, 1u) == gridDim.x - 1) { *ticket = 0u; peer_publish(a.push, st->epoch + 1u); }
+        }
+    }
     __syncthreads(); stamp(a.P, 3);
 }
 
@@ -731,7 +765,7 @@ struct SQkvArgs {
     const uint16_t *x, *norm_w; StreamPlan P; const uint16_t *lin_bias;
     uint16_t *q_out, *cache_k, *cache_v, *k_out, *v_out;
     const uint16_t *pending, *pending_w; uint16_t *h_out;
-    int h, n_q, n_kv, hd, capacity, sinks; float eps, log2theta; const float *pend_sum;
+    int h, n_q, n_kv, hd, capacity, sinks; float eps, log2theta; const float *pend_sum; PeerXchg pull;
 };
 // cos and sin of the RoPE angle of dim d at position pos: inv = exp2(-(d / half) * log2(theta)) (rope_kv_cache_store_decode.rs)
 __device__ __forceinline__ void rope_angle(int d, int half, uint32_t pos, float log2theta, float *c, float *s) {
@@ -791,7 +825,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkStat
     NormW nwv; norm_w_load(nwv, a.norm_w, a.h);
     pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS, PEND>(sm, a.x, nwv, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
+    stage_rmsnorm<BITS, PEND>(sm, a.x, nwv, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum, &a.pull, st);
     stamp(a.P, 2);
     EpiQkv epi(a, st->offset);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x200u);
@@ -802,7 +836,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkStat
 struct SGateUpArgs {
     const uint16_t *x, *norm_w; StreamPlan P; uint16_t *act_out;
     const uint16_t *pending, *pending_w; uint16_t *h_out;
-    int h, inter, act; float eps; const float *pend_sum;
+    int h, inter, act; float eps; const float *pend_sum; PeerXchg pull;
 };
 __device__ __forceinline__ uint16_t s_act_swiglu(float ga, float ua) {
     const float g = rT(ga), u = rT(ua);
@@ -837,7 +871,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st
     NormW nwv; norm_w_load(nwv, a.norm_w, a.h);
     pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS, PEND>(sm, a.x, nwv, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
+    stage_rmsnorm<BITS, PEND>(sm, a.x, nwv, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum, &a.pull, st);
     stamp(a.P, 2);
     EpiGateUp epi(a);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x400u);
@@ -848,7 +882,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st
 struct SHeadArgs {
     const uint16_t *x, *norm_w; StreamPlan P; uint16_t *logits; unsigned long long *scratch; uint32_t *counter;
     const uint16_t *pending, *pending_w; uint16_t *h_out; uint32_t *history;
-    int h, v, vocab_offset, finalize; float eps; const float *pend_sum;
+    int h, v, vocab_offset, finalize; float eps; const float *pend_sum; PeerXchg pull, amax;
 };
 __device__ __forceinline__ void s_finalize_token(FkState *st, uint32_t *history, unsigned long long best) {
     const uint32_t next = 0xffffffffu - (uint32_t)(best & 0xffffffffull);
@@ -856,6 +890,7 @@ __device__ __forceinline__ void s_finalize_token(FkState *st, uint32_t *history,
     if (history && st->hist_counter < st->hist_cap) history[st->hist_counter] = next;
     st->hist_counter += 1;
     st->offset += 1;
+    st->epoch += 1;
 }
 struct EpiHead {
     const SHeadArgs &a; unsigned long long best;
@@ -887,7 +922,7 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, 
     NormW nwv; norm_w_load(nwv, a.norm_w, a.h);
     pdl_wait();
     stamp(a.P, 1);
-    stage_rmsnorm<BITS, PEND>(sm, a.x, nwv, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum);
+    stage_rmsnorm<BITS, PEND>(sm, a.x, nwv, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum, &a.pull, st);
     stamp(a.P, 2);
     EpiHead epi(a);
     const bool ok = stream_run<BITS>(ws, a.P, sm, epi);
@@ -914,6 +949,29 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, 
         unsigned long long b = 0ull;
         for (int i = lane; i < (int)gridDim.x; i += 32) { const unsigned long long v = __ldcg(a.scratch + i); b = v > b ? v : b; }
         b = warp_max_u64(b);
+        if (a.amax.site >= 0) {
+            // vocabulary-sharded head: this rank's best key goes to every rank, then every rank takes the maximum of all
+            // keys (the same on every rank) and advances its own decode state
+            const uint32_t seq = st->epoch + 1u;
+            if (lane == 0) {
+                for (int p = 0; p < a.amax.map.world; ++p)
+                    *reinterpret_cast<unsigned long long *>(a.amax.map.base[p] + PeerArena::slot(a.amax.site, a.amax.map.rank)) = b;
+                peer_publish(a.amax, seq);
+            }
+            __syncwarp();
+            const bool ok = peer_wait(a.amax, seq);
+            if (!ok) atomicOr(&st->error, 0x8000u);
+            __syncwarp();
+            if (lane == 0) {
+                unsigned long long best = 0ull;
+                for (int p = 0; p < a.amax.map.world; ++p) {
+                    const unsigned long long v = __ldcg(reinterpret_cast<const unsigned long long *>(a.amax.map.base[a.amax.map.rank] + PeerArena::slot(a.amax.site, p)));
+                    best = v > best ? v : best;
+                }
+                s_finalize_token(st, a.history, best);
+            }
+            return;
+        }
         if (lane == 0) { if (a.finalize) s_finalize_token(st, a.history, b); else a.scratch[0] = b; }
     }
 }

@@ -342,7 +342,7 @@ class DecodeEngine:
     def task_graph(self) -> dict:
         """This engine's decode step as a v2 ``task_graph.json`` document (see task_graph.emit)."""
         return task_graph.emit(self.spec, self.capacity, self.rank, self.world,
-                               fused_weights=self.rt.tiled, want_logits=self.want_logits, embed_bits=getattr(self, "embed_bits", 16))
+                               fused_weights=self.rt.tiled, want_logits=self.want_logits, embed_bits=getattr(self, "embed_bits", 16), tp_exchange=getattr(self, "tp_exchange", "allreduce"))
 
     def _resolve(self, role: str) -> int:
         """Device address (or fk_weight id) behind one role string of the task graph."""
@@ -480,10 +480,16 @@ class DecodeEngine:
             N.check(self.rt.L.fk_peer_arena_open(self.rt.h, blob, self.rank, self.world), "fk_peer_arena_open")
         except N.FusekitError:
             return False
+        # with the arenas mapped the exchange is fused into the projection kernels (FK_TP_EXCHANGE=allreduce keeps one
+        # all-reduce task per row-split projection, served by the stand-alone peer kernel)
+        import os
+        if self.rt.tiled and os.environ.get("FK_TP_EXCHANGE", "peer") == "peer":
+            self.tp_exchange = "peer"
         return True
 
     def peer_disable(self):
         """Drop the peer mappings (some rank could not map them): the library collective takes over."""
+        self.tp_exchange = "allreduce"
         N.check(self.rt.L.fk_peer_arena_close(self.rt.h), "fk_peer_arena_close")
 
     def close(self):

@@ -29,15 +29,24 @@ def _bf16_round(v: float) -> float:
 
 
 def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fused_weights: bool = True,
-         want_logits: bool = False, embed_bits: int = 16) -> dict:
+         want_logits: bool = False, embed_bits: int = 16, tp_exchange: str = "allreduce") -> dict:
     """Build the v2 task graph of one decode step for `spec` (one tensor-parallel rank of it).
 
     `fused_weights`: weights in the streaming layout (gate/up paired, residual add after an all-reduce fused into the next
-    norm-first kernel); False describes the generic kernels on MLX-layout rows."""
+    norm-first kernel); False describes the generic kernels on MLX-layout rows.
+    `tp_exchange`: how the partial rows of the row-split projections meet -- "allreduce": an all-reduce task after each
+    (library collective or the stand-alone peer kernel); "peer": no task of its own, the projection pushes its partial rows
+    into every rank's arena and the next norm-first kernel sums them (exchange site 2l for o_proj, 2l + 1 for down_proj of
+    layer l, 2L for the argmax keys of the vocabulary-sharded head)."""
     s, hd, H = spec, spec.head_dim, spec.hidden
     nq, nkv, inter, vocab = s.n_q // tp_size, s.n_kv // tp_size, s.inter // tp_size, s.vocab // tp_size
     tp = tp_size > 1
     fused = fused_weights
+    peer = tp and tp_exchange == "peer"
+    if peer and not fused:
+        raise ValueError("the fused peer exchange needs the streaming weight layout")
+    if peer and 2 * s.n_layers + 1 > 160:
+        raise ValueError("the fused peer exchange has 160 sites: at most 79 layers")
     tasks: list[dict] = []
 
     def add(kind, layer, bufs, iargs, fargs=()):
@@ -59,11 +68,13 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
         cap, theta = s.layer_capacity(l, capacity), s.layer_theta(l)
         ck, cv = f"layer_cache_k.{l}", f"layer_cache_v.{l}"
         if s.arch == "qwen2":
-            x_in, pend = x(l), {}
-            if tp and l > 0 and fused:                     # x[l] = T(all-reduced down_proj + h[l-1])
+            x_in, pend, pull = x(l), {}, 0
+            if tp and l > 0 and fused and peer:            # x[l] = T(sum of the ranks' down_proj partials + h[l-1])
+                x_in, pend, pull = hb(l - 1), {11: x(l)}, 2 * (l - 1) + 2
+            elif tp and l > 0 and fused:                   # x[l] = T(all-reduced down_proj + h[l-1])
                 x_in, pend = hb(l - 1), {9: "global_scratch.tp_partial_b", 11: x(l)}
             add(K_QKV, l, {0: x_in, 1: lp(l, "input_layernorm.weight"), 2: lp(l, "self_attn.qkv_proj"), 3: lp(l, "self_attn.qkv_proj.bias"),
-                           4: "layer_scratch.q_buf", 5: ck, 6: cv, **pend}, [H, nq, nkv, hd, cap, 1], [s.eps, theta])
+                           4: "layer_scratch.q_buf", 5: ck, 6: cv, **pend}, [H, nq, nkv, hd, cap, 1, pull], [s.eps, theta])
         else:
             x_in, pend = x(l), {}
             if l > 0:                                      # Gemma: x[l] = T(h[l-1] + rmsnorm(down_out[l-1]))
@@ -79,6 +90,13 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
             add(K_LIN, l, {0: "layer_scratch.sdpa_buf", 1: lp(l, "self_attn.o_proj"), 2: x(l), 3: hb(l)}, [ko, H])
             add(K_GATEUP, l, {0: hb(l), 1: lp(l, "post_attention_layernorm.weight"), **gateup(l), 4: "layer_scratch.silu_up"}, [H, inter, s.act], [s.eps])
             add(K_LIN, l, {0: "layer_scratch.silu_up", 1: lp(l, "mlp.down_proj"), 2: hb(l), 3: x(l + 1)}, [inter, H])
+        elif s.arch == "qwen2" and peer:
+            # row-split o/down with the exchange fused in: the projection pushes fp32 partial rows to every rank (site in i3),
+            # the next norm-first kernel waits for all ranks, sums in rank order and adds the residual (site in its last iarg)
+            add(K_LIN, l, {0: "layer_scratch.sdpa_buf", 1: lp(l, "self_attn.o_proj")}, [ko, H, 0, 2 * l + 1])
+            add(K_GATEUP, l, {0: x(l), 11: hb(l), 1: lp(l, "post_attention_layernorm.weight"), **gateup(l), 4: "layer_scratch.silu_up"},
+                [H, inter, s.act, 0, 2 * l + 1], [s.eps])
+            add(K_LIN, l, {0: "layer_scratch.silu_up", 1: lp(l, "mlp.down_proj")}, [inter, H, 0, 2 * l + 2])
         elif s.arch == "qwen2":
             # row-split o/down: fp32 partial -> all-reduce over the ranks; the residual add rides in the next norm-first
             # kernel's prologue (streamed weights) or in a small kernel (generic weights)
@@ -103,12 +121,14 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
     x_fin, pend = x(L), {}
     if s.arch == "gemma3":
         x_fin, pend = hb(L - 1), {9: f"layer_scratch.{L-1}.out_buf", 10: lp(L - 1, "post_feedforward_layernorm.weight"), 11: x(L)}
+    elif tp and fused and peer:
+        x_fin, pend = hb(L - 1), {11: x(L)}
     elif tp and fused:
         x_fin, pend = hb(L - 1), {9: "global_scratch.tp_partial_b", 11: x(L)}
     add(K_HEAD, -1, {0: x_fin, 1: "param.final_norm", 2: "param.lm_head", 3: "global_scratch.logits" if want_logits else None,
                      4: "global_scratch.argmax_scratch", 5: "global_scratch.head_counter", **pend},
-        [H, vocab, tp_rank * vocab, 0 if tp else 1], [s.eps])
-    if tp:
+        [H, vocab, tp_rank * vocab, 0 if tp else 1] + ([2 * (L - 1) + 2, 2 * L + 1] if (tp and fused and peer) else []), [s.eps])
+    if tp and not (fused and peer):
         add(K_ALLREDUCE, -1, {0: "global_scratch.argmax_scratch"}, [1, 1])
         add(K_ARGMAX, -1, {4: "global_scratch.argmax_scratch"}, [1])
 

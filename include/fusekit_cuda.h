@@ -71,6 +71,8 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      buf9 pending_y|0  buf10 pending_norm_w  buf11 h_out   (Gemma: x <- T(x + rmsnorm(pending_y)));
  *                      with buf10 = 0, buf9 is an fp32 all-reduced projection: x <- T(buf9 + x) (tensor parallel)
  *                      i0 H  i1 n_q  i2 n_kv  i3 head_dim  i4 capacity  i5 sinks(1 = RoPE + cache store)
+ *                      i6 pull site + 1 (0 = none): x <- T(sum over ranks of the partial rows pushed to that exchange site + x),
+ *                      written to buf11 (tensor parallel with the exchange fused in, see LINEAR_RESIDUAL i3)
  *                      f0 eps  f1 rope_theta
  * QK_NORM_ROPE_STORE   buf0 q(in/out)  buf1 k_in  buf2 v_in  buf3 q_norm_w  buf4 k_norm_w  buf5 cache_k  buf6 cache_v
  *                      i0 n_q  i1 n_kv  i2 head_dim  i3 capacity   f0 eps  f1 rope_theta
@@ -82,12 +84,20 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      i2 activation rows M (0 or 1: one row).  M = 2..16: x is T[M, K], residual and y_out are T[M, N], row m
  *                      is the result the one-row task gives for x[m] (reference: the fusekit_qmm tiles for M > 1,
  *                      src/codegen/msl.rs:2318-2439, chosen in kernels/mod.rs:1442-1473); streamed 4-bit weights only
+ *                      i3 push site + 1 (0 = none; no reference counterpart): a row-split projection of a tensor-parallel layer
+ *                      stores its fp32 partial rows into every rank's peer arena (fk_peer_arena_open) and the last block
+ *                      publishes a flag; buf3 / buf4 may then be 0.  The norm-first task that follows names the same site as
+ *                      its pull site, waits (bounded) for all ranks and sums in rank order.  Sites are numbered from 0 in task
+ *                      order, at most 160, each written once per token
  * RMSNORM_GATEUP_ACT   buf0 x  buf1 norm_w  buf2 weight(gate)  buf3 weight(up)  buf4 act_out T[I]
  *                      buf9..11 pending (as RMSNORM_QKV)     i0 H  i1 I  i2 act   f0 eps
  *                      i3 activation rows M (0 or 1: one row).  M = 2..16: x is T[M, H], act_out is T[M, I], every row normalised
  *                      by its own RMS; paired 4-bit weights, no pending inputs (reference: fusekit_qmm_t_swiglu_pair_impl, msl.rs:2489)
+ *                      i4 pull site + 1 (as RMSNORM_QKV i6)
  * FINAL_RMSNORM_LM_HEAD buf0 x  buf1 norm_w  buf2 weight(head)  buf3 logits_out|0  buf4 argmax scratch(u64)
  *                      buf5 counter(u32)  buf9..11 pending     i0 H  i1 V(local)  i2 vocab_offset  i3 finalize(1/0)   f0 eps
+ *                      i4 pull site + 1 (as RMSNORM_QKV i6); i5 argmax site + 1: a vocabulary-sharded head pushes its best key
+ *                      to every rank, takes the maximum over the ranks and advances the decode state itself
  * ARGMAX_FINALIZE      buf4 argmax scratch  i0 entries
  * ALLREDUCE            buf0 f32 buffer   i0 count
  * RESIDUAL_ADD         buf0 sum f32[N]  buf1 residual T[N]  buf2 y_out T[N]   i0 N

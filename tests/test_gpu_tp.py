@@ -1,5 +1,6 @@
-"""Tensor-parallel decode on 2 GPUs against the single-rank oracle, once with the library all-reduce (NCCL, captured in
-the graph) and once with the peer-memory all-reduce kernel.  Skipped where fewer than two CUDA devices are visible."""
+"""Tensor-parallel decode on 2 GPUs against the single-rank oracle: with the library all-reduce (NCCL, captured in the
+graph), with the stand-alone peer-memory all-reduce kernel, and with the exchange fused into the projection kernels (no
+all-reduce task at all).  Skipped where fewer than two CUDA devices are visible."""
 import os
 import subprocess
 import sys
@@ -26,11 +27,18 @@ WORKER = textwrap.dedent("""
     eng = DecodeEngine(spec, 64, device=rank, tp_rank=rank, tp_size=world)
     eng.comm_init(uid[0])
     if mode == "peer":
+        os.environ["FK_TP_EXCHANGE"] = "allreduce"
+    if mode in ("peer", "fused"):
         handles = [None] * world
         dist.all_gather_object(handles, eng.peer_export())
         assert eng.peer_open(handles), "peer arenas could not be mapped"
     eng.load_synthetic(); eng.prefill_kv_synthetic(ctx)
+    from fusekit_b200 import _native as N
+    kinds = [t.kind for t in eng.build_dispatches()]
+    assert (N.TASK_ALLREDUCE in kinds) == (mode != "fused"), kinds
     toks, secs = eng.decode_chunk(ctx, 3, steps)
+    toks2, _ = eng.decode_chunk(ctx + steps, int(toks[-1]), 4)          # a second chunk: the exchange sequence numbers carry on
+    toks = np.concatenate([toks, toks2])
     gathered = [None] * world
     dist.all_gather_object(gathered, [int(t) for t in toks])
     assert all(g == gathered[0] for g in gathered), gathered        # every rank decodes the same stream
@@ -45,12 +53,12 @@ WORKER = textwrap.dedent("""
 """)
 
 
-@pytest.mark.parametrize("mode", ["nccl", "peer"])
+@pytest.mark.parametrize("mode", ["nccl", "peer", "fused"])
 def test_two_rank_tensor_parallel_decode(tmp_path, mode):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
-    port = 29700 + os.getpid() % 2000 + (1 if mode == "peer" else 0)
+    port = 29700 + os.getpid() % 2000 + {"nccl": 0, "peer": 1, "fused": 2}[mode]
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER.format(root=ROOT, port=port))
     procs = [subprocess.Popen([sys.executable, str(script), str(r), "2", mode], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)

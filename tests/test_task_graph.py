@@ -110,3 +110,25 @@ def test_reader_refuses_what_it_cannot_dispatch():
     bad["tasks"][1]["extra_bindings"][0]["role"] = "layer_scratch.nonesuch"
     with pytest.raises(KeyError):
         e.dispatches_from(bad)
+
+
+def test_fused_peer_exchange_graph_has_no_allreduce_tasks():
+    """Tensor parallel with the exchange fused in: five tasks per layer as on one GPU, the row-split projections carry a
+    push site, the norm-first kernels after them the matching pull site, the head pulls the last down_proj and exchanges
+    the argmax keys itself."""
+    spec = CONFIGS["qwen2.5-32b"]
+    g = TG.emit(spec, 4352, tp_rank=3, tp_size=8, tp_exchange="peer")
+    kinds = [t["kind"] for t in g["tasks"]]
+    assert TG.K_ALLREDUCE not in kinds and TG.K_ARGMAX not in kinds and TG.K_RESADD not in kinds
+    assert len(kinds) == 2 + 5 * spec.n_layers
+    L = spec.n_layers
+    lin = [t for t in g["tasks"] if t["kind"] == TG.K_LIN]
+    assert [t["iargs"][3] for t in lin] == [s + 1 for s in range(2 * L)]                    # sites 0 .. 2L-1 in order
+    gu = [t for t in g["tasks"] if t["kind"] == TG.K_GATEUP]
+    assert [t["iargs"][4] for t in gu] == [2 * l + 1 for l in range(L)]
+    qkv = [t for t in g["tasks"] if t["kind"] == TG.K_QKV]
+    assert [t["iargs"][6] for t in qkv] == [0] + [2 * l + 2 for l in range(L - 1)]
+    head = g["tasks"][-1]
+    assert head["kind"] == TG.K_HEAD and head["iargs"][3] == 0 and head["iargs"][4:6] == [2 * L, 2 * L + 1]
+    with pytest.raises(ValueError):
+        TG.emit(spec, 4352, tp_rank=0, tp_size=8, fused_weights=False, tp_exchange="peer")
