@@ -85,7 +85,7 @@ __device__ __forceinline__ unsigned long long argmax_key(uint16_t bits, uint32_t
 // ---------------------------------------------------------------- peer arenas of the tensor-parallel exchange
 #define FK_PEER_MAX 8
 #define FK_PEER_BLOCKS 8                    // blocks of an all-reduce; block b of every rank works on slice b
-#define FK_PEER_SLOT_BYTES (32 * 1024)      // payload limit per all-reduce
+#define FK_PEER_SLOT_BYTES (64 * 1024)      // bytes of a (site, source rank) slot: 16 Ki fp32 for the all-reduce kernel, 8 Ki (value, sequence) pairs for a fused exchange
 #define FK_PEER_SITES 162                   // 2 parities of the all-reduce kernel + up to 160 fused exchange sites (2 per layer + argmax)
 #define FK_PEER_SITE0 2
 #define FK_PEER_SPIN_LIMIT (1u << 22)
@@ -102,29 +102,36 @@ struct PeerArena {
 };
 struct PeerMap { unsigned char *base[FK_PEER_MAX]; int rank, world; unsigned int spin_limit; };     // base[r]: rank r's arena as mapped in this process; spin_limit: polls before a wait gives up
 
-// One fused exchange as a kernel sees it.  Producer side (a row-split projection): every finished fp32 partial row goes
-// into this rank's slot of `site` in every rank's arena (plain peer stores); the block that takes the last ticket of the
-// grid publishes flag = sequence number to every rank with a system-scope release.  Consumer side (the next norm-first
-// kernel): poll this rank's own arena until every source rank's flag has reached the sequence number (bounded), then add
-// the slots in rank order -- the same order on every rank, so all ranks hold bit-identical sums.
+// One fused exchange as a kernel sees it.  A slot holds (value, sequence number) pairs, 8 bytes each and written with one
+// 8-byte store, so a pair is either old or new as a whole and needs no fence, flag or ticket (the scheme of low-latency
+// collectives).  Producer side (a row-split projection): every finished fp32 partial row goes, paired with the token's
+// sequence number, into this rank's slot of `site` in every rank's arena (plain peer stores).  Consumer side (the next
+// norm-first kernel): read the pairs of all source ranks from this rank's own arena until their sequence numbers match
+// (bounded), and add the values in rank order -- the same order on every rank, so all ranks hold bit-identical sums.  A site
+// is written once per token, so the previous token's pairs (sequence number - 1) can never be mistaken for this token's.
 struct PeerXchg { PeerMap map; int site; };      // site < 0: no exchange
-__device__ __forceinline__ void peer_publish(const PeerXchg &x, uint32_t seq) {      // one thread, after the ticket says "last"
-    __threadfence_system();
+__device__ __forceinline__ void peer_store_pair(const PeerXchg &x, int index, uint32_t value_bits, uint32_t seq) {
     for (int p = 0; p < x.map.world; ++p) {
-        unsigned int *f = reinterpret_cast<unsigned int *>(x.map.base[p] + PeerArena::flag(x.site, x.map.rank, 0));
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
+        uint2 *dst = reinterpret_cast<uint2 *>(x.map.base[p] + PeerArena::slot(x.site, x.map.rank)) + index;
+        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(value_bits), "r"(seq) : "memory");
     }
 }
-// threads 0 .. world-1 of a block each wait for one source rank; returns false (on those threads) if the wait ran out
-__device__ __forceinline__ bool peer_wait(const PeerXchg &x, uint32_t seq) {
-    bool ok = true;
-    if ((int)threadIdx.x < x.map.world) {
-        const unsigned int *f = reinterpret_cast<const unsigned int *>(x.map.base[x.map.rank] + PeerArena::flag(x.site, (int)threadIdx.x, 0));
-        unsigned int it = 0, v;
-        do {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-        } while ((int)(v - seq) < 0 && ++it < x.map.spin_limit);
-        ok = (int)(v - seq) >= 0;
-    }
+// two pairs (16 bytes) of source rank `src` as they are now (the caller checks the sequence numbers)
+__device__ __forceinline__ uint4 peer_peek_pairs(const PeerXchg &x, int src, int index) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(x.map.base[x.map.rank] + PeerArena::slot(x.site, src)) + (index >> 1);
+    uint4 w;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(p) : "memory");
+    return w;
+}
+// the same, polled until both pairs carry `seq`; false if the wait ran out
+__device__ __forceinline__ bool peer_wait_pairs(const PeerXchg &x, int src, int index, uint32_t seq, uint4 &w) {
+    unsigned int it = 0;
+    while ((w.y != seq || w.w != seq) && ++it < x.map.spin_limit) w = peer_peek_pairs(x, src, index);
+    return w.y == seq && w.w == seq;
+}
+__device__ __forceinline__ bool peer_load_pairs(const PeerXchg &x, int src, int index, uint32_t seq, uint32_t &v0, uint32_t &v1) {
+    uint4 w = peer_peek_pairs(x, src, index);
+    const bool ok = peer_wait_pairs(x, src, index, seq, w);
+    v0 = w.x; v1 = w.z;
     return ok;
 }

@@ -434,6 +434,7 @@ __global__ void __launch_bounds__(FK_SDPA_THREADS) k_sdpa_decode(const FkState *
 
 // ---------------------------------------------------------------- cluster SDPA
 #define FK_SDPA_CL 8            // CTAs per kv head (portable cluster size); they split the keys
+#define FK_SDPA_CLMAX 16        // the tensor-core kernel also runs as a cluster of 16 (non-portable size) when few kv heads leave SMs idle
 #define FK_SDPA_CW 16           // warps per CTA
 #define FK_SDPA_KPW 8           // keys per warp iteration (4 lanes per key)
 __host__ __device__ inline size_t sdpa_cl_smem_bytes(int G, int hd) {
@@ -630,8 +631,8 @@ template <int HD> struct SdpaMmaLayout {
     __host__ __device__ static constexpr int q() { return 0; }
     __host__ __device__ static constexpr int tiles() { return 8 * QSTRIDE; }
     __host__ __device__ static constexpr int cpart() { return tiles() + FK_SDPA_CW * WTILE; }
-    __host__ __device__ static constexpr int wexp(int G) { return cpart() + (G * HD + FK_SDPA_CL) * 4; }      // after the received o slices
-    __host__ __device__ static constexpr int bytes(int G) { return wexp(G) + FK_SDPA_CL * G * 2 * 4 + 64; }
+    __host__ __device__ static constexpr int wexp(int G) { return cpart() + (G * HD + FK_SDPA_CLMAX) * 4; }      // after the received o slices
+    __host__ __device__ static constexpr int bytes(int G) { return wexp(G) + FK_SDPA_CLMAX * G * 2 * 4 + 64; }
 };
 __host__ __device__ inline size_t sdpa_mma_smem_bytes(int G, int hd) { return hd == 256 ? SdpaMmaLayout<256>::bytes(G) : hd == 128 ? SdpaMmaLayout<128>::bytes(G) : SdpaMmaLayout<64>::bytes(G); }
 template <int HD>
@@ -806,10 +807,10 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
         const int gg = i / HD, d = i - gg * HD;
         float M = -INFINITY;
 #pragma unroll
-        for (int rr = 0; rr < FK_SDPA_CL; ++rr) if (rr < CL) M = fmaxf(M, recv_ml[(rr * G + gg) * 2]);
+        for (int rr = 0; rr < FK_SDPA_CLMAX; ++rr) if (rr < CL) M = fmaxf(M, recv_ml[(rr * G + gg) * 2]);
         float Ls = 0.0f, O = 0.0f;
 #pragma unroll
-        for (int rr = 0; rr < FK_SDPA_CL; ++rr) if (rr < CL) {
+        for (int rr = 0; rr < FK_SDPA_CLMAX; ++rr) if (rr < CL) {
             const float mr = recv_ml[(rr * G + gg) * 2];
             const float e = mr == -INFINITY ? 0.0f : expf(mr - M);
             Ls = fmaf(recv_ml[(rr * G + gg) * 2 + 1], e, Ls); O = fmaf(recv_o[rr * per + il], e, O);
@@ -844,7 +845,8 @@ __global__ void __launch_bounds__(256) k_allreduce_peer(T *buf, int n, PeerMap P
         const T v = buf[i];
         for (int p = 0; p < P.world; ++p) reinterpret_cast<T *>(P.base[p] + PeerArena::slot(par, P.rank))[i] = v;
     }
-    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) __threadfence_system();       // one fence per block orders all of the block's peer stores
     __syncthreads();
     // 2. tell every rank that slice b of this rank is in; 3. wait for slice b of every rank
     if ((int)threadIdx.x < P.world) {

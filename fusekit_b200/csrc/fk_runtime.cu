@@ -132,7 +132,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     e = getenv("FK_SDPA"); if (e && !strcmp(e, "ticket")) c->sdpa_cluster = false;
     if (e && !strcmp(e, "mma")) c->sdpa_mma = true;
     if (e && !strcmp(e, "fma")) c->sdpa_mma = false;
-    e = getenv("FK_SDPA_CL"); if (e && (atoi(e) == 1 || atoi(e) == 2 || atoi(e) == 4 || atoi(e) == 8)) c->sdpa_cl = atoi(e);      // CTAs per kv head of the tensor-core attention
+    e = getenv("FK_SDPA_CL"); if (e && (atoi(e) == 1 || atoi(e) == 2 || atoi(e) == 4 || atoi(e) == 8 || atoi(e) == 16)) c->sdpa_cl = atoi(e);      // CTAs per kv head of the tensor-core attention
     e = getenv("FK_WARPS"); if (e) c->force_warps = atoi(e);
     e = getenv("FK_WIDE_UPTO"); if (e) c->wide_upto = atoi(e);      // 16-warp blocks for weights of up to this many tiles per warp of the machine
     e = getenv("FK_SPLIT"); if (e) c->force_split = atoi(e);        // log2 of the warps sharing a row tile (tuning)
@@ -140,6 +140,9 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
 #define BIG4P(K) CU(big_smem(K<4, 8, true>)); CU(big_smem(K<4, 16, true>)); CU(big_smem(K<8, 8, true>)); CU(big_smem(K<8, 16, true>)); CU(big_smem(K<16, 8, true>)); CU(big_smem(K<16, 16, true>))
     BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head); BIG4P(k_s_rmsnorm_qkv); BIG4P(k_s_gateup); BIG4P(k_s_head);
     CU(big_smem(k_sdpa_mma<64>)); CU(big_smem(k_sdpa_mma<128>)); CU(big_smem(k_sdpa_mma<256>));
+    CU(cudaFuncSetAttribute(k_sdpa_mma<64>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    CU(cudaFuncSetAttribute(k_sdpa_mma<128>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    CU(cudaFuncSetAttribute(k_sdpa_mma<256>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     CU(big_smem(k_qmm4<false>)); CU(big_smem(k_qmm4<true>));
     CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
@@ -537,7 +540,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             SQkvArgs sa{a.x, a.norm_w, StreamPlan(), a.lin_bias, a.q_out, a.cache_k, a.cache_v, a.k_out, a.v_out, a.pending, a.pending_w, a.h_out,
                         H, nq, nkv, hd, cap, sinks, a.eps, a.log2theta, nullptr, PeerXchg()};
             { fk_status xs = make_xchg(c, i[6], &sa.pull, "rmsnorm_qkv"); if (xs) return xs; }
-            if (sa.pull.site >= 0 && (b[9] || b[10] || H * 4 > FK_PEER_SLOT_BYTES)) return fail(FK_ERR_VALUE, "rmsnorm_qkv: a pulled exchange excludes pending inputs and needs H <= %d", FK_PEER_SLOT_BYTES / 4);
+            if (sa.pull.site >= 0 && (b[9] || b[10] || H * 8 > FK_PEER_SLOT_BYTES)) return fail(FK_ERR_VALUE, "rmsnorm_qkv: a pulled exchange excludes pending inputs and needs H <= %d", FK_PEER_SLOT_BYTES / 8);
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }      // fp32 all-reduced projection + residual
             if (H > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "rmsnorm_qkv: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             const Shape sh = make_plan(c, w, &sa.P, nextw);
@@ -569,7 +572,8 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (G <= 8 && (variant == 4 || (variant == 0 && hd <= 128 && c->sdpa_mma && c->sdpa_cluster))) {
             const size_t smem = sdpa_mma_smem_bytes(G, hd);
             // CTAs per kv head: 8 even for short caches (measured at 513 keys: 6.9 us with 8, 7.7 with 4, 10.6 with 2, 13.1 with 1)
-            const int cl = c->sdpa_cl > 0 ? c->sdpa_cl : FK_SDPA_CL;
+            // 16 when few kv heads would leave most SMs idle on a long cache (a tensor-parallel slice of the 32B shape: 1 to 4 kv heads)
+            const int cl = c->sdpa_cl > 0 ? c->sdpa_cl : ((nkv * 16 <= c->sm_count / 2 && cap >= 2048) ? FK_SDPA_CLMAX : FK_SDPA_CL);
             const dim3 cgrid(cl, nkv), cblock(FK_SDPA_CW * 32);
             if (hd == 64) e = launch_cluster(c, k_sdpa_mma<64>, cgrid, cblock, smem, cl, (const FkState *)c->state, a);
             else if (hd == 128) e = launch_cluster(c, k_sdpa_mma<128>, cgrid, cblock, smem, cl, (const FkState *)c->state, a);
@@ -607,7 +611,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             if (w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "linear_residual takes plain row order");
             SLinArgs sa{a.x, StreamPlan(), a.residual, a.y, a.y_f32, i[0], i[1], PeerXchg()};
             { fk_status xs = make_xchg(c, i[3], &sa.push, "linear_residual"); if (xs) return xs; }
-            if (sa.push.site >= 0 && i[1] * 4 > FK_PEER_SLOT_BYTES) return fail(FK_ERR_VALUE, "linear_residual: a pushed exchange needs N <= %d", FK_PEER_SLOT_BYTES / 4);
+            if (sa.push.site >= 0 && i[1] * 8 > FK_PEER_SLOT_BYTES) return fail(FK_ERR_VALUE, "linear_residual: a pushed exchange needs N <= %d", FK_PEER_SLOT_BYTES / 8);
             const Shape sh = make_plan(c, w, &sa.P, nextw);
             STREAM_LAUNCH(k_s_linear, w, sh, c->state, sa);
             break;
@@ -632,7 +636,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             SGateUpArgs sa{(const uint16_t *)b[0], (const uint16_t *)b[1], StreamPlan(), (uint16_t *)b[4],
                            (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0], nullptr, PeerXchg()};
             { fk_status xs = make_xchg(c, i[4], &sa.pull, "gateup"); if (xs) return xs; }
-            if (sa.pull.site >= 0 && (b[9] || b[10] || i[0] * 4 > FK_PEER_SLOT_BYTES)) return fail(FK_ERR_VALUE, "gateup: a pulled exchange excludes pending inputs and needs H <= %d", FK_PEER_SLOT_BYTES / 4);
+            if (sa.pull.site >= 0 && (b[9] || b[10] || i[0] * 8 > FK_PEER_SLOT_BYTES)) return fail(FK_ERR_VALUE, "gateup: a pulled exchange excludes pending inputs and needs H <= %d", FK_PEER_SLOT_BYTES / 8);
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "gateup: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             const Shape sh = make_plan(c, wg, &sa.P, nextw);
@@ -659,7 +663,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             SHeadArgs sa{a.x, a.norm_w, StreamPlan(), a.logits, a.scratch, a.counter, a.pending, a.pending_w, a.h_out, a.history,
                          a.h, a.v, a.vocab_offset, a.finalize, a.eps, nullptr, PeerXchg(), PeerXchg()};
             { fk_status xs = make_xchg(c, i[4], &sa.pull, "lm_head"); if (xs) return xs; xs = make_xchg(c, i[5], &sa.amax, "lm_head"); if (xs) return xs; }
-            if (sa.pull.site >= 0 && (b[9] || b[10] || i[0] * 4 > FK_PEER_SLOT_BYTES)) return fail(FK_ERR_VALUE, "lm_head: a pulled exchange excludes pending inputs and needs H <= %d", FK_PEER_SLOT_BYTES / 4);
+            if (sa.pull.site >= 0 && (b[9] || b[10] || i[0] * 8 > FK_PEER_SLOT_BYTES)) return fail(FK_ERR_VALUE, "lm_head: a pulled exchange excludes pending inputs and needs H <= %d", FK_PEER_SLOT_BYTES / 8);
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "lm_head: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             const Shape sh = make_plan(c, w, &sa.P, nextw);

@@ -287,26 +287,29 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
     }
     if (PEND && pull && pull->site >= 0) {      // tensor parallel, fused exchange: x' = T(sum over ranks of the partial rows + residual x)
         const uint32_t seq = st->epoch + 1u;
-        if (!peer_wait(*pull, seq)) atomicOr(&st->error, 0x8000u);      // bounded: on expiry the sums are wrong, nothing hangs
-        __syncthreads();
-        const unsigned char *own = pull->map.base[pull->map.rank];
+        bool ok = true;
 #pragma unroll
         for (int i = 0; i < FK_STAGE_MAXB; ++i) {
             const int blk = i * blockDim.x + threadIdx.x;
             if (blk < nblk) {
-                float4 s0 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), s1 = s0;
+                float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
                 for (int p = 0; p < pull->map.world; ++p) {
-                    const float *src = reinterpret_cast<const float *>(own + PeerArena::slot(pull->site, p)) + (size_t)blk * 8;
-                    const float4 a0 = __ldcg(reinterpret_cast<const float4 *>(src)), a1 = __ldcg(reinterpret_cast<const float4 *>(src + 4));
-                    s0.x += a0.x; s0.y += a0.y; s0.z += a0.z; s0.w += a0.w; s1.x += a1.x; s1.y += a1.y; s1.z += a1.z; s1.w += a1.w;
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2) {
+                        uint32_t v0, v1;
+                        ok = peer_load_pairs(*pull, p, blk * 8 + j, seq, v0, v1) && ok;      // bounded: on expiry the sums are wrong, nothing hangs
+                        sum[j] += __uint_as_float(v0); sum[j + 1] += __uint_as_float(v1);
+                    }
                 }
                 float f[8]; unpack8(xv[i], f);
-                const uint16_t o0 = f2bf(s0.x + f[0]), o1 = f2bf(s0.y + f[1]), o2 = f2bf(s0.z + f[2]), o3 = f2bf(s0.w + f[3]);
-                const uint16_t o4 = f2bf(s1.x + f[4]), o5 = f2bf(s1.y + f[5]), o6 = f2bf(s1.z + f[6]), o7 = f2bf(s1.w + f[7]);
-                xv[i] = make_uint4(o0 | ((uint32_t)o1 << 16), o2 | ((uint32_t)o3 << 16), o4 | ((uint32_t)o5 << 16), o6 | ((uint32_t)o7 << 16));
+                uint16_t o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = f2bf(sum[j] + f[j]);
+                xv[i] = make_uint4(o[0] | ((uint32_t)o[1] << 16), o[2] | ((uint32_t)o[3] << 16), o[4] | ((uint32_t)o[5] << 16), o[6] | ((uint32_t)o[7] << 16));
                 if (blockIdx.x == 0 && h_out) *reinterpret_cast<uint4 *>(h_out + (size_t)blk * 8) = xv[i];
             }
         }
+        if (!ok) atomicOr(&st->error, 0x8000u);
     } else if (PEND && pend_sum) {     // tensor parallel: x' = T(all-reduced projection + residual x); block 0 publishes it
 #pragma unroll
         for (int i = 0; i < FK_STAGE_MAXB; ++i) {
@@ -714,8 +717,8 @@ struct SLinArgs { const uint16_t *x; StreamPlan P; const uint16_t *residual; uin
 
 // y = T(acc + float(residual)) (src/codegen/msl.rs:2759-2775); residual optional; optional fp32 copy of acc
 struct EpiLinear {
-    const SLinArgs &a; float res[2]; int ptile;
-    __device__ __forceinline__ EpiLinear(const SLinArgs &a_) : a(a_), ptile(-1) { res[0] = res[1] = 0.0f; }
+    const SLinArgs &a; float res[2]; int ptile; uint32_t seq;
+    __device__ __forceinline__ EpiLinear(const SLinArgs &a_, uint32_t seq_) : a(a_), ptile(-1), seq(seq_) { res[0] = res[1] = 0.0f; }
     __device__ __forceinline__ void prefetch(int tile, int g) {
         ptile = tile;
 #pragma unroll
@@ -730,9 +733,7 @@ struct EpiLinear {
             if (r >= a.n) continue;
             if (a.y_f32) a.y_f32[r] = v[q];
             if (a.y) a.y[r] = f2bf(v[q] + res[q]);
-            if (a.push.site >= 0)           // row-split projection of a tensor-parallel layer: the fp32 partial goes to every rank
-                for (int p = 0; p < a.push.map.world; ++p)
-                    reinterpret_cast<float *>(a.push.map.base[p] + PeerArena::slot(a.push.site, a.push.map.rank))[r] = v[q];
+            if (a.push.site >= 0) peer_store_pair(a.push, r, __float_as_uint(v[q]), seq);     // row-split projection: the fp32 partial goes to every rank
         }
     }
 };
@@ -747,17 +748,9 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st
     stamp(a.P, 1);
     stage_plain<BITS, (WARPS == 16 ? 5 : 2)>(sm, a.x, a.k, a.P.W.nsb);
     stamp(a.P, 2);
-    EpiLinear epi(a);
+    EpiLinear epi(a, st->epoch + 1u);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x100u);
     pdl_launch_dependents();
-    if (a.push.site >= 0) {             // the block that takes the grid's last ticket tells every rank that this rank's rows are in
-        __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned int *ticket = reinterpret_cast<unsigned int *>(a.push.map.base[a.push.map.rank] + PeerArena::ticket(a.push.site));
-            if (atomicAdd(ticket, 1u) == gridDim.x - 1) { *ticket = 0u; peer_publish(a.push, st->epoch + 1u); }
-        }
-    }
     __syncthreads(); stamp(a.P, 3);
 }
 
@@ -950,24 +943,20 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_head(FkState *st, 
         for (int i = lane; i < (int)gridDim.x; i += 32) { const unsigned long long v = __ldcg(a.scratch + i); b = v > b ? v : b; }
         b = warp_max_u64(b);
         if (a.amax.site >= 0) {
-            // vocabulary-sharded head: this rank's best key goes to every rank, then every rank takes the maximum of all
-            // keys (the same on every rank) and advances its own decode state
+            // vocabulary-sharded head: this rank's best key goes to every rank (two (word, sequence) pairs), then every rank
+            // takes the maximum of all keys (the same on every rank) and advances its own decode state
             const uint32_t seq = st->epoch + 1u;
             if (lane == 0) {
-                for (int p = 0; p < a.amax.map.world; ++p)
-                    *reinterpret_cast<unsigned long long *>(a.amax.map.base[p] + PeerArena::slot(a.amax.site, a.amax.map.rank)) = b;
-                peer_publish(a.amax, seq);
-            }
-            __syncwarp();
-            const bool ok = peer_wait(a.amax, seq);
-            if (!ok) atomicOr(&st->error, 0x8000u);
-            __syncwarp();
-            if (lane == 0) {
-                unsigned long long best = 0ull;
+                peer_store_pair(a.amax, 0, (uint32_t)(b & 0xffffffffull), seq);
+                peer_store_pair(a.amax, 1, (uint32_t)(b >> 32), seq);
+                unsigned long long best = 0ull; bool ok = true;
                 for (int p = 0; p < a.amax.map.world; ++p) {
-                    const unsigned long long v = __ldcg(reinterpret_cast<const unsigned long long *>(a.amax.map.base[a.amax.map.rank] + PeerArena::slot(a.amax.site, p)));
+                    uint32_t lo, hi;
+                    ok = peer_load_pairs(a.amax, p, 0, seq, lo, hi) && ok;
+                    const unsigned long long v = ((unsigned long long)hi << 32) | lo;
                     best = v > best ? v : best;
                 }
+                if (!ok) atomicOr(&st->error, 0x8000u);
                 s_finalize_token(st, a.history, best);
             }
             return;
