@@ -97,8 +97,8 @@ struct PeerArena {
     __host__ __device__ static size_t flags0() { return (size_t)FK_PEER_SITES * FK_PEER_MAX * FK_PEER_SLOT_BYTES; }
     __host__ __device__ static size_t flag(int site, int src, int block) { return flags0() + (((size_t)site * FK_PEER_MAX + src) * FK_PEER_BLOCKS + block) * 128; }
     __host__ __device__ static size_t counter(int block) { return flag(FK_PEER_SITES, 0, 0) + (size_t)block * 128; }
-    __host__ __device__ static size_t ticket(int site) { return counter(FK_PEER_BLOCKS) + (size_t)site * 128; }
-    __host__ __device__ static size_t bytes() { return ticket(FK_PEER_SITES); }
+    __host__ __device__ static size_t xsum(int site) { return counter(FK_PEER_BLOCKS) + (size_t)site * (FK_PEER_SLOT_BYTES / 2); }   // the summed vector of a site, local use
+    __host__ __device__ static size_t bytes() { return xsum(FK_PEER_SITES); }
 };
 struct PeerMap { unsigned char *base[FK_PEER_MAX]; int rank, world; unsigned int spin_limit; };     // base[r]: rank r's arena as mapped in this process; spin_limit: polls before a wait gives up
 

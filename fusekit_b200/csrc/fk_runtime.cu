@@ -442,8 +442,17 @@ static Shape plan_shape(Ctx *c, const Weight *w) {
     }
     const int slots = c->sm_count * per_sm;
     const long long total_warps = (long long)slots * s.warps;
-    int ls = 0;
-    while ((2 << ls) <= s.warps && (long long)w->ntiles * (2 << ls) <= total_warps && (1 << ls) < w->nsb) ++ls;
+    // the split with the shortest critical path: rounds of the busiest block x units of a warp per round, plus half a unit per
+    // round for the fold when a tile is shared (a whole tile per warp leaves up to half the warps idle in the last round when
+    // tiles / warps is 1.5, and a weight with few tiles of long K wants as many parts as it takes to reach every SM)
+    (void)total_warps;
+    int ls = 0; double best = 1e30;
+    for (int l = 0; (1 << l) <= s.warps && ((1 << l) < 2 * w->nsb || l == 0); ++l) {
+        const int S = 1 << l, tpb_l = s.warps >> l;
+        const long long rounds_l = (w->ntiles + tpb_l - 1) / tpb_l, grid_l = rounds_l < slots ? rounds_l : slots;
+        const double cost = (double)((rounds_l + grid_l - 1) / grid_l) * ((w->nsb + S - 1) / S + (S > 1 ? 0.5 : 0.0));
+        if (cost < best - 1e-9) { best = cost; ls = l; }
+    }
     if (c->force_split >= 0) { ls = c->force_split; while ((1 << ls) > s.warps) --ls; }
     s.lsplit = ls;
     const int tpb = s.warps >> ls, rounds = (w->ntiles + tpb - 1) / tpb;

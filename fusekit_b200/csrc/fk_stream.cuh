@@ -285,28 +285,57 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
         const int blk = i * blockDim.x + threadIdx.x;
         xv[i] = blk < nblk ? __ldcg(reinterpret_cast<const uint4 *>(x + (size_t)blk * 8)) : make_uint4(0, 0, 0, 0);
     }
-    if (PEND && pull && pull->site >= 0) {      // tensor parallel, fused exchange: x' = T(sum over ranks of the partial rows + residual x)
+    if (PEND && pull && pull->site >= 0) {
+        // Tensor parallel, fused exchange: x' = T(sum over ranks of the partial rows + residual x).  Two steps, so that the cost
+        // does not grow with the number of ranks: (A) the blocks of this kernel share the sum -- a block takes a slice of the
+        // vector, one thread per (element pair, source rank) fetches the pushed (value, sequence) pairs, the ranks are added in
+        // rank order through shared memory, and the rounded pair goes, with the sequence number, into this GPU's summed vector
+        // of the site; (B) every block reads the whole summed vector from there.  Waits are bounded: on expiry the error word is
+        // set and the values are wrong, nothing hangs.
         const uint32_t seq = st->epoch + 1u;
+        const int world = pull->map.world, couples = h >> 1;
+        const int per_block = (couples + (int)gridDim.x - 1) / (int)gridDim.x, c0 = (int)blockIdx.x * per_block;
+        const int c1 = c0 + per_block < couples ? c0 + per_block : couples, pass = 256 / world;
+        unsigned char *own = pull->map.base[pull->map.rank];
+        uint2 *xsum = reinterpret_cast<uint2 *>(own + PeerArena::xsum(pull->site));
+        float2 *part = reinterpret_cast<float2 *>(sm.fold);            // [pass][world]; the fold buffer is free until the unit loop
         bool ok = true;
+        for (int base = c0; base < c1; base += pass) {
+            const int n = c1 - base < pass ? c1 - base : pass;
+            if ((int)threadIdx.x < n * world) {
+                const int e = (int)threadIdx.x / world, p = (int)threadIdx.x - e * world;
+                uint32_t v0, v1;
+                ok = peer_load_pairs(*pull, p, 2 * (base + e), seq, v0, v1) && ok;
+                part[e * world + p] = make_float2(__uint_as_float(v0), __uint_as_float(v1));
+            }
+            __syncthreads();
+            if ((int)threadIdx.x < n) {
+                const int ce = base + (int)threadIdx.x;
+                float s0 = 0.0f, s1 = 0.0f;
+                for (int p = 0; p < world; ++p) { const float2 v = part[threadIdx.x * world + p]; s0 += v.x; s1 += v.y; }
+                const uint32_t xr = __ldcg(reinterpret_cast<const uint32_t *>(x) + ce);
+                const uint32_t o = (uint32_t)f2bf(s0 + bf_lo(xr)) | ((uint32_t)f2bf(s1 + bf_hi(xr)) << 16);
+                asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(xsum + ce), "r"(o), "r"(seq) : "memory");
+                if (h_out) reinterpret_cast<uint32_t *>(h_out)[ce] = o;
+            }
+            __syncthreads();
+        }
 #pragma unroll
         for (int i = 0; i < FK_STAGE_MAXB; ++i) {
             const int blk = i * blockDim.x + threadIdx.x;
             if (blk < nblk) {
-                float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-                for (int p = 0; p < pull->map.world; ++p) {
+                uint32_t o[4];
 #pragma unroll
-                    for (int j = 0; j < 8; j += 2) {
-                        uint32_t v0, v1;
-                        ok = peer_load_pairs(*pull, p, blk * 8 + j, seq, v0, v1) && ok;      // bounded: on expiry the sums are wrong, nothing hangs
-                        sum[j] += __uint_as_float(v0); sum[j + 1] += __uint_as_float(v1);
-                    }
+                for (int j = 0; j < 4; j += 2) {          // two (pair, sequence) entries per 16-byte load
+                    const uint4 *src = reinterpret_cast<const uint4 *>(xsum + blk * 4 + j);
+                    uint4 w; unsigned int it = 0;
+                    do {
+                        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(src) : "memory");
+                    } while ((w.y != seq || w.w != seq) && ++it < pull->map.spin_limit);
+                    ok = ok && w.y == seq && w.w == seq;
+                    o[j] = w.x; o[j + 1] = w.z;
                 }
-                float f[8]; unpack8(xv[i], f);
-                uint16_t o[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = f2bf(sum[j] + f[j]);
-                xv[i] = make_uint4(o[0] | ((uint32_t)o[1] << 16), o[2] | ((uint32_t)o[3] << 16), o[4] | ((uint32_t)o[5] << 16), o[6] | ((uint32_t)o[7] << 16));
-                if (blockIdx.x == 0 && h_out) *reinterpret_cast<uint4 *>(h_out + (size_t)blk * 8) = xv[i];
+                xv[i] = make_uint4(o[0], o[1], o[2], o[3]);
             }
         }
         if (!ok) atomicOr(&st->error, 0x8000u);
