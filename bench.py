@@ -221,6 +221,79 @@ def timed_chunks(eng, ctx, warmup, steps, barrier, sampler=None):
     return dev_s, wall_s, first, last, tok
 
 
+def run_batch(args, local: int):
+    """Benchmark configuration 5 at batch M: M independent sequences advanced together on one GPU, every projection
+    reading its weights once per step for all rows.  `value` counts the tokens of all sequences; the first tokens of
+    sequence 0 are compared with a batch-1 CPU oracle run of that sequence (the same bounded sample is the CPU baseline)."""
+    import torch
+    from fusekit_b200.batch import BatchDecodeEngine
+    from fusekit_b200.model_spec import CONFIGS
+    config, bits, ctx = WORKLOADS[args.workload]
+    spec = CONFIGS[config].with_bits(bits)
+    M = args.batch
+    cap = ctx + CHUNK * max(args.steps, args.warmup) + 8
+    eng = BatchDecodeEngine(spec, cap, M, device=local, qmm={"auto": 0, "tcgen05": 1, "mma": 2}[args.qmm])
+    eng.load_synthetic(); eng.prefill_kv_synthetic(ctx); eng.capture()
+    seeds = np.array([3 + 7 * m for m in range(M)], np.uint32)
+    first = None
+    for i in range(max(args.warmup, 1)):
+        out, _ = eng.decode_chunk(ctx + i * CHUNK, seeds, CHUNK)
+        first = out if first is None else first
+    sampler = ClockSampler(local); sampler.start()
+    torch.cuda.synchronize(); eng.rt.sync()
+    dev_s, t0, tok = 0.0, time.perf_counter(), seeds
+    for i in range(args.steps):
+        out, s = eng.decode_chunk(ctx + i * CHUNK, tok, CHUNK)
+        tok, dev_s = out[-1], dev_s + s
+    eng.rt.sync()
+    wall_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+    steps_total = args.steps * CHUNK
+    wbytes = spec.weight_bytes_per_token()
+    kv = spec.kv_bytes_per_token(ctx + CHUNK * args.steps // 2) * M
+    peak, peak_kind = measured_peak()
+    cpu_baseline, parity = None, None
+    if not args.no_cpu_baseline:
+        from oracle import oracle as O
+        cores = O.set_num_threads(host_cores())
+        m0 = O.Model(O.model_config(spec, ctx + 64))
+        hd = spec.head_dim
+        for l in range(spec.n_layers):           # sequence 0's pre-fill, the streams the engine used
+            k = np.zeros((spec.n_kv, ctx + 64, hd), np.uint16); v = np.zeros_like(k)
+            for hh in range(spec.n_kv):
+                k[hh, :ctx] = O.fill_normal_bf16(BatchDecodeEngine.cache_stream(spec, l, "k", 0), hh * 1048576 * hd, ctx * hd, 0.0, 1.0).reshape(ctx, hd)
+                v[hh, :ctx] = O.fill_normal_bf16(BatchDecodeEngine.cache_stream(spec, l, "v", 0), hh * 1048576 * hd, ctx * hd, 0.0, 1.0).reshape(ctx, hd)
+            m0.set_cache(l, k, v)
+        t1 = time.perf_counter(); m0.step(int(seeds[0]), ctx); t1 = time.perf_counter() - t1
+        n = int(max(1, min(CHUNK, args.cpu_budget / max(t1, 1e-3))))
+        t1 = time.perf_counter()
+        mism, ties = O.compare_greedy(first[:n, 0], m0, int(seeds[0]), ctx)
+        secs = time.perf_counter() - t1
+        m0.close()
+        cpu_baseline = {"value": n / secs, "unit": "tok/s", "cores": cores, "kind": "port",
+                        "sample": f"{n} tokens of one sequence of {args.workload} on the CPU oracle ({cores} threads): the CPU decodes sequences one at a time"}
+        parity = {"tokens_compared": n, "mismatches": len(mism), "near_ties": len(ties)}
+        if mism:
+            raise SystemExit(f"bench: batch row 0 differs from the CPU oracle beyond a near-tie: {mism}")
+    nodes = len(eng.tasks)
+    eng.close()
+    tps = steps_total * M / dev_s
+    print(json.dumps({
+        "metric": f"batch-{M} decode tok/s (all sequences), {args.workload}", "value": tps, "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4", "data": "synthetic",
+        "config": {"workload": args.workload, "batch": M, "tokens_per_step": CHUNK * M, "ctx_start": ctx, "graph_nodes_per_token": nodes,
+                   "projection_kernel": args.qmm, "l2": "inputs (weights) larger than L2"},
+        "e2e": {"value": steps_total * M / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 80, "d2h_bytes_per_step": CHUNK * M * 4 + 84},
+        "gpu_launches": nodes * steps_total, "clocks": clocks,
+        "per_sequence_tok_s": steps_total / dev_s,
+        "roofline": {"bound": "hbm", "kernel": "whole step (weights once per step + every sequence's KV)", "achieved": (wbytes + kv) * steps_total / dev_s / 1e9,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": (wbytes + kv) * steps_total / dev_s / 1e9 / peak,
+                     "bytes_per_launch": wbytes + kv, "weight_stream_gbs": wbytes * steps_total / dev_s / 1e9, "traffic": None},
+        "cpu_baseline": cpu_baseline, "parity_checked": parity is not None and not parity["mismatches"], "parity": parity,
+    }), flush=True)
+
+
 def main():
     global CHUNK
     ap = argparse.ArgumentParser()
@@ -232,6 +305,8 @@ def main():
     ap.add_argument("--chunk", type=int, default=CHUNK, help="tokens per step (64 = the reference's FK_CHUNK); smaller for profiler captures")
     ap.add_argument("--tp", action="store_true", help="N ranks form one tensor-parallel group (one stream) instead of N replicas")
     ap.add_argument("--no-tp-extra", action="store_true", help="with N > 1 replicas, skip the additional 32B tensor-parallel run")
+    ap.add_argument("--batch", type=int, default=1, help="independent sequences decoded together (2..16: the batch decode engine, one GPU)")
+    ap.add_argument("--qmm", default="auto", choices=["auto", "tcgen05", "mma"], help="kernel of the several-row projections in batch decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--profile-nodes", type=int, default=5, help="repeats of the per-kernel timing pass (0 = skip)")
@@ -241,6 +316,11 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+
+    if args.batch > 1:
+        if rank == 0:
+            run_batch(args, local)
         return
 
     import torch

@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("FUSEKIT_CUDA_LIB") or os.path.join(_HERE, "libfusekit
 
 (TASK_STEP_INIT, TASK_EMBED_LOOKUP_DECODE, TASK_RMSNORM_QKV, TASK_QK_NORM_ROPE_STORE, TASK_SDPA_DECODE,
  TASK_LINEAR_RESIDUAL, TASK_RMSNORM_GATEUP_ACT, TASK_FINAL_RMSNORM_LM_HEAD, TASK_ARGMAX_FINALIZE,
- TASK_ALLREDUCE, TASK_RESIDUAL_ADD) = range(11)
+ TASK_ALLREDUCE, TASK_RESIDUAL_ADD, TASK_RMSNORM_ROWS, TASK_ROPE_STORE_ROWS, TASK_ARGMAX_ROWS) = range(14)
 ACT_SWIGLU, ACT_GEGLU_TANH = 0, 1
 
 
@@ -73,6 +73,7 @@ def lib():
         "fk_step": [u64, u64, u32, u32, P(u32), P(C.c_double)],
         "fk_decode_chunk": [u64, u64, u32, u32, i32, vp, P(C.c_double)],
         "fk_decode_chunk_host": [u64, u64, u32, u32, i32, vp, P(C.c_double)],
+        "fk_decode_chunk_rows": [u64, u64, u32, vp, i32, i32, vp, P(C.c_double)],
         "fk_debug_timeline": [u64, u64],
         "fk_sdpa_decode_noalloc": [vp, vp, vp, vp, i32, i32, i32, i32, u32, f32, vp], "fk_comm_unique_id": [vp, sz], "fk_comm_init": [u64, vp, i32, i32],
     }

@@ -280,6 +280,7 @@ struct SdpaArgs {
     const uint16_t *q, *ck, *cv; uint16_t *out; float *part; uint32_t *counter;
     int n_q, n_kv, hd, capacity, chunk; float scale; unsigned long long *tl;
     int pos_override;       // >= 0: decode position given by the caller instead of the device-resident state
+    int rows;               // > 1: independent sequences (grid.z), each with its own q / out row and its own cache [n_kv, capacity, hd]
 };
 __device__ __forceinline__ void sd_stamp(unsigned long long *tl, int slot) {
     if (tl && threadIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tl[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = t; }
@@ -655,7 +656,9 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
     const int kv_len = (int)min(pos + 1u, (uint32_t)a.capacity);
     const int kpc = ((kv_len + CL * FK_SDPA_MK - 1) / (CL * FK_SDPA_MK)) * FK_SDPA_MK;
     const int k_begin = rank * kpc, k_end = min(kv_len, k_begin + kpc);
-    const uint16_t *K = a.ck + (size_t)kvh * a.capacity * HD, *V = a.cv + (size_t)kvh * a.capacity * HD;
+    const size_t seq = blockIdx.z;               // sequence of a batch: its own q row, output row and cache
+    a.q += seq * (size_t)a.n_q * HD; a.out += seq * (size_t)a.n_q * HD;
+    const uint16_t *K = a.ck + (seq * a.n_kv + kvh) * (size_t)a.capacity * HD, *V = a.cv + (seq * a.n_kv + kvh) * (size_t)a.capacity * HD;
     if (tid == 0 && k_begin < k_end) {           // every row but the newest predates the QKV kernel in flight: warm L2 meanwhile
         const uint32_t bytes = (uint32_t)(k_end - k_begin) * HD * 2;
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(K + (size_t)k_begin * HD), "r"(bytes) : "memory");
@@ -987,6 +990,67 @@ __global__ void k_residual_add(const float *sum, const uint16_t *residual, uint1
     pdl_wait(); pdl_launch_dependents();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) y[i] = f2bf(sum[i] + (residual ? bf2f(residual[i]) : 0.0f));
+}
+
+// ---------------------------------------------------------------- several independent sequences per step (batch decode)
+// The reference never batches independent sequences (python/fusekit_runtime/dispatch.py:2268-2289): its M > 1 kernels serve
+// consecutive positions of one sequence.  Here row m of every tensor belongs to sequence m, all sequences sit at the same
+// position, and each has its own KV cache; the result of row m is what the one-row path gives for that sequence alone.
+struct NormRowsArgs { const uint16_t *x, *w; uint16_t *y; int h, rows; float eps; };
+// y[m, :] = T(w * T(x[m, :] * r_m)), r_m = 1 / sqrt(mean(x[m]^2) + eps): the two roundings of the fused kernels
+// (src/codegen/kernels/mod.rs:4464-4472), one block per row
+__global__ void __launch_bounds__(256) k_rmsnorm_rows(const FkState *st, NormRowsArgs a) {
+    __shared__ float red[40];
+    pdl_wait(); pdl_launch_dependents();
+    const uint16_t *x = a.x + (size_t)blockIdx.x * a.h; uint16_t *y = a.y + (size_t)blockIdx.x * a.h;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < a.h; i += blockDim.x) { const float v = bf2f(__ldcg(x + i)); ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.h), a.eps)));
+    for (int i = threadIdx.x; i < a.h; i += blockDim.x) y[i] = f2bf(bf2f(a.w[i]) * rT(bf2f(__ldcg(x + i)) * r));
+}
+struct RopeRowsArgs { const uint16_t *qkv; uint16_t *q_out, *cache_k, *cache_v; int n_q, n_kv, hd, capacity, rows; float log2theta; };
+// RoPE on the q and k heads of every sequence's raw projection row (q | k | v, bias already added), k and v into that
+// sequence's cache row of the current position (src/codegen/kernels/rmsnorm_qkv.rs:635-697): block (head, sequence)
+__global__ void k_rope_store_rows(const FkState *st, RopeRowsArgs a) {
+    pdl_wait(); pdl_launch_dependents();
+    const int head = blockIdx.x, m = blockIdx.y, d = threadIdx.x, half = a.hd >> 1;
+    const uint32_t pos = st->offset; const int wrow = (int)(pos % (uint32_t)a.capacity);
+    const int nrow = (a.n_q + 2 * a.n_kv) * a.hd;
+    const uint16_t *src = a.qkv + (size_t)m * nrow + (size_t)head * a.hd;
+    if (d >= half) return;
+    if (head < a.n_q + a.n_kv) {
+        uint16_t o0, o1; rope_pair(bf2f(src[d]), bf2f(src[d + half]), d, half, pos, a.log2theta, &o0, &o1);
+        uint16_t *dst = head < a.n_q ? a.q_out + ((size_t)m * a.n_q + head) * a.hd
+                                     : a.cache_k + (((size_t)m * a.n_kv + (head - a.n_q)) * a.capacity + wrow) * a.hd;
+        dst[d] = o0; dst[d + half] = o1;
+    } else {
+        uint16_t *dst = a.cache_v + (((size_t)m * a.n_kv + (head - a.n_q - a.n_kv)) * a.capacity + wrow) * a.hd;
+        dst[d] = src[d]; dst[d + half] = src[d + half];
+    }
+}
+struct ArgmaxRowsArgs { const uint16_t *logits; uint32_t *counter, *history; int v, rows; };
+// greedy token of every sequence from its T-rounded logits, ties to the lowest index (argmax_logits_scan.rs:83-124); the
+// block that finishes last advances the shared position.  history[step * rows + m] receives sequence m's token.
+__global__ void __launch_bounds__(1024) k_argmax_rows(FkState *st, ArgmaxRowsArgs a) {
+    __shared__ unsigned long long wbest[32];
+    pdl_wait(); pdl_launch_dependents();
+    const int m = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const uint16_t *lg = a.logits + (size_t)m * a.v;
+    unsigned long long best = 0ull;
+    for (int i = threadIdx.x; i < a.v; i += blockDim.x) { const unsigned long long key = argmax_key(__ldcg(lg + i), (uint32_t)i); best = key > best ? key : best; }
+    best = warp_max_u64(best);
+    if (lane == 0) wbest[wid] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < (int)(blockDim.x >> 5); ++i) best = wbest[i] > best ? wbest[i] : best;
+        const uint32_t next = 0xffffffffu - (uint32_t)(best & 0xffffffffull);
+        st->token[m] = next;
+        const uint32_t step = st->hist_counter;
+        if (a.history && (step + 1) * (uint32_t)a.rows <= st->hist_cap) a.history[step * a.rows + m] = next;
+        __threadfence();
+        if (atomicAdd(a.counter, 1u) == (uint32_t)a.rows - 1u) { *a.counter = 0u; st->hist_counter = step + 1; st->offset += 1; st->epoch += 1; }
+    }
 }
 
 // smoke kernel: out = T(float(a) + float(b)) (metal/elementwise.metal:11-20 elementwise_add_bf16)

@@ -7,6 +7,7 @@
 #include "fk_synth.cuh"
 #include "fk_stream.cuh"
 #include "fk_qmm.cuh"
+#include "fk_qmm_tc.cuh"
 
 #include <dlfcn.h>
 #include <math.h>
@@ -79,7 +80,7 @@ struct Ctx {
     std::vector<Weight> weights; std::vector<Graph> graphs; std::vector<void *> allocs;
     bool pending = false; bool pdl = true; int sm_count = 148;
     float *qmm_scratch = nullptr; unsigned int *qmm_counters = nullptr;   // K-split partial sums and tickets of the several-row projection
-    bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; int force_split = -1; int wide_upto = 3; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_cl = 0;
+    bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; int force_split = -1; bool qmm_tc = false; int wide_upto = 3; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_cl = 0;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
@@ -135,6 +136,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     e = getenv("FK_SDPA_CL"); if (e && (atoi(e) == 1 || atoi(e) == 2 || atoi(e) == 4 || atoi(e) == 8 || atoi(e) == 16)) c->sdpa_cl = atoi(e);      // CTAs per kv head of the tensor-core attention
     e = getenv("FK_WARPS"); if (e) c->force_warps = atoi(e);
     e = getenv("FK_WIDE_UPTO"); if (e) c->wide_upto = atoi(e);      // 16-warp blocks for weights of up to this many tiles per warp of the machine
+    e = getenv("FK_QMM_TC"); if (e && e[0] == '1') c->qmm_tc = true;     // several-row projections on tcgen05 by default
     e = getenv("FK_SPLIT"); if (e) c->force_split = atoi(e);        // log2 of the warps sharing a row tile (tuning)
 #define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>)); CU(big_smem(K<16, 8>)); CU(big_smem(K<16, 16>))
 #define BIG4P(K) CU(big_smem(K<4, 8, true>)); CU(big_smem(K<4, 16, true>)); CU(big_smem(K<8, 8, true>)); CU(big_smem(K<8, 16, true>)); CU(big_smem(K<16, 8, true>)); CU(big_smem(K<16, 16, true>))
@@ -143,7 +145,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     CU(cudaFuncSetAttribute(k_sdpa_mma<64>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     CU(cudaFuncSetAttribute(k_sdpa_mma<128>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     CU(cudaFuncSetAttribute(k_sdpa_mma<256>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-    CU(big_smem(k_qmm4<false>)); CU(big_smem(k_qmm4<true>));
+    CU(big_smem(k_qmm4<false>)); CU(big_smem(k_qmm4<true>)); CU(big_smem(k_qmm_tc<16>)); CU(big_smem(k_qmm_tc<32>));
     CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
     CU(big_smem(k_linear_residual<4>)); CU(big_smem(k_linear_residual<8>)); CU(big_smem(k_linear_residual<16>));
@@ -187,7 +189,8 @@ extern "C" fk_status fk_info(fk_handle h, char *buf, size_t cap) {
 static const char *kKernelNames[FK_TASK_KIND_COUNT] = {
     "fusekit_step_init", "fusekit_embed_lookup_decode", "fusekit_rmsnorm_qkv", "fusekit_qk_norm_rope_store",
     "fusekit_sdpa_decode", "fusekit_linear_residual", "fusekit_rmsnorm_gateup_act", "fusekit_final_rmsnorm_lm_head",
-    "fusekit_argmax_finalize", "fusekit_allreduce", "fusekit_residual_add"};
+    "fusekit_argmax_finalize", "fusekit_allreduce", "fusekit_residual_add", "fusekit_rmsnorm_rows", "fusekit_rope_store_rows",
+    "fusekit_argmax_rows"};
 extern "C" fk_status fk_kernel_names(char *buf, size_t cap) {
     if (!buf || cap == 0) return fail(FK_ERR_VALUE, "buf is null");
     std::string s;
@@ -576,6 +579,17 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         SdpaArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], (uint32_t *)b[5],
                    nq, nkv, hd, cap, chunks, f[0], c->timeline ? c->timeline + (size_t)c->timeline_task * 512 * 8 : nullptr, -1};
         const int variant = i[4];      // 0 = by shape, 1 = FMA cluster kernel, 2 = global-partials kernel, 4 = tensor-core cluster kernel
+        if (i[5] > 1) {                // several sequences, each with its own cache: the tensor-core cluster kernel with the batch on grid.z
+            if (i[5] > FK_MAX_ROWS || G > 8) return fail(FK_ERR_VALUE, "sdpa: at most %d sequences", FK_MAX_ROWS);
+            a.rows = i[5];
+            const size_t smem = sdpa_mma_smem_bytes(G, hd);
+            const int cl = c->sdpa_cl > 0 ? c->sdpa_cl : FK_SDPA_CL;
+            const dim3 cgrid(cl, nkv, i[5]), cblock(FK_SDPA_CW * 32);
+            if (hd == 64) e = launch_cluster(c, k_sdpa_mma<64>, cgrid, cblock, smem, cl, (const FkState *)c->state, a);
+            else if (hd == 128) e = launch_cluster(c, k_sdpa_mma<128>, cgrid, cblock, smem, cl, (const FkState *)c->state, a);
+            else e = launch_cluster(c, k_sdpa_mma<256>, cgrid, cblock, smem, cl, (const FkState *)c->state, a);
+            break;
+        }
         // tensor-core cluster kernel: the default up to head_dim 128; at 256 (two q heads per kv head in the Gemma shape)
         // the FMA kernel below is faster (11.0 against 12.1 us), so it runs only when asked for
         if (G <= 8 && (variant == 4 || (variant == 0 && hd <= 128 && c->sdpa_mma && c->sdpa_cluster))) {
@@ -607,9 +621,17 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (!w || !w->finalized) return fail(FK_ERR_VALUE, "linear_residual: weight missing or not finalized");
         if (w->k != i[0] || w->n != i[1] || !b[0] || (!b[3] && !b[4] && i[3] <= 0)) return fail(FK_ERR_VALUE, "linear_residual: shape mismatch");
         if (i[2] > 1) {                                    // 2..16 activation rows: the quantised matrix product
-            if (i[2] > FK_QMM_MAXM) return fail(FK_ERR_VALUE, "linear_residual: at most %d activation rows", FK_QMM_MAXM);
             if (!w->tiled || w->bits != 4 || w->rows_kind != FK_ROWS_PLAIN || !b[3] || b[4])
                 return fail(FK_ERR_VALUE, "linear_residual with several rows takes streamed 4-bit weights in plain row order and a T output");
+            if (i[5] == 1 || (i[5] == 0 && c->qmm_tc)) {          // the tcgen05 form (i5: 1 = ask for it, 2 = ask for the mma.sync form)
+                if (i[2] > FK_TC_MAXM) return fail(FK_ERR_VALUE, "linear_residual: the tcgen05 form takes at most %d activation rows", FK_TC_MAXM);
+                QmmTcArgs ta{(const uint16_t *)b[0], w->tview(), (const uint16_t *)b[2], (uint16_t *)b[3], i[2], i[0], i[1]};
+                const dim3 tgrid((unsigned)((w->ntiles + 7) / 8)), tblock(FK_TC_THREADS);
+                if (i[2] <= 16) e = launch(c, k_qmm_tc<16>, tgrid, tblock, qmm_tc_smem_bytes(), c->state, ta);
+                else e = launch(c, k_qmm_tc<32>, tgrid, tblock, qmm_tc_smem_bytes(), c->state, ta);
+                break;
+            }
+            if (i[2] > FK_QMM_MAXM) return fail(FK_ERR_VALUE, "linear_residual: at most %d activation rows", FK_QMM_MAXM);
             QmmArgs qa{(const uint16_t *)b[0], w->tview(), (const uint16_t *)b[2], (uint16_t *)b[3], c->qmm_scratch, c->qmm_counters,
                        i[2], i[0], i[1], 1, nullptr, 0.0f, 0};
             e = launch_qmm(c, w, qa, false);
@@ -704,6 +726,26 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
     case FK_TASK_RESIDUAL_ADD: {
         if (!b[0] || !b[2] || i[0] <= 0) return fail(FK_ERR_VALUE, "residual_add: bad arguments");
         e = launch(c, k_residual_add, dim3((i[0] + 255) / 256), dim3(256), 0, (const float *)b[0], (const uint16_t *)b[1], (uint16_t *)b[2], i[0]);
+        break;
+    }
+    case FK_TASK_RMSNORM_ROWS: {
+        if (!b[0] || !b[1] || !b[2] || i[0] <= 0 || i[1] <= 0 || i[1] > FK_MAX_ROWS) return fail(FK_ERR_VALUE, "rmsnorm_rows: bad arguments");
+        NormRowsArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], (uint16_t *)b[2], i[0], i[1], f[0]};
+        e = launch(c, k_rmsnorm_rows, dim3(i[1]), dim3(256), 0, (const FkState *)c->state, a);
+        break;
+    }
+    case FK_TASK_ROPE_STORE_ROWS: {
+        const int nq = i[0], nkv = i[1], hd = i[2], cap = i[3], rows = i[4];
+        if (!b[0] || !b[1] || !b[5] || !b[6] || nq <= 0 || nkv <= 0 || hd <= 0 || (hd & 1) || hd > 2048 || cap <= 0 || rows <= 0 || rows > FK_MAX_ROWS)
+            return fail(FK_ERR_VALUE, "rope_store_rows: bad arguments");
+        RopeRowsArgs a{(const uint16_t *)b[0], (uint16_t *)b[1], (uint16_t *)b[5], (uint16_t *)b[6], nq, nkv, hd, cap, rows, (float)log2((double)f[1])};
+        e = launch(c, k_rope_store_rows, dim3(nq + 2 * nkv, rows), dim3((hd / 2 + 31) / 32 * 32), 0, (const FkState *)c->state, a);
+        break;
+    }
+    case FK_TASK_ARGMAX_ROWS: {
+        if (!b[0] || !b[5] || i[0] <= 0 || i[1] <= 0 || i[1] > FK_MAX_ROWS) return fail(FK_ERR_VALUE, "argmax_rows: bad arguments");
+        ArgmaxRowsArgs a{(const uint16_t *)b[0], (uint32_t *)b[5], c->history, i[0], i[1]};
+        e = launch(c, k_argmax_rows, dim3(i[1]), dim3(1024), 0, c->state, a);
         break;
     }
     default: return fail(FK_ERR_VALUE, "unknown task kind %d", t.kind);
@@ -889,6 +931,35 @@ extern "C" fk_status fk_decode_chunk(fk_handle h, fk_graph gid, uint32_t base_of
     float ms = 0.0f; CU(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
     if (gpu_seconds) *gpu_seconds = ms * 1e-3;
     if (out_history) memcpy(out_history, hist, sizeof(uint32_t) * count);
+    const FkState *st = (const FkState *)(c->pinned + 32);
+    if (st->error) return fail(FK_ERR_DEVICE, "device error word 0x%x", st->error);
+    return FK_OK;
+}
+// `rows` independent sequences at one position: the graph holds the batch tasks, sequence m starts from seed_tokens[m];
+// out_history[step * rows + m] is the token sequence m produced at step `step`
+extern "C" fk_status fk_decode_chunk_rows(fk_handle h, fk_graph gid, uint32_t base_offset, const uint32_t *seed_tokens, int rows, int count,
+                                          uint32_t *out_history, double *gpu_seconds) {
+    CTX(h); Graph *g = get_g(c, gid);
+    if (!g) return fail(FK_ERR_VALUE, "bad graph id");
+    if (!seed_tokens || rows <= 0 || rows > FK_MAX_ROWS) return fail(FK_ERR_VALUE, "rows must be in 1..%d", FK_MAX_ROWS);
+    if (count <= 0 || (uint64_t)count * rows > c->hist_cap) return fail(FK_ERR_VALUE, "count * rows must be in 1..%u", c->hist_cap);
+    if (c->pending) return fail(FK_ERR_STATE, "a launch is pending; call fk_wait");
+    for (int m = 0; m < rows; ++m)
+        if (c->vocab && seed_tokens[m] >= c->vocab) return fail(FK_ERR_VALUE, "token id %u is outside the embedding table (%u rows)", seed_tokens[m], c->vocab);
+    FkState *s0 = (FkState *)c->pinned; memset(s0, 0, sizeof(FkState));
+    for (int m = 0; m < rows; ++m) s0->token[m] = seed_tokens[m];
+    s0->offset = base_offset; s0->hist_cap = c->hist_cap;
+    CU(cudaMemcpyAsync(c->state, s0, FK_STATE_SET_BYTES, cudaMemcpyHostToDevice, c->stream));
+    CU(cudaEventRecord(c->ev0, c->stream));
+    for (int j = 0; j < count; ++j) CU(cudaGraphLaunch(g->exec, c->stream));
+    CU(cudaEventRecord(c->ev1, c->stream));
+    uint32_t *hist = c->pinned + 64;
+    CU(cudaMemcpyAsync(hist, c->history, sizeof(uint32_t) * count * rows, cudaMemcpyDeviceToHost, c->stream));
+    CU(cudaMemcpyAsync(c->pinned + 32, c->state, sizeof(FkState), cudaMemcpyDeviceToHost, c->stream));
+    CU(cudaStreamSynchronize(c->stream));
+    float ms = 0.0f; CU(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+    if (gpu_seconds) *gpu_seconds = ms * 1e-3;
+    if (out_history) memcpy(out_history, hist, sizeof(uint32_t) * count * rows);
     const FkState *st = (const FkState *)(c->pinned + 32);
     if (st->error) return fail(FK_ERR_DEVICE, "device error word 0x%x", st->error);
     return FK_OK;

@@ -49,7 +49,11 @@ enum {
     FK_TASK_ARGMAX_FINALIZE = 8,       /* argmax_logits_finalize.rs:16-115 (+ history capture) */
     FK_TASK_ALLREDUCE = 9,             /* no reference counterpart: tensor-parallel sum over ranks */
     FK_TASK_RESIDUAL_ADD = 10,         /* no reference counterpart: y = T(sum + residual) after FK_TASK_ALLREDUCE */
-    FK_TASK_KIND_COUNT = 11
+    FK_TASK_RMSNORM_ROWS = 11,         /* batch of sequences: RMSNorm of every row (kernels/mod.rs:4464-4472 arithmetic; the reference
+                                          never batches independent sequences, python/fusekit_runtime/dispatch.py:2268-2289) */
+    FK_TASK_ROPE_STORE_ROWS = 12,      /* batch: RoPE on q / k and the cache store of every sequence (rmsnorm_qkv.rs:635-697) */
+    FK_TASK_ARGMAX_ROWS = 13,          /* batch: greedy token of every sequence + position advance (argmax_logits_scan.rs:83-124) */
+    FK_TASK_KIND_COUNT = 14
 };
 
 /* activation selector for FK_TASK_RMSNORM_GATEUP_ACT */
@@ -77,6 +81,7 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  * QK_NORM_ROPE_STORE   buf0 q(in/out)  buf1 k_in  buf2 v_in  buf3 q_norm_w  buf4 k_norm_w  buf5 cache_k  buf6 cache_v
  *                      i0 n_q  i1 n_kv  i2 head_dim  i3 capacity   f0 eps  f1 rope_theta
  * SDPA_DECODE          buf0 q  buf1 cache_k  buf2 cache_v  buf3 out  buf4 partials(f32)  buf5 counter(u32)
+ *                      i5 sequences M (0 / 1: one)
  *                      i0 n_q  i1 n_kv  i2 head_dim  i3 capacity  i4 kernel choice (0 = by shape and capacity, 1 = cluster,
  *                      2 = global partials + ticket, 4 = tensor-core cluster)   f0 scale
  *                      partials: n_q * ceil(capacity / 32) * (head_dim + 2) floats; counter: n_kv words, zero before first use
@@ -89,6 +94,7 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      publishes a flag; buf3 / buf4 may then be 0.  The norm-first task that follows names the same site as
  *                      its pull site, waits (bounded) for all ranks and sums in rank order.  Sites are numbered from 0 in task
  *                      order, at most 160, each written once per token
+ *                      i5 kernel of the M > 1 form: 0 = default, 1 = tcgen05 (M <= 32), 2 = mma.sync (M <= 16)
  * RMSNORM_GATEUP_ACT   buf0 x  buf1 norm_w  buf2 weight(gate)  buf3 weight(up)  buf4 act_out T[I]
  *                      buf9..11 pending (as RMSNORM_QKV)     i0 H  i1 I  i2 act   f0 eps
  *                      i3 activation rows M (0 or 1: one row).  M = 2..16: x is T[M, H], act_out is T[M, I], every row normalised
@@ -101,6 +107,13 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  * ARGMAX_FINALIZE      buf4 argmax scratch  i0 entries
  * ALLREDUCE            buf0 f32 buffer   i0 count
  * RESIDUAL_ADD         buf0 sum f32[N]  buf1 residual T[N]  buf2 y_out T[N]   i0 N
+ * RMSNORM_ROWS         buf0 x T[M,H]  buf1 norm_w T[H]  buf2 y_out T[M,H]   i0 H  i1 M   f0 eps
+ * ROPE_STORE_ROWS      buf0 qkv T[M,(n_q+2n_kv)*hd] (bias added)  buf1 q_out T[M,n_q*hd]  buf5 cache_k  buf6 cache_v
+ *                      (caches [M, n_kv, capacity, hd])   i0 n_q  i1 n_kv  i2 head_dim  i3 capacity  i4 M   f1 rope_theta
+ * ARGMAX_ROWS          buf0 logits T[M,V]  buf5 counter(u32, zero before first use)   i0 V  i1 M
+ *                      token[m] of the decode state and history[step * M + m] receive sequence m's token
+ * Batch decode (M = 2..16 independent sequences at one position): EMBED with i1 = M, LINEAR_RESIDUAL / RMSNORM_GATEUP_ACT
+ * with their row counts, SDPA_DECODE with i5 = M (q and out T[M, n_q*hd], caches [M, n_kv, capacity, hd]).
  */
 typedef struct fk_task {
     int32_t  kind;
@@ -187,6 +200,10 @@ fk_status fk_step(fk_handle h, fk_graph g, uint32_t token, uint32_t offset, uint
  * (decode_chunk_gpu_chain, lib.rs:1275-1420) */
 fk_status fk_decode_chunk(fk_handle h, fk_graph g, uint32_t base_offset, uint32_t seed_token, int count,
                           uint32_t *out_history, double *gpu_seconds);
+/* `rows` independent sequences decoded together (a graph of the batch tasks): sequence m starts from seed_tokens[m], all at
+ * base_offset; out_history[step * rows + m].  No reference counterpart (its M > 1 means positions of one sequence). */
+fk_status fk_decode_chunk_rows(fk_handle h, fk_graph g, uint32_t base_offset, const uint32_t *seed_tokens, int rows, int count,
+                               uint32_t *out_history, double *gpu_seconds);
 /* same result with a host round trip per token (decode_chunk_host_loop, lib.rs:1129-1257) */
 fk_status fk_decode_chunk_host(fk_handle h, fk_graph g, uint32_t base_offset, uint32_t seed_token, int count,
                                uint32_t *out_history, double *gpu_seconds);

@@ -116,6 +116,24 @@ def test_linear_residual_rows(runtime, m, k, n, residual):
     assert runtime.state_get()[2] == 0
 
 
+@pytest.mark.parametrize("m", [2, 8, 16, 17, 32])
+@pytest.mark.parametrize("k,n", [(896, 1152), (896, 100), (4864, 896), (3584, 4736), (64, 8), (320, 1088)])
+@pytest.mark.parametrize("residual", [False, True])
+def test_linear_residual_rows_tcgen05(runtime, m, k, n, residual):
+    """The same product on the 5th-generation tensor cores (weight rows on the MMA's M axis, activation rows on N,
+    accumulators in tensor memory): up to 32 rows, each equal to the one-row task's result."""
+    w = O.gen_weight(stream_id(1, f"qmm.{k}.{n}"), n, k, 4)
+    x, res = normal(f"qx{k}.{m}", m * k).reshape(m, k), normal(f"qr{n}.{m}", m * n).reshape(m, n)
+    want = np.stack([O.qmatvec(w, x[i], res[i] if residual else None) for i in range(m)])
+    xd, yd = runtime.to_device(x), runtime.alloc(m * n * 2)
+    rd = runtime.to_device(res) if residual else 0
+    runtime.launch(T(N.TASK_LINEAR_RESIDUAL, 0, {0: xd, 1: dev_weight(runtime, w), 2: rd, 3: yd}, [k, n, m, 0, 0, 1]))
+    got = runtime.download(yd, (m, n), np.uint16)
+    for i in range(m):
+        assert_close_bf16(got[i], want[i], f"tcgen05 qmm row {i}/{m} {k}->{n}")
+    assert runtime.state_get()[2] == 0
+
+
 @pytest.mark.parametrize("m", [2, 7, 16])
 @pytest.mark.parametrize("act", [0, 1])
 @pytest.mark.parametrize("h,inter", [(896, 4864), (256, 100), (3584, 1024), (512, 19200)])
