@@ -23,7 +23,10 @@ from .runtime import Runtime
 
 
 class BatchDecodeEngine:
-    def __init__(self, spec: ModelSpec, capacity: int, rows: int, device: int = 0, runtime: Runtime | None = None, qmm: int = 0):
+    consecutive = False          # rows are independent sequences; PrefillEngine makes them consecutive positions of one
+
+    def __init__(self, spec: ModelSpec, capacity: int, rows: int, device: int = 0, runtime: Runtime | None = None, qmm: int = 0,
+                 caches=None):
         if spec.arch != "qwen2" or spec.bits != 4:
             raise ValueError("batch decode is wired for Qwen-shaped layers with 4-bit weights")
         if not 2 <= rows <= 16:
@@ -45,8 +48,11 @@ class BatchDecodeEngine:
         chunks = (capacity + 31) // 32
         self.sdpa_part, self.sdpa_counter = rt.alloc(64), rt.alloc(64)      # unused by the cluster kernel, required by the task
         self.cache = []
-        for _ in range(L):
-            n = M * s.n_kv * capacity * hd * 2
+        for l in range(L):
+            if caches is not None:              # caches owned by another engine on the same runtime: (k, v, ...) per layer
+                self.cache.append((caches[l][0], caches[l][1]))
+                continue
+            n = (1 if self.consecutive else M) * s.n_kv * capacity * hd * 2
             self.cache.append((rt.alloc(n), rt.alloc(n)))
         self.W: dict[str, int] = {}
         self.V: dict[str, int] = {}
@@ -124,9 +130,9 @@ class BatchDecodeEngine:
                 T(N.TASK_RMSNORM_ROWS, l, {0: self.x_ptr(l), 1: self.V[f"layers.{l}.input_norm"], 2: self.xn}, [H, M], [s.eps]),
                 T(N.TASK_LINEAR_RESIDUAL, l, {0: self.xn, 1: self.W[f"layers.{l}.qkv"], 2: self.V[f"layers.{l}.qkv_bias_rows"], 3: self.qkv},
                   [H, self.nqkv, M, 0, 0, q]),
-                T(N.TASK_ROPE_STORE_ROWS, l, {0: self.qkv, 1: self.q, 5: ck, 6: cv}, [s.n_q, s.n_kv, hd, self.capacity, M], [0.0, s.theta]),
+                T(N.TASK_ROPE_STORE_ROWS, l, {0: self.qkv, 1: self.q, 5: ck, 6: cv}, [s.n_q, s.n_kv, hd, self.capacity, M, int(self.consecutive)], [0.0, s.theta]),
                 T(N.TASK_SDPA_DECODE, l, {0: self.q, 1: ck, 2: cv, 3: self.sdpa, 4: self.sdpa_part, 5: self.sdpa_counter},
-                  [s.n_q, s.n_kv, hd, self.capacity, 0, M], [scale]),
+                  [s.n_q, s.n_kv, hd, self.capacity, 0, M, int(self.consecutive)], [scale]),
                 T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa, 1: self.W[f"layers.{l}.o"], 2: self.x_ptr(l), 3: self.hb_ptr(l)}, [s.n_q * hd, H, M, 0, 0, q]),
                 T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: self.hb_ptr(l), 1: self.V[f"layers.{l}.post_attention_norm"], 2: self.W[f"layers.{l}.gateup"],
                                                   4: self.act}, [H, I, 0, M], [s.eps]),
@@ -136,7 +142,7 @@ class BatchDecodeEngine:
         tasks += [
             T(N.TASK_RMSNORM_ROWS, -1, {0: self.x_ptr(L), 1: self.V["final_norm"], 2: self.xn}, [H, M], [s.eps]),
             T(N.TASK_LINEAR_RESIDUAL, -1, {0: self.xn, 1: self.W["lm_head"], 3: self.logits}, [H, s.vocab, M, 0, 0, q]),
-            T(N.TASK_ARGMAX_ROWS, -1, {0: self.logits, 5: self.counter}, [s.vocab, M]),
+            T(N.TASK_ARGMAX_ROWS, -1, {0: self.logits, 5: self.counter}, [s.vocab, M, M if self.consecutive else 1]),
         ]
         return tasks
 
@@ -169,3 +175,29 @@ class BatchDecodeEngine:
 
     def close(self):
         self.rt.close()
+
+
+class PrefillEngine(BatchDecodeEngine):
+    """Chunked prefill (and verify rows): the M rows of a step are M consecutive positions of ONE sequence.
+
+    Reference: the prefill path keeps its M > 1 trace shapes for prompt chunks and speculative verify rows
+    (src/commands/patch.rs:112-152, python/fusekit_runtime/__init__.py:2535-2592, 2825-2850).  Row m of a chunk sits at
+    position offset + m, its K/V rows go into the one shared cache before attention, and it attends keys 0 .. offset + m
+    (causal); every row's greedy prediction comes back, so the same step serves prompt ingestion (the last row's prediction
+    is the first generated token) and the verification of M drafted tokens.  Pass `caches` (and `runtime`) of a DecodeEngine
+    to fill the caches that engine then decodes from."""
+    consecutive = True
+
+    def prefill(self, tokens, base_offset: int = 0):
+        """Run `tokens` through the model in chunks of `rows` positions starting at `base_offset`; returns the greedy
+        prediction after every position, [len(tokens)].  A last partial chunk is padded with token 0: the padded rows write
+        cache rows beyond the prompt, which later positions overwrite before anything attends them."""
+        toks = [int(t) for t in tokens]
+        M, preds = self.rows, []
+        for c0 in range(0, len(toks), M):
+            chunk = toks[c0:c0 + M]
+            if base_offset + c0 + M > self.capacity:
+                raise ValueError("prefill chunk reaches beyond the cache capacity")
+            out, _ = self.decode_chunk(base_offset + c0, np.array(chunk + [0] * (M - len(chunk)), np.uint32), 1)
+            preds.extend(int(t) for t in out[0][:len(chunk)])
+        return np.array(preds, np.uint32)

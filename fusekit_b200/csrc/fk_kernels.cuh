@@ -281,6 +281,8 @@ struct SdpaArgs {
     int n_q, n_kv, hd, capacity, chunk; float scale; unsigned long long *tl;
     int pos_override;       // >= 0: decode position given by the caller instead of the device-resident state
     int rows;               // > 1: independent sequences (grid.z), each with its own q / out row and its own cache [n_kv, capacity, hd]
+    int consecutive;        // with rows > 1: the rows are consecutive positions of ONE sequence (prefill chunk / verify rows): row m
+                            // sits at position offset + m and attends the shared cache up to and including its own row
 };
 __device__ __forceinline__ void sd_stamp(unsigned long long *tl, int slot) {
     if (tl && threadIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tl[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = t; }
@@ -652,12 +654,12 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
     sd_stamp(a.tl, 0);
     pdl_launch_dependents();
     auto started = cluster.barrier_arrive();     // waited for before the first remote store: every CTA of the cluster is running by then
-    const uint32_t pos = a.pos_override >= 0 ? (uint32_t)a.pos_override : st->offset;
+    const uint32_t pos = (a.pos_override >= 0 ? (uint32_t)a.pos_override : st->offset) + (a.consecutive ? blockIdx.z : 0u);
     const int kv_len = (int)min(pos + 1u, (uint32_t)a.capacity);
     const int kpc = ((kv_len + CL * FK_SDPA_MK - 1) / (CL * FK_SDPA_MK)) * FK_SDPA_MK;
     const int k_begin = rank * kpc, k_end = min(kv_len, k_begin + kpc);
-    const size_t seq = blockIdx.z;               // sequence of a batch: its own q row, output row and cache
-    a.q += seq * (size_t)a.n_q * HD; a.out += seq * (size_t)a.n_q * HD;
+    const size_t row = blockIdx.z, seq = a.consecutive ? 0 : row;     // row of a batch: its own q and output; sequence: its own cache
+    a.q += row * (size_t)a.n_q * HD; a.out += row * (size_t)a.n_q * HD;
     const uint16_t *K = a.ck + (seq * a.n_kv + kvh) * (size_t)a.capacity * HD, *V = a.cv + (seq * a.n_kv + kvh) * (size_t)a.capacity * HD;
     if (tid == 0 && k_begin < k_end) {           // every row but the newest predates the QKV kernel in flight: warm L2 meanwhile
         const uint32_t bytes = (uint32_t)(k_end - k_begin) * HD * 2;
@@ -687,7 +689,7 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
     // decoded was written by earlier tokens.  The block that holds that newest row is fetched again after the wait.
     const int kb0 = k_begin + wid * FK_SDPA_MK;
     const int newest = (int)(pos % (uint32_t)a.capacity);
-    const bool pre = QREG && kb0 < k_end;
+    const bool pre = QREG && kb0 < k_end && !a.consecutive;      // several new rows in one cache: nothing is fetched early
     if (pre) { load_v_tile(kb0); load_k(kb0, 0, 0); load_k(kb0, 1, NKR - 1); }
     pdl_wait();
     if (pre && newest >= kb0 && newest < kb0 + FK_SDPA_MK) { load_v_tile(kb0); load_k(kb0, 0, 0); load_k(kb0, 1, NKR - 1); }
@@ -1009,27 +1011,29 @@ __global__ void __launch_bounds__(256) k_rmsnorm_rows(const FkState *st, NormRow
     const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.h), a.eps)));
     for (int i = threadIdx.x; i < a.h; i += blockDim.x) y[i] = f2bf(bf2f(a.w[i]) * rT(bf2f(__ldcg(x + i)) * r));
 }
-struct RopeRowsArgs { const uint16_t *qkv; uint16_t *q_out, *cache_k, *cache_v; int n_q, n_kv, hd, capacity, rows; float log2theta; };
+struct RopeRowsArgs { const uint16_t *qkv; uint16_t *q_out, *cache_k, *cache_v; int n_q, n_kv, hd, capacity, rows; float log2theta; int consecutive; };
 // RoPE on the q and k heads of every sequence's raw projection row (q | k | v, bias already added), k and v into that
 // sequence's cache row of the current position (src/codegen/kernels/rmsnorm_qkv.rs:635-697): block (head, sequence)
 __global__ void k_rope_store_rows(const FkState *st, RopeRowsArgs a) {
     pdl_wait(); pdl_launch_dependents();
     const int head = blockIdx.x, m = blockIdx.y, d = threadIdx.x, half = a.hd >> 1;
-    const uint32_t pos = st->offset; const int wrow = (int)(pos % (uint32_t)a.capacity);
+    // independent sequences share the position and have a cache each; consecutive rows of one sequence share the cache
+    const uint32_t pos = st->offset + (a.consecutive ? (uint32_t)m : 0u); const int wrow = (int)(pos % (uint32_t)a.capacity);
+    const size_t seq = a.consecutive ? 0 : (size_t)m;
     const int nrow = (a.n_q + 2 * a.n_kv) * a.hd;
     const uint16_t *src = a.qkv + (size_t)m * nrow + (size_t)head * a.hd;
     if (d >= half) return;
     if (head < a.n_q + a.n_kv) {
         uint16_t o0, o1; rope_pair(bf2f(src[d]), bf2f(src[d + half]), d, half, pos, a.log2theta, &o0, &o1);
         uint16_t *dst = head < a.n_q ? a.q_out + ((size_t)m * a.n_q + head) * a.hd
-                                     : a.cache_k + (((size_t)m * a.n_kv + (head - a.n_q)) * a.capacity + wrow) * a.hd;
+                                     : a.cache_k + ((seq * a.n_kv + (head - a.n_q)) * a.capacity + wrow) * a.hd;
         dst[d] = o0; dst[d + half] = o1;
     } else {
-        uint16_t *dst = a.cache_v + (((size_t)m * a.n_kv + (head - a.n_q - a.n_kv)) * a.capacity + wrow) * a.hd;
+        uint16_t *dst = a.cache_v + ((seq * a.n_kv + (head - a.n_q - a.n_kv)) * a.capacity + wrow) * a.hd;
         dst[d] = src[d]; dst[d + half] = src[d + half];
     }
 }
-struct ArgmaxRowsArgs { const uint16_t *logits; uint32_t *counter, *history; int v, rows; };
+struct ArgmaxRowsArgs { const uint16_t *logits; uint32_t *counter, *history; int v, rows, advance; };
 // greedy token of every sequence from its T-rounded logits, ties to the lowest index (argmax_logits_scan.rs:83-124); the
 // block that finishes last advances the shared position.  history[step * rows + m] receives sequence m's token.
 __global__ void __launch_bounds__(1024) k_argmax_rows(FkState *st, ArgmaxRowsArgs a) {
@@ -1049,7 +1053,7 @@ __global__ void __launch_bounds__(1024) k_argmax_rows(FkState *st, ArgmaxRowsArg
         const uint32_t step = st->hist_counter;
         if (a.history && (step + 1) * (uint32_t)a.rows <= st->hist_cap) a.history[step * a.rows + m] = next;
         __threadfence();
-        if (atomicAdd(a.counter, 1u) == (uint32_t)a.rows - 1u) { *a.counter = 0u; st->hist_counter = step + 1; st->offset += 1; st->epoch += 1; }
+        if (atomicAdd(a.counter, 1u) == (uint32_t)a.rows - 1u) { *a.counter = 0u; st->hist_counter = step + 1; st->offset += (uint32_t)a.advance; st->epoch += 1; }
     }
 }
 

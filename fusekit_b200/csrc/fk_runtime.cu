@@ -581,7 +581,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         const int variant = i[4];      // 0 = by shape, 1 = FMA cluster kernel, 2 = global-partials kernel, 4 = tensor-core cluster kernel
         if (i[5] > 1) {                // several sequences, each with its own cache: the tensor-core cluster kernel with the batch on grid.z
             if (i[5] > FK_MAX_ROWS || G > 8) return fail(FK_ERR_VALUE, "sdpa: at most %d sequences", FK_MAX_ROWS);
-            a.rows = i[5];
+            a.rows = i[5]; a.consecutive = i[6] ? 1 : 0;
             const size_t smem = sdpa_mma_smem_bytes(G, hd);
             const int cl = c->sdpa_cl > 0 ? c->sdpa_cl : FK_SDPA_CL;
             const dim3 cgrid(cl, nkv, i[5]), cblock(FK_SDPA_CW * 32);
@@ -738,13 +738,13 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         const int nq = i[0], nkv = i[1], hd = i[2], cap = i[3], rows = i[4];
         if (!b[0] || !b[1] || !b[5] || !b[6] || nq <= 0 || nkv <= 0 || hd <= 0 || (hd & 1) || hd > 2048 || cap <= 0 || rows <= 0 || rows > FK_MAX_ROWS)
             return fail(FK_ERR_VALUE, "rope_store_rows: bad arguments");
-        RopeRowsArgs a{(const uint16_t *)b[0], (uint16_t *)b[1], (uint16_t *)b[5], (uint16_t *)b[6], nq, nkv, hd, cap, rows, (float)log2((double)f[1])};
+        RopeRowsArgs a{(const uint16_t *)b[0], (uint16_t *)b[1], (uint16_t *)b[5], (uint16_t *)b[6], nq, nkv, hd, cap, rows, (float)log2((double)f[1]), i[5] ? 1 : 0};
         e = launch(c, k_rope_store_rows, dim3(nq + 2 * nkv, rows), dim3((hd / 2 + 31) / 32 * 32), 0, (const FkState *)c->state, a);
         break;
     }
     case FK_TASK_ARGMAX_ROWS: {
         if (!b[0] || !b[5] || i[0] <= 0 || i[1] <= 0 || i[1] > FK_MAX_ROWS) return fail(FK_ERR_VALUE, "argmax_rows: bad arguments");
-        ArgmaxRowsArgs a{(const uint16_t *)b[0], (uint32_t *)b[5], c->history, i[0], i[1]};
+        ArgmaxRowsArgs a{(const uint16_t *)b[0], (uint32_t *)b[5], c->history, i[0], i[1], i[2] > 0 ? i[2] : 1};
         e = launch(c, k_argmax_rows, dim3(i[1]), dim3(1024), 0, c->state, a);
         break;
     }

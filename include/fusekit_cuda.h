@@ -112,6 +112,11 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      (caches [M, n_kv, capacity, hd])   i0 n_q  i1 n_kv  i2 head_dim  i3 capacity  i4 M   f1 rope_theta
  * ARGMAX_ROWS          buf0 logits T[M,V]  buf5 counter(u32, zero before first use)   i0 V  i1 M
  *                      token[m] of the decode state and history[step * M + m] receive sequence m's token
+ *                      ROPE_STORE_ROWS i5 = 1, SDPA_DECODE i6 = 1: the M rows are consecutive positions offset .. offset + M - 1 of
+ *                      ONE sequence (a prefill chunk, or verify rows of speculative decoding; reference: the M > 1 trace
+ *                      shapes, python/fusekit_runtime/__init__.py:2825-2850, src/commands/patch.rs:112-152) sharing one cache
+ *                      [n_kv, capacity, hd]; row m attends keys 0 .. offset + m.  ARGMAX_ROWS i2: positions the step advances
+ *                      by (default 1; M for such a chunk)
  * Batch decode (M = 2..16 independent sequences at one position): EMBED with i1 = M, LINEAR_RESIDUAL / RMSNORM_GATEUP_ACT
  * with their row counts, SDPA_DECODE with i5 = M (q and out T[M, n_q*hd], caches [M, n_kv, capacity, hd]).
  */

@@ -3,7 +3,7 @@ python/fusekit_runtime/dispatch.py:2268-2289; each row is defined as what the on
 import numpy as np
 import pytest
 
-from fusekit_b200.batch import BatchDecodeEngine
+from fusekit_b200.batch import BatchDecodeEngine, PrefillEngine
 from fusekit_b200.model_spec import CONFIGS
 from oracle import oracle as O
 from tests.helpers import compare_greedy, oracle_config
@@ -53,3 +53,42 @@ def test_batch_engine_refuses_unsupported_models():
         BatchDecodeEngine(CONFIGS["tiny-qwen"].with_bits(8), 64, 4)
     with pytest.raises(ValueError):
         BatchDecodeEngine(CONFIGS["tiny-qwen"], 64, 17)
+
+
+@pytest.mark.parametrize("rows,qmm", [(8, 2), (16, 2), (5, 1)])
+def test_chunked_prefill_matches_the_oracle_stepping_the_prompt(rows, qmm):
+    """A 37-token prompt through the prefill engine in chunks of `rows` consecutive positions: the prediction after every
+    position equals the oracle's when it steps the same prompt token by token, the caches agree with the oracle's within the
+    stage tolerance, and the batch-1 engine decodes on from those caches."""
+    from fusekit_b200.model_spec import stream_id
+    from fusekit_b200.runtime import DecodeEngine
+    from tests.helpers import assert_close_bf16
+    spec, cap = CONFIGS["tiny-qwen"], 96
+    prompt = [O.uniform_u32(stream_id(spec.seed, "prompt"), i, spec.vocab) for i in range(37)]
+    m = O.Model(oracle_config(spec, cap))
+    want = [m.step(t, i)[0] for i, t in enumerate(prompt)]
+    dec = DecodeEngine(spec, cap)
+    try:
+        dec.load_synthetic()
+        pre = PrefillEngine(spec, cap, rows, runtime=dec.rt, qmm=qmm, caches=dec.cache)
+        pre.load_synthetic()
+        got = pre.prefill(prompt)
+        flips = [i for i in range(len(prompt)) if int(got[i]) != want[i]]
+        assert len(flips) <= 2, (flips, got, want)             # near-ties of the toy head; the caches below are the stronger check
+        hd = spec.head_dim
+        for l in range(spec.n_layers):
+            k = dec.rt.download(dec.cache[l][0], (spec.n_kv, cap, hd), np.uint16)[:, :len(prompt)]
+            v = dec.rt.download(dec.cache[l][1], (spec.n_kv, cap, hd), np.uint16)[:, :len(prompt)]
+            n = spec.n_kv * cap * hd
+            ok_, ov = m.vec(l, 7, n).reshape(spec.n_kv, cap, hd)[:, :len(prompt)], m.vec(l, 8, n).reshape(spec.n_kv, cap, hd)[:, :len(prompt)]
+            assert_close_bf16(k.reshape(-1), ok_.reshape(-1), f"cache_k layer {l}", rel_rms_tol=5e-3)
+            assert_close_bf16(v.reshape(-1), ov.reshape(-1), f"cache_v layer {l}", rel_rms_tol=5e-3)
+        # decode continues from the prefilled caches on the batch-1 engine
+        nxt, _ = dec.decode_chunk(len(prompt), int(got[-1]), 8)
+        m2 = O.Model(oracle_config(spec, cap))
+        for i, t in enumerate(prompt):
+            m2.step(t, i)
+        mism, ties = compare_greedy(nxt, m2, int(got[-1]), len(prompt), tie_ulps=4.0)
+        assert not mism and len(ties) <= 2, (mism, ties)
+    finally:
+        dec.close()
