@@ -14,7 +14,8 @@ LIB_PATH = os.environ.get("FUSEKIT_CUDA_LIB") or os.path.join(_HERE, "libfusekit
 
 (TASK_STEP_INIT, TASK_EMBED_LOOKUP_DECODE, TASK_RMSNORM_QKV, TASK_QK_NORM_ROPE_STORE, TASK_SDPA_DECODE,
  TASK_LINEAR_RESIDUAL, TASK_RMSNORM_GATEUP_ACT, TASK_FINAL_RMSNORM_LM_HEAD, TASK_ARGMAX_FINALIZE,
- TASK_ALLREDUCE, TASK_RESIDUAL_ADD, TASK_RMSNORM_ROWS, TASK_ROPE_STORE_ROWS, TASK_ARGMAX_ROWS) = range(14)
+ TASK_ALLREDUCE, TASK_RESIDUAL_ADD, TASK_RMSNORM_ROWS, TASK_ROPE_STORE_ROWS, TASK_ARGMAX_ROWS, TASK_KV_STORE_QUANT,
+ TASK_SDPA_DECODE_QUANT) = range(16)
 ACT_SWIGLU, ACT_GEGLU_TANH = 0, 1
 
 

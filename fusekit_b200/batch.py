@@ -2,7 +2,7 @@
 
 Benchmark configuration 5 asks for batch 16 on the 32B shape.  The reference has no counterpart -- its M > 1 kernels serve
 consecutive positions of one sequence (python/fusekit_runtime/dispatch.py:2268-2289) -- so row m of every tensor is defined
-as what the batch-1 path produces for sequence m alone, and that is what the tests check (M batch-1 oracle runs).
+as what the batch-1 path produces for sequence m alone, and that is what the tests check (M batch-1 runs of the CPU restatement).
 
 A step replays, per layer: RMSNorm of the M rows -> QKV projection of all rows (+bias) -> RoPE and the K/V store into each
 sequence's cache -> attention per sequence -> o_proj + residual -> norm-first gate/up + SwiGLU -> down_proj + residual; then

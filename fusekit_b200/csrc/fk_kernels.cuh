@@ -276,6 +276,67 @@ __global__ void k_qk_norm_rope_store(const FkState *st, QkNormArgs a) {
     if (!is_q && d < a.hd) a.cache_v[((size_t)kh * a.capacity + wrow) * a.hd + d] = a.v_in[kh * a.hd + d];
 }
 
+struct KvQuantArgs {
+    uint16_t *q; const uint16_t *k_in, *v_in; uint32_t *kp, *vp; uint16_t *ks, *kb, *vs, *vb;
+    int n_q, n_kv, hd, capacity, bits; float log2theta;
+};
+// RoPE + store into a quantised cache (src/codegen/kernels/rope_kv_cache_store_decode_quant.rs; the fused form
+// rmsnorm_qkv.rs:435-612): q heads are rotated and rounded to T in place; a k head is rotated in fp32 from its T-rounded
+// projection and quantised unrounded, a v head is quantised from its T values.  Per group of 64: min / max, the edge of
+// larger magnitude anchors the grid (negative scale when that is the maximum), q0 = round(edge / scale), scale = edge / q0
+// and bias = edge unless q0 is 0, q = clamp(round((x - bias) / scale)); scales and biases stored as T.  One block per head.
+__global__ void k_rope_quant_store(const FkState *st, KvQuantArgs a) {
+    __shared__ float row[512]; __shared__ float wmin[16], wmax[16];
+    pdl_launch_dependents(); pdl_wait();
+    const int head = blockIdx.x, d = threadIdx.x, half = a.hd >> 1, lane = d & 31, wid = d >> 5;
+    const uint32_t pos = st->offset; const int wrow = (int)(pos % (uint32_t)a.capacity);
+    if (head < a.n_q) {
+        if (d < half) {
+            uint16_t o0, o1; rope_pair(bf2f(a.q[head * a.hd + d]), bf2f(a.q[head * a.hd + d + half]), d, half, pos, a.log2theta, &o0, &o1);
+            a.q[head * a.hd + d] = o0; a.q[head * a.hd + d + half] = o1;
+        }
+        return;
+    }
+    const bool is_v = head >= a.n_q + a.n_kv; const int kh = head - a.n_q - (is_v ? a.n_kv : 0);
+    if (is_v) { if (d < a.hd) row[d] = bf2f(a.v_in[kh * a.hd + d]); }
+    else if (d < half) {
+        const float e = __fmul_rn(-__fdiv_rn((float)d, (float)half), a.log2theta);
+        const float ang = __fmul_rn((float)pos, exp2f(e));
+        float sn, cs; sincosf(ang, &sn, &cs);
+        const float lo = bf2f(a.k_in[kh * a.hd + d]), hi = bf2f(a.k_in[kh * a.hd + d + half]);
+        row[d] = __fsub_rn(__fmul_rn(lo, cs), __fmul_rn(hi, sn)); row[d + half] = __fadd_rn(__fmul_rn(hi, cs), __fmul_rn(lo, sn));
+    }
+    __syncthreads();
+    const float x = d < a.hd ? row[d] : 0.0f;
+    float mn = d < a.hd ? x : INFINITY, mx = d < a.hd ? x : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o)); mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o)); }
+    if (lane == 0) { wmin[wid] = mn; wmax[wid] = mx; }
+    __syncthreads();
+    const int grp = d >> 6;                                  // group of 64 = two warps
+    const float vmin = fminf(wmin[2 * grp], wmin[2 * grp + 1]), vmax = fmaxf(wmax[2 * grp], wmax[2 * grp + 1]);
+    const int mask = (1 << a.bits) - 1;
+    const float scale_abs = fmaxf(__fdiv_rn(__fsub_rn(vmax, vmin), (float)mask), 1.0e-7f);
+    const bool lo_anchor = fabsf(vmin) > fabsf(vmax);
+    float scale = lo_anchor ? scale_abs : -scale_abs;
+    const float edge = lo_anchor ? vmin : vmax;
+    const float q0 = roundf(__fdiv_rn(edge, scale));
+    const bool at_zero = q0 == 0.0f;
+    if (!at_zero) scale = __fdiv_rn(edge, q0);
+    const float bias = at_zero ? 0.0f : edge;
+    const float inv = scale != 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+    int qi = (int)roundf(__fmul_rn(__fsub_rn(x, bias), inv)); qi = qi < 0 ? 0 : (qi > mask ? mask : qi);
+    const int per = 32 / a.bits;
+    uint32_t word = d < a.hd ? ((uint32_t)qi << ((d % per) * a.bits)) : 0u;
+    for (int o = 1; o < per; o <<= 1) word |= __shfl_xor_sync(0xffffffffu, word, o);
+    const size_t crow = (size_t)kh * a.capacity + wrow;
+    if (d < a.hd && (d % per) == 0) (is_v ? a.vp : a.kp)[crow * (a.hd / per) + d / per] = word;
+    if (d < a.hd && (d & 63) == 0) {
+        (is_v ? a.vs : a.ks)[crow * (a.hd >> 6) + grp] = f2bf(scale);
+        (is_v ? a.vb : a.kb)[crow * (a.hd >> 6) + grp] = f2bf(bias);
+    }
+}
+
 struct SdpaArgs {
     const uint16_t *q, *ck, *cv; uint16_t *out; float *part; uint32_t *counter;
     int n_q, n_kv, hd, capacity, chunk; float scale; unsigned long long *tl;
@@ -433,6 +494,149 @@ __global__ void __launch_bounds__(FK_SDPA_THREADS) k_sdpa_decode(const FkState *
     }
     __syncthreads();
     sd_stamp(a.tl, 6);
+}
+
+struct SdpaQArgs {
+    const uint16_t *q; const uint32_t *kp, *vp; const uint16_t *ks, *kb, *vs, *vb; uint16_t *out; float *part; uint32_t *counter;
+    int n_q, n_kv, hd, capacity, chunk; float scale;
+};
+// Split-K GQA decode attention over a QUANTISED cache: packed words [n_kv, capacity, hd * bits / 32] with T scales and biases
+// [n_kv, capacity, hd / 64] per cache row; keys and values are dequantised in registers, float(q) * s + b
+// (src/codegen/kernels/sdpa_decode_quant.rs:301-372 scores, 429-470 weighted values, 506-680 the split form).  Same
+// decomposition as k_sdpa_decode: 32 keys per block, partial (m, l, o) per chunk, the last block of a kv head merges.
+template <int BITS>
+__global__ void __launch_bounds__(FK_SDPA_THREADS) k_sdpa_decode_q(const FkState *st, SdpaQArgs a) {
+    extern __shared__ float sm[];
+    const int G = a.n_q / a.n_kv, hd = a.hd, kvh = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x;
+    const int nparts = FK_SDPA_THREADS / hd;               // key slices of the PV phase
+    float *qs = sm;                                        // [G][hd]
+    float *sc = qs + G * hd;                               // [G][KEYS]
+    float *ml = sc + G * FK_SDPA_KEYS;                     // [G][2]
+    float *op = ml + 2 * G;                                // [nparts][G][hd]
+    float *wc = op + nparts * G * hd;                      // [G][chunks] merge weights
+    __shared__ int is_last;
+    pdl_launch_dependents(); pdl_wait();
+    const uint32_t pos = st->offset;
+    const int kv_len = (int)min(pos + 1u, (uint32_t)a.capacity);
+    const int n_active = (kv_len + FK_SDPA_KEYS - 1) / FK_SDPA_KEYS;
+    if (chunk >= n_active) return;
+    const int k0 = chunk * FK_SDPA_KEYS, bs = min(FK_SDPA_KEYS, kv_len - k0);
+    constexpr int PER = 32 / BITS; constexpr uint32_t MASK = (1u << BITS) - 1u;
+    const int nw = hd / PER, ng = hd >> 6;                 // packed words and quantisation groups per cache row
+    const size_t row0 = (size_t)kvh * a.capacity + k0;     // first cache row of this block
+    // V values of this thread's (dim, key slice), fetched before the score phase so the latency overlaps it
+    const int vd = tid % hd, vpart = tid / hd, kpp = FK_SDPA_KEYS / nparts;
+    float vreg[FK_SDPA_KEYS];                           // dequantised V values of this thread's (dim, key slice)
+#pragma unroll
+    for (int i = 0; i < FK_SDPA_KEYS; ++i) {
+        vreg[i] = 0.0f;
+        const int key = vpart * kpp + i;
+        if (i < kpp && key < bs) {
+            const uint32_t w = __ldg(a.vp + (row0 + key) * nw + vd / PER);
+            const float sc = bf2f(__ldg(a.vs + (row0 + key) * ng + (vd >> 6))), bi = bf2f(__ldg(a.vb + (row0 + key) * ng + (vd >> 6)));
+            vreg[i] = __fadd_rn(__fmul_rn((float)((w >> ((vd % PER) * BITS)) & MASK), sc), bi);
+        }
+    }
+    for (int i = tid; i < G * hd; i += FK_SDPA_THREADS) qs[i] = bf2f(a.q[kvh * G * hd + i]);
+    __syncthreads();
+    {   // scores: 8 threads per key, each over head_dim/8 dims
+        const int key = tid >> 3, part = tid & 7, dpp = hd >> 3;
+        float dot[FK_SDPA_MAXG];
+#pragma unroll
+        for (int g = 0; g < FK_SDPA_MAXG; ++g) dot[g] = 0.0f;
+        if (key < bs) {
+            // every key element is float(q) * s + b with the row's T scale and bias of its group (sdpa_decode_quant.rs:301-372)
+            const int d0 = part * dpp;
+            const float sc = bf2f(__ldg(a.ks + (row0 + key) * ng + (d0 >> 6))), bi = bf2f(__ldg(a.kb + (row0 + key) * ng + (d0 >> 6)));
+            const uint32_t *kw = a.kp + (row0 + key) * nw + d0 / PER;
+            for (int c = 0; c < dpp / PER; ++c) {
+                const uint32_t w = __ldg(kw + c);
+                const float *qp = qs + d0 + c * PER;
+#pragma unroll
+                for (int j = 0; j < PER; ++j) {
+                    const float kf = __fadd_rn(__fmul_rn((float)((w >> (j * BITS)) & MASK), sc), bi);
+#pragma unroll
+                    for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) dot[g] = fmaf(qp[g * hd + j], kf, dot[g]);
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) {
+            float d = dot[g];
+            d += __shfl_xor_sync(0xffffffffu, d, 1); d += __shfl_xor_sync(0xffffffffu, d, 2); d += __shfl_xor_sync(0xffffffffu, d, 4);
+            if (part == 0) sc[g * FK_SDPA_KEYS + key] = key < bs ? d * a.scale : -INFINITY;
+        }
+    }
+    __syncthreads();
+    const int lane = tid & 31, wid = tid >> 5;
+    if (wid < G) {      // softmax pieces of head `wid` over the 32 keys
+        const float s0 = sc[wid * FK_SDPA_KEYS + lane];
+        const float m = warp_max(s0);
+        const float p0 = lane < bs ? expf(s0 - m) : 0.0f;
+        sc[wid * FK_SDPA_KEYS + lane] = p0;
+        const float l = warp_sum(p0);
+        if (lane == 0) { ml[2 * wid] = m; ml[2 * wid + 1] = l; }
+    }
+    __syncthreads();
+    {   // o[g][d] over this thread's key slice
+        float o[FK_SDPA_MAXG];
+#pragma unroll
+        for (int g = 0; g < FK_SDPA_MAXG; ++g) o[g] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < FK_SDPA_KEYS; ++i) {
+            if (i < kpp) {
+                const float v = vreg[i]; const int key = vpart * kpp + i;
+#pragma unroll
+                for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) o[g] = fmaf(sc[g * FK_SDPA_KEYS + key], v, o[g]);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < FK_SDPA_MAXG; ++g) if (g < G) op[(vpart * G + g) * hd + vd] = o[g];
+    }
+    __syncthreads();
+    const int stride = hd + 2;
+    for (int i = tid; i < G * hd; i += FK_SDPA_THREADS) {
+        float o = 0.0f;
+        for (int q = 0; q < nparts; ++q) o += op[q * G * hd + i];
+        const int g = i / hd, d = i - g * hd;
+        float *p = a.part + ((size_t)(kvh * G + g) * a.chunk + chunk) * stride;
+        if (n_active == 1) a.out[(kvh * G + g) * hd + d] = f2bf(o * __fdiv_rn(1.0f, ml[2 * g + 1]));
+        else { p[2 + d] = o; if (d == 0) { p[0] = ml[2 * g]; p[1] = ml[2 * g + 1]; } }
+    }
+    if (n_active == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t t = atomicAdd(a.counter + kvh, 1u);
+        is_last = (t == (uint32_t)(n_active - 1));
+        if (is_last) a.counter[kvh] = 0u;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (wid < G) {      // merge weights w_c = exp(m_c - M) and the normaliser, one warp per head
+        const float *p = a.part + (size_t)(kvh * G + wid) * a.chunk * stride;
+        float M = -INFINITY;
+        for (int c = lane; c < n_active; c += 32) M = fmaxf(M, __ldcg(p + (size_t)c * stride));
+        M = warp_max(M);
+        float L = 0.0f;
+        for (int c = lane; c < n_active; c += 32) {
+            const float w = expf(__ldcg(p + (size_t)c * stride) - M);
+            wc[wid * a.chunk + c] = w;
+            L = fmaf(__ldcg(p + (size_t)c * stride + 1), w, L);
+        }
+        L = warp_sum(L);
+        if (lane == 0) ml[2 * wid + 1] = L;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * hd; i += FK_SDPA_THREADS) {
+        const int g = i / hd, d = i - g * hd;
+        const float *p = a.part + (size_t)(kvh * G + g) * a.chunk * stride + 2 + d;
+        float O = 0.0f;
+        for (int c = 0; c < n_active; ++c) O = fmaf(__ldcg(p + (size_t)c * stride), wc[g * a.chunk + c], O);
+        a.out[(kvh * G + g) * hd + d] = f2bf(O * __fdiv_rn(1.0f, ml[2 * g + 1]));
+    }
+    __syncthreads();
 }
 
 // ---------------------------------------------------------------- cluster SDPA

@@ -146,7 +146,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     CU(cudaFuncSetAttribute(k_sdpa_mma<128>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     CU(cudaFuncSetAttribute(k_sdpa_mma<256>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     CU(big_smem(k_qmm4<false>)); CU(big_smem(k_qmm4<true>)); CU(big_smem(k_qmm_tc<16>)); CU(big_smem(k_qmm_tc<32>));
-    CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
+    CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_decode_q<4>)); CU(big_smem(k_sdpa_decode_q<8>)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
     CU(big_smem(k_linear_residual<4>)); CU(big_smem(k_linear_residual<8>)); CU(big_smem(k_linear_residual<16>));
     CU(big_smem(k_rmsnorm_gateup_act<4>)); CU(big_smem(k_rmsnorm_gateup_act<8>)); CU(big_smem(k_rmsnorm_gateup_act<16>));
@@ -190,7 +190,7 @@ static const char *kKernelNames[FK_TASK_KIND_COUNT] = {
     "fusekit_step_init", "fusekit_embed_lookup_decode", "fusekit_rmsnorm_qkv", "fusekit_qk_norm_rope_store",
     "fusekit_sdpa_decode", "fusekit_linear_residual", "fusekit_rmsnorm_gateup_act", "fusekit_final_rmsnorm_lm_head",
     "fusekit_argmax_finalize", "fusekit_allreduce", "fusekit_residual_add", "fusekit_rmsnorm_rows", "fusekit_rope_store_rows",
-    "fusekit_argmax_rows"};
+    "fusekit_argmax_rows", "fusekit_kv_store_quant", "fusekit_sdpa_decode_quant"};
 extern "C" fk_status fk_kernel_names(char *buf, size_t cap) {
     if (!buf || cap == 0) return fail(FK_ERR_VALUE, "buf is null");
     std::string s;
@@ -746,6 +746,28 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (!b[0] || !b[5] || i[0] <= 0 || i[1] <= 0 || i[1] > FK_MAX_ROWS) return fail(FK_ERR_VALUE, "argmax_rows: bad arguments");
         ArgmaxRowsArgs a{(const uint16_t *)b[0], (uint32_t *)b[5], c->history, i[0], i[1], i[2] > 0 ? i[2] : 1};
         e = launch(c, k_argmax_rows, dim3(i[1]), dim3(1024), 0, c->state, a);
+        break;
+    }
+    case FK_TASK_KV_STORE_QUANT: {
+        const int nq = i[0], nkv = i[1], hd = i[2], cap = i[3], bits = i[4];
+        if (!b[0] || !b[1] || !b[2] || !b[3] || !b[4] || !b[5] || !b[6] || !b[7] || !b[8] || nq <= 0 || nkv <= 0 || (hd != 64 && hd != 128 && hd != 256) ||
+            cap <= 0 || (bits != 4 && bits != 8)) return fail(FK_ERR_VALUE, "kv_store_quant: bad arguments (head_dim in {64,128,256}, bits 4 or 8)");
+        KvQuantArgs a{(uint16_t *)b[0], (const uint16_t *)b[1], (const uint16_t *)b[2], (uint32_t *)b[3], (uint32_t *)b[4], (uint16_t *)b[5],
+                      (uint16_t *)b[6], (uint16_t *)b[7], (uint16_t *)b[8], nq, nkv, hd, cap, bits, (float)log2((double)f[1])};
+        e = launch(c, k_rope_quant_store, dim3(nq + 2 * nkv), dim3(hd), 0, (const FkState *)c->state, a);
+        break;
+    }
+    case FK_TASK_SDPA_DECODE_QUANT: {
+        const int nq = i[0], nkv = i[1], hd = i[2], cap = i[3], bits = i[4];
+        if (nkv <= 0 || nq % nkv || nq / nkv > FK_SDPA_MAXG || (hd != 64 && hd != 128 && hd != 256) || (bits != 4 && bits != 8) ||
+            !b[0] || !b[1] || !b[2] || !b[3] || !b[4] || !b[5] || !b[6] || !b[7] || !b[8] || !b[9]) return fail(FK_ERR_VALUE, "sdpa_decode_quant: bad arguments");
+        const int chunks = (cap + FK_SDPA_KEYS - 1) / FK_SDPA_KEYS, G = nq / nkv;
+        SdpaQArgs a{(const uint16_t *)b[0], (const uint32_t *)b[1], (const uint32_t *)b[2], (const uint16_t *)b[6], (const uint16_t *)b[7],
+                    (const uint16_t *)b[8], (const uint16_t *)b[9], (uint16_t *)b[3], (float *)b[4], (uint32_t *)b[5], nq, nkv, hd, cap, chunks, f[0]};
+        const size_t smem = sdpa_smem_bytes(G, hd, chunks);
+        if (smem > 200 * 1024) return fail(FK_ERR_VALUE, "sdpa_decode_quant: capacity too large for the merge table");
+        if (bits == 4) e = launch(c, k_sdpa_decode_q<4>, dim3(chunks, nkv), dim3(FK_SDPA_THREADS), smem, (const FkState *)c->state, a);
+        else e = launch(c, k_sdpa_decode_q<8>, dim3(chunks, nkv), dim3(FK_SDPA_THREADS), smem, (const FkState *)c->state, a);
         break;
     }
     default: return fail(FK_ERR_VALUE, "unknown task kind %d", t.kind);

@@ -185,11 +185,14 @@ class DecodeEngine:
     """One model instance (or one tensor-parallel slice of it) resident on a GPU."""
 
     def __init__(self, spec: ModelSpec, capacity: int, device: int = 0, tp_rank: int = 0, tp_size: int = 1,
-                 want_logits: bool = False, runtime: Runtime | None = None):
+                 want_logits: bool = False, runtime: Runtime | None = None, kv_bits: int = 0):
         check_tp(spec, tp_size)
         self.spec, self.capacity, self.rank, self.world = spec, capacity, tp_rank, tp_size
         self.rt = runtime or Runtime(device)
         self.want_logits = want_logits
+        self.kv_bits = kv_bits           # 4 / 8: quantised KV cache (reference: the *_quant cache kernels); 0: bf16
+        if kv_bits and (kv_bits not in (4, 8) or spec.arch != "qwen2" or tp_size > 1):
+            raise ValueError("the quantised KV cache is wired for Qwen-shaped layers on one GPU, 4 or 8 bits")
         s = spec
         self.nq, self.nkv, self.inter, self.vocab = s.n_q // tp_size, s.n_kv // tp_size, s.inter // tp_size, s.vocab // tp_size
         self.W: dict[str, int] = {}      # name -> fk_weight id
@@ -221,8 +224,16 @@ class DecodeEngine:
         self.argmax_scratch = rt.alloc(8 * 1024)
         self.head_counter = rt.alloc(4)
         self.logits = rt.alloc(self.vocab * 2) if self.want_logits else 0
+        self.cacheq: list[dict] = []                   # quantised caches: packed words + scales / biases per layer
         for l in range(L):
             cap = s.layer_capacity(l, self.capacity)
+            if self.kv_bits:
+                rows, ng = self.nkv * cap, s.head_dim // 64
+                nb = rows * s.head_dim * self.kv_bits // 8
+                self.cacheq.append({"k": rt.alloc(nb), "v": rt.alloc(nb), "k_scales": rt.alloc(rows * ng * 2), "k_biases": rt.alloc(rows * ng * 2),
+                                    "v_scales": rt.alloc(rows * ng * 2), "v_biases": rt.alloc(rows * ng * 2)})
+                self.cache.append((0, 0, cap))
+                continue
             k, v = C.c_uint64(), C.c_uint64()
             N.check(rt.L.fk_kv_cache_alloc(rt.h, self.nkv, cap, s.head_dim, C.byref(k), C.byref(v)), "fk_kv_cache_alloc")
             self.cache.append((k.value, v.value, cap))
@@ -284,7 +295,7 @@ class DecodeEngine:
         """Choose the tile row order the consuming kernel wants, then freeze the weight."""
         s, rt = self.spec, self.rt
         paired = rt.tiled
-        if name.endswith(".qkv") and s.arch == "qwen2" and paired:
+        if name.endswith(".qkv") and s.arch == "qwen2" and paired and not self.kv_bits:
             rt.weight_set_rows(wid, 1, s.head_dim, (self.nq + self.nkv) * s.head_dim)
         if paired and (name.endswith(".gate") or name.endswith(".up")):
             self.W[name] = wid                       # frozen together once both halves exist
@@ -342,7 +353,7 @@ class DecodeEngine:
     def task_graph(self) -> dict:
         """This engine's decode step as a v2 ``task_graph.json`` document (see task_graph.emit)."""
         return task_graph.emit(self.spec, self.capacity, self.rank, self.world,
-                               fused_weights=self.rt.tiled, want_logits=self.want_logits, embed_bits=getattr(self, "embed_bits", 16), tp_exchange=getattr(self, "tp_exchange", "allreduce"))
+                               fused_weights=self.rt.tiled, want_logits=self.want_logits, embed_bits=getattr(self, "embed_bits", 16), tp_exchange=getattr(self, "tp_exchange", "allreduce"), kv_bits=getattr(self, "kv_bits", 0))
 
     def _resolve(self, role: str) -> int:
         """Device address (or fk_weight id) behind one role string of the task graph."""
@@ -357,6 +368,8 @@ class DecodeEngine:
                  "pre_feedforward_layernorm.weight": "pre_feedforward_norm", "post_feedforward_layernorm.weight": "post_feedforward_norm",
                  "self_attn.q_norm.weight": "q_norm", "self_attn.k_norm.weight": "k_norm"}
             return self.W[f"layers.{l}.{w[rel]}"] if rel in w else self.V[f"layers.{l}.{v[rel]}"]
+        if p[0].startswith("layer_cache_") and getattr(self, "kv_bits", 0):
+            return self.cacheq[int(p[1])][p[0][len("layer_cache_"):]]
         if p[0] == "layer_cache_k":
             return self.cache[int(p[1])][0]
         if p[0] == "layer_cache_v":
@@ -430,6 +443,22 @@ class DecodeEngine:
             toks.extend(int(v) for v in out); secs += t; tok = int(out[-1]); off += n
         return np.array(toks, np.uint32), secs
 
+    def generate_sampled(self, seed_token: int, base_offset: int, max_tokens: int, temperature: float = 1.0, top_k: int = 0,
+                         top_p: float = 1.0, seed: int = 0):
+        """Sampling beyond greedy, the way the reference does it: the fused step still runs on the GPU, the logits of every
+        step come back to the host and the sampler picks the next token there (the reference hands logits to mlx-lm's
+        sampler whenever the request is not greedy, python/fusekit_runtime/__init__.py:4782-4843).  Needs an engine created
+        with want_logits=True.  Returns the sampled tokens."""
+        if not self.logits:
+            raise N.FusekitError("sampling needs an engine created with want_logits=True")
+        rng = np.random.default_rng(seed)
+        toks, tok = [], int(seed_token)
+        for i in range(max_tokens):
+            self.decode_chunk(base_offset + i, tok, 1)
+            tok = sample_logits(self.last_logits(), temperature, top_k, top_p, rng)
+            toks.append(tok)
+        return np.array(toks, np.uint32)
+
     def profile_nodes(self, repeats: int = 3):
         if not self.graph:
             self.capture()
@@ -494,6 +523,25 @@ class DecodeEngine:
 
     def close(self):
         self.rt.close()
+
+
+def sample_logits(logits_bf16: np.ndarray, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, rng=None) -> int:
+    """One token from bf16 logits (bit patterns): temperature scaling, then top-k and nucleus (top-p) filtering, then a draw.
+    temperature <= 0 or top_k == 1 is the greedy choice with ties to the lowest index, like the on-device argmax."""
+    x = (np.asarray(logits_bf16, np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    if temperature <= 0.0 or top_k == 1:
+        return int(np.argmax(x))                  # first maximum = lowest index
+    x = x / temperature
+    order = np.argsort(-x, kind="stable")
+    if top_k and top_k > 0:
+        order = order[:top_k]
+    p = np.exp(x[order] - x[order[0]])
+    p /= p.sum()
+    if top_p < 1.0:
+        keep = int(np.searchsorted(np.cumsum(p), top_p, side="left")) + 1      # smallest prefix whose mass reaches top_p
+        order, p = order[:keep], p[:keep] / p[:keep].sum()
+    rng = rng or np.random.default_rng()
+    return int(order[int(rng.choice(len(order), p=p))])
 
 
 def _ensure_nccl_path():

@@ -16,9 +16,11 @@ from .model_spec import ModelSpec
 
 VERSION = 2
 KINDS = ["step_init", "embed_lookup_decode", "rmsnorm_qkv", "qk_norm_rope_store", "sdpa_decode", "linear_residual",
-         "rmsnorm_gateup_act", "final_rmsnorm_lm_head", "argmax_finalize", "allreduce", "residual_add"]
+         "rmsnorm_gateup_act", "final_rmsnorm_lm_head", "argmax_finalize", "allreduce", "residual_add", "rmsnorm_rows",
+         "rope_store_rows", "argmax_rows", "kv_store_quant", "sdpa_decode_quant"]
 KERNEL = {k: "fusekit_" + k for k in KINDS}
-(K_STEP, K_EMBED, K_QKV, K_QKNORM, K_SDPA, K_LIN, K_GATEUP, K_HEAD, K_ARGMAX, K_ALLREDUCE, K_RESADD) = range(11)
+(K_STEP, K_EMBED, K_QKV, K_QKNORM, K_SDPA, K_LIN, K_GATEUP, K_HEAD, K_ARGMAX, K_ALLREDUCE, K_RESADD, K_NORMROWS, K_ROPEROWS,
+ K_ARGMAXROWS, K_KVQ, K_SDPAQ) = range(16)
 
 
 def _bf16_round(v: float) -> float:
@@ -29,7 +31,7 @@ def _bf16_round(v: float) -> float:
 
 
 def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fused_weights: bool = True,
-         want_logits: bool = False, embed_bits: int = 16, tp_exchange: str = "allreduce") -> dict:
+         want_logits: bool = False, embed_bits: int = 16, tp_exchange: str = "allreduce", kv_bits: int = 0) -> dict:
     """Build the v2 task graph of one decode step for `spec` (one tensor-parallel rank of it).
 
     `fused_weights`: weights in the streaming layout (gate/up paired, residual add after an all-reduce fused into the next
@@ -37,12 +39,17 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
     `tp_exchange`: how the partial rows of the row-split projections meet -- "allreduce": an all-reduce task after each
     (library collective or the stand-alone peer kernel); "peer": no task of its own, the projection pushes its partial rows
     into every rank's arena and the next norm-first kernel sums them (exchange site 2l for o_proj, 2l + 1 for down_proj of
-    layer l, 2L for the argmax keys of the vocabulary-sharded head)."""
+    layer l, 2L for the argmax keys of the vocabulary-sharded head).
+    `kv_bits`: 4 or 8 = quantised KV cache (Qwen-shaped layers, one GPU): the QKV task writes raw projections, a
+    kv_store_quant task rotates and quantises, sdpa_decode_quant attends the packed cache
+    (src/codegen/kernels/rope_kv_cache_store_decode_quant.rs, sdpa_decode_quant.rs)."""
     s, hd, H = spec, spec.head_dim, spec.hidden
     nq, nkv, inter, vocab = s.n_q // tp_size, s.n_kv // tp_size, s.inter // tp_size, s.vocab // tp_size
     tp = tp_size > 1
     fused = fused_weights
     peer = tp and tp_exchange == "peer"
+    if kv_bits and (kv_bits not in (4, 8) or s.arch != "qwen2" or tp):
+        raise ValueError("the quantised KV cache is wired for Qwen-shaped layers on one GPU, 4 or 8 bits")
     if peer and not fused:
         raise ValueError("the fused peer exchange needs the streaming weight layout")
     if peer and 2 * s.n_layers + 1 > 160:
@@ -73,8 +80,15 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
                 x_in, pend, pull = hb(l - 1), {11: x(l)}, 2 * (l - 1) + 2
             elif tp and l > 0 and fused:                   # x[l] = T(all-reduced down_proj + h[l-1])
                 x_in, pend = hb(l - 1), {9: "global_scratch.tp_partial_b", 11: x(l)}
-            add(K_QKV, l, {0: x_in, 1: lp(l, "input_layernorm.weight"), 2: lp(l, "self_attn.qkv_proj"), 3: lp(l, "self_attn.qkv_proj.bias"),
-                           4: "layer_scratch.q_buf", 5: ck, 6: cv, **pend}, [H, nq, nkv, hd, cap, 1, pull], [s.eps, theta])
+            if kv_bits:
+                cq = {n: f"layer_cache_{n}.{l}" for n in ("k", "v", "k_scales", "k_biases", "v_scales", "v_biases")}
+                add(K_QKV, l, {0: x_in, 1: lp(l, "input_layernorm.weight"), 2: lp(l, "self_attn.qkv_proj"), 3: lp(l, "self_attn.qkv_proj.bias"),
+                               4: "layer_scratch.q_buf", 7: "layer_scratch.k_buf", 8: "layer_scratch.v_buf"}, [H, nq, nkv, hd, cap, 0], [s.eps, theta])
+                add(K_KVQ, l, {0: "layer_scratch.q_buf", 1: "layer_scratch.k_buf", 2: "layer_scratch.v_buf", 3: cq["k"], 4: cq["v"], 5: cq["k_scales"],
+                               6: cq["k_biases"], 7: cq["v_scales"], 8: cq["v_biases"]}, [nq, nkv, hd, cap, kv_bits], [0.0, theta])
+            else:
+                add(K_QKV, l, {0: x_in, 1: lp(l, "input_layernorm.weight"), 2: lp(l, "self_attn.qkv_proj"), 3: lp(l, "self_attn.qkv_proj.bias"),
+                               4: "layer_scratch.q_buf", 5: ck, 6: cv, **pend}, [H, nq, nkv, hd, cap, 1, pull], [s.eps, theta])
         else:
             x_in, pend = x(l), {}
             if l > 0:                                      # Gemma: x[l] = T(h[l-1] + rmsnorm(down_out[l-1]))
@@ -83,8 +97,13 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
                            7: "layer_scratch.k_buf", 8: "layer_scratch.v_buf", **pend}, [H, nq, nkv, hd, cap, 0], [s.eps, theta])
             add(K_QKNORM, l, {0: "layer_scratch.q_buf", 1: "layer_scratch.k_buf", 2: "layer_scratch.v_buf", 3: lp(l, "self_attn.q_norm.weight"),
                               4: lp(l, "self_attn.k_norm.weight"), 5: ck, 6: cv}, [nq, nkv, hd, cap], [s.eps, theta])
-        add(K_SDPA, l, {0: "layer_scratch.q_buf", 1: ck, 2: cv, 3: "layer_scratch.sdpa_buf", 4: "global_scratch.sdpa_partials",
-                        5: "global_scratch.sdpa_counter"}, [nq, nkv, hd, cap], [scale])
+        if kv_bits:
+            add(K_SDPAQ, l, {0: "layer_scratch.q_buf", 1: cq["k"], 2: cq["v"], 3: "layer_scratch.sdpa_buf", 4: "global_scratch.sdpa_partials",
+                             5: "global_scratch.sdpa_counter", 6: cq["k_scales"], 7: cq["k_biases"], 8: cq["v_scales"], 9: cq["v_biases"]},
+                [nq, nkv, hd, cap, kv_bits], [scale])
+        else:
+            add(K_SDPA, l, {0: "layer_scratch.q_buf", 1: ck, 2: cv, 3: "layer_scratch.sdpa_buf", 4: "global_scratch.sdpa_partials",
+                            5: "global_scratch.sdpa_counter"}, [nq, nkv, hd, cap], [scale])
         ko = nq * hd
         if s.arch == "qwen2" and not tp:
             add(K_LIN, l, {0: "layer_scratch.sdpa_buf", 1: lp(l, "self_attn.o_proj"), 2: x(l), 3: hb(l)}, [ko, H])
@@ -134,7 +153,7 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
 
     # ---- v2 envelope: tasks with bindings, a linear event chain, layer groups, the decode pipeline
     out_slots = {K_EMBED: [1], K_QKV: [4, 5, 6, 7, 8, 11], K_QKNORM: [0, 5, 6], K_SDPA: [3, 4, 5], K_LIN: [3, 4], K_GATEUP: [4, 11],
-                 K_HEAD: [3, 4, 5, 11], K_ARGMAX: [], K_ALLREDUCE: [0], K_RESADD: [2]}
+                 K_HEAD: [3, 4, 5, 11], K_ARGMAX: [], K_ALLREDUCE: [0], K_RESADD: [2], K_KVQ: [0, 3, 4, 5, 6, 7, 8], K_SDPAQ: [3, 4, 5]}
     jtasks, groups = [], {}
     for i, t in enumerate(tasks):
         ins, outs, extra = [], [], []

@@ -53,7 +53,9 @@ enum {
                                           never batches independent sequences, python/fusekit_runtime/dispatch.py:2268-2289) */
     FK_TASK_ROPE_STORE_ROWS = 12,      /* batch: RoPE on q / k and the cache store of every sequence (rmsnorm_qkv.rs:635-697) */
     FK_TASK_ARGMAX_ROWS = 13,          /* batch: greedy token of every sequence + position advance (argmax_logits_scan.rs:83-124) */
-    FK_TASK_KIND_COUNT = 14
+    FK_TASK_KV_STORE_QUANT = 14,       /* kernels/rope_kv_cache_store_decode_quant.rs (fused form rmsnorm_qkv.rs:435-612): RoPE + quantised KV store */
+    FK_TASK_SDPA_DECODE_QUANT = 15,    /* kernels/sdpa_decode_quant.rs:301-680: attention over the quantised cache */
+    FK_TASK_KIND_COUNT = 16
 };
 
 /* activation selector for FK_TASK_RMSNORM_GATEUP_ACT */
@@ -112,6 +114,13 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      (caches [M, n_kv, capacity, hd])   i0 n_q  i1 n_kv  i2 head_dim  i3 capacity  i4 M   f1 rope_theta
  * ARGMAX_ROWS          buf0 logits T[M,V]  buf5 counter(u32, zero before first use)   i0 V  i1 M
  *                      token[m] of the decode state and history[step * M + m] receive sequence m's token
+ * KV_STORE_QUANT       buf0 q T[n_q*hd] (raw projection in, rotated out)  buf1 k_in T[n_kv*hd]  buf2 v_in T[n_kv*hd]  (RMSNORM_QKV
+ *                      without sinks)  buf3 cache_k packed u32 [n_kv, capacity, hd*bits/32]  buf4 cache_v packed  buf5 k scales
+ *                      buf6 k biases  buf7 v scales  buf8 v biases (T[n_kv, capacity, hd/64])
+ *                      i0 n_q  i1 n_kv  i2 head_dim  i3 capacity  i4 bits (4 / 8)   f1 rope_theta
+ * SDPA_DECODE_QUANT    buf0 q  buf1 cache_k packed  buf2 cache_v packed  buf3 out  buf4 partials(f32)  buf5 counter(u32)
+ *                      buf6 k scales  buf7 k biases  buf8 v scales  buf9 v biases   i0 n_q  i1 n_kv  i2 head_dim  i3 capacity
+ *                      i4 bits   f0 scale      (partials and counter as SDPA_DECODE)
  *                      ROPE_STORE_ROWS i5 = 1, SDPA_DECODE i6 = 1: the M rows are consecutive positions offset .. offset + M - 1 of
  *                      ONE sequence (a prefill chunk, or verify rows of speculative decoding; reference: the M > 1 trace
  *                      shapes, python/fusekit_runtime/__init__.py:2825-2850, src/commands/patch.rs:112-152) sharing one cache

@@ -285,6 +285,95 @@ void fko_sdpa_decode(const bf16_t *q, const bf16_t *ck, const bf16_t *cv, int n_
     }
 }
 
+/* ------------------------------------------------------------ quantised KV cache
+ * One cache row (a head's k after RoPE, kept in fp32, or its v rounded to T) is quantised per group of `group` values with
+ * the edge-anchored affine rule of src/codegen/kernels/rmsnorm_qkv.rs:560-590 (the same in
+ * rope_kv_cache_store_decode_quant.rs): scale_abs = max((max - min) / (2^bits - 1), 1e-7); the edge of larger magnitude
+ * anchors the grid (scale negative when that is the maximum); q0 = round(edge / scale), and unless q0 is 0 the scale
+ * becomes edge / q0 and the bias the edge, so the edge is represented exactly; q = clamp(round((x - bias) / scale)).
+ * scales and biases are stored as T.  round() is round-half-away-from-zero (Metal's round). */
+void fko_kv_quantize_row(const float *x, int n, int group, int bits, uint32_t *packed, bf16_t *scales, bf16_t *biases) {
+    const int mask = (1 << bits) - 1, per = 32 / bits;
+    for (int i = 0; i < n / per; ++i) packed[i] = 0u;
+    for (int g = 0; g < n / group; ++g) {
+        float vmin = INFINITY, vmax = -INFINITY;
+        for (int d = 0; d < group; ++d) { float v = x[g * group + d]; vmin = v < vmin ? v : vmin; vmax = v > vmax ? v : vmax; }
+        float scale_abs = (vmax - vmin) / (float)mask; if (scale_abs < 1.0e-7f) scale_abs = 1.0e-7f;
+        const int lo = fabsf(vmin) > fabsf(vmax);
+        float scale = lo ? scale_abs : -scale_abs;
+        const float edge = lo ? vmin : vmax;
+        const float q0 = roundf(edge / scale);
+        const int at_zero = (q0 == 0.0f);
+        if (!at_zero) scale = edge / q0;
+        const float bias = at_zero ? 0.0f : edge;
+        const float inv = (scale != 0.0f) ? (1.0f / scale) : 0.0f;
+        for (int d = 0; d < group; ++d) {
+            const int idx = g * group + d;
+            float t = x[idx] - bias; t = t * inv;
+            int qi = (int)roundf(t); qi = qi < 0 ? 0 : (qi > mask ? mask : qi);
+            packed[idx / per] |= ((uint32_t)qi & (uint32_t)mask) << ((idx % per) * bits);
+        }
+        scales[g] = f2bf(scale); biases[g] = f2bf(bias);
+    }
+}
+/* RoPE of T-rounded heads with the rotated values left in fp32 (the quantising store reads them unrounded,
+ * rmsnorm_qkv.rs:516-525) */
+void fko_rope_f32(const bf16_t *v, int n_heads, int hd, uint32_t pos, float theta, float *out) {
+    const int half = hd / 2; const float l2t = (float)log2((double)theta);
+    for (int h = 0; h < n_heads; ++h)
+        for (int d = 0; d < half; ++d) {
+            float e = -((float)d / (float)half); e = e * l2t;
+            float inv = exp2f(e);
+            float ang = (float)pos * inv;
+            float c = cosf(ang), s = sinf(ang);
+            float lo = bf2f(v[h * hd + d]), hi = bf2f(v[h * hd + d + half]);
+            float a = lo * c, b = hi * s; out[h * hd + d] = a - b;
+            float p = hi * c, q = lo * s; out[h * hd + d + half] = p + q;
+        }
+}
+static inline float kv_deq(const uint32_t *packed, const bf16_t *sc, const bf16_t *bi, int64_t row, int d, int hd, int group, int bits) {
+    const int per = 32 / bits; const uint32_t mask = (1u << bits) - 1u;
+    const uint32_t w = packed[row * (hd / per) + d / per];
+    const float q = (float)((w >> ((d % per) * bits)) & mask);
+    float t = q * bf2f(sc[row * (hd / group) + d / group]);
+    return t + bf2f(bi[row * (hd / group) + d / group]);
+}
+/* SDPA over a quantised cache: every key / value element is float(q) * s + b with the T scales and biases
+ * (sdpa_decode_quant.rs:301-372, 429-470); everything else as fko_sdpa_decode */
+void fko_sdpa_decode_quant(const bf16_t *q, const uint32_t *kp, const bf16_t *ks, const bf16_t *kb, const uint32_t *vp, const bf16_t *vs,
+                           const bf16_t *vb, int n_q, int n_kv, int hd, int64_t capacity, int64_t kv_len, float scale, int group, int bits,
+                           bf16_t *out) {
+    #pragma omp parallel for schedule(static)
+    for (int h = 0; h < n_q; ++h) {
+        const int kvh = h / (n_q / n_kv);
+        float qf[512], o[512], sblk[64];
+        for (int d = 0; d < hd; ++d) { qf[d] = bf2f(q[h * hd + d]); o[d] = 0.0f; }
+        float m = -INFINITY, l = 0.0f;
+        for (int64_t blk = 0; blk < kv_len; blk += 64) {
+            int bs = (int)((kv_len - blk) < 64 ? (kv_len - blk) : 64);
+            float mb = -INFINITY;
+            for (int i = 0; i < bs; ++i) {
+                const int64_t row = (int64_t)kvh * capacity + blk + i; float dot = 0.0f;
+                for (int d = 0; d < hd; ++d) { float p = qf[d] * kv_deq(kp, ks, kb, row, d, hd, group, bits); dot = dot + p; }
+                sblk[i] = dot * scale; mb = sblk[i] > mb ? sblk[i] : mb;
+            }
+            float mn = m > mb ? m : mb;
+            float alpha = expf(m - mn);
+            float lb = 0.0f;
+            for (int i = 0; i < bs; ++i) { sblk[i] = expf(sblk[i] - mn); lb = lb + sblk[i]; }
+            l = l * alpha; l = l + lb;
+            for (int d = 0; d < hd; ++d) {
+                float c = 0.0f;
+                for (int i = 0; i < bs; ++i) { float p = sblk[i] * kv_deq(vp, vs, vb, (int64_t)kvh * capacity + blk + i, d, hd, group, bits); c = c + p; }
+                o[d] = o[d] * alpha; o[d] = o[d] + c;
+            }
+            m = mn;
+        }
+        float inv_l = 1.0f / l;
+        for (int d = 0; d < hd; ++d) out[h * hd + d] = f2bf(o[d] * inv_l);
+    }
+}
+
 /* ------------------------------------------------------------ activations
  * SwiGLU: g=float(T(gate)), u=float(T(up)), y=T(((1/(1+exp(-g)))*g)*u)
  * (src/codegen/msl.rs:1286-1294). */
@@ -344,11 +433,14 @@ typedef struct {
     bf16_t *w_in, *w_post;            /* Qwen: input / post-attention norms   */
     bf16_t *w_postattn, *w_preffn, *w_postffn, *w_qn, *w_kn;   /* Gemma extras */
     bf16_t *ck, *cv; int64_t cap; int sliding; float theta;
+    /* quantised cache (fko_model_set_kv_quant): packed words [n_kv, cap, hd*bits/32], scales / biases [n_kv, cap, hd/group] */
+    uint32_t *kp, *vp; bf16_t *ks, *kb, *vs, *vb;
 } fko_layer;
 
 typedef struct {
     fko_config c; fko_layer *L; bf16_t *embed; bf16_t *w_final; fko_linear head;
     float embed_scale;
+    int kv_bits, kv_group;    /* 0: bf16 cache */
 } fko_model;
 
 static uint64_t sid(uint64_t seed, const char *fmt, int layer) {
@@ -441,10 +533,23 @@ fko_model *fko_model_create(const fko_config *cfg) {
     }
     return M;
 }
+/* switch the model to a quantised KV cache (bits 4 / 8, group 64); the caches start empty */
+void fko_model_set_kv_quant(fko_model *M, int bits, int group) {
+    const int nkv = M->c.n_kv / M->c.tp_size, hd = M->c.head_dim;
+    M->kv_bits = bits; M->kv_group = group;
+    for (int l = 0; l < M->c.n_layers; ++l) {
+        fko_layer *Y = &M->L[l];
+        const size_t rows = (size_t)nkv * Y->cap;
+        Y->kp = (uint32_t *)calloc(rows * hd * bits / 32, 4); Y->vp = (uint32_t *)calloc(rows * hd * bits / 32, 4);
+        Y->ks = (bf16_t *)calloc(rows * hd / group, 2); Y->kb = (bf16_t *)calloc(rows * hd / group, 2);
+        Y->vs = (bf16_t *)calloc(rows * hd / group, 2); Y->vb = (bf16_t *)calloc(rows * hd / group, 2);
+    }
+}
 void fko_model_free(fko_model *M) {
     if (!M) return;
     for (int l = 0; l < M->c.n_layers; ++l) {
         fko_layer *Y = &M->L[l];
+        free(Y->kp); free(Y->vp); free(Y->ks); free(Y->kb); free(Y->vs); free(Y->vb);
         free_linear(&Y->q); free_linear(&Y->k); free_linear(&Y->v); free_linear(&Y->o);
         free_linear(&Y->gate); free_linear(&Y->up); free_linear(&Y->down);
         free(Y->w_in); free(Y->w_post); free(Y->w_postattn); free(Y->w_preffn); free(Y->w_postffn);
@@ -499,15 +604,30 @@ void fko_layer_step(fko_model *M, int l, bf16_t *x, uint32_t pos) {
     fko_linear_apply(&Y->k, nf, NULL, k, NULL);
     fko_linear_apply(&Y->v, nf, NULL, v, NULL);
     if (c->arch == 1) { head_norm(q, nq, hd, Y->w_qn, c->eps); head_norm(k, nkv, hd, Y->w_kn, c->eps); }
-    fko_rope(q, nq, hd, pos, Y->theta); fko_rope(k, nkv, hd, pos, Y->theta);
     /* cache row = pos % capacity; kv_len = min(pos+1, capacity)
      * (rope_kv_cache_store_decode.rs:95; python/fusekit_runtime/dispatch.py:2324-2354) */
     int64_t row = (int64_t)pos % Y->cap, kv_len = (int64_t)pos + 1 < Y->cap ? (int64_t)pos + 1 : Y->cap;
+    if (M->kv_bits) {       /* quantised cache: k rotated in fp32 and quantised unrounded, v quantised from its T values */
+        const int G = M->kv_group, B = M->kv_bits, nw = hd * B / 32, ng = hd / G;
+        float *kr = (float *)malloc(sizeof(float) * (size_t)nkv * hd), *vr = (float *)malloc(sizeof(float) * (size_t)nkv * hd);
+        fko_rope_f32(k, nkv, hd, pos, Y->theta, kr);
+        for (int i = 0; i < nkv * hd; ++i) vr[i] = bf2f(v[i]);
+        fko_rope(q, nq, hd, pos, Y->theta);
+        for (int hh = 0; hh < nkv; ++hh) {
+            const int64_t r = (int64_t)hh * Y->cap + row;
+            fko_kv_quantize_row(kr + hh * hd, hd, G, B, Y->kp + r * nw, Y->ks + r * ng, Y->kb + r * ng);
+            fko_kv_quantize_row(vr + hh * hd, hd, G, B, Y->vp + r * nw, Y->vs + r * ng, Y->vb + r * ng);
+        }
+        free(kr); free(vr);
+        fko_sdpa_decode_quant(q, Y->kp, Y->ks, Y->kb, Y->vp, Y->vs, Y->vb, nq, nkv, hd, Y->cap, kv_len, scale, G, B, a);
+    } else {
+    fko_rope(q, nq, hd, pos, Y->theta); fko_rope(k, nkv, hd, pos, Y->theta);
     for (int hh = 0; hh < nkv; ++hh) {
         memcpy(Y->ck + ((int64_t)hh * Y->cap + row) * hd, k + hh * hd, (size_t)hd * 2);
         memcpy(Y->cv + ((int64_t)hh * Y->cap + row) * hd, v + hh * hd, (size_t)hd * 2);
     }
     fko_sdpa_decode(q, Y->ck, Y->cv, nq, nkv, hd, Y->cap, kv_len, scale, a);
+    }
     for (int i = 0; i < nq * hd; ++i) af[i] = bf2f(a[i]);
     if (c->arch == 0) {
         fko_linear_apply(&Y->o, af, x, h, NULL);                    /* h = T(Wo a + x) */

@@ -86,6 +86,10 @@ def lib():
     L.fko_head_step.restype = u32; L.fko_head_step.argtypes = [vp, vp, vp]
     L.fko_decode_greedy.restype = C.c_double; L.fko_decode_greedy.argtypes = [vp, u32, u32, i32, vp]
     L.fko_num_threads.restype = i32
+    L.fko_kv_quantize_row.restype = None; L.fko_kv_quantize_row.argtypes = [vp, i32, i32, i32, vp, vp, vp]
+    L.fko_rope_f32.restype = None; L.fko_rope_f32.argtypes = [vp, i32, i32, u32, f32, vp]
+    L.fko_sdpa_decode_quant.restype = None; L.fko_sdpa_decode_quant.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, f32, i32, i32, vp]
+    L.fko_model_set_kv_quant.restype = None; L.fko_model_set_kv_quant.argtypes = [vp, i32, i32]
     L.fko_set_num_threads.restype = None; L.fko_set_num_threads.argtypes = [i32]
     L.fko_f32_to_bf16.restype = C.c_uint16; L.fko_f32_to_bf16.argtypes = [f32]
     L.fko_bf16_to_f32.restype = f32; L.fko_bf16_to_f32.argtypes = [C.c_uint16]
@@ -209,6 +213,26 @@ def act(gate_acc: np.ndarray, up_acc: np.ndarray, kind: int) -> np.ndarray:
     return y
 
 
+def kv_quantize_row(x_f32: np.ndarray, bits: int, group: int = 64):
+    """One cache row quantised with the reference's edge-anchored rule: (packed u32, scales bf16, biases bf16)."""
+    x = np.ascontiguousarray(x_f32, np.float32)
+    packed = np.zeros(x.size * bits // 32, np.uint32); sc = np.zeros(x.size // group, np.uint16); bi = np.zeros(x.size // group, np.uint16)
+    lib().fko_kv_quantize_row(_p(x), x.size, group, bits, _p(packed), _p(sc), _p(bi))
+    return packed, sc, bi
+
+
+def rope_f32(v_bf16: np.ndarray, n_heads: int, hd: int, pos: int, theta: float) -> np.ndarray:
+    out = np.empty(n_heads * hd, np.float32)
+    lib().fko_rope_f32(_p(np.ascontiguousarray(v_bf16, np.uint16)), n_heads, hd, pos, theta, _p(out))
+    return out
+
+
+def sdpa_decode_quant(q, kp, ks, kb, vp, vs, vb, n_q, n_kv, hd, capacity, kv_len, scale, bits, group=64) -> np.ndarray:
+    out = np.empty(n_q * hd, np.uint16)
+    lib().fko_sdpa_decode_quant(_p(q), _p(kp), _p(ks), _p(kb), _p(vp), _p(vs), _p(vb), n_q, n_kv, hd, capacity, kv_len, scale, group, bits, _p(out))
+    return out
+
+
 def argmax_bf16(logits: np.ndarray) -> int:
     return int(lib().fko_argmax_bf16(_p(logits), logits.size))
 
@@ -247,6 +271,10 @@ class Model:
 
     def __del__(self):
         self.close()
+
+    def set_kv_quant(self, bits: int, group: int = 64):
+        """Switch to a quantised KV cache (empty): store and attention follow the reference's quantised kernels."""
+        lib().fko_model_set_kv_quant(self._h, bits, group)
 
     def prefill_kv(self, ctx: int):
         lib().fko_model_prefill_kv(self._h, ctx)
