@@ -187,12 +187,12 @@ class DecodeEngine:
     def __init__(self, spec: ModelSpec, capacity: int, device: int = 0, tp_rank: int = 0, tp_size: int = 1,
                  want_logits: bool = False, runtime: Runtime | None = None, kv_bits: int = 0):
         check_tp(spec, tp_size)
-        self.spec, self.capacity, self.rank, self.world = spec, capacity, tp_rank, tp_size
-        self.rt = runtime or Runtime(device)
-        self.want_logits = want_logits
         self.kv_bits = kv_bits           # 4 / 8: quantised KV cache (reference: the *_quant cache kernels); 0: bf16
         if kv_bits and (kv_bits not in (4, 8) or spec.arch != "qwen2" or tp_size > 1):
             raise ValueError("the quantised KV cache is wired for Qwen-shaped layers on one GPU, 4 or 8 bits")
+        self.spec, self.capacity, self.rank, self.world = spec, capacity, tp_rank, tp_size
+        self.rt = runtime or Runtime(device)
+        self.want_logits = want_logits
         s = spec
         self.nq, self.nkv, self.inter, self.vocab = s.n_q // tp_size, s.n_kv // tp_size, s.inter // tp_size, s.vocab // tp_size
         self.W: dict[str, int] = {}      # name -> fk_weight id
