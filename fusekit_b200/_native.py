@@ -19,6 +19,11 @@ LIB_PATH = os.environ.get("FUSEKIT_CUDA_LIB") or os.path.join(_HERE, "libfusekit
 ACT_SWIGLU, ACT_GEGLU_TANH = 0, 1
 
 
+class RoleBinding(C.Structure):
+    """Mirror of ``fk_role_binding``: one role string of a task graph and the address / weight id behind it."""
+    _fields_ = [("role", C.c_char_p), ("value", C.c_uint64)]
+
+
 class FusekitError(RuntimeError):
     pass
 
@@ -67,7 +72,9 @@ def lib():
         "fk_state_set": [u64, u32, u32], "fk_state_get": [u64, P(u32), P(u32), P(u32)],
         "fk_peer_arena_export": [u64, C.c_void_p, C.c_size_t], "fk_peer_arena_open": [u64, C.c_void_p, i32, i32],
         "fk_peer_arena_loopback": [u64, i32, i32, u32], "fk_peer_arena_close": [u64],
-        "fk_graph_capture": [u64, P(Task), i32, P(u64)], "fk_graph_launch": [u64, u64, P(C.c_double)],
+        "fk_graph_capture": [u64, P(Task), i32, P(u64)],
+        "fk_tasks_from_json": [C.c_char_p, P(RoleBinding), i32, P(Task), i32, P(i32)],
+        "fk_graph_capture_json": [u64, C.c_char_p, P(RoleBinding), i32, P(u64)], "fk_graph_launch": [u64, u64, P(C.c_double)],
         "fk_graph_launch_async": [u64, u64], "fk_wait": [u64, P(C.c_double)],
         "fk_graph_profile_nodes": [u64, u64, i32, P(C.c_double), i32, P(i32)], "fk_graph_node_count": [u64, u64, P(i32)],
         "fk_time_tasks": [u64, P(Task), i32, i32, P(C.c_double)],

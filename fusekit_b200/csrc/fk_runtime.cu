@@ -8,6 +8,7 @@
 #include "fk_stream.cuh"
 #include "fk_qmm.cuh"
 #include "fk_qmm_tc.cuh"
+#include "fk_json.h"
 
 #include <dlfcn.h>
 #include <math.h>
@@ -856,6 +857,60 @@ extern "C" fk_status fk_graph_capture(fk_handle h, const fk_task *tasks, int n, 
     CU(cudaGraphUpload(g.exec, c->stream));
     c->graphs.push_back(g); *out = c->graphs.size();
     return FK_OK;
+}
+// ------------------------------------------------------------------ task_graph.json behind the C ABI
+// The file-level boundary of the reference: load_dispatcher(metallib, task_graph) reads the document and the host resolves
+// every role string to a live buffer (python_runtime/src/lib.rs:115-169; src/runtime/plan.rs:39-164, 409-431).  Here the
+// library parses the v2 document itself and the caller supplies the role -> address (or weight id) table, so a host without
+// Python can replay a graph: tasks are taken in `decode_pipeline` order, `kind`, `layer_idx`, `iargs`, `fargs` as written
+// by the emitter, and every explicit binding below slot 100 must be in the table.
+extern "C" fk_status fk_tasks_from_json(const char *json_text, const fk_role_binding *roles, int n_roles, fk_task *tasks_out, int cap, int *n_out) {
+    if (!json_text || (!roles && n_roles > 0) || n_roles < 0 || !n_out) return fail(FK_ERR_VALUE, "fk_tasks_from_json: null argument");
+    JParser jp(json_text); JVal doc;
+    if (!jp.parse(doc) || doc.kind != JVal::OBJ) return fail(FK_ERR_VALUE, "task graph: not a JSON object (%s)", jp.err.c_str());
+    const JVal *ver = doc.get("version"), *am = doc.get("active_m"), *tasks = doc.get("tasks"), *pipe = doc.get("decode_pipeline"), *caps = doc.get("decode_capabilities");
+    if (!ver || !ver->is_int() || (int)ver->num != 2) return fail(FK_ERR_VALUE, "task graph: version %d (this runtime reads 2)", ver && ver->kind == JVal::NUM ? (int)ver->num : -1);
+    if (am && am->is_int() && (int)am->num != 1) return fail(FK_ERR_VALUE, "task graph: active_m %d (only batch-1 decode graphs are dispatchable)", (int)am->num);
+    if (caps) { const JVal *d = caps->get("dispatchable"); if (d && d->kind == JVal::BOOL && !d->b) return fail(FK_ERR_VALUE, "task graph is marked not dispatchable"); }
+    if (!tasks || tasks->kind != JVal::ARR || !pipe || pipe->kind != JVal::ARR) return fail(FK_ERR_VALUE, "task graph: tasks / decode_pipeline missing");
+    std::map<long long, const JVal *> by_id;
+    for (const JVal &t : tasks->arr) { const JVal *id = t.get("id"); if (id && id->is_int()) by_id[(long long)id->num] = &t; }
+    std::map<std::string, uint64_t> table;
+    for (int r = 0; r < n_roles; ++r) if (roles[r].role) table[roles[r].role] = roles[r].value;
+    *n_out = (int)pipe->arr.size();
+    if (!tasks_out) return FK_OK;                       // size query
+    if (cap < *n_out) return fail(FK_ERR_VALUE, "tasks_out holds %d entries, %d needed", cap, *n_out);
+    for (size_t j = 0; j < pipe->arr.size(); ++j) {
+        const JVal &idv = pipe->arr[j];
+        if (!idv.is_int() || !by_id.count((long long)idv.num)) return fail(FK_ERR_VALUE, "decode_pipeline[%zu] names no task", j);
+        const JVal &t = *by_id[(long long)idv.num];
+        fk_task &o = tasks_out[j]; memset(&o, 0, sizeof o);
+        const JVal *kind = t.get("kind"), *layer = t.get("layer_idx"), *ia = t.get("iargs"), *fa = t.get("fargs"), *eb = t.get("extra_bindings");
+        if (!kind || !kind->is_int() || kind->num < 0 || kind->num >= FK_TASK_KIND_COUNT) return fail(FK_ERR_VALUE, "task %lld: missing or unknown kind", (long long)idv.num);
+        o.kind = (int32_t)kind->num; o.layer = layer && layer->is_int() ? (int32_t)layer->num : -1;
+        if (ia && ia->kind == JVal::ARR) { if (ia->arr.size() > 8) return fail(FK_ERR_VALUE, "task %lld: more than 8 iargs", (long long)idv.num);
+                                            for (size_t q = 0; q < ia->arr.size(); ++q) o.iarg[q] = (int32_t)ia->arr[q].num; }
+        if (fa && fa->kind == JVal::ARR) { if (fa->arr.size() > 4) return fail(FK_ERR_VALUE, "task %lld: more than 4 fargs", (long long)idv.num);
+                                            for (size_t q = 0; q < fa->arr.size(); ++q) o.farg[q] = (float)fa->arr[q].num; }
+        if (eb && eb->kind == JVal::ARR) for (const JVal &bnd : eb->arr) {
+            const JVal *slot = bnd.get("slot"), *role = bnd.get("role");
+            if (!slot || !slot->is_int() || !role || role->kind != JVal::STR) return fail(FK_ERR_VALUE, "task %lld: malformed binding", (long long)idv.num);
+            if (slot->num >= 100) continue;             // uniforms the runtime owns (token_id_in, layer_offset, next_token_out)
+            if (slot->num < 0 || slot->num >= 12) return fail(FK_ERR_VALUE, "task %lld: buffer slot %d out of range", (long long)idv.num, (int)slot->num);
+            auto it = table.find(role->str);
+            if (it == table.end()) return fail(FK_ERR_VALUE, "task %lld: role '%s' is not in the binding table", (long long)idv.num, role->str.c_str());
+            o.buf[(int)slot->num] = it->second;
+        }
+    }
+    return FK_OK;
+}
+extern "C" fk_status fk_graph_capture_json(fk_handle h, const char *json_text, const fk_role_binding *roles, int n_roles, fk_graph *out) {
+    int n = 0;
+    fk_status s = fk_tasks_from_json(json_text, roles, n_roles, nullptr, 0, &n); if (s) return s;
+    if (n <= 0) return fail(FK_ERR_VALUE, "task graph: empty decode_pipeline");
+    std::vector<fk_task> tasks((size_t)n);
+    s = fk_tasks_from_json(json_text, roles, n_roles, tasks.data(), n, &n); if (s) return s;
+    return fk_graph_capture(h, tasks.data(), n, out);
 }
 extern "C" fk_status fk_graph_node_count(fk_handle h, fk_graph gid, int *n_out) {
     CTX(h); Graph *g = get_g(c, gid);

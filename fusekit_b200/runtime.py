@@ -403,6 +403,36 @@ class DecodeEngine:
             out.append(N.Task.make(t["kind"], t.get("layer_idx", -1), bufs, t["iargs"], t["fargs"]))
         return out
 
+    def role_table(self, graph: dict) -> list:
+        """(role, address-or-weight-id) for every explicit binding of the document: the table the library's own JSON reader
+        (fk_tasks_from_json / fk_graph_capture_json) resolves role strings through."""
+        roles = sorted({b["role"] for t in graph["tasks"] for b in t["extra_bindings"] if b["slot"] < 100})
+        return [(r, self._resolve(r)) for r in roles]
+
+    def dispatches_from_json(self, text: str, table=None) -> list:
+        """The fk_task list of a task_graph.json text as the library parses it (no Python between the file and the records)."""
+        import json
+        table = self.role_table(json.loads(text)) if table is None else table
+        L = N.lib()
+        arr = (N.RoleBinding * max(1, len(table)))(*[N.RoleBinding(r.encode(), int(v)) for r, v in table])
+        n = C.c_int32()
+        N.check(L.fk_tasks_from_json(text.encode(), arr, len(table), None, 0, C.byref(n)), "fk_tasks_from_json")
+        out = (N.Task * max(1, n.value))()
+        N.check(L.fk_tasks_from_json(text.encode(), arr, len(table), out, n.value, C.byref(n)), "fk_tasks_from_json")
+        return list(out)[: n.value]
+
+    def capture_json(self, text: str) -> int:
+        """Capture the decode step straight from a task_graph.json text (reference: load_dispatcher + build_icb,
+        python_runtime/src/lib.rs:115-169, 459-570)."""
+        import json
+        table = self.role_table(json.loads(text))
+        arr = (N.RoleBinding * len(table))(*[N.RoleBinding(r.encode(), int(v)) for r, v in table])
+        g = C.c_uint64()
+        N.check(self.rt.L.fk_graph_capture_json(self.rt.h, text.encode(), arr, len(table), C.byref(g)), "fk_graph_capture_json")
+        self.tasks = self.replay = self.dispatches_from_json(text, table)
+        self.graph = g.value
+        return self.graph
+
     def build_dispatches(self) -> list:
         """The per-token kernel list in replay order (reference order: embed -> per layer RmsNormQkv,
         SDPA, LinearResidual, gate/up chain, LinearResidual -> final head -> argmax;

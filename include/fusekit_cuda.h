@@ -199,6 +199,14 @@ fk_status fk_state_get(fk_handle h, uint32_t *token, uint32_t *offset, uint32_t 
 /* ---- per-token graph (reference: build_icb lib.rs:459-570, execute_icb lib.rs:718-760,
  *      submit_icb_async / wait_pending_icb lib.rs:659-715, profile_icb_commands lib.rs:821-869) - */
 fk_status fk_graph_capture(fk_handle h, const fk_task *tasks, int n, fk_graph *out);
+/* The file-level boundary: a v2 task_graph.json (src/codegen/task_graph_json.rs:33-226; reader src/runtime/plan.rs:39-164 and
+ * load_dispatcher, python_runtime/src/lib.rs:115-169) parsed inside the library.  The caller supplies the table that maps
+ * every role string of the document (slot_role_key, src/codegen/kernels/mod.rs:5531-5576: param.*, layer_param.<i>.*,
+ * layer_cache_k.<i>, layer_scratch.*, global_scratch.*) to a device address or fk_weight id; tasks come out in
+ * decode_pipeline order.  fk_tasks_from_json with tasks_out = NULL only counts; it needs no device. */
+typedef struct fk_role_binding { const char *role; uint64_t value; } fk_role_binding;
+fk_status fk_tasks_from_json(const char *json_text, const fk_role_binding *roles, int n_roles, fk_task *tasks_out, int cap, int *n_out);
+fk_status fk_graph_capture_json(fk_handle h, const char *json_text, const fk_role_binding *roles, int n_roles, fk_graph *out);
 fk_status fk_graph_launch(fk_handle h, fk_graph g, double *gpu_seconds);
 fk_status fk_graph_launch_async(fk_handle h, fk_graph g);
 fk_status fk_wait(fk_handle h, double *gpu_seconds);

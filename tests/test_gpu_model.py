@@ -332,3 +332,20 @@ def test_task_graph_file_drives_the_same_dispatch_list(runtime, tmp_path):
     a = eng.build_dispatches()
     b = eng.dispatches_from(task_graph.read(tmp_path / "task_graph.json"))
     assert len(a) == len(b) and all(bytes(x) == bytes(y) for x, y in zip(a, b))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["tiny-qwen", "tiny-gemma"])
+def test_graph_captured_from_json_text_decodes_the_same_tokens(runtime, tmp_path, name):
+    """The library's own reader: fk_graph_capture_json on the file's text + the role table replays the same decode as the
+    fk_task list resolved on the host."""
+    from fusekit_b200 import task_graph
+    eng = DecodeEngine(CONFIGS[name], 256, runtime=runtime)
+    eng.load_synthetic(); eng.prefill_kv_synthetic(12)
+    task_graph.write(tmp_path / "task_graph.json", eng.task_graph())
+    want, _ = eng.decode_chunk(12, 5, 24)
+    eng.graph = 0
+    eng.capture_json((tmp_path / "task_graph.json").read_text())
+    eng.prefill_kv_synthetic(12)
+    got, _ = eng.decode_chunk(12, 5, 24)
+    assert np.array_equal(got, want)

@@ -132,3 +132,43 @@ def test_fused_peer_exchange_graph_has_no_allreduce_tasks():
     assert head["kind"] == TG.K_HEAD and head["iargs"][3] == 0 and head["iargs"][4:6] == [2 * L, 2 * L + 1]
     with pytest.raises(ValueError):
         TG.emit(spec, 4352, tp_rank=0, tp_size=8, fused_weights=False, tp_exchange="peer")
+
+
+def _records(tasks):
+    return [bytes(t) for t in tasks]
+
+
+@pytest.mark.parametrize("name,world,mode,kvb", [("qwen2.5-7b", 1, "allreduce", 0), ("gemma3-4b", 1, "allreduce", 0), ("qwen2.5-32b", 8, "peer", 0),
+                                                   ("qwen2.5-7b", 2, "allreduce", 0), ("tiny-qwen", 1, "allreduce", 8)])
+def test_library_json_reader_matches_the_python_resolution(name, world, mode, kvb):
+    """The C-ABI reader (fk_tasks_from_json) turns the document text + a role table into byte-identical fk_task records to the
+    Python resolution, pretty-printed or compact."""
+    spec = CONFIGS[name]
+    e = _fake_engine(spec, world, world - 1, True)
+    e.tp_exchange, e.kv_bits = mode, kvb
+    if kvb:
+        e.cacheq = [{k: 0x700000 + 64 * l + i for i, k in enumerate(["k", "k_scales", "k_biases", "v", "v_scales", "v_biases"])} for l in range(spec.n_layers)]
+    g = e.task_graph()
+    want = _records(e.dispatches_from(g))
+    for text in (json.dumps(g, indent=2), json.dumps(g, separators=(",", ":"))):
+        got = _records(e.dispatches_from_json(text))
+        assert got == want
+
+
+def test_library_json_reader_refusals():
+    from fusekit_b200 import _native as N
+    e = _fake_engine(CONFIGS["tiny-qwen"])
+    g = e.task_graph()
+    table = e.role_table(g)
+    for bad, word in (({**g, "version": 1}, "version"), ({**g, "active_m": 16}, "active_m"),
+                      ({**g, "decode_capabilities": {"dispatchable": False, "reasons": []}}, "dispatchable"),
+                      ({**g, "decode_pipeline": [9999]}, "names no task")):
+        with pytest.raises(N.FusekitError, match=word):
+            e.dispatches_from_json(json.dumps(bad), table)
+    with pytest.raises(N.FusekitError, match="not a JSON object"):
+        e.dispatches_from_json('{"version": 2, "tasks": [', table)
+    with pytest.raises(N.FusekitError, match="layer_scratch.q_buf"):
+        e.dispatches_from_json(json.dumps(g), [(r, v) for r, v in table if r != "layer_scratch.q_buf"])
+    worse = json.loads(json.dumps(g)); worse["tasks"][0]["kind"] = 99
+    with pytest.raises(N.FusekitError, match="kind"):
+        e.dispatches_from_json(json.dumps(worse), table)
