@@ -9,6 +9,8 @@
 #include "fk_qmm.cuh"
 #include "fk_qmm_tc.cuh"
 #include "fk_json.h"
+#include <chrono>
+#include <thread>
 
 #include <dlfcn.h>
 #include <math.h>
@@ -40,6 +42,8 @@ struct Nccl {
     int (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     int (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     int (*CommDestroy)(ncclComm_t) = nullptr;
+    int (*CommAbort)(ncclComm_t) = nullptr;
+    int (*CommGetAsyncError)(ncclComm_t, int *) = nullptr;
     const char *(*GetErrorString)(int) = nullptr;
 };
 static Nccl g_nccl;
@@ -53,6 +57,8 @@ static fk_status nccl_load() {
     g_nccl.AllReduce = (int (*)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t))dlsym(g_nccl.dl, "ncclAllReduce");
     g_nccl.CommDestroy = (int (*)(ncclComm_t))dlsym(g_nccl.dl, "ncclCommDestroy");
     g_nccl.GetErrorString = (const char *(*)(int))dlsym(g_nccl.dl, "ncclGetErrorString");
+    g_nccl.CommAbort = (int (*)(ncclComm_t))dlsym(g_nccl.dl, "ncclCommAbort");
+    g_nccl.CommGetAsyncError = (int (*)(ncclComm_t, int *))dlsym(g_nccl.dl, "ncclCommGetAsyncError");
     if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce) return fail(FK_ERR_NCCL, "libnccl lacks required symbols");
     return FK_OK;
 }
@@ -83,6 +89,7 @@ struct Ctx {
     float *qmm_scratch = nullptr; unsigned int *qmm_counters = nullptr;   // K-split partial sums and tickets of the several-row projection
     bool use_tiled = true; int stages = FK_STAGES; int force_warps = 0; int force_split = -1; bool qmm_tc = false; int wide_upto = 3; bool sdpa_cluster = true; bool sdpa_mma = true; int sdpa_cl = 0;
     ncclComm_t comm = nullptr; int rank = 0, world = 1;
+    bool comm_lost = false; long comm_timeout_ms = 0;
     unsigned long long *timeline = nullptr; int timeline_task = 0;      // tuning aid: per-task slices of 512 x 8 stamps
     long long launches = 0;
     uint32_t vocab = 0;                         // rows of the embedding table of the last embed task seen (0 = unknown)
@@ -130,6 +137,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     CU(cudaMalloc(&c->history, sizeof(uint32_t) * c->hist_cap)); CU(cudaMemset(c->history, 0, sizeof(uint32_t) * c->hist_cap));
     CU(cudaMallocHost(&c->pinned, sizeof(uint32_t) * (c->hist_cap + 64)));
     const char *e = getenv("FK_PDL"); if (e && e[0] == '0') c->pdl = false;
+    e = getenv("FK_COMM_TIMEOUT_MS"); if (e) c->comm_timeout_ms = atol(e);
     e = getenv("FK_LAYOUT"); if (e && !strcmp(e, "mlx")) c->use_tiled = false;
     e = getenv("FK_SDPA"); if (e && !strcmp(e, "ticket")) c->sdpa_cluster = false;
     if (e && !strcmp(e, "mma")) c->sdpa_mma = true;
@@ -718,6 +726,7 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             else e = launch(c, k_allreduce_peer<float, false>, dim3(nbk), dim3(256), 0, (float *)b[0], i[0], c->peers, c->state);
             break;
         }
+        if (c->comm_lost) return fail(FK_ERR_STATE, "the communicator was aborted after an error; open a new context");
         if (!c->comm) return fail(FK_ERR_STATE, "allreduce task without fk_comm_init");
         const int dtype = i[1] == 1 ? 5 /* ncclUint64 */ : 7 /* ncclFloat32 */, op = i[1] == 1 ? 2 /* ncclMax */ : 0 /* ncclSum */;
         int r = g_nccl.AllReduce((const void *)b[0], (void *)b[0], (size_t)i[0], dtype, op, c->comm, c->stream);
@@ -858,6 +867,47 @@ extern "C" fk_status fk_graph_capture(fk_handle h, const fk_task *tasks, int n, 
     c->graphs.push_back(g); *out = c->graphs.size();
     return FK_OK;
 }
+// ------------------------------------------------------------------ waiting with a communicator attached
+// A rank whose peer died would wait in cudaStreamSynchronize for ever: the collective kernel never completes.  With a
+// communicator the wait polls the stream and ncclCommGetAsyncError instead; on an asynchronous error (or after
+// FK_COMM_TIMEOUT_MS without progress, off by default) the communicator is aborted, which ends its kernels, the stream is
+// drained and the call returns FK_ERR_NCCL.  The context then refuses further token replays (its graphs hold collective
+// nodes of the dead communicator).  Reference analogue: strict dispatch / fallback on a failed submit
+// (python/fusekit_runtime/__init__.py:2889-2895).
+static fk_status comm_check(Ctx *c) {
+    if (!c->comm || !g_nccl.CommGetAsyncError) return FK_OK;
+    int async = 0;
+    const int r = g_nccl.CommGetAsyncError(c->comm, &async);
+    if (r == 0 && (async == 0 || async == 7 /* ncclInProgress */)) return FK_OK;
+    const int code = r != 0 ? r : async;
+    if (g_nccl.CommAbort) g_nccl.CommAbort(c->comm); else if (g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
+    c->comm = nullptr; c->comm_lost = true;
+    return fail(FK_ERR_NCCL, "communicator error (%s); communicator aborted", g_nccl.GetErrorString ? g_nccl.GetErrorString(code) : "async error");
+}
+static fk_status stream_wait(Ctx *c) {
+    if (!c->comm) { CU(cudaStreamSynchronize(c->stream)); return FK_OK; }
+    const auto t0 = std::chrono::steady_clock::now();
+    for (unsigned spins = 0;; ++spins) {
+        const cudaError_t q = cudaStreamQuery(c->stream);
+        if (q == cudaSuccess) break;
+        if (q != cudaErrorNotReady) { CU(q); }
+        fk_status s = comm_check(c);
+        if (s) { cudaStreamSynchronize(c->stream); return s; }
+        if (c->comm_timeout_ms > 0 && (spins & 255) == 255) {
+            const long ms = (long)std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+            if (ms > c->comm_timeout_ms) {
+                if (g_nccl.CommAbort) g_nccl.CommAbort(c->comm);
+                c->comm = nullptr; c->comm_lost = true;
+                cudaStreamSynchronize(c->stream);
+                return fail(FK_ERR_NCCL, "no progress for %ld ms with a collective in flight; communicator aborted", ms);
+            }
+        }
+        if (spins > 2000) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    return comm_check(c);          // an error raised while the last kernels drained
+}
+extern "C" fk_status fk_comm_check(fk_handle h) { CTX(h); if (c->comm_lost) return fail(FK_ERR_STATE, "the communicator was aborted after an error"); return comm_check(c); }
+
 // ------------------------------------------------------------------ task_graph.json behind the C ABI
 // The file-level boundary of the reference: load_dispatcher(metallib, task_graph) reads the document and the host resolves
 // every role string to a live buffer (python_runtime/src/lib.rs:115-169; src/runtime/plan.rs:39-164, 409-431).  Here the
@@ -932,7 +982,7 @@ extern "C" fk_status fk_wait(fk_handle h, double *gpu_seconds) {
     CTX(h);
     if (!c->pending) return fail(FK_ERR_STATE, "nothing pending");
     c->pending = false;
-    CU(cudaEventSynchronize(c->ev1));
+    { fk_status s = stream_wait(c); if (s) return s; }
     float ms = 0.0f; CU(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
     if (gpu_seconds) *gpu_seconds = ms * 1e-3;
     return FK_OK;
@@ -997,6 +1047,7 @@ extern "C" fk_status fk_decode_chunk(fk_handle h, fk_graph gid, uint32_t base_of
     if (!g) return fail(FK_ERR_VALUE, "bad graph id");
     if (count <= 0 || (uint32_t)count > c->hist_cap) return fail(FK_ERR_VALUE, "count must be in 1..%u", c->hist_cap);
     if (c->pending) return fail(FK_ERR_STATE, "a launch is pending; call fk_wait");
+    if (c->comm_lost) return fail(FK_ERR_STATE, "the communicator was aborted after an error; open a new context");
     fk_status s = set_state(c, seed_token, base_offset); if (s) return s;
     CU(cudaEventRecord(c->ev0, c->stream));
     for (int j = 0; j < count; ++j) CU(cudaGraphLaunch(g->exec, c->stream));
@@ -1004,7 +1055,7 @@ extern "C" fk_status fk_decode_chunk(fk_handle h, fk_graph gid, uint32_t base_of
     uint32_t *hist = c->pinned + 64;
     CU(cudaMemcpyAsync(hist, c->history, sizeof(uint32_t) * count, cudaMemcpyDeviceToHost, c->stream));
     CU(cudaMemcpyAsync(c->pinned + 32, c->state, sizeof(FkState), cudaMemcpyDeviceToHost, c->stream));
-    CU(cudaStreamSynchronize(c->stream));
+    s = stream_wait(c); if (s) return s;
     float ms = 0.0f; CU(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
     if (gpu_seconds) *gpu_seconds = ms * 1e-3;
     if (out_history) memcpy(out_history, hist, sizeof(uint32_t) * count);
@@ -1033,7 +1084,7 @@ extern "C" fk_status fk_decode_chunk_rows(fk_handle h, fk_graph gid, uint32_t ba
     uint32_t *hist = c->pinned + 64;
     CU(cudaMemcpyAsync(hist, c->history, sizeof(uint32_t) * count * rows, cudaMemcpyDeviceToHost, c->stream));
     CU(cudaMemcpyAsync(c->pinned + 32, c->state, sizeof(FkState), cudaMemcpyDeviceToHost, c->stream));
-    CU(cudaStreamSynchronize(c->stream));
+    { fk_status s = stream_wait(c); if (s) return s; }
     float ms = 0.0f; CU(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
     if (gpu_seconds) *gpu_seconds = ms * 1e-3;
     if (out_history) memcpy(out_history, hist, sizeof(uint32_t) * count * rows);

@@ -270,6 +270,11 @@ fk_status fk_peer_arena_loopback(fk_handle h, int rank, int world, uint32_t spin
 /* ---- tensor parallelism (no reference counterpart; NCCL over NVLink) ------ */
 fk_status fk_comm_unique_id(void *id128, size_t cap);          /* rank 0 makes the 128-byte id */
 fk_status fk_comm_init(fk_handle h, const void *id128, int rank, int world);
+/* Poll the communicator for an asynchronous error (ncclCommGetAsyncError); on one the communicator is aborted and
+ * FK_ERR_NCCL returned, afterwards FK_ERR_STATE.  fk_wait / fk_decode_chunk[_rows] poll the same way while they wait, so a
+ * rank whose peer died returns instead of blocking; FK_COMM_TIMEOUT_MS (environment, off by default) bounds the wait with a
+ * collective in flight.  No counterpart in the reference (single device). */
+fk_status fk_comm_check(fk_handle h);
 
 #ifdef __cplusplus
 }

@@ -69,3 +69,46 @@ def test_close_releases_device_memory():
         if i == 0:
             free0 = free
     assert free >= free0 - (8 << 20), (free0, free)
+
+
+FAKE_NCCL_WORKER = r"""
+import ctypes as C, os, sys
+sys.path.insert(0, {root!r})
+from fusekit_b200 import _native as N
+from fusekit_b200.model_spec import CONFIGS
+from fusekit_b200.runtime import DecodeEngine, comm_unique_id
+fake = C.CDLL(os.environ["FK_NCCL_LIB"], mode=C.RTLD_GLOBAL)
+eng = DecodeEngine(CONFIGS["tiny-qwen"], 64, device=0, tp_rank=0, tp_size=2)
+eng.comm_init(comm_unique_id())
+eng.load_synthetic(); eng.prefill_kv_synthetic(8)
+toks, _ = eng.decode_chunk(8, 3, 4)                       # collectives are no-ops here: only the control flow matters
+assert len(toks) == 4 and fake.fake_nccl_allreduce_count() > 0
+assert eng.rt.L.fk_comm_check(eng.rt.h) == 0
+fake.fake_nccl_set_async_error(6)                         # ncclRemoteError: a peer went away
+out = (C.c_uint32 * 4)()
+st = eng.rt.L.fk_decode_chunk(eng.rt.h, eng.graph, 12, int(toks[-1]), 4, out, None)
+assert st == -4 and b"aborted" in eng.rt.L.fk_last_error(), (st, eng.rt.L.fk_last_error())
+assert fake.fake_nccl_abort_count() == 1
+st = eng.rt.L.fk_decode_chunk(eng.rt.h, eng.graph, 12, int(toks[-1]), 4, out, None)      # refused before anything is launched
+assert st == -3 and fake.fake_nccl_abort_count() == 1, (st, eng.rt.L.fk_last_error())
+assert eng.rt.L.fk_comm_check(eng.rt.h) == -3
+eng.close()
+print("fake-nccl ok")
+"""
+
+
+def test_communicator_error_aborts_and_reaches_the_host(tmp_path):
+    """The library polls ncclCommGetAsyncError while it waits; on an asynchronous error it aborts the communicator, returns
+    FK_ERR_NCCL and refuses further replays.  The failure is injected on the host through a stand-in libnccl (no collective
+    runs, no GPU fault); a child process so the stand-in is the first NCCL the library loads."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    so = tmp_path / "libfakenccl.so"
+    subprocess.check_call(["gcc", "-shared", "-fPIC", "-O1", "-o", str(so), os.path.join(root, "tests", "fake_nccl.c")])
+    script = tmp_path / "worker.py"
+    script.write_text(FAKE_NCCL_WORKER.format(root=root))
+    env = dict(os.environ, FK_NCCL_LIB=str(so))
+    p = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0 and "fake-nccl ok" in p.stdout, (p.stdout + p.stderr)[-3000:]
