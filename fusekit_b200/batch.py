@@ -134,8 +134,9 @@ class BatchDecodeEngine:
                 T(N.TASK_SDPA_DECODE, l, {0: self.q, 1: ck, 2: cv, 3: self.sdpa, 4: self.sdpa_part, 5: self.sdpa_counter},
                   [s.n_q, s.n_kv, hd, self.capacity, 0, M, int(self.consecutive)], [scale]),
                 T(N.TASK_LINEAR_RESIDUAL, l, {0: self.sdpa, 1: self.W[f"layers.{l}.o"], 2: self.x_ptr(l), 3: self.hb_ptr(l)}, [s.n_q * hd, H, M, 0, 0, q]),
-                T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: self.hb_ptr(l), 1: self.V[f"layers.{l}.post_attention_norm"], 2: self.W[f"layers.{l}.gateup"],
-                                                  4: self.act}, [H, I, 0, M], [s.eps]),
+                # the norm runs once for all blocks; the gate/up product takes the rows as they are (no norm weight bound)
+                T(N.TASK_RMSNORM_ROWS, l, {0: self.hb_ptr(l), 1: self.V[f"layers.{l}.post_attention_norm"], 2: self.xn}, [H, M], [s.eps]),
+                T(N.TASK_RMSNORM_GATEUP_ACT, l, {0: self.xn, 2: self.W[f"layers.{l}.gateup"], 4: self.act}, [H, I, 0, M], [s.eps]),
                 T(N.TASK_LINEAR_RESIDUAL, l, {0: self.act, 1: self.W[f"layers.{l}.down"], 2: self.hb_ptr(l), 3: self.x_ptr(l + 1)}, [I, H, M, 0, 0, q]),
             ]
         L = s.n_layers

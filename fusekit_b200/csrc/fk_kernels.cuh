@@ -865,7 +865,7 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
     const size_t row = blockIdx.z, seq = a.consecutive ? 0 : row;     // row of a batch: its own q and output; sequence: its own cache
     a.q += row * (size_t)a.n_q * HD; a.out += row * (size_t)a.n_q * HD;
     const uint16_t *K = a.ck + (seq * a.n_kv + kvh) * (size_t)a.capacity * HD, *V = a.cv + (seq * a.n_kv + kvh) * (size_t)a.capacity * HD;
-    if (tid == 0 && k_begin < k_end) {           // every row but the newest predates the QKV kernel in flight: warm L2 meanwhile
+    if (tid == 0 && k_begin < k_end && a.rows <= 1) {           // every row but the newest predates the QKV kernel in flight: warm L2 meanwhile (one sequence: its cache fits L2)
         const uint32_t bytes = (uint32_t)(k_end - k_begin) * HD * 2;
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(K + (size_t)k_begin * HD), "r"(bytes) : "memory");
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(V + (size_t)k_begin * HD), "r"(bytes) : "memory");
@@ -1205,15 +1205,34 @@ __global__ void k_residual_add(const float *sum, const uint16_t *residual, uint1
 struct NormRowsArgs { const uint16_t *x, *w; uint16_t *y; int h, rows; float eps; };
 // y[m, :] = T(w * T(x[m, :] * r_m)), r_m = 1 / sqrt(mean(x[m]^2) + eps): the two roundings of the fused kernels
 // (src/codegen/kernels/mod.rs:4464-4472), one block per row
-__global__ void __launch_bounds__(256) k_rmsnorm_rows(const FkState *st, NormRowsArgs a) {
+__global__ void __launch_bounds__(1024) k_rmsnorm_rows(const FkState *st, NormRowsArgs a) {
     __shared__ float red[40];
     pdl_wait(); pdl_launch_dependents();
     const uint16_t *x = a.x + (size_t)blockIdx.x * a.h; uint16_t *y = a.y + (size_t)blockIdx.x * a.h;
+    // eight values per thread and round in registers between the two passes (h a multiple of 8: the rows are 16-byte aligned)
+    const int nv = a.h / 8;
+    uint4 keep = make_uint4(0, 0, 0, 0);
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < a.h; i += blockDim.x) { const float v = bf2f(__ldcg(x + i)); ss = fmaf(v, v, ss); }
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(x) + i);
+        if (i == (int)threadIdx.x) keep = v;
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float lo = bf_lo(w[j]), hi = bf_hi(w[j]); ss = fmaf(lo, lo, ss); ss = fmaf(hi, hi, ss); }
+    }
+    for (int i = nv * 8 + threadIdx.x; i < a.h; i += blockDim.x) { const float v = bf2f(__ldcg(x + i)); ss = fmaf(v, v, ss); }
     ss = block_sum(ss, red);
     const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.h), a.eps)));
-    for (int i = threadIdx.x; i < a.h; i += blockDim.x) y[i] = f2bf(bf2f(a.w[i]) * rT(bf2f(__ldcg(x + i)) * r));
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        const uint4 v = i == (int)threadIdx.x ? keep : __ldcg(reinterpret_cast<const uint4 *>(x) + i);
+        const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(a.w) + i);
+        const uint32_t xs[4] = {v.x, v.y, v.z, v.w}, ws[4] = {wv.x, wv.y, wv.z, wv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = pack_bf16(bf_lo(ws[j]) * rT(bf_lo(xs[j]) * r), bf_hi(ws[j]) * rT(bf_hi(xs[j]) * r));
+        reinterpret_cast<uint4 *>(y)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    for (int i = nv * 8 + threadIdx.x; i < a.h; i += blockDim.x) y[i] = f2bf(bf2f(a.w[i]) * rT(bf2f(__ldcg(x + i)) * r));
 }
 struct RopeRowsArgs { const uint16_t *qkv; uint16_t *q_out, *cache_k, *cache_v; int n_q, n_kv, hd, capacity, rows; float log2theta; int consecutive; };
 // RoPE on the q and k heads of every sequence's raw projection row (q | k | v, bias already added), k and v into that

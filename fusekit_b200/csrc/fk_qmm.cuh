@@ -29,7 +29,7 @@
 
 // scratch: gridDim.x * FK_QMM_PART_FLOATS floats; counters: one per set of 8 tiles, zero before the launch and after it
 // GATEUP form: W holds gate/up row pairs (tile rows g = gate, g + 8 = up of output tile * 8 + g), x is normalised on the
-// way into shared memory (norm_w, eps), y[m][n] takes the activation (act: 0 SwiGLU, 1 GeGLU-tanh); n = outputs per row.
+// way into shared memory (norm_w, eps; norm_w == nullptr: x is normalised already), y[m][n] takes the activation (act: 0 SwiGLU, 1 GeGLU-tanh); n = outputs per row.
 struct QmmArgs { const uint16_t *x; TiledW W; const uint16_t *residual; uint16_t *y; float *scratch; unsigned int *counters; int m, k, n, kparts;
                  const uint16_t *norm_w; float eps; int act; };
 
@@ -70,7 +70,9 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmA
     };
     while (issued < FK_STAGES && issued < total) issue();                    // weights are constants: fetched before the wait below
     pdl_wait();
-    if (GATEUP) {                                                            // RMSNorm scale of every row, over the whole of K
+    // norm_w == nullptr: the rows come in normalised already (a separate RMSNorm kernel ran once for all blocks)
+    const bool norm = GATEUP && a.norm_w != nullptr;
+    if (norm) {                                                              // RMSNorm scale of every row, over the whole of K
         if (tid < FK_QMM_MAXM && tid >= a.m) s_r[tid] = 0.0f;
         for (int mm = wid; mm < a.m; mm += FK_QMM_WARPS) {
             float ss = 0.0f;
@@ -96,7 +98,7 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmA
     // loads are separate from the permute + store so that the arithmetic of a step sits between the two.
     const int items = nbs * 8 * (FK_QMM_KC / 8);
     auto stage_load = [&](int ss, uint4 (&v)[4], uint4 &wv) {
-        if (GATEUP) {                                                        // a thread's four items share their k range: one vector of norm weights
+        if (norm) {                                                          // a thread's four items share their k range: one vector of norm weights
             const int k0 = ss * FK_QMM_KC + (tid & 63) * 8;
             wv = k0 < a.k ? __ldg(reinterpret_cast<const uint4 *>(a.norm_w + k0)) : make_uint4(0, 0, 0, 0);
         }
@@ -113,7 +115,7 @@ __global__ void __launch_bounds__(FK_QMM_WARPS * 32, 2) k_qmm4(FkState *st, QmmA
         for (int q = 0; q < 4; ++q) {
             const int idx = tid + q * FK_QMM_WARPS * 32, m = idx >> 6, item = idx & 63;
             uint32_t h[4] = {v[q].x, v[q].y, v[q].z, v[q].w};            // (x0,x1) (x2,x3) (x4,x5) (x6,x7)
-            if (GATEUP) {                                                // y = T(w * T(x * r)), two roundings as in the one-row kernel
+            if (norm) {                                                  // y = T(w * T(x * r)), two roundings as in the one-row kernel
                 float f[8], wf[8]; unpack8(v[q], f); unpack8(wv, wf);
                 const float r = s_r[m & (FK_QMM_MAXM - 1)];
 #pragma unroll

@@ -592,7 +592,12 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             if (i[5] > FK_MAX_ROWS || G > 8) return fail(FK_ERR_VALUE, "sdpa: at most %d sequences", FK_MAX_ROWS);
             a.rows = i[5]; a.consecutive = i[6] ? 1 : 0;
             const size_t smem = sdpa_mma_smem_bytes(G, hd);
-            const int cl = c->sdpa_cl > 0 ? c->sdpa_cl : FK_SDPA_CL;
+            // one CTA of this kernel fills an SM (16 warps x 128 registers), so the CTAs of all sequences should fit the SMs at
+            // once: 8 per kv head only while rows x kv heads x 8 does, down to one CTA that walks a whole cache (16 sequences of
+            // the 32B shape: 128 CTAs; with 8 per kv head the 1024 CTAs took eight waves, 157 us a layer)
+            int cl = FK_SDPA_CL;
+            while (cl > 1 && cl * nkv * i[5] > c->sm_count) cl >>= 1;
+            if (c->sdpa_cl > 0) cl = c->sdpa_cl;
             const dim3 cgrid(cl, nkv, i[5]), cblock(FK_SDPA_CW * 32);
             if (hd == 64) e = launch_cluster(c, k_sdpa_mma<64>, cgrid, cblock, smem, cl, (const FkState *)c->state, a);
             else if (hd == 128) e = launch_cluster(c, k_sdpa_mma<128>, cgrid, cblock, smem, cl, (const FkState *)c->state, a);
@@ -741,7 +746,8 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
     case FK_TASK_RMSNORM_ROWS: {
         if (!b[0] || !b[1] || !b[2] || i[0] <= 0 || i[1] <= 0 || i[1] > FK_MAX_ROWS) return fail(FK_ERR_VALUE, "rmsnorm_rows: bad arguments");
         NormRowsArgs a{(const uint16_t *)b[0], (const uint16_t *)b[1], (uint16_t *)b[2], i[0], i[1], f[0]};
-        e = launch(c, k_rmsnorm_rows, dim3(i[1]), dim3(256), 0, (const FkState *)c->state, a);
+        if (i[0] % 8 || (b[0] | b[1] | b[2]) % 16) return fail(FK_ERR_VALUE, "rmsnorm_rows: hidden size must be a multiple of 8 and the buffers 16-byte aligned");
+        e = launch(c, k_rmsnorm_rows, dim3(i[1]), dim3(i[0] >= 8192 ? 1024 : i[0] >= 2048 ? 512 : 256), 0, (const FkState *)c->state, a);
         break;
     }
     case FK_TASK_ROPE_STORE_ROWS: {

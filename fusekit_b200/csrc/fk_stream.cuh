@@ -45,6 +45,9 @@ __host__ __device__ inline int unit_k(int bits) { return bits == 4 ? 512 : bits 
 #ifndef FK_J_UNROLL
 #define FK_J_UNROLL 8                   // unroll factor of the group loop inside a unit (code size against scheduling freedom)
 #endif
+#ifndef FK_COLDIGITS
+#define FK_COLDIGITS 1                  // 4-bit units: the digits of a group on the accumulator columns (0: groups on the columns)
+#endif
 #define FK_STR(x) #x
 #define FK_UNROLL(n) _Pragma(FK_STR(unroll n))
 
@@ -189,26 +192,36 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
     constexpr int TPG = BITS == 4 ? 8 : 4;          // threads per group
 #pragma unroll
     for (int o = 1; o < TPG; o <<= 1) { s8 += __shfl_xor_sync(0xffffffffu, s8, o); m8 = fmaxf(m8, __shfl_xor_sync(0xffffffffu, m8, o)); }
-    // scale = 2^(20 - exponent(max)): the largest activation becomes an integer in [2^20, 2^21)
-    int e = m8 > 0.0f ? (int)((__float_as_uint(m8) >> 23) & 0xffu) - 127 : 20;
+    // scale = 2^(XB - exponent(max)): the largest activation becomes an integer in [2^XB, 2^(XB+1)).  XB = 20 with unsigned low
+    // digits; 19 with balanced digits (4-bit column form), where v + 8256 must stay below 2^21 for the top digit to fit s8
+    constexpr bool BAL = BITS == 4 && FK_COLDIGITS;
+    constexpr int XB = BAL ? 19 : 20;
+    int e = m8 > 0.0f ? (int)((__float_as_uint(m8) >> 23) & 0xffu) - 127 : XB;
     e = e < -100 ? -100 : (e > 100 ? 100 : e);
-    const float scale = __uint_as_float((uint32_t)(127 + 20 - e) << 23), inv = __uint_as_float((uint32_t)(127 - 20 + e) << 23);
+    const float scale = __uint_as_float((uint32_t)(127 + XB - e) << 23), inv = __uint_as_float((uint32_t)(127 - XB + e) << 23);
     if (!valid) return;
-    // three 7-bit digits of the 21-bit integers (d0, d1 unsigned, d2 signed): byte 0 of xi, xi >> 7, xi >> 14, gathered four at
-    // a time with byte permutes and masked as a word
+    // three 7-bit digits of the integers: byte 0 of xi, xi >> 7, xi >> 14, gathered four at a time with byte permutes and masked
+    // as a word.  Unsigned form: d0, d1 in [0, 127], d2 signed.  Balanced form: v + 64 + 64 * 128 is split the same way and 64
+    // taken off the two low digits again, so every digit is signed and centred -- the partial sums that different lanes
+    // accumulate (low digits / top digit) then both have random signs instead of one of them growing with K.
     uint32_t x0[8], x7[8], x14[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { const int v = __float2int_rn(f[i] * scale); x0[i] = (uint32_t)v; x7[i] = (uint32_t)(v >> 7); x14[i] = (uint32_t)(v >> 14); }
+    for (int i = 0; i < 8; ++i) { const int v = __float2int_rn(f[i] * scale) + (BAL ? 8256 : 0); x0[i] = (uint32_t)v; x7[i] = (uint32_t)(v >> 7); x14[i] = (uint32_t)(v >> 14); }
     auto bytes4 = [](uint32_t a, uint32_t b, uint32_t c, uint32_t d) {      // byte 0 of a, b, c, d
         return __byte_perm(__byte_perm(a, b, 0x0040u), __byte_perm(c, d, 0x0040u), 0x5410u);
+    };
+    auto low7 = [](uint32_t w) {                 // per byte: u = w & 127, or u - 64 as s8 (flip bit 6, copy it into bit 7)
+        if (!BAL) return w & 0x7f7f7f7fu;
+        const uint32_t t = (w & 0x7f7f7f7fu) ^ 0x40404040u;
+        return t | ((t & 0x40404040u) << 1);
     };
     if (BITS == 4) {
         const int grp = blk >> 3, bb = blk & 7;
         // [digit][lane t = bb & 3]{word A even, word B even, word A odd, word B odd}: the even nibbles of both words feed one MMA,
-        // the odd nibbles (used unshifted, as 16 q) the other
+        // the odd nibbles the other
         uint32_t *dst = reinterpret_cast<uint32_t *>(sm.xs) + (size_t)grp * 48 + (bb & 3) * 4 + (bb >> 2);
-        dst[0] = bytes4(x0[0], x0[2], x0[4], x0[6]) & 0x7f7f7f7fu; dst[2] = bytes4(x0[1], x0[3], x0[5], x0[7]) & 0x7f7f7f7fu;
-        dst[16] = bytes4(x7[0], x7[2], x7[4], x7[6]) & 0x7f7f7f7fu; dst[18] = bytes4(x7[1], x7[3], x7[5], x7[7]) & 0x7f7f7f7fu;
+        dst[0] = low7(bytes4(x0[0], x0[2], x0[4], x0[6])); dst[2] = low7(bytes4(x0[1], x0[3], x0[5], x0[7]));
+        dst[16] = low7(bytes4(x7[0], x7[2], x7[4], x7[6])); dst[18] = low7(bytes4(x7[1], x7[3], x7[5], x7[7]));
         dst[32] = bytes4(x14[0], x14[2], x14[4], x14[6]); dst[34] = bytes4(x14[1], x14[3], x14[5], x14[7]);
         if (bb == 0) sm.xsi[grp] = make_float2(s8, inv);
     } else {
@@ -499,9 +512,49 @@ __device__ __forceinline__ void unit_compute_q(uint32_t ub, const StreamSmem &sm
     acc_hi = fmaf(s11, c[3] * i1, acc_hi); acc_hi = fmaf(b11, X1, acc_hi);
 }
 
+// 4-bit units, digits on the accumulator columns.  The three digits of a group's activations share their k slots, so they can
+// sit in three columns of ONE B operand: lanes with lane / 4 = 0, 1, 2 load digit 0, 1, 2 of group J (the other lanes load
+// digit 0 again; their columns are never read), and two MMAs per group -- even nibbles, then the odd nibbles shifted down --
+// leave sum(q * digit_c) of rows g, g + 8 in columns 0..2: 16 MMAs per unit instead of 48 and no zeroed operands.  All digits
+// go in as s8 (balanced digits, see store_block).  Column c belongs to lane t = c / 2: t = 0 folds
+// d0 + 128 d1 (< 2^24), t = 1 holds 16384 d2, t = 2, 3 contribute zero through their multipliers; each lane scales its part
+// by the group's power of two and the row's scale and the parts meet in the warp sum over t at the end of the row tile.
+__device__ __forceinline__ void unit_compute_q4c(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t xb = smem_u32(sm.xs) + (uint32_t)sb * (8u * 192u) + (uint32_t)(g < 3 ? g : 0) * 64u + (uint32_t)t * 16u;
+    const int mulA = t == 0 ? 1 : (t == 1 ? 16384 : 0), mulB = t == 0 ? 128 : 0;
+    const uint32_t xi = smem_u32(sm.xsi) + (uint32_t)sb * 64u;          // (sum, 1 / scale) of the eight groups
+    const uint32_t sv = ub + 4096u - (uint32_t)t * 16u;                 // the scale / bias vectors of rows g, g + 8: lanes (g, 0..3)
+    const uint2 s0 = lds64o<0>(sv), s1 = lds64o<16>(sv), s2 = lds64o<32>(sv), s3 = lds64o<48>(sv);
+    const uint4 i01 = lds128o<0>(xi), i23 = lds128o<16>(xi), i45 = lds128o<32>(xi), i67 = lds128o<48>(xi);
+    constexpr uint32_t M = 0x0F0F0F0Fu;
+#define FK_GC(J, SV, INV, HALF)                                                                                              \
+    {                                                                                                                        \
+        const uint4 w = lds128o<J * 512>(ub);                                                                                \
+        const uint4 x = lds128o<J * 192>(xb);                                                                                \
+        int d[4];                                                                                                            \
+        imma_us0(d, w.x & M, w.z & M, w.y & M, w.w & M, x.x, x.y);                                                           \
+        imma_us(d, (w.x >> 4) & M, (w.z >> 4) & M, (w.y >> 4) & M, (w.w >> 4) & M, x.z, x.w);                                \
+        const float inv = __uint_as_float(INV);                                                                              \
+        const float flo = (float)(d[0] * mulA + d[1] * mulB) * inv, fhi = (float)(d[2] * mulA + d[3] * mulB) * inv;          \
+        acc_lo = fmaf(HALF ? bf_hi(SV.x) : bf_lo(SV.x), flo, acc_lo);                                                        \
+        acc_hi = fmaf(HALF ? bf_hi(SV.y) : bf_lo(SV.y), fhi, acc_hi);                                                        \
+    }
+    FK_GC(0, s0, i01.y, 0) FK_GC(1, s0, i01.w, 1) FK_GC(2, s1, i23.y, 0) FK_GC(3, s1, i23.w, 1)
+    FK_GC(4, s2, i45.y, 0) FK_GC(5, s2, i45.w, 1) FK_GC(6, s3, i67.y, 0) FK_GC(7, s3, i67.w, 1)
+#undef FK_GC
+    // b * sum(x) of the lane's own two groups (2t, 2t + 1), as laid out in its own vector
+    const uint4 own = lds128o<4096>(ub);
+    const uint4 xo = lds128(xi + (uint32_t)t * 16u);
+    const float X0 = __uint_as_float(xo.x), X1 = __uint_as_float(xo.z);
+    acc_lo = fmaf(bf_lo(own.z), X0, acc_lo); acc_lo = fmaf(bf_hi(own.z), X1, acc_lo);
+    acc_hi = fmaf(bf_lo(own.w), X0, acc_hi); acc_hi = fmaf(bf_hi(own.w), X1, acc_hi);
+}
+
 template <int BITS>
 __device__ __forceinline__ void unit_compute(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     if constexpr (BITS == 16) unit_compute_bf16(ub, sm, sb, lane, acc_lo, acc_hi);
+    else if constexpr (BITS == 4 && FK_COLDIGITS) unit_compute_q4c(ub, sm, sb, lane, acc_lo, acc_hi);
     else unit_compute_q<BITS>(ub, sm, sb, lane, acc_lo, acc_hi);
 }
 

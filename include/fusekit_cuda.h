@@ -100,7 +100,8 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  * RMSNORM_GATEUP_ACT   buf0 x  buf1 norm_w  buf2 weight(gate)  buf3 weight(up)  buf4 act_out T[I]
  *                      buf9..11 pending (as RMSNORM_QKV)     i0 H  i1 I  i2 act   f0 eps
  *                      i3 activation rows M (0 or 1: one row).  M = 2..16: x is T[M, H], act_out is T[M, I], every row normalised
- *                      by its own RMS; paired 4-bit weights, no pending inputs (reference: fusekit_qmm_t_swiglu_pair_impl, msl.rs:2489)
+ *                      by its own RMS (buf1 = 0: the rows are normalised already, e.g. by RMSNORM_ROWS, and only the product and
+ *                      the activation run); paired 4-bit weights, no pending inputs (reference: fusekit_qmm_t_swiglu_pair_impl, msl.rs:2489)
  *                      i4 pull site + 1 (as RMSNORM_QKV i6)
  * FINAL_RMSNORM_LM_HEAD buf0 x  buf1 norm_w  buf2 weight(head)  buf3 logits_out|0  buf4 argmax scratch(u64)
  *                      buf5 counter(u32)  buf9..11 pending     i0 H  i1 V(local)  i2 vocab_offset  i3 finalize(1/0)   f0 eps
