@@ -149,6 +149,8 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     e = getenv("FK_SPLIT"); if (e) c->force_split = atoi(e);        // log2 of the warps sharing a row tile (tuning)
 #define BIG4(K) CU(big_smem(K<4, 8>)); CU(big_smem(K<4, 16>)); CU(big_smem(K<8, 8>)); CU(big_smem(K<8, 16>)); CU(big_smem(K<16, 8>)); CU(big_smem(K<16, 16>))
 #define BIG4P(K) CU(big_smem(K<4, 8, true>)); CU(big_smem(K<4, 16, true>)); CU(big_smem(K<8, 8, true>)); CU(big_smem(K<8, 16, true>)); CU(big_smem(K<16, 8, true>)); CU(big_smem(K<16, 16, true>))
+#define BIG4A(K) CU(big_smem(K<4, 8, false, true>)); CU(big_smem(K<4, 16, false, true>)); CU(big_smem(K<8, 8, false, true>)); CU(big_smem(K<8, 16, false, true>)); CU(big_smem(K<16, 8, false, true>)); CU(big_smem(K<16, 16, false, true>))
+    BIG4A(k_s_rmsnorm_qkv);
     BIG4(k_s_linear); BIG4(k_s_rmsnorm_qkv); BIG4(k_s_gateup); BIG4(k_s_head); BIG4P(k_s_rmsnorm_qkv); BIG4P(k_s_gateup); BIG4P(k_s_head);
     CU(big_smem(k_sdpa_mma<64>)); CU(big_smem(k_sdpa_mma<128>)); CU(big_smem(k_sdpa_mma<256>));
     CU(cudaFuncSetAttribute(k_sdpa_mma<64>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
@@ -559,15 +561,34 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
             if (sinks && (w->rows_kind != FK_ROWS_ROPE_PAIRS || w->hd != hd || w->n_rot != (nq + nkv) * hd)) return fail(FK_ERR_VALUE, "rmsnorm_qkv: weight rows must be laid out as RoPE pairs (fk_weight_set_rows)");
             if (!sinks && w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "rmsnorm_qkv without sinks takes plain row order");
             SQkvArgs sa{a.x, a.norm_w, StreamPlan(), a.lin_bias, a.q_out, a.cache_k, a.cache_v, a.k_out, a.v_out, a.pending, a.pending_w, a.h_out,
-                        H, nq, nkv, hd, cap, sinks, a.eps, a.log2theta, nullptr, PeerXchg()};
+                        H, nq, nkv, hd, cap, sinks, a.eps, a.log2theta, nullptr, PeerXchg(), QkvAttend{nullptr, nullptr, nullptr, 0.0f}};
+            if (i[7]) {         // attention as the kernel's tail: buf7 = attention output, buf8 = scratch (64 bytes of counters, then partials)
+                if (!sinks || !b[7] || !b[8] || (b[8] & 15) || (hd != 64 && hd != 128) || nkv <= 0 || nq % nkv || nq / nkv > 8 || !(f[2] > 0.0f))
+                    return fail(FK_ERR_VALUE, "rmsnorm_qkv with attention: needs the cache sinks, head_dim 64 or 128, at most 8 q heads per kv head, output, scratch and scale");
+                sa.k_out = sa.v_out = nullptr;
+                sa.att = QkvAttend{(uint16_t *)b[7], (float *)(b[8] + 64), (unsigned int *)b[8], f[2]};
+            }
             { fk_status xs = make_xchg(c, i[6], &sa.pull, "rmsnorm_qkv"); if (xs) return xs; }
             if (sa.pull.site >= 0 && (b[9] || b[10] || H * 8 > FK_PEER_SLOT_BYTES)) return fail(FK_ERR_VALUE, "rmsnorm_qkv: a pulled exchange excludes pending inputs and needs H <= %d", FK_PEER_SLOT_BYTES / 8);
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }      // fp32 all-reduced projection + residual
             if (H > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "rmsnorm_qkv: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             const Shape sh = make_plan(c, w, &sa.P, nextw);
-            STREAM_LAUNCH_P(k_s_rmsnorm_qkv, (sa.pending || sa.pend_sum || sa.pull.site >= 0), w, sh, c->state, sa);
+            if (sa.att.out && (sh.grid > c->sm_count * (sh.warps == 8 ? 2 : 1) || sh.grid < nkv || sh.grid > FK_ATTEND_MAX_BLOCKS))
+                return fail(FK_ERR_VALUE, "rmsnorm_qkv with attention: %d blocks do not fit the device at once (or fewer blocks than kv heads)", sh.grid);
+            const bool pend = sa.pending || sa.pend_sum || sa.pull.site >= 0;
+            if (sa.att.out) {
+                if (pend) return fail(FK_ERR_VALUE, "rmsnorm_qkv with attention takes no pending inputs");
+#define QKV_ATT(BITS_, WARPS_) launch(c, k_s_rmsnorm_qkv<BITS_, WARPS_, false, true>, dim3(sh.grid), dim3(WARPS_ * 32), sh.smem, c->state, sa)
+                if (w->bits == 4) e = sh.warps == 8 ? QKV_ATT(4, 8) : QKV_ATT(4, 16);
+                else if (w->bits == 8) e = sh.warps == 8 ? QKV_ATT(8, 8) : QKV_ATT(8, 16);
+                else e = sh.warps == 8 ? QKV_ATT(16, 8) : QKV_ATT(16, 16);
+#undef QKV_ATT
+                break;
+            }
+            STREAM_LAUNCH_P(k_s_rmsnorm_qkv, pend, w, sh, c->state, sa);
             break;
         }
+        if (i[7]) return fail(FK_ERR_VALUE, "rmsnorm_qkv with attention needs weights in the streaming layout");
         if (b[9] && !b[10]) return fail(FK_ERR_VALUE, "rmsnorm_qkv: the fused all-reduce residual needs 4/8-bit streamed weights");
         const int grid = grid_for(c, w->n / 2, 8);
         BITS_SWITCH(w->bits, e = launch(c, k_rmsnorm_qkv<B>, dim3(grid), dim3(256), smem_bytes_for(H), (const FkState *)c->state, a));

@@ -31,6 +31,7 @@
 // the unit a few fetches ahead -- were each measured and dropped: all slower.)
 #pragma once
 #include "fk_common.cuh"
+#include "fk_attend.cuh"
 
 #define FK_UNIT_VEC 288                 // uint4 per unit: 8 groups x 32 lanes + 32 scale/bias vectors (also the ring slot size)
 #define FK_UNIT_BYTES (FK_UNIT_VEC * 16)
@@ -841,6 +842,7 @@ struct SQkvArgs {
     uint16_t *q_out, *cache_k, *cache_v, *k_out, *v_out;
     const uint16_t *pending, *pending_w; uint16_t *h_out;
     int h, n_q, n_kv, hd, capacity, sinks; float eps, log2theta; const float *pend_sum; PeerXchg pull;
+    QkvAttend att;          // att.out != null: decode attention over the cache as the kernel's tail (fk_attend.cuh)
 };
 // cos and sin of the RoPE angle of dim d at position pos: inv = exp2(-(d / half) * log2(theta)) (rope_kv_cache_store_decode.rs)
 __device__ __forceinline__ void rope_angle(int d, int half, uint32_t pos, float log2theta, float *c, float *s) {
@@ -890,7 +892,9 @@ struct EpiQkv {
         } else { store(r0, f2bf(lo)); store(r1, f2bf(hi)); }
     }
 };
-template <int BITS, int WARPS, bool PEND = false>
+// ATT: the instance that can carry the attention tail (a kernel of its own, so that the call does not cost the plain form
+// registers or a stack frame)
+template <int BITS, int WARPS, bool PEND = false, bool ATT = false>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkState *st, SQkvArgs a) {
     extern __shared__ __align__(128) unsigned char smem_stream[];
     const StreamSmem sm = stream_carve(smem_stream, a.P.W.nsb, a.P.stages, BITS);
@@ -902,9 +906,16 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_rmsnorm_qkv(FkStat
     stamp(a.P, 1);
     stage_rmsnorm<BITS, PEND>(sm, a.x, nwv, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum, &a.pull, st);
     stamp(a.P, 2);
-    EpiQkv epi(a, st->offset);
+    const uint32_t pos = st->offset;
+    EpiQkv epi(a, pos);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x200u);
     pdl_launch_dependents();
+    if constexpr (ATT) if (a.att.out) {        // a warp's ring slots are its own again; the staged activations are dead after the first hand-off
+        unsigned char *tiles = reinterpret_cast<unsigned char *>(sm.ring);
+        constexpr int stride_w = FK_STAGES * (BITS == 16 ? 256 : FK_UNIT_VEC) * 16;
+        if (a.hd == 128) qkv_attend<128>(a.att, st, a.q_out, a.cache_k, a.cache_v, a.n_q, a.n_kv, a.capacity, pos, tiles, stride_w, tiles + SdpaMmaLayout<128>::WTILE);
+        else qkv_attend<64>(a.att, st, a.q_out, a.cache_k, a.cache_v, a.n_q, a.n_kv, a.capacity, pos, tiles, stride_w, tiles + SdpaMmaLayout<64>::WTILE);
+    }
     __syncthreads(); stamp(a.P, 3);
 }
 

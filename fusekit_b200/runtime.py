@@ -185,7 +185,7 @@ class DecodeEngine:
     """One model instance (or one tensor-parallel slice of it) resident on a GPU."""
 
     def __init__(self, spec: ModelSpec, capacity: int, device: int = 0, tp_rank: int = 0, tp_size: int = 1,
-                 want_logits: bool = False, runtime: Runtime | None = None, kv_bits: int = 0):
+                 want_logits: bool = False, runtime: Runtime | None = None, kv_bits: int = 0, fuse_attention: bool | None = None):
         check_tp(spec, tp_size)
         self.kv_bits = kv_bits           # 4 / 8: quantised KV cache (reference: the *_quant cache kernels); 0: bf16
         if kv_bits and (kv_bits not in (4, 8) or spec.arch != "qwen2" or tp_size > 1):
@@ -193,6 +193,13 @@ class DecodeEngine:
         self.spec, self.capacity, self.rank, self.world = spec, capacity, tp_rank, tp_size
         self.rt = runtime or Runtime(device)
         self.want_logits = want_logits
+        # attention in the tail of the QKV kernel (no sdpa task): Qwen-shaped layers on one GPU, streaming layout, bf16 cache.  Off
+        # unless asked for (FK_ATTEND=1): its two grid-wide hand-offs through global memory cost more than the launch they save
+        # (689 against 780 tok/s on the 7B shape at context 512)
+        import os
+        can_fuse = (spec.arch == "qwen2" and not kv_bits and self.rt.tiled and spec.head_dim in (64, 128) and spec.n_q // spec.n_kv <= 8)
+        can_fuse = can_fuse and tp_size == 1
+        self.fuse_attention = can_fuse and (os.environ.get("FK_ATTEND", "0") == "1" if fuse_attention is None else bool(fuse_attention))
         s = spec
         self.nq, self.nkv, self.inter, self.vocab = s.n_q // tp_size, s.n_kv // tp_size, s.inter // tp_size, s.vocab // tp_size
         self.W: dict[str, int] = {}      # name -> fk_weight id
@@ -221,6 +228,8 @@ class DecodeEngine:
         chunks = (max_cap + 31) // 32
         self.sdpa_part = rt.alloc(self.nq * chunks * (s.head_dim + 2) * 4)
         self.sdpa_counter = rt.alloc(max(self.nkv, 1) * 4)
+        # attention as the tail of the QKV kernel: 64 bytes of hand-off counters + one partial per block (<= 512) and q head (<= 8)
+        self.attend_scratch = rt.alloc(64 + 512 * 8 * (s.head_dim + 2) * 4)
         self.argmax_scratch = rt.alloc(8 * 1024)
         self.head_counter = rt.alloc(4)
         self.logits = rt.alloc(self.vocab * 2) if self.want_logits else 0
@@ -353,7 +362,8 @@ class DecodeEngine:
     def task_graph(self) -> dict:
         """This engine's decode step as a v2 ``task_graph.json`` document (see task_graph.emit)."""
         return task_graph.emit(self.spec, self.capacity, self.rank, self.world,
-                               fused_weights=self.rt.tiled, want_logits=self.want_logits, embed_bits=getattr(self, "embed_bits", 16), tp_exchange=getattr(self, "tp_exchange", "allreduce"), kv_bits=getattr(self, "kv_bits", 0))
+                               fused_weights=self.rt.tiled, want_logits=self.want_logits, embed_bits=getattr(self, "embed_bits", 16), tp_exchange=getattr(self, "tp_exchange", "allreduce"), kv_bits=getattr(self, "kv_bits", 0),
+                               fuse_attention=getattr(self, "fuse_attention", False))
 
     def _resolve(self, role: str) -> int:
         """Device address (or fk_weight id) behind one role string of the task graph."""
@@ -377,7 +387,7 @@ class DecodeEngine:
         if p[0] == "global_scratch":
             if p[1] == "x_in":
                 return self.x_ptr(int(p[2]))
-            return {"sdpa_partials": self.sdpa_part, "sdpa_counter": self.sdpa_counter, "argmax_scratch": self.argmax_scratch,
+            return {"sdpa_partials": self.sdpa_part, "sdpa_counter": self.sdpa_counter, "argmax_scratch": self.argmax_scratch, "attend_scratch": getattr(self, "attend_scratch", 0),
                     "head_counter": self.head_counter, "logits": self.logits, "tp_partial_a": self.part_f32, "tp_partial_b": self.part_f32_b}[p[1]]
         if p[0] == "layer_scratch":
             if p[1].isdigit():

@@ -31,7 +31,8 @@ def _bf16_round(v: float) -> float:
 
 
 def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fused_weights: bool = True,
-         want_logits: bool = False, embed_bits: int = 16, tp_exchange: str = "allreduce", kv_bits: int = 0) -> dict:
+         want_logits: bool = False, embed_bits: int = 16, tp_exchange: str = "allreduce", kv_bits: int = 0,
+         fuse_attention: bool = False) -> dict:
     """Build the v2 task graph of one decode step for `spec` (one tensor-parallel rank of it).
 
     `fused_weights`: weights in the streaming layout (gate/up paired, residual add after an all-reduce fused into the next
@@ -42,7 +43,9 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
     layer l, 2L for the argmax keys of the vocabulary-sharded head).
     `kv_bits`: 4 or 8 = quantised KV cache (Qwen-shaped layers, one GPU): the QKV task writes raw projections, a
     kv_store_quant task rotates and quantises, sdpa_decode_quant attends the packed cache
-    (src/codegen/kernels/rope_kv_cache_store_decode_quant.rs, sdpa_decode_quant.rs)."""
+    (src/codegen/kernels/rope_kv_cache_store_decode_quant.rs, sdpa_decode_quant.rs).
+    `fuse_attention`: Qwen-shaped layers with the streaming layout and a bf16 cache: no sdpa_decode task, the QKV task attends
+    the cache in its tail (iarg 7, slot 7 = attention output, slot 8 = scratch, farg 2 = scale)."""
     s, hd, H = spec, spec.head_dim, spec.hidden
     nq, nkv, inter, vocab = s.n_q // tp_size, s.n_kv // tp_size, s.inter // tp_size, s.vocab // tp_size
     tp = tp_size > 1
@@ -50,6 +53,7 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
     peer = tp and tp_exchange == "peer"
     if kv_bits and (kv_bits not in (4, 8) or s.arch != "qwen2" or tp):
         raise ValueError("the quantised KV cache is wired for Qwen-shaped layers on one GPU, 4 or 8 bits")
+    attend = bool(fuse_attention) and s.arch == "qwen2" and fused and not kv_bits and not tp and hd in (64, 128) and s.n_q // s.n_kv <= 8
     if peer and not fused:
         raise ValueError("the fused peer exchange needs the streaming weight layout")
     if peer and 2 * s.n_layers + 1 > 160:
@@ -86,6 +90,10 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
                                4: "layer_scratch.q_buf", 7: "layer_scratch.k_buf", 8: "layer_scratch.v_buf"}, [H, nq, nkv, hd, cap, 0], [s.eps, theta])
                 add(K_KVQ, l, {0: "layer_scratch.q_buf", 1: "layer_scratch.k_buf", 2: "layer_scratch.v_buf", 3: cq["k"], 4: cq["v"], 5: cq["k_scales"],
                                6: cq["k_biases"], 7: cq["v_scales"], 8: cq["v_biases"]}, [nq, nkv, hd, cap, kv_bits], [0.0, theta])
+            elif attend:
+                add(K_QKV, l, {0: x_in, 1: lp(l, "input_layernorm.weight"), 2: lp(l, "self_attn.qkv_proj"), 3: lp(l, "self_attn.qkv_proj.bias"),
+                               4: "layer_scratch.q_buf", 5: ck, 6: cv, 7: "layer_scratch.sdpa_buf", 8: "global_scratch.attend_scratch", **pend},
+                    [H, nq, nkv, hd, cap, 1, pull, 1], [s.eps, theta, 1.0 / math.sqrt(hd)])
             else:
                 add(K_QKV, l, {0: x_in, 1: lp(l, "input_layernorm.weight"), 2: lp(l, "self_attn.qkv_proj"), 3: lp(l, "self_attn.qkv_proj.bias"),
                                4: "layer_scratch.q_buf", 5: ck, 6: cv, **pend}, [H, nq, nkv, hd, cap, 1, pull], [s.eps, theta])
@@ -101,7 +109,7 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
             add(K_SDPAQ, l, {0: "layer_scratch.q_buf", 1: cq["k"], 2: cq["v"], 3: "layer_scratch.sdpa_buf", 4: "global_scratch.sdpa_partials",
                              5: "global_scratch.sdpa_counter", 6: cq["k_scales"], 7: cq["k_biases"], 8: cq["v_scales"], 9: cq["v_biases"]},
                 [nq, nkv, hd, cap, kv_bits], [scale])
-        else:
+        elif not attend:
             add(K_SDPA, l, {0: "layer_scratch.q_buf", 1: ck, 2: cv, 3: "layer_scratch.sdpa_buf", 4: "global_scratch.sdpa_partials",
                             5: "global_scratch.sdpa_counter"}, [nq, nkv, hd, cap], [scale])
         ko = nq * hd

@@ -79,6 +79,10 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      i0 H  i1 n_q  i2 n_kv  i3 head_dim  i4 capacity  i5 sinks(1 = RoPE + cache store)
  *                      i6 pull site + 1 (0 = none): x <- T(sum over ranks of the partial rows pushed to that exchange site + x),
  *                      written to buf11 (tensor parallel with the exchange fused in, see LINEAR_RESIDUAL i3)
+ *                      i7 = 1: decode attention over the cache as the kernel's tail (streaming layout, sinks, head_dim 64 / 128,
+ *                      <= 8 q heads per kv head; replaces the SDPA_DECODE task that would follow, sdpa_decode.rs:697-715, 992-1046):
+ *                      buf7 = attention output T[n_q * head_dim], buf8 = scratch, 16-byte aligned, zero before first use:
+ *                      64 bytes of hand-off counters + 512 * 8 * (head_dim + 2) floats of partials;  f2 = attention scale
  *                      f0 eps  f1 rope_theta
  * QK_NORM_ROPE_STORE   buf0 q(in/out)  buf1 k_in  buf2 v_in  buf3 q_norm_w  buf4 k_norm_w  buf5 cache_k  buf6 cache_v
  *                      i0 n_q  i1 n_kv  i2 head_dim  i3 capacity   f0 eps  f1 rope_theta

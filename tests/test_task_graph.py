@@ -172,3 +172,21 @@ def test_library_json_reader_refusals():
     worse = json.loads(json.dumps(g)); worse["tasks"][0]["kind"] = 99
     with pytest.raises(N.FusekitError, match="kind"):
         e.dispatches_from_json(json.dumps(worse), table)
+
+
+def test_attention_fused_into_the_qkv_task():
+    """fuse_attention: four tasks per Qwen-shaped layer, the QKV task carries the attention output, scratch and scale; shapes
+    the tail does not cover (Gemma's per-head norms, a quantised cache) keep their attention task."""
+    spec = CONFIGS["qwen2.5-7b"]
+    g = TG.emit(spec, 1024, fuse_attention=True)
+    kinds = [t["kind"] for t in g["tasks"]]
+    assert TG.K_SDPA not in kinds and len(kinds) == 2 + 4 * spec.n_layers
+    qkv = g["tasks"][1]
+    assert qkv["kind"] == TG.K_QKV and qkv["iargs"][7] == 1 and abs(qkv["fargs"][2] - spec.head_dim ** -0.5) < 1e-7
+    slots = TG.task_slots(qkv)
+    assert slots[7] == "layer_scratch.sdpa_buf" and slots[8] == "global_scratch.attend_scratch"
+    assert TG.K_SDPA in [t["kind"] for t in TG.emit(CONFIGS["gemma3-4b"], 1024, fuse_attention=True)["tasks"]]
+    assert TG.K_SDPAQ in [t["kind"] for t in TG.emit(CONFIGS["tiny-qwen"], 64, kv_bits=8, fuse_attention=True)["tasks"]]
+    e = _fake_engine(spec)
+    e.fuse_attention, e.attend_scratch = True, 0x600000
+    assert _records(e.dispatches_from_json(json.dumps(e.task_graph()))) == _records(e.build_dispatches())
