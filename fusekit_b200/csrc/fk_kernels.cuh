@@ -839,7 +839,8 @@ template <int HD> struct SdpaMmaLayout {
     __host__ __device__ static constexpr int tiles() { return 8 * QSTRIDE; }
     __host__ __device__ static constexpr int cpart() { return tiles() + FK_SDPA_CW * WTILE; }
     __host__ __device__ static constexpr int wexp(int G) { return cpart() + (G * HD + FK_SDPA_CLMAX) * 4; }      // after the received o slices
-    __host__ __device__ static constexpr int bytes(int G) { return wexp(G) + FK_SDPA_CLMAX * G * 2 * 4 + 64; }
+    __host__ __device__ static constexpr int fexp(int G) { return wexp(G) + FK_SDPA_CLMAX * G * 2 * 4; }              // [16][G] factors + [G] maxima + [G] 1 / l
+    __host__ __device__ static constexpr int bytes(int G) { return fexp(G) + (16 * G + 2 * G) * 4 + 64; }
 };
 __host__ __device__ inline size_t sdpa_mma_smem_bytes(int G, int hd) { return hd == 256 ? SdpaMmaLayout<256>::bytes(G) : hd == 128 ? SdpaMmaLayout<128>::bytes(G) : SdpaMmaLayout<64>::bytes(G); }
 template <int HD>
@@ -883,6 +884,17 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
             *reinterpret_cast<uint4 *>(vt + row * L::VSTRIDE + c * 16) = v;
         }
     };
+    // the same tile by asynchronous copies (no registers, nothing waits until cp.async.wait_all): rows past the end are zero-filled
+    auto load_v_tile_async = [&](int kb) {
+#pragma unroll
+        for (int i = 0; i < FK_SDPA_MK * (HD / 8) / 32; ++i) {
+            const int idx = lane + 32 * i, row = idx / (HD / 8), c = idx - row * (HD / 8);
+            const bool in = kb + row < k_end;
+            const uint4 *src = reinterpret_cast<const uint4 *>(V + (size_t)(in ? kb + row : k_begin) * HD) + c;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(vt + row * L::VSTRIDE + c * 16);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(in ? 16 : 0) : "memory");
+        }
+    };
     auto load_k = [&](int kb, int nb, int slot) {
         const int key = min(kb + 8 * nb + g, k_end - 1);                  // clamped: masked below
         const uint4 *kp = reinterpret_cast<const uint4 *>(K + (size_t)key * HD + t * (HD / 4));
@@ -894,13 +906,19 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
     const int kb0 = k_begin + wid * FK_SDPA_MK;
     const int newest = (int)(pos % (uint32_t)a.capacity);
     const bool pre = QREG && kb0 < k_end && !a.consecutive;      // several new rows in one cache: nothing is fetched early
-    if (pre) { load_v_tile(kb0); load_k(kb0, 0, 0); load_k(kb0, 1, NKR - 1); }
+    // Nothing here may wait for the early fetch: the V tile goes by asynchronous copies, the K rows stay unread in registers, so
+    // the wait for the previous kernel and the round trip for q run under the same memory latency instead of after it.
+    if (pre) { load_v_tile_async(kb0); load_k(kb0, 0, 0); load_k(kb0, 1, NKR - 1); }
     pdl_wait();
-    if (pre && newest >= kb0 && newest < kb0 + FK_SDPA_MK) { load_v_tile(kb0); load_k(kb0, 0, 0); load_k(kb0, 1, NKR - 1); }
+    if (pre && newest >= kb0 && newest < kb0 + FK_SDPA_MK) {
+        asm volatile("cp.async.wait_all;" ::: "memory");          // the stale copy of the newest row must have landed before it is overwritten
+        load_v_tile_async(kb0); load_k(kb0, 0, 0); load_k(kb0, 1, NKR - 1);
+    }
     for (int i = tid; i < G * HD / 2; i += NT) {             // q as bf16 rows
         const int gg = (2 * i) / HD, d = 2 * i - gg * HD;
         *reinterpret_cast<uint32_t *>(qs + gg * L::QSTRIDE + d * 2) = __ldcg(reinterpret_cast<const uint32_t *>(a.q + kvh * G * HD) + i);
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
     sd_stamp(a.tl, 1);
     // A fragments of q: row g (rows >= G and 8..15 are zero); in registers up to head_dim 128, re-read from shared memory above
@@ -989,42 +1007,60 @@ __global__ void __launch_bounds__(FK_SDPA_CW * 32) k_sdpa_mma(const FkState *st,
     const int total = G * HD, per = (total + CL - 1) / CL;
     float *recv_o = cpart;                                   // [CL][per]
     float *recv_ml = wexp;                                   // [CL][G][2]
+    // the factors exp(m_w - M) depend on (warp, head) only: one thread per pair computes them once, the element loop below is
+    // then multiply-adds (an expf per element and source made the two folds the longest phases of the kernel at short contexts)
+    float *fexp = reinterpret_cast<float *>(smem_att + L::fexp(G));          // [16][G], then M[G], then 1 / l [G]
+    float *fmax = fexp + 16 * G;
+    if (tid < nwp * G) {
+        const int w = tid / G, gg = tid - w * G;
+        float M = -INFINITY;
+        for (int w2 = 0; w2 < nwp; ++w2) M = fmaxf(M, reinterpret_cast<const float *>(tiles + w2 * L::WTILE)[gg * stride]);
+        const float mw = reinterpret_cast<const float *>(tiles + w * L::WTILE)[gg * stride];
+        fexp[w * G + gg] = mw == -INFINITY ? 0.0f : expf(mw - M);
+        if (w == 0) fmax[gg] = M;
+    }
+    if (nwp == 0 && tid < G) fmax[tid] = -INFINITY;
+    __syncthreads();
     cluster.barrier_wait(std::move(started));
     for (int i = tid; i < total + G; i += NT) {              // i >= total: the (m, l) pair of head i - total
         const int gg = i < total ? i / HD : i - total, d = i < total ? i - gg * HD : -1;
-        float M = -INFINITY;
-        for (int w = 0; w < nwp; ++w) M = fmaxf(M, reinterpret_cast<const float *>(tiles + w * L::WTILE)[gg * stride]);
         float acc = 0.0f;
         for (int w = 0; w < nwp; ++w) {
             const float *pw = reinterpret_cast<const float *>(tiles + w * L::WTILE) + gg * stride;
-            const float e = pw[0] == -INFINITY ? 0.0f : expf(pw[0] - M);
-            acc = fmaf(d < 0 ? pw[1] : pw[2 + d], e, acc);
+            acc = fmaf(d < 0 ? pw[1] : pw[2 + d], fexp[w * G + gg], acc);
         }
         if (d >= 0) {
             const int dst = i / per;
             cluster.map_shared_rank(recv_o, dst)[rank * per + (i - dst * per)] = acc;
         } else {
+            const float M = fmax[gg];
             for (int dst = 0; dst < CL; ++dst) { float *q2 = cluster.map_shared_rank(recv_ml, dst) + (rank * G + gg) * 2; q2[0] = M; q2[1] = acc; }
         }
     }
     sd_stamp(a.tl, 3);
     cluster.sync();
     sd_stamp(a.tl, 4);
+    if (tid < CL * G) {                                      // factor of (source CTA, head), once
+        const int rr = tid / G, gg = tid - rr * G;
+        float M = -INFINITY;
+        for (int r2 = 0; r2 < CL; ++r2) M = fmaxf(M, recv_ml[(r2 * G + gg) * 2]);
+        const float mr = recv_ml[(rr * G + gg) * 2];
+        fexp[rr * G + gg] = mr == -INFINITY ? 0.0f : expf(mr - M);
+    }
+    __syncthreads();
+    if (tid < G) {
+        float Ls = 0.0f;
+        for (int rr = 0; rr < CL; ++rr) Ls = fmaf(recv_ml[(rr * G + tid) * 2 + 1], fexp[rr * G + tid], Ls);
+        fmax[G + tid] = __fdiv_rn(1.0f, Ls);
+    }
+    __syncthreads();
     for (int il = tid; il < per; il += NT) {
         const int i = rank * per + il;
         if (i >= total) break;
         const int gg = i / HD, d = i - gg * HD;
-        float M = -INFINITY;
-#pragma unroll
-        for (int rr = 0; rr < FK_SDPA_CLMAX; ++rr) if (rr < CL) M = fmaxf(M, recv_ml[(rr * G + gg) * 2]);
-        float Ls = 0.0f, O = 0.0f;
-#pragma unroll
-        for (int rr = 0; rr < FK_SDPA_CLMAX; ++rr) if (rr < CL) {
-            const float mr = recv_ml[(rr * G + gg) * 2];
-            const float e = mr == -INFINITY ? 0.0f : expf(mr - M);
-            Ls = fmaf(recv_ml[(rr * G + gg) * 2 + 1], e, Ls); O = fmaf(recv_o[rr * per + il], e, O);
-        }
-        a.out[(kvh * G + gg) * HD + d] = f2bf(O * __fdiv_rn(1.0f, Ls));
+        float O = 0.0f;
+        for (int rr = 0; rr < CL; ++rr) O = fmaf(recv_o[rr * per + il], fexp[rr * G + gg], O);
+        a.out[(kvh * G + gg) * HD + d] = f2bf(O * fmax[G + gg]);
     }
     sd_stamp(a.tl, 6);
 }

@@ -195,7 +195,7 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
     for (int o = 1; o < TPG; o <<= 1) { s8 += __shfl_xor_sync(0xffffffffu, s8, o); m8 = fmaxf(m8, __shfl_xor_sync(0xffffffffu, m8, o)); }
     // scale = 2^(XB - exponent(max)): the largest activation becomes an integer in [2^XB, 2^(XB+1)).  XB = 20 with unsigned low
     // digits; 19 with balanced digits (4-bit column form), where v + 8256 must stay below 2^21 for the top digit to fit s8
-    constexpr bool BAL = BITS == 4 && FK_COLDIGITS;
+    constexpr bool BAL = FK_COLDIGITS != 0;
     constexpr int XB = BAL ? 19 : 20;
     int e = m8 > 0.0f ? (int)((__float_as_uint(m8) >> 23) & 0xffu) - 127 : XB;
     e = e < -100 ? -100 : (e > 100 ? 100 : e);
@@ -230,8 +230,8 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
         uint32_t *dst = reinterpret_cast<uint32_t *>(sm.xs) + (size_t)grp * 24 + t * 2 + half;   // [digit][lane][A|B] as words
 #pragma unroll
         for (int q = 0; q < 2; ++q) {                    // the two 4-blocks of this thread: lanes t and t+1
-            dst[2 * q] = bytes4(x0[4 * q], x0[4 * q + 1], x0[4 * q + 2], x0[4 * q + 3]) & 0x7f7f7f7fu;
-            dst[8 + 2 * q] = bytes4(x7[4 * q], x7[4 * q + 1], x7[4 * q + 2], x7[4 * q + 3]) & 0x7f7f7f7fu;
+            dst[2 * q] = low7(bytes4(x0[4 * q], x0[4 * q + 1], x0[4 * q + 2], x0[4 * q + 3]));
+            dst[8 + 2 * q] = low7(bytes4(x7[4 * q], x7[4 * q + 1], x7[4 * q + 2], x7[4 * q + 3]));
             dst[16 + 2 * q] = bytes4(x14[4 * q], x14[4 * q + 1], x14[4 * q + 2], x14[4 * q + 3]);
         }
         if ((blk & 3) == 0) sm.xsi[blk >> 2] = make_float2(s8, inv);
@@ -262,12 +262,16 @@ __device__ __forceinline__ void stage_plain(const StreamSmem &sm, const uint16_t
             const int blk = b0 + i * blockDim.x + threadIdx.x;
             v[i] = blk < nblk ? __ldcg(reinterpret_cast<const uint4 *>(x + (size_t)blk * 8)) : make_uint4(0, 0, 0, 0);
         }
-#pragma unroll
+        // one copy of the conversion code, the held vectors rotated through v[0]: this code runs once per launch, so its size
+        // (instruction fetch) counts as much as its instruction count
+#pragma unroll 1
         for (int i = 0; i < MAXB; ++i) {
             const int blk = b0 + i * blockDim.x + threadIdx.x;
             if (b0 + i * (int)blockDim.x >= nblk) break;   // uniform across the block
-            float f[8]; unpack8(v[i], f);
+            float f[8]; unpack8(v[0], f);
             store_block<BITS>(sm, blk, f, blk < nblk);
+#pragma unroll
+            for (int j = 0; j + 1 < MAXB; ++j) v[j] = v[j + 1];
         }
     }
     __syncthreads();
@@ -403,14 +407,19 @@ __device__ __forceinline__ void stage_rmsnorm(const StreamSmem &sm, const uint16
     ss = block_sum(ss, sm.red);
     stamp_raw(tl, 5);
     const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)h), eps)));
+    uint4 wl[FK_STAGE_MAXB];
 #pragma unroll
-    for (int i = 0; i < FK_STAGE_MAXB; ++i) {
+    for (int i = 0; i < FK_STAGE_MAXB; ++i) wl[i] = wv[i];
+#pragma unroll 1
+    for (int i = 0; i < FK_STAGE_MAXB; ++i) {             // one copy of the conversion code (see stage_plain)
         const int blk = i * blockDim.x + threadIdx.x;
         if (i * (int)blockDim.x >= nblk) break;            // uniform across the block
-        float f[8], wf[8]; unpack8(xv[i], f); unpack8(wv[i], wf);
+        float f[8], wf[8]; unpack8(xv[0], f); unpack8(wl[0], wf);
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = rT(wf[j] * rT(f[j] * r));
         store_block<BITS>(sm, blk, f, blk < nblk);
+#pragma unroll
+        for (int j = 0; j + 1 < FK_STAGE_MAXB; ++j) { xv[j] = xv[j + 1]; wl[j] = wl[j + 1]; }
     }
     __syncthreads();
 }
@@ -513,17 +522,21 @@ __device__ __forceinline__ void unit_compute_q(uint32_t ub, const StreamSmem &sm
     acc_hi = fmaf(s11, c[3] * i1, acc_hi); acc_hi = fmaf(b11, X1, acc_hi);
 }
 
-// 4-bit units, digits on the accumulator columns.  The three digits of a group's activations share their k slots, so they can
+// 4- and 8-bit units, digits on the accumulator columns (8 bits: one MMA per 32-activation group, eight per unit instead of 24).  The three digits of a group's activations share their k slots, so they can
 // sit in three columns of ONE B operand: lanes with lane / 4 = 0, 1, 2 load digit 0, 1, 2 of group J (the other lanes load
 // digit 0 again; their columns are never read), and two MMAs per group -- even nibbles, then the odd nibbles shifted down --
 // leave sum(q * digit_c) of rows g, g + 8 in columns 0..2: 16 MMAs per unit instead of 48 and no zeroed operands.  All digits
 // go in as s8 (balanced digits, see store_block).  Column c belongs to lane t = c / 2: t = 0 folds
 // d0 + 128 d1 (< 2^24), t = 1 holds 16384 d2, t = 2, 3 contribute zero through their multipliers; each lane scales its part
 // by the group's power of two and the row's scale and the parts meet in the warp sum over t at the end of the row tile.
-__device__ __forceinline__ void unit_compute_q4c(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
+template <int BITS>
+__device__ __forceinline__ void unit_compute_qc(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t xb = smem_u32(sm.xs) + (uint32_t)sb * (8u * 192u) + (uint32_t)(g < 3 ? g : 0) * 64u + (uint32_t)t * 16u;
+    // staged digits: [group][digit][lane t]{...}; a group is one MMA k extent at 8 bits (32 activations), two at 4 bits (64)
+    constexpr uint32_t GB = BITS == 4 ? 192u : 96u, DB = GB / 3, LB = BITS == 4 ? 16u : 8u;
+    const uint32_t xb = smem_u32(sm.xs) + (uint32_t)sb * (8u * GB) + (uint32_t)(g < 3 ? g : 0) * DB + (uint32_t)t * LB;
     const int mulA = t == 0 ? 1 : (t == 1 ? 16384 : 0), mulB = t == 0 ? 128 : 0;
+    const float fA = (float)mulA, fB = (float)mulB;
     const uint32_t xi = smem_u32(sm.xsi) + (uint32_t)sb * 64u;          // (sum, 1 / scale) of the eight groups
     const uint32_t sv = ub + 4096u - (uint32_t)t * 16u;                 // the scale / bias vectors of rows g, g + 8: lanes (g, 0..3)
     const uint2 s0 = lds64o<0>(sv), s1 = lds64o<16>(sv), s2 = lds64o<32>(sv), s3 = lds64o<48>(sv);
@@ -532,12 +545,19 @@ __device__ __forceinline__ void unit_compute_q4c(uint32_t ub, const StreamSmem &
 #define FK_GC(J, SV, INV, HALF)                                                                                              \
     {                                                                                                                        \
         const uint4 w = lds128o<J * 512>(ub);                                                                                \
-        const uint4 x = lds128o<J * 192>(xb);                                                                                \
         int d[4];                                                                                                            \
-        imma_us0(d, w.x & M, w.z & M, w.y & M, w.w & M, x.x, x.y);                                                           \
-        imma_us(d, (w.x >> 4) & M, (w.z >> 4) & M, (w.y >> 4) & M, (w.w >> 4) & M, x.z, x.w);                                \
+        float flo, fhi;                                                                                                      \
         const float inv = __uint_as_float(INV);                                                                              \
-        const float flo = (float)(d[0] * mulA + d[1] * mulB) * inv, fhi = (float)(d[2] * mulA + d[3] * mulB) * inv;          \
+        if (BITS == 4) {                                                                                                     \
+            const uint4 x = lds128o<J * 192>(xb);                                                                            \
+            imma_us0(d, w.x & M, w.z & M, w.y & M, w.w & M, x.x, x.y);                                                       \
+            imma_us(d, (w.x >> 4) & M, (w.z >> 4) & M, (w.y >> 4) & M, (w.w >> 4) & M, x.z, x.w);                            \
+            flo = (float)(d[0] * mulA + d[1] * mulB) * inv; fhi = (float)(d[2] * mulA + d[3] * mulB) * inv;                  \
+        } else {        /* sums up to 255 * 64 * 32: the top digit's factor is applied in fp32 */                            \
+            const uint2 x = lds64o<J * 96>(xb);                                                                              \
+            imma_us0(d, w.x, w.z, w.y, w.w, x.x, x.y);                                                                       \
+            flo = fmaf((float)d[1], fB, (float)d[0] * fA) * inv; fhi = fmaf((float)d[3], fB, (float)d[2] * fA) * inv;        \
+        }                                                                                                                    \
         acc_lo = fmaf(HALF ? bf_hi(SV.x) : bf_lo(SV.x), flo, acc_lo);                                                        \
         acc_hi = fmaf(HALF ? bf_hi(SV.y) : bf_lo(SV.y), fhi, acc_hi);                                                        \
     }
@@ -555,7 +575,7 @@ __device__ __forceinline__ void unit_compute_q4c(uint32_t ub, const StreamSmem &
 template <int BITS>
 __device__ __forceinline__ void unit_compute(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     if constexpr (BITS == 16) unit_compute_bf16(ub, sm, sb, lane, acc_lo, acc_hi);
-    else if constexpr (BITS == 4 && FK_COLDIGITS) unit_compute_q4c(ub, sm, sb, lane, acc_lo, acc_hi);
+    else if constexpr (FK_COLDIGITS) unit_compute_qc<BITS>(ub, sm, sb, lane, acc_lo, acc_hi);
     else unit_compute_q<BITS>(ub, sm, sb, lane, acc_lo, acc_hi);
 }
 
