@@ -213,3 +213,93 @@ def read(path) -> dict:
     import json
     with open(path) as f:
         return json.load(f)
+
+
+# ------------------------------------------------------------------ lowering a graph the reference wrote
+# A task_graph.json written by the reference for a real model names Metal kernels with a fusion-id suffix
+# (`fusekit_rmsnorm_qkv_f12`) and carries no shapes: they are constants of the generated shader source.  The per-token list
+# it replays has a fixed family order (src/codegen/task_graph_json.rs:1619-1664; python/fusekit_runtime/dispatch.py:3163-3611):
+# step_init, embed, per layer [rmsnorm_qkv, sdpa_decode, linear_residual (o_proj), chain (norm -> gate, up -> activation),
+# linear_residual (down_proj)], final head, argmax scan / finalize, optional history capture.  Lowering = check that order,
+# take the shapes from the model's config.json (checkpoint.spec_from_config), emit this build's graph for them, and say which
+# of the reference's parameter roles feed each role of the lowered graph (q|k|v rows concatenated, gate/up paired).
+_REF_FAMILIES = ("step_init", "embed_lookup_decode", "rmsnorm_qkv", "sdpa_decode", "linear_residual", "chain", "final_rmsnorm_lm_head",
+                 "argmax_logits_scan", "argmax_logits_finalize", "history_capture")
+_REF_SKIP = ("step_init", "argmax_logits_scan", "argmax_logits_finalize", "history_capture")     # fused into neighbours here
+
+
+def reference_family(kernel: str) -> str:
+    """`fusekit_<family>[_f<id>][_partial|_combine]` -> family; raises on a kernel this build has no lowering for."""
+    import re
+    m = re.fullmatch(r"fusekit_([a-z0-9_]+?)(?:_f\d+)?(?:_(?:partial|combine))?", kernel)
+    name = m.group(1) if m else ""
+    if name not in _REF_FAMILIES:
+        raise ValueError(f"no lowering for reference kernel {kernel!r}")
+    return name
+
+
+def lower_reference(doc: dict, spec: ModelSpec, capacity: int, **emit_kw) -> tuple[dict, dict]:
+    """Lower a task graph written by the reference (Qwen-shaped default decode list) to this build's graph for `spec`.
+
+    Returns (graph, sources): `graph` is emit(spec, capacity, ...); `sources[role]` lists, in row order, the reference's
+    parameter roles (`layer_param.<i>.self_attn.q_proj` ...) whose `weight` / `scales` / `biases` tensors make up that role of
+    the lowered graph.  Raises ValueError when the document is not a dispatchable v2 batch-1 graph, when its per-layer kernel
+    order is not the one listed above, or when a projection the lowered graph needs is bound nowhere in the layer."""
+    if doc.get("version") != VERSION or doc.get("active_m", 1) != 1:
+        raise ValueError("reference graph: version 2 and active_m 1 expected")
+    if not doc.get("decode_capabilities", {}).get("dispatchable", False):
+        raise ValueError("reference graph is not dispatchable")
+    if spec.arch != "qwen2":
+        raise ValueError("the lowering covers the Qwen-shaped default dispatch list")
+    by_id = {t["id"]: t for t in doc["tasks"]}
+    per_layer: dict[int, list] = {}
+    head_seen = embed_seen = False
+    for tid in doc["decode_pipeline"]:
+        t = by_id[tid]
+        fam = reference_family(t["kernel"])
+        if fam in _REF_SKIP:
+            continue
+        if fam == "embed_lookup_decode":
+            embed_seen = True
+        elif fam == "final_rmsnorm_lm_head":
+            head_seen = True
+        else:
+            if "layer_idx" not in t:
+                raise ValueError(f"reference task {tid} ({t['kernel']}) carries no layer_idx")
+            fams = per_layer.setdefault(int(t["layer_idx"]), [])
+            if not (fam == "sdpa_decode" and fams and fams[-1][0] == "sdpa_decode"):      # partial + combine count once
+                fams.append((fam, t))
+    if not embed_seen or not head_seen:
+        raise ValueError("reference graph lacks the embed lookup or the final head")
+    if sorted(per_layer) != list(range(spec.n_layers)):
+        raise ValueError(f"reference graph has layers {sorted(per_layer)[:3]}..., the model {spec.n_layers}")
+    want = ["rmsnorm_qkv", "sdpa_decode", "linear_residual", "chain", "linear_residual"]
+    sources: dict[str, list] = {"param.embed_tokens": ["param.embed_tokens"], "param.final_norm": ["param.final_norm"], "param.lm_head": ["param.lm_head"]}
+    for l in range(spec.n_layers):
+        got = [f for f, _ in per_layer[l]]
+        if got != want:
+            raise ValueError(f"layer {l}: kernel order {got}, expected {want}")
+        bound = set()
+        for _, t in per_layer[l]:
+            for b in list(t.get("extra_bindings", [])) + [{"role": x.get("role_name", "")} for x in t.get("inputs", [])]:
+                r = b.get("role", "")
+                if r.startswith(f"layer_param.{l}."):
+                    rel = r[len(f"layer_param.{l}."):]
+                    for suffix in (".weight", ".scales", ".biases", ".bias"):
+                        if rel.endswith(suffix):
+                            rel = rel[: -len(suffix)]
+                            break
+                    bound.add(rel)
+        need = ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj", "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj"]
+        missing = [n for n in need if n not in bound]
+        if missing:
+            raise ValueError(f"layer {l}: the reference graph binds no {missing}")
+        lp = f"layer_param.{l}."
+        sources[lp + "self_attn.qkv_proj"] = [lp + "self_attn.q_proj", lp + "self_attn.k_proj", lp + "self_attn.v_proj"]
+        sources[lp + "self_attn.qkv_proj.bias"] = [lp + "self_attn.q_proj.bias", lp + "self_attn.k_proj.bias", lp + "self_attn.v_proj.bias"]
+        sources[lp + "self_attn.o_proj"] = [lp + "self_attn.o_proj"]
+        sources[lp + "mlp.gate_up_proj"] = [lp + "mlp.gate_proj", lp + "mlp.up_proj"]
+        sources[lp + "mlp.down_proj"] = [lp + "mlp.down_proj"]
+        sources[lp + "input_layernorm.weight"] = [lp + "input_layernorm.weight"]
+        sources[lp + "post_attention_layernorm.weight"] = [lp + "post_attention_layernorm.weight"]
+    return emit(spec, capacity, **emit_kw), sources

@@ -190,3 +190,64 @@ def test_attention_fused_into_the_qkv_task():
     e = _fake_engine(spec)
     e.fuse_attention, e.attend_scratch = True, 0x600000
     assert _records(e.dispatches_from_json(json.dumps(e.task_graph()))) == _records(e.build_dispatches())
+
+
+def _reference_style_graph(spec, split_sdpa=True, drop=None, swap=False):
+    """A document shaped like the reference's own output for a Qwen-shaped model: suffixed kernel names, no shapes, one role per
+    tensor, the replay order of task_graph_json.rs:1619-1664."""
+    tasks, fid = [], [0]
+
+    def add(name, layer=None, roles=()):
+        fid[0] += 1
+        t = {"id": len(tasks), "fusion_id": fid[0], "kernel": name if name in ("fusekit_step_init", "fusekit_history_capture") else f"{name}_f{fid[0]}",
+             "grid_threads": [64, 1, 1], "threadgroup": [64, 1, 1], "inputs": [], "outputs": [],
+             "extra_bindings": [{"slot": 3 + i, "role": r} for i, r in enumerate(roles)], "depends_on": [], "trigger_event": len(tasks)}
+        if layer is not None:
+            t["layer_idx"] = layer
+        tasks.append(t)
+
+    add("fusekit_step_init")
+    add("fusekit_embed_lookup_decode", roles=["param.embed_tokens"])
+    for l in range(spec.n_layers):
+        lp = f"layer_param.{l}."
+        qkv = [lp + f"self_attn.{p}_proj.{s}" for p in "qkv" for s in ("weight", "scales", "biases", "bias")] + [lp + "input_layernorm.weight"]
+        fams = [("fusekit_rmsnorm_qkv", qkv), ("fusekit_sdpa_decode", ["layer_cache_k", "layer_cache_v"]),
+                ("fusekit_linear_residual", [lp + "self_attn.o_proj.weight", lp + "self_attn.o_proj.scales", lp + "self_attn.o_proj.biases"]),
+                ("fusekit_chain", [lp + f"mlp.{p}_proj.{s}" for p in ("gate", "up") for s in ("weight", "scales", "biases")] + [lp + "post_attention_layernorm.weight"]),
+                ("fusekit_linear_residual", [lp + f"mlp.down_proj.{s}" for s in ("weight", "scales", "biases")])]
+        if swap and l == 1:
+            fams[2], fams[3] = fams[3], fams[2]
+        for name, roles in fams:
+            if drop and l == 0:
+                roles = [r for r in roles if drop not in r]
+            add(name, l, roles)
+            if name == "fusekit_sdpa_decode" and split_sdpa:            # the runtime's partial / combine split
+                tasks[-1]["kernel"] += "_partial"
+                add(name, l, []); tasks[-1]["kernel"] += "_combine"
+    add("fusekit_final_rmsnorm_lm_head", roles=["param.final_norm", "param.lm_head"])
+    add("fusekit_argmax_logits_scan"); add("fusekit_argmax_logits_finalize")
+    return {"version": 2, "active_m": 1, "tasks": tasks, "events": [], "scratch_buffers": [], "initial_tasks": [0], "model_params": [],
+            "layer_groups": [], "decode_pipeline": list(range(len(tasks))), "decode_capabilities": {"dispatchable": True, "reasons": []}}
+
+
+def test_lowering_of_a_reference_written_graph():
+    """The reference's own dialect (suffixed Metal kernel names, no shapes) lowers to this build's graph once the model shape is
+    known; a wrong family order, a missing projection or an unknown kernel are refused."""
+    spec = CONFIGS["tiny-qwen"]
+    for split in (True, False):
+        g, src = TG.lower_reference(_reference_style_graph(spec, split), spec, 256)
+        assert g == TG.emit(spec, 256)
+        assert src["layer_param.1.self_attn.qkv_proj"] == [f"layer_param.1.self_attn.{p}_proj" for p in "qkv"]
+        assert src["layer_param.0.mlp.gate_up_proj"] == ["layer_param.0.mlp.gate_proj", "layer_param.0.mlp.up_proj"]
+        roles = {b["role"] for t in g["tasks"] for b in t["extra_bindings"] if b["role"].startswith(("param.", "layer_param."))}
+        assert roles <= set(src)               # every parameter role of the lowered graph has its sources named
+    assert TG.reference_family("fusekit_chain_f1234") == "chain" and TG.reference_family("fusekit_sdpa_decode_f7_combine") == "sdpa_decode"
+    with pytest.raises(ValueError, match="kernel order"):
+        TG.lower_reference(_reference_style_graph(spec, swap=True), spec, 256)
+    with pytest.raises(ValueError, match="v_proj"):
+        TG.lower_reference(_reference_style_graph(spec, drop="v_proj"), spec, 256)
+    bad = _reference_style_graph(spec); bad["tasks"][3]["kernel"] = "fusekit_moe_router_f9"
+    with pytest.raises(ValueError, match="no lowering"):
+        TG.lower_reference(bad, spec, 256)
+    with pytest.raises(ValueError, match="layers"):
+        TG.lower_reference(_reference_style_graph(spec), CONFIGS["qwen2.5-0.5b"], 256)
