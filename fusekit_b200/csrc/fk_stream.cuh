@@ -8,19 +8,23 @@
 // shared memory; a warp then needs one conflict-free LDS.128 per group.
 //
 // Arithmetic: integer tensor cores, exact.  The activations of a quantisation group (bf16, 8 significant bits)
-// are scaled by a power of two so the largest lands in [2^20, 2^21), rounded to integers (exact for everything
-// within 2^-13 of the group maximum, +-2^-21 of it below) and split into three 7-bit digits d0, d1 (unsigned) and
-// d2 (signed).  Packed nibbles become bytes four at a time with one AND each: w & 0x0F0F0F0F are the even nibbles,
-// w & 0xF0F0F0F0 the odd ones left in place as 16 q (two ALU ops per eight weights; their MMA chains are shifted back
-// by 4 when the digits are recombined); 8-bit weights are used as stored.  mma.sync.m16n8k32 (u8 x u8/s8, s32
-// accumulate) forms sum(q * digit) exactly; the digit sums are recombined in s32 (4 bit) or fp32 (8 bit).  The tensor pipe is the dot-product
-// unit because unpack + convert + FMA on the CUDA cores costs >2 issue slots per weight, more than an SM has at
-// HBM speed.  The eight groups of a unit go to the eight accumulator columns: a lane holds the digits of the group whose
-// column it feeds (group lane / 4) and zeros for the other seven MMAs, so after a unit every lane owns four (row, group)
-// sums and applies s * c / scale_g + b * sum(x_g) to them.  (Two 8-bit digits -- 16-bit activations with the rounding
-// loss of a group added back times the mean weight code -- ran 6 % faster, 829 against 782 tok/s on the 7B shape, and stayed
-// inside the per-stage tolerance, but the 64-token greedy check of that shape then showed a flip three bf16 ulps wide
-// where this form shows none wider than two: not kept.)
+// are scaled by a power of two so the largest lands in [2^19, 2^20), rounded to integers (exact for everything
+// within 2^-12 of the group maximum, +-2^-20 of it below) and split into three balanced 7-bit digits (all signed,
+// v = d0 + 128 d1 + 16384 d2).  Packed nibbles become bytes four at a time: w & 0x0F0F0F0F are the even nibbles,
+// (w >> 4) & 0x0F0F0F0F the odd ones; 8-bit weights are used as stored.  mma.sync.m16n8k32 (u8 x s8, s32 accumulate)
+// forms sum(q * digit) exactly.  The three digits of a group share their k slots, so they sit in three columns of ONE
+// B operand (lanes with lane / 4 = 0, 1, 2 load digit 0, 1, 2): two MMAs per 4-bit group, one per 8-bit group, no zeroed
+// operands; the lane that owns a column folds its digits exactly, scales by the group's power of two and the row's
+// scale, adds b * sum(x_g), and the parts meet in the warp sum at the end of the row tile.  The tensor pipe is the
+// dot-product unit because unpack + convert + FMA on the CUDA cores costs >2 issue slots per weight, more than an SM has
+// at HBM speed.
+// History of the mapping (7B-shaped q4, tok/s on one B200): fp16 MMA after unpacking 600; groups on the eight columns with
+// zero vectors loaded from shared memory 741 (shared-memory bandwidth bound: 24 four-wavefront loads per unit); the same
+// with each lane loading only its own group's digits and selecting zeros 777 (48 MMAs per unit, tensor pipe 38 %,
+// math_pipe_throttle the top stall); digits on the columns 794 (16 MMAs per unit, memory-bound).  Two 8-bit digits
+// (16-bit activations, the rounding loss of a group added back times the mean weight code) ran 6 % faster than the three-
+// digit form of its day and stayed inside the per-stage tolerance, but its 64-token greedy check showed a flip three bf16
+// ulps wide: not kept.
 //
 // Scheduling: blocks of 16 warps, one per SM (8 warps, two per SM, for weights with many rounds of tiles), each warp with
 // its own ring and mbarriers.  With at least one row tile per warp in the grid a warp owns whole tiles (all of K); otherwise
@@ -45,9 +49,6 @@ __host__ __device__ inline int unit_k(int bits) { return bits == 4 ? 512 : bits 
 #define FK_WAIT_LIMIT (1u << 24)        // bounded mbarrier wait; on expiry the kernel flags an error and leaves
 #ifndef FK_J_UNROLL
 #define FK_J_UNROLL 8                   // unroll factor of the group loop inside a unit (code size against scheduling freedom)
-#endif
-#ifndef FK_COLDIGITS
-#define FK_COLDIGITS 1                  // 4-bit units: the digits of a group on the accumulator columns (0: groups on the columns)
 #endif
 #define FK_STR(x) #x
 #define FK_UNROLL(n) _Pragma(FK_STR(unroll n))
@@ -100,10 +101,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     return false;
 }
 // D[16x8] += A[16x32] * B[32x8], 8-bit operands, s32 accumulators.  B signed for the top digit only.
-__device__ __forceinline__ void imma_uu(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 __device__ __forceinline__ void imma_us(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -193,26 +190,25 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
     constexpr int TPG = BITS == 4 ? 8 : 4;          // threads per group
 #pragma unroll
     for (int o = 1; o < TPG; o <<= 1) { s8 += __shfl_xor_sync(0xffffffffu, s8, o); m8 = fmaxf(m8, __shfl_xor_sync(0xffffffffu, m8, o)); }
-    // scale = 2^(XB - exponent(max)): the largest activation becomes an integer in [2^XB, 2^(XB+1)).  XB = 20 with unsigned low
-    // digits; 19 with balanced digits (4-bit column form), where v + 8256 must stay below 2^21 for the top digit to fit s8
-    constexpr bool BAL = FK_COLDIGITS != 0;
-    constexpr int XB = BAL ? 19 : 20;
+    // scale = 2^(XB - exponent(max)): the largest activation becomes an integer in [2^19, 2^20), so that v + 8256 (the offset of
+    // the balanced digits below) stays under 2^21 and the top digit fits s8
+    constexpr int XB = 19;
     int e = m8 > 0.0f ? (int)((__float_as_uint(m8) >> 23) & 0xffu) - 127 : XB;
     e = e < -100 ? -100 : (e > 100 ? 100 : e);
     const float scale = __uint_as_float((uint32_t)(127 + XB - e) << 23), inv = __uint_as_float((uint32_t)(127 - XB + e) << 23);
     if (!valid) return;
     // three 7-bit digits of the integers: byte 0 of xi, xi >> 7, xi >> 14, gathered four at a time with byte permutes and masked
-    // as a word.  Unsigned form: d0, d1 in [0, 127], d2 signed.  Balanced form: v + 64 + 64 * 128 is split the same way and 64
-    // taken off the two low digits again, so every digit is signed and centred -- the partial sums that different lanes
-    // accumulate (low digits / top digit) then both have random signs instead of one of them growing with K.
+    // as a word.  Balanced: v + 64 + 64 * 128 is split and 64 taken off the two low digits again, so every digit is signed and
+    // centred -- the partial sums that different lanes accumulate (low digits / top digit) then both have random signs.  (With
+    // unsigned low digits the low-digit sums grow with K and the fp32 accumulation noise with them: three times as many
+    // one-ulp flips per stage against the CPU restatement.)
     uint32_t x0[8], x7[8], x14[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { const int v = __float2int_rn(f[i] * scale) + (BAL ? 8256 : 0); x0[i] = (uint32_t)v; x7[i] = (uint32_t)(v >> 7); x14[i] = (uint32_t)(v >> 14); }
+    for (int i = 0; i < 8; ++i) { const int v = __float2int_rn(f[i] * scale) + 8256; x0[i] = (uint32_t)v; x7[i] = (uint32_t)(v >> 7); x14[i] = (uint32_t)(v >> 14); }
     auto bytes4 = [](uint32_t a, uint32_t b, uint32_t c, uint32_t d) {      // byte 0 of a, b, c, d
         return __byte_perm(__byte_perm(a, b, 0x0040u), __byte_perm(c, d, 0x0040u), 0x5410u);
     };
-    auto low7 = [](uint32_t w) {                 // per byte: u = w & 127, or u - 64 as s8 (flip bit 6, copy it into bit 7)
-        if (!BAL) return w & 0x7f7f7f7fu;
+    auto low7 = [](uint32_t w) {                 // per byte: (w & 127) - 64 as s8 (flip bit 6, copy it into bit 7)
         const uint32_t t = (w & 0x7f7f7f7fu) ^ 0x40404040u;
         return t | ((t & 0x40404040u) << 1);
     };
@@ -434,10 +430,6 @@ template <int OFF> __device__ __forceinline__ uint2 lds64o(uint32_t addr) {
     uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF)); return v;
 }
 // first MMA of a chain: the accumulator starts at zero (constant-zero inputs instead of cleared registers)
-__device__ __forceinline__ void imma_uu0(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
 __device__ __forceinline__ void imma_us0(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
@@ -456,72 +448,6 @@ __device__ __forceinline__ void unit_compute_bf16(uint32_t ub, const StreamSmem 
     }
     acc_lo += c[0][0] + c[1][0]; acc_hi += c[0][2] + c[1][2];
 }
-// one group of a 4- or 8-bit unit: rows g (w.x word A, w.y word B) and g + 8 (w.z, w.w) against the group's three digits.
-// `x0`, `x1`, `x2`: the B-operand registers of the digits -- the lane's own digits when the group is the lane's
-// (lane / 4 == J), zeros otherwise, so column J of the accumulators collects group J.
-template <int BITS, int J>
-__device__ __forceinline__ void group_compute(uint32_t ub, const uint4 &x0, const uint4 &x1, const uint4 &x2, int (&cc)[3][4], int (&co)[3][4]) {
-    const uint4 w = lds128o<J * 512>(ub);
-    if (BITS == 4) {
-        // Even MMA: k-slots 4t.. = word A even nibbles, 4t+16.. = word B even nibbles; odd MMA the same with the odd nibbles
-        // left in the high half of each byte (16 q, exact in u8 and in s32).  Digit vectors: {A even, B even, A odd, B odd}.
-        const uint32_t ea = w.x & 0x0F0F0F0Fu, oa = w.x & 0xF0F0F0F0u, ea8 = w.z & 0x0F0F0F0Fu, oa8 = w.z & 0xF0F0F0F0u;
-        const uint32_t eb = w.y & 0x0F0F0F0Fu, ob = w.y & 0xF0F0F0F0u, eb8 = w.w & 0x0F0F0F0Fu, ob8 = w.w & 0xF0F0F0F0u;
-        if (J == 0) {
-            imma_uu0(cc[0], ea, ea8, eb, eb8, x0.x, x0.y); imma_uu0(cc[1], ea, ea8, eb, eb8, x1.x, x1.y); imma_us0(cc[2], ea, ea8, eb, eb8, x2.x, x2.y);
-            imma_uu0(co[0], oa, oa8, ob, ob8, x0.z, x0.w); imma_uu0(co[1], oa, oa8, ob, ob8, x1.z, x1.w); imma_us0(co[2], oa, oa8, ob, ob8, x2.z, x2.w);
-        } else {
-            imma_uu(cc[0], ea, ea8, eb, eb8, x0.x, x0.y); imma_uu(cc[1], ea, ea8, eb, eb8, x1.x, x1.y); imma_us(cc[2], ea, ea8, eb, eb8, x2.x, x2.y);
-            imma_uu(co[0], oa, oa8, ob, ob8, x0.z, x0.w); imma_uu(co[1], oa, oa8, ob, ob8, x1.z, x1.w); imma_us(co[2], oa, oa8, ob, ob8, x2.z, x2.w);
-        }
-    } else {            // digit vectors: {word A, word B} in .x, .y
-        if (J == 0) { imma_uu0(cc[0], w.x, w.z, w.y, w.w, x0.x, x0.y); imma_uu0(cc[1], w.x, w.z, w.y, w.w, x1.x, x1.y); imma_us0(cc[2], w.x, w.z, w.y, w.w, x2.x, x2.y); }
-        else { imma_uu(cc[0], w.x, w.z, w.y, w.w, x0.x, x0.y); imma_uu(cc[1], w.x, w.z, w.y, w.w, x1.x, x1.y); imma_us(cc[2], w.x, w.z, w.y, w.w, x2.x, x2.y); }
-    }
-}
-template <int BITS> __device__ __forceinline__ uint4 sel4(bool p, const uint4 &v) {
-    if (BITS == 4) return make_uint4(p ? v.x : 0u, p ? v.y : 0u, p ? v.z : 0u, p ? v.w : 0u);
-    return make_uint4(p ? v.x : 0u, p ? v.y : 0u, 0u, 0u);
-}
-// `ub`: shared address of this lane's first vector of the unit.  The lane loads the digits of ITS group (group lane / 4 of
-// the super-block) once per unit; for the other seven groups its B registers are zero.  (Loading zeros from shared memory
-// for those, as an earlier form did, cost four wavefronts per load, 24 loads per unit: shared-memory bandwidth, not issue
-// slots, bounded the kernel.  Lanes of neighbouring groups sit 192 (96) bytes apart: no bank conflicts.)
-template <int BITS>
-__device__ __forceinline__ void unit_compute_q(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
-    const int g = lane >> 2, t = lane & 3;
-    // [digit][fragment] MMA chains; at 4 bits the odd nibbles are used in place (bytes 16 q) and accumulate in chains of their own
-    int cc[3][4], co[3][4];
-    constexpr uint32_t GB = BITS == 4 ? 192u : 96u, DB = GB / 3, LB = BITS == 4 ? 16u : 8u;
-    const uint32_t xg = smem_u32(sm.xs) + (uint32_t)(sb * 8 + g) * GB + (uint32_t)t * LB;
-    uint4 x0, x1, x2;
-    if (BITS == 4) { x0 = lds128(xg); x1 = lds128(xg + DB); x2 = lds128(xg + 2 * DB); }
-    else {
-        const uint2 a = lds64(xg), b = lds64(xg + DB), c2 = lds64(xg + 2 * DB);
-        x0 = make_uint4(a.x, a.y, 0u, 0u); x1 = make_uint4(b.x, b.y, 0u, 0u); x2 = make_uint4(c2.x, c2.y, 0u, 0u);
-    }
-#define FK_GROUP(J) group_compute<BITS, J>(ub, sel4<BITS>(g == J, x0), sel4<BITS>(g == J, x1), sel4<BITS>(g == J, x2), cc, co)
-    FK_GROUP(0); FK_GROUP(1); FK_GROUP(2); FK_GROUP(3); FK_GROUP(4); FK_GROUP(5); FK_GROUP(6); FK_GROUP(7);
-#undef FK_GROUP
-    const uint4 sb4 = lds128o<4096>(ub);
-    const float2 xi0 = sm.xsi[sb * 8 + 2 * t], xi1 = sm.xsi[sb * 8 + 2 * t + 1];      // (group sum, 1/scale)
-    const float X0 = xi0.x, X1 = xi1.x, i0 = xi0.y, i1 = xi1.y;
-    const float s00 = bf_lo(sb4.x), s01 = bf_hi(sb4.x), s10 = bf_lo(sb4.y), s11 = bf_hi(sb4.y);
-    const float b00 = bf_lo(sb4.z), b01 = bf_hi(sb4.z), b10 = bf_lo(sb4.w), b11 = bf_hi(sb4.w);
-    float c[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        if (BITS == 4)   // all six chains in s32 (|sum| < 2^31: 15 * 64 * 32 * 2^14 twice), one conversion: the same single rounding as below
-            c[i] = (float)(cc[0][i] + (cc[1][i] << 7) + (cc[2][i] << 14) + (co[0][i] >> 4) + (co[1][i] << 3) + (co[2][i] << 10));
-        else             // digits recombined: (d0 + 128 d1) in s32, + 16384 d2 in fp32 (each part exact)
-            c[i] = fmaf(16384.0f, (float)cc[2][i], (float)(cc[0][i] + (cc[1][i] << 7)));
-    }
-    acc_lo = fmaf(s00, c[0] * i0, acc_lo); acc_lo = fmaf(b00, X0, acc_lo);
-    acc_lo = fmaf(s01, c[1] * i1, acc_lo); acc_lo = fmaf(b01, X1, acc_lo);
-    acc_hi = fmaf(s10, c[2] * i0, acc_hi); acc_hi = fmaf(b10, X0, acc_hi);
-    acc_hi = fmaf(s11, c[3] * i1, acc_hi); acc_hi = fmaf(b11, X1, acc_hi);
-}
-
 // 4- and 8-bit units, digits on the accumulator columns (8 bits: one MMA per 32-activation group, eight per unit instead of 24).  The three digits of a group's activations share their k slots, so they can
 // sit in three columns of ONE B operand: lanes with lane / 4 = 0, 1, 2 load digit 0, 1, 2 of group J (the other lanes load
 // digit 0 again; their columns are never read), and two MMAs per group -- even nibbles, then the odd nibbles shifted down --
@@ -575,8 +501,7 @@ __device__ __forceinline__ void unit_compute_qc(uint32_t ub, const StreamSmem &s
 template <int BITS>
 __device__ __forceinline__ void unit_compute(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     if constexpr (BITS == 16) unit_compute_bf16(ub, sm, sb, lane, acc_lo, acc_hi);
-    else if constexpr (FK_COLDIGITS) unit_compute_qc<BITS>(ub, sm, sb, lane, acc_lo, acc_hi);
-    else unit_compute_q<BITS>(ub, sm, sb, lane, acc_lo, acc_hi);
+    else unit_compute_qc<BITS>(ub, sm, sb, lane, acc_lo, acc_hi);
 }
 
 // ------------------------------------------------------------------ per-warp unit stream
