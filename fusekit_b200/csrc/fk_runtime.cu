@@ -156,7 +156,7 @@ extern "C" fk_status fk_open(int device, fk_handle *out) {
     CU(cudaFuncSetAttribute(k_sdpa_mma<64>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     CU(cudaFuncSetAttribute(k_sdpa_mma<128>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     CU(cudaFuncSetAttribute(k_sdpa_mma<256>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-    CU(big_smem(k_qmm4<false>)); CU(big_smem(k_qmm4<true>)); CU(big_smem(k_qmm_tc<16>)); CU(big_smem(k_qmm_tc<32>));
+    CU(big_smem(k_qmm4<false>)); CU(big_smem(k_qmm4<true>)); CU(big_smem(k_qmm_tc<32>)); CU(big_smem(k_qmm_tc2));
     CU(big_smem(k_sdpa_decode)); CU(big_smem(k_sdpa_decode_q<4>)); CU(big_smem(k_sdpa_decode_q<8>)); CU(big_smem(k_sdpa_cluster<64, 8>)); CU(big_smem(k_sdpa_cluster<128, 8>)); CU(big_smem(k_sdpa_cluster<256, 2>));
     CU(big_smem(k_rmsnorm_qkv<4>)); CU(big_smem(k_rmsnorm_qkv<8>)); CU(big_smem(k_rmsnorm_qkv<16>));
     CU(big_smem(k_linear_residual<4>)); CU(big_smem(k_linear_residual<8>)); CU(big_smem(k_linear_residual<16>));
@@ -658,12 +658,20 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         if (i[2] > 1) {                                    // 2..16 activation rows: the quantised matrix product
             if (!w->tiled || w->bits != 4 || w->rows_kind != FK_ROWS_PLAIN || !b[3] || b[4])
                 return fail(FK_ERR_VALUE, "linear_residual with several rows takes streamed 4-bit weights in plain row order and a T output");
-            if (i[5] == 1 || (i[5] == 0 && c->qmm_tc)) {          // the tcgen05 form (i5: 1 = ask for it, 2 = ask for the mma.sync form)
+            if ((i[5] == 1 || (i[5] == 0 && c->qmm_tc)) && i[2] <= 16) {       // the warp-specialised tcgen05 form (i5: 1 = ask for it, 2 = mma.sync)
+                const int t128 = (w->ntiles + 7) / 8;
+                int kparts = t128 < c->sm_count ? c->sm_count / t128 : 1;
+                if (kparts > w->nsb) kparts = w->nsb;
+                if (kparts < 1) kparts = 1;
+                QmmTc2Args ta{(const uint16_t *)b[0], w->tview(), (const uint16_t *)b[2], (uint16_t *)b[3], c->qmm_scratch, c->qmm_counters, i[2], i[0], i[1], kparts};
+                e = launch(c, k_qmm_tc2, dim3((unsigned)(t128 * kparts)), dim3(FK_TC2_THREADS), qmm_tc2_smem_bytes(), c->state, ta);
+                break;
+            }
+            if (i[5] == 1 || (i[5] == 0 && c->qmm_tc)) {             // 17 .. 32 rows: one CTA per 128 weight rows, all of K
                 if (i[2] > FK_TC_MAXM) return fail(FK_ERR_VALUE, "linear_residual: the tcgen05 form takes at most %d activation rows", FK_TC_MAXM);
                 QmmTcArgs ta{(const uint16_t *)b[0], w->tview(), (const uint16_t *)b[2], (uint16_t *)b[3], i[2], i[0], i[1]};
                 const dim3 tgrid((unsigned)((w->ntiles + 7) / 8)), tblock(FK_TC_THREADS);
-                if (i[2] <= 16) e = launch(c, k_qmm_tc<16>, tgrid, tblock, qmm_tc_smem_bytes(), c->state, ta);
-                else e = launch(c, k_qmm_tc<32>, tgrid, tblock, qmm_tc_smem_bytes(), c->state, ta);
+                e = launch(c, k_qmm_tc<32>, tgrid, tblock, qmm_tc_smem_bytes(), c->state, ta);
                 break;
             }
             if (i[2] > FK_QMM_MAXM) return fail(FK_ERR_VALUE, "linear_residual: at most %d activation rows", FK_QMM_MAXM);

@@ -50,6 +50,9 @@ __host__ __device__ inline int unit_k(int bits) { return bits == 4 ? 512 : bits 
 #ifndef FK_J_UNROLL
 #define FK_J_UNROLL 8                   // unroll factor of the group loop inside a unit (code size against scheduling freedom)
 #endif
+#ifndef FK_ROLLED_UPTO
+#define FK_ROLLED_UPTO 2                // runs of at most this many units per warp take the rolled (small-code) unit arithmetic
+#endif
 #define FK_STR(x) #x
 #define FK_UNROLL(n) _Pragma(FK_STR(unroll n))
 
@@ -498,6 +501,51 @@ __device__ __forceinline__ void unit_compute_qc(uint32_t ub, const StreamSmem &s
     acc_hi = fmaf(bf_lo(own.w), X0, acc_hi); acc_hi = fmaf(bf_hi(own.w), X1, acc_hi);
 }
 
+// The same unit with the group loop rolled (two groups per iteration, addresses computed): a sixth of the code.  A warp whose
+// whole run is one or two units executes the unit code once, cold -- there the instruction fetch of the unrolled form costs
+// more than its address arithmetic saves.
+template <int BITS>
+__device__ __noinline__ float2 unit_compute_qc_rolled(uint32_t ub, uint32_t xs0, uint32_t xi0, int sb, int lane, float acc_lo, float acc_hi) {
+    const int g = lane >> 2, t = lane & 3;
+    constexpr uint32_t GB = BITS == 4 ? 192u : 96u, DB = GB / 3, LB = BITS == 4 ? 16u : 8u;
+    uint32_t xb = xs0 + (uint32_t)sb * (8u * GB) + (uint32_t)(g < 3 ? g : 0) * DB + (uint32_t)t * LB;
+    const int mulA = t == 0 ? 1 : (t == 1 ? 16384 : 0), mulB = t == 0 ? 128 : 0;
+    const float fA = (float)mulA, fB = (float)mulB;
+    uint32_t xi = xi0 + (uint32_t)sb * 64u, sv = ub + 4096u - (uint32_t)t * 16u, wb = ub;
+    constexpr uint32_t M = 0x0F0F0F0Fu;
+    float lo = acc_lo, hi = acc_hi;
+#pragma unroll 1
+    for (int j = 0; j < 4; ++j, xb += 2 * GB, xi += 16, sv += 16, wb += 1024) {
+        const uint2 s2 = lds64(sv);
+        const uint4 iv = lds128(xi);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 w = lds128(wb + h * 512u);
+            int d[4];
+            float flo, fhi;
+            const float inv = __uint_as_float(h ? iv.w : iv.y);
+            if (BITS == 4) {
+                const uint4 x = lds128(xb + h * GB);
+                imma_us0(d, w.x & M, w.z & M, w.y & M, w.w & M, x.x, x.y);
+                imma_us(d, (w.x >> 4) & M, (w.z >> 4) & M, (w.y >> 4) & M, (w.w >> 4) & M, x.z, x.w);
+                flo = (float)(d[0] * mulA + d[1] * mulB) * inv; fhi = (float)(d[2] * mulA + d[3] * mulB) * inv;
+            } else {
+                const uint2 x = lds64(xb + h * GB);
+                imma_us0(d, w.x, w.z, w.y, w.w, x.x, x.y);
+                flo = fmaf((float)d[1], fB, (float)d[0] * fA) * inv; fhi = fmaf((float)d[3], fB, (float)d[2] * fA) * inv;
+            }
+            lo = fmaf(h ? bf_hi(s2.x) : bf_lo(s2.x), flo, lo);
+            hi = fmaf(h ? bf_hi(s2.y) : bf_lo(s2.y), fhi, hi);
+        }
+    }
+    const uint4 own = lds128(ub + 4096u);
+    const uint4 xo = lds128(xi0 + (uint32_t)sb * 64u + (uint32_t)t * 16u);
+    const float X0 = __uint_as_float(xo.x), X1 = __uint_as_float(xo.z);
+    lo = fmaf(bf_lo(own.z), X0, lo); lo = fmaf(bf_hi(own.z), X1, lo);
+    hi = fmaf(bf_lo(own.w), X0, hi); hi = fmaf(bf_hi(own.w), X1, hi);
+    return make_float2(lo, hi);
+}
+
 template <int BITS>
 __device__ __forceinline__ void unit_compute(uint32_t ub, const StreamSmem &sm, int sb, int lane, float &acc_lo, float &acc_hi) {
     if constexpr (BITS == 16) unit_compute_bf16(ub, sm, sb, lane, acc_lo, acc_hi);
@@ -610,7 +658,11 @@ __device__ __forceinline__ bool stream_run(WarpStream &ws, const StreamPlan &p, 
             for (int n = ws.cnt; n > 0; --n, ++sb) {
                 const uint32_t s = (uint32_t)ws.consumed & (FK_STAGES - 1);
                 if (!mbar_wait_a(ws.bar + s * 8u, ((uint32_t)ws.consumed / FK_STAGES) & 1u)) { ok = false; break; }
-                unit_compute<BITS>(ws.ring + s * (uint32_t)FK_UNIT_BYTES + lane_off, sm, sb, lane, acc_lo, acc_hi);
+                if (BITS != 16 && ws.cnt <= FK_ROLLED_UPTO) {
+                    const float2 r2 = unit_compute_qc_rolled<BITS == 16 ? 4 : BITS>(ws.ring + s * (uint32_t)FK_UNIT_BYTES + lane_off, smem_u32(sm.xs), smem_u32(sm.xsi), sb, lane, acc_lo, acc_hi);
+                    acc_lo = r2.x; acc_hi = r2.y;
+                } else
+                    unit_compute<BITS>(ws.ring + s * (uint32_t)FK_UNIT_BYTES + lane_off, sm, sb, lane, acc_lo, acc_hi);
                 __syncwarp();
                 ++ws.consumed;
                 if (ws.valid()) { ws.issue(); if (!ws.valid()) ws.drained(); }      // refill the stage just drained
