@@ -1,7 +1,7 @@
 """Whole-model parity on the configurations that are benchmarked: the CPU oracle is walked along the GPU's greedy token
 stream (reference: scripts/check_correctness.py:28-172 compares argmax, top-5 and max/mean logit differences between the
 fused path and plain mlx-lm), hidden states are checked per layer on identical layer inputs, and the measured worst
-values are appended to gpurun_out/parity_measured.jsonl when that folder exists."""
+values are printed and, when FK_RESULTS_DIR names a folder, appended to parity_measured.jsonl there."""
 import dataclasses
 import json
 import os
@@ -20,8 +20,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def record(**kw):
-    d = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(d):
+    d = os.environ.get("FK_RESULTS_DIR", "")
+    if d and os.path.isdir(d):
         with open(os.path.join(d, "parity_measured.jsonl"), "a") as f:
             f.write(json.dumps(kw) + "\n")
     print("parity:", kw)
