@@ -251,3 +251,31 @@ def test_lowering_of_a_reference_written_graph():
         TG.lower_reference(bad, spec, 256)
     with pytest.raises(ValueError, match="layers"):
         TG.lower_reference(_reference_style_graph(spec), CONFIGS["qwen2.5-0.5b"], 256)
+
+
+def test_library_json_reader_tolerates_formatting_and_rejects_garbage():
+    """Whitespace, escapes in strings, unknown extra keys, exponents in numbers: accepted.  Truncated text, wrong value types, deep
+    nesting: refused with FK_ERR_VALUE, never a crash."""
+    import ctypes as C
+    from fusekit_b200 import _native as N
+    e = _fake_engine(CONFIGS["tiny-qwen"])
+    g = e.task_graph()
+    table = e.role_table(g)
+    want = _records(e.dispatches_from(g))
+    noisy = json.loads(json.dumps(g))
+    noisy['comment "quoted" \n'] = {"nested": [1, 2.5e0, -3, True, None, "\u00e9\t"]}
+    noisy["tasks"][0]["fargs"] = [float(x) for x in noisy["tasks"][0]["fargs"]]
+    text = json.dumps(noisy, indent=1).replace("\n", "\r\n\t ")
+    assert _records(e.dispatches_from_json(text, table)) == want
+    L = N.lib()
+    arr = (N.RoleBinding * len(table))(*[N.RoleBinding(r.encode(), int(v)) for r, v in table])
+    n = C.c_int32()
+    full = json.dumps(g)
+    for bad in (full[: len(full) // 2], "[]", "null", "{" * 200 + "}" * 200, full.replace('"decode_pipeline": [', '"decode_pipeline": {', 1),
+                full.replace('"version": 2', '"version": "2"', 1), ""):
+        st = L.fk_tasks_from_json(bad.encode(), arr, len(table), None, 0, C.byref(n))
+        assert st == -1, (st, bad[:40])
+    assert L.fk_tasks_from_json(None, arr, len(table), None, 0, C.byref(n)) == -1
+    # a too small output array is refused, the count is still reported
+    out = (N.Task * 1)()
+    assert L.fk_tasks_from_json(full.encode(), arr, len(table), out, 1, C.byref(n)) == -1 and n.value == len(g["tasks"])
