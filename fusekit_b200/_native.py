@@ -74,6 +74,7 @@ def lib():
         "fk_peer_arena_loopback": [u64, i32, i32, u32], "fk_peer_arena_close": [u64],
         "fk_graph_capture": [u64, P(Task), i32, P(u64)],
         "fk_comm_check": [u64],
+        "fk_weight_plan": [u64, u64, P(i32), P(i32), P(i32)],
         "fk_tasks_from_json": [C.c_char_p, P(RoleBinding), i32, P(Task), i32, P(i32)],
         "fk_graph_capture_json": [u64, C.c_char_p, P(RoleBinding), i32, P(u64)], "fk_graph_launch": [u64, u64, P(C.c_double)],
         "fk_graph_launch_async": [u64, u64], "fk_wait": [u64, P(C.c_double)],

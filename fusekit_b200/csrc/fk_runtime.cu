@@ -683,7 +683,11 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
         LinArgs a{(const uint16_t *)b[0], w->view(), (const uint16_t *)b[2], (uint16_t *)b[3], (float *)b[4], i[0], i[1]};
         if (w->tiled) {
             if (w->rows_kind != FK_ROWS_PLAIN) return fail(FK_ERR_VALUE, "linear_residual takes plain row order");
-            SLinArgs sa{a.x, StreamPlan(), a.residual, a.y, a.y_f32, i[0], i[1], PeerXchg()};
+            SLinArgs sa{a.x, StreamPlan(), a.residual, a.y, a.y_f32, i[0], i[1], PeerXchg(), nullptr, nullptr};
+            if (b[5]) {           // the activations once more as digits (written by the gate/up task): digits, then the (sum, 1 / scale) pairs
+                if (w->bits == 16 || (b[5] & 15) || i[0] % 64) return fail(FK_ERR_VALUE, "linear_residual: staged digits need 4/8-bit weights, K a multiple of 64 and a 16-byte aligned buffer");
+                sa.xdig = (const uint4 *)b[5]; sa.xdig_xsi = (const uint2 *)(b[5] + (((uint64_t)i[0] * 3 + 15) & ~(uint64_t)15));
+            }
             { fk_status xs = make_xchg(c, i[3], &sa.push, "linear_residual"); if (xs) return xs; }
             if (sa.push.site >= 0 && i[1] * 8 > FK_PEER_SLOT_BYTES) return fail(FK_ERR_VALUE, "linear_residual: a pushed exchange needs N <= %d", FK_PEER_SLOT_BYTES / 8);
             const Shape sh = make_plan(c, w, &sa.P, nextw);
@@ -708,12 +712,18 @@ static fk_status run_task(Ctx *c, const fk_task &t, const Weight *nextw = nullpt
                 break;
             }
             SGateUpArgs sa{(const uint16_t *)b[0], (const uint16_t *)b[1], StreamPlan(), (uint16_t *)b[4],
-                           (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0], nullptr, PeerXchg()};
+                           (const uint16_t *)b[9], (const uint16_t *)b[10], (uint16_t *)b[11], i[0], i[1], i[2], f[0], nullptr, PeerXchg(), nullptr, nullptr};
             { fk_status xs = make_xchg(c, i[4], &sa.pull, "gateup"); if (xs) return xs; }
             if (sa.pull.site >= 0 && (b[9] || b[10] || i[0] * 8 > FK_PEER_SLOT_BYTES)) return fail(FK_ERR_VALUE, "gateup: a pulled exchange excludes pending inputs and needs H <= %d", FK_PEER_SLOT_BYTES / 8);
             if (b[9] && !b[10]) { sa.pending = nullptr; sa.pend_sum = (const float *)b[9]; }
             if (i[0] > 8 * 256 * FK_STAGE_MAXB) return fail(FK_ERR_VALUE, "gateup: hidden size above %d", 8 * 256 * FK_STAGE_MAXB);
             const Shape sh = make_plan(c, wg, &sa.P, nextw);
+            if (b[5]) {           // also leave the activations as digits for the next projection (buf5: 3 bytes per activation, then 8 per group)
+                const int rounds = (wg->ntiles + sh.grid * sh.warps - 1) / (sh.grid * sh.warps);
+                if (wg->bits == 16 || sh.lsplit != 0 || i[1] % 64 || (b[5] & 15) || rounds * sh.warps * 8 > 2 * FK_STREAM_MAXWARPS * 16 * 2)
+                    return fail(FK_ERR_VALUE, "gateup: digits for the next projection need 4/8-bit weights, whole tiles per warp (fk_weight_plan), I a multiple of 64 and at most %d outputs per block", 2 * FK_STREAM_MAXWARPS * 16 * 2);
+                sa.dig_out = (uint32_t *)b[5]; sa.dig_xsi = (float2 *)(b[5] + (((uint64_t)i[1] * 3 + 15) & ~(uint64_t)15));
+            }
             STREAM_LAUNCH_P(k_s_gateup, (sa.pending || sa.pend_sum || sa.pull.site >= 0), wg, sh, c->state, sa);
             break;
         }
@@ -940,6 +950,14 @@ static fk_status stream_wait(Ctx *c) {
         if (spins > 2000) std::this_thread::sleep_for(std::chrono::microseconds(50));
     }
     return comm_check(c);          // an error raised while the last kernels drained
+}
+// the launch shape the runtime will use for a streamed weight: blocks, warps per block, log2 of the warps sharing a row tile
+extern "C" fk_status fk_weight_plan(fk_handle h, fk_weight wid, int *grid, int *warps, int *lsplit) {
+    CTX(h); Weight *w = get_w(c, wid);
+    if (!w || !w->finalized || !w->tiled) return fail(FK_ERR_VALUE, "fk_weight_plan: a finalized weight in the streaming layout is needed");
+    const Shape sh = plan_shape(c, w);
+    if (grid) *grid = sh.grid; if (warps) *warps = sh.warps; if (lsplit) *lsplit = sh.lsplit;
+    return FK_OK;
 }
 extern "C" fk_status fk_comm_check(fk_handle h) { CTX(h); if (c->comm_lost) return fail(FK_ERR_STATE, "the communicator was aborted after an error"); return comm_check(c); }
 

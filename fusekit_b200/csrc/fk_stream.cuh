@@ -177,11 +177,13 @@ __device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
     return (uint32_t)(a & 255) | ((uint32_t)(b & 255) << 8) | ((uint32_t)(c & 255) << 16) | ((uint32_t)(d & 255) << 24);
 }
+// `xsw` / `xsi`: where the digits and the (sum, 1 / scale) pairs go -- the kernel's shared memory, or a global buffer of the
+// same layout that a later kernel copies in (the gate/up kernel prepares down_proj's activations that way).
 template <int BITS>
-__device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const float (&f)[8], bool valid) {
+__device__ __forceinline__ void store_block_to(uint32_t *xsw, float2 *xsi, int blk, const float (&f)[8], bool valid) {
     if (BITS == 16) {       // bf16 weights: the activations are bf16 already; lane t of k16 step s reads {x[2t], x[2t+1]} and {x[2t+8], x[2t+9]}
         if (!valid) return;
-        uint32_t *dst = reinterpret_cast<uint32_t *>(sm.xs) + (size_t)(blk >> 1) * 8 + (blk & 1);
+        uint32_t *dst = xsw + (size_t)(blk >> 1) * 8 + (blk & 1);
 #pragma unroll
         for (int t = 0; t < 4; ++t) dst[2 * t] = (uint32_t)f2bf(f[2 * t]) | ((uint32_t)f2bf(f[2 * t + 1]) << 16);
         return;
@@ -219,22 +221,26 @@ __device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const
         const int grp = blk >> 3, bb = blk & 7;
         // [digit][lane t = bb & 3]{word A even, word B even, word A odd, word B odd}: the even nibbles of both words feed one MMA,
         // the odd nibbles the other
-        uint32_t *dst = reinterpret_cast<uint32_t *>(sm.xs) + (size_t)grp * 48 + (bb & 3) * 4 + (bb >> 2);
+        uint32_t *dst = xsw + (size_t)grp * 48 + (bb & 3) * 4 + (bb >> 2);
         dst[0] = low7(bytes4(x0[0], x0[2], x0[4], x0[6])); dst[2] = low7(bytes4(x0[1], x0[3], x0[5], x0[7]));
         dst[16] = low7(bytes4(x7[0], x7[2], x7[4], x7[6])); dst[18] = low7(bytes4(x7[1], x7[3], x7[5], x7[7]));
         dst[32] = bytes4(x14[0], x14[2], x14[4], x14[6]); dst[34] = bytes4(x14[1], x14[3], x14[5], x14[7]);
-        if (bb == 0) sm.xsi[grp] = make_float2(s8, inv);
+        if (bb == 0) xsi[grp] = make_float2(s8, inv);
     } else {
         const int k0 = blk * 8, grp = k0 >> 5, o = k0 & 31, half = o >> 4, t = (o >> 2) & 3;
-        uint32_t *dst = reinterpret_cast<uint32_t *>(sm.xs) + (size_t)grp * 24 + t * 2 + half;   // [digit][lane][A|B] as words
+        uint32_t *dst = xsw + (size_t)grp * 24 + t * 2 + half;   // [digit][lane][A|B] as words
 #pragma unroll
         for (int q = 0; q < 2; ++q) {                    // the two 4-blocks of this thread: lanes t and t+1
             dst[2 * q] = low7(bytes4(x0[4 * q], x0[4 * q + 1], x0[4 * q + 2], x0[4 * q + 3]));
             dst[8 + 2 * q] = low7(bytes4(x7[4 * q], x7[4 * q + 1], x7[4 * q + 2], x7[4 * q + 3]));
             dst[16 + 2 * q] = bytes4(x14[4 * q], x14[4 * q + 1], x14[4 * q + 2], x14[4 * q + 3]);
         }
-        if ((blk & 3) == 0) sm.xsi[blk >> 2] = make_float2(s8, inv);
+        if ((blk & 3) == 0) xsi[blk >> 2] = make_float2(s8, inv);
     }
+}
+template <int BITS>
+__device__ __forceinline__ void store_block(const StreamSmem &sm, int blk, const float (&f)[8], bool valid) {
+    store_block_to<BITS>(reinterpret_cast<uint32_t *>(sm.xs), sm.xsi, blk, f, valid);
 }
 // zero vectors, padded tail of xs / xsum (k rounded up to whole units)
 template <int BITS>
@@ -791,7 +797,23 @@ __global__ void k_dequant_tiled(TiledW W, int which, long long row0, long long n
 
 // ================================================================ streamed kernels
 
-struct SLinArgs { const uint16_t *x; StreamPlan P; const uint16_t *residual; uint16_t *y; float *y_f32; int k, n; PeerXchg push; };
+struct SLinArgs { const uint16_t *x; StreamPlan P; const uint16_t *residual; uint16_t *y; float *y_f32; int k, n; PeerXchg push;
+                  const uint4 *xdig; const uint2 *xdig_xsi; };       // x once more, already as digits + (sum, 1 / scale) pairs (see SGateUpArgs)
+// staging by copy: the digits of all k activations (3 bytes each) and the per-group pairs, prepared by the producing kernel
+template <int BITS>
+__device__ __forceinline__ void stage_copy(const StreamSmem &sm, const uint4 *dig, const uint2 *xsi, int k) {
+    const int n16 = (k * 3) >> 4, np = k / (BITS == 4 ? 64 : 32);              // 16-byte vectors of digits; (sum, inv) pairs
+    uint4 *xs = reinterpret_cast<uint4 *>(sm.xs); uint2 *xp = reinterpret_cast<uint2 *>(sm.xsi);
+    for (int i0 = 0; i0 < n16; i0 += 8 * (int)blockDim.x) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { const int i = i0 + u * (int)blockDim.x + (int)threadIdx.x; v[u] = i < n16 ? __ldcg(dig + i) : make_uint4(0, 0, 0, 0); }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { const int i = i0 + u * (int)blockDim.x + (int)threadIdx.x; if (i < n16) xs[i] = v[u]; }
+    }
+    for (int i = threadIdx.x; i < np; i += blockDim.x) xp[i] = __ldcg(xsi + i);
+    __syncthreads();
+}
 // Epilogues are functors: prefetch(tile, g) is called once per lane (lanes with (lane & 3) == 0) for the first tile the
 // lane will finish, before the streaming loop; operator() gets the finished sums of tile rows g and g + 8.
 
@@ -826,7 +848,9 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_linear(FkState *st
     stage_pad<BITS>(sm, a.k, a.P.W.nsb);
     pdl_wait();
     stamp(a.P, 1);
-    stage_plain<BITS, (WARPS == 16 ? 5 : 2)>(sm, a.x, a.k, a.P.W.nsb);
+    bool copied = false;
+    if constexpr (BITS != 16) if (a.xdig) { stage_copy<BITS>(sm, a.xdig, a.xdig_xsi, a.k); copied = true; }
+    if (!copied) stage_plain<BITS, (WARPS == 16 ? 5 : 2)>(sm, a.x, a.k, a.P.W.nsb);
     stamp(a.P, 2);
     EpiLinear epi(a, st->epoch + 1u);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x100u);
@@ -920,6 +944,10 @@ struct SGateUpArgs {
     const uint16_t *x, *norm_w; StreamPlan P; uint16_t *act_out;
     const uint16_t *pending, *pending_w; uint16_t *h_out;
     int h, inter, act; float eps; const float *pend_sum; PeerXchg pull;
+    // optional: the activation vector again as the integer digits the next projection (down_proj, same bit width) stages --
+    // [groups][digits] in the shared-memory layout of store_block, then the (sum, 1 / scale) pairs -- so that its 112+ blocks
+    // copy 3 bytes per activation instead of each converting all of them (2.9 us of staging per layer on the 7B shape)
+    uint32_t *dig_out; float2 *dig_xsi;
 };
 __device__ __forceinline__ uint16_t s_act_swiglu(float ga, float ua) {
     const float g = rT(ga), u = rT(ua);
@@ -936,14 +964,33 @@ __device__ __forceinline__ uint16_t s_act_geglu(float ga, float ua) {
 // RMSNorm -> gate & up -> activation tail in registers (src/codegen/kernels/fused_chain.rs:2902-3552; msl.rs:1286-1294).
 // The paired weight interleaves 8 gate rows with the 8 matching up rows per tile, so a lane holds both.
 struct EpiGateUp {
-    const SGateUpArgs &a;
-    __device__ __forceinline__ EpiGateUp(const SGateUpArgs &a_) : a(a_) {}
+    const SGateUpArgs &a; uint16_t *stash;       // stash: the block's own outputs, [round][warp][8], for the digit pass (or null)
+    __device__ __forceinline__ EpiGateUp(const SGateUpArgs &a_, uint16_t *stash_) : a(a_), stash(stash_) {}
     __device__ __forceinline__ void prefetch(int, int) {}
     __device__ __forceinline__ void operator()(int tile, int g, float gate, float up) {
         const int r = tile * 8 + g;
-        if (r < a.inter) a.act_out[r] = a.act == 1 ? s_act_geglu(gate, up) : s_act_swiglu(gate, up);
+        const uint16_t v = a.act == 1 ? s_act_geglu(gate, up) : s_act_swiglu(gate, up);
+        if (r < a.inter) a.act_out[r] = v;
+        if (stash) {                              // whole tiles per warp (no K split): tile = (round * grid + block) * warps + warp
+            const int nw = (int)blockDim.x >> 5, lt = tile - (int)blockIdx.x * nw, span = (int)gridDim.x * nw, round = lt / span;
+            stash[(round * nw + (lt - round * span)) * 8 + g] = r < a.inter ? v : (uint16_t)0;
+        }
     }
 };
+// after the last round: the stashed outputs of this block, eight (one tile) per thread, as digits in global memory
+template <int BITS>
+__device__ __forceinline__ void gateup_digits(const SGateUpArgs &a, const uint16_t *stash) {
+    const int nw = (int)blockDim.x >> 5, ntiles = a.P.W.ntiles, span = (int)gridDim.x * nw, first = (int)blockIdx.x * nw;
+    const int rounds = first < ntiles ? (ntiles - first + span - 1) / span : 0, total = rounds * nw;
+    for (int i0 = 0; i0 < total; i0 += (int)blockDim.x) {          // warp-uniform trip count: store_block_to shuffles across the warp
+        const int i = i0 + (int)threadIdx.x, round = i / nw, tile = (round * (int)gridDim.x + (int)blockIdx.x) * nw + (i - round * nw);
+        const bool valid = i < total && tile < ntiles && tile * 8 < a.inter;
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = valid ? bf2f(stash[i * 8 + j]) : 0.0f;
+        store_block_to<BITS>(a.dig_out, a.dig_xsi, valid ? tile : 0, f, valid);
+    }
+}
 template <int BITS, int WARPS, bool PEND = false>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st, SGateUpArgs a) {
     extern __shared__ __align__(128) unsigned char smem_stream[];
@@ -951,15 +998,19 @@ __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_s_gateup(FkState *st
     stamp(a.P, 0);
     WarpStream ws; stream_begin(ws, a.P, sm);
     stage_pad<BITS>(sm, a.h, a.P.W.nsb);
+    if (BITS != 16 && a.dig_out) for (int i = threadIdx.x; i < 2 * FK_STREAM_MAXWARPS * 16; i += blockDim.x) sm.fold[i] = 0.0f;
     NormW nwv; norm_w_load(nwv, a.norm_w, a.h);
     pdl_wait();
     stamp(a.P, 1);
     stage_rmsnorm<BITS, PEND>(sm, a.x, nwv, a.h, a.P.W.nsb, a.eps, a.pending, a.pending_w, a.h_out, a.P.timeline, a.pend_sum, &a.pull, st);
     stamp(a.P, 2);
-    EpiGateUp epi(a);
+    uint16_t *stash = (BITS != 16 && a.dig_out) ? reinterpret_cast<uint16_t *>(sm.fold) : nullptr;     // the fold buffer is idle without a K split
+    EpiGateUp epi(a, stash);
     if (!stream_run<BITS>(ws, a.P, sm, epi)) atomicOr(&st->error, 0x400u);
     pdl_launch_dependents();
-    __syncthreads(); stamp(a.P, 3);
+    __syncthreads();
+    if constexpr (BITS != 16) if (stash) gateup_digits<BITS>(a, stash);
+    stamp(a.P, 3);
 }
 
 struct SHeadArgs {

@@ -220,6 +220,7 @@ class DecodeEngine:
         self.v_buf = rt.alloc(self.nkv * s.head_dim * 2)
         self.sdpa_buf = rt.alloc(self.nq * s.head_dim * 2)
         self.act_buf = rt.alloc(self.inter * 2)
+        self.act_digits = rt.alloc(self.inter * 3 + 16 + (self.inter // 32 + 1) * 8)      # the same vector as staged digits + per-group pairs
         self.o_buf = rt.alloc(H * 2)                  # Gemma: o_proj output before its post-norm
         self.d_buf = rt.alloc(L * H * 2)              # Gemma: down_proj output before its post-norm
         self.part_f32 = rt.alloc(H * 4)               # tensor-parallel partial sums (o_proj)
@@ -363,7 +364,32 @@ class DecodeEngine:
         """This engine's decode step as a v2 ``task_graph.json`` document (see task_graph.emit)."""
         return task_graph.emit(self.spec, self.capacity, self.rank, self.world,
                                fused_weights=self.rt.tiled, want_logits=self.want_logits, embed_bits=getattr(self, "embed_bits", 16), tp_exchange=getattr(self, "tp_exchange", "allreduce"), kv_bits=getattr(self, "kv_bits", 0),
-                               fuse_attention=getattr(self, "fuse_attention", False))
+                               fuse_attention=getattr(self, "fuse_attention", False), act_digits=self._act_digits())
+
+    def _act_digits(self) -> bool:
+        """Whether gate/up can leave down_proj's activations as staged digits: one GPU, Qwen-shaped, 4/8-bit streaming layout, and
+        the gate/up weight of every layer launched with whole tiles per warp (asked of the library: fk_weight_plan)."""
+        import os
+        s = self.spec
+        if getattr(self, "_act_digits_ok", None) is not None:
+            return self._act_digits_ok
+        if not getattr(self, "W", None) or "layers.0.gateup" not in self.W:
+            return False                     # asked before the weights exist: no digits, and no verdict cached
+        ok = (s.arch == "qwen2" and getattr(self, "world", 1) == 1 and s.bits in (4, 8) and getattr(self.rt, "tiled", False)
+              and s.inter % 64 == 0 and os.environ.get("FK_ACT_DIGITS", "1") != "0" and hasattr(self.rt, "L") and bool(getattr(self, "act_digits", 0)))
+        if ok:
+            for l in range(s.n_layers):
+                g, w, ls = C.c_int32(), C.c_int32(), C.c_int32()
+                wid = self.W.get(f"layers.{l}.gateup")
+                if not wid or self.rt.L.fk_weight_plan(self.rt.h, wid, C.byref(g), C.byref(w), C.byref(ls)) != 0 or ls.value != 0:
+                    ok = False
+                    break
+                tiles = (2 * s.inter + 15) // 16
+                if -(-tiles // (g.value * w.value)) * w.value * 8 > 1024:
+                    ok = False
+                    break
+        self._act_digits_ok = ok
+        return ok
 
     def _resolve(self, role: str) -> int:
         """Device address (or fk_weight id) behind one role string of the task graph."""
@@ -393,7 +419,7 @@ class DecodeEngine:
             if p[1].isdigit():
                 return {"h_attn": self.hb_ptr, "out_buf": self.d_ptr}[p[2]](int(p[1]))
             return {"q_buf": self.q_buf, "k_buf": self.k_buf, "v_buf": self.v_buf, "sdpa_buf": self.sdpa_buf, "silu_up": self.act_buf,
-                    "o_buf": self.o_buf}[p[1]]
+                    "o_buf": self.o_buf, "silu_up_digits": getattr(self, "act_digits", 0)}[p[1]]
         raise KeyError(f"unknown task-graph role {role!r}")
 
     def dispatches_from(self, graph: dict) -> list:

@@ -32,7 +32,7 @@ def _bf16_round(v: float) -> float:
 
 def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fused_weights: bool = True,
          want_logits: bool = False, embed_bits: int = 16, tp_exchange: str = "allreduce", kv_bits: int = 0,
-         fuse_attention: bool = False) -> dict:
+         fuse_attention: bool = False, act_digits: bool = False) -> dict:
     """Build the v2 task graph of one decode step for `spec` (one tensor-parallel rank of it).
 
     `fused_weights`: weights in the streaming layout (gate/up paired, residual add after an all-reduce fused into the next
@@ -45,7 +45,9 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
     kv_store_quant task rotates and quantises, sdpa_decode_quant attends the packed cache
     (src/codegen/kernels/rope_kv_cache_store_decode_quant.rs, sdpa_decode_quant.rs).
     `fuse_attention`: Qwen-shaped layers with the streaming layout and a bf16 cache: no sdpa_decode task, the QKV task attends
-    the cache in its tail (iarg 7, slot 7 = attention output, slot 8 = scratch, farg 2 = scale)."""
+    the cache in its tail (iarg 7, slot 7 = attention output, slot 8 = scratch, farg 2 = scale).
+    `act_digits`: one GPU, Qwen-shaped layers, 4/8-bit streaming layout: the gate/up task also leaves its output as the integer
+    digits down_proj stages (slot 5 of both tasks, `layer_scratch.silu_up_digits`), so down_proj copies instead of converting."""
     s, hd, H = spec, spec.head_dim, spec.hidden
     nq, nkv, inter, vocab = s.n_q // tp_size, s.n_kv // tp_size, s.inter // tp_size, s.vocab // tp_size
     tp = tp_size > 1
@@ -115,8 +117,9 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
         ko = nq * hd
         if s.arch == "qwen2" and not tp:
             add(K_LIN, l, {0: "layer_scratch.sdpa_buf", 1: lp(l, "self_attn.o_proj"), 2: x(l), 3: hb(l)}, [ko, H])
-            add(K_GATEUP, l, {0: hb(l), 1: lp(l, "post_attention_layernorm.weight"), **gateup(l), 4: "layer_scratch.silu_up"}, [H, inter, s.act], [s.eps])
-            add(K_LIN, l, {0: "layer_scratch.silu_up", 1: lp(l, "mlp.down_proj"), 2: hb(l), 3: x(l + 1)}, [inter, H])
+            dig = {5: "layer_scratch.silu_up_digits"} if (act_digits and fused and s.bits in (4, 8) and inter % 64 == 0) else {}
+            add(K_GATEUP, l, {0: hb(l), 1: lp(l, "post_attention_layernorm.weight"), **gateup(l), 4: "layer_scratch.silu_up", **dig}, [H, inter, s.act], [s.eps])
+            add(K_LIN, l, {0: "layer_scratch.silu_up", 1: lp(l, "mlp.down_proj"), 2: hb(l), 3: x(l + 1), **dig}, [inter, H])
         elif s.arch == "qwen2" and peer:
             # row-split o/down with the exchange fused in: the projection pushes fp32 partial rows to every rank (site in i3),
             # the next norm-first kernel waits for all ranks, sums in rank order and adds the residual (site in its last iarg)
@@ -160,7 +163,7 @@ def emit(spec: ModelSpec, capacity: int, tp_rank: int = 0, tp_size: int = 1, fus
         add(K_ARGMAX, -1, {4: "global_scratch.argmax_scratch"}, [1])
 
     # ---- v2 envelope: tasks with bindings, a linear event chain, layer groups, the decode pipeline
-    out_slots = {K_EMBED: [1], K_QKV: [4, 5, 6, 7, 8, 11], K_QKNORM: [0, 5, 6], K_SDPA: [3, 4, 5], K_LIN: [3, 4], K_GATEUP: [4, 11],
+    out_slots = {K_EMBED: [1], K_QKV: [4, 5, 6, 7, 8, 11], K_QKNORM: [0, 5, 6], K_SDPA: [3, 4, 5], K_LIN: [3, 4], K_GATEUP: [4, 5, 11],
                  K_HEAD: [3, 4, 5, 11], K_ARGMAX: [], K_ALLREDUCE: [0], K_RESADD: [2], K_KVQ: [0, 3, 4, 5, 6, 7, 8], K_SDPAQ: [3, 4, 5]}
     jtasks, groups = [], {}
     for i, t in enumerate(tasks):

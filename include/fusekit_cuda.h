@@ -92,6 +92,7 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      2 = global partials + ticket, 4 = tensor-core cluster)   f0 scale
  *                      partials: n_q * ceil(capacity / 32) * (head_dim + 2) floats; counter: n_kv words, zero before first use
  * LINEAR_RESIDUAL      buf0 x T[K]  buf1 weight  buf2 residual|0  buf3 y_out T[N]  buf4 y_f32_out|0   i0 K  i1 N
+ *                      buf5 (optional, one row): x as staged digits, written by RMSNORM_GATEUP_ACT buf5 (then buf0 is not read)
  *                      i2 activation rows M (0 or 1: one row).  M = 2..16: x is T[M, K], residual and y_out are T[M, N], row m
  *                      is the result the one-row task gives for x[m] (reference: the fusekit_qmm tiles for M > 1,
  *                      src/codegen/msl.rs:2318-2439, chosen in kernels/mod.rs:1442-1473); streamed 4-bit weights only
@@ -107,6 +108,10 @@ enum { FK_ACT_SWIGLU = 0, FK_ACT_GEGLU_TANH = 1 };
  *                      by its own RMS (buf1 = 0: the rows are normalised already, e.g. by RMSNORM_ROWS, and only the product and
  *                      the activation run); paired 4-bit weights, no pending inputs (reference: fusekit_qmm_t_swiglu_pair_impl, msl.rs:2489)
  *                      i4 pull site + 1 (as RMSNORM_QKV i6)
+ *                      buf5 (optional, one row, 4/8-bit): the activation vector once more as the integer digits the next
+ *                      projection of the same bit width stages -- 3 bytes per activation, then (16-byte aligned) 8 bytes per
+ *                      group of 64 (4-bit) / 32 (8-bit) -- for LINEAR_RESIDUAL buf5; needs whole tiles per warp (fk_weight_plan:
+ *                      lsplit 0) and I a multiple of 64.  No counterpart in the reference (its kernels read T activations).
  * FINAL_RMSNORM_LM_HEAD buf0 x  buf1 norm_w  buf2 weight(head)  buf3 logits_out|0  buf4 argmax scratch(u64)
  *                      buf5 counter(u32)  buf9..11 pending     i0 H  i1 V(local)  i2 vocab_offset  i3 finalize(1/0)   f0 eps
  *                      i4 pull site + 1 (as RMSNORM_QKV i6); i5 argmax site + 1: a vocabulary-sharded head pushes its best key
@@ -280,6 +285,10 @@ fk_status fk_comm_init(fk_handle h, const void *id128, int rank, int world);
  * rank whose peer died returns instead of blocking; FK_COMM_TIMEOUT_MS (environment, off by default) bounds the wait with a
  * collective in flight.  No counterpart in the reference (single device). */
 fk_status fk_comm_check(fk_handle h);
+/* The launch shape the runtime uses for a finalized weight in the streaming layout: blocks, warps per block, and log2 of the
+ * warps that share a row tile (0: a warp owns whole tiles).  Reference analogue: kernel_grid_threads / kernel_threadgroup
+ * (src/codegen/kernels/mod.rs:5648-5700, 6218-7567), which the host also queries before building its dispatch list. */
+fk_status fk_weight_plan(fk_handle h, fk_weight w, int *grid, int *warps, int *lsplit);
 
 #ifdef __cplusplus
 }

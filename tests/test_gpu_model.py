@@ -376,3 +376,27 @@ def test_attention_in_the_qkv_tail_matches_the_attention_kernel(runtime, name, c
     a, b = O.bf16_to_f32(outs[0]), O.bf16_to_f32(outs[1])
     assert rel_rms(outs[1], outs[0]) <= 2e-3 and float(np.abs(a - b).max()) <= 2e-2 * max(1.0, float(np.abs(a).max()))
     assert int((toks[0] != toks[1]).sum()) <= 24        # streams may part at a near-tie; each is checked against the oracle on its own
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,bits", [("tiny-qwen", 4), ("qwen2.5-7b", 4), ("qwen2.5-7b", 8), ("qwen2.5-32b", 4)])
+def test_down_proj_staged_from_digits_written_by_gateup(runtime, monkeypatch, name, bits):
+    """With the activation digits prepared by the gate/up kernel, down_proj stages by copy: the digits are what its own
+    conversion would have produced, so tokens and residual streams are bit-identical to the path that converts."""
+    import dataclasses
+    from fusekit_b200 import _native as N
+    spec = dataclasses.replace(CONFIGS[name].with_bits(bits), name=f"{name}-digits{bits}", n_layers=2, vocab=min(CONFIGS[name].vocab, 16384))
+    outs = []
+    for on in ("1", "0"):
+        monkeypatch.setenv("FK_ACT_DIGITS", on)
+        eng = DecodeEngine(spec, 96, runtime=runtime)
+        eng.load_synthetic(); eng.prefill_kv_synthetic(20)
+        tasks = eng.build_dispatches()
+        wired = any(t.kind == N.TASK_LINEAR_RESIDUAL and t.buf[5] for t in tasks)
+        toks, _ = eng.decode_chunk(20, 7, 16)
+        outs.append((wired, toks.copy(), eng.residual_stream()[-1].copy()))
+        assert eng.rt.state_get()[2] == 0
+    assert outs[1][0] is False
+    if not outs[0][0]:
+        pytest.skip("the gate/up weight of this shape is launched with a K split: no digits wired")
+    assert np.array_equal(outs[0][1], outs[1][1]) and np.array_equal(outs[0][2], outs[1][2])
