@@ -982,8 +982,10 @@ template <int BITS>
 __device__ __forceinline__ void gateup_digits(const SGateUpArgs &a, const uint16_t *stash) {
     const int nw = (int)blockDim.x >> 5, ntiles = a.P.W.ntiles, span = (int)gridDim.x * nw, first = (int)blockIdx.x * nw;
     const int rounds = first < ntiles ? (ntiles - first + span - 1) / span : 0, total = rounds * nw;
-    for (int i0 = 0; i0 < total; i0 += (int)blockDim.x) {          // warp-uniform trip count: store_block_to shuffles across the warp
-        const int i = i0 + (int)threadIdx.x, round = i / nw, tile = (round * (int)gridDim.x + (int)blockIdx.x) * nw + (i - round * nw);
+    // whole warps take 32 tiles at a time (store_block_to shuffles across the warp: every lane of a warp that enters takes part);
+    // warps with nothing to do skip the pass
+    for (int i0 = (int)(threadIdx.x & ~31u); i0 < total; i0 += (int)blockDim.x) {
+        const int i = i0 + (int)(threadIdx.x & 31u), round = i / nw, tile = (round * (int)gridDim.x + (int)blockIdx.x) * nw + (i - round * nw);
         const bool valid = i < total && tile < ntiles && tile * 8 < a.inter;
         float f[8];
 #pragma unroll
